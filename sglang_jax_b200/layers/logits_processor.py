@@ -1,0 +1,99 @@
+"""Hidden states -> logits (+ logprobs).
+
+Reference: `python/sgl_jax/srt/layers/logits_processor.py` (`LogitsProcessorOutput` :27,
+`LogitsMetadata` :97, `LogitsProcessor` :249, `_get_logits` :523).  Only the last token of
+every sequence is projected unless input logprobs are requested; the vocab-parallel
+product is gathered over the tensor ranks; padding columns are sliced off; optional
+final soft-cap.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..parallel import state as ps
+
+
+@dataclass
+class LogitsProcessorOutput:
+    next_token_logits: torch.Tensor | None = None          # [B, V]
+    hidden_states: torch.Tensor | None = None
+    next_token_logprobs: torch.Tensor | None = None        # [B]
+    next_token_top_logprobs_val: list | None = None
+    next_token_top_logprobs_idx: list | None = None
+    next_token_token_ids_logprobs_val: list | None = None
+    next_token_token_ids_logprobs_idx: list | None = None
+    input_token_logprobs: torch.Tensor | None = None       # flat over requested input positions
+    input_top_logprobs_val: list | None = None
+    input_top_logprobs_idx: list | None = None
+    input_token_ids_logprobs_val: list | None = None
+    input_token_ids_logprobs_idx: list | None = None
+    routed_experts: Any = None
+    extras: dict = field(default_factory=dict)
+
+
+class LogitsProcessor(nn.Module):
+    def __init__(self, vocab_size: int, soft_cap: float | None = None, skip_all_gather: bool = False):
+        super().__init__()
+        self.vocab_size = vocab_size
+        self.soft_cap = soft_cap
+        self.skip_all_gather = skip_all_gather
+
+    def _project(self, hidden: torch.Tensor, lm_head) -> torch.Tensor:
+        logits = ops.linear(hidden, lm_head.weight)
+        if lm_head.tp_size > 1 and not self.skip_all_gather:
+            comm = ps.get_state().fused_comm
+            if comm is not None and comm.supports_logits_gather(logits):
+                logits = comm.logits_gather(logits)
+            else:
+                logits = ps.all_gather(logits, dim=-1)
+        logits = logits[:, : self.vocab_size]
+        if self.soft_cap:
+            logits = self.soft_cap * torch.tanh(logits.float() / self.soft_cap)
+        return logits
+
+    def forward(self, hidden_states: torch.Tensor, lm_head, forward_batch) -> LogitsProcessorOutput:
+        fb = forward_batch
+        if fb.forward_mode.is_decode() or fb.last_token_indices is None:
+            last = hidden_states
+        else:
+            last = hidden_states[fb.last_token_indices]
+        out = LogitsProcessorOutput(next_token_logits=self._project(last, lm_head))
+        if fb.capture_hidden_mode == 1:
+            out.hidden_states = last
+        elif fb.capture_hidden_mode == 2:
+            out.hidden_states = hidden_states
+        if fb.return_logprob and fb.forward_mode.is_extend() and fb.extend_logprob_start_lens_cpu is not None:
+            self._input_logprobs(hidden_states, lm_head, fb, out)
+        return out
+
+    def _input_logprobs(self, hidden_states, lm_head, fb, out: LogitsProcessorOutput):
+        """Log-probabilities of the prompt tokens from `logprob_start_len` on: row i of a
+        sequence predicts token i+1, so the rows `[start, len-1)` are scored against the
+        input ids shifted by one."""
+        rows, targets, counts = [], [], []
+        o = 0
+        ids = fb.input_ids
+        for b, (ext, start) in enumerate(zip(fb.extend_seq_lens_cpu.tolist(),
+                                             fb.extend_logprob_start_lens_cpu.tolist())):
+            n = max(ext - 1 - start, 0)
+            if n:
+                rows.append(torch.arange(o + start, o + start + n, device=hidden_states.device))
+                targets.append(ids[o + start + 1: o + start + 1 + n])
+            counts.append(n)
+            o += ext
+        out.extras["input_logprob_counts"] = counts
+        if not rows:
+            out.input_token_logprobs = torch.empty(0, device=hidden_states.device)
+            return
+        rows_t = torch.cat(rows)
+        tgt = torch.cat(targets).long()
+        logits = self._project(hidden_states[rows_t], lm_head).float()
+        lp = torch.log_softmax(logits, dim=-1)
+        out.input_token_logprobs = lp.gather(1, tgt.unsqueeze(1)).squeeze(1)
+        out.extras["input_logprobs_full"] = lp

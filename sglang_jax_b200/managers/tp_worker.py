@@ -1,0 +1,212 @@
+"""Model worker: owns a `ModelRunner` and turns a `ModelWorkerBatch` into sampled tokens.
+
+Reference: `python/sgl_jax/srt/managers/tp_worker.py:61-822` (`ModelWorker`, limits derived
+at :150-164 / :244, `forward_batch_generation` :468, `MockModelWorker` :722).  The reference
+is single-controller: one process feeds every device of the mesh.  Here there is one worker
+process per GPU; the worker on tensor-rank 0 lives beside the scheduler and broadcasts each
+step's batch to the follower ranks, which run `run_tp_follower` below.
+"""
+
+from __future__ import annotations
+
+import logging
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+import torch
+
+from ..configs.model_config import ModelConfig
+from ..managers.schedule_batch import ForwardMode, ModelWorkerBatch
+from ..model_executor.model_runner import ModelRunner
+from ..parallel import state as ps
+
+logger = logging.getLogger(__name__)
+
+
+@dataclass
+class GenerationBatchResult:
+    logits_output: Any
+    next_token_ids: Any              # device tensor (or numpy once resolved)
+    bid: int = 0
+    cache_miss_count: int = 0
+    extend_input_len_per_req: list | None = None
+    extend_logprob_start_len_per_req: list | None = None
+    accept_lens: Any = None
+    copy_done: Any = None            # CUDA event: D2H of `next_token_ids_cpu` finished
+    next_token_ids_cpu: Any = None
+    forward_batch: Any = None
+
+
+class _Control:
+    """Non-batch messages rank 0 sends to follower ranks."""
+
+    def __init__(self, kind: str, payload: Any = None):
+        self.kind = kind
+        self.payload = payload
+
+
+class ModelWorker:
+    def __init__(self, server_args, model_config: ModelConfig | None = None, is_draft_worker: bool = False,
+                 req_to_token_pool=None, token_to_kv_pool=None, max_total_num_tokens=None, model_path=None):
+        self.server_args = server_args
+        st = ps.get_state()
+        self.tp_rank = st.tp.rank
+        self.tp_size = st.tp.size
+        self.model_config = model_config or ModelConfig.from_server_args(
+            server_args, model_path=model_path or server_args.model_path, is_draft_model=is_draft_worker)
+        self.model_runner = ModelRunner(self.model_config, server_args, st.device,
+                                        req_to_token_pool=req_to_token_pool, is_draft_worker=is_draft_worker,
+                                        token_to_kv_pool=token_to_kv_pool, max_total_num_tokens=max_total_num_tokens)
+        self.device = self.model_runner.device
+        self.max_total_num_tokens = self.model_runner.max_total_num_tokens
+        self.max_prefill_tokens = server_args.max_prefill_tokens
+        self.max_running_requests = self.model_runner.max_running_requests
+        # longest request (prompt + output) one row can hold
+        self.max_req_len = min(self.model_config.context_len - 1, self.max_total_num_tokens - 1)
+        self.max_req_input_len = self.max_req_len - 5
+        self.random_seed = server_args.random_seed
+        self.broadcast_batches = self.tp_size > 1 and self.tp_rank == 0 and not is_draft_worker
+        self._pinned_ids = None
+
+    # ------------------------------------------------------------------
+    def get_worker_info(self):
+        return (self.max_total_num_tokens, self.max_prefill_tokens, self.max_running_requests,
+                self.max_req_len, self.max_req_input_len, self.random_seed, str(self.device),
+                self.model_runner.req_to_token_pool.size, self.model_runner.req_to_token_pool.max_context_len)
+
+    def get_memory_pool(self):
+        return self.model_runner.req_to_token_pool, self.model_runner.token_to_kv_pool
+
+    def get_pad_input_ids_func(self):
+        return getattr(self.model_runner.model, "pad_input_ids", None)
+
+    @property
+    def sliding_window_size(self):
+        return self.model_config.sliding_window
+
+    # ------------------------------------------------------------------
+    def forward_batch_generation(self, batch: ModelWorkerBatch, launch_done=None, skip_sample: bool = False
+                                 ) -> GenerationBatchResult:
+        if self.broadcast_batches:
+            ps.broadcast_object(batch, src=0, group=ps.get_state().tp)
+        out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
+        res = GenerationBatchResult(out, ids, bid=batch.bid, forward_batch=fb)
+        if ids is not None and self.device.type == "cuda":
+            # start the D2H copy right away; the scheduler waits on the event when it needs the ids
+            n = ids.numel()
+            buf = torch.empty(n, dtype=torch.int32, pin_memory=True)
+            buf.copy_(ids, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            res.next_token_ids_cpu, res.copy_done = buf, ev
+        if launch_done is not None:
+            launch_done.set()
+        return res
+
+    def resolve(self, res: GenerationBatchResult) -> np.ndarray:
+        """Host copy of the sampled ids (blocks until the step has finished)."""
+        if res.next_token_ids is None:
+            return np.empty(0, np.int32)
+        if res.copy_done is not None:
+            res.copy_done.synchronize()
+            return res.next_token_ids_cpu.numpy()
+        return res.next_token_ids.cpu().numpy().astype(np.int32)
+
+    def forward_batch_embedding(self, batch: ModelWorkerBatch):
+        if self.broadcast_batches:
+            ps.broadcast_object(_Control("embed", batch), src=0, group=ps.get_state().tp)
+        batch.capture_hidden_mode = 1
+        out, _, _ = self.model_runner.forward(batch, skip_sample=True)
+        return out.hidden_states
+
+    def send_control(self, kind: str, payload=None):
+        if self.broadcast_batches:
+            ps.broadcast_object(_Control(kind, payload), src=0, group=ps.get_state().tp)
+
+    def flush(self):
+        self.send_control("flush")
+
+    def shutdown(self):
+        self.send_control("shutdown")
+
+
+def run_tp_follower(server_args, worker: ModelWorker | None = None):
+    """Event loop of tensor ranks > 0: execute whatever rank 0 broadcasts."""
+    worker = worker or ModelWorker(server_args)
+    tp = ps.get_state().tp
+    while True:
+        msg = ps.broadcast_object(None, src=0, group=tp)
+        if isinstance(msg, _Control):
+            if msg.kind == "shutdown":
+                break
+            if msg.kind == "flush":
+                worker.model_runner.req_to_token_pool.page_table.zero_()
+            elif msg.kind == "embed":
+                msg.payload.capture_hidden_mode = 1
+                worker.model_runner.forward(msg.payload, skip_sample=True)
+            continue
+        worker.model_runner.forward(msg)
+    return worker
+
+
+class MockModelWorker:
+    """Scheduler-test stand-in: no model, deterministic fake tokens
+    (reference `tp_worker.py:722`)."""
+
+    def __init__(self, server_args=None, max_total_num_tokens=4096, max_running_requests=64,
+                 context_len=2048, vocab_size=1024, page_size=1, eos_after: int | None = None):
+        self.server_args = server_args
+        self.max_total_num_tokens = max_total_num_tokens
+        self.max_prefill_tokens = 16384
+        self.max_running_requests = max_running_requests
+        self.max_req_len = context_len - 1
+        self.max_req_input_len = context_len - 6
+        self.random_seed = 42
+        self.device = torch.device("cpu")
+        self.vocab_size = vocab_size
+        self.page_size = page_size
+        self.tp_size = 1
+        self.tp_rank = 0
+        from ..mem_cache.memory_pool import ReqToTokenPool
+        self.req_to_token_pool = ReqToTokenPool(max_running_requests + 8, context_len + 8, "cpu", page_size)
+        self.model_config = type("MC", (), {"vocab_size": vocab_size, "context_len": context_len,
+                                            "hf_eos_token_id": set(), "is_embedding": False,
+                                            "sliding_window": None, "num_experts": None})()
+        self.forward_ct = 0
+        self.batches: list[ModelWorkerBatch] = []
+
+    def get_worker_info(self):
+        return (self.max_total_num_tokens, self.max_prefill_tokens, self.max_running_requests, self.max_req_len,
+                self.max_req_input_len, self.random_seed, "cpu", self.req_to_token_pool.size,
+                self.req_to_token_pool.max_context_len)
+
+    def get_memory_pool(self):
+        return self.req_to_token_pool, None
+
+    def forward_batch_generation(self, batch: ModelWorkerBatch, launch_done=None, skip_sample=False):
+        self.forward_ct += 1
+        self.batches.append(batch)
+        # next token = (sum of the sequence's current length and last input id) mod vocab: cheap,
+        # deterministic and independent of batch composition
+        if batch.forward_mode.is_extend():
+            last = np.cumsum(batch.extend_seq_lens) - 1
+            last_ids = batch.input_ids[last]
+        else:
+            last_ids = batch.input_ids
+        ids = ((np.abs(last_ids).astype(np.int64) * 31 + batch.seq_lens) % self.vocab_size).astype(np.int32)
+        if launch_done is not None:
+            launch_done.set()
+        return GenerationBatchResult(None, ids, bid=batch.bid)
+
+    def resolve(self, res):
+        return np.asarray(res.next_token_ids)
+
+    def send_control(self, *a, **k):
+        pass
+
+    def flush(self):
+        pass
+
+    def shutdown(self):
+        pass

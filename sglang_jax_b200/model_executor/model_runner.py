@@ -1,0 +1,198 @@
+"""Per-GPU model executor.
+
+Reference: `python/sgl_jax/srt/model_executor/model_runner.py:73-1106` plus the KV sizing
+mixin (`model_runner_kv_cache_mixin.py`: cell size :293, `profile_max_num_token` :426,
+`_resolve_max_num_reqs` :488, `init_memory_pool` :760).  Where the reference jit-compiles
+one XLA executable per shape bucket, this runner launches hand-written kernels eagerly for
+prefill and replays captured CUDA graphs for decode (`cuda_graph_runner.py`).
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import time
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..configs.model_config import AttentionArch, ModelConfig
+from ..layers.radix_attention import AttentionBackend
+from ..layers.sampler import Sampler, SamplingMetadata
+from ..managers.schedule_batch import ForwardMode, ModelWorkerBatch
+from ..mem_cache.memory_pool import MHATokenToKVPool, MLATokenToKVPool, ReqToTokenPool, SWAKVPool
+from ..model_loader.loader import get_model_loader
+from ..parallel import state as ps
+from .forward_batch_info import ForwardBatch, _PinnedRing
+
+logger = logging.getLogger(__name__)
+
+
+class ModelRunner:
+    def __init__(self, model_config: ModelConfig, server_args, device: str | torch.device | None = None,
+                 req_to_token_pool: ReqToTokenPool | None = None, is_draft_worker: bool = False,
+                 token_to_kv_pool=None, max_total_num_tokens: int | None = None):
+        self.model_config = model_config
+        self.server_args = server_args
+        self.is_draft_worker = is_draft_worker
+        st = ps.get_state()
+        self.device = torch.device(device) if device is not None else st.device
+        self.tp_size = st.tp.size
+        self.tp_rank = st.tp.rank
+        self.page_size = server_args.page_size
+        self.dtype = model_config.dtype
+        ops.set_force_reference(server_args.disable_custom_kernels or self.device.type == "cpu")
+        self.attn_backend = AttentionBackend(
+            "native" if (server_args.attention_backend == "native" or self.device.type == "cpu") else "fa")
+        self.forward_ct = 0
+        self.graph_replays = 0
+        self.graph_recaptures = 0
+
+        t0 = time.time()
+        free_before = self._free_mem()
+        loader = get_model_loader(server_args.load_format, seed=0)
+        self.model = loader.load_model(model_config, self.device)
+        self.weight_bytes = sum(p.numel() * p.element_size() for p in self.model.parameters())
+        logger.info("model loaded in %.1fs, %.2f GB weights on %s", time.time() - t0,
+                    self.weight_bytes / 2 ** 30, self.device)
+        self.sampler = Sampler(server_args.random_seed, server_args.use_sort_for_toppk_minp,
+                               server_args.enable_deterministic_sampling, server_args.enable_nan_detection)
+        self._init_memory_pool(free_before, req_to_token_pool, token_to_kv_pool, max_total_num_tokens)
+        self.staging = _PinnedRing(4, 1 << 16, str(self.device))
+        # future-token map: slot = req row + 1; see `managers/tp_worker_overlap_thread.py`
+        self.future_token_ids_map = torch.zeros(self.req_to_token_pool.size + 2, dtype=torch.int32,
+                                                device=self.device)
+        self.cuda_graph_runner = None
+        self._init_fused_comm()
+        if self.device.type == "cuda" and not server_args.disable_cuda_graph and not is_draft_worker:
+            from .cuda_graph_runner import CudaGraphRunner
+            self.cuda_graph_runner = CudaGraphRunner(self)
+
+    # ------------------------------------------------------------------ memory
+    def _free_mem(self) -> int:
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            free, _ = torch.cuda.mem_get_info(self.device)
+            return free
+        import psutil
+        return psutil.virtual_memory().available
+
+    def _total_mem(self) -> int:
+        if self.device.type == "cuda":
+            return torch.cuda.mem_get_info(self.device)[1]
+        import psutil
+        return psutil.virtual_memory().total
+
+    def cell_size(self) -> int:
+        """Bytes of KV cache one token occupies on this rank."""
+        mc = self.model_config
+        kv_dtype = self.kv_cache_dtype
+        n_layers = getattr(self.model, "num_kv_layers", None) or mc.num_hidden_layers
+        if mc.attention_arch == AttentionArch.MLA:
+            return MLATokenToKVPool.cell_size(mc.kv_lora_rank, mc.qk_rope_head_dim, n_layers, kv_dtype)
+        return MHATokenToKVPool.cell_size(mc.get_num_kv_heads(self.tp_size), mc.head_dim, n_layers, kv_dtype)
+
+    def profile_max_num_token(self, free_before: int) -> int:
+        if os.environ.get("SGLANG_CI_SMALL_KV_SIZE"):
+            return int(os.environ["SGLANG_CI_SMALL_KV_SIZE"])
+        total = self._total_mem()
+        free_now = self._free_mem()
+        if self.device.type == "cuda":
+            rest = free_now - total * (1.0 - self.server_args.mem_fraction_static)
+        else:
+            rest = min(free_now * 0.25, 4 << 30)   # CPU runs are tests: stay small
+        n = int(rest // self.cell_size())
+        if self.tp_size > 1:
+            t = torch.tensor([n], dtype=torch.int64)
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=ps.get_state().tp.cpu_group)
+            n = int(t.item())
+        return n
+
+    def _init_memory_pool(self, free_before, req_to_token_pool, token_to_kv_pool, max_total):
+        sa, mc = self.server_args, self.model_config
+        kvd = sa.kv_cache_dtype
+        self.kv_cache_dtype = {"auto": self.dtype, "bf16": torch.bfloat16, "bfloat16": torch.bfloat16,
+                               "fp8_e4m3": torch.float8_e4m3fn, "fp8_e5m2": torch.float8_e5m2}[kvd]
+        if token_to_kv_pool is not None:
+            # draft worker shares the target's row table and allocator; it owns its own KV tensors
+            self.max_total_num_tokens = max_total
+        else:
+            n = self.profile_max_num_token(free_before)
+            if sa.max_total_tokens is not None:
+                n = min(n, sa.max_total_tokens)
+            n = n // self.page_size * self.page_size
+            if n <= 0:
+                raise RuntimeError("Not enough memory for the KV cache; raise --mem-fraction-static")
+            self.max_total_num_tokens = n
+        ctx = mc.context_len
+        max_reqs = sa.max_running_requests
+        if max_reqs is None:
+            max_reqs = min(max(int(self.max_total_num_tokens / ctx * 512), 256), 2048)
+        self.max_running_requests = max_reqs
+        if req_to_token_pool is None:
+            # a few spare rows: requests being chunk-prefilled or retracted hold rows too
+            req_to_token_pool = ReqToTokenPool(max_reqs + 8, ctx + 8, str(self.device), self.page_size)
+        self.req_to_token_pool = req_to_token_pool
+        n_layers = getattr(self.model, "num_kv_layers", None) or mc.num_hidden_layers
+        if mc.attention_arch == AttentionArch.MLA:
+            self.token_to_kv_pool = MLATokenToKVPool(self.max_total_num_tokens, self.page_size, self.kv_cache_dtype,
+                                                     mc.kv_lora_rank, mc.qk_rope_head_dim, n_layers, str(self.device))
+        elif getattr(self.model, "swa_layer_ids", None) and not sa.disable_hybrid_swa_memory:
+            swa_ids = self.model.swa_layer_ids
+            full_ids = [i for i in range(mc.num_hidden_layers) if i not in set(swa_ids)]
+            ratio = sa.swa_full_tokens_ratio
+            full = self.max_total_num_tokens
+            swa = max(int(full * ratio) // self.page_size * self.page_size, self.page_size)
+            self.token_to_kv_pool = SWAKVPool(full, swa, self.page_size, self.kv_cache_dtype,
+                                              mc.get_num_kv_heads(self.tp_size), mc.head_dim, swa_ids, full_ids,
+                                              str(self.device))
+        else:
+            self.token_to_kv_pool = MHATokenToKVPool(self.max_total_num_tokens, self.page_size, self.kv_cache_dtype,
+                                                     mc.get_num_kv_heads(self.tp_size), mc.head_dim, n_layers,
+                                                     str(self.device))
+        logger.info("KV pool: %d tokens, %.2f GB, max_running_requests=%d", self.max_total_num_tokens,
+                    self.token_to_kv_pool.get_kv_size_bytes() / 2 ** 30, max_reqs)
+
+    def _init_fused_comm(self):
+        st = ps.get_state()
+        if (self.tp_size > 1 and self.device.type == "cuda" and not self.server_args.disable_fused_comm
+                and not self.server_args.disable_custom_kernels and st.fused_comm is None):
+            try:
+                from ..parallel.fused_comm import FusedComm
+                st.fused_comm = FusedComm.create(st, self.model_config.hidden_size, self.dtype)
+            except Exception as e:  # NCCL path remains fully functional
+                logger.warning("fused communication kernels unavailable (%s); using NCCL", e)
+                st.fused_comm = None
+
+    # ------------------------------------------------------------------ forward
+    def resolve_future_token_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Negative ids are placeholders `-slot` for tokens the previous step is still
+        sampling; replace them from the device-side future map."""
+        return torch.where(input_ids < 0, self.future_token_ids_map[(-input_ids).clamp_min(0).long()], input_ids)
+
+    @torch.inference_mode()
+    def forward(self, batch: ModelWorkerBatch, skip_sample: bool = False):
+        """One step: returns `(logits_output, next_token_ids [B] int32 device tensor, forward_batch)`."""
+        self.forward_ct += 1
+        if batch.forward_mode.is_idle():
+            return None, torch.empty(0, dtype=torch.int32, device=self.device), None
+        gr = self.cuda_graph_runner
+        if gr is not None and gr.can_run(batch):
+            return gr.replay(batch)
+        fb = ForwardBatch.init_new(batch, self)
+        if self.server_args is not None and not self.server_args.disable_overlap_schedule:
+            fb.input_ids = self.resolve_future_token_ids(fb.input_ids)
+        out = self.model(fb.input_ids, fb)
+        if skip_sample:
+            return out, None, fb
+        meta = SamplingMetadata.from_worker_batch(batch, self.device)
+        ids = self.sampler(out, meta)
+        if batch.future_slots is not None:
+            slots = torch.from_numpy(batch.future_slots).to(self.device, non_blocking=True).long()
+            self.future_token_ids_map[slots] = ids
+        return out, ids, fb
+
+    def sample(self, logits_output, batch: ModelWorkerBatch):
+        return self.sampler(logits_output, SamplingMetadata.from_worker_batch(batch, self.device))

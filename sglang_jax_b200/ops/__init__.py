@@ -1,0 +1,102 @@
+"""Hot ops of the model forward.
+
+Every op has two implementations: the hand-written sm_100a kernel (module
+`native`, a C-ABI shared library loaded with ctypes) and a plain-PyTorch statement
+(module `reference`).  bf16 CUDA tensors take the native path; CPU tensors and other
+dtypes take the reference path.  On a machine with a GPU the native library is
+mandatory: if it cannot be loaded the first bf16 CUDA call raises instead of
+quietly running the reference.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import reference
+
+_FORCE_REFERENCE = False
+
+
+def set_force_reference(flag: bool):
+    """Route every op through the PyTorch statements (debugging / `--disable-custom-kernels`)."""
+    global _FORCE_REFERENCE
+    _FORCE_REFERENCE = bool(flag)
+
+
+def use_native(x: torch.Tensor) -> bool:
+    return (not _FORCE_REFERENCE) and x.is_cuda and x.dtype == torch.bfloat16
+
+
+def _native():
+    from . import native
+    return native
+
+
+def rmsnorm(x, w, eps, gemma=False):
+    if use_native(x):
+        return _native().rmsnorm(x, w, eps, gemma)
+    return reference.rmsnorm(x, w, eps, gemma)
+
+
+def fused_add_rmsnorm(x, residual, w, eps, gemma=False):
+    if use_native(x):
+        return _native().fused_add_rmsnorm(x, residual, w, eps, gemma)
+    return reference.fused_add_rmsnorm(x, residual, w, eps, gemma)
+
+
+def silu_and_mul(x):
+    if use_native(x):
+        return _native().silu_and_mul(x)
+    return reference.silu_and_mul(x)
+
+
+def linear(x, w, bias=None):
+    if use_native(x) and w.dtype == torch.bfloat16:
+        return _native().linear(x, w, bias)
+    return reference.linear(x, w, bias)
+
+
+def rope_qknorm_kvwrite(qkv, positions, cos_sin, q_norm_w, k_norm_w, eps, num_q_heads, num_kv_heads,
+                        head_dim, kv_buffer, out_cache_loc, page_size, is_neox=True, rotary_dim=None,
+                        gemma_norm=False):
+    if use_native(qkv) and (kv_buffer is None or kv_buffer.dtype == torch.bfloat16) and not gemma_norm:
+        return _native().rope_qknorm_kvwrite(qkv, positions, cos_sin, q_norm_w, k_norm_w, eps, num_q_heads,
+                                             num_kv_heads, head_dim, kv_buffer, out_cache_loc, page_size,
+                                             is_neox, rotary_dim)
+    return reference.rope_qknorm_kvwrite(qkv, positions, cos_sin, q_norm_w, k_norm_w, eps, num_q_heads,
+                                         num_kv_heads, head_dim, kv_buffer, out_cache_loc, page_size,
+                                         is_neox, rotary_dim, gemma_norm)
+
+
+def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
+                    cu_q_lens=None, prefix_lens=None, sliding_window=0, soft_cap=0.0, sinks=None,
+                    custom_mask=None, max_q_len=0, max_seq_len=0):
+    if use_native(q) and kv_buffer.dtype == torch.bfloat16 and sinks is None and custom_mask is None \
+            and q.shape[-1] in (64, 128):
+        return _native().paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size,
+                                         scale, cu_q_lens, prefix_lens, sliding_window, soft_cap,
+                                         max_q_len, max_seq_len)
+    return reference.paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
+                                     cu_q_lens, prefix_lens, sliding_window, soft_cap, sinks, custom_mask)
+
+
+def embedding(ids, table, vocab_start=0, masked=False):
+    if use_native(table) and ids.dtype == torch.int32:
+        return _native().embedding(ids, table, vocab_start, masked)
+    return reference.embedding(ids, table, vocab_start, masked)
+
+
+def argmax(logits):
+    """Greedy pick per row; the first maximal index wins."""
+    if (not _FORCE_REFERENCE) and logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16):
+        return _native().argmax(logits)
+    return torch.argmax(logits, dim=-1).to(torch.int32)
+
+
+def topk_route(router_logits, top_k, scoring="softmax", renormalize=True, correction_bias=None,
+               num_expert_group=0, topk_group=0, routed_scaling_factor=1.0):
+    if (not _FORCE_REFERENCE) and router_logits.is_cuda and router_logits.shape[-1] <= 512:
+        return _native().topk_route(router_logits, top_k, scoring, renormalize, correction_bias,
+                                    num_expert_group, topk_group, routed_scaling_factor)
+    return reference.topk_route(router_logits, top_k, scoring, renormalize, correction_bias,
+                                num_expert_group, topk_group, routed_scaling_factor)
