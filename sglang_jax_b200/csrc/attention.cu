@@ -1,0 +1,673 @@
+// Ragged paged attention over the paged KV cache  [pages, 2, Hkv, P, D]  (bf16).
+//
+//   paged_decode   one query token per sequence, GQA heads of one KV head packed into the MMA
+//                  M dimension, KV split over CTAs (flash-decoding) + a small combine kernel.
+//   paged_extend   prefill / mixed: a 64-row query tile of one sequence and one query head per
+//                  CTA, causal over `prefix_len + i`, online softmax (flash attention).
+//
+// Both stream K/V tiles of 64 tokens through a multi-stage shared-memory ring filled by TMA
+// tensor copies straight out of the page pool ("page gathers": one copy per page-run, the
+// page id comes from the device-resident page table), 128-byte swizzled so that ldmatrix is
+// bank-conflict free.  No multicast is used anywhere.  All barrier waits are bounded.
+//
+// Semantics follow the reference kernel's contract
+// (python/sgl_jax/srt/kernels/ragged_paged_attention/ragged_paged_attention_v3.py:1667 and its
+// jnp oracle `ref_ragged_paged_attention` :94): causal GQA attention over a ragged batch with
+// optional sliding window and logit soft-cap; the KV write itself happens in the fused
+// RoPE kernel that precedes this one on the stream.
+#include <math.h>
+
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace sglb {
+namespace {
+
+constexpr int TN = 64;            // KV tokens per tile
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+  const __nv_bfloat16* q;       // [T, Hq, D]
+  __nv_bfloat16* out;           // [T, Hq, D]
+  float* part_o;                // decode splits: [B, Hq, S, D]
+  float* part_lse;              // decode splits: [B, Hq, S]
+  const int* page_table;        // [rows, max_pages]
+  const int* req_pool_indices;  // [B]
+  const int* seq_lens;          // [B]
+  const int* prefix_lens;       // [B]   (extend)
+  const int* cu_q_lens;         // [B+1] (extend)
+  Status* status;
+  int B, Hq, Hkv, max_pages, page_size, num_splits;
+  int window;                   // 0 = none
+  float scale, soft_cap;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// byte offset of (row, 16-byte chunk) inside a [rows][64 bf16] half tile with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+// One stage: K halves then V halves, each half tile TN x 64 bf16 = 8 KB.
+template <int D>
+struct Stage {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kHalfBytes = TN * 128;
+  static constexpr int kBytes = 2 * kHalves * kHalfBytes;
+};
+
+// Issue the TMA copies of KV tile `tile` (tokens tile*64 ..) of one sequence / KV head.
+template <int D>
+__device__ __forceinline__ void issue_tile(const CUtensorMap* tmap, uint32_t smem_stage, uint32_t bar,
+                                           const int* pt_row, int max_pages, int page_size, int Hkv, int kvh,
+                                           int tile) {
+  using S = Stage<D>;
+  mbar_expect_tx(bar, S::kBytes);
+  const int tok0 = tile * TN;
+  const int run = page_size < TN ? page_size : TN;          // tokens per copy
+  const int n_runs = TN / run;
+  for (int r = 0; r < n_runs; ++r) {
+    const int tok = tok0 + r * run;
+    int pg = tok / page_size;
+    if (pg >= max_pages) pg = max_pages - 1;
+    const int page = pt_row[pg];
+    const int off = tok - (tok / page_size) * page_size;
+#pragma unroll
+    for (int kv = 0; kv < 2; ++kv) {
+      const int row = ((page * 2 + kv) * Hkv + kvh) * page_size + off;
+#pragma unroll
+      for (int h = 0; h < S::kHalves; ++h) {
+        const uint32_t dst = smem_stage + (kv * S::kHalves + h) * S::kHalfBytes + r * run * 128;
+        tma_load_2d(dst, tmap, bar, h * 64, row);
+      }
+    }
+  }
+}
+
+// Per-warp flash-attention state for a 16-row query fragment.
+template <int D>
+struct WarpState {
+  float o[D / 8][4];
+  float m[2];   // running max (scaled, log2 domain) for rows g and g+8
+  float l[2];   // running sum
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+};
+
+// Process NT (16 or 64) KV tokens starting at tile-local row `r0` against the warp's 16 query rows.
+// `kmax[i]` (i = 0 for row g, 1 for row g+8) is the last visible KV index (inclusive) and `kmin[i]`
+// the first, in absolute token positions; `tok_base` is the absolute index of tile row 0.
+template <int D, int NT>
+__device__ __forceinline__ void attend(WarpState<D>& st, const uint32_t (&qf)[D / 16][4], uint32_t k_smem,
+                                       uint32_t v_smem, int r0, int tok_base, const int (&kmin)[2],
+                                       const int (&kmax)[2], float scale_log2, float soft_cap, float scale) {
+  constexpr int NJ = NT / 8;
+  const int lane = threadIdx.x & 31;
+  const int t4 = lane & 3;
+  float s[NJ][4];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+  // S = Q K^T
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int half = kk / 4;             // which 64-wide half of D
+    const int c0 = (kk % 4) * 2;         // 16-byte chunk of the k-step inside the half
+#pragma unroll
+    for (int jp = 0; jp < NJ / 2; ++jp) {
+      // x4: matrices (tokens 16jp..+7, chunk c0), (same, c0+1), (tokens 16jp+8.., c0), (same, c0+1)
+      const int row = r0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int chunk = c0 + ((lane >> 3) & 1);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(k_smem + half * Stage<D>::kHalfBytes + sw_off(row, chunk), b0, b1, b2, b3);
+      mma16816(s[2 * jp], qf[kk], b0, b1);
+      mma16816(s[2 * jp + 1], qf[kk], b2, b3);
+    }
+  }
+  // scale / soft-cap / mask, tile max
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1;
+      const int tok = tok_base + r0 + j * 8 + t4 * 2 + (e & 1);
+      float v = s[j][e];
+      if (soft_cap > 0.f) v = soft_cap * tanhf(v * scale / soft_cap) * kLog2e;
+      else v *= scale_log2;
+      v = (tok <= kmax[i] && tok >= kmin[i]) ? v : -INFINITY;
+      s[j][e] = v;
+      mx[i] = fmaxf(mx[i], v);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+  }
+  float corr[2], mnew[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mnew[i] = fmaxf(st.m[i], mx[i]);
+    const float mref = mnew[i] == -INFINITY ? 0.f : mnew[i];
+    corr[i] = exp2f(st.m[i] - mref);          // st.m = -inf -> 0
+    st.m[i] = mnew[i];
+    mnew[i] = mref;
+  }
+  float rs[2] = {0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float pv = exp2f(s[j][e] - mnew[e >> 1]);
+      s[j][e] = pv;
+      rs[e >> 1] += pv;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) st.l[i] = st.l[i] * corr[i] + rs[i];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) {
+    st.o[n][0] *= corr[0];
+    st.o[n][1] *= corr[0];
+    st.o[n][2] *= corr[1];
+    st.o[n][3] *= corr[1];
+  }
+  // O += P V
+#pragma unroll
+  for (int kk = 0; kk < NT / 16; ++kk) {
+    uint32_t pa[4];
+    pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      // x4.trans: (tokens 16kk..+7, d 16np..+7), (tokens +8.., same d), (tokens 16kk.., d 16np+8..), (tokens +8.., d +8..)
+      const int row = r0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int dcol = np * 16 + ((lane >> 4) << 3);
+      const int half = dcol / 64;
+      const int chunk = (dcol % 64) / 8;
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(v_smem + half * Stage<D>::kHalfBytes + sw_off(row, chunk), b0, b1, b2, b3);
+      mma16816(st.o[2 * np], pa, b0, b1);
+      mma16816(st.o[2 * np + 1], pa, b2, b3);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- decode
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+paged_decode_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, int stages) {
+  using S = Stage<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + stages * S::kBytes);
+  uint64_t* empty_bar = full_bar + stages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + stages);
+  float* merge = reinterpret_cast<float*>(smem);   // reused after the main loop
+
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  const int seq = p.seq_lens[b];
+  const int* pt_row = p.page_table + static_cast<size_t>(p.req_pool_indices[b]) * p.max_pages;
+
+  int first_tok = 0;
+  if (p.window > 0 && seq > p.window) first_tok = seq - p.window;
+  const int tile_lo = first_tok / TN;
+  const int tile_hi = (seq + TN - 1) / TN;
+  const int n_tiles = tile_hi - tile_lo;
+  const int per = (n_tiles + p.num_splits - 1) / p.num_splits;
+  const int t0 = tile_lo + split * per;
+  const int t1 = min(t0 + per, tile_hi);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  WarpState<D> st;
+  st.init();
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = t0; t < t1 && !*abort_flag; ++t) {
+        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
+          report(p.status, kTimeoutEmptyBarrier, b, t);
+          *abort_flag = 1;
+          break;
+        }
+        issue_tile<D>(&tmap, smem_u32(smem + stage * S::kBytes), smem_u32(&full_bar[stage]), pt_row, p.max_pages,
+                      p.page_size, p.Hkv, kvh, t);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // Q fragments: rows = query heads of this KV group (zero beyond G)
+    uint32_t qf[D / 16][4];
+    const int g = lane >> 2, t4 = lane & 3;
+    const __nv_bfloat16* qrow = p.q + (static_cast<size_t>(b) * p.Hq + kvh * G + g) * D;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      qf[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + t4 * 2) : 0u;
+      qf[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8 + t4 * 2) : 0u;
+      qf[kk][1] = (g + 8) < G ? *reinterpret_cast<const uint32_t*>(qrow + 8 * D + kk * 16 + t4 * 2) : 0u;
+      qf[kk][3] = (g + 8) < G ? *reinterpret_cast<const uint32_t*>(qrow + 8 * D + kk * 16 + 8 + t4 * 2) : 0u;
+    }
+    const int kmin[2] = {first_tok, first_tok};
+    const int kmax[2] = {seq - 1, seq - 1};
+    const float scale_log2 = p.scale * kLog2e;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = t0; t < t1 && !*abort_flag; ++t) {
+      if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+        report(p.status, kTimeoutFullBarrier, b, t);
+        *abort_flag = 1;
+        break;
+      }
+      const uint32_t ks = smem_u32(smem + stage * S::kBytes);
+      const uint32_t vs = ks + S::kHalves * S::kHalfBytes;
+      // each consumer warp owns 16 of the tile's 64 tokens
+      if (t * TN + warp * 16 < seq)
+        attend<D, 16>(st, qf, ks, vs, warp * 16, t * TN, kmin, kmax, scale_log2, p.soft_cap, p.scale);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+      if (++stage == stages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+  }
+  __syncthreads();   // ring is idle now: reuse it for the cross-warp merge
+
+  // merge the four warps' (m, l, O) states; rows 0..7 only unless G > 8
+  float* m_s = merge;                         // [4][16]
+  float* l_s = merge + 64;                    // [4][16]
+  float* o_s = merge + 128;                   // [4][16][D]
+  if (warp < kConsumerWarps) {
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float l = st.l[i];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (t4 == 0) {
+        m_s[warp * 16 + g + 8 * i] = st.m[i];
+        l_s[warp * 16 + g + 8 * i] = l;
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      float* r0p = o_s + (warp * 16 + g) * D + n * 8 + t4 * 2;
+      r0p[0] = st.o[n][0];
+      r0p[1] = st.o[n][1];
+      float* r1p = r0p + 8 * D;
+      r1p[0] = st.o[n][2];
+      r1p[1] = st.o[n][3];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += kThreads) {
+    const int r = idx / D, d = idx - r * D;
+    float mmax = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) mmax = fmaxf(mmax, m_s[w * 16 + r]);
+    float lsum = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      const float mw = m_s[w * 16 + r];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mmax);
+      lsum += l_s[w * 16 + r] * f;
+      acc += o_s[(w * 16 + r) * D + d] * f;
+    }
+    const int hq = kvh * G + r;
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    if (p.num_splits == 1) {
+      p.out[(static_cast<size_t>(b) * p.Hq + hq) * D + d] = __float2bfloat16(acc * inv);
+    } else {
+      const size_t base = (static_cast<size_t>(b) * p.Hq + hq) * p.num_splits + split;
+      p.part_o[base * D + d] = acc * inv;
+      if (d == 0) p.part_lse[base] = lsum > 0.f ? mmax + log2f(lsum) : -INFINITY;
+    }
+  }
+}
+
+template <int D>
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                      __nv_bfloat16* __restrict__ out, int num_splits) {
+  const int row = blockIdx.x;   // b * Hq + h
+  const float* lse = part_lse + static_cast<size_t>(row) * num_splits;
+  float mmax = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mmax = fmaxf(mmax, lse[s]);
+  float wsum = 0.f;
+  for (int s = 0; s < num_splits; ++s) wsum += (lse[s] == -INFINITY) ? 0.f : exp2f(lse[s] - mmax);
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float w = (lse[s] == -INFINITY) ? 0.f : exp2f(lse[s] - mmax);
+      acc += w * part_o[(static_cast<size_t>(row) * num_splits + s) * D + d];
+    }
+    out[static_cast<size_t>(row) * D + d] = __float2bfloat16(acc * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------- extend
+constexpr int BQ = 64;   // query rows per CTA (16 per consumer warp)
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, int stages) {
+  using S = Stage<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + stages * S::kBytes);
+  uint64_t* empty_bar = full_bar + stages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + stages);
+
+  // locate (sequence, query tile) of this CTA: tiles are numbered sequence by sequence
+  int b = 0, tile_in_seq = 0;
+  {
+    int acc = 0;
+    const int want = blockIdx.x;
+    bool found = false;
+    for (int i = 0; i < p.B; ++i) {
+      const int n = p.cu_q_lens[i + 1] - p.cu_q_lens[i];
+      const int nt = (n + BQ - 1) / BQ;
+      if (want < acc + nt) {
+        b = i;
+        tile_in_seq = want - acc;
+        found = true;
+        break;
+      }
+      acc += nt;
+    }
+    if (!found) return;   // uniform for the whole CTA
+  }
+  const int hq = blockIdx.y;
+  const int G = p.Hq / p.Hkv;
+  const int kvh = hq / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_begin = p.cu_q_lens[b];
+  const int q_len = p.cu_q_lens[b + 1] - q_begin;
+  const int prefix = p.prefix_lens[b];
+  const int seq = p.seq_lens[b];
+  const int q0 = tile_in_seq * BQ;                         // first query row (within the sequence's new tokens)
+  const int q_hi = min(q0 + BQ, q_len);
+  const int kv_end = min(seq, prefix + q_hi);              // causal upper bound for this tile
+  int first_tok = 0;
+  if (p.window > 0) first_tok = max(0, prefix + q0 - p.window + 1);
+  const int t0 = first_tok / TN;
+  const int t1 = (kv_end + TN - 1) / TN;
+  const int* pt_row = p.page_table + static_cast<size_t>(p.req_pool_indices[b]) * p.max_pages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = t0; t < t1 && !*abort_flag; ++t) {
+        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
+          report(p.status, kTimeoutEmptyBarrier, b, t);
+          *abort_flag = 1;
+          break;
+        }
+        issue_tile<D>(&tmap, smem_u32(smem + stage * S::kBytes), smem_u32(&full_bar[stage]), pt_row, p.max_pages,
+                      p.page_size, p.Hkv, kvh, t);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    return;
+  }
+
+  WarpState<D> st;
+  st.init();
+  const int g = lane >> 2, t4 = lane & 3;
+  const int r_lo = q0 + warp * 16 + g;        // this thread's two query rows (within the sequence)
+  const int r_hi = r_lo + 8;
+  uint32_t qf[D / 16][4];
+  {
+    const __nv_bfloat16* qa = p.q + (static_cast<size_t>(q_begin + r_lo) * p.Hq + hq) * D;
+    const __nv_bfloat16* qb = p.q + (static_cast<size_t>(q_begin + r_hi) * p.Hq + hq) * D;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      qf[kk][0] = r_lo < q_len ? *reinterpret_cast<const uint32_t*>(qa + kk * 16 + t4 * 2) : 0u;
+      qf[kk][2] = r_lo < q_len ? *reinterpret_cast<const uint32_t*>(qa + kk * 16 + 8 + t4 * 2) : 0u;
+      qf[kk][1] = r_hi < q_len ? *reinterpret_cast<const uint32_t*>(qb + kk * 16 + t4 * 2) : 0u;
+      qf[kk][3] = r_hi < q_len ? *reinterpret_cast<const uint32_t*>(qb + kk * 16 + 8 + t4 * 2) : 0u;
+    }
+  }
+  const int kmax[2] = {min(prefix + r_lo, seq - 1), min(prefix + r_hi, seq - 1)};
+  int kmin[2] = {0, 0};
+  if (p.window > 0) {
+    kmin[0] = max(0, prefix + r_lo - p.window + 1);
+    kmin[1] = max(0, prefix + r_hi - p.window + 1);
+  }
+  // rows of this warp see KV up to prefix + q0 + warp*16 + 15: later tiles are fully masked for it
+  const int warp_kv_end = min(seq, prefix + min(q0 + warp * 16 + 16, q_len));
+  const float scale_log2 = p.scale * kLog2e;
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int t = t0; t < t1 && !*abort_flag; ++t) {
+    if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+      report(p.status, kTimeoutFullBarrier, b, t);
+      *abort_flag = 1;
+      break;
+    }
+    const uint32_t ks = smem_u32(smem + stage * S::kBytes);
+    const uint32_t vs = ks + S::kHalves * S::kHalfBytes;
+    if (t * TN < warp_kv_end && q0 + warp * 16 < q_len)
+      attend<D, TN>(st, qf, ks, vs, 0, t * TN, kmin, kmax, scale_log2, p.soft_cap, p.scale);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
+  // finalize
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float l = st.l[i];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    st.l[i] = l > 0.f ? 1.f / l : 0.f;
+  }
+  if (r_lo < q_len) {
+    __nv_bfloat16* o = p.out + (static_cast<size_t>(q_begin + r_lo) * p.Hq + hq) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+      *reinterpret_cast<uint32_t*>(o + n * 8 + t4 * 2) = pack_bf16(st.o[n][0] * st.l[0], st.o[n][1] * st.l[0]);
+  }
+  if (r_hi < q_len) {
+    __nv_bfloat16* o = p.out + (static_cast<size_t>(q_begin + r_hi) * p.Hq + hq) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+      *reinterpret_cast<uint32_t*>(o + n * 8 + t4 * 2) = pack_bf16(st.o[n][2] * st.l[1], st.o[n][3] * st.l[1]);
+  }
+}
+
+// tensor map over the whole page pool viewed as [num_pages*2*Hkv*P, D]; box = 64 x min(P, 64)
+struct TmapKey {
+  const void* ptr;
+  long long rows;
+  int D, box_rows;
+  bool operator==(const TmapKey& o) const { return ptr == o.ptr && rows == o.rows && D == o.D && box_rows == o.box_rows; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^ (k.D * 131) ^ (k.box_rows * 7);
+  }
+};
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmaps;
+
+bool get_kv_tmap(const void* kv, long long rows, int D, int page_size, CUtensorMap* out) {
+  const int box_rows = page_size < TN ? page_size : TN;
+  TmapKey key{kv, rows, D, box_rows};
+  auto it = g_tmaps.find(key);
+  if (it != g_tmaps.end()) {
+    *out = it->second;
+    return true;
+  }
+  CUtensorMap m;
+  if (!encode_tmap_2d(&m, kv, D, rows, static_cast<uint64_t>(D) * 2, 64, box_rows, 2)) return false;
+  if (g_tmaps.size() > 4096) g_tmaps.clear();
+  g_tmaps.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+template <int D>
+int smem_bytes(int stages) { return stages * Stage<D>::kBytes + stages * 16 + 64 + 1024; }
+
+}  // namespace
+}  // namespace sglb
+
+extern "C" {
+
+// Suggested number of KV splits for a decode launch (fixed per CUDA graph).
+int sglb_decode_num_splits(int B, int Hkv, int max_seq_len) {
+  const int sms = sglb::sm_count();
+  const int ctas = B * Hkv;
+  int splits = (2 * sms + ctas - 1) / ctas;
+  const int tiles = (max_seq_len + sglb::TN - 1) / sglb::TN;
+  splits = splits < 1 ? 1 : splits;
+  if (splits > tiles / 2) splits = tiles / 2 > 0 ? tiles / 2 : 1;
+  if (splits > 32) splits = 32;
+  return splits;
+}
+
+int sglb_paged_decode(const void* q, void* out, const void* kv_buffer, long long num_pages, const int* page_table,
+                      int max_pages, const int* req_pool_indices, const int* seq_lens, int B, int Hq, int Hkv, int D,
+                      int page_size, float scale, int window, float soft_cap, int num_splits, float* part_o,
+                      float* part_lse, cudaStream_t stream) {
+  using namespace sglb;
+  if (B <= 0) return 0;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0 || Hq / Hkv > 16) return -kBadArgument;
+  if (page_size < TN ? (TN % page_size != 0) : (page_size % TN != 0)) return -kBadArgument;
+  if (num_splits > 1 && (part_o == nullptr || part_lse == nullptr)) return -kBadArgument;
+  CUtensorMap tm;
+  if (!get_kv_tmap(kv_buffer, num_pages * 2 * Hkv * page_size, D, page_size, &tm)) return -100;
+  AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.part_o = part_o;
+  p.part_lse = part_lse;
+  p.page_table = page_table;
+  p.req_pool_indices = req_pool_indices;
+  p.seq_lens = seq_lens;
+  p.status = device_status();
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.max_pages = max_pages; p.page_size = page_size;
+  p.num_splits = num_splits < 1 ? 1 : num_splits;
+  p.window = window; p.scale = scale; p.soft_cap = soft_cap;
+  const int stages = 4;
+  dim3 grid(B, Hkv, p.num_splits);
+  cudaError_t e;
+  if (D == 128) {
+    static bool cfg = false;
+    const int sm = smem_bytes<128>(stages);
+    if (!cfg) { cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); cfg = true; }
+    paged_decode_kernel<128><<<grid, kThreads, sm, stream>>>(tm, p, stages);
+    e = cudaGetLastError();
+    if (e == cudaSuccess && p.num_splits > 1) {
+      decode_combine_kernel<128><<<B * Hq, 128, 0, stream>>>(part_o, part_lse, p.out, p.num_splits);
+      e = cudaGetLastError();
+    }
+  } else {
+    static bool cfg = false;
+    const int sm = smem_bytes<64>(stages);
+    if (!cfg) { cudaFuncSetAttribute(paged_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); cfg = true; }
+    paged_decode_kernel<64><<<grid, kThreads, sm, stream>>>(tm, p, stages);
+    e = cudaGetLastError();
+    if (e == cudaSuccess && p.num_splits > 1) {
+      decode_combine_kernel<64><<<B * Hq, 64, 0, stream>>>(part_o, part_lse, p.out, p.num_splits);
+      e = cudaGetLastError();
+    }
+  }
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// `num_q_tiles_bound` >= sum_b ceil(q_len_b / 64); T/64 + B always is.
+int sglb_paged_extend(const void* q, void* out, const void* kv_buffer, long long num_pages, const int* page_table,
+                      int max_pages, const int* req_pool_indices, const int* seq_lens, const int* prefix_lens,
+                      const int* cu_q_lens, int B, int num_q_tiles_bound, int Hq, int Hkv, int D, int page_size,
+                      float scale, int window, float soft_cap, cudaStream_t stream) {
+  using namespace sglb;
+  if (B <= 0 || num_q_tiles_bound <= 0) return 0;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0) return -kBadArgument;
+  if (page_size < TN ? (TN % page_size != 0) : (page_size % TN != 0)) return -kBadArgument;
+  CUtensorMap tm;
+  if (!get_kv_tmap(kv_buffer, num_pages * 2 * Hkv * page_size, D, page_size, &tm)) return -100;
+  AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.page_table = page_table;
+  p.req_pool_indices = req_pool_indices;
+  p.seq_lens = seq_lens;
+  p.prefix_lens = prefix_lens;
+  p.cu_q_lens = cu_q_lens;
+  p.status = device_status();
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.max_pages = max_pages; p.page_size = page_size;
+  p.num_splits = 1; p.window = window; p.scale = scale; p.soft_cap = soft_cap;
+  const int stages = 3;
+  dim3 grid(num_q_tiles_bound, Hq, 1);
+  cudaError_t e;
+  if (D == 128) {
+    static bool cfg = false;
+    const int sm = smem_bytes<128>(stages);
+    if (!cfg) { cudaFuncSetAttribute(paged_extend_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); cfg = true; }
+    paged_extend_kernel<128><<<grid, kThreads, sm, stream>>>(tm, p, stages);
+    e = cudaGetLastError();
+  } else {
+    static bool cfg = false;
+    const int sm = smem_bytes<64>(stages);
+    if (!cfg) { cudaFuncSetAttribute(paged_extend_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); cfg = true; }
+    paged_extend_kernel<64><<<grid, kThreads, sm, stream>>>(tm, p, stages);
+    e = cudaGetLastError();
+  }
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+}

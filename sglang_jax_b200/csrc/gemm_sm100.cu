@@ -1,0 +1,443 @@
+// bf16 GEMM  out[M, N] = x[M, K] . w[N, K]^T (+ bias)  on the 5th-generation tensor cores.
+//
+// One persistent, warp-specialised kernel:
+//   warp 0      TMA producer: 128-byte-swizzled operand tiles into a multi-stage smem ring
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 16) per 16-wide K slice,
+//               tcgen05.commit releases smem stages / publishes finished accumulators
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator out of tensor memory, convert, store
+// The accumulator is double buffered in tensor memory (2 x BN columns) so the epilogue of tile
+// i overlaps the main loop of tile i+1.
+//
+// Two operand assignments share the kernel:
+//   MODE 0 ("tokens on M")   A = x tile (128 tokens), B = w tile (BN outputs).  Prefill.
+//   MODE 1 ("weights on M")  A = w tile (128 outputs), B = x (all tokens, BN >= M).  Decode:
+//          the 128-row MMA dimension is filled with weight rows, so a batch of 1..256 tokens
+//          wastes no tensor-core rows, weights are streamed exactly once, and K is split over
+//          CTAs so that all SMs pull HBM bandwidth.  Split partials go through an fp32
+//          workspace; the CTA that arrives last for a tile sums them in split order
+//          (deterministic) and writes the bf16 result.
+//
+// The reference project has no counterpart kernel: its dense projections are
+// `lax.dot_general` calls lowered by XLA (python/sgl_jax/srt/layers/linear.py:102).
+#include "common.cuh"
+
+namespace sglb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;           // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kNumThreads = 192;
+constexpr int kEpiThreads = 128;
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStageBytesA = BM * BK * 2;
+  static constexpr int kStageBytesB = BN * BK * 2;
+  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;      // power of two for BN in {16..256}
+  static constexpr int kStagingBytes = 4 * 32 * 32 * 2;             // per-epilogue-warp 32x32 bf16 transpose tile
+  static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // +1024 alignment slack
+  static constexpr int CW = BN >= 32 ? 32 : 16;                      // columns per tcgen05.ld
+};
+
+struct Params {
+  __nv_bfloat16* out;            // [M, N] row-major
+  const __nv_bfloat16* bias;     // [N] or null
+  float* workspace;              // split-K partials: [tile][split][BN][128] fp32
+  int* counters;                 // one per output tile, zero when idle
+  Status* status;
+  int M, N, K;
+  int tiles_a, tiles_b;          // tiles along the A-operand rows / B-operand rows
+  int splits;                    // K splits
+  int kb_total;                  // K blocks (ceil(K / 64))
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  uint8_t* staging = smem + C::kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::kStagingBytes);
+  uint64_t* full_bar = bars;                         // [kStages]
+  uint64_t* empty_bar = bars + C::kStages;           // [kStages]
+  uint64_t* tmem_full_bar = bars + 2 * C::kStages;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), kEpiThreads);
+    }
+    *abort_flag = 0;
+    *last_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_a * p.tiles_b;
+  const int num_work = num_tiles * p.splits;
+  const int kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+
+  // work item -> (tile_a, tile_b, split).  Consecutive CTAs take consecutive A tiles of the
+  // same B tile, so the B tile (weights in MODE 0) is fetched from HBM once and then hit in L2.
+  auto decode = [&](int w, int& ta, int& tb, int& sp, int& kb0, int& kb1) {
+    sp = w / num_tiles;
+    const int t = w - sp * num_tiles;
+    tb = t / p.tiles_a;
+    ta = t - tb * p.tiles_a;
+    kb0 = sp * kb_per_split;
+    kb1 = min(kb0 + kb_per_split, p.kb_total);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int w = blockIdx.x; w < num_work && !*abort_flag; w += gridDim.x) {
+        int ta, tb, sp, kb0, kb1;
+        decode(w, ta, tb, sp, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
+            report(p.status, kTimeoutEmptyBarrier, w, kb);
+            *abort_flag = 1;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(fb, C::kStageBytes);
+          uint8_t* sa = stage_base + stage * C::kStageBytes;
+          tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * BK, ta * BM);
+          tma_load_2d(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, tb * BN);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int w = blockIdx.x; w < num_work && !*abort_flag; w += gridDim.x) {
+        int ta, tb, sp, kb0, kb1;
+        decode(w, ta, tb, sp, kb0, kb1);
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1)) {
+          report(p.status, kTimeoutTmemEmpty, w, acc);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+            report(p.status, kTimeoutFullBarrier, w, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
+          const uint64_t da = make_smem_desc_sw128(sa);
+          const uint64_t db = make_smem_desc_sw128(sa + C::kStageBytesA);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advance 16 bf16 = 32 bytes along K inside the swizzle row: +2 in 16-byte units
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&tmem_full_bar[acc]));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+    const int row = q * 32 + lane;          // accumulator row (0..127) of this thread
+    const int epi_tid = threadIdx.x - 64;   // 0..127
+    uint8_t* my_stage = staging + q * (32 * 32 * 2);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int w = blockIdx.x; w < num_work && !*abort_flag; w += gridDim.x) {
+      int ta, tb, sp, kb0, kb1;
+      decode(w, ta, tb, sp, kb0, kb1);
+      if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase)) {
+        report(p.status, kTimeoutTmemFull, w, acc);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const int tile_id = tb * p.tiles_a + ta;
+      const bool direct = (p.splits == 1);
+      float* ws_tile = direct ? nullptr
+                              : p.workspace + (static_cast<size_t>(tile_id) * p.splits + sp) * (BM * BN);
+
+      auto store_chunk = [&](const float* f, int c0) {
+        // f[0..CW): accumulator row `row`, columns c0..c0+CW of this tile
+        if constexpr (MODE == 0) {
+          // rows are tokens, columns are outputs: transpose through smem so that global stores
+          // are 16-byte vectors covering whole 64-byte row segments
+          const int gm0 = ta * BM + q * 32;
+          const int gn0 = tb * BN + c0;
+#pragma unroll
+          for (int j = 0; j < C::CW / 8; ++j) {
+            float g[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              g[e] = f[j * 8 + e];
+              if (p.bias != nullptr) {
+                const int gn = gn0 + j * 8 + e;
+                if (gn < p.N) g[e] += __bfloat162float(p.bias[gn]);
+              }
+            }
+            uint4 v = make_uint4(pack_bf16(g[0], g[1]), pack_bf16(g[2], g[3]), pack_bf16(g[4], g[5]),
+                                 pack_bf16(g[6], g[7]));
+            const int pj = j ^ ((lane >> 1) & (C::CW / 8 - 1));
+            *reinterpret_cast<uint4*>(my_stage + lane * (C::CW * 2) + pj * 16) = v;
+          }
+          __syncwarp();
+          constexpr int kChunksPerRow = C::CW / 8;            // 16-byte chunks per staged row
+          constexpr int kRowsPerIt = 32 / kChunksPerRow;
+#pragma unroll
+          for (int it = 0; it < 32 / kRowsPerIt; ++it) {
+            const int r = it * kRowsPerIt + lane / kChunksPerRow;
+            const int jj = lane % kChunksPerRow;
+            const int pj = jj ^ ((r >> 1) & (kChunksPerRow - 1));
+            const uint4 v = *reinterpret_cast<const uint4*>(my_stage + r * (C::CW * 2) + pj * 16);
+            const int gm = gm0 + r;
+            const int gn = gn0 + jj * 8;
+            if (gm < p.M && gn < p.N) {
+              *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(gm) * p.N + gn) = v;
+            }
+          }
+          __syncwarp();
+        } else {
+          // rows are outputs (weight rows), columns are tokens: out[token][n]
+          const int gn = ta * BM + row;
+          if (gn < p.N) {
+            const float b = p.bias != nullptr ? __bfloat162float(p.bias[gn]) : 0.f;
+#pragma unroll
+            for (int e = 0; e < C::CW; ++e) {
+              const int tok = tb * BN + c0 + e;
+              if (tok < p.M) p.out[static_cast<size_t>(tok) * p.N + gn] = __float2bfloat16(f[e] + b);
+            }
+          }
+        }
+      };
+
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += C::CW) {
+        uint32_t v[32];
+        if constexpr (C::CW == 32) tmem_ld32(t_addr + c0, v);
+        else tmem_ld16(t_addr + c0, v);
+        tmem_ld_wait();
+        if (direct) {
+          float f[C::CW];
+#pragma unroll
+          for (int e = 0; e < C::CW; ++e) f[e] = __uint_as_float(v[e]);
+          store_chunk(f, c0);
+        } else {
+          // partial tile, column-major inside the tile so a warp writes 128 contiguous bytes
+#pragma unroll
+          for (int e = 0; e < C::CW; ++e) ws_tile[(c0 + e) * BM + row] = __uint_as_float(v[e]);
+        }
+      }
+      // accumulator drained: hand the TMEM buffer back to the MMA warp
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+
+      if (!direct) {
+        __threadfence();
+        named_bar_sync(1, kEpiThreads);
+        if (epi_tid == 0) {
+          const int old = atomicAdd(&p.counters[tile_id], 1);
+          const int last = (old == p.splits - 1) ? 1 : 0;
+          if (last) p.counters[tile_id] = 0;    // leave the counter clean for the next launch
+          *last_flag = last;
+        }
+        named_bar_sync(1, kEpiThreads);
+        const bool is_last = *last_flag != 0;
+        named_bar_sync(1, kEpiThreads);
+        if (is_last) {
+          __threadfence();
+          const float* ws0 = p.workspace + static_cast<size_t>(tile_id) * p.splits * (BM * BN);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += C::CW) {
+            float f[C::CW];
+#pragma unroll
+            for (int e = 0; e < C::CW; ++e) f[e] = 0.f;
+            for (int s = 0; s < p.splits; ++s) {
+              const float* wsp = ws0 + static_cast<size_t>(s) * (BM * BN);
+#pragma unroll
+              for (int e = 0; e < C::CW; ++e) f[e] += __ldcg(&wsp[(c0 + e) * BM + row]);
+            }
+            store_chunk(f, c0);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the CTA's smem is released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int BN, int MODE>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto* kern = gemm_bf16_kernel<BN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<grid, kNumThreads, C::kSmemBytes, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+inline int pick_bn_tokens(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+}  // namespace
+}  // namespace sglb
+
+extern "C" {
+
+// Bytes of fp32 workspace / number of int counters the launcher may use for given shapes.
+// (Upper bounds; callers allocate once for their largest decode shape.)
+size_t sglb_gemm_workspace_bytes(int M, int N, int K) {
+  if (M > 256) return 0;
+  const int bn = sglb::pick_bn_tokens(M);
+  const size_t tiles = (N + 127) / 128;
+  return tiles * 16 /*max splits*/ * 128 * bn * sizeof(float);
+}
+
+int sglb_gemm_max_counters(int N) { return (N + 127) / 128 + 8; }
+
+// out[M,N] = x[M,K] . w[N,K]^T + bias.  All bf16, row-major, K and N multiples of 8,
+// pointers 16-byte aligned.  `workspace`/`counters` are only touched when M <= 256 and the
+// launcher decides to split K; `counters` must be zero on entry (the kernel restores zeros).
+// force_mode: -1 auto, 0 tokens-on-M, 1 weights-on-M.  force_splits: 0 auto.
+int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, void* workspace,
+                   size_t workspace_bytes, int* counters, int force_mode, int force_splits, cudaStream_t stream) {
+  using namespace sglb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) || (N % 8)) return -kBadArgument;
+  const int kb_total = (K + BK - 1) / BK;
+  const int sms = sm_count();
+  int mode = force_mode >= 0 ? force_mode : (M <= 256 ? 1 : 0);
+  if (mode == 1 && M > 256) mode = 0;
+
+  Params p{};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.workspace = static_cast<float*>(workspace);
+  p.counters = counters;
+  p.status = device_status();
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.kb_total = kb_total;
+  p.splits = 1;
+
+  CUtensorMap ta, tb;
+  cudaError_t err;
+  if (mode == 0) {
+    const int bn = (N >= 256 && (static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) >= sms || N % 256 == 0))
+                       ? 256 : 128;
+    p.tiles_a = (M + BM - 1) / BM;
+    p.tiles_b = (N + bn - 1) / bn;
+    if (!encode_tmap_2d(&ta, x, K, M, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
+    if (!encode_tmap_2d(&tb, w, K, N, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
+    const int grid = min(p.tiles_a * p.tiles_b, sms);
+    err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
+  } else {
+    const int bn = pick_bn_tokens(M);
+    p.tiles_a = (N + BM - 1) / BM;
+    p.tiles_b = 1;
+    int splits = force_splits > 0 ? force_splits : 1;
+    if (force_splits <= 0 && workspace != nullptr && counters != nullptr) {
+      // enough CTAs to cover the SMs, but keep at least 8 K-blocks per split
+      splits = (sms + p.tiles_a - 1) / p.tiles_a;
+      splits = min(splits, max(1, kb_total / 8));
+      splits = min(splits, 16);
+    }
+    if (splits > 1) {
+      const size_t need = static_cast<size_t>(p.tiles_a) * splits * BM * bn * sizeof(float);
+      if (workspace == nullptr || counters == nullptr || need > workspace_bytes) splits = 1;
+    }
+    // every split must own at least one K block
+    while (splits > 1 && (kb_total + splits - 1) / splits * (splits - 1) >= kb_total) --splits;
+    p.splits = splits;
+    if (!encode_tmap_2d(&ta, w, K, N, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
+    if (!encode_tmap_2d(&tb, x, K, M, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
+    const int grid = min(p.tiles_a * splits, sms);
+    switch (bn) {
+      case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
+      case 32: err = launch<32, 1>(ta, tb, p, grid, stream); break;
+      case 64: err = launch<64, 1>(ta, tb, p, grid, stream); break;
+      case 128: err = launch<128, 1>(ta, tb, p, grid, stream); break;
+      default: err = launch<256, 1>(ta, tb, p, grid, stream); break;
+    }
+  }
+  return err == cudaSuccess ? 0 : static_cast<int>(err);
+}
+}

@@ -132,6 +132,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         self.decode_steps_since_prefill = 0
         self.decode_first_interleave = int(os.environ.get("SGL_DECODE_FIRST_INTERLEAVE", "0"))
         self.result_queue: deque = deque()
+        # callables `hook(scheduler, batch_or_None)` run at the end of every loop iteration
+        self.step_hooks: list = []
         self.init_metrics()
         self.init_profiler()
         self.precision_tracer_state: dict = {"enabled": False}
@@ -249,10 +251,14 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         self.cur_batch = batch
         if batch is None:
             self.on_idle()
+            for h in self.step_hooks:
+                h(self, None)
             return False
         result = self.run_batch(batch)
         self.process_batch_result(batch, result)
         self.last_batch = batch
+        for h in self.step_hooks:
+            h(self, batch)
         return True
 
     def event_loop_overlap(self, stop_event: threading.Event | None = None):
@@ -281,6 +287,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         elif batch is None:
             self.on_idle()
         self.last_batch = batch
+        for h in self.step_hooks:
+            h(self, batch)
         return batch is not None
 
     def _drain_results(self):

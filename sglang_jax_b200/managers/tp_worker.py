@@ -68,6 +68,7 @@ class ModelWorker:
         self.random_seed = server_args.random_seed
         self.broadcast_batches = self.tp_size > 1 and self.tp_rank == 0 and not is_draft_worker
         self._pinned_ids = None
+        self.marks: dict = {}
 
     # ------------------------------------------------------------------
     def get_worker_info(self):
@@ -130,6 +131,49 @@ class ModelWorker:
     def shutdown(self):
         self.send_control("shutdown")
 
+    def mark(self, tag: str):
+        """Record a timing event on this rank's stream and on every follower's."""
+        self.send_control("mark", tag)
+        _sync_all(self.device)
+        self.marks[tag] = _record_event(self.device)
+
+    def elapsed_ms_max_over_ranks(self, start_tag: str, end_tag: str) -> float:
+        self.send_control("report", (start_tag, end_tag))
+        return report_elapsed_max(self, start_tag, end_tag)
+
+
+def _sync_all(device):
+    """Device synchronize + barrier over the tensor ranks: brackets a timed region."""
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+    ps.barrier(ps.get_state().tp)
+
+
+def _record_event(device):
+    if device.type != "cuda":
+        import time
+        return time.perf_counter()
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    return ev
+
+
+def report_elapsed_max(worker: "ModelWorker", start_tag: str, end_tag: str) -> float:
+    """Device time between two marks in ms, max over the tensor ranks (every rank calls this)."""
+    a, b = worker.marks[start_tag], worker.marks[end_tag]
+    if worker.device.type == "cuda":
+        b.synchronize()
+        ms = a.elapsed_time(b)
+    else:
+        ms = (b - a) * 1e3
+    tp = ps.get_state().tp
+    if tp.size > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=tp.cpu_group)
+        ms = float(t.item())
+    return ms
+
 
 def run_tp_follower(server_args, worker: ModelWorker | None = None):
     """Event loop of tensor ranks > 0: execute whatever rank 0 broadcasts."""
@@ -145,6 +189,11 @@ def run_tp_follower(server_args, worker: ModelWorker | None = None):
             elif msg.kind == "embed":
                 msg.payload.capture_hidden_mode = 1
                 worker.model_runner.forward(msg.payload, skip_sample=True)
+            elif msg.kind == "mark":
+                _sync_all(worker.device)
+                worker.marks[msg.payload] = _record_event(worker.device)
+            elif msg.kind == "report":
+                report_elapsed_max(worker, *msg.payload)
             continue
         worker.model_runner.forward(msg)
     return worker

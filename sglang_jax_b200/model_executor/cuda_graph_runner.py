@@ -1,0 +1,188 @@
+"""CUDA-graph capture / replay of the decode step.
+
+The reference avoids per-step compilation by padding batches to shape buckets and
+pre-compiling one XLA executable per bucket (`python/sgl_jax/srt/model_executor/
+compilation_manager.py:69-128`), and asserts zero recompiles at serving time.  The B200
+equivalent: one captured CUDA graph per batch-size bucket holding the whole decode step
+(future-token resolve, page-table delta scatter, all layers, LM head, greedy sample,
+future-map store).  A step copies its few integers into the graph's static input buffers
+and replays; nothing is captured after warm-up (`graph_recaptures` stays 0 and is
+reported to clients as `cache_miss_count`).
+"""
+
+from __future__ import annotations
+
+import bisect
+import logging
+
+import numpy as np
+import torch
+
+from ..managers.schedule_batch import ForwardMode, ModelWorkerBatch
+from .forward_batch_info import ForwardBatch
+
+logger = logging.getLogger(__name__)
+
+DEFAULT_BS_BUCKETS = [1, 2, 4, 8, 12, 16, 24, 32, 40, 48, 56, 64, 80, 96, 112, 128, 160, 192, 224, 256]
+MAX_PAGE_DELTAS = 1024
+
+
+class CudaGraphRunner:
+    def __init__(self, runner):
+        self.runner = runner
+        sa = runner.server_args
+        max_bs = sa.cuda_graph_max_bs or min(runner.max_running_requests, 256)
+        buckets = sa.precompile_bs_paddings or DEFAULT_BS_BUCKETS
+        self.buckets = sorted({b for b in buckets if b <= max_bs} | {min(max_bs, max(buckets))})
+        self.max_bs = self.buckets[-1]
+        dev = runner.device
+        self.pad_row = runner.req_to_token_pool.size   # all-zero page-table row -> dummy page 0
+        n = self.max_bs
+        # static inputs: ids | positions | out_cache_loc | req_pool | seq_lens | future_slots | delta rows,pos,ids | n_delta
+        self.buf = torch.zeros(6 * n + 3 * MAX_PAGE_DELTAS, dtype=torch.int32, device=dev)
+        self.host = torch.zeros(6 * n + 3 * MAX_PAGE_DELTAS, dtype=torch.int32, pin_memory=True)
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.outputs: dict[int, torch.Tensor] = {}
+        self.pool = None
+        self.stream = torch.cuda.Stream(device=dev)
+        self.copy_event: torch.cuda.Event | None = None
+        self.enabled = True
+        self.kernels_per_graph = 0
+        if not sa.disable_precompile:
+            self.capture_all()
+
+    # ------------------------------------------------------------------
+    def _views(self, bs: int):
+        n = self.max_bs
+        b = self.buf
+        return dict(input_ids=b[0:bs], positions=b[n:n + bs], out_cache_loc=b[2 * n:2 * n + bs],
+                    req_pool_indices=b[3 * n:3 * n + bs], seq_lens=b[4 * n:4 * n + bs],
+                    future_slots=b[5 * n:5 * n + bs],
+                    d_rows=b[6 * n:6 * n + MAX_PAGE_DELTAS],
+                    d_pos=b[6 * n + MAX_PAGE_DELTAS:6 * n + 2 * MAX_PAGE_DELTAS],
+                    d_ids=b[6 * n + 2 * MAX_PAGE_DELTAS:6 * n + 3 * MAX_PAGE_DELTAS])
+
+    def _step(self, bs: int) -> torch.Tensor:
+        r = self.runner
+        v = self._views(bs)
+        from ..ops import native
+        # page-table deltas: unused entries point at the padding row, which stays zero
+        native.page_table_scatter(r.req_to_token_pool.page_table, v["d_rows"], v["d_pos"], v["d_ids"])
+        ids = native.resolve_future(v["input_ids"], r.future_token_ids_map)
+        fb = ForwardBatch(
+            forward_mode=ForwardMode.DECODE, batch_size=bs, num_tokens=bs, input_ids=ids, positions=v["positions"],
+            out_cache_loc=v["out_cache_loc"], req_pool_indices=v["req_pool_indices"], seq_lens=v["seq_lens"],
+            page_table=r.req_to_token_pool.page_table, page_size=r.page_size,
+            max_seq_len=r.model_config.context_len, token_to_kv_pool=r.token_to_kv_pool,
+            attn_backend=r.attn_backend, in_graph=True)
+        out = r.model(ids, fb)
+        tok = native.argmax(out.next_token_logits)
+        r.future_token_ids_map[v["future_slots"].long()] = tok
+        return tok
+
+    def capture_all(self):
+        r = self.runner
+        logger.info("capturing CUDA graphs for decode batch sizes %s", self.buckets)
+        # make the padded inputs valid before the warm-up runs
+        self._fill_padding(0, self.max_bs)
+        with torch.inference_mode():
+            for bs in reversed(self.buckets):
+                torch.cuda.synchronize()
+                s = self.stream
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    for _ in range(2):
+                        self._step(bs)     # warm-up: lazy inits (function attributes, scratch) happen here
+                torch.cuda.current_stream().wait_stream(s)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                from ..ops import native
+                n0 = native.launch_count
+                with torch.cuda.graph(g, pool=self.pool, stream=s):
+                    out = self._step(bs)
+                # kernels of this library inside one replay (torch's own small ops not counted)
+                self.kernels_per_graph = native.launch_count - n0
+                self.pool = self.pool or g.pool()
+                self.graphs[bs] = g
+                self.outputs[bs] = out
+        torch.cuda.synchronize()
+
+    def _fill_padding(self, lo: int, hi: int):
+        n = self.max_bs
+        h = self.host.numpy()
+        h[0 * n + lo:0 * n + hi] = 0
+        h[1 * n + lo:1 * n + hi] = 0
+        h[2 * n + lo:2 * n + hi] = 0
+        h[3 * n + lo:3 * n + hi] = self.pad_row
+        h[4 * n + lo:4 * n + hi] = 1
+        h[5 * n + lo:5 * n + hi] = 0
+        h[6 * n:6 * n + MAX_PAGE_DELTAS] = self.pad_row
+        h[6 * n + MAX_PAGE_DELTAS:] = 0
+        self.buf.copy_(self.host, non_blocking=False)
+
+    # ------------------------------------------------------------------
+    def can_run(self, batch: ModelWorkerBatch) -> bool:
+        si = batch.sampling_info
+        return (self.enabled and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
+                and not batch.return_logprob and batch.capture_hidden_mode == 0 and batch.spec_info is None
+                and (si is None or (si.is_all_greedy and si.linear_penalty is None and si.vocab_mask is None
+                                    and si.logit_bias is None))
+                and (batch.page_delta_rows is None or len(batch.page_delta_rows) <= MAX_PAGE_DELTAS)
+                and not any(batch.lora_ids or []))
+
+    def replay(self, batch: ModelWorkerBatch):
+        r = self.runner
+        bs = len(batch.req_pool_indices)
+        bucket = self.buckets[bisect.bisect_left(self.buckets, bs)]
+        if bucket not in self.graphs:
+            # capture on demand (only when precompile was disabled); counted like a jit cache miss
+            r.graph_recaptures += 1
+            self._capture_one(bucket)
+        n = self.max_bs
+        if self.copy_event is not None:
+            self.copy_event.synchronize()     # the previous step's H2D has consumed the pinned buffer
+        h = self.host.numpy()
+        h[0:bs] = batch.input_ids
+        h[n:n + bs] = batch.positions
+        h[2 * n:2 * n + bs] = batch.out_cache_loc
+        h[3 * n:3 * n + bs] = batch.req_pool_indices
+        h[4 * n:4 * n + bs] = batch.seq_lens
+        h[5 * n:5 * n + bs] = batch.future_slots if batch.future_slots is not None else 0
+        if bucket > bs:
+            h[0:n][bs:bucket] = 0
+            h[n:2 * n][bs:bucket] = 0
+            h[2 * n:3 * n][bs:bucket] = 0
+            h[3 * n:4 * n][bs:bucket] = self.pad_row
+            h[4 * n:5 * n][bs:bucket] = 1
+            h[5 * n:6 * n][bs:bucket] = 0
+        nd = 0 if batch.page_delta_rows is None else len(batch.page_delta_rows)
+        d0 = 6 * n
+        h[d0:d0 + MAX_PAGE_DELTAS] = self.pad_row
+        h[d0 + MAX_PAGE_DELTAS:d0 + 3 * MAX_PAGE_DELTAS] = 0
+        if nd:
+            h[d0:d0 + nd] = batch.page_delta_rows
+            h[d0 + MAX_PAGE_DELTAS:d0 + MAX_PAGE_DELTAS + nd] = batch.page_delta_pos
+            h[d0 + 2 * MAX_PAGE_DELTAS:d0 + 2 * MAX_PAGE_DELTAS + nd] = batch.page_delta_ids
+        self.buf.copy_(self.host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.copy_event = ev
+        self.graphs[bucket].replay()
+        r.graph_replays += 1
+        r.h2d_bytes_total += self.host.numel() * 4
+        return None, self.outputs[bucket][:bs], None
+
+    def _capture_one(self, bs: int):
+        with torch.inference_mode():
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            s = self.stream
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._step(bs)
+            torch.cuda.current_stream().wait_stream(s)
+            with torch.cuda.graph(g, pool=self.pool, stream=s):
+                out = self._step(bs)
+            self.pool = self.pool or g.pool()
+            self.graphs[bs] = g
+            self.outputs[bs] = out

@@ -48,6 +48,7 @@ class ModelRunner:
         self.forward_ct = 0
         self.graph_replays = 0
         self.graph_recaptures = 0
+        self.h2d_bytes_total = 0
 
         t0 = time.time()
         free_before = self._free_mem()
@@ -182,6 +183,7 @@ class ModelRunner:
         if gr is not None and gr.can_run(batch):
             return gr.replay(batch)
         fb = ForwardBatch.init_new(batch, self)
+        self.h2d_bytes_total += fb.h2d_bytes
         if self.server_args is not None and not self.server_args.disable_overlap_schedule:
             fb.input_ids = self.resolve_future_token_ids(fb.input_ids)
         out = self.model(fb.input_ids, fb)

@@ -95,8 +95,5 @@ def argmax(logits):
 
 def topk_route(router_logits, top_k, scoring="softmax", renormalize=True, correction_bias=None,
                num_expert_group=0, topk_group=0, routed_scaling_factor=1.0):
-    if (not _FORCE_REFERENCE) and router_logits.is_cuda and router_logits.shape[-1] <= 512:
-        return _native().topk_route(router_logits, top_k, scoring, renormalize, correction_bias,
-                                    num_expert_group, topk_group, routed_scaling_factor)
     return reference.topk_route(router_logits, top_k, scoring, renormalize, correction_bias,
                                 num_expert_group, topk_group, routed_scaling_factor)

@@ -1,0 +1,252 @@
+"""ctypes bindings of `libsglb200.so` (the sm_100a kernels under `csrc/`).
+
+The library has a plain C ABI: raw device pointers, sizes and a `cudaStream_t`.  Tensors
+are passed by `data_ptr()`, outputs are allocated here with torch (which also makes them
+CUDA-graph capturable), and every launch goes to torch's current stream.  A non-zero
+return code raises; `check_status()` reads the device status word that bounded waits
+write when they give up.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
+
+import torch
+
+_LIB = None
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsglb200.so")
+LOADED = False
+
+
+def lib():
+    global _LIB, LOADED
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(_LIB_PATH):
+        # source checkout on a box with nvcc: build on first use
+        try:
+            from ..csrc.build import build
+            build()
+        except Exception as e:
+            raise RuntimeError(
+                f"native kernel library {_LIB_PATH} is missing and could not be built ({e}); "
+                f"run `python -m sglang_jax_b200.csrc.build`") from e
+    L = ctypes.CDLL(_LIB_PATH)
+    L.sglb_version.restype = ctypes.c_char_p
+    L.sglb_gemm_workspace_bytes.restype = c_size_t
+    L.sglb_gemm_workspace_bytes.argtypes = [c_int, c_int, c_int]
+    L.sglb_gemm_max_counters.argtypes = [c_int]
+    L.sglb_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t,
+                                 c_void_p, c_int, c_int, c_void_p]
+    L.sglb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float, c_int, c_void_p]
+    L.sglb_fused_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float, c_int,
+                                         c_void_p]
+    L.sglb_silu_and_mul.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p]
+    L.sglb_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p]
+    L.sglb_argmax.argtypes = [c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p]
+    L.sglb_rope_qknorm_kvwrite.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                           c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                           c_void_p]
+    L.sglb_page_table_scatter.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    L.sglb_resolve_future.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
+    L.sglb_decode_num_splits.argtypes = [c_int, c_int, c_int]
+    L.sglb_paged_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_int, c_void_p,
+                                    c_void_p, c_void_p]
+    L.sglb_paged_extend.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                    c_float, c_void_p]
+    L.sglb_read_status.argtypes = [c_void_p]
+    _LIB = L
+    LOADED = True
+    return L
+
+
+# number of kernel launches issued through this module (bench bookkeeping)
+launch_count = 0
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str):
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise RuntimeError(f"native op {what} failed with code {rc}")
+
+
+def _p(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def check_status():
+    """Raise if a kernel recorded a bounded-wait timeout (synchronises the device)."""
+    buf = (c_int * 4)()
+    code = lib().sglb_read_status(buf)
+    if code != 0:
+        names = {1: "timeout waiting for TMA data", 2: "timeout waiting for a free stage",
+                 3: "timeout waiting for the accumulator", 4: "timeout waiting for TMEM to drain",
+                 5: "timeout waiting for a peer flag", 6: "bad argument"}
+        raise RuntimeError(f"kernel status {code} ({names.get(code, '?')}), block={buf[1]} aux=({buf[2]}, {buf[3]})")
+
+
+# ------------------------------------------------------------------------------------ ops
+def rmsnorm(x, w, eps, gemma=False):
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    H = x.shape[-1]
+    _check(lib().sglb_rmsnorm(_p(y), _p(x), _p(w), x.numel() // H, H, eps, int(gemma), _stream()), "rmsnorm")
+    return y
+
+
+def fused_add_rmsnorm(x, residual, w, eps, gemma=False):
+    """Updates `residual` in place; returns (normed, residual)."""
+    x = x.contiguous()
+    assert residual.is_contiguous()
+    y = torch.empty_like(x)
+    H = x.shape[-1]
+    _check(lib().sglb_fused_add_rmsnorm(_p(y), _p(x), _p(residual), _p(w), x.numel() // H, H, eps, int(gemma),
+                                        _stream()), "fused_add_rmsnorm")
+    return y, residual
+
+
+def silu_and_mul(x):
+    x = x.contiguous()
+    I = x.shape[-1] // 2
+    out = torch.empty((*x.shape[:-1], I), dtype=x.dtype, device=x.device)
+    _check(lib().sglb_silu_and_mul(_p(out), _p(x), x.numel() // (2 * I), I, _stream()), "silu_and_mul")
+    return out
+
+
+class _GemmScratch:
+    """Per-device split-K workspace (fp32 partial tiles) and tile counters.  Allocated once,
+    outside any CUDA-graph capture, and shared by every GEMM on the stream (launches on one
+    stream are ordered, and the kernel leaves the counters zeroed)."""
+
+    def __init__(self, device):
+        self.bytes = 64 << 20
+        self.workspace = torch.empty(self.bytes, dtype=torch.uint8, device=device)
+        self.counters = torch.zeros(4096, dtype=torch.int32, device=device)
+
+
+_scratch: dict = {}
+
+
+def gemm_scratch(device) -> _GemmScratch:
+    key = (device.type, device.index)
+    s = _scratch.get(key)
+    if s is None:
+        s = _GemmScratch(device)
+        _scratch[key] = s
+    return s
+
+
+def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0):
+    K = x.shape[-1]
+    N = w.shape[0]
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    if K % 8 or N % 8 or not w.is_contiguous() or x2.data_ptr() % 16 or w.data_ptr() % 16:
+        from . import reference
+        return reference.linear(x, w, bias)
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return out.view(*x.shape[:-1], N)
+    sc = gemm_scratch(x.device)
+    _check(lib().sglb_gemm_bf16(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _p(sc.workspace), sc.bytes,
+                                _p(sc.counters), force_mode, force_splits, _stream()), "gemm_bf16")
+    return out.view(*x.shape[:-1], N)
+
+
+def rope_qknorm_kvwrite(qkv, positions, cos_sin, q_norm_w, k_norm_w, eps, num_q_heads, num_kv_heads, head_dim,
+                        kv_buffer, out_cache_loc, page_size, is_neox=True, rotary_dim=None):
+    qkv = qkv.contiguous()
+    T = qkv.shape[0]
+    rd = rotary_dim or head_dim
+    if (is_neox and cos_sin is not None and (rd // 2) % 32 != 0) or head_dim not in (64, 128, 256) \
+            or positions.dtype != torch.int32 or (out_cache_loc is not None and out_cache_loc.dtype != torch.int32):
+        from . import reference
+        return reference.rope_qknorm_kvwrite(qkv, positions, cos_sin, q_norm_w, k_norm_w, eps, num_q_heads,
+                                             num_kv_heads, head_dim, kv_buffer, out_cache_loc, page_size, is_neox,
+                                             rotary_dim)
+    q = torch.empty((T, num_q_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    _check(lib().sglb_rope_qknorm_kvwrite(_p(q), _p(qkv), _p(positions), _p(cos_sin), _p(q_norm_w), _p(k_norm_w),
+                                          eps, T, num_q_heads, num_kv_heads, head_dim, rd, _p(kv_buffer),
+                                          _p(out_cache_loc), page_size, int(is_neox), _stream()),
+           "rope_qknorm_kvwrite")
+    return q
+
+
+def decode_num_splits(B: int, Hkv: int, max_seq_len: int) -> int:
+    return lib().sglb_decode_num_splits(B, Hkv, max(max_seq_len, 1))
+
+
+def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale, cu_q_lens=None,
+                    prefix_lens=None, sliding_window=0, soft_cap=0.0, max_q_len=0, max_seq_len=0, num_splits=None):
+    T, Hq, D = q.shape
+    Hkv = kv_buffer.shape[2]
+    B = req_pool_indices.shape[0]
+    ok_page = (64 % page_size == 0) if page_size < 64 else (page_size % 64 == 0)
+    if not ok_page or Hq // Hkv > 16:
+        from . import reference
+        return reference.paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
+                                         cu_q_lens, prefix_lens, sliding_window, soft_cap)
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    num_pages = kv_buffer.shape[0]
+    max_pages = page_table.shape[1]
+    L = lib()
+    if cu_q_lens is None:
+        if num_splits is None:
+            num_splits = decode_num_splits(B, Hkv, max_seq_len or page_table.shape[1] * page_size)
+        part_o = part_lse = None
+        if num_splits > 1:
+            part_o = torch.empty((B, Hq, num_splits, D), dtype=torch.float32, device=q.device)
+            part_lse = torch.empty((B, Hq, num_splits), dtype=torch.float32, device=q.device)
+        _check(L.sglb_paged_decode(_p(q), _p(out), _p(kv_buffer), num_pages, _p(page_table), max_pages,
+                                   _p(req_pool_indices), _p(seq_lens), B, Hq, Hkv, D, page_size, scale,
+                                   int(sliding_window or 0), float(soft_cap or 0.0), num_splits, _p(part_o),
+                                   _p(part_lse), _stream()), "paged_decode")
+    else:
+        bound = T // 64 + B
+        _check(L.sglb_paged_extend(_p(q), _p(out), _p(kv_buffer), num_pages, _p(page_table), max_pages,
+                                   _p(req_pool_indices), _p(seq_lens), _p(prefix_lens), _p(cu_q_lens), B, bound, Hq,
+                                   Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
+                                   _stream()), "paged_extend")
+    return out
+
+
+def embedding(ids, table, vocab_start=0, masked=False):
+    ids = ids.contiguous()
+    T = ids.numel()
+    H = table.shape[1]
+    out = torch.empty((T, H), dtype=table.dtype, device=table.device)
+    _check(lib().sglb_embedding(_p(out), _p(ids), _p(table), T, H, table.shape[0], vocab_start, int(masked),
+                                _stream()), "embedding")
+    return out.view(*ids.shape, H)
+
+
+def argmax(logits):
+    assert logits.dim() == 2 and logits.stride(1) == 1
+    B, V = logits.shape
+    out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    _check(lib().sglb_argmax(_p(out), _p(logits), B, V, logits.stride(0), logits.element_size(), _stream()),
+           "argmax")
+    return out
+
+
+def page_table_scatter(table, rows, pos, ids):
+    n = rows.numel()
+    _check(lib().sglb_page_table_scatter(_p(table), table.shape[1], _p(rows), _p(pos), _p(ids), n, _stream()),
+           "page_table_scatter")
+
+
+def resolve_future(ids, future_map):
+    _check(lib().sglb_resolve_future(_p(ids), _p(future_map), ids.numel(), _stream()), "resolve_future")
+    return ids

@@ -1,0 +1,174 @@
+"""Numerics of every sm_100a kernel against the plain-PyTorch fp32 statement of the same op."""
+
+import math
+
+import pytest
+import torch
+
+from sglang_jax_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native():
+    from sglang_jax_b200.ops import native
+    native.lib()
+    yield native
+    torch.cuda.synchronize()
+    native.check_status()
+
+
+def _bf16(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+def _close(a, b, atol, rtol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).float().mean().item()
+    assert bad < 1e-4, f"max err {err.max().item():.4g}, {bad * 100:.3f}% outside tol"
+
+
+@pytest.mark.parametrize("T,H", [(1, 256), (7, 5120), (128, 5120), (33, 8192), (5, 2048)])
+def test_rmsnorm(native, T, H):
+    x, w = _bf16(T, H, seed=1), _bf16(H, seed=2) * 0.1 + 1
+    _close(native.rmsnorm(x, w, 1e-6), ref.rmsnorm(x.float(), w.float(), 1e-6), 2e-2, 2e-2)
+    r = _bf16(T, H, seed=3)
+    r2 = r.clone()
+    y, rout = native.fused_add_rmsnorm(x, r2, w, 1e-6)
+    ey, er = ref.fused_add_rmsnorm(x, r, w, 1e-6)
+    assert torch.equal(rout, er)
+    _close(y, ey, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("T,I", [(1, 512), (130, 25600), (4096, 3200)])
+def test_silu_and_mul(native, T, I):
+    x = _bf16(T, 2 * I, seed=4)
+    _close(native.silu_and_mul(x), ref.silu_and_mul(x.float()), 1e-2, 2e-2)
+
+
+def test_embedding_argmax(native):
+    table = _bf16(1000, 256, seed=5)
+    ids = torch.randint(0, 1000, (77,), device="cuda", dtype=torch.int32)
+    assert torch.equal(native.embedding(ids, table), table[ids.long()])
+    assert torch.equal(native.embedding(ids, table[100:600].contiguous(), 100, True),
+                       ref.embedding(ids, table[100:600], 100, True))
+    for dt in (torch.float32, torch.bfloat16):
+        logits = torch.randn(9, 151936, device="cuda").to(dt)
+        logits[3, 77] = logits[3, 5000] = 100.0     # tie: first index wins
+        assert torch.equal(native.argmax(logits).long(), torch.argmax(logits.float(), dim=-1))
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (1, 512, 256), (8, 5120, 5120), (16, 1024, 4096), (33, 6400, 5120), (128, 5120, 8192),
+    (128, 10240, 5120), (200, 2048, 1024), (256, 512, 25600),
+    (257, 512, 512), (512, 5120, 5120), (1000, 768, 2048), (4096, 5120, 3200), (300, 1032, 264),
+])
+def test_gemm(native, M, N, K):
+    x = _bf16(M, K, seed=6)
+    w = _bf16(N, K, scale=0.05, seed=7)
+    b = _bf16(N, seed=8)
+    expect = x.float() @ w.float().t()
+    got = native.linear(x, w)
+    torch.cuda.synchronize()
+    native.check_status()
+    tol = 0.02 * math.sqrt(K) * 0.05 + 0.02
+    _close(got, expect, tol, 1.5e-2)
+    _close(native.linear(x, w, b), expect + b.float(), tol, 1.5e-2)
+
+
+@pytest.mark.parametrize("mode,splits", [(0, 1), (1, 1), (1, 2), (1, 5)])
+def test_gemm_forced_modes(native, mode, splits):
+    M, N, K = 96, 1024, 4096
+    x, w = _bf16(M, K, seed=9), _bf16(N, K, scale=0.05, seed=10)
+    got = native.linear(x, w, None, force_mode=mode, force_splits=splits)
+    torch.cuda.synchronize()
+    native.check_status()
+    _close(got, x.float() @ w.float().t(), 0.1, 1.5e-2)
+    # split-K leaves its tile counters clean
+    assert int(native.gemm_scratch(x.device).counters.abs().sum().item()) == 0
+
+
+def _make_cache(num_pages, Hkv, P, D, seed):
+    return _bf16(num_pages, 2, Hkv, P, D, seed=seed)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,qk_norm,neox", [(128, 8, 2, True, True), (128, 4, 4, False, True),
+                                                   (64, 4, 2, True, True), (128, 8, 1, False, False)])
+def test_rope_kvwrite(native, D, Hq, Hkv, qk_norm, neox):
+    T, P, pages = 37, 16, 12
+    qkv = _bf16(T, (Hq + 2 * Hkv) * D, seed=11)
+    pos = torch.randint(0, 4000, (T,), device="cuda", dtype=torch.int32)
+    loc = (torch.randperm((pages - 1) * P, device="cuda")[:T] + P).to(torch.int32)
+    cs = ref.build_cos_sin_cache(D, 4096, 1e6, device="cuda")
+    qw = (_bf16(D, seed=12) * 0.1 + 1) if qk_norm else None
+    kw = (_bf16(D, seed=13) * 0.1 + 1) if qk_norm else None
+    c1, c2 = torch.zeros(pages, 2, Hkv, P, D, device="cuda", dtype=torch.bfloat16), None
+    c2 = c1.clone()
+    q1 = native.rope_qknorm_kvwrite(qkv, pos, cs, qw, kw, 1e-6, Hq, Hkv, D, c1, loc, P, neox)
+    q2 = ref.rope_qknorm_kvwrite(qkv, pos, cs, qw, kw, 1e-6, Hq, Hkv, D, c2, loc, P, neox)
+    _close(q1, q2, 3e-2, 2e-2)
+    _close(c1, c2, 3e-2, 2e-2)
+
+
+def _attn_setup(B, seqs, P, Hkv, D, seed=0):
+    pages_per = [(s + P - 1) // P for s in seqs]
+    num_pages = sum(pages_per) + 3
+    cache = _make_cache(num_pages, Hkv, P, D, seed)
+    max_pages = max(pages_per) + 2
+    pt = torch.zeros(B + 3, max_pages, dtype=torch.int32, device="cuda")
+    perm = (torch.randperm(num_pages - 1, device="cuda") + 1).to(torch.int32)
+    o = 0
+    rows = torch.randperm(B + 2, device="cuda")[:B].to(torch.int32)
+    for b in range(B):
+        pt[rows[b], :pages_per[b]] = perm[o:o + pages_per[b]]
+        o += pages_per[b]
+    return cache, pt, rows
+
+
+@pytest.mark.parametrize("P", [16, 64, 128])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 1, 128), (16, 4, 128), (4, 2, 64)])
+def test_paged_decode(native, P, Hq, Hkv, D):
+    seqs = [1, 17, 64, 65, 300, 1000, 129, 2047]
+    B = len(seqs)
+    cache, pt, rows = _attn_setup(B, seqs, P, Hkv, D, seed=20)
+    q = _bf16(B, Hq, D, seed=21)
+    sl = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    scale = D ** -0.5
+    expect = ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale)
+    for splits in (1, 3, None):
+        got = native.paged_attention(q, cache, pt, rows, sl, P, scale, max_seq_len=max(seqs), num_splits=splits)
+        torch.cuda.synchronize()
+        native.check_status()
+        _close(got, expect, 2e-2, 2e-2)
+    got = native.paged_attention(q, cache, pt, rows, sl, P, scale, sliding_window=100, max_seq_len=max(seqs))
+    _close(got, ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, sliding_window=100), 2e-2, 2e-2)
+    got = native.paged_attention(q, cache, pt, rows, sl, P, scale, soft_cap=30.0, max_seq_len=max(seqs))
+    _close(got, ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, soft_cap=30.0), 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("P", [16, 64])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64)])
+def test_paged_extend(native, P, Hq, Hkv, D):
+    prefix = [0, 64, 5, 130, 0, 1]
+    ext = [1, 63, 64, 200, 513, 17]
+    seqs = [a + b for a, b in zip(prefix, ext)]
+    B = len(seqs)
+    cache, pt, rows = _attn_setup(B, seqs, P, Hkv, D, seed=30)
+    T = sum(ext)
+    q = _bf16(T, Hq, D, seed=31)
+    sl = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    pl = torch.tensor(prefix, dtype=torch.int32, device="cuda")
+    cu = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
+    cu[1:] = torch.tensor(ext, device="cuda").cumsum(0)
+    scale = D ** -0.5
+    got = native.paged_attention(q, cache, pt, rows, sl, P, scale, cu, pl)
+    torch.cuda.synchronize()
+    native.check_status()
+    _close(got, ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, cu, pl), 2e-2, 2e-2)
+    got = native.paged_attention(q, cache, pt, rows, sl, P, scale, cu, pl, sliding_window=70)
+    _close(got, ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, cu, pl, sliding_window=70),
+           2e-2, 2e-2)
