@@ -1,0 +1,135 @@
+#!/usr/bin/env python
+"""Kernel micro-benchmarks with roofline fractions (counterpart of the reference's
+`benchmark/kernels/*`): CUDA-event timing after warm-up, L2 flushed between iterations,
+achieved TFLOP/s or GB/s and the fraction of the measured peaks in MEASURED_PEAKS.json.
+
+    python benchmark/kernels/bench_kernels.py gemm attention elementwise
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from sglang_jax_b200.ops import native  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def timeit(fn, iters=20, warmup=3, flush=True):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm():
+    hbm, tf, src = peaks()
+    shapes = [  # (M, N, K, label)  Qwen3-32B TP1 and TP8 shards
+        (8192, 10240, 5120, "qkv prefill tp1"), (8192, 5120, 8192, "o prefill tp1"),
+        (8192, 51200, 5120, "gate_up prefill tp1"), (8192, 5120, 25600, "down prefill tp1"),
+        (8192, 6400, 5120, "gate_up prefill tp8"), (8192, 5120, 3200, "down prefill tp8"),
+        (4096, 10240, 5120, "qkv prefill 4k"), (1024, 5120, 5120, "mid"),
+        (128, 10240, 5120, "qkv decode tp1"), (128, 5120, 8192, "o decode tp1"),
+        (128, 51200, 5120, "gate_up decode tp1"), (128, 5120, 25600, "down decode tp1"),
+        (128, 1280, 5120, "qkv decode tp8"), (128, 6400, 5120, "gate_up decode tp8"),
+        (128, 5120, 3200, "down decode tp8"), (128, 18992, 5120, "lm_head decode tp8"),
+        (16, 51200, 5120, "gate_up bs16"), (1, 51200, 5120, "gate_up bs1"),
+    ]
+    print(f"{'shape':>28} {'label':>22} {'ours ms':>9} {'TFLOP/s':>9} {'GB/s':>8} {'roof%':>7} {'torch ms':>9} {'vs torch':>8}")
+    for M, N, K, label in shapes:
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        t = timeit(lambda: native.linear(x, w))
+        tt = timeit(lambda: torch.nn.functional.linear(x, w))
+        flops = 2.0 * M * N * K
+        byts = 2.0 * (M * K + N * K + M * N)
+        tfl = flops / t / 1e9
+        gbs = byts / t / 1e6
+        roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3   # ms at the roofline
+        print(f"{f'{M}x{N}x{K}':>28} {label:>22} {t:9.4f} {tfl:9.1f} {gbs:8.0f} {100 * roof / t:6.1f}% {tt:9.4f} {tt / t:8.2f}")
+    torch.cuda.synchronize()
+    native.check_status()
+    print(f"(roofline = slower of FLOPs / {tf} TFLOP/s and bytes / {hbm} GB/s, {src})")
+
+
+def bench_attention():
+    hbm, tf, src = peaks()
+    print(f"{'case':>40} {'ms':>9} {'GB/s':>8} {'of hbm':>7}")
+    D, P = 128, 64
+    for B, Hq, Hkv, S in [(128, 64, 8, 1400), (128, 8, 1, 1400), (128, 64, 8, 2300), (32, 64, 8, 4096), (256, 8, 1, 1400)]:
+        pages_per = (S + P - 1) // P
+        num_pages = B * pages_per + 1
+        cache = torch.randn(num_pages, 2, Hkv, P, D, device="cuda").bfloat16()
+        pt = (torch.arange(B * pages_per, device="cuda", dtype=torch.int32) + 1).view(B, pages_per).contiguous()
+        rows = torch.arange(B, device="cuda", dtype=torch.int32)
+        sl = torch.full((B,), S, device="cuda", dtype=torch.int32)
+        q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+        t = timeit(lambda: native.paged_attention(q, cache, pt, rows, sl, P, D ** -0.5, max_seq_len=S))
+        byts = B * S * 2 * Hkv * D * 2
+        print(f"{f'decode B={B} Hq={Hq} Hkv={Hkv} S={S}':>40} {t:9.4f} {byts / t / 1e6:8.0f} {100 * byts / t / 1e6 / hbm:6.1f}%")
+    print(f"{'case':>40} {'ms':>9} {'TFLOP/s':>8}")
+    for B, Hq, Hkv, S in [(4, 64, 8, 2048), (8, 8, 1, 1024), (1, 64, 8, 8192)]:
+        pages_per = (S + P - 1) // P
+        num_pages = B * pages_per + 1
+        cache = torch.randn(num_pages, 2, Hkv, P, D, device="cuda").bfloat16()
+        pt = (torch.arange(B * pages_per, device="cuda", dtype=torch.int32) + 1).view(B, pages_per).contiguous()
+        rows = torch.arange(B, device="cuda", dtype=torch.int32)
+        sl = torch.full((B,), S, device="cuda", dtype=torch.int32)
+        pl = torch.zeros(B, device="cuda", dtype=torch.int32)
+        cu = (torch.arange(B + 1, device="cuda", dtype=torch.int32) * S).contiguous()
+        q = torch.randn(B * S, Hq, D, device="cuda").bfloat16()
+        t = timeit(lambda: native.paged_attention(q, cache, pt, rows, sl, P, D ** -0.5, cu, pl), iters=5)
+        flops = 4.0 * B * Hq * D * S * S / 2
+        print(f"{f'extend B={B} Hq={Hq} Hkv={Hkv} S={S}':>40} {t:9.4f} {flops / t / 1e9:8.1f}")
+    torch.cuda.synchronize()
+    native.check_status()
+
+
+def bench_elementwise():
+    hbm, tf, src = peaks()
+    T, H, I = 8192, 5120, 25600
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    r = torch.randn(T, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda").bfloat16()
+    t = timeit(lambda: native.fused_add_rmsnorm(x, r, w, 1e-6))
+    print(f"fused_add_rmsnorm {T}x{H}: {t:.4f} ms, {4 * T * H * 2 / t / 1e6:.0f} GB/s ({100 * 4 * T * H * 2 / t / 1e6 / hbm:.1f}% of {src} copy bw)")
+    g = torch.randn(T, 2 * I // 8, device="cuda").bfloat16()
+    t = timeit(lambda: native.silu_and_mul(g))
+    print(f"silu_and_mul {T}x{I // 8}: {t:.4f} ms, {3 * T * (I // 8) * 2 / t / 1e6:.0f} GB/s")
+
+
+if __name__ == "__main__":
+    which = sys.argv[1:] or ["gemm", "attention", "elementwise"]
+    torch.manual_seed(0)
+    for w in which:
+        {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[w]()

@@ -54,8 +54,9 @@ class Engine(EngineBase):
                 kwargs["log_level"] = "error"
             server_args = ServerArgs(**kwargs)
         self.server_args = server_args
-        atexit.register(self.shutdown)
         self._shutdown_done = False
+        self.tokenizer_manager = None
+        atexit.register(self.shutdown)
         self._threads: list[threading.Thread] = []
         self._procs: list[mp.Process] = []
         self._stop = threading.Event()
@@ -181,7 +182,8 @@ class Engine(EngineBase):
             return
         self._shutdown_done = True
         self._stop.set()
-        self.tokenizer_manager.gracefully_exit = True
+        if getattr(self, "tokenizer_manager", None) is not None:
+            self.tokenizer_manager.gracefully_exit = True
         if self.scheduler is not None:
             try:
                 self.scheduler.shutdown()

@@ -98,7 +98,7 @@ class RotaryEmbedding(nn.Module):
         self.register_buffer("cos_sin_cache", self._compute_cos_sin_cache(), persistent=False)
 
     def _compute_inv_freq(self, base) -> torch.Tensor:
-        return 1.0 / (base ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim))
+        return 1.0 / (base ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32, device="cpu") / self.rotary_dim))
 
     def _mscale(self) -> float:
         return 1.0
@@ -165,7 +165,7 @@ class YarnRotaryEmbedding(RotaryEmbedding):
         return self.mscale_value
 
     def _compute_inv_freq(self, base):
-        pos_freqs = base ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim)
+        pos_freqs = base ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32, device="cpu") / self.rotary_dim)
         extra = 1.0 / pos_freqs
         inter = 1.0 / (self.scaling_factor * pos_freqs)
         low = max(math.floor(_yarn_find_correction_dim(self.beta_fast, self.rotary_dim, base, self.orig_max_pos)), 0)
@@ -173,7 +173,7 @@ class YarnRotaryEmbedding(RotaryEmbedding):
                    self.rotary_dim - 1)
         if low == high:
             high += 0.001
-        ramp = ((torch.arange(self.rotary_dim // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+        ramp = ((torch.arange(self.rotary_dim // 2, dtype=torch.float32, device="cpu") - low) / (high - low)).clamp(0, 1)
         mask = (1 - ramp) * self.extrapolation_factor
         return inter * (1 - mask) + extra * mask
 
@@ -189,8 +189,8 @@ class ProportionalRotaryEmbedding(RotaryEmbedding):
     def _compute_inv_freq(self, base):
         half = self.rotary_dim // 2
         n_rot = int(half * self.partial)
-        inv = 1.0 / (base ** (torch.arange(0, 2 * n_rot, 2, dtype=torch.float32) / self.rotary_dim))
-        return torch.cat([inv, torch.zeros(half - n_rot)])
+        inv = 1.0 / (base ** (torch.arange(0, 2 * n_rot, 2, dtype=torch.float32, device="cpu") / self.rotary_dim))
+        return torch.cat([inv, torch.zeros(half - n_rot, device="cpu")])
 
 
 class MRotaryEmbedding(RotaryEmbedding):

@@ -45,11 +45,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
 
 
 def build_cos_sin_cache(rotary_dim: int, max_pos: int, base: float, inv_freq: torch.Tensor | None = None,
-                        mscale: float = 1.0, device="cpu") -> torch.Tensor:
-    """fp32 `[max_pos, rotary_dim]`: first half cos, second half sin."""
+                        mscale: float = 1.0, device=None) -> torch.Tensor:
+    """fp32 `[max_pos, rotary_dim]`: first half cos, second half sin.  Computed on the host in
+    fp32 and then moved to `device` (default: the ambient default device)."""
+    if device is None:
+        device = torch.empty(0).device
     if inv_freq is None:
-        inv_freq = 1.0 / (base ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
-    t = torch.arange(max_pos, dtype=torch.float32)
+        inv_freq = 1.0 / (base ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32, device="cpu") / rotary_dim))
+    t = torch.arange(max_pos, dtype=torch.float32, device="cpu")
     freqs = torch.outer(t, inv_freq.float().cpu())
     return torch.cat([freqs.cos() * mscale, freqs.sin() * mscale], dim=-1).to(device)
 
