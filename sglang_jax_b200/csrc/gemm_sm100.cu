@@ -19,7 +19,12 @@
 //
 // The reference project has no counterpart kernel: its dense projections are
 // `lax.dot_general` calls lowered by XLA (python/sgl_jax/srt/layers/linear.py:102).
+#include <stdio.h>
+
+#include <mutex>
+
 #include "common.cuh"
+#include "gemm_noalloc.h"
 
 namespace sglb {
 namespace {
@@ -439,5 +444,147 @@ int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, in
     }
   }
   return err == cudaSuccess ? 0 : static_cast<int>(err);
+}
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in gemm_noalloc.h).
+//
+// Same decode-shaped GEMM (weights on the MMA M dimension, K split over CTAs), but every byte of
+// scratch it needs — split-K partial tiles, tile counters and its status word — lives in the
+// file-scope device array below, so the call performs no cudaMalloc / cudaFree and calls no
+// allocating library routine.  The array is part of the library image: each GPU that loads the
+// library carries kNoAllocScratchBytes of it until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace sglb {
+namespace {
+
+constexpr size_t kNoAllocHeaderBytes = 8192;                       // status word + tile counters
+constexpr size_t kNoAllocCounterOffset = 256;                      // counters start here
+constexpr int kNoAllocMaxCounters = (kNoAllocHeaderBytes - kNoAllocCounterOffset) / sizeof(int);
+constexpr size_t kNoAllocWorkspaceBytes = size_t(8) << 20;         // 8 MiB of fp32 partial tiles
+constexpr size_t kNoAllocScratchBytes = kNoAllocHeaderBytes + kNoAllocWorkspaceBytes;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// Host code may not use `g_noalloc_scratch` as a pointer: on the host that name is only a handle
+// for the runtime.  The device address is looked up once per device, with that device current.
+unsigned char* g_noalloc_dev_ptr[16] = {};
+std::mutex g_noalloc_mu;
+thread_local char g_noalloc_error[256] = "";
+
+unsigned char* noalloc_scratch_ptr(int* rc) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 16) {
+    *rc = e != cudaSuccess ? static_cast<int>(e) : -kBadArgument;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_dev_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *rc = e != cudaSuccess ? static_cast<int>(e) : -kBadArgument;
+      return nullptr;
+    }
+    g_noalloc_dev_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *rc = 0;
+  return g_noalloc_dev_ptr[dev];
+}
+
+}  // namespace
+}  // namespace sglb
+
+extern "C" {
+
+size_t sglb_gemm_bf16_noalloc_scratch_bytes() { return sglb::kNoAllocScratchBytes; }
+
+const char* sglb_gemm_bf16_noalloc_last_error() { return sglb::g_noalloc_error; }
+
+int sglb_gemm_bf16_noalloc(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                           int splits, cudaStream_t stream) {
+  using namespace sglb;
+  auto fail = [&](int code, const char* fmt, long long a = 0, long long b = 0) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), fmt, a, b);
+    return code;
+  };
+  g_noalloc_error[0] = 0;
+  if (M <= 0 || N <= 0 || K <= 0) return fail(-kBadArgument, "M, N and K must be positive");
+  if (M > 256) return fail(-kBadArgument, "M = %lld exceeds the 256-token limit of the allocation-free GEMM", M);
+  if ((K % 8) || (N % 8)) return fail(-kBadArgument, "N and K must be multiples of 8");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(-kBadArgument, "x, w and out must be 16-byte aligned");
+  const int kb_total = (K + BK - 1) / BK;
+  const int bn = pick_bn_tokens(M);
+  const int tiles = (N + BM - 1) / BM;
+  const int sms = sm_count();
+  if (splits <= 0) {
+    splits = (sms + tiles - 1) / tiles;
+    splits = min(splits, max(1, kb_total / 8));
+    splits = min(splits, 16);
+    // auto mode never asks for more scratch than the static array holds
+    while (splits > 1 && static_cast<size_t>(tiles) * splits * BM * bn * sizeof(float) > kNoAllocWorkspaceBytes) --splits;
+  }
+  while (splits > 1 && (kb_total + splits - 1) / splits * (splits - 1) >= kb_total) --splits;
+  const size_t need = splits > 1 ? static_cast<size_t>(tiles) * splits * BM * bn * sizeof(float) : 0;
+  if (need > kNoAllocWorkspaceBytes)
+    return fail(-kBadArgument, "split-K partials need %lld bytes but the static scratch holds %lld; lower `splits`",
+                static_cast<long long>(need), static_cast<long long>(kNoAllocWorkspaceBytes));
+  if (splits > 1 && tiles > kNoAllocMaxCounters)
+    return fail(-kBadArgument, "N needs %lld tile counters but the static scratch holds %lld", tiles,
+                kNoAllocMaxCounters);
+  int rc = 0;
+  unsigned char* scratch = noalloc_scratch_ptr(&rc);
+  if (scratch == nullptr) return fail(rc, "cudaGetSymbolAddress failed for the static scratch (code %lld)", rc);
+  // The array keeps whatever the previous call left: status word and counters must start at zero.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, kNoAllocHeaderBytes, stream);
+  if (e != cudaSuccess) return fail(static_cast<int>(e), "cudaMemsetAsync failed (code %lld)", e);
+
+  Params p{};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.status = reinterpret_cast<Status*>(scratch);
+  p.counters = reinterpret_cast<int*>(scratch + kNoAllocCounterOffset);
+  p.workspace = reinterpret_cast<float*>(scratch + kNoAllocHeaderBytes);
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.kb_total = kb_total;
+  p.splits = splits;
+  p.tiles_a = tiles;
+  p.tiles_b = 1;
+  CUtensorMap ta, tb;
+  if (!encode_tmap_2d(&ta, w, K, N, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return fail(-100, "tensor map (w) failed");
+  if (!encode_tmap_2d(&tb, x, K, M, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return fail(-101, "tensor map (x) failed");
+  const int grid = min(tiles * splits, sms);
+  switch (bn) {
+    case 16: e = launch<16, 1>(ta, tb, p, grid, stream); break;
+    case 32: e = launch<32, 1>(ta, tb, p, grid, stream); break;
+    case 64: e = launch<64, 1>(ta, tb, p, grid, stream); break;
+    case 128: e = launch<128, 1>(ta, tb, p, grid, stream); break;
+    default: e = launch<256, 1>(ta, tb, p, grid, stream); break;
+  }
+  if (e != cudaSuccess) return fail(static_cast<int>(e), "kernel launch failed (code %lld)", e);
+  return 0;
+}
+
+// Copies the entry point's status word (code, block, aux0, aux1) to the host; synchronises.
+int sglb_gemm_bf16_noalloc_status(int* out4) {
+  using namespace sglb;
+  int rc = 0;
+  unsigned char* scratch = noalloc_scratch_ptr(&rc);
+  if (scratch == nullptr) return rc;
+  Status h;
+  cudaError_t e = cudaMemcpy(&h, scratch, sizeof(h), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (out4) {
+    out4[0] = h.code;
+    out4[1] = h.block;
+    out4[2] = h.aux0;
+    out4[3] = h.aux1;
+  }
+  return h.code;
 }
 }
