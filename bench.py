@@ -223,7 +223,7 @@ def main():
                 state["tokens"] += len(batch.reqs)
                 state["d2h"] += 4 * len(batch.reqs)
             else:
-                n_out = sum(1 for r in batch.reqs if not r.is_chunked)
+                n_out = sum(1 for r in batch.reqs if r is not batch.chunked_req)
                 state["tokens"] += n_out
                 state["d2h"] += 4 * len(batch.reqs)
         if state["steps"] == W and state["phase"] == "warmup":

@@ -664,8 +664,11 @@ class ScheduleBatch:
         reqs = self.reqs
         pool = self.req_to_token_pool
         alloc = self.token_to_kv_pool_allocator
-        if self.output_ids is not None and len(self.output_ids) == len(reqs):
-            self.input_ids = np.asarray(self.output_ids, dtype=np.int32)
+        if self.enable_overlap:
+            # The previous step may still be in flight: feed placeholders `-(row + 1)`.  The
+            # future-token map slot of a row always holds the latest token sampled for the
+            # request that occupies the row, whether or not the host has seen it yet.
+            self.input_ids = -(np.asarray([r.req_pool_idx for r in reqs], dtype=np.int32) + 1)
         else:
             self.input_ids = np.asarray([r.output_ids[-1] if r.output_ids else r.origin_input_ids[-1]
                                          for r in reqs], dtype=np.int32)

@@ -279,8 +279,6 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                 self._drain_results()
             result = self.run_batch(batch)
             self.result_queue.append((batch.copy(), result))
-            # the next step reads this step's tokens through the future map
-            batch.output_ids = -(batch.req_pool_indices.astype(np.int32) + 1)
         if len(self.result_queue) > (1 if batch is not None else 0):
             b, r = self.result_queue.popleft()
             self.process_batch_result(b, r)
@@ -559,8 +557,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             mwb.future_slots = (mwb.req_pool_indices.astype(np.int64) + 1)
             if mwb.forward_mode.is_extend():
                 # rows of non-final chunks produce no token; park their sample in the spare slot 0
-                chunk_rows = np.array([r.is_chunked > 0 and i < len(batch.reqs) - batch.num_decode_in_mixed
-                                       for i, r in enumerate(batch.reqs)])
+                # (`is_chunked` lags one step in overlap mode; `batch.chunked_req` is exact)
+                chunk_rows = np.array([r is batch.chunked_req for r in batch.reqs])
                 mwb.future_slots = np.where(chunk_rows, 0, mwb.future_slots)
         if batch.has_grammar:
             self._fill_vocab_mask(batch, mwb)

@@ -224,6 +224,7 @@ class MockModelWorker:
                                             "sliding_window": None, "num_experts": None})()
         self.forward_ct = 0
         self.batches: list[ModelWorkerBatch] = []
+        self.future_map = np.zeros(self.req_to_token_pool.size + 2, np.int32)
 
     def get_worker_info(self):
         return (self.max_total_num_tokens, self.max_prefill_tokens, self.max_running_requests, self.max_req_len,
@@ -238,12 +239,18 @@ class MockModelWorker:
         self.batches.append(batch)
         # next token = (sum of the sequence's current length and last input id) mod vocab: cheap,
         # deterministic and independent of batch composition
+        input_ids = np.asarray(batch.input_ids).copy()
+        neg = input_ids < 0
+        if neg.any():   # overlap mode: placeholders -slot resolve through the future map
+            input_ids[neg] = self.future_map[-input_ids[neg]]
         if batch.forward_mode.is_extend():
             last = np.cumsum(batch.extend_seq_lens) - 1
-            last_ids = batch.input_ids[last]
+            last_ids = input_ids[last]
         else:
-            last_ids = batch.input_ids
-        ids = ((np.abs(last_ids).astype(np.int64) * 31 + batch.seq_lens) % self.vocab_size).astype(np.int32)
+            last_ids = input_ids
+        ids = ((last_ids.astype(np.int64) * 31 + batch.seq_lens) % self.vocab_size).astype(np.int32)
+        if batch.future_slots is not None:
+            self.future_map[np.asarray(batch.future_slots)] = ids
         if launch_done is not None:
             launch_done.set()
         return GenerationBatchResult(None, ids, bid=batch.bid)

@@ -146,10 +146,14 @@ def all_gather(x: torch.Tensor, dim: int = -1, group: GroupInfo | None = None) -
     g = group or _STATE.tp
     if g.size == 1:
         return x
-    out = torch.empty((g.size, *x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(out, x.contiguous(), group=g.device_group)
+    x = x.contiguous()
+    flat = torch.empty((g.size * x.shape[0], *x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(flat, x, group=g.device_group)
     if dim < 0:
         dim += x.dim()
+    if dim == 0:
+        return flat
+    out = flat.view(g.size, *x.shape)
     return out.movedim(0, dim).reshape(*x.shape[:dim], g.size * x.shape[dim], *x.shape[dim + 1:])
 
 
