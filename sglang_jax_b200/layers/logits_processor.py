@@ -44,8 +44,11 @@ class LogitsProcessor(nn.Module):
         self.soft_cap = soft_cap
         self.skip_all_gather = skip_all_gather
 
-    def _project(self, hidden: torch.Tensor, lm_head) -> torch.Tensor:
+    def _project(self, hidden: torch.Tensor, lm_head, local_only: bool = False) -> torch.Tensor:
         logits = ops.linear(hidden, lm_head.weight)
+        if local_only:
+            # this rank's vocab shard (padding columns included); the sampler reduces across ranks
+            return logits
         if lm_head.tp_size > 1 and not self.skip_all_gather:
             comm = ps.get_state().fused_comm
             if comm is not None and comm.supports_logits_gather(logits):
@@ -63,7 +66,10 @@ class LogitsProcessor(nn.Module):
             last = hidden_states
         else:
             last = hidden_states[fb.last_token_indices]
-        out = LogitsProcessorOutput(next_token_logits=self._project(last, lm_head))
+        local_only = bool(fb.extras.get("skip_logits_gather")) and lm_head.tp_size > 1 and not self.soft_cap
+        out = LogitsProcessorOutput(next_token_logits=self._project(last, lm_head, local_only))
+        if local_only:
+            out.extras["vocab_shard"] = (lm_head.vocab_start, self.vocab_size)
         if fb.capture_hidden_mode == 1:
             out.hidden_states = last
         elif fb.capture_hidden_mode == 2:

@@ -75,8 +75,16 @@ class CudaGraphRunner:
             page_table=r.req_to_token_pool.page_table, page_size=r.page_size,
             max_seq_len=r.model_config.context_len, token_to_kv_pool=r.token_to_kv_pool,
             attn_backend=r.attn_backend, in_graph=True)
+        from ..parallel import state as ps
+        comm = ps.get_state().fused_comm
+        if comm is not None:
+            fb.extras["skip_logits_gather"] = True
         out = r.model(ids, fb)
-        tok = native.argmax(out.next_token_logits)
+        if "vocab_shard" in out.extras:
+            start, vocab = out.extras["vocab_shard"]
+            tok = comm.argmax_gather(out.next_token_logits, start, vocab)
+        else:
+            tok = native.argmax(out.next_token_logits)
         r.future_token_ids_map[v["future_slots"].long()] = tok
         return tok
 

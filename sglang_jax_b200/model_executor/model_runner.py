@@ -158,14 +158,25 @@ class ModelRunner:
 
     def _init_fused_comm(self):
         st = ps.get_state()
-        if (self.tp_size > 1 and self.device.type == "cuda" and not self.server_args.disable_fused_comm
-                and not self.server_args.disable_custom_kernels and st.fused_comm is None):
-            try:
-                from ..parallel.fused_comm import FusedComm
-                st.fused_comm = FusedComm.create(st, self.model_config.hidden_size, self.dtype)
-            except Exception as e:  # NCCL path remains fully functional
-                logger.warning("fused communication kernels unavailable (%s); using NCCL", e)
-                st.fused_comm = None
+        want = (self.tp_size > 1 and self.device.type == "cuda" and not self.server_args.disable_fused_comm
+                and not self.server_args.disable_custom_kernels and st.fused_comm is None)
+        if not want:
+            return
+        ok = 1
+        try:
+            from ..parallel.fused_comm import FusedComm
+            sa = self.server_args
+            max_tokens = max(sa.chunked_prefill_size or 0, sa.max_prefill_tokens) + self.max_running_requests
+            st.fused_comm = FusedComm.create(st, self.model_config.hidden_size, self.dtype, max_tokens)
+        except Exception as e:  # NCCL path remains fully functional
+            logger.warning("fused communication kernels unavailable (%s); using NCCL", e)
+            ok = 0
+        # all ranks must take the same path
+        import torch.distributed as dist
+        t = torch.tensor([ok], dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=st.tp.cpu_group)
+        if int(t.item()) == 0:
+            st.fused_comm = None
 
     # ------------------------------------------------------------------ forward
     def resolve_future_token_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
@@ -186,11 +197,21 @@ class ModelRunner:
         self.h2d_bytes_total += fb.h2d_bytes
         if self.server_args is not None and not self.server_args.disable_overlap_schedule:
             fb.input_ids = self.resolve_future_token_ids(fb.input_ids)
+        comm = ps.get_state().fused_comm
+        si = batch.sampling_info
+        if (comm is not None and not skip_sample and not batch.return_logprob and si is not None and si.is_all_greedy
+                and si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None
+                and batch.capture_hidden_mode == 0 and len(batch.req_pool_indices) <= 1024):
+            fb.extras["skip_logits_gather"] = True     # greedy: reduce (max, index) pairs, not logits
         out = self.model(fb.input_ids, fb)
         if skip_sample:
             return out, None, fb
-        meta = SamplingMetadata.from_worker_batch(batch, self.device)
-        ids = self.sampler(out, meta)
+        if "vocab_shard" in out.extras:
+            start, vocab = out.extras["vocab_shard"]
+            ids = comm.argmax_gather(out.next_token_logits, start, vocab)
+        else:
+            meta = SamplingMetadata.from_worker_batch(batch, self.device)
+            ids = self.sampler(out, meta)
         if batch.future_slots is not None:
             slots = torch.from_numpy(batch.future_slots).to(self.device, non_blocking=True).long()
             self.future_token_ids_map[slots] = ids

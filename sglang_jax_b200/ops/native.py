@@ -145,7 +145,7 @@ def gemm_scratch(device) -> _GemmScratch:
     return s
 
 
-def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0):
+def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0, out=None):
     K = x.shape[-1]
     N = w.shape[0]
     x2 = x.reshape(-1, K)
@@ -154,8 +154,16 @@ def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0):
     M = x2.shape[0]
     if K % 8 or N % 8 or not w.is_contiguous() or x2.data_ptr() % 16 or w.data_ptr() % 16:
         from . import reference
-        return reference.linear(x, w, bias)
-    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        y = reference.linear(x, w, bias)
+        if out is not None:
+            out.copy_(y.view_as(out))
+            return out
+        return y
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    else:
+        assert out.is_contiguous() and out.numel() == M * N and out.data_ptr() % 16 == 0
+        out = out.view(M, N)
     if M == 0:
         return out.view(*x.shape[:-1], N)
     sc = gemm_scratch(x.device)
