@@ -218,6 +218,14 @@ def main():
         if batch is None:
             return
         state["steps"] += 1
+        now = time.perf_counter()
+        if state["phase"] == "timed" and "last_t" in state:
+            kind = "decode" if batch.forward_mode.is_decode() else "prefill"
+            state.setdefault(kind + "_s", 0.0)
+            state.setdefault(kind + "_n", 0)
+            state[kind + "_s"] += now - state["last_t"]
+            state[kind + "_n"] += 1
+        state["last_t"] = now
         if state["phase"] == "timed":
             if batch.forward_mode.is_decode():
                 state["tokens"] += len(batch.reqs)
@@ -310,6 +318,9 @@ def main():
         "clocks": clock_info, "e2e": e2e, "gpu_launches": int(gpu_launches),
         "timed_tokens": state["tokens"], "init_s": round(init_s, 1), "kernel_status": native_status,
         "wall_ms_per_step": round((state["wall1"] - state["wall0"]) * 1e3 / K, 4),
+        "step_breakdown": {k: {"steps": state.get(k + "_n", 0),
+                               "host_ms_per_step": round(1e3 * state.get(k + "_s", 0.0) / max(state.get(k + "_n", 0), 1), 3)}
+                           for k in ("prefill", "decode")},
     }
     if args.layers:
         out["invalid"] = "debug run with fewer layers than the named model"
