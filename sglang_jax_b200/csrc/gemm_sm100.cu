@@ -55,8 +55,66 @@ struct Params {
   Status* status;
   int M, N, K;
   int tiles_a, tiles_b;          // tiles along the A-operand rows / B-operand rows
-  int splits;                    // K splits
+  int splits;                    // K splits (interleaved policy); workspace slots per tile
   int kb_total;                  // K blocks (ceil(K / 64))
+  int units_per_cta;             // > 0: stream-K policy, each CTA owns this many consecutive K-block units
+  int total_units;               // tiles * kb_total
+};
+
+// One piece of work: K blocks [kb0, kb1) of output tile (ta, tb).  `n_contrib` CTAs contribute to
+// the tile; this one writes workspace slot `slot` (n_contrib == 1: the tile is stored directly).
+struct Seg {
+  int ta, tb, kb0, kb1, tile_id, slot, n_contrib;
+};
+
+// Two decompositions share the kernel:
+//  * interleaved (units_per_cta == 0): work item w = blockIdx.x + i * gridDim.x is a whole tile or one
+//    of `splits` equal K ranges of it.  Consecutive CTAs take consecutive A tiles of the same B
+//    tile, so the B tile is fetched from HBM once and then hit in L2 (prefill).
+//  * stream-K (units_per_cta > 0): the tiles' K blocks form one long list that is cut into equal
+//    consecutive ranges, one per CTA, so every SM streams the same number of weight bytes whatever
+//    the tile count is (decode).  A range may end / start in the middle of a tile: those tiles get
+//    their partial sums through the workspace.
+struct SegIter {
+  int it, u, u_end;
+  __device__ explicit SegIter(const Params& p) : it(0), u(0), u_end(0) {
+    if (p.units_per_cta > 0) {
+      u = blockIdx.x * p.units_per_cta;
+      u_end = min(p.total_units, u + p.units_per_cta);
+    }
+  }
+  __device__ bool next(const Params& p, Seg& s) {
+    if (p.units_per_cta > 0) {
+      if (u >= u_end) return false;
+      const int tile = u / p.kb_total;
+      s.kb0 = u - tile * p.kb_total;
+      s.kb1 = min(p.kb_total, s.kb0 + (u_end - u));
+      u += s.kb1 - s.kb0;
+      s.tile_id = tile;
+      s.tb = tile / p.tiles_a;
+      s.ta = tile - s.tb * p.tiles_a;
+      const int first_cta = (tile * p.kb_total) / p.units_per_cta;
+      const int last_cta = ((tile + 1) * p.kb_total - 1) / p.units_per_cta;
+      s.slot = blockIdx.x - first_cta;
+      s.n_contrib = last_cta - first_cta + 1;
+      return true;
+    }
+    const int num_tiles = p.tiles_a * p.tiles_b;
+    const int w = blockIdx.x + it * gridDim.x;
+    if (w >= num_tiles * p.splits) return false;
+    ++it;
+    const int sp = w / num_tiles;
+    const int t = w - sp * num_tiles;
+    const int kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+    s.tb = t / p.tiles_a;
+    s.ta = t - s.tb * p.tiles_a;
+    s.kb0 = sp * kb_per_split;
+    s.kb1 = min(s.kb0 + kb_per_split, p.kb_total);
+    s.tile_id = t;
+    s.slot = sp;
+    s.n_contrib = p.splits;
+    return true;
+  }
 };
 
 template <int BN, int MODE>
@@ -105,32 +163,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_a * p.tiles_b;
-  const int num_work = num_tiles * p.splits;
-  const int kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
-
-  // work item -> (tile_a, tile_b, split).  Consecutive CTAs take consecutive A tiles of the
-  // same B tile, so the B tile (weights in MODE 0) is fetched from HBM once and then hit in L2.
-  auto decode = [&](int w, int& ta, int& tb, int& sp, int& kb0, int& kb1) {
-    sp = w / num_tiles;
-    const int t = w - sp * num_tiles;
-    tb = t / p.tiles_a;
-    ta = t - tb * p.tiles_a;
-    kb0 = sp * kb_per_split;
-    kb1 = min(kb0 + kb_per_split, p.kb_total);
-  };
-
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int w = blockIdx.x; w < num_work && !*abort_flag; w += gridDim.x) {
-        int ta, tb, sp, kb0, kb1;
-        decode(w, ta, tb, sp, kb0, kb1);
-        for (int kb = kb0; kb < kb1; ++kb) {
+      SegIter iter(p);
+      Seg sg;
+      while (!*abort_flag && iter.next(p, sg)) {
+        const int ta = sg.ta, tb = sg.tb;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
-            report(p.status, kTimeoutEmptyBarrier, w, kb);
+            report(p.status, kTimeoutEmptyBarrier, sg.tile_id, kb);
             *abort_flag = 1;
             break;
           }
@@ -154,11 +198,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (int w = blockIdx.x; w < num_work && !*abort_flag; w += gridDim.x) {
-        int ta, tb, sp, kb0, kb1;
-        decode(w, ta, tb, sp, kb0, kb1);
+      SegIter iter(p);
+      Seg sg;
+      while (!*abort_flag && iter.next(p, sg)) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1)) {
-          report(p.status, kTimeoutTmemEmpty, w, acc);
+          report(p.status, kTimeoutTmemEmpty, sg.tile_id, acc);
           *abort_flag = 1;
           break;
         }
@@ -167,7 +212,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         bool ok = true;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
-            report(p.status, kTimeoutFullBarrier, w, kb);
+            report(p.status, kTimeoutFullBarrier, sg.tile_id, kb);
             *abort_flag = 1;
             ok = false;
             break;
@@ -201,20 +246,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* my_stage = staging + q * (32 * 32 * 2);
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int w = blockIdx.x; w < num_work && !*abort_flag; w += gridDim.x) {
-      int ta, tb, sp, kb0, kb1;
-      decode(w, ta, tb, sp, kb0, kb1);
+    SegIter iter(p);
+    Seg sg;
+    while (!*abort_flag && iter.next(p, sg)) {
+      const int ta = sg.ta, tb = sg.tb;
       if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase)) {
-        report(p.status, kTimeoutTmemFull, w, acc);
+        report(p.status, kTimeoutTmemFull, sg.tile_id, acc);
         *abort_flag = 1;
         break;
       }
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      const int tile_id = tb * p.tiles_a + ta;
-      const bool direct = (p.splits == 1);
+      const int tile_id = sg.tile_id;
+      const bool direct = (sg.n_contrib == 1);
       float* ws_tile = direct ? nullptr
-                              : p.workspace + (static_cast<size_t>(tile_id) * p.splits + sp) * (BM * BN);
+                              : p.workspace + (static_cast<size_t>(tile_id) * p.splits + sg.slot) * (BM * BN);
 
       auto store_chunk = [&](const float* f, int c0) {
         // f[0..CW): accumulator row `row`, columns c0..c0+CW of this tile
@@ -297,7 +343,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         named_bar_sync(1, kEpiThreads);
         if (epi_tid == 0) {
           const int old = atomicAdd(&p.counters[tile_id], 1);
-          const int last = (old == p.splits - 1) ? 1 : 0;
+          const int last = (old == sg.n_contrib - 1) ? 1 : 0;
           if (last) p.counters[tile_id] = 0;    // leave the counter clean for the next launch
           *last_flag = last;
         }
@@ -312,7 +358,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             float f[C::CW];
 #pragma unroll
             for (int e = 0; e < C::CW; ++e) f[e] = 0.f;
-            for (int s = 0; s < p.splits; ++s) {
+            for (int s = 0; s < sg.n_contrib; ++s) {
               const float* wsp = ws0 + static_cast<size_t>(s) * (BM * BN);
 #pragma unroll
               for (int e = 0; e < C::CW; ++e) f[e] += __ldcg(&wsp[(c0 + e) * BM + row]);
@@ -419,22 +465,36 @@ int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, in
     p.tiles_a = (N + BM - 1) / BM;
     p.tiles_b = 1;
     int splits = force_splits > 0 ? force_splits : 1;
+    int grid = 0;
     if (force_splits <= 0 && workspace != nullptr && counters != nullptr) {
-      // enough CTAs to cover the SMs, but keep at least 8 K-blocks per split
-      splits = (sms + p.tiles_a - 1) / p.tiles_a;
-      splits = min(splits, max(1, kb_total / 8));
-      splits = min(splits, 16);
+      // stream-K: equal consecutive K-block ranges per CTA.  A range is kept long enough that the
+      // fp32 fix-up traffic of a shared tile (2 * 128 * bn * 4 bytes per contributor) stays small
+      // next to the weight bytes the contributor streams (16 KiB per K block).
+      const int total = p.tiles_a * kb_total;
+      const int min_upc = bn >= 128 ? 16 : (bn >= 64 ? 12 : 8);
+      int upc = (total + sms - 1) / sms;
+      if (upc < min_upc) upc = min_upc;
+      const int max_contrib = (kb_total + upc - 1) / upc + 1;
+      const size_t need = static_cast<size_t>(p.tiles_a) * max_contrib * BM * bn * sizeof(float);
+      if (need <= workspace_bytes && p.tiles_a <= 4096) {
+        p.units_per_cta = upc;
+        p.total_units = total;
+        splits = max_contrib;               // workspace slots per tile
+        grid = (total + upc - 1) / upc;
+      }
     }
-    if (splits > 1) {
-      const size_t need = static_cast<size_t>(p.tiles_a) * splits * BM * bn * sizeof(float);
-      if (workspace == nullptr || counters == nullptr || need > workspace_bytes) splits = 1;
+    if (p.units_per_cta == 0) {
+      if (splits > 1) {
+        const size_t need = static_cast<size_t>(p.tiles_a) * splits * BM * bn * sizeof(float);
+        if (workspace == nullptr || counters == nullptr || need > workspace_bytes) splits = 1;
+      }
+      // every split must own at least one K block
+      while (splits > 1 && (kb_total + splits - 1) / splits * (splits - 1) >= kb_total) --splits;
+      grid = min(p.tiles_a * splits, sms);
     }
-    // every split must own at least one K block
-    while (splits > 1 && (kb_total + splits - 1) / splits * (splits - 1) >= kb_total) --splits;
     p.splits = splits;
     if (!encode_tmap_2d(&ta, w, K, N, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
     if (!encode_tmap_2d(&tb, x, K, M, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
-    const int grid = min(p.tiles_a * splits, sms);
     switch (bn) {
       case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
       case 32: err = launch<32, 1>(ta, tb, p, grid, stream); break;

@@ -128,7 +128,7 @@ class _GemmScratch:
     stream are ordered, and the kernel leaves the counters zeroed)."""
 
     def __init__(self, device):
-        self.bytes = 64 << 20
+        self.bytes = 128 << 20
         self.workspace = torch.empty(self.bytes, dtype=torch.uint8, device=device)
         self.counters = torch.zeros(4096, dtype=torch.int32, device=device)
 
