@@ -59,12 +59,21 @@ struct Params {
   int kb_total;                  // K blocks (ceil(K / 64))
   int units_per_cta;             // > 0: stream-K policy, each CTA owns this many consecutive K-block units
   int total_units;               // tiles * kb_total
+  // grouped GEMM (MoE experts): rows of x are sorted by group, w is [groups * N, K]
+  const int* group_offsets;      // [groups + 1] row offsets into x / out, device memory; null = dense
+  const int* tile_group;         // MODE 0: group of each 128-row token tile
+  const int* tile_row0;          // MODE 0: first row of each token tile
+  const int* num_token_tiles;    // MODE 0: number of valid entries in the two lists (device scalar)
+  int groups;
 };
 
 // One piece of work: K blocks [kb0, kb1) of output tile (ta, tb).  `n_contrib` CTAs contribute to
 // the tile; this one writes workspace slot `slot` (n_contrib == 1: the tile is stored directly).
 struct Seg {
   int ta, tb, kb0, kb1, tile_id, slot, n_contrib;
+  int a_row, b_row;     // TMA row coordinates of the A / B operand tiles
+  int m0, m_limit;      // first output token row of the tile, exclusive bound of valid token rows
+  int n0;               // first output column of the tile
 };
 
 // Two decompositions share the kernel:
@@ -75,6 +84,7 @@ struct Seg {
 //    consecutive ranges, one per CTA, so every SM streams the same number of weight bytes whatever
 //    the tile count is (decode).  A range may end / start in the middle of a tile: those tiles get
 //    their partial sums through the workspace.
+template <int BN, int MODE>
 struct SegIter {
   int it, u, u_end;
   __device__ explicit SegIter(const Params& p) : it(0), u(0), u_end(0) {
@@ -83,7 +93,20 @@ struct SegIter {
       u_end = min(p.total_units, u + p.units_per_cta);
     }
   }
+  __device__ __forceinline__ void dense_coords(const Params& p, Seg& s) const {
+    s.a_row = s.ta * BM;
+    s.b_row = s.tb * BN;
+    if (MODE == 0) {
+      s.m0 = s.ta * BM;
+      s.n0 = s.tb * BN;
+    } else {
+      s.m0 = s.tb * BN;
+      s.n0 = s.ta * BM;
+    }
+    s.m_limit = p.M;
+  }
   __device__ bool next(const Params& p, Seg& s) {
+    if (p.group_offsets != nullptr) return MODE == 0 ? next_grouped_tokens_on_m(p, s) : next_grouped_weights_on_m(p, s);
     if (p.units_per_cta > 0) {
       if (u >= u_end) return false;
       const int tile = u / p.kb_total;
@@ -97,6 +120,7 @@ struct SegIter {
       const int last_cta = ((tile + 1) * p.kb_total - 1) / p.units_per_cta;
       s.slot = blockIdx.x - first_cta;
       s.n_contrib = last_cta - first_cta + 1;
+      dense_coords(p, s);
       return true;
     }
     const int num_tiles = p.tiles_a * p.tiles_b;
@@ -113,6 +137,58 @@ struct SegIter {
     s.tile_id = t;
     s.slot = sp;
     s.n_contrib = p.splits;
+    dense_coords(p, s);
+    return true;
+  }
+  // Grouped, decode shape: stream-K over (group, weight tile, K block); the group's tokens are the
+  // B operand (at most BN of them).  Groups without tokens are skipped.
+  __device__ bool next_grouped_weights_on_m(const Params& p, Seg& s) {
+    while (u < u_end) {
+      const int tile = u / p.kb_total;                 // = group * tiles_a + ta
+      const int g = tile / p.tiles_a;
+      const int row_lo = p.group_offsets[g], row_hi = p.group_offsets[g + 1];
+      const int kb0 = u - tile * p.kb_total;
+      const int kb1 = min(p.kb_total, kb0 + (u_end - u));
+      u += kb1 - kb0;
+      if (row_hi <= row_lo) continue;
+      s.kb0 = kb0;
+      s.kb1 = kb1;
+      s.tile_id = tile;
+      s.ta = tile - g * p.tiles_a;
+      s.tb = 0;
+      const int first_cta = (tile * p.kb_total) / p.units_per_cta;
+      const int last_cta = ((tile + 1) * p.kb_total - 1) / p.units_per_cta;
+      s.slot = blockIdx.x - first_cta;
+      s.n_contrib = last_cta - first_cta + 1;
+      s.a_row = g * p.N + s.ta * BM;
+      s.b_row = row_lo;
+      s.m0 = row_lo;
+      s.m_limit = min(row_hi, row_lo + BN);
+      s.n0 = s.ta * BM;
+      return true;
+    }
+    return false;
+  }
+  // Grouped, prefill shape: whole (token tile, weight tile) pairs from the device-side tile list.
+  __device__ bool next_grouped_tokens_on_m(const Params& p, Seg& s) {
+    const int n_tok_tiles = *p.num_token_tiles;
+    const int w = blockIdx.x + it * gridDim.x;
+    if (w >= n_tok_tiles * p.tiles_b) return false;
+    ++it;
+    s.tb = w / n_tok_tiles;
+    s.ta = w - s.tb * n_tok_tiles;
+    const int g = p.tile_group[s.ta];
+    const int row0 = p.tile_row0[s.ta];
+    s.kb0 = 0;
+    s.kb1 = p.kb_total;
+    s.tile_id = w;
+    s.slot = 0;
+    s.n_contrib = 1;
+    s.a_row = row0;
+    s.b_row = g * p.N + s.tb * BN;
+    s.m0 = row0;
+    s.m_limit = min(p.group_offsets[g + 1], row0 + BM);
+    s.n0 = s.tb * BN;
     return true;
   }
 };
@@ -168,10 +244,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      SegIter iter(p);
+      SegIter<BN, MODE> iter(p);
       Seg sg;
       while (!*abort_flag && iter.next(p, sg)) {
-        const int ta = sg.ta, tb = sg.tb;
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
             report(p.status, kTimeoutEmptyBarrier, sg.tile_id, kb);
@@ -181,8 +256,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t fb = smem_u32(&full_bar[stage]);
           mbar_expect_tx(fb, C::kStageBytes);
           uint8_t* sa = stage_base + stage * C::kStageBytes;
-          tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * BK, ta * BM);
-          tma_load_2d(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, tb * BN);
+          tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * BK, sg.a_row);
+          tma_load_2d(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, sg.b_row);
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1;
@@ -198,7 +273,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      SegIter iter(p);
+      SegIter<BN, MODE> iter(p);
       Seg sg;
       while (!*abort_flag && iter.next(p, sg)) {
         const int kb0 = sg.kb0, kb1 = sg.kb1;
@@ -246,10 +321,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* my_stage = staging + q * (32 * 32 * 2);
     int acc = 0;
     uint32_t acc_phase = 0;
-    SegIter iter(p);
+    SegIter<BN, MODE> iter(p);
     Seg sg;
     while (!*abort_flag && iter.next(p, sg)) {
-      const int ta = sg.ta, tb = sg.tb;
       if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase)) {
         report(p.status, kTimeoutTmemFull, sg.tile_id, acc);
         *abort_flag = 1;
@@ -267,8 +341,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if constexpr (MODE == 0) {
           // rows are tokens, columns are outputs: transpose through smem so that global stores
           // are 16-byte vectors covering whole 64-byte row segments
-          const int gm0 = ta * BM + q * 32;
-          const int gn0 = tb * BN + c0;
+          const int gm0 = sg.m0 + q * 32;
+          const int gn0 = sg.n0 + c0;
 #pragma unroll
           for (int j = 0; j < C::CW / 8; ++j) {
             float g[8];
@@ -296,20 +370,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint4 v = *reinterpret_cast<const uint4*>(my_stage + r * (C::CW * 2) + pj * 16);
             const int gm = gm0 + r;
             const int gn = gn0 + jj * 8;
-            if (gm < p.M && gn < p.N) {
+            if (gm < sg.m_limit && gn < p.N) {
               *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(gm) * p.N + gn) = v;
             }
           }
           __syncwarp();
         } else {
           // rows are outputs (weight rows), columns are tokens: out[token][n]
-          const int gn = ta * BM + row;
+          const int gn = sg.n0 + row;
           if (gn < p.N) {
             const float b = p.bias != nullptr ? __bfloat162float(p.bias[gn]) : 0.f;
 #pragma unroll
             for (int e = 0; e < C::CW; ++e) {
-              const int tok = tb * BN + c0 + e;
-              if (tok < p.M) p.out[static_cast<size_t>(tok) * p.N + gn] = __float2bfloat16(f[e] + b);
+              const int tok = sg.m0 + c0 + e;
+              if (tok < sg.m_limit) p.out[static_cast<size_t>(tok) * p.N + gn] = __float2bfloat16(f[e] + b);
             }
           }
         }
@@ -647,4 +721,86 @@ int sglb_gemm_bf16_noalloc_status(int* out4) {
   }
   return h.code;
 }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grouped GEMM for MoE experts: out[r, :] = x[r, :] . w[g(r)]^T for rows r sorted by group g.
+//   x    [rows, K]  (rows = routed (token, expert) pairs, sorted by expert)
+//   w    [groups, N, K]
+//   out  [rows, N]
+//   group_offsets [groups + 1] (device)
+// rows <= 256: decode shape, weights on the MMA M dimension, stream-K over (group, weight tile, K);
+// every group must then hold at most BN >= rows tokens, which `rows <= BN` guarantees.
+// rows  > 256: prefill shape, (token tile, weight tile) pairs from the device-side tile list built
+// by sglb_moe_align (tile_group / tile_row0 / num_token_tiles, at most rows/128 + groups tiles).
+// The reference's counterpart is the Megablox grouped matmul
+// (python/sgl_jax/srt/kernels/gmm/megablox_gmm_kernel/gmm.py:311).
+// ---------------------------------------------------------------------------------------------
+extern "C" int sglb_grouped_gemm_bf16(const void* x, const void* w, void* out, const int* group_offsets,
+                                       const int* tile_group, const int* tile_row0, const int* num_token_tiles,
+                                       int rows, int N, int K, int groups, void* workspace, size_t workspace_bytes,
+                                       int* counters, cudaStream_t stream) {
+  using namespace sglb;
+  if (rows <= 0 || groups <= 0) return 0;
+  if ((K % 8) || (N % 8)) return -kBadArgument;
+  const int kb_total = (K + BK - 1) / BK;
+  const int sms = sm_count();
+  Params p{};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.workspace = static_cast<float*>(workspace);
+  p.counters = counters;
+  p.status = device_status();
+  p.M = rows;
+  p.N = N;
+  p.K = K;
+  p.kb_total = kb_total;
+  p.splits = 1;
+  p.group_offsets = group_offsets;
+  p.groups = groups;
+  CUtensorMap ta, tb;
+  cudaError_t err;
+  if (rows <= 256) {
+    const int bn = pick_bn_tokens(rows);
+    p.tiles_a = (N + BM - 1) / BM;        // weight tiles per group
+    p.tiles_b = 1;
+    const int total = groups * p.tiles_a * kb_total;
+    const int min_upc = bn >= 128 ? 16 : (bn >= 64 ? 12 : 8);
+    int upc = (total + sms - 1) / sms;
+    if (upc < min_upc) upc = min_upc;
+    int max_contrib = (kb_total + upc - 1) / upc + 1;
+    size_t need = static_cast<size_t>(groups) * p.tiles_a * max_contrib * BM * bn * sizeof(float);
+    if (need > workspace_bytes || groups * p.tiles_a > 4096 || workspace == nullptr || counters == nullptr) {
+      // no room for shared tiles: whole tiles per CTA
+      upc = kb_total * ((total / kb_total + sms - 1) / sms);
+      max_contrib = 1;
+    }
+    p.units_per_cta = upc;
+    p.total_units = total;
+    p.splits = max_contrib;
+    const int grid = (total + upc - 1) / upc;
+    // weights [groups*N, K] on the A operand; when N is not a multiple of 128 the last tile of a
+    // group reads rows of the next group, which are masked at the store (gn < N).
+    if (!encode_tmap_2d(&ta, w, K, static_cast<uint64_t>(groups) * N, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
+    if (!encode_tmap_2d(&tb, x, K, rows, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
+    switch (bn) {
+      case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
+      case 32: err = launch<32, 1>(ta, tb, p, grid, stream); break;
+      case 64: err = launch<64, 1>(ta, tb, p, grid, stream); break;
+      case 128: err = launch<128, 1>(ta, tb, p, grid, stream); break;
+      default: err = launch<256, 1>(ta, tb, p, grid, stream); break;
+    }
+  } else {
+    if (tile_group == nullptr || tile_row0 == nullptr || num_token_tiles == nullptr) return -kBadArgument;
+    const int bn = (N % 256 == 0) ? 256 : 128;
+    p.tile_group = tile_group;
+    p.tile_row0 = tile_row0;
+    p.num_token_tiles = num_token_tiles;
+    p.tiles_a = rows / BM + groups;       // upper bound of token tiles
+    p.tiles_b = (N + bn - 1) / bn;
+    if (!encode_tmap_2d(&ta, x, K, rows, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
+    if (!encode_tmap_2d(&tb, w, K, static_cast<uint64_t>(groups) * N, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
+    const int grid = min(p.tiles_a * p.tiles_b, sms);
+    err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
+  }
+  return err == cudaSuccess ? 0 : static_cast<int>(err);
 }

@@ -95,5 +95,19 @@ def argmax(logits):
 
 def topk_route(router_logits, top_k, scoring="softmax", renormalize=True, correction_bias=None,
                num_expert_group=0, topk_group=0, routed_scaling_factor=1.0):
+    if (not _FORCE_REFERENCE) and router_logits.is_cuda and router_logits.shape[-1] <= 512 and top_k <= 16 \
+            and router_logits.dtype in (torch.float32, torch.bfloat16):
+        from . import moe_native
+        return moe_native.topk_route(router_logits, top_k, scoring, renormalize, correction_bias,
+                                     num_expert_group, topk_group, routed_scaling_factor)
     return reference.topk_route(router_logits, top_k, scoring, renormalize, correction_bias,
                                 num_expert_group, topk_group, routed_scaling_factor)
+
+
+def fused_experts(x, w13, w2, topk_weights, topk_ids, expert_start=0, workspace=None, add=None):
+    """Routed-expert FFN: `w13 [E_local, 2I, H]` (gate rows then up rows), `w2 [E_local, H, I]`."""
+    if use_native(x) and w13.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and w2.shape[-1] % 8 == 0:
+        from . import moe_native
+        return moe_native.fused_experts(x, w13, w2, topk_weights, topk_ids, expert_start, workspace, add)
+    y = reference.moe_forward(x, w13, w2, topk_weights, topk_ids, expert_start)
+    return y if add is None else (y.float() + add.float()).to(y.dtype)

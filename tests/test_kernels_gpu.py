@@ -172,3 +172,37 @@ def test_paged_extend(native, P, Hq, Hkv, D):
     got = native.paged_attention(q, cache, pt, rows, sl, P, scale, cu, pl, sliding_window=70)
     _close(got, ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, cu, pl, sliding_window=70),
            2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("E,k,scoring,groups,topk_group,bias,renorm", [
+    (128, 8, "softmax", 0, 0, False, True), (64, 4, "softmax", 0, 0, False, False),
+    (256, 8, "sigmoid", 8, 4, True, True), (256, 8, "sigmoid", 8, 4, False, True), (16, 2, "tanh", 0, 0, False, True),
+])
+def test_topk_route(native, E, k, scoring, groups, topk_group, bias, renorm):
+    from sglang_jax_b200.ops import moe_native
+    g = torch.Generator(device="cuda").manual_seed(40)
+    logits = torch.randn(77, E, device="cuda", generator=g)
+    b = torch.randn(E, device="cuda", generator=g) * 0.1 if bias else None
+    w, ids = moe_native.topk_route(logits, k, scoring, renorm, b, groups, topk_group, 2.5)
+    ew, eids = ref.topk_route(logits, k, scoring, renorm, b, groups, topk_group, 2.5)
+    assert torch.equal(ids.sort(-1).values, eids.sort(-1).values)
+    order, eorder = ids.argsort(-1), eids.argsort(-1)
+    torch.testing.assert_close(w.gather(1, order), ew.gather(1, eorder), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("T,E,E_local,e0,k,H,I", [
+    (5, 16, 16, 0, 2, 256, 128), (40, 32, 8, 8, 4, 512, 384), (128, 128, 16, 32, 8, 2048, 768),
+    (700, 32, 32, 0, 4, 512, 256), (1500, 64, 16, 16, 8, 1024, 768),
+])
+def test_fused_experts(native, T, E, E_local, e0, k, H, I):
+    from sglang_jax_b200.ops import moe_native
+    x = _bf16(T, H, seed=50)
+    w13 = _bf16(E_local, 2 * I, H, scale=0.05, seed=51)
+    w2 = _bf16(E_local, H, I, scale=0.05, seed=52)
+    logits = torch.randn(T, E, device="cuda", generator=torch.Generator(device="cuda").manual_seed(53))
+    tw, ids = ref.topk_route(logits, k)
+    got = moe_native.fused_experts(x, w13, w2, tw, ids, e0)
+    torch.cuda.synchronize()
+    native.check_status()
+    exp = ref.moe_forward(x.float(), w13.float(), w2.float(), tw, ids, e0)
+    _close(got, exp, 3e-2, 3e-2)
