@@ -23,3 +23,20 @@ def row_linear_add_norm(lin, x, residual, norm):
                                                norm.variance_epsilon, norm.gemma)
     y = lin(x)
     return norm(y, residual)
+
+
+def partial_add_norm(make_partial, num_tokens: int, hidden: int, residual, norm, tp_size: int):
+    """Like `row_linear_add_norm` for a block whose per-rank partial sum is produced by arbitrary
+    code (an MoE layer): `make_partial(out_or_None)` must return the `[T, H]` partial, written into
+    `out` when one is given."""
+    comm = ps.get_state().fused_comm
+    if comm is not None and tp_size > 1 and num_tokens <= comm.max_tokens and hidden == comm.hidden:
+        buf = comm.partial_buffer(num_tokens)
+        y = make_partial(buf)
+        if y.data_ptr() != buf.data_ptr():
+            buf.copy_(y)
+        return comm.allreduce_add_rmsnorm(num_tokens, residual, norm.weight, norm.variance_epsilon, norm.gemma)
+    y = make_partial(None)
+    if tp_size > 1:
+        y = ps.all_reduce(y)
+    return norm(y, residual)

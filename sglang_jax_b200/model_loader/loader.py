@@ -85,7 +85,8 @@ class DefaultModelLoader:
             model = cls(model_config.hf_config, dtype=model_config.dtype, quant_config=quant_config) \
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
         it = self._iterator(model_config.model_path)
-        model.load_weights(it)
+        loaded = model.load_weights(it)
+        check_all_loaded(model, loaded)
         return model.eval()
 
     def _iterator(self, path):
@@ -111,6 +112,18 @@ class DummyModelLoader:
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
         initialize_dummy_weights(model, self.seed)
         return model.eval()
+
+
+def check_all_loaded(model, loaded):
+    """A parameter the checkpoint did not provide would silently stay uninitialised memory."""
+    if loaded is None:
+        return
+    tied = {"lm_head.weight"} if getattr(model, "tie", False) else set()
+    optional = getattr(model, "optional_params", set())
+    missing = [n for n, _ in model.named_parameters() if n not in loaded and n not in tied
+               and not any(n.endswith(o) for o in optional)]
+    if missing:
+        raise RuntimeError(f"checkpoint is missing {len(missing)} parameters, e.g. {missing[:5]}")
 
 
 def _accepts_quant(cls) -> bool:

@@ -93,11 +93,17 @@ class FusedComm:
         return (x.is_cuda and x.dtype == torch.bfloat16 and w.shape[0] == self.hidden
                 and x.shape[0] <= self.max_tokens and x.dim() == 2)
 
+    def partial_buffer(self, T: int) -> torch.Tensor:
+        """This rank's `[T, hidden]` slot for a partial sum that `allreduce_add_rmsnorm` will reduce."""
+        return self.ypart.tensor[: T * self.hidden].view(T, self.hidden)
+
     def gemm_allreduce_add_rmsnorm(self, x, w, residual, norm_w, eps, gemma=False):
         T = x.shape[0]
+        native.linear(x, w, None, out=self.partial_buffer(T))
+        return self.allreduce_add_rmsnorm(T, residual, norm_w, eps, gemma)
+
+    def allreduce_add_rmsnorm(self, T: int, residual, norm_w, eps, gemma=False):
         H = self.hidden
-        ypart = self.ypart.tensor[: T * H].view(T, H)
-        native.linear(x, w, None, out=ypart)
         assert residual is None or (residual.is_contiguous() and residual.shape == (T, H))
         rc = self.L.sglb_ar_residual_rmsnorm(self.ypart.ptrs, self.gathered.ptrs, self.flags.ptrs,
                                              self.epochs.data_ptr(),

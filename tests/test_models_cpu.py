@@ -1,0 +1,121 @@
+"""Model families against HF transformers in fp32 on CPU (greedy tokens must match exactly)."""
+
+import json
+import os
+
+import pytest
+import torch
+from safetensors.torch import save_file
+
+
+def _save(path, hf_model, cfg: dict, arch: str, model_type: str, rename=None):
+    os.makedirs(path, exist_ok=True)
+    sd = {k: v.contiguous().clone() for k, v in hf_model.state_dict().items()}
+    if cfg.get("tie_word_embeddings"):
+        sd.pop("lm_head.weight", None)
+    if rename:
+        sd = rename(sd)
+    save_file(sd, os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(dict(cfg, architectures=[arch], model_type=model_type, torch_dtype="float32"), f)
+    return path
+
+
+def _generate(path, ids, n=10, **kw):
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    ps.reset_state()
+    eng = Engine(model_path=path, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                 max_total_tokens=4096, enable_single_process=True, **kw)
+    try:
+        outs = eng.generate(input_ids=ids, sampling_params={"max_new_tokens": n, "temperature": 0, "ignore_eos": True})
+        return [o["output_ids"] for o in outs]
+    finally:
+        eng.shutdown()
+
+
+def _hf_generate(hf, ids, n=10):
+    out = []
+    for i in ids:
+        with torch.no_grad():
+            out.append(hf.generate(torch.tensor([i]), max_new_tokens=n, do_sample=False)[0, len(i):].tolist())
+    return out
+
+
+PROMPTS = [list(range(5, 40)), [9, 8, 7, 6, 5, 4, 3] * 5, [100, 200, 300]]
+
+
+def _init(hf, std=0.05):
+    torch.manual_seed(0)
+    for p in hf.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, std)
+    return hf.float().eval()
+
+
+def test_llama_matches_hf(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, rms_norm_eps=1e-5, rope_theta=500000.0, vocab_size=512,
+               tie_word_embeddings=False, max_position_embeddings=512,
+               rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 64})
+    hf = _init(LlamaForCausalLM(LlamaConfig(**cfg)))
+    path = _save(str(tmp_path / "llama"), hf, cfg, "LlamaForCausalLM", "llama")
+    assert _generate(path, PROMPTS) == _hf_generate(hf, PROMPTS)
+
+
+def test_qwen2_bias_matches_hf(tmp_path):
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=512, tie_word_embeddings=True,
+               max_position_embeddings=512)
+    hf = _init(Qwen2ForCausalLM(Qwen2Config(**cfg)))
+    for n, p in hf.named_parameters():
+        if n.endswith("bias"):
+            p.data.normal_(0, 0.05)
+    path = _save(str(tmp_path / "qwen2"), hf, cfg, "Qwen2ForCausalLM", "qwen2")
+    assert _generate(path, PROMPTS) == _hf_generate(hf, PROMPTS)
+
+
+def test_qwen3_moe_matches_hf_fused_and_per_expert_checkpoints(tmp_path):
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, rope_theta=1e6,
+               vocab_size=512, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+               mlp_only_layers=[], tie_word_embeddings=False, max_position_embeddings=512)
+    hf = _init(Qwen3MoeForCausalLM(Qwen3MoeConfig(**cfg)))
+    want = _hf_generate(hf, PROMPTS)
+    fused = _save(str(tmp_path / "moe_fused"), hf, cfg, "Qwen3MoeForCausalLM", "qwen3_moe")
+    assert _generate(fused, PROMPTS) == want
+
+    def per_expert(sd):
+        out = {}
+        for k, v in sd.items():
+            if k.endswith("mlp.experts.gate_up_proj"):
+                base = k[: -len("gate_up_proj")]
+                I = v.shape[1] // 2
+                for e in range(v.shape[0]):
+                    out[f"{base}{e}.gate_proj.weight"] = v[e, :I].contiguous()
+                    out[f"{base}{e}.up_proj.weight"] = v[e, I:].contiguous()
+            elif k.endswith("mlp.experts.down_proj"):
+                base = k[: -len("down_proj")]
+                for e in range(v.shape[0]):
+                    out[f"{base}{e}.down_proj.weight"] = v[e].contiguous()
+            else:
+                out[k] = v
+        return out
+
+    hub = _save(str(tmp_path / "moe_hub"), hf, cfg, "Qwen3MoeForCausalLM", "qwen3_moe", rename=per_expert)
+    assert _generate(hub, PROMPTS) == want
+
+
+def test_missing_parameter_is_an_error(tmp_path):
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    cfg = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=2,
+               num_key_value_heads=2, head_dim=32, vocab_size=128, tie_word_embeddings=False)
+    hf = _init(Qwen3ForCausalLM(Qwen3Config(**cfg)))
+    path = _save(str(tmp_path / "broken"), hf, cfg, "Qwen3ForCausalLM", "qwen3",
+                 rename=lambda sd: {k: v for k, v in sd.items() if "down_proj" not in k})
+    with pytest.raises(RuntimeError, match="missing"):
+        _generate(path, PROMPTS[:1], n=1)
