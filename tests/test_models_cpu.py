@@ -119,3 +119,23 @@ def test_missing_parameter_is_an_error(tmp_path):
                  rename=lambda sd: {k: v for k, v in sd.items() if "down_proj" not in k})
     with pytest.raises(RuntimeError, match="missing"):
         _generate(path, PROMPTS[:1], n=1)
+
+
+def test_deepseek_v3_mla_moe_matches_hf(tmp_path):
+    from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=3,
+               num_attention_heads=4, num_key_value_heads=4, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=32,
+               qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=3,
+               n_group=4, topk_group=2, scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True,
+               routed_scaling_factor=2.5, first_k_dense_replace=1, moe_layer_freq=1, rms_norm_eps=1e-6,
+               rope_theta=10000.0, vocab_size=512, tie_word_embeddings=False, max_position_embeddings=512,
+               rope_scaling=None, attention_bias=False)
+    hf = _init(DeepseekV3ForCausalLM(DeepseekV3Config(**cfg)))
+    for n, b in hf.named_buffers():
+        if "e_score_correction_bias" in n:
+            b.data.normal_(0, 0.1)
+    for n, p in hf.named_parameters():
+        if "e_score_correction_bias" in n:
+            p.data.normal_(0, 0.1)
+    path = _save(str(tmp_path / "dsv3"), hf, cfg, "DeepseekV3ForCausalLM", "deepseek_v3")
+    assert _generate(path, PROMPTS, n=8) == _hf_generate(hf, PROMPTS, n=8)
