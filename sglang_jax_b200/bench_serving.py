@@ -1,0 +1,278 @@
+"""Serving benchmark client (reference `python/sgl_jax/bench_serving.py`): an asyncio load generator
+against the native `/generate` or the OpenAI `/v1/completions` endpoint with the datasets `random`
+(synthetic ids) and `generated-shared-prefix`, a request rate / max-concurrency limiter, and the
+reference's metric definitions (`calculate_metrics` :1942-2117): TTFT = latency of the first streamed
+chunk, ITL = gaps between chunks, TPOT = (latency - TTFT) / (output_len - 1), throughput =
+tokens / duration, percentiles p50/p90/p99, peak output tok/s from 1-second buckets.
+
+    python -m sglang_jax_b200.bench_serving --backend sglang --dataset-name random \
+        --random-input-len 1024 --random-output-len 512 --num-prompts 1024 --max-concurrency 64
+"""
+
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import random
+import sys
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+
+
+@dataclass
+class RequestFuncOutput:
+    success: bool = False
+    latency: float = 0.0
+    ttft: float = 0.0
+    itl: list[float] = field(default_factory=list)
+    prompt_len: int = 0
+    output_len: int = 0
+    error: str = ""
+    start: float = 0.0
+    chunk_times: list[float] = field(default_factory=list)
+
+
+def sample_random_requests(input_len: int, output_len: int, num_prompts: int, range_ratio: float, vocab_size: int,
+                           seed: int = 1) -> list[tuple[list[int], int]]:
+    rng = np.random.RandomState(seed)
+    lo_i, lo_o = max(int(input_len * range_ratio), 1), max(int(output_len * range_ratio), 1)
+    ins = rng.randint(lo_i, input_len + 1, size=num_prompts)
+    outs = rng.randint(lo_o, output_len + 1, size=num_prompts)
+    return [(rng.randint(0, vocab_size, size=int(n)).tolist(), int(o)) for n, o in zip(ins, outs)]
+
+
+def sample_generated_shared_prefix_requests(num_groups: int, prompts_per_group: int, system_prompt_len: int,
+                                            question_len: int, output_len: int, vocab_size: int, seed: int = 1):
+    rng = np.random.RandomState(seed)
+    reqs = []
+    for _ in range(num_groups):
+        sys_ids = rng.randint(0, vocab_size, size=system_prompt_len).tolist()
+        for _ in range(prompts_per_group):
+            reqs.append((sys_ids + rng.randint(0, vocab_size, size=question_len).tolist(), output_len))
+    random.Random(seed).shuffle(reqs)
+    return reqs
+
+
+async def _request_sglang_generate(session, url, ids, out_len, extra) -> RequestFuncOutput:
+    out = RequestFuncOutput(prompt_len=len(ids))
+    body = {"input_ids": ids, "stream": True,
+            "sampling_params": {"temperature": 0.0, "max_new_tokens": out_len, "ignore_eos": True, **extra}}
+    out.start = st = time.perf_counter()
+    last = st
+    n_tok = 0
+    try:
+        async with session.post(url + "/generate", json=body) as resp:
+            if resp.status != 200:
+                out.error = f"HTTP {resp.status}: {await resp.text()}"
+                return out
+            async for raw in resp.content:
+                line = raw.decode().strip()
+                if not line.startswith("data:"):
+                    continue
+                payload = line[5:].strip()
+                if payload == "[DONE]":
+                    break
+                d = json.loads(payload)
+                if "error" in d:
+                    out.error = str(d["error"])
+                    return out
+                now = time.perf_counter()
+                n_new = d["meta_info"]["completion_tokens"]
+                if n_new > n_tok:
+                    if n_tok == 0:
+                        out.ttft = now - st
+                    else:
+                        out.itl.extend([(now - last) / (n_new - n_tok)] * (n_new - n_tok))
+                    out.chunk_times.append(now)
+                    last = now
+                    n_tok = n_new
+        out.latency = time.perf_counter() - st
+        out.output_len = n_tok
+        out.success = n_tok > 0
+    except Exception as e:  # connection errors are data, not crashes
+        out.error = repr(e)
+    return out
+
+
+async def _request_openai_completions(session, url, ids, out_len, extra, model) -> RequestFuncOutput:
+    out = RequestFuncOutput(prompt_len=len(ids))
+    body = {"model": model, "prompt": ids, "max_tokens": out_len, "temperature": 0.0, "stream": True,
+            "ignore_eos": True, "stream_options": {"include_usage": True}, **extra}
+    out.start = st = time.perf_counter()
+    last = st
+    n = 0
+    try:
+        async with session.post(url + "/v1/completions", json=body) as resp:
+            if resp.status != 200:
+                out.error = f"HTTP {resp.status}"
+                return out
+            async for raw in resp.content:
+                line = raw.decode().strip()
+                if not line.startswith("data:") or line.endswith("[DONE]"):
+                    continue
+                d = json.loads(line[5:])
+                now = time.perf_counter()
+                if d.get("usage"):
+                    out.output_len = d["usage"]["completion_tokens"]
+                if d.get("choices"):
+                    if n == 0:
+                        out.ttft = now - st
+                    else:
+                        out.itl.append(now - last)
+                    out.chunk_times.append(now)
+                    last = now
+                    n += 1
+        out.latency = time.perf_counter() - st
+        out.output_len = out.output_len or n
+        out.success = n > 0
+    except Exception as e:
+        out.error = repr(e)
+    return out
+
+
+def calculate_metrics(outputs: list[RequestFuncOutput], duration: float) -> dict:
+    ok = [o for o in outputs if o.success]
+    ttfts = [o.ttft for o in ok]
+    itls = [x for o in ok for x in o.itl]
+    tpots = [(o.latency - o.ttft) / (o.output_len - 1) for o in ok if o.output_len > 1]
+    e2e = [o.latency for o in ok]
+    total_in = sum(o.prompt_len for o in ok)
+    total_out = sum(o.output_len for o in ok)
+
+    def pct(xs, q):
+        return float(np.percentile(xs, q)) * 1000 if xs else 0.0
+
+    # peak output throughput over 1-second buckets of chunk arrival times
+    peak = 0.0
+    if ok:
+        t0 = min(o.start for o in ok)
+        buckets: dict[int, int] = {}
+        for o in ok:
+            per = o.output_len / max(len(o.chunk_times), 1)
+            for t in o.chunk_times:
+                buckets[int(t - t0)] = buckets.get(int(t - t0), 0) + per
+        peak = max(buckets.values()) if buckets else 0.0
+    m = {"completed": len(ok), "failed": len(outputs) - len(ok), "duration_s": duration,
+         "total_input_tokens": total_in, "total_output_tokens": total_out,
+         "request_throughput": len(ok) / duration, "input_throughput": total_in / duration,
+         "output_throughput": total_out / duration, "total_throughput": (total_in + total_out) / duration,
+         "peak_output_throughput": peak, "concurrency": sum(e2e) / duration if duration else 0.0}
+    for name, xs in (("ttft", ttfts), ("itl", itls), ("tpot", tpots), ("e2e_latency", e2e)):
+        m[f"mean_{name}_ms"] = float(np.mean(xs)) * 1000 if xs else 0.0
+        m[f"median_{name}_ms"] = pct(xs, 50)
+        m[f"p90_{name}_ms"] = pct(xs, 90)
+        m[f"p99_{name}_ms"] = pct(xs, 99)
+    return m
+
+
+async def benchmark(args, reqs) -> dict:
+    import aiohttp
+    url = args.base_url or f"http://{args.host}:{args.port}"
+    extra = json.loads(args.extra_request_body) if args.extra_request_body else {}
+    sem = asyncio.Semaphore(args.max_concurrency) if args.max_concurrency else None
+    timeout = aiohttp.ClientTimeout(total=6 * 3600)
+    conn = aiohttp.TCPConnector(limit=0)
+    async with aiohttp.ClientSession(timeout=timeout, connector=conn) as session:
+        if args.flush_cache:
+            async with session.post(url + "/flush_cache"):
+                pass
+
+        async def one(ids, out_len):
+            async def call():
+                if args.backend == "sglang":
+                    return await _request_sglang_generate(session, url, ids, out_len, extra)
+                return await _request_openai_completions(session, url, ids, out_len, extra, args.model or "default")
+            if sem is None:
+                return await call()
+            async with sem:
+                return await call()
+
+        if args.profile:
+            async with session.post(url + "/start_profile", json={"num_steps": args.profile_num_steps}):
+                pass
+        t0 = time.perf_counter()
+        tasks = []
+        for ids, out_len in reqs:
+            tasks.append(asyncio.create_task(one(ids, out_len)))
+            if args.request_rate != float("inf"):
+                await asyncio.sleep(np.random.exponential(1.0 / args.request_rate))
+        outputs = await asyncio.gather(*tasks)
+        duration = time.perf_counter() - t0
+    m = calculate_metrics(outputs, duration)
+    m.update(backend=args.backend, dataset_name=args.dataset_name, request_rate=args.request_rate,
+             max_concurrency=args.max_concurrency)
+    errs = [o.error for o in outputs if not o.success][:3]
+    if errs:
+        m["errors"] = errs
+    return m
+
+
+def print_metrics(m: dict):
+    w = 50
+    print("=" * w + "\n" + " Serving Benchmark Result ".center(w, "=") + "\n")
+    for k in ("backend", "max_concurrency", "completed", "failed", "duration_s", "total_input_tokens",
+              "total_output_tokens", "request_throughput", "input_throughput", "output_throughput",
+              "peak_output_throughput", "total_throughput", "concurrency"):
+        v = m.get(k)
+        print(f"{k:<36}{v:>14.2f}" if isinstance(v, float) else f"{k:<36}{str(v):>14}")
+    for name in ("ttft", "tpot", "itl", "e2e_latency"):
+        print(f"--- {name} (ms): mean {m[f'mean_{name}_ms']:.2f}  median {m[f'median_{name}_ms']:.2f}  "
+              f"p90 {m[f'p90_{name}_ms']:.2f}  p99 {m[f'p99_{name}_ms']:.2f}")
+    print("=" * w)
+
+
+def run_benchmark(args) -> dict:
+    random.seed(args.seed)
+    np.random.seed(args.seed)
+    if args.dataset_name == "random":
+        reqs = sample_random_requests(args.random_input_len, args.random_output_len, args.num_prompts,
+                                      args.random_range_ratio, args.vocab_size, args.seed)
+    elif args.dataset_name == "generated-shared-prefix":
+        reqs = sample_generated_shared_prefix_requests(args.gsp_num_groups, args.gsp_prompts_per_group,
+                                                       args.gsp_system_prompt_len, args.gsp_question_len,
+                                                       args.gsp_output_len, args.vocab_size, args.seed)
+    else:
+        raise SystemExit(f"dataset {args.dataset_name} needs files that are not available offline; "
+                         f"use random or generated-shared-prefix")
+    m = asyncio.run(benchmark(args, reqs))
+    print_metrics(m)
+    if args.output_file:
+        with open(args.output_file, "a") as f:
+            f.write(json.dumps(m) + "\n")
+    return m
+
+
+def build_parser():
+    p = argparse.ArgumentParser()
+    p.add_argument("--backend", default="sglang", choices=["sglang", "sglang-oai", "vllm"])
+    p.add_argument("--base-url", default=None)
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=30000)
+    p.add_argument("--model", default=None)
+    p.add_argument("--dataset-name", default="random", choices=["random", "generated-shared-prefix", "sharegpt"])
+    p.add_argument("--num-prompts", type=int, default=1000)
+    p.add_argument("--random-input-len", type=int, default=1024)
+    p.add_argument("--random-output-len", type=int, default=1024)
+    p.add_argument("--random-range-ratio", type=float, default=1.0)
+    p.add_argument("--vocab-size", type=int, default=32000)
+    p.add_argument("--request-rate", type=float, default=float("inf"))
+    p.add_argument("--max-concurrency", type=int, default=None)
+    p.add_argument("--gsp-num-groups", type=int, default=64)
+    p.add_argument("--gsp-prompts-per-group", type=int, default=16)
+    p.add_argument("--gsp-system-prompt-len", type=int, default=2048)
+    p.add_argument("--gsp-question-len", type=int, default=128)
+    p.add_argument("--gsp-output-len", type=int, default=256)
+    p.add_argument("--seed", type=int, default=1)
+    p.add_argument("--extra-request-body", default=None)
+    p.add_argument("--output-file", default=None)
+    p.add_argument("--flush-cache", action="store_true")
+    p.add_argument("--profile", action="store_true")
+    p.add_argument("--profile-num-steps", type=int, default=5)
+    return p
+
+
+if __name__ == "__main__":
+    run_benchmark(build_parser().parse_args())

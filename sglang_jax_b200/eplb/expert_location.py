@@ -1,0 +1,123 @@
+"""Logical -> physical expert placement with redundancy (reference
+`python/sgl_jax/srt/eplb/expert_location.py`, `eplb_algorithms/deepseek.py`).
+
+`ExpertLocation` maps each logical expert to one or more physical slots spread over the EP
+ranks; the router's ids are rewritten to physical slots (replicas picked round-robin by token) so
+hot experts are served by several GPUs.  `rebalance` implements the DeepSeek EPLB heuristic:
+replicate the heaviest experts, then pack physical experts onto ranks greedily by load."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+def replicate_experts(weight: np.ndarray, num_phy: int) -> tuple[np.ndarray, np.ndarray]:
+    """Give the `num_phy - num_logical` spare slots to the experts with the highest load per replica.
+    Returns (phy2log [num_phy], replica_count [num_logical])."""
+    n = len(weight)
+    assert num_phy >= n
+    phy2log = list(range(n))
+    cnt = np.ones(n, dtype=np.int64)
+    for _ in range(num_phy - n):
+        e = int(np.argmax(weight / cnt))
+        phy2log.append(e)
+        cnt[e] += 1
+    return np.asarray(phy2log, dtype=np.int64), cnt
+
+
+def balanced_packing(weight: np.ndarray, num_packs: int) -> np.ndarray:
+    """Assign items to `num_packs` equal-size packs, heaviest first into the lightest pack.
+    Returns pack index per item."""
+    n = len(weight)
+    assert n % num_packs == 0
+    cap = n // num_packs
+    order = np.argsort(-weight, kind="stable")
+    load = np.zeros(num_packs)
+    fill = np.zeros(num_packs, dtype=np.int64)
+    out = np.empty(n, dtype=np.int64)
+    for i in order:
+        cand = [p for p in range(num_packs) if fill[p] < cap]
+        p = min(cand, key=lambda q: (load[q], q))
+        out[i] = p
+        load[p] += weight[i]
+        fill[p] += 1
+    return out
+
+
+def rebalance(expert_load: np.ndarray, num_phy: int, num_ranks: int) -> np.ndarray:
+    """phy2log of length `num_phy`, ordered so that rank r owns slots [r*S, (r+1)*S)."""
+    phy2log, cnt = replicate_experts(expert_load.astype(np.float64), num_phy)
+    per_replica = expert_load[phy2log] / cnt[phy2log]
+    pack = balanced_packing(per_replica, num_ranks)
+    order = np.argsort(pack, kind="stable")
+    return phy2log[order]
+
+
+class ExpertLocation:
+    def __init__(self, num_logical: int, ep_size: int, num_redundant: int = 0, phy2log: np.ndarray | None = None,
+                 device="cpu"):
+        self.num_logical = num_logical
+        self.num_physical = num_logical + num_redundant
+        assert self.num_physical % ep_size == 0
+        self.ep_size = ep_size
+        if phy2log is None:     # "trivial": spares replicate experts 0, 1, 2, ...
+            phy2log = np.concatenate([np.arange(num_logical), np.arange(num_redundant) % num_logical])
+        self.set_mapping(np.asarray(phy2log, dtype=np.int64), device)
+
+    def set_mapping(self, phy2log: np.ndarray, device="cpu"):
+        self.phy2log = phy2log
+        reps = [[] for _ in range(self.num_logical)]
+        for p, l in enumerate(phy2log):
+            reps[int(l)].append(p)
+        self.max_rep = max(len(r) for r in reps)
+        table = np.full((self.num_logical, self.max_rep), -1, dtype=np.int64)
+        for l, r in enumerate(reps):
+            assert r, f"logical expert {l} has no physical slot"
+            table[l, : len(r)] = r
+        self.log2phy = torch.as_tensor(table, device=device)
+        self.rep_count = torch.as_tensor([len(r) for r in reps], device=device)
+
+    def logical_to_physical(self, topk_ids: torch.Tensor) -> torch.Tensor:
+        ids = topk_ids.long()
+        if self.log2phy.device != ids.device:
+            self.log2phy = self.log2phy.to(ids.device)
+            self.rep_count = self.rep_count.to(ids.device)
+        tok = torch.arange(ids.shape[0], device=ids.device).view(-1, 1)
+        pick = tok % self.rep_count[ids]
+        return self.log2phy[ids, pick].to(topk_ids.dtype)
+
+    def physical_weights(self, logical_weights: torch.Tensor) -> torch.Tensor:
+        """Gather `[num_logical, ...]` expert weights into physical slot order."""
+        return logical_weights[torch.as_tensor(self.phy2log, device=logical_weights.device)]
+
+    @classmethod
+    def from_load(cls, expert_load, ep_size: int, num_redundant: int, device="cpu") -> "ExpertLocation":
+        load = np.asarray(expert_load, dtype=np.float64)
+        return cls(len(load), ep_size, num_redundant, rebalance(load, len(load) + num_redundant, ep_size), device)
+
+
+class ExpertDistributionRecorder:
+    """Ring buffer of per-layer expert hit counts (`--enable-expert-distribution-recorder`)."""
+
+    def __init__(self, num_layers: int, num_experts: int, buffer_size: int = 100, output_file: str | None = None):
+        self.buf = np.zeros((buffer_size, num_layers, num_experts), dtype=np.int64)
+        self.pos = 0
+        self.filled = 0
+        self.output_file = output_file
+
+    def record(self, layer_id: int, topk_ids: torch.Tensor):
+        c = torch.bincount(topk_ids.reshape(-1).long().cpu(), minlength=self.buf.shape[2]).numpy()
+        self.buf[self.pos, layer_id] = c[: self.buf.shape[2]]
+
+    def step(self):
+        self.pos = (self.pos + 1) % len(self.buf)
+        self.filled = min(self.filled + 1, len(self.buf))
+        self.buf[self.pos] = 0
+
+    def aggregate(self) -> np.ndarray:
+        return self.buf[: max(self.filled, 1)].sum(0)
+
+    def dump(self):
+        if self.output_file:
+            np.save(self.output_file, self.aggregate())
