@@ -101,7 +101,7 @@ template <int VPT>
 __global__ void __launch_bounds__(1024, 1)
 ar_residual_rmsnorm_kernel(const Peers ypart, const Peers gathered, const Peers flags, uint32_t* epochs,
                            __nv_bfloat16* residual, const __nv_bfloat16* w, int T, int H, int rank, int world,
-                           float eps, int gemma, int has_residual, Status* st) {
+                           float eps, int gemma, int has_residual, int rs_mode, Status* st) {
   __shared__ float red[32];
   const int rows_per = (T + world - 1) / world;
   const int r0 = rank * rows_per;
@@ -121,8 +121,16 @@ ar_residual_rmsnorm_kernel(const Peers ypart, const Peers gathered, const Peers 
         if (idx < nvec) {
           uint4 part[kMaxWorld];
 #pragma unroll
-          for (int p = 0; p < kMaxWorld; ++p)
-            if (p < world) part[p] = __ldcg(reinterpret_cast<const uint4*>(ypart.p[p]) + base + idx);
+          for (int p = 0; p < kMaxWorld; ++p) {
+            if (p < world) {
+              // rs_mode: the GEMM epilogues already pushed every rank's slice into this rank's
+              // buffer as [src rank][local row][H]; otherwise pull the slice from each peer.
+              const uint4* src = rs_mode
+                  ? reinterpret_cast<const uint4*>(ypart.p[rank]) + (static_cast<size_t>(p) * rows_per + (row - r0)) * nvec + idx
+                  : reinterpret_cast<const uint4*>(ypart.p[p]) + base + idx;
+              part[p] = __ldcg(src);
+            }
+          }
 #pragma unroll
           for (int e = 0; e < 8; ++e) vals[i][e] = 0.f;
 #pragma unroll
@@ -288,7 +296,7 @@ int sglb_comm_flag_bytes() { return sglb::kMaxBlocks * sglb::kMaxWorld * 4; }
 // symmetric buffers; entry `rank` is the local one).  `residual` may be null (no residual add).
 int sglb_ar_residual_rmsnorm(void* const* ypart_ptrs, void* const* gathered_ptrs, void* const* flag_ptrs,
                              void* epochs, void* residual, const void* w, int T, int H, int rank, int world, float eps,
-                             int gemma, cudaStream_t stream) {
+                             int gemma, int rs_mode, cudaStream_t stream) {
   using namespace sglb;
   if (T <= 0) return 0;
   if (world < 1 || world > kMaxWorld || H % 8 || H > 8 * 1024 * 4) return -kBadArgument;
@@ -306,9 +314,9 @@ int sglb_ar_residual_rmsnorm(void* const* ypart_ptrs, void* const* gathered_ptrs
   Status* st = device_status();
   const int hr = residual != nullptr;
   switch (vpt) {
-    case 1: ar_residual_rmsnorm_kernel<1><<<blocks, threads, 0, stream>>>(yp, gp, fp, ep, res, ww, T, H, rank, world, eps, gemma, hr, st); break;
-    case 2: ar_residual_rmsnorm_kernel<2><<<blocks, threads, 0, stream>>>(yp, gp, fp, ep, res, ww, T, H, rank, world, eps, gemma, hr, st); break;
-    default: ar_residual_rmsnorm_kernel<4><<<blocks, threads, 0, stream>>>(yp, gp, fp, ep, res, ww, T, H, rank, world, eps, gemma, hr, st); break;
+    case 1: ar_residual_rmsnorm_kernel<1><<<blocks, threads, 0, stream>>>(yp, gp, fp, ep, res, ww, T, H, rank, world, eps, gemma, hr, rs_mode, st); break;
+    case 2: ar_residual_rmsnorm_kernel<2><<<blocks, threads, 0, stream>>>(yp, gp, fp, ep, res, ww, T, H, rank, world, eps, gemma, hr, rs_mode, st); break;
+    default: ar_residual_rmsnorm_kernel<4><<<blocks, threads, 0, stream>>>(yp, gp, fp, ep, res, ww, T, H, rank, world, eps, gemma, hr, rs_mode, st); break;
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -20,6 +20,7 @@
 // The reference project has no counterpart kernel: its dense projections are
 // `lax.dot_general` calls lowered by XLA (python/sgl_jax/srt/layers/linear.py:102).
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -33,6 +34,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;           // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kNumThreads = 192;
 constexpr int kEpiThreads = 128;
+constexpr int kDoneCounterOffset = 2048;   // second counter bank (stream-K clean-up)
 
 template <int BN>
 struct Cfg {
@@ -65,7 +67,21 @@ struct Params {
   const int* tile_row0;          // MODE 0: first row of each token tile
   const int* num_token_tiles;    // MODE 0: number of valid entries in the two lists (device scalar)
   int groups;
+  // fused reduce-scatter epilogue (tensor parallel row-parallel GEMM): token row t of the partial
+  // product is stored straight into the receive buffer of the rank that owns the row,
+  //   rs_peer[t / rs_rows_per] + ((rs_rank * rs_rows_per + t % rs_rows_per) * N + n),
+  // over NVLink peer mappings, tile by tile while the remaining tiles are still being computed.
+  __nv_bfloat16* rs_peer[8];
+  int rs_world, rs_rank, rs_rows_per;
+  unsigned long long* debug_stamps;   // optional [16] globaltimer stamps of CTA 0 (profiling aid)
 };
+
+__device__ __forceinline__ __nv_bfloat16* out_ptr(const Params& p, int tok, int gn) {
+  if (p.rs_world == 0) return p.out + static_cast<size_t>(tok) * p.N + gn;
+  const int owner = tok / p.rs_rows_per;
+  const int local = tok - owner * p.rs_rows_per;
+  return p.rs_peer[owner] + (static_cast<size_t>(p.rs_rank) * p.rs_rows_per + local) * p.N + gn;
+}
 
 // One piece of work: K blocks [kb0, kb1) of output tile (ta, tb).  `n_contrib` CTAs contribute to
 // the tile; this one writes workspace slot `slot` (n_contrib == 1: the tile is stored directly).
@@ -214,6 +230,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  auto stamp = [&](int i) {
+    if (p.debug_stamps != nullptr && blockIdx.x == 0) p.debug_stamps[i] = global_timer_ns();
+  };
+  if (threadIdx.x == 0) stamp(0);
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_a);
@@ -238,6 +258,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) stamp(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -264,6 +285,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
+      stamp(2);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -312,6 +334,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
+      stamp(3);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -321,8 +344,72 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* my_stage = staging + q * (32 * 32 * 2);
     int acc = 0;
     uint32_t acc_phase = 0;
+    Seg pending[2];
+    int n_pending = 0;
     SegIter<BN, MODE> iter(p);
     Seg sg;
+    auto store_chunk = [&](const Seg& sg, const float* f, int c0) {
+      // f[0..CW): accumulator row `row`, columns c0..c0+CW of this tile
+      if constexpr (MODE == 0) {
+        // rows are tokens, columns are outputs: transpose through smem so that global stores
+        // are 16-byte vectors covering whole 64-byte row segments
+        const int gm0 = sg.m0 + q * 32;
+        const int gn0 = sg.n0 + c0;
+#pragma unroll
+        for (int j = 0; j < C::CW / 8; ++j) {
+          float g[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            g[e] = f[j * 8 + e];
+            if (p.bias != nullptr) {
+              const int gn = gn0 + j * 8 + e;
+              if (gn < p.N) g[e] += __bfloat162float(p.bias[gn]);
+            }
+          }
+          uint4 v = make_uint4(pack_bf16(g[0], g[1]), pack_bf16(g[2], g[3]), pack_bf16(g[4], g[5]),
+                               pack_bf16(g[6], g[7]));
+          const int pj = j ^ ((lane >> 1) & (C::CW / 8 - 1));
+          *reinterpret_cast<uint4*>(my_stage + lane * (C::CW * 2) + pj * 16) = v;
+        }
+        __syncwarp();
+        constexpr int kChunksPerRow = C::CW / 8;            // 16-byte chunks per staged row
+        constexpr int kRowsPerIt = 32 / kChunksPerRow;
+#pragma unroll
+        for (int it = 0; it < 32 / kRowsPerIt; ++it) {
+          const int r = it * kRowsPerIt + lane / kChunksPerRow;
+          const int jj = lane % kChunksPerRow;
+          const int pj = jj ^ ((r >> 1) & (kChunksPerRow - 1));
+          const uint4 v = *reinterpret_cast<const uint4*>(my_stage + r * (C::CW * 2) + pj * 16);
+          const int gm = gm0 + r;
+          const int gn = gn0 + jj * 8;
+          if (gm < sg.m_limit && gn < p.N) {
+            *reinterpret_cast<uint4*>(out_ptr(p, gm, gn)) = v;
+          }
+        }
+        __syncwarp();
+      } else {
+        // rows are outputs (weight rows), columns are tokens: out[token][n].  Transpose the
+        // [128 n] x [CW tokens] chunk through shared memory so that every token's 128 outputs
+        // leave as 16-byte vectors (256 contiguous bytes per token).
+        __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(staging);
+        const int gn_row = sg.n0 + row;
+        const float b = (p.bias != nullptr && gn_row < p.N) ? __bfloat162float(p.bias[gn_row]) : 0.f;
+#pragma unroll
+        for (int e = 0; e < C::CW; ++e) st[e * BM + row] = __float2bfloat16(f[e] + b);
+        named_bar_sync(2, kEpiThreads);
+#pragma unroll
+        for (int v = 0; v < C::CW * (BM / 8) / kEpiThreads; ++v) {
+          const int vid = v * kEpiThreads + epi_tid;
+          const int e = vid / (BM / 8);
+          const int part = vid - e * (BM / 8);
+          const int tok = sg.m0 + c0 + e;
+          const int gn = sg.n0 + part * 8;
+          if (tok < sg.m_limit && gn < p.N)
+            *reinterpret_cast<uint4*>(out_ptr(p, tok, gn)) = *reinterpret_cast<const uint4*>(st + e * BM + part * 8);
+        }
+        named_bar_sync(2, kEpiThreads);
+      }
+    };
     while (!*abort_flag && iter.next(p, sg)) {
       if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase)) {
         report(p.status, kTimeoutTmemFull, sg.tile_id, acc);
@@ -330,64 +417,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         break;
       }
       tc_fence_after_sync();
+      if (epi_tid == 0) stamp(4);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       const int tile_id = sg.tile_id;
       const bool direct = (sg.n_contrib == 1);
       float* ws_tile = direct ? nullptr
                               : p.workspace + (static_cast<size_t>(tile_id) * p.splits + sg.slot) * (BM * BN);
 
-      auto store_chunk = [&](const float* f, int c0) {
-        // f[0..CW): accumulator row `row`, columns c0..c0+CW of this tile
-        if constexpr (MODE == 0) {
-          // rows are tokens, columns are outputs: transpose through smem so that global stores
-          // are 16-byte vectors covering whole 64-byte row segments
-          const int gm0 = sg.m0 + q * 32;
-          const int gn0 = sg.n0 + c0;
-#pragma unroll
-          for (int j = 0; j < C::CW / 8; ++j) {
-            float g[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              g[e] = f[j * 8 + e];
-              if (p.bias != nullptr) {
-                const int gn = gn0 + j * 8 + e;
-                if (gn < p.N) g[e] += __bfloat162float(p.bias[gn]);
-              }
-            }
-            uint4 v = make_uint4(pack_bf16(g[0], g[1]), pack_bf16(g[2], g[3]), pack_bf16(g[4], g[5]),
-                                 pack_bf16(g[6], g[7]));
-            const int pj = j ^ ((lane >> 1) & (C::CW / 8 - 1));
-            *reinterpret_cast<uint4*>(my_stage + lane * (C::CW * 2) + pj * 16) = v;
-          }
-          __syncwarp();
-          constexpr int kChunksPerRow = C::CW / 8;            // 16-byte chunks per staged row
-          constexpr int kRowsPerIt = 32 / kChunksPerRow;
-#pragma unroll
-          for (int it = 0; it < 32 / kRowsPerIt; ++it) {
-            const int r = it * kRowsPerIt + lane / kChunksPerRow;
-            const int jj = lane % kChunksPerRow;
-            const int pj = jj ^ ((r >> 1) & (kChunksPerRow - 1));
-            const uint4 v = *reinterpret_cast<const uint4*>(my_stage + r * (C::CW * 2) + pj * 16);
-            const int gm = gm0 + r;
-            const int gn = gn0 + jj * 8;
-            if (gm < sg.m_limit && gn < p.N) {
-              *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(gm) * p.N + gn) = v;
-            }
-          }
-          __syncwarp();
-        } else {
-          // rows are outputs (weight rows), columns are tokens: out[token][n]
-          const int gn = sg.n0 + row;
-          if (gn < p.N) {
-            const float b = p.bias != nullptr ? __bfloat162float(p.bias[gn]) : 0.f;
-#pragma unroll
-            for (int e = 0; e < C::CW; ++e) {
-              const int tok = sg.m0 + c0 + e;
-              if (tok < sg.m_limit) p.out[static_cast<size_t>(tok) * p.N + gn] = __float2bfloat16(f[e] + b);
-            }
-          }
-        }
-      };
 
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += C::CW) {
@@ -399,11 +435,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           float f[C::CW];
 #pragma unroll
           for (int e = 0; e < C::CW; ++e) f[e] = __uint_as_float(v[e]);
-          store_chunk(f, c0);
+          store_chunk(sg, f, c0);
         } else {
-          // partial tile, column-major inside the tile so a warp writes 128 contiguous bytes
+          // layout [col / 4][row][4]: the 32 rows of a warp write 512 contiguous bytes
+          uint4* dst = reinterpret_cast<uint4*>(ws_tile) + (c0 / 4) * BM + row;
 #pragma unroll
-          for (int e = 0; e < C::CW; ++e) ws_tile[(c0 + e) * BM + row] = __uint_as_float(v[e]);
+          for (int e = 0; e < C::CW / 4; ++e) dst[e * BM] = make_uint4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
         }
       }
       // accumulator drained: hand the TMEM buffer back to the MMA warp
@@ -415,38 +452,134 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (!direct) {
         __threadfence();
         named_bar_sync(1, kEpiThreads);
-        if (epi_tid == 0) {
-          const int old = atomicAdd(&p.counters[tile_id], 1);
-          const int last = (old == sg.n_contrib - 1) ? 1 : 0;
-          if (last) p.counters[tile_id] = 0;    // leave the counter clean for the next launch
-          *last_flag = last;
-        }
-        named_bar_sync(1, kEpiThreads);
-        const bool is_last = *last_flag != 0;
-        named_bar_sync(1, kEpiThreads);
-        if (is_last) {
-          __threadfence();
-          const float* ws0 = p.workspace + static_cast<size_t>(tile_id) * p.splits * (BM * BN);
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += C::CW) {
-            float f[C::CW];
-#pragma unroll
-            for (int e = 0; e < C::CW; ++e) f[e] = 0.f;
-            for (int s = 0; s < sg.n_contrib; ++s) {
-              const float* wsp = ws0 + static_cast<size_t>(s) * (BM * BN);
-#pragma unroll
-              for (int e = 0; e < C::CW; ++e) f[e] += __ldcg(&wsp[(c0 + e) * BM + row]);
-            }
-            store_chunk(f, c0);
+        if (epi_tid == 0) stamp(8);
+        if (p.units_per_cta > 0) {
+          // stream-K: publish the partial now, reduce later (after all of this CTA's partials are
+          // out, so that no CTA ever waits for a CTA that is itself waiting)
+          if (epi_tid == 0) atomicAdd(&p.counters[tile_id], 1);
+          if (n_pending < 2) pending[n_pending++] = sg;
+        } else {
+          if (epi_tid == 0) {
+            const int old = atomicAdd(&p.counters[tile_id], 1);
+            const int last = (old == sg.n_contrib - 1) ? 1 : 0;
+            if (last) p.counters[tile_id] = 0;    // leave the counter clean for the next launch
+            *last_flag = last;
           }
+          named_bar_sync(1, kEpiThreads);
+          const bool is_last = *last_flag != 0;
+          named_bar_sync(1, kEpiThreads);
+          if (is_last) {
+            __threadfence();
+            const float* ws0 = p.workspace + static_cast<size_t>(tile_id) * p.splits * (BM * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += C::CW) {
+              float f[C::CW];
+#pragma unroll
+              for (int e = 0; e < C::CW; ++e) f[e] = 0.f;
+              for (int sp = 0; sp < sg.n_contrib; ++sp) {
+                const uint4* src = reinterpret_cast<const uint4*>(ws0 + static_cast<size_t>(sp) * (BM * BN)) + (c0 / 4) * BM + row;
+#pragma unroll
+                for (int e = 0; e < C::CW / 4; ++e) {
+                  const uint4 q4 = __ldcg(src + e * BM);
+                  f[4 * e] += __uint_as_float(q4.x);
+                  f[4 * e + 1] += __uint_as_float(q4.y);
+                  f[4 * e + 2] += __uint_as_float(q4.z);
+                  f[4 * e + 3] += __uint_as_float(q4.w);
+                }
+              }
+              store_chunk(sg, f, c0);
+            }
+          }
+        }
+      }
+    }
+
+    // ---- stream-K: cooperative reduction of the tiles this CTA shares with its neighbours.  Every
+    // contributor of a tile sums a different subset of the tile's column chunks over all partials
+    // (in slot order: deterministic), so the fix-up work per CTA is one tile's worth of reads no
+    // matter how many CTAs share the tile.
+    for (int pi = 0; pi < n_pending && !*abort_flag; ++pi) {
+      const Seg ps = pending[pi];
+      if (epi_tid == 0) {
+        const uint64_t t0 = global_timer_ns();
+        uint32_t spins = 0;
+        int ok = 1;
+        while (*reinterpret_cast<volatile int*>(&p.counters[ps.tile_id]) < ps.n_contrib) {
+          if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+            report(p.status, kTimeoutTmemFull, ps.tile_id, 100 + ps.slot);
+            *abort_flag = 1;
+            ok = 0;
+            break;
+          }
+        }
+        *last_flag = ok;
+        __threadfence();
+      }
+      named_bar_sync(1, kEpiThreads);
+      const bool ok = *last_flag != 0;
+      named_bar_sync(1, kEpiThreads);
+      if (epi_tid == 0) stamp(9 + 2 * pi);
+      if (ok) {
+        const float* ws0 = p.workspace + static_cast<size_t>(ps.tile_id) * p.splits * (BM * BN);
+#pragma unroll 1
+        for (int c0 = ps.slot * C::CW; c0 < BN; c0 += ps.n_contrib * C::CW) {
+          float f[C::CW];
+#pragma unroll
+          for (int e = 0; e < C::CW; ++e) f[e] = 0.f;
+          int sp = 0;
+          for (; sp + 1 < ps.n_contrib; sp += 2) {      // two partials in flight per thread
+            const uint4* s0 = reinterpret_cast<const uint4*>(ws0 + static_cast<size_t>(sp) * (BM * BN)) + (c0 / 4) * BM + row;
+            const uint4* s1 = s0 + (BM * BN) / 4;
+            uint4 a4[C::CW / 4], b4[C::CW / 4];
+#pragma unroll
+            for (int e = 0; e < C::CW / 4; ++e) {
+              a4[e] = __ldcg(s0 + e * BM);
+              b4[e] = __ldcg(s1 + e * BM);
+            }
+#pragma unroll
+            for (int e = 0; e < C::CW / 4; ++e) {
+              f[4 * e] += __uint_as_float(a4[e].x);
+              f[4 * e + 1] += __uint_as_float(a4[e].y);
+              f[4 * e + 2] += __uint_as_float(a4[e].z);
+              f[4 * e + 3] += __uint_as_float(a4[e].w);
+              f[4 * e] += __uint_as_float(b4[e].x);
+              f[4 * e + 1] += __uint_as_float(b4[e].y);
+              f[4 * e + 2] += __uint_as_float(b4[e].z);
+              f[4 * e + 3] += __uint_as_float(b4[e].w);
+            }
+          }
+          if (sp < ps.n_contrib) {
+            const uint4* s0 = reinterpret_cast<const uint4*>(ws0 + static_cast<size_t>(sp) * (BM * BN)) + (c0 / 4) * BM + row;
+#pragma unroll
+            for (int e = 0; e < C::CW / 4; ++e) {
+              const uint4 q4 = __ldcg(s0 + e * BM);
+              f[4 * e] += __uint_as_float(q4.x);
+              f[4 * e + 1] += __uint_as_float(q4.y);
+              f[4 * e + 2] += __uint_as_float(q4.z);
+              f[4 * e + 3] += __uint_as_float(q4.w);
+            }
+          }
+          store_chunk(ps, f, c0);
+        }
+      }
+      // the contributor that finishes last leaves both counters clean for the next launch
+      named_bar_sync(1, kEpiThreads);
+      if (epi_tid == 0) stamp(10 + 2 * pi);
+      if (epi_tid == 0) {
+        const int old = atomicAdd(&p.counters[kDoneCounterOffset + ps.tile_id], 1);
+        if (old == ps.n_contrib - 1) {
+          p.counters[kDoneCounterOffset + ps.tile_id] = 0;
+          p.counters[ps.tile_id] = 0;
         }
       }
     }
   }
 
   // ------------------------------------------------------------------ teardown
+  if (threadIdx.x == 64) stamp(5);
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) stamp(6);
   if (*abort_flag) {
     // give copies that are still in flight time to land before the CTA's smem is released
     const uint64_t t0 = global_timer_ns();
@@ -456,6 +589,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::kTmemCols);
+    if (lane == 0) stamp(7);
   }
 }
 
@@ -501,14 +635,49 @@ int sglb_gemm_max_counters(int N) { return (N + 127) / 128 + 8; }
 // pointers 16-byte aligned.  `workspace`/`counters` are only touched when M <= 256 and the
 // launcher decides to split K; `counters` must be zero on entry (the kernel restores zeros).
 // force_mode: -1 auto, 0 tokens-on-M, 1 weights-on-M.  force_splits: 0 auto.
+int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                        void* workspace, size_t workspace_bytes, int* counters, int force_mode, int force_splits,
+                        void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream);
+
 int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, void* workspace,
                    size_t workspace_bytes, int* counters, int force_mode, int force_splits, cudaStream_t stream) {
+  return sglb_gemm_bf16_impl(x, w, bias, out, M, N, K, workspace, workspace_bytes, counters, force_mode, force_splits,
+                             nullptr, 0, 0, stream);
+}
+
+// Row-parallel GEMM whose epilogue performs the reduce-scatter sends: `rs_peers[r]` is rank r's
+// receive buffer ([world][ceil(M / world)][N] bf16, symmetric memory).  A cross-rank barrier must
+// separate this launch from the kernel that reduces the received slices (sglb_ar_residual_rmsnorm
+// with rs_mode = 1 starts with one).
+int sglb_gemm_bf16_rs(const void* x, const void* w, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                      int* counters, void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream) {
+  if (rs_world < 1 || rs_world > 8 || rs_peers == nullptr) return -sglb::kBadArgument;
+  return sglb_gemm_bf16_impl(x, w, nullptr, nullptr, M, N, K, workspace, workspace_bytes, counters, -1, 0, rs_peers,
+                             rs_world, rs_rank, stream);
+}
+
+static unsigned long long* g_debug_stamps = nullptr;
+// Profiling aid: when set, CTA 0 of every dense GEMM launch writes globaltimer stamps (kernel start,
+// after set-up barrier, producer done, MMA issue done, first accumulator ready, epilogue done,
+// teardown barrier, TMEM freed) into this device buffer of 16 u64.
+void sglb_gemm_set_debug_stamps(void* dev_ptr) { g_debug_stamps = static_cast<unsigned long long*>(dev_ptr); }
+
+int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                        void* workspace, size_t workspace_bytes, int* counters, int force_mode, int force_splits,
+                        void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream) {
   using namespace sglb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (N % 8)) return -kBadArgument;
   const int kb_total = (K + BK - 1) / BK;
   const int sms = sm_count();
-  int mode = force_mode >= 0 ? force_mode : (M <= 256 ? 1 : 0);
+  // Decode-sized batches: both operand assignments stream the weights once; they differ in how many
+  // activation bytes each K block re-reads from L2 per weight byte (tokens-on-M with 256 weight rows
+  // per tile: M*128 B per 32 KiB of weights; weights-on-M: BN*128 B per 16 KiB).
+  static const int decode_mode = [] {
+    const char* e = getenv("SGLB_DECODE_GEMM_MODE");
+    return e ? atoi(e) : 1;
+  }();
+  int mode = force_mode >= 0 ? force_mode : (M <= 256 ? decode_mode : 0);
   if (mode == 1 && M > 256) mode = 0;
 
   Params p{};
@@ -522,6 +691,13 @@ int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, in
   p.K = K;
   p.kb_total = kb_total;
   p.splits = 1;
+  p.debug_stamps = g_debug_stamps;
+  if (rs_world > 0) {
+    p.rs_world = rs_world;
+    p.rs_rank = rs_rank;
+    p.rs_rows_per = (M + rs_world - 1) / rs_world;
+    for (int r = 0; r < rs_world; ++r) p.rs_peer[r] = static_cast<__nv_bfloat16*>(rs_peers[r]);
+  }
 
   CUtensorMap ta, tb;
   cudaError_t err;
@@ -532,7 +708,22 @@ int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, in
     p.tiles_b = (N + bn - 1) / bn;
     if (!encode_tmap_2d(&ta, x, K, M, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
     if (!encode_tmap_2d(&tb, w, K, N, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
-    const int grid = min(p.tiles_a * p.tiles_b, sms);
+    int grid = min(p.tiles_a * p.tiles_b, sms);
+    if (M <= 256 && force_splits <= 0 && workspace != nullptr && counters != nullptr) {
+      // decode-sized: stream-K so that every SM streams the same number of weight bytes
+      const int tiles = p.tiles_a * p.tiles_b;
+      const int total = tiles * kb_total;
+      int upc = (total + sms - 1) / sms;
+      if (upc < 8) upc = min(8, kb_total);
+      const int max_contrib = (kb_total + upc - 1) / upc + 1;
+      const size_t need = static_cast<size_t>(tiles) * max_contrib * BM * bn * sizeof(float);
+      if (need <= workspace_bytes && tiles <= kDoneCounterOffset) {
+        p.units_per_cta = upc;
+        p.total_units = total;
+        p.splits = max_contrib;
+        grid = (total + upc - 1) / upc;
+      }
+    }
     err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
   } else {
     const int bn = pick_bn_tokens(M);
@@ -547,10 +738,10 @@ int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, in
       const int total = p.tiles_a * kb_total;
       const int min_upc = bn >= 128 ? 16 : (bn >= 64 ? 12 : 8);
       int upc = (total + sms - 1) / sms;
-      if (upc < min_upc) upc = min_upc;
+      if (upc < min_upc) upc = min(min_upc, kb_total);   // never force several tiles onto one CTA
       const int max_contrib = (kb_total + upc - 1) / upc + 1;
       const size_t need = static_cast<size_t>(p.tiles_a) * max_contrib * BM * bn * sizeof(float);
-      if (need <= workspace_bytes && p.tiles_a <= 4096) {
+      if (need <= workspace_bytes && p.tiles_a <= kDoneCounterOffset) {
         p.units_per_cta = upc;
         p.total_units = total;
         splits = max_contrib;               // workspace slots per tile
@@ -766,10 +957,10 @@ extern "C" int sglb_grouped_gemm_bf16(const void* x, const void* w, void* out, c
     const int total = groups * p.tiles_a * kb_total;
     const int min_upc = bn >= 128 ? 16 : (bn >= 64 ? 12 : 8);
     int upc = (total + sms - 1) / sms;
-    if (upc < min_upc) upc = min_upc;
+    if (upc < min_upc) upc = min(min_upc, kb_total > 0 ? kb_total : 1);
     int max_contrib = (kb_total + upc - 1) / upc + 1;
     size_t need = static_cast<size_t>(groups) * p.tiles_a * max_contrib * BM * bn * sizeof(float);
-    if (need > workspace_bytes || groups * p.tiles_a > 4096 || workspace == nullptr || counters == nullptr) {
+    if (need > workspace_bytes || groups * p.tiles_a > kDoneCounterOffset || workspace == nullptr || counters == nullptr) {
       // no room for shared tiles: whole tiles per CTA
       upc = kb_total * ((total / kb_total + sms - 1) / sms);
       max_contrib = 1;

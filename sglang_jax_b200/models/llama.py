@@ -21,6 +21,7 @@ from ..layers.layernorm import RMSNorm
 from ..layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
 from ..layers.logits_processor import LogitsProcessor
 from ..layers.radix_attention import RadixAttention
+from ..utils.precision_tracer import precision_tracer
 
 
 class DenseMLP(nn.Module):
@@ -104,11 +105,18 @@ class DenseModel(nn.Module):
         h = self.layers[0].input_layernorm(residual)
         aux = []
         n = len(self.layers)
+        tracing = precision_tracer.enabled
+        if tracing:
+            precision_tracer.begin_forward()
+            precision_tracer.record(residual, "embed_tokens", forward_batch.forward_mode.name)
         for i, layer in enumerate(self.layers):
             if i in self.layers_to_capture:
                 aux.append(residual)
             nxt = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
             h, residual = layer(h, residual, forward_batch, nxt)
+            if tracing:
+                precision_tracer.record(residual, "layer_residual", forward_batch.forward_mode.name, i)
+                precision_tracer.record(h, "layer_output_normed", forward_batch.forward_mode.name, i)
         return (h, aux) if self.layers_to_capture else h
 
 

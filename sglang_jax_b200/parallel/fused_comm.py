@@ -52,7 +52,11 @@ class FusedComm:
         L.sglb_ar_residual_rmsnorm.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                                ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int,
-                                               ctypes.c_void_p]
+                                               ctypes.c_int, ctypes.c_void_p]
+        L.sglb_gemm_bf16_rs.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                        ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        self.push_epilogue = True   # GEMM epilogue does the reduce-scatter sends
         L.sglb_argmax_gather.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
@@ -68,7 +72,7 @@ class FusedComm:
                     symm_mem.enable_symm_mem_for_group(group.group_name)
         except Exception:
             pass
-        n = max_tokens * hidden
+        n = (max_tokens + 8) * hidden     # room for ceil(T / world) * world rows
         self.ypart = _Symm(n, dtype, self.device, group)        # row-parallel GEMM partials
         self.gathered = _Symm(n, dtype, self.device, group)     # normalised activations, all rows
         self.flags = _Symm(L.sglb_comm_flag_bytes() // 4, torch.int32, self.device, group)
@@ -98,18 +102,25 @@ class FusedComm:
         return self.ypart.tensor[: T * self.hidden].view(T, self.hidden)
 
     def gemm_allreduce_add_rmsnorm(self, x, w, residual, norm_w, eps, gemma=False):
-        T = x.shape[0]
+        T, K = x.shape
+        if self.push_epilogue and K % 8 == 0 and x.is_contiguous() and w.is_contiguous():
+            sc = native.gemm_scratch(x.device)
+            rc = self.L.sglb_gemm_bf16_rs(x.data_ptr(), w.data_ptr(), T, self.hidden, K, sc.workspace.data_ptr(),
+                                          sc.bytes, sc.counters.data_ptr(), self.ypart.ptrs, self.world, self.rank,
+                                          torch.cuda.current_stream().cuda_stream)
+            native._check(rc, "gemm_bf16_rs")
+            return self.allreduce_add_rmsnorm(T, residual, norm_w, eps, gemma, rs_mode=1)
         native.linear(x, w, None, out=self.partial_buffer(T))
         return self.allreduce_add_rmsnorm(T, residual, norm_w, eps, gemma)
 
-    def allreduce_add_rmsnorm(self, T: int, residual, norm_w, eps, gemma=False):
+    def allreduce_add_rmsnorm(self, T: int, residual, norm_w, eps, gemma=False, rs_mode: int = 0):
         H = self.hidden
         assert residual is None or (residual.is_contiguous() and residual.shape == (T, H))
         rc = self.L.sglb_ar_residual_rmsnorm(self.ypart.ptrs, self.gathered.ptrs, self.flags.ptrs,
                                              self.epochs.data_ptr(),
                                              residual.data_ptr() if residual is not None else None,
                                              norm_w.data_ptr(), T, H, self.rank, self.world, float(eps), int(gemma),
-                                             torch.cuda.current_stream().cuda_stream)
+                                             rs_mode, torch.cuda.current_stream().cuda_stream)
         native._check(rc, "ar_residual_rmsnorm")
         return self.gathered.tensor[: T * H].view(T, H), residual
 

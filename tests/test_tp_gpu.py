@@ -79,7 +79,7 @@ def _kernels(rank, world):
         res_mine = res.clone()
         rc = comm.L.sglb_ar_residual_rmsnorm(comm.ypart.ptrs, comm.gathered.ptrs, comm.flags.ptrs,
                                              comm.epochs.data_ptr(), res_mine.data_ptr(), w.data_ptr(), T, H, rank,
-                                             world, 1e-6, 0, torch.cuda.current_stream().cuda_stream)
+                                             world, 1e-6, 0, 0, torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         torch.cuda.synchronize()
         native.check_status()
@@ -93,6 +93,24 @@ def _kernels(rank, world):
         res_err = (res_mine[lo:hi].float() - exp_res[lo:hi].float()).abs().max().item() if hi > lo else 0.0
         report[T] = (err, res_err)
         assert err < 0.1 and res_err < 0.07, (T, err, res_err)
+    # GEMM whose epilogue pushes the reduce-scatter slices, then reduce + norm + all-gather
+    for T in (5, 128, 400):
+        K = 512
+        gx = [torch.Generator(device=dev).manual_seed(300 + r) for r in range(world)]
+        xs = [torch.randn(T, K, device=dev, generator=g).to(torch.bfloat16) for g in gx]
+        ws = [(torch.randn(H, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for g in gx]
+        g0 = torch.Generator(device=dev).manual_seed(9)
+        res = torch.randn(T, H, device=dev, generator=g0).to(torch.bfloat16)
+        nw = (torch.randn(H, device=dev, generator=g0) * 0.1 + 1).to(torch.bfloat16)
+        mine = res.clone()
+        out, _ = comm.gemm_allreduce_add_rmsnorm(xs[rank], ws[rank], mine, nw, 1e-6)
+        torch.cuda.synchronize()
+        native.check_status()
+        total = sum((x.float() @ w_.float().t()).to(torch.bfloat16).float() for x, w_ in zip(xs, ws)) + res.float()
+        exp = ref.rmsnorm(total.to(torch.bfloat16), nw, 1e-6)
+        err = (out.float() - exp.float()).abs().max().item()
+        assert err < 0.15, ("gemm_rs", T, err)
+        report[f"gemm_rs_{T}"] = err
     # vocab-parallel argmax
     B, V = 37, 1000
     g = torch.Generator(device=dev).manual_seed(5)
