@@ -58,6 +58,15 @@ def load_hf_config(model_path: str, trust_remote_code: bool = False, revision: s
     return cfg
 
 
+# target architecture -> class that loads its MTP / NextN layers as a draft model
+_NEXTN_ARCH = {
+    "MiMoForCausalLM": "MiMoMTP",
+    "DeepseekV3ForCausalLM": "DeepseekV3ForCausalLMNextN",
+    "MiMoV2FlashForCausalLM": "MiMoV2NextN",
+    "Glm4MoeForCausalLM": "Glm4MoeForCausalLMNextN",
+}
+
+
 class ModelConfig:
     def __init__(self, model_path: str, hf_config=None, dtype: str = "auto", context_length: int | None = None,
                  trust_remote_code: bool = False, revision: str | None = None, quantization: str | None = None,
@@ -78,6 +87,9 @@ class ModelConfig:
         self.is_embedding = is_embedding
         self.is_draft_model = is_draft_model
         self.architectures = list(getattr(self.hf_config, "architectures", None) or ["LlamaForCausalLM"])
+        if is_draft_model:
+            # multi-token-prediction heads live in the target checkpoint under their own class
+            self.architectures = [_NEXTN_ARCH.get(a, a) for a in self.architectures]
         self.quantization = quantization
         self.moe_backend = MoEBackend(moe_backend)
         self.ep_size = ep_size

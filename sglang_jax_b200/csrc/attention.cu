@@ -43,6 +43,9 @@ struct AttnParams {
   int B, Hq, Hkv, max_pages, page_size, num_splits;
   int window;                   // 0 = none
   float scale, soft_cap;
+  // extend only: visibility inside the last `tail_len` keys, [B, mask_rows, tail_len] bytes (null = causal)
+  const uint8_t* tail_mask;
+  int tail_len, mask_rows;
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -116,10 +119,13 @@ struct WarpState {
 // Process NT (16 or 64) KV tokens starting at tile-local row `r0` against the warp's 16 query rows.
 // `kmax[i]` (i = 0 for row g, 1 for row g+8) is the last visible KV index (inclusive) and `kmin[i]`
 // the first, in absolute token positions; `tok_base` is the absolute index of tile row 0.
-template <int D, int NT>
+// With MASK, keys at absolute index >= `tail_start` are visible to row i only where
+// `mask_row[i][key - tail_start]` is non-zero (speculative token trees, bidirectional blocks).
+template <int D, int NT, bool MASK = false>
 __device__ __forceinline__ void attend(WarpState<D>& st, const uint32_t (&qf)[D / 16][4], uint32_t k_smem,
                                        uint32_t v_smem, int r0, int tok_base, const int (&kmin)[2],
-                                       const int (&kmax)[2], float scale_log2, float soft_cap, float scale) {
+                                       const int (&kmax)[2], float scale_log2, float soft_cap, float scale,
+                                       const uint8_t* const* mask_row = nullptr, int tail_start = 0) {
   constexpr int NJ = NT / 8;
   const int lane = threadIdx.x & 31;
   const int t4 = lane & 3;
@@ -153,7 +159,11 @@ __device__ __forceinline__ void attend(WarpState<D>& st, const uint32_t (&qf)[D 
       float v = s[j][e];
       if (soft_cap > 0.f) v = soft_cap * tanhf(v * scale / soft_cap) * kLog2e;
       else v *= scale_log2;
-      v = (tok <= kmax[i] && tok >= kmin[i]) ? v : -INFINITY;
+      bool ok = tok <= kmax[i] && tok >= kmin[i];
+      if (MASK) {
+        if (ok && tok >= tail_start) ok = mask_row[i] != nullptr && mask_row[i][tok - tail_start] != 0;
+      }
+      v = ok ? v : -INFINITY;
       s[j][e] = v;
       mx[i] = fmaxf(mx[i], v);
     }
@@ -424,7 +434,8 @@ paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
   const int seq = p.seq_lens[b];
   const int q0 = tile_in_seq * BQ;                         // first query row (within the sequence's new tokens)
   const int q_hi = min(q0 + BQ, q_len);
-  const int kv_end = min(seq, prefix + q_hi);              // causal upper bound for this tile
+  const bool masked = p.tail_mask != nullptr;
+  const int kv_end = masked ? seq : min(seq, prefix + q_hi);   // causal upper bound for this tile
   int first_tok = 0;
   if (p.window > 0) first_tok = max(0, prefix + q0 - p.window + 1);
   const int t0 = first_tok / TN;
@@ -480,14 +491,21 @@ paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
       qf[kk][3] = r_hi < q_len ? *reinterpret_cast<const uint32_t*>(qb + kk * 16 + 8 + t4 * 2) : 0u;
     }
   }
-  const int kmax[2] = {min(prefix + r_lo, seq - 1), min(prefix + r_hi, seq - 1)};
+  const int kmax[2] = {masked ? seq - 1 : min(prefix + r_lo, seq - 1), masked ? seq - 1 : min(prefix + r_hi, seq - 1)};
+  const uint8_t* mask_row[2] = {nullptr, nullptr};
+  if (masked) {
+    const uint8_t* mb = p.tail_mask + static_cast<size_t>(b) * p.mask_rows * p.tail_len;
+    if (r_lo < q_len && r_lo < p.mask_rows) mask_row[0] = mb + static_cast<size_t>(r_lo) * p.tail_len;
+    if (r_hi < q_len && r_hi < p.mask_rows) mask_row[1] = mb + static_cast<size_t>(r_hi) * p.tail_len;
+  }
+  const int tail_start = seq - p.tail_len;
   int kmin[2] = {0, 0};
   if (p.window > 0) {
     kmin[0] = max(0, prefix + r_lo - p.window + 1);
     kmin[1] = max(0, prefix + r_hi - p.window + 1);
   }
   // rows of this warp see KV up to prefix + q0 + warp*16 + 15: later tiles are fully masked for it
-  const int warp_kv_end = min(seq, prefix + min(q0 + warp * 16 + 16, q_len));
+  const int warp_kv_end = masked ? seq : min(seq, prefix + min(q0 + warp * 16 + 16, q_len));
   const float scale_log2 = p.scale * kLog2e;
   int stage = 0;
   uint32_t phase = 0;
@@ -499,8 +517,13 @@ paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
     }
     const uint32_t ks = smem_u32(smem + stage * S::kBytes);
     const uint32_t vs = ks + S::kHalves * S::kHalfBytes;
-    if (t * TN < warp_kv_end && q0 + warp * 16 < q_len)
-      attend<D, TN>(st, qf, ks, vs, 0, t * TN, kmin, kmax, scale_log2, p.soft_cap, p.scale);
+    if (t * TN < warp_kv_end && q0 + warp * 16 < q_len) {
+      if (masked && (t + 1) * TN > tail_start)
+        attend<D, TN, true>(st, qf, ks, vs, 0, t * TN, kmin, kmax, scale_log2, p.soft_cap, p.scale, mask_row,
+                            tail_start);
+      else
+        attend<D, TN>(st, qf, ks, vs, 0, t * TN, kmin, kmax, scale_log2, p.soft_cap, p.scale);
+    }
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
     if (++stage == stages) {
@@ -631,11 +654,30 @@ int sglb_paged_decode(const void* q, void* out, const void* kv_buffer, long long
 }
 
 // `num_q_tiles_bound` >= sum_b ceil(q_len_b / 64); T/64 + B always is.
+// `tail_mask` (optional, [B, mask_rows, tail_len] bytes): visibility of the last `tail_len` keys of
+// every sequence per query row; earlier keys are visible to all rows and the causal rule is dropped.
+int sglb_paged_extend_masked(const void* q, void* out, const void* kv_buffer, long long num_pages,
+                             const int* page_table, int max_pages, const int* req_pool_indices, const int* seq_lens,
+                             const int* prefix_lens, const int* cu_q_lens, int B, int num_q_tiles_bound, int Hq,
+                             int Hkv, int D, int page_size, float scale, int window, float soft_cap,
+                             const void* tail_mask, int tail_len, int mask_rows, cudaStream_t stream);
+
 int sglb_paged_extend(const void* q, void* out, const void* kv_buffer, long long num_pages, const int* page_table,
                       int max_pages, const int* req_pool_indices, const int* seq_lens, const int* prefix_lens,
                       const int* cu_q_lens, int B, int num_q_tiles_bound, int Hq, int Hkv, int D, int page_size,
                       float scale, int window, float soft_cap, cudaStream_t stream) {
+  return sglb_paged_extend_masked(q, out, kv_buffer, num_pages, page_table, max_pages, req_pool_indices, seq_lens,
+                                  prefix_lens, cu_q_lens, B, num_q_tiles_bound, Hq, Hkv, D, page_size, scale, window,
+                                  soft_cap, nullptr, 0, 0, stream);
+}
+
+int sglb_paged_extend_masked(const void* q, void* out, const void* kv_buffer, long long num_pages,
+                             const int* page_table, int max_pages, const int* req_pool_indices, const int* seq_lens,
+                             const int* prefix_lens, const int* cu_q_lens, int B, int num_q_tiles_bound, int Hq,
+                             int Hkv, int D, int page_size, float scale, int window, float soft_cap,
+                             const void* tail_mask, int tail_len, int mask_rows, cudaStream_t stream) {
   using namespace sglb;
+  if (tail_mask != nullptr && (tail_len <= 0 || mask_rows <= 0)) return -kBadArgument;
   if (B <= 0 || num_q_tiles_bound <= 0) return 0;
   if ((D != 64 && D != 128) || Hq % Hkv != 0) return -kBadArgument;
   if (page_size < TN ? (TN % page_size != 0) : (page_size % TN != 0)) return -kBadArgument;
@@ -652,6 +694,9 @@ int sglb_paged_extend(const void* q, void* out, const void* kv_buffer, long long
   p.status = device_status();
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.max_pages = max_pages; p.page_size = page_size;
   p.num_splits = 1; p.window = window; p.scale = scale; p.soft_cap = soft_cap;
+  p.tail_mask = static_cast<const uint8_t*>(tail_mask);
+  p.tail_len = tail_mask ? tail_len : 0;
+  p.mask_rows = mask_rows;
   const int stages = 3;
   dim3 grid(num_q_tiles_bound, Hq, 1);
   cudaError_t e;

@@ -136,7 +136,39 @@ __global__ void argmax_kernel(int* __restrict__ out, const T* __restrict__ logit
   const T* row = logits + blockIdx.x * row_stride;
   float best = -FLT_MAX;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  int scalar_from = 0;
+  if constexpr (sizeof(T) == 2) {
+    // 16-byte loads, four in flight per thread, when the row starts on a 16-byte boundary
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const int nvec = V / 8;
+      const uint4* rv = reinterpret_cast<const uint4*>(row);
+      constexpr int U = 4;
+      for (int base = threadIdx.x; base < nvec; base += blockDim.x * U) {
+        uint4 q[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * blockDim.x;
+          q[u] = idx < nvec ? __ldg(rv + idx) : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * blockDim.x;
+          const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float v = __uint_as_float((e & 1) ? (w[e >> 1] & 0xffff0000u) : (w[e >> 1] << 16));
+            const int i = idx * 8 + e;
+            if (v > best || (v == best && i < bi)) {
+              best = v;
+              bi = i;
+            }
+          }
+        }
+      }
+      scalar_from = nvec * 8;
+    }
+  }
+  for (int i = scalar_from + threadIdx.x; i < V; i += blockDim.x) {
     float v;
     if constexpr (sizeof(T) == 2) v = __bfloat162float(row[i]);
     else v = row[i];

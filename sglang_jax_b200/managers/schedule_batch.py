@@ -582,8 +582,14 @@ class ScheduleBatch:
         self.has_grammar = self.has_grammar or running_batch.has_grammar
 
     # ------------------------------------------------------------------ decode
+    # KV slots a speculative step reserves per request (set by the scheduler)
+    spec_alloc_len: int = 0
+
     def new_page_count_next_decode(self) -> int:
         ps = self.page_size
+        if self.spec_algorithm is not None and self.spec_alloc_len:
+            n = self.spec_alloc_len
+            return sum((r.kv_committed_len % ps + n + ps - 1) // ps for r in self.reqs)
         if ps == 1:
             return len(self.reqs)
         return sum(1 for r in self.reqs if r.kv_committed_len % ps == 0)
@@ -658,10 +664,24 @@ class ScheduleBatch:
             self.tree_cache.dec_lock_ref(r.last_node)
         pool.free(r.req_pool_idx)
 
+    def sampling_info_for_spec(self) -> ModelWorkerSamplingInfo:
+        return ModelWorkerSamplingInfo.from_reqs(self.reqs, self.vocab_size)
+
     def prepare_for_decode(self):
         """One new token per request (reference :1680-1811)."""
         self.forward_mode = ForwardMode.DECODE
         reqs = self.reqs
+        if self.spec_algorithm is not None:
+            # the speculative worker reserves its own slots (several tokens per request)
+            self.input_ids = np.empty(0, np.int32)
+            self.output_ids = None
+            self.req_pool_indices = np.asarray([r.req_pool_idx for r in reqs], dtype=np.int32)
+            self.seq_lens = np.asarray([r.kv_committed_len for r in reqs], dtype=np.int32)
+            self.out_cache_loc = np.empty(0, np.int32)
+            self.prefix_lens, self.extend_lens, self.extend_num_tokens = [], [], 0
+            self.num_decode_in_mixed = 0
+            self.decoding_reqs = None
+            return
         pool = self.req_to_token_pool
         alloc = self.token_to_kv_pool_allocator
         if self.enable_overlap:

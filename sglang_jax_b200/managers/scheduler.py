@@ -74,6 +74,11 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         self.page_size = server_args.page_size
         self.schedule_policy_name = server_args.schedule_policy
         self.enable_overlap = not server_args.disable_overlap_schedule
+        if server_args.speculative_algorithm is not None:
+            # a speculative step needs the accepted tokens of the previous one on the host
+            self.enable_overlap = False
+            server_args.disable_overlap_schedule = True
+            server_args.enable_mixed_chunk = False
         self.stream_interval = server_args.stream_interval
         self.spec_algorithm = server_args.speculative_algorithm
         self.is_embedding = server_args.is_embedding
@@ -98,6 +103,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             except Exception as e:  # the scheduler only needs it for stop strings
                 logger.warning("scheduler runs without a tokenizer: %s", e)
         self.draft_worker = None
+        self.spec_num_total_accepted_tokens = 0
+        self.spec_num_total_forward_ct = 0
         if self.spec_algorithm is not None and hasattr(tp_worker, "model_runner"):
             from ..speculative.spec_info import create_spec_worker
             self.draft_worker = create_spec_worker(server_args, tp_worker)
@@ -513,6 +520,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
 
     def update_running_batch(self, batch: ScheduleBatch) -> ScheduleBatch:
         batch.filter_batch()
+        if self.draft_worker is not None:
+            batch.spec_alloc_len = self.draft_worker.alloc_len
         if batch.is_empty():
             batch.batch_is_full = False
             return batch
@@ -577,7 +586,10 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         if self.is_embedding:
             self.process_batch_result_embedding(batch, result.embeddings)
         elif batch.forward_mode.is_decode():
-            self.process_batch_result_decode(batch, result)
+            if getattr(result, "spec_tokens", None) is not None:
+                self.process_batch_result_spec_decode(batch, result)
+            else:
+                self.process_batch_result_decode(batch, result)
         elif batch.forward_mode.is_extend():
             self.process_batch_result_prefill(batch, result)
         self.watchdog_last_forward_ct = self.forward_ct

@@ -93,6 +93,42 @@ class SchedulerOutputProcessorMixin:
         if self.forward_ct_decode % self.server_args.decode_log_interval == 0:
             self.log_decode_stats(batch)
 
+    def process_batch_result_spec_decode(self, batch: ScheduleBatch, result):
+        """A speculative step yields 1..num_draft_tokens tokens per request (reference
+        `scheduler_output_processor_mixin.py`, `accept_lens` / strided `next_token_ids`).
+        Tokens are appended one at a time so a stop condition inside the accepted run cuts
+        it; then the unused part of the step's KV reservation is returned."""
+        ps = self.page_size
+        alloc = self.token_to_kv_pool_allocator
+        for i, req in enumerate(batch.reqs):
+            if req.finished() or req.is_retracted:
+                continue
+            L = req.kv_committed_len
+            m = 0
+            for tok in result.spec_tokens[i]:
+                req.output_ids.append(int(tok))
+                m += 1
+                req.check_finished()
+                if req.finished():
+                    break
+            req.spec_verify_ct += 1
+            req.spec_accepted_tokens += m - 1
+            self.num_generated_tokens += m
+            self.spec_num_total_accepted_tokens += m
+            self.spec_num_total_forward_ct += 1
+            req.kv_committed_len = L + m
+            keep = (req.kv_committed_len + ps - 1) // ps * ps
+            end = int(result.alloc_ends[i])
+            if end > keep:
+                alloc.free(self.req_to_token_pool.read(req.req_pool_idx, end)[keep:].copy(), dp_rank=batch.dp_rank)
+            req.kv_allocated_len = req.kv_committed_len
+            if req.finished():
+                self._finish_req(req)
+        self.stream_output(batch.reqs, batch.return_logprob)
+        self.forward_ct_decode += 1
+        if self.forward_ct_decode % self.server_args.decode_log_interval == 0:
+            self.log_decode_stats(batch)
+
     def process_batch_result_embedding(self, batch: ScheduleBatch, embeddings):
         emb = embeddings.float().cpu().tolist()
         rids, outs, ptoks, reasons = [], [], [], []

@@ -141,6 +141,16 @@ class KVCache:
     def cell_size_bytes(self) -> int:
         raise NotImplementedError
 
+    def move_kv(self, src_loc: torch.Tensor, dst_loc: torch.Tensor):
+        """Copy the entries of token slots `src_loc` to `dst_loc` in every layer (all sources
+        are read before any destination is written)."""
+        self.move_kv_cache(dst_loc, src_loc)
+
+    def move_kv_cache(self, tgt_loc: torch.Tensor, src_loc: torch.Tensor):
+        for layer in range(self.layer_num):
+            a, b = self.gather(layer + self.start_layer, src_loc)
+            self.set_kv_buffer(layer + self.start_layer, tgt_loc, a, b)
+
 
 class MHATokenToKVPool(KVCache):
     def __init__(self, size, page_size, dtype, head_num, head_dim, layer_num, device,

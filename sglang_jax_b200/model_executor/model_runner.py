@@ -195,6 +195,15 @@ class ModelRunner:
             return gr.replay(batch)
         fb = ForwardBatch.init_new(batch, self)
         self.h2d_bytes_total += fb.h2d_bytes
+        si = batch.spec_info
+        if si is not None:
+            # speculative forwards keep their token ids / positions on the device
+            if getattr(si, "input_ids", None) is not None:
+                fb.input_ids = si.input_ids
+            if getattr(si, "positions", None) is not None:
+                fb.positions = si.positions
+            if getattr(si, "all_logits", False):
+                fb.last_token_indices = None
         if self.server_args is not None and not self.server_args.disable_overlap_schedule:
             fb.input_ids = self.resolve_future_token_ids(fb.input_ids)
         comm = ps.get_state().fused_comm

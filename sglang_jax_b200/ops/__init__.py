@@ -71,11 +71,12 @@ def rope_qknorm_kvwrite(qkv, positions, cos_sin, q_norm_w, k_norm_w, eps, num_q_
 def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
                     cu_q_lens=None, prefix_lens=None, sliding_window=0, soft_cap=0.0, sinks=None,
                     custom_mask=None, max_q_len=0, max_seq_len=0):
-    if use_native(q) and kv_buffer.dtype == torch.bfloat16 and sinks is None and custom_mask is None \
+    compact_mask = custom_mask is None or (custom_mask.dim() == 3 and cu_q_lens is not None)
+    if use_native(q) and kv_buffer.dtype == torch.bfloat16 and sinks is None and compact_mask \
             and q.shape[-1] in (64, 128):
         return _native().paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size,
                                          scale, cu_q_lens, prefix_lens, sliding_window, soft_cap,
-                                         max_q_len, max_seq_len)
+                                         max_q_len, max_seq_len, tail_mask=custom_mask)
     return reference.paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
                                      cu_q_lens, prefix_lens, sliding_window, soft_cap, sinks, custom_mask)
 

@@ -58,6 +58,12 @@ def lib():
     L.sglb_paged_extend.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                     c_float, c_void_p]
+    L.sglb_paged_extend_masked.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p]
+    L.sglb_verify_tree_greedy.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                          c_int, c_void_p]
+    L.sglb_tree_mask.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     L.sglb_read_status.argtypes = [c_void_p]
     _LIB = L
     LOADED = True
@@ -196,7 +202,8 @@ def decode_num_splits(B: int, Hkv: int, max_seq_len: int) -> int:
 
 
 def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale, cu_q_lens=None,
-                    prefix_lens=None, sliding_window=0, soft_cap=0.0, max_q_len=0, max_seq_len=0, num_splits=None):
+                    prefix_lens=None, sliding_window=0, soft_cap=0.0, max_q_len=0, max_seq_len=0, num_splits=None,
+                    tail_mask=None):
     T, Hq, D = q.shape
     Hkv = kv_buffer.shape[2]
     B = req_pool_indices.shape[0]
@@ -204,7 +211,7 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
     if not ok_page or Hq // Hkv > 16:
         from . import reference
         return reference.paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
-                                         cu_q_lens, prefix_lens, sliding_window, soft_cap)
+                                         cu_q_lens, prefix_lens, sliding_window, soft_cap, None, tail_mask)
     q = q.contiguous()
     out = torch.empty_like(q)
     num_pages = kv_buffer.shape[0]
@@ -221,6 +228,15 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    _p(req_pool_indices), _p(seq_lens), B, Hq, Hkv, D, page_size, scale,
                                    int(sliding_window or 0), float(soft_cap or 0.0), num_splits, _p(part_o),
                                    _p(part_lse), _stream()), "paged_decode")
+    elif tail_mask is not None:
+        # [B, rows, tail] visibility of the trailing keys (speculative trees / bidirectional blocks)
+        tm = tail_mask.to(torch.uint8).contiguous()
+        bound = T // 64 + B
+        _check(L.sglb_paged_extend_masked(_p(q), _p(out), _p(kv_buffer), num_pages, _p(page_table), max_pages,
+                                          _p(req_pool_indices), _p(seq_lens), _p(prefix_lens), _p(cu_q_lens), B,
+                                          bound, Hq, Hkv, D, page_size, scale, int(sliding_window or 0),
+                                          float(soft_cap or 0.0), _p(tm), tm.shape[2], tm.shape[1], _stream()),
+               "paged_extend_masked")
     else:
         bound = T // 64 + B
         _check(L.sglb_paged_extend(_p(q), _p(out), _p(kv_buffer), num_pages, _p(page_table), max_pages,
@@ -228,6 +244,30 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
                                    _stream()), "paged_extend")
     return out
+
+
+def verify_tree_greedy(tokens, parent, target_ids, max_depth: int):
+    """`(accept [B], path [B, max_depth+1], bonus [B])`, all int64; see `speculative/eagle_util.py`."""
+    B, n = tokens.shape
+    tok = tokens.long().contiguous()
+    par = parent.long().contiguous()
+    tgt = target_ids.long().contiguous()
+    accept = torch.empty(B, dtype=torch.long, device=tok.device)
+    path = torch.empty((B, max_depth + 1), dtype=torch.long, device=tok.device)
+    bonus = torch.empty(B, dtype=torch.long, device=tok.device)
+    _check(lib().sglb_verify_tree_greedy(_p(tok), _p(par), _p(tgt), _p(accept), _p(path), _p(bonus), B, n,
+                                         int(max_depth), _stream()), "verify_tree_greedy")
+    return accept, path, bonus
+
+
+def tree_mask(parent):
+    """Ancestor mask `[B, n, n]` (uint8) and depths `[B, n]` of trees given by parent indices."""
+    B, n = parent.shape
+    par = parent.long().contiguous()
+    mask = torch.empty((B, n, n), dtype=torch.uint8, device=par.device)
+    depth = torch.empty((B, n), dtype=torch.long, device=par.device)
+    _check(lib().sglb_tree_mask(_p(par), _p(mask), _p(depth), B, n, _stream()), "tree_mask")
+    return mask, depth
 
 
 def embedding(ids, table, vocab_start=0, masked=False):

@@ -147,7 +147,12 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
         allowed = kpos <= qpos
         if sliding_window and sliding_window > 0:
             allowed &= kpos > qpos - sliding_window
-        if custom_mask is not None:
+        if custom_mask is not None and custom_mask.dim() == 3:
+            # compact form [B, q, tail]: the last `tail` keys follow the mask, earlier keys are visible
+            tail = custom_mask.shape[2]
+            allowed = torch.ones(n, S, dtype=torch.bool, device=q.device)
+            allowed[:, S - tail:] = custom_mask[b, :n].bool()
+        elif custom_mask is not None:
             m = custom_mask[mask_off:mask_off + n * S].view(n, S).bool()
             mask_off += n * S
             allowed = m

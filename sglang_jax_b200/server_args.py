@@ -283,9 +283,9 @@ class ServerArgs:
             if self.speculative_algorithm in ("EAGLE", "EAGLE3", "STANDALONE"):
                 assert self.speculative_draft_model_path, (
                     f"{self.speculative_algorithm} needs --speculative-draft-model-path")
-            if not self.disable_overlap_schedule and self.speculative_eagle_topk > 1:
-                # Tree drafting needs the verified ids before the next draft step.
-                self.disable_overlap_schedule = True
+            # Each speculative step needs the previous step's accepted tokens on the host.
+            self.disable_overlap_schedule = True
+            self.enable_mixed_chunk = False
         if self.disaggregation_mode != "null":
             assert self.disaggregation_bootstrap_url, "PD mode requires --disaggregation-bootstrap-url"
             assert self.page_size >= 16, "PD mode requires a page_size of at least 16"

@@ -100,3 +100,111 @@ def write_tiny_qwen3_checkpoint(path: str, seed: int = 0, config: dict | None = 
     sd = {k: v.to(dtype).contiguous() for k, v in tiny_qwen3_state_dict(cfg, seed).items()}
     save_file(sd, os.path.join(path, "model.safetensors"))
     return path
+
+
+def write_tiny_eagle_checkpoint(path: str, target_config: dict = TINY_QWEN3, kind: str = "eagle", seed: int = 3,
+                                draft_vocab_size: int | None = None) -> str:
+    """A random EAGLE (`kind="eagle"`) or EAGLE-3 (`kind="eagle3"`) draft head sized for
+    `target_config`, in the layout those checkpoints use (no embedding table; EAGLE shares
+    the target LM head, EAGLE-3 has its own, optionally over a reduced vocabulary)."""
+    from safetensors.torch import save_file
+    g = torch.Generator().manual_seed(seed)
+    H, I, V = target_config["hidden_size"], target_config["intermediate_size"], target_config["vocab_size"]
+    nh, nkv, D = target_config["num_attention_heads"], target_config["num_key_value_heads"], target_config["head_dim"]
+
+    def w(*shape):
+        return torch.empty(*shape, dtype=torch.float32).normal_(0, 0.02, generator=g)
+
+    cfg = dict(target_config)
+    cfg["num_hidden_layers"] = 1
+    cfg["model_type"] = "llama"
+    cfg["tie_word_embeddings"] = False
+    sd = {}
+    if kind == "eagle":
+        cfg["architectures"] = ["LlamaForCausalLMEagle"]
+        pre = "layers.0."
+        qkv_in = H
+        sd["fc.weight"] = w(H, 2 * H)
+        sd["fc.bias"] = torch.zeros(H)
+    else:
+        cfg["architectures"] = ["LlamaForCausalLMEagle3"]
+        dv = draft_vocab_size or V
+        cfg["draft_vocab_size"] = dv
+        pre = "midlayer."
+        qkv_in = 2 * H
+        sd["fc.weight"] = w(H, 3 * H)
+        sd[pre + "input_layernorm.weight"] = torch.ones(H)
+        sd[pre + "hidden_norm.weight"] = torch.ones(H)
+        sd["norm.weight"] = torch.ones(H)
+        sd["lm_head.weight"] = w(dv, H)
+        if dv != V:
+            # draft id i stands for target id i * (V // dv)
+            sd["d2t"] = (torch.arange(dv) * (V // dv) - torch.arange(dv)).to(torch.int64)
+    sd[pre + "self_attn.q_proj.weight"] = w(nh * D, qkv_in)
+    sd[pre + "self_attn.k_proj.weight"] = w(nkv * D, qkv_in)
+    sd[pre + "self_attn.v_proj.weight"] = w(nkv * D, qkv_in)
+    sd[pre + "self_attn.o_proj.weight"] = w(H, nh * D)
+    sd[pre + "mlp.gate_proj.weight"] = w(I, H)
+    sd[pre + "mlp.up_proj.weight"] = w(I, H)
+    sd[pre + "mlp.down_proj.weight"] = w(H, I)
+    sd[pre + "post_attention_layernorm.weight"] = torch.ones(H)
+    write_config_only(path, cfg)
+    save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(path, "model.safetensors"))
+    return path
+
+
+def write_tiny_mimo_checkpoint(path: str, seed: int = 0, num_mtp_layers: int = 1) -> str:
+    """A tiny MiMo-style checkpoint: Qwen2 decoder (biased q/k/v) plus `model.mtp_layers.*`."""
+    from safetensors.torch import save_file
+    cfg = dict(TINY_QWEN3, architectures=["MiMoForCausalLM"], model_type="mimo", tie_word_embeddings=False,
+               num_nextn_predict_layers=num_mtp_layers)
+    g = torch.Generator().manual_seed(seed + 100)
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    nh, nkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+
+    def w(*shape):
+        return torch.empty(*shape, dtype=torch.float32).normal_(0, 0.02, generator=g)
+
+    sd = {k: v for k, v in tiny_qwen3_state_dict(cfg, seed).items() if "q_norm" not in k and "k_norm" not in k}
+    prefixes = [f"model.layers.{i}." for i in range(cfg["num_hidden_layers"])] + \
+        [f"model.mtp_layers.{j}." for j in range(num_mtp_layers)]
+    for p in prefixes:
+        sd[p + "self_attn.q_proj.bias"] = w(nh * D)
+        sd[p + "self_attn.k_proj.bias"] = w(nkv * D)
+        sd[p + "self_attn.v_proj.bias"] = w(nkv * D)
+    for j in range(num_mtp_layers):
+        p = f"model.mtp_layers.{j}."
+        sd[p + "token_layernorm.weight"] = torch.ones(H)
+        sd[p + "hidden_layernorm.weight"] = torch.ones(H)
+        sd[p + "input_proj.weight"] = w(H, 2 * H)
+        sd[p + "input_layernorm.weight"] = torch.ones(H)
+        sd[p + "self_attn.q_proj.weight"] = w(nh * D, H)
+        sd[p + "self_attn.k_proj.weight"] = w(nkv * D, H)
+        sd[p + "self_attn.v_proj.weight"] = w(nkv * D, H)
+        sd[p + "self_attn.o_proj.weight"] = w(H, nh * D)
+        sd[p + "post_attention_layernorm.weight"] = torch.ones(H)
+        sd[p + "mlp.gate_proj.weight"] = w(I, H)
+        sd[p + "mlp.up_proj.weight"] = w(I, H)
+        sd[p + "mlp.down_proj.weight"] = w(H, I)
+        sd[p + "final_layernorm.weight"] = torch.ones(H)
+    write_config_only(path, cfg)
+    save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(path, "model.safetensors"))
+    return path
+
+
+def write_tiny_dflash_checkpoint(path: str, target_config: dict = TINY_QWEN3, seed: int = 5, block_size: int = 4,
+                                 target_layer_ids=(0, 1)) -> str:
+    """A random DFlash block drafter (one Qwen3-style layer, no embedding / head)."""
+    from safetensors.torch import save_file
+    cfg = dict(target_config, architectures=["DFlashDraftModel"], num_hidden_layers=1, tie_word_embeddings=False,
+               dflash_config=dict(target_layer_ids=list(target_layer_ids), block_size=block_size,
+                                  mask_token_id=target_config["vocab_size"] - 1))
+    sd = {k[len("model."):]: v for k, v in tiny_qwen3_state_dict(dict(cfg, tie_word_embeddings=True), seed).items()
+          if k.startswith("model.layers.") or k == "model.norm.weight"}
+    g = torch.Generator().manual_seed(seed)
+    H = cfg["hidden_size"]
+    sd["fc.weight"] = torch.empty(H, len(target_layer_ids) * H).normal_(0, 0.02, generator=g)
+    sd["hidden_norm.weight"] = torch.ones(H)
+    write_config_only(path, cfg)
+    save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(path, "model.safetensors"))
+    return path

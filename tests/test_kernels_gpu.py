@@ -206,3 +206,58 @@ def test_fused_experts(native, T, E, E_local, e0, k, H, I):
     native.check_status()
     exp = ref.moe_forward(x.float(), w13.float(), w2.float(), tw, ids, e0)
     _close(got, exp, 3e-2, 3e-2)
+
+
+def test_argmax_unaligned_rows(native):
+    logits = torch.randn(7, 1003, device="cuda").to(torch.bfloat16)     # odd rows start off a 16-byte boundary
+    assert torch.equal(native.argmax(logits).long(), torch.argmax(logits.float(), dim=-1))
+    wide = torch.randn(5, 4099, device="cuda").to(torch.bfloat16)[:, :4096]   # aligned base, strided rows
+    assert torch.equal(native.argmax(wide).long(), torch.argmax(wide.float(), dim=-1))
+
+
+@pytest.mark.parametrize("P", [1, 16, 64])
+@pytest.mark.parametrize("nq,tail", [(6, 6), (3, 9), (70, 70)])
+def test_paged_extend_tail_mask(native, P, nq, tail):
+    """Token-tree verification: the last `tail` keys follow an explicit mask, the prefix is visible."""
+    Hq, Hkv, D = 8, 2, 128
+    prefix = [0 + (tail - nq), 37 + (tail - nq), 128 + (tail - nq), 301 + (tail - nq)]
+    B = len(prefix)
+    seqs = [p + nq for p in prefix]
+    cache, pt, rows = _attn_setup(B, seqs, P, Hkv, D, seed=40)
+    q = _bf16(B * nq, Hq, D, seed=41)
+    sl = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    pl = torch.tensor(prefix, dtype=torch.int32, device="cuda")
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda") * nq
+    g = torch.Generator(device="cuda").manual_seed(42)
+    mask = torch.rand(B, nq, tail, device="cuda", generator=g) < 0.5
+    mask[:, :, 0] = True        # every row sees at least one tail key (sequence 0 may have no prefix)
+    scale = D ** -0.5
+    got = native.paged_attention(q, cache, pt, rows, sl, P, scale, cu, pl, tail_mask=mask)
+    torch.cuda.synchronize()
+    native.check_status()
+    want = ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, cu, pl, custom_mask=mask)
+    _close(got, want, 2e-2, 2e-2)
+
+
+def test_speculative_tree_kernels(native):
+    from sglang_jax_b200.speculative import eagle_util
+    g = torch.Generator().manual_seed(7)
+    B, n, depth = 33, 12, 5
+    # random trees: parent index < child index
+    parent = torch.stack([torch.cat([torch.tensor([-1]), torch.stack([torch.randint(0, i, (1,), generator=g)[0]
+                                                                      for i in range(1, n)])]) for _ in range(B)])
+    tokens = torch.randint(0, 6, (B, n), generator=g)
+    target = torch.randint(0, 6, (B, n), generator=g)
+    acc_c, path_c, bonus_c = eagle_util.verify_tree_greedy(tokens, parent, target, depth)
+    acc_g, path_g, bonus_g = native.verify_tree_greedy(tokens.cuda(), parent.cuda(), target.cuda(), depth)
+    assert torch.equal(acc_g.cpu(), acc_c) and torch.equal(bonus_g.cpu(), bonus_c)
+    assert torch.equal(path_g.cpu(), path_c)
+    mask, dep = native.tree_mask(parent.cuda())
+    for b in range(B):
+        for i in range(n):
+            anc, c = {i}, int(parent[b, i])
+            while c >= 0:
+                anc.add(c)
+                c = int(parent[b, c])
+            assert set(torch.nonzero(mask[b, i]).flatten().tolist()) == anc
+            assert int(dep[b, i]) == len(anc) - 1
