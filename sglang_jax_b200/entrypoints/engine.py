@@ -131,6 +131,16 @@ class Engine(EngineBase):
     def flush_cache(self):
         return self.loop.run_until_complete(self.tokenizer_manager.flush_cache())
 
+    def load_lora_adapter(self, lora_name: str, lora_path: str, pinned: bool = False):
+        from ..managers.io_struct import LoadLoRAAdapterReqInput
+        return self.loop.run_until_complete(self.tokenizer_manager.load_lora_adapter(
+            LoadLoRAAdapterReqInput(lora_name=lora_name, lora_path=lora_path, pinned=pinned)))
+
+    def unload_lora_adapter(self, lora_name: str):
+        from ..managers.io_struct import UnloadLoRAAdapterReqInput
+        return self.loop.run_until_complete(self.tokenizer_manager.unload_lora_adapter(
+            UnloadLoRAAdapterReqInput(lora_name=lora_name)))
+
     def pause_generation(self, mode: str = "abort"):
         return self.loop.run_until_complete(self.tokenizer_manager.pause_generation(PauseGenerationReqInput(mode=mode)))
 
@@ -263,10 +273,14 @@ def _launch_threads(engine: Engine, server_args: ServerArgs):
                 sched.event_loop_overlap(engine._stop)
             else:
                 sched.event_loop_normal(engine._stop)
-        except BaseException as e:   # surface init failures to the caller
+        except BaseException as e:   # surface init failures to the caller, later ones to the requests
+            from ..managers.io_struct import SchedulerFailure
             err.append(e)
+            was_ready = ready.is_set()
             ready.set()
             logger.exception("scheduler thread died")
+            if was_ready:
+                to_tok.put(SchedulerFailure(f"{type(e).__name__}: {e}"))
 
     t = threading.Thread(target=sched_main, daemon=True, name="scheduler")
     t.start()

@@ -22,7 +22,8 @@ from fastapi.responses import JSONResponse, Response, StreamingResponse
 
 from ..function_call.function_call_parser import FunctionCallParser
 from ..managers.io_struct import (CloseSessionReqInput, ConfigureLoggingReq, ContinueGenerationReqInput,
-                                  EmbeddingReqInput, GenerateReqInput, OpenSessionReqInput, ParseFunctionCallReq,
+                                  EmbeddingReqInput, GenerateReqInput, LoadLoRAAdapterReqInput, OpenSessionReqInput,
+                                  ParseFunctionCallReq, UnloadLoRAAdapterReqInput,
                                   PauseGenerationReqInput, ProfileReqInput, SeparateReasoningReqInput,
                                   SetInternalStateReq, StartTraceReqInput)
 from ..managers.template_manager import TemplateManager
@@ -195,6 +196,18 @@ async def flush_cache():
     return Response(content="Cache flushed.\nPlease check backend logs for more details. "
                             "(When there are running or waiting requests, the operation will not be performed.)\n",
                     status_code=200 if ret.success else 400)
+
+
+@app.post("/load_lora_adapter")
+async def load_lora_adapter(obj: LoadLoRAAdapterReqInput):
+    res = await _global_state.tokenizer_manager.load_lora_adapter(obj)
+    return JSONResponse(dataclasses.asdict(res), status_code=200 if res.success else 400)
+
+
+@app.post("/unload_lora_adapter")
+async def unload_lora_adapter(obj: UnloadLoRAAdapterReqInput):
+    res = await _global_state.tokenizer_manager.unload_lora_adapter(obj)
+    return JSONResponse(dataclasses.asdict(res), status_code=200 if res.success else 400)
 
 
 @app.api_route("/start_profile", methods=["GET", "POST"])

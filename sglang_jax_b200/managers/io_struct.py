@@ -537,13 +537,22 @@ class TraceStatusReqInput(RpcReqInput):
 class LoadLoRAAdapterReqInput(RpcReqInput):
     lora_name: str = ""
     lora_path: str = ""
+    pinned: bool = False
+    lora_id: str | None = None
 
 
 @dataclass
 class UnloadLoRAAdapterReqInput(RpcReqInput):
     lora_name: str = ""
+    lora_id: str | None = None
 
 
 @dataclass
 class LoRAUpdateOutput(RpcReqOutput):
     loaded_adapters: dict[str, str] = field(default_factory=dict)
+
+
+@dataclass
+class SchedulerFailure:
+    """Sent to the front end when the scheduler loop dies: every pending request fails."""
+    message: str = ""

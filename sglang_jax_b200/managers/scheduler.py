@@ -34,7 +34,8 @@ from ..mem_cache.radix_cache import RadixCache
 from ..sampling.sampling_params import SamplingParams
 from .io_struct import (AbortReq, BatchTokenIDOut, CloseSessionReqInput, CloseSessionReqOutput,
                         ConfigureLoggingReq, ConfigureLoggingReqOutput, ContinueGenerationReqInput,
-                        FlushCacheReqInput, FlushCacheReqOutput, GetInternalStateReq,
+                        FlushCacheReqInput, FlushCacheReqOutput, GetInternalStateReq, LoadLoRAAdapterReqInput,
+                        LoRAUpdateOutput, UnloadLoRAAdapterReqInput,
                         GetInternalStateReqOutput, GetLoadReqInput, GetLoadReqOutput, HealthCheckOutput,
                         OpenSessionReqInput, OpenSessionReqOutput, PauseGenerationReqInput, ProfileReq,
                         ReleaseMemoryOccupationReqInput, ReleaseMemoryOccupationReqOutput,
@@ -164,6 +165,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             SetInternalStateReq: self.set_internal_state,
             GetLoadReqInput: lambda r: GetLoadReqOutput(**self.get_load()),
             ProfileReq: self.profile,
+            LoadLoRAAdapterReqInput: self.load_lora_adapter,
+            UnloadLoRAAdapterReqInput: self.unload_lora_adapter,
             OpenSessionReqInput: self.open_session,
             CloseSessionReqInput: self.close_session,
             ConfigureLoggingReq: self.configure_logging,
@@ -477,6 +480,13 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             self.chunked_req.init_next_round_input(None)
             self.chunked_req = adder.add_chunked_req(self.chunked_req)
 
+        # adapters of one batch must fit the LoRA slots (reference `scheduler.py` lora_set check)
+        lora_set = None
+        if self.server_args.enable_lora:
+            lora_set = {r.lora_id for r in self.running_batch.reqs if r.lora_id is not None}
+            if self.chunked_req is not None and self.chunked_req.lora_id is not None:
+                lora_set.add(self.chunked_req.lora_id)
+
         for req in list(self.waiting_queue):
             if running_bs + len(adder.can_run_list) >= self.max_running_requests:
                 self.running_batch.batch_is_full = True
@@ -486,8 +496,13 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                 break
             if adder.new_chunked_req is not None:
                 break   # one request is chunked per step; the rest of its budget is spent
+            if lora_set is not None and req.lora_id is not None and req.lora_id not in lora_set:
+                if len(lora_set) >= self.server_args.max_loras_per_batch:
+                    continue      # would exceed the adapters one batch can hold; try a later request
             req.init_next_round_input(self.tree_cache)
             res = adder.add_one_req(req)
+            if lora_set is not None and res == AddReqResult.CONTINUE and req.lora_id is not None:
+                lora_set.add(req.lora_id)
             if res != AddReqResult.CONTINUE:
                 if res == AddReqResult.NO_TOKEN:
                     self.running_batch.batch_is_full = True
@@ -692,6 +707,15 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
     def continue_generation(self, recv: ContinueGenerationReqInput):
         self._paused = False
         return None
+
+    # ------------------------------------------------------------------ LoRA
+    def load_lora_adapter(self, recv: LoadLoRAAdapterReqInput) -> LoRAUpdateOutput:
+        ok, msg = self.tp_worker.load_lora_adapter(recv)
+        return LoRAUpdateOutput(request_id=recv.request_id, success=ok, error_msg=msg)
+
+    def unload_lora_adapter(self, recv: UnloadLoRAAdapterReqInput) -> LoRAUpdateOutput:
+        ok, msg = self.tp_worker.unload_lora_adapter(recv)
+        return LoRAUpdateOutput(request_id=recv.request_id, success=ok, error_msg=msg)
 
     def flush_cache_wrapped(self, recv: FlushCacheReqInput):
         ok, n = self.flush_cache()

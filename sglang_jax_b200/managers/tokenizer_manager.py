@@ -24,7 +24,8 @@ from typing import Any, AsyncGenerator
 
 from ..sampling.sampling_params import SamplingParams
 from .io_struct import (AbortReq, BatchEmbeddingOut, BatchStrOut, CloseSessionReqInput, ConfigureLoggingReq,
-                        ContinueGenerationReqInput, EmbeddingReqInput, FlushCacheReqInput, FlushCacheReqOutput,
+                        ContinueGenerationReqInput, EmbeddingReqInput, FlushCacheReqInput, FlushCacheReqOutput, LoadLoRAAdapterReqInput,
+                        LoRAUpdateOutput, SchedulerFailure, UnloadLoRAAdapterReqInput,
                         GenerateReqInput, GetInternalStateReq, GetInternalStateReqOutput, GetLoadReqInput,
                         GetLoadReqOutput, OpenSessionReqInput, PauseGenerationReqInput, ProfileReq,
                         ProfileReqOutput, ProfileReqType, SetInternalStateReq, SetInternalStateReqOutput,
@@ -40,6 +41,7 @@ class ReqState:
     event: asyncio.Event
     obj: Any
     created_time: float
+    lora_id: Any = None
     first_token_time: float = 0.0
     finished_time: float = 0.0
     last_output_offset: int = 0
@@ -126,7 +128,12 @@ class TokenizerManager:
         self.is_pause_cond: asyncio.Condition | None = None
         self.session_futures: dict = {}
         self.lora_registry = None
+        if server_args.enable_lora:
+            from ..lora.lora_registry import LoRARegistry
+            self.lora_registry = LoRARegistry(server_args.lora_paths)
+        self.lora_update_lock: asyncio.Lock | None = None
         self.cache_miss_count = 0
+        self.fatal_error: str | None = None
 
         s = self.send_to_scheduler
         self.flush_cache_communicator = _Communicator(s)
@@ -136,12 +143,14 @@ class TokenizerManager:
         self.get_load_communicator = _Communicator(s)
         self.session_communicator = _Communicator(s)
         self.generic_communicator = _Communicator(s)
+        self.lora_communicator = _Communicator(s)
         self._result_dispatch = {
             FlushCacheReqOutput: self.flush_cache_communicator.handle_recv,
             GetInternalStateReqOutput: self.get_internal_state_communicator.handle_recv,
             SetInternalStateReqOutput: self.set_internal_state_communicator.handle_recv,
             ProfileReqOutput: self.profile_communicator.handle_recv,
             GetLoadReqOutput: self.get_load_communicator.handle_recv,
+            LoRAUpdateOutput: self.lora_communicator.handle_recv,
         }
         self.metrics_collector = None
         if self.enable_metrics:
@@ -217,6 +226,7 @@ class TokenizerManager:
 
     def _send_one_request(self, obj, tokenized, created) -> ReqState:
         state = ReqState([], False, asyncio.Event(), obj, created)
+        state.lora_id = getattr(tokenized, "lora_id", None)
         self.rid_to_state[obj.rid] = state
         self.send_to_scheduler.send_pyobj(tokenized)
         return state
@@ -230,6 +240,9 @@ class TokenizerManager:
                     self.abort_request(obj.rid)
                     raise ValueError(f"Request is disconnected from the client side. Abort request rid={obj.rid}")
                 continue
+            if self.fatal_error is not None and not state.out_list:
+                self.rid_to_state.pop(obj.rid, None)
+                raise RuntimeError(f"scheduler failure: {self.fatal_error}")
             out = state.out_list[-1]
             state.out_list = []
             if state.finished:
@@ -324,6 +337,48 @@ class TokenizerManager:
             self.is_pause = False
             self.send_to_scheduler.send_pyobj(obj)
             self.is_pause_cond.notify_all()
+
+    # ------------------------------------------------------------------ LoRA (reference
+    # `tokenizer_manager.py` load/unload_lora_adapter)
+    async def load_lora_adapter(self, obj: LoadLoRAAdapterReqInput) -> LoRAUpdateOutput:
+        self.auto_create_handle_loop()
+        if self.lora_registry is None:
+            return LoRAUpdateOutput(success=False, error_msg="LoRA is not enabled (--enable-lora)")
+        if self.lora_update_lock is None:
+            self.lora_update_lock = asyncio.Lock()
+        from ..lora.lora_registry import LoRARef
+        async with self.lora_update_lock:
+            if self.lora_registry.get(obj.lora_name) is not None:
+                return LoRAUpdateOutput(success=False, error_msg=f"LoRA adapter {obj.lora_name} is already loaded",
+                                        loaded_adapters=self._loaded_loras())
+            ref = LoRARef(lora_name=obj.lora_name, lora_path=obj.lora_path)
+            obj.lora_id = ref.lora_id
+            res = (await self.lora_communicator(obj))[0]
+            if res.success:
+                self.lora_registry.register(ref)
+            res.loaded_adapters = self._loaded_loras()
+            return res
+
+    async def unload_lora_adapter(self, obj: UnloadLoRAAdapterReqInput) -> LoRAUpdateOutput:
+        self.auto_create_handle_loop()
+        if self.lora_registry is None:
+            return LoRAUpdateOutput(success=False, error_msg="LoRA is not enabled (--enable-lora)")
+        if self.lora_update_lock is None:
+            self.lora_update_lock = asyncio.Lock()
+        async with self.lora_update_lock:
+            try:
+                lora_id = self.lora_registry.unregister(obj.lora_name)
+            except ValueError as e:
+                return LoRAUpdateOutput(success=False, error_msg=str(e), loaded_adapters=self._loaded_loras())
+            # new requests can no longer name the adapter; wait for the running ones
+            await self.lora_registry.wait_for_unload(lora_id)
+            obj.lora_id = lora_id
+            res = (await self.lora_communicator(obj))[0]
+            res.loaded_adapters = self._loaded_loras()
+            return res
+
+    def _loaded_loras(self) -> dict:
+        return {n: r.lora_path for n, r in self.lora_registry.all().items()}
 
     async def get_internal_state(self) -> list[dict]:
         self.auto_create_handle_loop()
@@ -439,6 +494,11 @@ class TokenizerManager:
 
     def _dispatch_output(self, obj):
         self.last_receive_tstamp = time.time()
+        if isinstance(obj, SchedulerFailure):
+            self.fatal_error = obj.message or "the scheduler died"
+            for st in list(self.rid_to_state.values()):
+                st.event.set()
+            return
         if isinstance(obj, (BatchStrOut, BatchEmbeddingOut)):
             self._handle_batch_output(obj)
             return
@@ -489,6 +549,8 @@ class TokenizerManager:
                 state.finished_time = time.time()
                 meta["e2e_latency"] = state.finished_time - state.created_time
                 del self.rid_to_state[rid]
+                if self.lora_registry is not None and getattr(state, "lora_id", None) is not None:
+                    self.lora_registry.release(state.lora_id)
                 if self.crash_dump_folder:
                     self.crash_dump_request_list.append((state.obj, out, state.created_time, time.time()))
                     if len(self.crash_dump_request_list) > 1000:

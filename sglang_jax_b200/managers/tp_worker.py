@@ -121,6 +121,23 @@ class ModelWorker:
         out, _, _ = self.model_runner.forward(batch, skip_sample=True)
         return out.hidden_states
 
+    def load_lora_adapter(self, recv) -> tuple[bool, str]:
+        from ..lora.lora_registry import LoRARef
+        lm = self.model_runner.lora_manager
+        if lm is None:
+            return False, "LoRA is not enabled (--enable-lora)"
+        if self.broadcast_batches:
+            ps.broadcast_object(_Control("load_lora", recv), src=0, group=ps.get_state().tp)
+        return lm.load_adapter(LoRARef(lora_id=recv.lora_id, lora_name=recv.lora_name, lora_path=recv.lora_path))
+
+    def unload_lora_adapter(self, recv) -> tuple[bool, str]:
+        lm = self.model_runner.lora_manager
+        if lm is None:
+            return False, "LoRA is not enabled (--enable-lora)"
+        if self.broadcast_batches:
+            ps.broadcast_object(_Control("unload_lora", recv), src=0, group=ps.get_state().tp)
+        return lm.unload_adapter(recv.lora_id)
+
     def send_control(self, kind: str, payload=None):
         if self.broadcast_batches:
             ps.broadcast_object(_Control(kind, payload), src=0, group=ps.get_state().tp)
@@ -194,6 +211,13 @@ def run_tp_follower(server_args, worker: ModelWorker | None = None):
                 worker.marks[msg.payload] = _record_event(worker.device)
             elif msg.kind == "report":
                 report_elapsed_max(worker, *msg.payload)
+            elif msg.kind == "load_lora":
+                from ..lora.lora_registry import LoRARef
+                r = msg.payload
+                worker.model_runner.lora_manager.load_adapter(
+                    LoRARef(lora_id=r.lora_id, lora_name=r.lora_name, lora_path=r.lora_path))
+            elif msg.kind == "unload_lora":
+                worker.model_runner.lora_manager.unload_adapter(msg.payload.lora_id)
             continue
         worker.model_runner.forward(msg)
     return worker

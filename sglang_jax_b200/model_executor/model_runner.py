@@ -65,6 +65,10 @@ class ModelRunner:
         self.future_token_ids_map = torch.zeros(self.req_to_token_pool.size + 2, dtype=torch.int32,
                                                 device=self.device)
         self.cuda_graph_runner = None
+        self.lora_manager = None
+        if server_args.enable_lora and not is_draft_worker:
+            from ..lora.lora_manager import LoRAManager
+            self.lora_manager = LoRAManager(self.model, server_args, self.dtype, self.device)
         self._init_fused_comm()
         if self.device.type == "cuda" and not server_args.disable_cuda_graph and not is_draft_worker:
             from .cuda_graph_runner import CudaGraphRunner
@@ -212,7 +216,13 @@ class ModelRunner:
                 and si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None
                 and batch.capture_hidden_mode == 0 and len(batch.req_pool_indices) <= 1024):
             fb.extras["skip_logits_gather"] = True     # greedy: reduce (max, index) pairs, not logits
-        out = self.model(fb.input_ids, fb)
+        if self.lora_manager is not None:
+            from ..lora.context_manager import lora_batch
+            per_req = batch.extend_seq_lens if batch.forward_mode.is_extend() else np.ones(len(batch.req_pool_indices), np.int64)
+            with lora_batch(self.lora_manager.prepare_batch(batch.lora_ids, per_req)):
+                out = self.model(fb.input_ids, fb)
+        else:
+            out = self.model(fb.input_ids, fb)
         if skip_sample:
             return out, None, fb
         if "vocab_shard" in out.extras:

@@ -64,6 +64,9 @@ def lib():
     L.sglb_verify_tree_greedy.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                           c_int, c_void_p]
     L.sglb_tree_mask.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    L.sglb_lora_shrink.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    L.sglb_lora_expand.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_void_p]
     L.sglb_read_status.argtypes = [c_void_p]
     _LIB = L
     LOADED = True
@@ -244,6 +247,23 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
                                    _stream()), "paged_extend")
     return out
+
+
+def lora_bgmv(x, y, a_buf, b_bufs, out_offsets, token_slots, scalings):
+    """`y[:, off_j:off_j+N_j] += scale[slot] * B_j[slot] (A[slot] x)[j*r:(j+1)*r]` per token, in place.
+    `a_buf [slots, stack*r, K]`, `b_bufs[j] [slots, N_j, r]`, `token_slots [T]` int32 (-1 = skip)."""
+    T, K = x.shape
+    R = a_buf.shape[1]
+    r = R // len(b_bufs)
+    x = x.contiguous()
+    assert y.stride(-1) == 1
+    h = torch.empty((T, R), dtype=torch.float32, device=x.device)
+    L = lib()
+    _check(L.sglb_lora_shrink(_p(h), _p(x), _p(a_buf), _p(token_slots), T, R, K, _stream()), "lora_shrink")
+    for j, (b, off) in enumerate(zip(b_bufs, out_offsets)):
+        _check(L.sglb_lora_expand(_p(y), _p(h), _p(b), _p(token_slots), _p(scalings), T, b.shape[1], r, R, j * r,
+                                  y.stride(0), int(off), _stream()), "lora_expand")
+    return y
 
 
 def verify_tree_greedy(tokens, parent, target_ids, max_depth: int):

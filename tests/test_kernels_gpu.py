@@ -261,3 +261,34 @@ def test_speculative_tree_kernels(native):
                 c = int(parent[b, c])
             assert set(torch.nonzero(mask[b, i]).flatten().tolist()) == anc
             assert int(dep[b, i]) == len(anc) - 1
+
+
+@pytest.mark.parametrize("T,K,outs,r", [(1, 1024, [512], 8), (37, 5120, [1024, 256, 256], 16), (300, 2048, [2048, 2048], 64)])
+def test_lora_bgmv(native, T, K, outs, r):
+    from sglang_jax_b200.lora.backend.base_backend import LoRABatchInfo
+    from sglang_jax_b200.lora.backend.bgmv_backend import BgmvBackend
+    slots = 4
+    stack = len(outs)
+    a = _bf16(slots, stack * r, K, scale=0.05, seed=50)
+    bs = [_bf16(slots, n, r, scale=0.05, seed=51 + j) for j, n in enumerate(outs)]
+    offs = [sum(outs[:j]) for j in range(stack)]
+    x = _bf16(T, K, seed=60)
+    y0 = _bf16(T, sum(outs), seed=61)
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(-1, slots, (T,), generator=g, dtype=torch.int32)
+    scal = torch.tensor([0.5, 2.0, 1.0, 0.25], device="cuda")
+    got = native.lora_bgmv(x, y0.clone(), a, bs, offs, tok.cuda(), scal)
+    torch.cuda.synchronize()
+    native.check_status()
+    order = torch.argsort(tok, stable=True)
+    st = tok[order]
+    first = int((st < 0).sum())
+    seg_slots, seg_bounds, i = [], [], first
+    while i < T:
+        j = i + int((st[i:] == st[i]).sum())
+        seg_slots.append(int(st[i]))
+        seg_bounds.append((i - first, j - first))
+        i = j
+    info = LoRABatchInfo(tok.cuda(), scal, None, True, order[first:].cuda(), seg_slots, seg_bounds)
+    want = BgmvBackend._segments(x.float(), y0.float().clone(), a.float(), [b.float() for b in bs], offs, info)
+    _close(got, want, 2e-2, 2e-2)
