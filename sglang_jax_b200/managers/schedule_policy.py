@@ -11,6 +11,8 @@ multiple and continued next step ("chunked prefill").
 
 from __future__ import annotations
 
+import numpy as np
+
 import random
 from collections import defaultdict
 from enum import Enum, auto
@@ -249,6 +251,15 @@ class PrefillAdder:
         if req.sampling_params.ignore_eos and cache_disabled:
             return self.add_one_req_ignore_eos(req)
         clip = global_config.clip_max_new_tokens_estimation
+        if req.host_hit_length > 0 and hasattr(self.tree_cache, "init_load_back"):
+            # part of the prefix lives on the host tier: give it device slots and start the copy
+            new_indices, new_last = self.tree_cache.init_load_back(req.last_host_node, req.host_hit_length)
+            req.host_hit_length = 0
+            if len(new_indices):
+                req.prefix_indices = np.concatenate([req.prefix_indices, new_indices]).astype(np.int32)
+                req.last_node = new_last
+                req.last_matched_prefix_len = len(req.prefix_indices)
+                req.extend_input_len = len(req.fill_ids) - len(req.prefix_indices)
         total_tokens = req.extend_input_len + min(req.sampling_params.max_new_tokens, clip)
         if total_tokens >= self.rem_total_tokens:
             return AddReqResult.NO_TOKEN

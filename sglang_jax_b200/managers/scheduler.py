@@ -242,6 +242,10 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                                          enable_kv_cache_events=bool(sa.kv_events_config),
                                          is_eagle=self.spec_algorithm in ("EAGLE", "EAGLE3"))
 
+    @property
+    def _hicache(self) -> bool:
+        return hasattr(self.tree_cache, "check_hicache_events")
+
     def _empty_batch(self) -> ScheduleBatch:
         return ScheduleBatch([], self.req_to_token_pool, self.token_to_kv_pool_allocator, self.tree_cache,
                              self.vocab_size, self.enable_overlap, self.page_size, self.spec_algorithm)
@@ -257,6 +261,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         if self._paused:
             time.sleep(0.001)
             return False
+        if self._hicache:
+            self.tree_cache.check_hicache_events()
         batch = self.get_next_batch_to_run()
         self.cur_batch = batch
         if batch is None:
@@ -281,6 +287,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             self._drain_results()
             time.sleep(0.001)
             return False
+        if self._hicache:
+            self.tree_cache.check_hicache_events()
         batch = self.get_next_batch_to_run()
         self.cur_batch = batch
         if batch is not None:
@@ -569,6 +577,9 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
     # ------------------------------------------------------------------ run
     def run_batch(self, batch: ScheduleBatch):
         self.forward_ct += 1
+        if self._hicache:
+            # pages being loaded back from the host tier must land before this batch reads them
+            self.tree_cache.ready_to_load_host_cache()
         self._profile_batch_predicate(batch)
         if self.is_embedding:
             mwb = batch.get_model_worker_batch()

@@ -67,6 +67,8 @@ def lib():
     L.sglb_lora_shrink.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     L.sglb_lora_expand.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_int, c_void_p]
+    L.sglb_kv_page_copy.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong,
+                                    c_longlong, c_void_p]
     L.sglb_read_status.argtypes = [c_void_p]
     _LIB = L
     LOADED = True
@@ -264,6 +266,20 @@ def lora_bgmv(x, y, a_buf, b_bufs, out_offsets, token_slots, scalings):
         _check(L.sglb_lora_expand(_p(y), _p(h), _p(b), _p(token_slots), _p(scalings), T, b.shape[1], r, R, j * r,
                                   y.stride(0), int(off), _stream()), "lora_expand")
     return y
+
+
+def kv_page_copy(dst: torch.Tensor, src: torch.Tensor, dst_pages: torch.Tensor, src_pages: torch.Tensor):
+    """`dst[dst_pages[i]] = src[src_pages[i]]` for 2-D page tables `[pages, page_elems]`; either tensor may
+    be pinned host memory.  Index tensors are int64 on the device.  Asynchronous on the current stream."""
+    n = dst_pages.numel()
+    if n == 0:
+        return
+    assert dst.dim() == 2 and src.dim() == 2 and dst.shape[1] == src.shape[1] and dst.dtype == src.dtype
+    assert dst.stride(1) == 1 and src.stride(1) == 1
+    es = dst.element_size()
+    _check(lib().sglb_kv_page_copy(dst.data_ptr(), src.data_ptr(), _p(dst_pages), _p(src_pages), n,
+                                   dst.shape[1] * es, dst.stride(0) * es, src.stride(0) * es, _stream()),
+           "kv_page_copy")
 
 
 def verify_tree_greedy(tokens, parent, target_ids, max_depth: int):

@@ -292,3 +292,29 @@ def test_lora_bgmv(native, T, K, outs, r):
     info = LoRABatchInfo(tok.cuda(), scal, None, True, order[first:].cuda(), seg_slots, seg_bounds)
     want = BgmvBackend._segments(x.float(), y0.float().clone(), a.float(), [b.float() for b in bs], offs, info)
     _close(got, want, 2e-2, 2e-2)
+
+
+def test_kv_page_copy_device_host_roundtrip(native):
+    """The page-copy kernel writes pinned host memory directly and reads it back (HiCache / PD staging)."""
+    from sglang_jax_b200.mem_cache.host_kv_pool import LRUHostKVPool
+    from sglang_jax_b200.mem_cache.memory_pool import MHATokenToKVPool
+    pool = MHATokenToKVPool(64 * 16, 16, torch.bfloat16, 2, 128, 3, "cuda")
+    for i, b in enumerate(pool.kv_buffer):
+        b.copy_(_bf16(*b.shape, seed=70 + i))
+    ref_bufs = [b.clone() for b in pool.kv_buffer]
+    host = LRUHostKVPool(pool, 32)
+    dev_pages = torch.tensor([3, 17, 40, 5, 64]).numpy()
+    hp = host.alloc(5)
+    host.backup_from_device(dev_pages, hp)
+    torch.cuda.synchronize()
+    for layer, b in enumerate(ref_bufs):
+        assert torch.equal(host.host_views[layer][torch.as_tensor(hp)], b.view(b.shape[0], -1)[dev_pages].cpu())
+    for b in pool.kv_buffer:
+        b.zero_()
+    new_pages = torch.tensor([9, 10, 11, 12, 13]).numpy()
+    host.load_to_device(hp, new_pages)
+    torch.cuda.synchronize()
+    native.check_status()
+    for layer, b in enumerate(ref_bufs):
+        assert torch.equal(pool.kv_buffer[layer][new_pages], b[dev_pages])
+        assert pool.kv_buffer[layer][20].abs().sum() == 0
