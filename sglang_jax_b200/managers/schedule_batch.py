@@ -149,6 +149,7 @@ class Req:
         self.extend_input_len = 0
         self.last_node: Any = None
         self.last_host_node: Any = None
+        self.swa_evicted_seqlen = 0          # SWA slots before this position were already released
         self.host_hit_length = 0
         self.cached_tokens = 0
         self.already_computed = 0
@@ -321,6 +322,7 @@ class Req:
         self.already_computed = 0
         self.kv_committed_len = 0
         self.kv_allocated_len = 0
+        self.swa_evicted_seqlen = 0
         self.input_token_logprobs_val = None if not self.input_logprob_sent else self.input_token_logprobs_val
 
     def offload_kv_cache(self, *a, **k):  # hook used by HiCache / PD
@@ -492,9 +494,15 @@ class ScheduleBatch:
         alloc = self.token_to_kv_pool_allocator
         out = fn()
         if out is None and self.tree_cache is not None:
-            self.tree_cache.evict(need_tokens, dp_rank=self.dp_rank)
+            self._cache_evict(need_tokens)
             out = fn()
         return out
+
+    def _cache_evict(self, need_tokens: int):
+        if hasattr(self.tree_cache, "swa_evictable_size"):
+            self.tree_cache.evict(need_tokens, need_tokens)      # (full, sliding-window) budgets
+        else:
+            self.tree_cache.evict(need_tokens, dp_rank=self.dp_rank)
 
     # ------------------------------------------------------------------ extend
     def prepare_for_extend(self):
@@ -600,7 +608,7 @@ class ScheduleBatch:
         if alloc.available_size(dp_rank=self.dp_rank) >= need:
             return True
         if self.tree_cache is not None:
-            self.tree_cache.evict(need, dp_rank=self.dp_rank)
+            self._cache_evict(need)
         return alloc.available_size(dp_rank=self.dp_rank) >= need
 
     def retract_decode(self, server_args=None):
@@ -622,7 +630,7 @@ class ScheduleBatch:
             if avail >= need:
                 return True
             if self.tree_cache is not None:
-                self.tree_cache.evict(need - avail, dp_rank=self.dp_rank)
+                self._cache_evict(need - avail)
             return alloc.available_size(dp_rank=self.dp_rank) >= need
 
         first = True
@@ -693,6 +701,10 @@ class ScheduleBatch:
             self.input_ids = np.asarray([r.output_ids[-1] if r.output_ids else r.origin_input_ids[-1]
                                          for r in reqs], dtype=np.int32)
         self.output_ids = None
+        if hasattr(self.tree_cache, "evict_req_swa"):
+            for r in reqs:
+                if r.kv_committed_len % max(self.tree_cache.sliding_window_size // 2, 1) == 0:
+                    self.tree_cache.evict_req_swa(r, r.kv_committed_len)
         old_lens = np.asarray([r.kv_committed_len for r in reqs], dtype=np.int32)
         new_lens = old_lens + 1
         last_loc = np.asarray([pool.req_to_token[r.req_pool_idx, r.kv_committed_len - 1] for r in reqs],

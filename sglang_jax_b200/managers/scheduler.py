@@ -226,6 +226,15 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
     def init_memory_pool_and_cache(self):
         sa = self.server_args
         kv = self.token_to_kv_pool
+        if kv is not None and hasattr(kv, "swa_pool"):
+            # hybrid sliding-window model: dual allocator + window-aware prefix cache
+            from ..mem_cache.allocator import SWATokenToKVPoolAllocator
+            from ..mem_cache.swa_radix_cache import SWARadixCache
+            self.token_to_kv_pool_allocator = SWATokenToKVPoolAllocator(kv.size, kv.size_swa, self.page_size, kvcache=kv)
+            self.tree_cache = SWARadixCache(self.req_to_token_pool, self.token_to_kv_pool_allocator,
+                                            self.model_config.sliding_window or 4096, self.page_size,
+                                            disable=sa.disable_radix_cache)
+            return
         if self.page_size == 1:
             self.token_to_kv_pool_allocator = TokenToKVPoolAllocator(self.max_total_num_tokens, kvcache=kv)
         else:
@@ -822,6 +831,20 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         if self.chunked_req is not None or self.result_queue:
             return
         if not self.running_batch.is_empty() or self.waiting_queue and any(r.req_pool_idx is not None for r in self.waiting_queue):
+            return
+        if hasattr(self.tree_cache, "swa_evictable_size"):
+            # hybrid sliding-window pools: the invariant holds for each pool separately
+            al, tc = self.token_to_kv_pool_allocator, self.tree_cache
+            ps_ = self.page_size
+            for name, avail, ev, prot, size in (
+                    ("full", al.full_available_size(), tc.full_evictable_size(), tc.full_protected_size(), al.size),
+                    ("swa", al.swa_available_size(), tc.swa_evictable_size(), tc.swa_protected_size(), al.size_swa)):
+                if avail + ev + prot != size // ps_ * ps_ or prot != 0:
+                    msg = (f"KV cache pool leak detected ({name})! available={avail} evictable={ev} "
+                           f"protected={prot} expected={size // ps_ * ps_}")
+                    logger.error(msg)
+                    if os.environ.get("SGLANG_STRICT_MEMORY_CHECK", "1") == "1":
+                        raise RuntimeError(msg)
             return
         avail = self.token_to_kv_pool_allocator.available_size()
         evictable = self.tree_cache.evictable_size()

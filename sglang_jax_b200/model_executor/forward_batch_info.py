@@ -139,6 +139,15 @@ class ForwardBatch:
             num_decode_in_mixed=batch.num_decode_in_mixed,
             h2d_bytes=total * 4,
         )
+        pool = runner.token_to_kv_pool
+        if hasattr(pool, "swa_pool") and B:
+            # sliding-window layers live in their own (smaller) pool: translate the rows' pages
+            P = runner.page_size
+            pt = runner.req_to_token_pool.page_table
+            rows_l = fb.req_pool_indices.long()
+            swa_pt = torch.zeros_like(pt)
+            swa_pt[rows_l] = (pool.full_to_swa_index_mapping[(pt[rows_l].long() * P)] // P).to(pt.dtype)
+            fb.extras["swa_page_table"] = swa_pt
         if is_ext:
             fb.extend_prefix_lens, fb.extend_seq_lens, fb.cu_q_lens = v[5], v[6], v[7]
             fb.extend_prefix_lens_cpu = np.asarray(batch.extend_prefix_lens)

@@ -139,3 +139,34 @@ def test_deepseek_v3_mla_moe_matches_hf(tmp_path):
             p.data.normal_(0, 0.1)
     path = _save(str(tmp_path / "dsv3"), hf, cfg, "DeepseekV3ForCausalLM", "deepseek_v3")
     assert _generate(path, PROMPTS, n=8) == _hf_generate(hf, PROMPTS, n=8)
+
+
+@pytest.mark.parametrize("hybrid", [True, False])
+def test_gemma2_sliding_window_softcap_matches_hf(tmp_path, hybrid):
+    """Alternating sliding/global layers through the dual KV pool, the SWA allocator and the
+    window-aware radix cache (`hybrid`), or a single pool (`disable_hybrid_swa_memory`)."""
+    from transformers import Gemma2Config, Gemma2ForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=512,
+               tie_word_embeddings=True, max_position_embeddings=512, sliding_window=16, query_pre_attn_scalar=32,
+               attn_logit_softcapping=50.0, final_logit_softcapping=30.0, hidden_activation="gelu_pytorch_tanh")
+    hf = _init(Gemma2ForCausalLM(Gemma2Config(**cfg, attn_implementation="eager")))
+    path = _save(str(tmp_path / "gemma2"), hf, cfg, "Gemma2ForCausalLM", "gemma2")
+    prompts = [list(range(5, 60)), [9, 8, 7, 6, 5, 4, 3] * 5, [100, 200, 300]]
+    want = _hf_generate(hf, prompts, n=12)
+    got = _generate(path, prompts, n=12, disable_hybrid_swa_memory=not hybrid)
+    assert got == want
+    # a second pass reuses cached prefixes (window-aware matching) and must not change the result
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    ps.reset_state()
+    eng = Engine(model_path=path, device="cpu", dtype="float32", page_size=4, skip_tokenizer_init=True,
+                 max_total_tokens=1024, enable_single_process=True, disable_hybrid_swa_memory=not hybrid)
+    try:
+        sp = {"max_new_tokens": 12, "temperature": 0, "ignore_eos": True}
+        first = [o["output_ids"] for o in eng.generate(input_ids=prompts, sampling_params=sp)]
+        second = eng.generate(input_ids=prompts, sampling_params=sp)
+        assert first == want and [o["output_ids"] for o in second] == want
+        assert second[0]["meta_info"]["cached_tokens"] > 0
+    finally:
+        eng.shutdown()
