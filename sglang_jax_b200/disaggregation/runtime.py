@@ -1,0 +1,68 @@
+"""Wiring of the PD pieces into a scheduler and their shutdown (reference
+`python/sgl_jax/srt/disaggregation/runtime.py:18`, `:163`)."""
+
+from __future__ import annotations
+
+import logging
+
+from . import pd_auth
+from .bootstrap import BootstrapClient, HeartbeatDaemon
+from .common.core import CommonKVManager
+from .host_ip import get_host_ip
+from .transfer.zmq_transfer import ZmqTransferBackend
+
+logger = logging.getLogger(__name__)
+
+
+def kv_layout_of(scheduler) -> dict:
+    from ..mem_cache.host_kv_pool import _layer_views
+    views = _layer_views(scheduler.token_to_kv_pool)
+    return {"page_size": scheduler.page_size, "num_layers": len(views),
+            "page_bytes_per_layer": [int(v.shape[1] * v.element_size()) for v in views],
+            "dtype": str(views[0].dtype).replace("torch.", ""), "tp_size": scheduler.server_args.tp_size,
+            "model": scheduler.model_config.architectures[0] if scheduler.model_config is not None else ""}
+
+
+def pick_transfer_mode(server_args, on_gpu: bool) -> str:
+    """`cuda_ipc` (NVLink peer reads) when both engines share a node and run on GPUs, else `tcp`.
+    `--disaggregation-enable-d2h` forces the host-staged path."""
+    if not on_gpu or server_args.disaggregation_enable_d2h:
+        return "tcp"
+    return getattr(server_args, "disaggregation_transfer_backend", None) or "tcp"
+
+
+def build_kv_manager(scheduler, role: str, engine_id: str):
+    sa = scheduler.server_args
+    secret = pd_auth.resolve_secret(sa.disaggregation_shared_secret)
+    host = get_host_ip(sa.disaggregation_host_ip) if sa.disaggregation_host_ip else "127.0.0.1"
+    layout = kv_layout_of(scheduler)
+    pool = scheduler.token_to_kv_pool
+    from ..mem_cache.host_kv_pool import _layer_views
+    on_gpu = _layer_views(pool)[0].is_cuda
+    backend = ZmqTransferBackend(pool, host, sa.disaggregation_transfer_port if role == "prefill" else 0,
+                                 pick_transfer_mode(sa, on_gpu), secret, sa.disaggregation_pull_timeout_seconds)
+    transfer_addr = backend.start() if role == "prefill" else None
+    mgr = CommonKVManager(role, backend, sum(layout["page_bytes_per_layer"]), host,
+                          sa.disaggregation_side_channel_port if role == "prefill" else 0, secret,
+                          sa.disaggregation_channel_number, sa.disaggregation_pull_timeout_seconds,
+                          sa.disaggregation_ack_timeout_seconds, sa.disaggregation_orphan_reaper_interval_seconds)
+    hb = None
+    if role == "prefill":
+        info = dict(layout, engine_id=engine_id, tp_rank=0, transfer_addr=transfer_addr, ack_addr=mgr.ack_addr,
+                    http_url=f"http://{sa.host}:{sa.port}", transfer_mode=backend.mode)
+        client = BootstrapClient(sa.disaggregation_bootstrap_url, secret, sa.disaggregation_bootstrap_timeout_seconds)
+        hb = HeartbeatDaemon(client, info).start()
+        logger.info("PD prefill engine %s registered: transfer %s, ack %s (%s)", engine_id, transfer_addr,
+                    mgr.ack_addr, backend.mode)
+    return mgr, hb
+
+
+def shutdown_disaggregation(scheduler, drain_timeout: float = 10.0):
+    mgr = getattr(scheduler, "disagg_kv_manager", None)
+    hb = getattr(scheduler, "disagg_heartbeat", None)
+    if hb is not None:
+        hb.stop()          # stop advertising first, then let running transfers finish
+    if mgr is not None:
+        if not mgr.drain(drain_timeout):
+            logger.warning("PD shutdown: %d transfers still in flight", mgr.inflight())
+        mgr.shutdown()

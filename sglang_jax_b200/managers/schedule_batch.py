@@ -672,6 +672,19 @@ class ScheduleBatch:
             self.tree_cache.dec_lock_ref(r.last_node)
         pool.free(r.req_pool_idx)
 
+    def prepare_for_transferred_decode(self):
+        """Requests whose prompt KV arrived from a prefill engine: they join the decode batch
+        as if their prefill had just run here."""
+        self.forward_mode = ForwardMode.DECODE
+        self.req_pool_indices = np.asarray([r.req_pool_idx for r in self.reqs], dtype=np.int32)
+        self.seq_lens = np.asarray([r.kv_committed_len for r in self.reqs], dtype=np.int32)
+        self.output_ids = None
+        self.input_ids = None
+        self.out_cache_loc = None
+        self.prefix_lens, self.extend_lens, self.extend_num_tokens = [], [], 0
+        self.num_decode_in_mixed = 0
+        self.decoding_reqs = None
+
     def sampling_info_for_spec(self) -> ModelWorkerSamplingInfo:
         return ModelWorkerSamplingInfo.from_reqs(self.reqs, self.vocab_size)
 

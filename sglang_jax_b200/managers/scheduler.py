@@ -59,6 +59,10 @@ class SyncError(RuntimeError):
     """A mirror scheduler on another node disagreed with node 0."""
 
 
+from ..disaggregation.decode import SchedulerDisaggregationDecodeMixin  # noqa: E402
+from ..disaggregation.prefill import SchedulerDisaggregationPrefillMixin  # noqa: E402
+
+
 class SendDataError(RuntimeError):
     pass
 
@@ -67,7 +71,8 @@ class ReceiveDataError(RuntimeError):
     pass
 
 
-class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerProfilerMixin):
+class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerProfilerMixin,
+                SchedulerDisaggregationPrefillMixin, SchedulerDisaggregationDecodeMixin):
     def __init__(self, server_args, port_args=None, tp_worker=None, recv_queue: queue.Queue | None = None,
                  send_queue: queue.Queue | None = None, tokenizer=None, model_config=None):
         self.server_args = server_args
@@ -153,6 +158,15 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         self.parent_pid = os.getppid()
         if server_args.watchdog_timeout and server_args.watchdog_timeout > 0 and port_args is not None:
             threading.Thread(target=self.watchdog_thread, daemon=True).start()
+
+        self.disagg_mode = server_args.disaggregation_mode
+        if self.disagg_mode == "prefill":
+            self.init_disaggregation_prefill()
+        elif self.disagg_mode == "decode":
+            # transferred requests enter the decode batch with a host-known first token
+            self.enable_overlap = False
+            server_args.disable_overlap_schedule = True
+            self.init_disaggregation_decode()
 
         self._dispatch = {
             TokenizedGenerateReqInput: self.handle_generate_request,
@@ -272,6 +286,10 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             return False
         if self._hicache:
             self.tree_cache.check_hicache_events()
+        if self.disagg_mode == "prefill":
+            self.process_disagg_prefill_inflight()
+        elif self.disagg_mode == "decode":
+            self.process_disagg_decode_queues()
         batch = self.get_next_batch_to_run()
         self.cur_batch = batch
         if batch is None:
@@ -298,6 +316,10 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             return False
         if self._hicache:
             self.tree_cache.check_hicache_events()
+        if self.disagg_mode == "prefill":
+            self.process_disagg_prefill_inflight()
+        elif self.disagg_mode == "decode":
+            self.process_disagg_decode_queues()
         batch = self.get_next_batch_to_run()
         self.cur_batch = batch
         if batch is not None:
@@ -399,6 +421,10 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                 return None
             if getattr(val, "is_invalid", False):
                 return self._reject(req, f"Invalid grammar request: {key}")
+        if self.disagg_mode == "prefill":
+            self.disagg_prefill_admit(req)
+        elif self.disagg_mode == "decode" and self.disagg_decode_admit(req):
+            return None
         self._add_request_to_queue(req)
         return None
 
@@ -649,6 +675,15 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                 r.req_pool_idx = None
         if hit:
             self.stream_output(hit, False)
+        if self.disagg_mode == "decode":
+            pq = self.disagg_prealloc_queue
+            for r in [r for r in pq.queue if match(r)]:
+                pq.queue.remove(r)
+                r.finished_reason = FINISH_ABORT(msg)
+                self.stream_output([r], False)
+            for r in self.disagg_transfer_queue.queue:
+                if match(r):
+                    r.to_abort, r.to_abort_message = True, msg
         gq = [r for r in self.grammar_queue if match(r)]
         self.grammar_queue = [r for r in self.grammar_queue if not match(r)]
         for r in gq:
@@ -829,6 +864,10 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         """Leak invariant on idle (reference :1723-1775): every slot is either free, held by an
         evictable tree node, or protected by a lock that some request still holds."""
         if self.chunked_req is not None or self.result_queue:
+            return
+        if self.disagg_mode == "prefill" and self.disagg_prefill_inflight:
+            return
+        if self.disagg_mode == "decode" and (self.disagg_prealloc_queue.queue or self.disagg_transfer_queue.queue):
             return
         if not self.running_batch.is_empty() or self.waiting_queue and any(r.req_pool_idx is not None for r in self.waiting_queue):
             return

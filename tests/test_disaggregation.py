@@ -1,0 +1,276 @@
+"""PD disaggregation on CPU: control plane units (state machine, registry + heartbeats, auth,
+reaper, watchdog, router) and an end-to-end prefill -> transfer -> decode run whose output
+must equal a single engine's (reference tests: `python/sgl_jax/test/disaggregation/`).
+Failures are injected on the host only: a peer that never answers, a dropped acknowledgement,
+a wrong secret."""
+
+import threading
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from sglang_jax_b200.disaggregation import pd_auth
+from sglang_jax_b200.disaggregation.base.kv_manager import KVPoll, StateHolder
+from sglang_jax_b200.disaggregation.bootstrap import (BootstrapClient, BootstrapServer, HeartbeatDaemon,
+                                                      IncompatiblePeer, PrefillInfoCache, Registry, check_compat)
+from sglang_jax_b200.disaggregation.common import metrics
+from sglang_jax_b200.disaggregation.common.core import CommonKVManager
+from sglang_jax_b200.disaggregation.debug_utils import kv_digest
+from sglang_jax_b200.disaggregation.decode_watchdog import EventLoopWatchdog
+from sglang_jax_b200.disaggregation.transfer.zmq_transfer import TransferError, ZmqTransferBackend
+from sglang_jax_b200.mem_cache.memory_pool import MHATokenToKVPool
+from sglang_jax_b200.utils.common import get_free_port
+
+
+def test_state_machine_rejects_illegal_moves():
+    s = StateHolder()
+    with pytest.raises(ValueError):
+        s.transition(KVPoll.TRANSFERRING)
+    s.transition(KVPoll.WAITING_FOR_INPUT)
+    s.transition(KVPoll.TRANSFERRING)
+    s.transition(KVPoll.SUCCESS)
+    with pytest.raises(ValueError):
+        s.transition(KVPoll.FAILED)
+    f = StateHolder()
+    f.fail("peer vanished")
+    assert f.state == KVPoll.FAILED and f.failure == "peer vanished"
+    f.fail("again")      # terminal: ignored
+    assert f.failure == "peer vanished"
+
+
+def test_auth_tokens_and_tags():
+    assert pd_auth.check_bearer(None, None)
+    hdr = pd_auth.auth_headers("s3cret")["Authorization"]
+    assert pd_auth.check_bearer(hdr, "s3cret") and not pd_auth.check_bearer(hdr, "other")
+    assert not pd_auth.check_bearer(None, "s3cret")
+    tag = pd_auth.sign(b"payload", "k")
+    assert pd_auth.verify(b"payload", tag, "k") and not pd_auth.verify(b"payload!", tag, "k")
+
+
+LAYOUT = {"page_size": 16, "num_layers": 2, "page_bytes_per_layer": [4096, 4096], "dtype": "float32", "tp_size": 1,
+          "model": "Qwen3ForCausalLM"}
+
+
+def test_registry_ttl_compat_and_protocol_floor():
+    reg = Registry(ttl=0.15)
+    reg.register(dict(LAYOUT, engine_id="p0", transfer_addr="h:1", protocol_version=3))
+    with pytest.raises(IncompatiblePeer):
+        reg.register(dict(LAYOUT, page_size=32, engine_id="p1", transfer_addr="h:2", protocol_version=3))
+    with pytest.raises(IncompatiblePeer):
+        reg.register(dict(LAYOUT, engine_id="p2", transfer_addr="h:3", protocol_version=1))
+    assert len(reg.table()["prefills"]) == 1
+    time.sleep(0.2)
+    assert reg.table()["prefills"] == []                     # missed its heartbeats
+    assert not reg.heartbeat("p0")
+    with pytest.raises(IncompatiblePeer):
+        check_compat(LAYOUT, dict(LAYOUT, dtype="bfloat16", protocol_version=3))
+
+
+def test_bootstrap_http_heartbeat_and_cache():
+    srv = BootstrapServer(port=get_free_port(), ttl=0.6, secret="abc").start()
+    try:
+        bad = BootstrapClient(srv.url, secret="wrong")
+        with pytest.raises(Exception):
+            bad.prefills()
+        cl = BootstrapClient(srv.url, secret="abc")
+        hb = HeartbeatDaemon(cl, dict(LAYOUT, engine_id="p0", tp_rank=0, transfer_addr="127.0.0.1:5", ack_addr="a:1",
+                                      http_url="http://x"), interval=0.1).start()
+        cache = PrefillInfoCache(cl, LAYOUT, refresh_interval=0.05)
+        assert cache.lookup("p0")["transfer_addr"] == "127.0.0.1:5"
+        assert cache.lookup(None, room=77)["engine_id"] == "p0"
+        time.sleep(0.9)                                       # several TTLs: heartbeats keep it alive
+        assert cache.lookup("p0") is not None and hb.beats >= 3
+        srv.registry.unregister("p0")                         # registry forgot us (e.g. it restarted)
+        time.sleep(0.3)
+        assert hb.reregistrations >= 1 and cache.lookup("p0") is not None
+        hb.stop()
+        time.sleep(0.1)                                       # let the cached table age out
+        assert cache.lookup("p0") is None
+        other = PrefillInfoCache(cl, dict(LAYOUT, page_size=64), refresh_interval=0)
+        assert other.engines() == []
+    finally:
+        srv.stop()
+
+
+def _pool(seed=None):
+    pool = MHATokenToKVPool(16 * 16, 16, torch.float32, 2, 8, 2, "cpu")
+    if seed is not None:
+        g = torch.Generator().manual_seed(seed)
+        for b in pool.kv_buffer:
+            b.copy_(torch.randn(b.shape, generator=g))
+    return pool
+
+
+def test_transfer_pull_ack_and_digest():
+    metrics.reset()
+    src, dst = _pool(1), _pool()
+    page_bytes = sum(b[0].numel() * 4 for b in src.kv_buffer)
+    pb = ZmqTransferBackend(src, secret="k")
+    pb.start()
+    pm = CommonKVManager("prefill", pb, page_bytes, secret="k", reaper_interval=0.05, ack_timeout=5)
+    dm = CommonKVManager("decode", ZmqTransferBackend(dst, secret="k", pull_timeout=5), page_bytes, secret="k",
+                         reaper_interval=0.05, pull_timeout=5)
+    try:
+        recv = dm.create_receiver("r1")
+        recv.init(np.array([9, 3, 4]), "room-1", pb.addr)      # decode may ask before prefill is ready
+        time.sleep(0.05)
+        assert recv.poll() in (KVPoll.WAITING_FOR_INPUT, KVPoll.TRANSFERRING)
+        send = pm.create_sender("r1")
+        send.init(np.array([2, 5, 7]), "room-1", first_token=42, meta={"kv_len": 40})
+        send.send()
+        t0 = time.time()
+        while time.time() - t0 < 5 and not (recv.poll().terminal and send.poll().terminal):
+            time.sleep(0.01)
+        assert recv.poll() == KVPoll.SUCCESS and send.poll() == KVPoll.SUCCESS
+        assert recv.meta["first_token"] == 42 and recv.meta["kv_len"] == 40
+        assert kv_digest(src, [2, 5, 7]) == kv_digest(dst, [9, 3, 4])
+        assert "room-1" not in pb.registered                   # released after the acknowledgement
+        snap = metrics.snapshot()
+        assert any(k.startswith("pd_transfer_total") and "success" in k for k in snap)
+        send.clear(), recv.clear()
+        assert pm.drain(1) and dm.drain(1)
+        with pytest.raises(RuntimeError):
+            pm.create_sender("late")
+    finally:
+        pm.shutdown(), dm.shutdown()
+
+
+def test_reaper_fails_orphans_and_wrong_secret_is_refused():
+    src, dst = _pool(2), _pool()
+    pb = ZmqTransferBackend(src, secret="k")
+    pb.start()
+    pm = CommonKVManager("prefill", pb, 1, secret="k", reaper_interval=0.05, ack_timeout=0.2)
+    dm = CommonKVManager("decode", ZmqTransferBackend(dst, secret="nope", pull_timeout=0.5), 1, secret="nope",
+                         reaper_interval=0.05, pull_timeout=0.5)
+    try:
+        # nobody ever pulls: the sender is reaped after ack_timeout and its pages are released
+        s = pm.create_sender("orphan")
+        s.init(np.array([1]), "room-x", 1)
+        s.send()
+        t0 = time.time()
+        while time.time() - t0 < 3 and s.poll() != KVPoll.FAILED:
+            time.sleep(0.02)
+        assert s.poll() == KVPoll.FAILED and "acknowledgement" in s.state.failure and "room-x" not in pb.registered
+        # a decode engine with the wrong secret cannot read pages
+        s2 = pm.create_sender("guarded")
+        s2.init(np.array([1]), "room-y", 1)
+        s2.send()
+        r = dm.create_receiver("guarded")
+        r.init(np.array([3]), "room-y", pb.addr)
+        t0 = time.time()
+        while time.time() - t0 < 3 and not r.poll().terminal:
+            time.sleep(0.02)
+        assert r.poll() == KVPoll.FAILED and "unauthorized" in r.state.failure
+        assert torch.count_nonzero(dst.kv_buffer[0][3]) == 0
+        # a peer that is not there at all: bounded wait, then FAILED
+        r2 = dm.create_receiver("nobody")
+        r2.init(np.array([4]), "room-z", f"127.0.0.1:{get_free_port()}")
+        t0 = time.time()
+        while time.time() - t0 < 4 and not r2.poll().terminal:
+            time.sleep(0.02)
+        assert r2.poll() == KVPoll.FAILED and "timed out" in r2.state.failure
+    finally:
+        pm.shutdown(), dm.shutdown()
+
+
+def test_decode_watchdog_flags_a_stalled_loop():
+    stalls = []
+    wd = EventLoopWatchdog(0.1, has_work=lambda: True, on_stall=stalls.append, poll=0.02).start()
+    try:
+        for _ in range(10):
+            wd.beat()
+            time.sleep(0.02)
+        assert not stalls
+        time.sleep(0.3)                 # the loop "hangs" (host-side stand-in: it simply stops beating)
+        assert stalls and stalls[0] > 0.1
+    finally:
+        wd.stop()
+    idle = EventLoopWatchdog(0.05, has_work=lambda: False, on_stall=stalls.append, poll=0.01).start()
+    n = len(stalls)
+    time.sleep(0.2)
+    idle.stop()
+    assert len(stalls) == n             # nothing pending: silence is fine
+
+
+def test_router_policies_and_room_fanout():
+    from sglang_jax_b200.disaggregation.mini_lb import MiniLoadBalancer, PrefillEndpoint
+    from sglang_jax_b200.disaggregation.router_args import RouterArgs
+    lb = MiniLoadBalancer(RouterArgs(prefill_urls=["http://p0", "http://p1"], decode_urls=["http://d0", "http://d1", "http://d2"]))
+    picks = [lb.pick() for _ in range(6)]
+    assert [p.http_url for p, _ in picks] == ["http://p0", "http://p1"] * 3
+    assert [d for _, d in picks] == ["http://d0", "http://d1", "http://d2"] * 2
+    lb.args.policy = "shortest_queue"
+    lb.prefills[0].inflight = 5
+    lb.decode_inflight["http://d0"] = 2
+    p, d = lb.pick()
+    assert p.http_url == "http://p1" and d == "http://d1"
+    ep = PrefillEndpoint("http://p0", "10.0.0.1:30001", "e0")
+    pre, dec = lb._augment({"input_ids": [[1, 2], [3, 4]], "stream": True}, ep, 100)
+    assert pre["bootstrap_room"] == [100, 101] and pre["stream"] is False
+    assert dec["bootstrap_host"] == ["10.0.0.1"] * 2 and dec["bootstrap_port"] == [30001] * 2 and dec["stream"]
+    pre, dec = lb._augment({"text": "hi"}, ep, 7)
+    assert pre["bootstrap_room"] == 7 and dec["bootstrap_host"] == "10.0.0.1"
+    empty = MiniLoadBalancer(RouterArgs(decode_urls=["http://d0"]))
+    with pytest.raises(RuntimeError):
+        empty.pick()
+
+
+def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
+    from sglang_jax_b200.entrypoints.engine import Engine
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import write_tiny_qwen3_checkpoint
+    ckpt = write_tiny_qwen3_checkpoint(str(tmp_path / "m"))
+    rng = np.random.RandomState(1)
+    prompts = [rng.randint(5, 1000, size=n).tolist() for n in (40, 17, 70)]
+    sp = {"temperature": 0.0, "max_new_tokens": 8, "ignore_eos": True}
+    common = dict(model_path=ckpt, device="cpu", enable_single_process=True, page_size=16, skip_tokenizer_init=True,
+                  max_total_tokens=2048, dtype="float32", log_level="error")
+    ps.reset_state()
+    plain = Engine(**common)
+    try:
+        want = [o["output_ids"] for o in plain.generate(input_ids=prompts, sampling_params=sp)]
+    finally:
+        plain.shutdown()
+    srv = BootstrapServer(port=get_free_port(), secret="pd").start()
+    pd_kw = dict(disaggregation_bootstrap_url=srv.url, disaggregation_shared_secret="pd",
+                 disaggregation_transfer_port=0, disaggregation_side_channel_port=0)
+    prefill = Engine(**common, disaggregation_mode="prefill", chunked_prefill_size=32, **pd_kw)
+    decode = Engine(**common, disaggregation_mode="decode", **pd_kw)
+    try:
+        res = {}
+
+        def run(name, eng):
+            res[name] = eng.generate(input_ids=prompts, sampling_params=sp, bootstrap_room=[11, 12, 13])
+
+        ts = [threading.Thread(target=run, args=("decode", decode)), threading.Thread(target=run, args=("prefill", prefill))]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout=120)
+        assert "decode" in res and "prefill" in res
+        assert [o["output_ids"] for o in res["decode"]] == want
+        assert [o["output_ids"] for o in res["prefill"]] == [w[:1] for w in want]
+        # both engines are clean afterwards: the prefill released the pages once they were acknowledged
+        t0 = time.time()
+        while time.time() - t0 < 5 and prefill.scheduler.disagg_prefill_inflight:
+            time.sleep(0.02)
+        assert prefill.scheduler.disagg_sent == 3 and decode.scheduler.disagg_received == 3
+        time.sleep(0.1)
+        prefill.scheduler.check_memory()
+        decode.scheduler.check_memory()
+        # a request whose prefill never happens fails cleanly on the decode side (bounded pull)
+        decode.scheduler.disagg_kv_manager.backend.pull_timeout = 0.5
+        lost = decode.generate(input_ids=prompts[:1], sampling_params=sp, bootstrap_room=[999])[0]
+        fr = lost["meta_info"]["finish_reason"]
+        assert fr["type"] == "abort" and fr["err_type"] == "KVTransferError" and lost["output_ids"] == []
+        time.sleep(0.1)
+        decode.scheduler.check_memory()
+    finally:
+        from sglang_jax_b200.disaggregation.runtime import shutdown_disaggregation
+        shutdown_disaggregation(prefill.scheduler, 1)
+        shutdown_disaggregation(decode.scheduler, 1)
+        prefill.shutdown()
+        decode.shutdown()
+        srv.stop()
