@@ -25,8 +25,10 @@ from ..parallel import state as ps
 
 class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, hidden_size: int, intermediate_size: int, dtype=torch.bfloat16,
-                 ep_size: int | None = None, tp_size=None, tp_rank=None, layer_id: int = 0):
+                 ep_size: int | None = None, tp_size=None, tp_rank=None, layer_id: int = 0,
+                 activation: str = "silu"):
         super().__init__()
+        self.activation = activation
         self.tp_size = tp_size if tp_size is not None else ps.tp_size()
         self.tp_rank = tp_rank if tp_rank is not None else ps.tp_rank()
         ep = ep_size if ep_size is not None else ps.ep_size()
@@ -70,14 +72,22 @@ class FusedMoE(nn.Module):
         shared expert's partial output)."""
         if self.routed_experts_capturer is not None:
             self.routed_experts_capturer.capture(self.layer_id, topk_ids)
-        if ops.use_native(x):
+        if ops.use_native(x) and self.activation == "silu":
             from ..ops import moe_native
             pairs = x.shape[0] * topk_ids.shape[1]
             if self.workspace is None or self.workspace.max_pairs < pairs:
                 self.workspace = moe_native.MoeWorkspace(max(pairs, 2048), self.num_local_experts, x.device)
             return moe_native.fused_experts(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids,
                                             self.expert_start, self.workspace, add, out)
-        y = ops.fused_experts(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids, self.expert_start, None, add)
+        if self.activation == "silu":
+            y = ops.fused_experts(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids, self.expert_start, None,
+                                  add)
+        else:
+            from ..ops import reference
+            y = reference.moe_forward(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids, self.expert_start,
+                                      act=self.activation)
+            if add is not None:
+                y = (y.float() + add.float()).to(y.dtype)
         if out is not None:
             out.copy_(y)
             return out

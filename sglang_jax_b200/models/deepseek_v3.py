@@ -100,10 +100,10 @@ class MLAAttention(nn.Module):
 
 
 class DeepseekMoE(nn.Module):
-    def __init__(self, config, layer_id, dtype):
+    def __init__(self, config, layer_id, dtype, correction_bias: bool | None = None):
         super().__init__()
         E = config.n_routed_experts
-        bias = getattr(config, "topk_method", "greedy") == "noaux_tc"
+        bias = getattr(config, "topk_method", "greedy") == "noaux_tc" if correction_bias is None else correction_bias
         self.gate = GateLogit(config.hidden_size, E, dtype, correction_bias=bias,
                               score_func=getattr(config, "scoring_func", "softmax"))
         self.topk = TopK(config.num_experts_per_tok, renormalize=getattr(config, "norm_topk_prob", False),

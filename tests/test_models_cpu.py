@@ -170,3 +170,135 @@ def test_gemma2_sliding_window_softcap_matches_hf(tmp_path, hybrid):
         assert second[0]["meta_info"]["cached_tokens"] > 0
     finally:
         eng.shutdown()
+
+
+def test_glm4_moe_matches_hf(tmp_path):
+    from transformers import Glm4MoeConfig, Glm4MoeForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=3,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-5, rope_theta=10000.0,
+               vocab_size=512, tie_word_embeddings=False, max_position_embeddings=512, partial_rotary_factor=0.5,
+               n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, n_group=2, topk_group=1,
+               routed_scaling_factor=1.5, norm_topk_prob=True, first_k_dense_replace=1, use_qk_norm=True,
+               attention_bias=True)
+    hf = _init(Glm4MoeForCausalLM(Glm4MoeConfig(**cfg)))
+    for n, p in hf.named_parameters():
+        if n.endswith("bias") and p.dim() == 1:
+            p.data.normal_(0, 0.05)
+    for n, b in hf.named_buffers():
+        if "e_score_correction_bias" in n:
+            b.data.normal_(0, 0.1)
+    path = _save(str(tmp_path / "glm4moe"), hf, cfg, "Glm4MoeForCausalLM", "glm4_moe")
+    assert _generate(path, PROMPTS) == _hf_generate(hf, PROMPTS)
+
+
+def test_minimax_m2_matches_hf(tmp_path):
+    from transformers import MiniMaxM2Config, MiniMaxM2ForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, vocab_size=512, tie_word_embeddings=False,
+               max_position_embeddings=512, num_local_experts=8, num_experts_per_tok=2,
+               rope_parameters={"rope_theta": 10000.0, "rope_type": "default"})
+    hf = _init(MiniMaxM2ForCausalLM(MiniMaxM2Config(**cfg)))
+    for n, b in hf.named_buffers():
+        if "e_score_correction_bias" in n:
+            b.data.normal_(0, 0.1)
+    for n, p in hf.named_parameters():
+        if "q_norm" in n or "k_norm" in n:
+            p.data.uniform_(0.5, 1.5)
+    path = _save(str(tmp_path / "m2"), hf, dict(cfg, rope_theta=10000.0), "MiniMaxM2ForCausalLM", "minimax_m2")
+    assert _generate(path, PROMPTS) == _hf_generate(hf, PROMPTS)
+
+
+def _dense_reference_generate(step_logits, prompts, n):
+    """Greedy decoding with a plain full-sequence forward (no KV cache) as the oracle."""
+    outs = []
+    for p in prompts:
+        ids = list(p)
+        for _ in range(n):
+            ids.append(int(step_logits(torch.tensor(ids))[-1].argmax()))
+        outs.append(ids[len(p):])
+    return outs
+
+
+def test_grok_matches_plain_torch_restatement(tmp_path):
+    """No HF class exists for Grok: the oracle is a direct restatement of the layer math in
+    plain torch over the same random checkpoint."""
+    import math
+    from safetensors.torch import save_file
+    torch.manual_seed(0)
+    H, I, nh, nkv, D, V, L, E, K = 64, 96, 4, 2, 16, 128, 2, 4, 2
+    cfg = dict(architectures=["Grok1ForCausalLM"], model_type="grok-1", hidden_size=H, intermediate_size=I,
+               moe_intermediate_size=I, num_hidden_layers=L, num_attention_heads=nh, num_key_value_heads=nkv,
+               head_dim=D, rms_norm_eps=1e-5, rope_theta=10000, vocab_size=V, max_position_embeddings=256,
+               num_local_experts=E, num_experts_per_tok=K, attn_logit_softcapping=30.0, router_logit_softcapping=30.0,
+               final_logit_softcapping=0.0, embedding_multiplier_scale=3.0, output_multiplier_scale=0.5,
+               residual_moe=True, torch_dtype="float32", tie_word_embeddings=False)
+    sd = {"model.embed_tokens.weight": torch.randn(V, H) * 0.3, "lm_head.weight": torch.randn(V, H) * 0.3,
+          "model.norm.weight": torch.rand(H) + 0.5}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        sd[p + "self_attn.q_proj.weight"] = torch.randn(nh * D, H) * 0.2
+        sd[p + "self_attn.k_proj.weight"] = torch.randn(nkv * D, H) * 0.2
+        sd[p + "self_attn.v_proj.weight"] = torch.randn(nkv * D, H) * 0.2
+        sd[p + "self_attn.o_proj.weight"] = torch.randn(H, nh * D) * 0.2
+        for nm in ("pre_attn_norm", "post_attn_norm", "pre_moe_norm", "post_moe_norm"):
+            sd[p + nm + ".weight"] = torch.rand(H) + 0.5
+        sd[p + "block_sparse_moe.gate.weight"] = torch.randn(E, H)
+        for e in range(E):
+            sd[p + f"block_sparse_moe.experts.{e}.w1.weight"] = torch.randn(I, H) * 0.2
+            sd[p + f"block_sparse_moe.experts.{e}.w3.weight"] = torch.randn(I, H) * 0.2
+            sd[p + f"block_sparse_moe.experts.{e}.w2.weight"] = torch.randn(H, I) * 0.2
+        sd[p + "mlp.gate_proj.weight"] = torch.randn(I, H) * 0.2
+        sd[p + "mlp.up_proj.weight"] = torch.randn(I, H) * 0.2
+        sd[p + "mlp.down_proj.weight"] = torch.randn(H, I) * 0.2
+    path = str(tmp_path / "grok")
+    os.makedirs(path)
+    save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * w
+
+    def rope(x, pos):
+        half = D // 2
+        inv = 1.0 / (10000 ** (torch.arange(0, D, 2).float() / D))
+        ang = pos[:, None].float() * inv[None]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        x1, x2 = x[..., :half], x[..., half:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+    gelu = lambda t: torch.nn.functional.gelu(t, approximate="tanh")
+
+    def logits_of(ids):
+        T = len(ids)
+        pos = torch.arange(T)
+        x = sd["model.embed_tokens.weight"][ids] * 3.0
+        for i in range(L):
+            p = f"model.layers.{i}."
+            h = rms(x, sd[p + "pre_attn_norm.weight"])
+            q = rope((h @ sd[p + "self_attn.q_proj.weight"].T).view(T, nh, D), pos)
+            k = rope((h @ sd[p + "self_attn.k_proj.weight"].T).view(T, nkv, D), pos)
+            v = (h @ sd[p + "self_attn.v_proj.weight"].T).view(T, nkv, D)
+            k, v = k.repeat_interleave(nh // nkv, 1), v.repeat_interleave(nh // nkv, 1)
+            s = torch.einsum("qhd,khd->hqk", q, k) * D ** -0.5
+            s = 30.0 * torch.tanh(s / 30.0)
+            s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(T, nh * D)
+            x = x + rms(a @ sd[p + "self_attn.o_proj.weight"].T, sd[p + "post_attn_norm.weight"])
+            h = rms(x, sd[p + "pre_moe_norm.weight"])
+            rl = h @ sd[p + "block_sparse_moe.gate.weight"].T
+            rl = 30.0 * torch.tanh(rl / 30.0)
+            w, idx = torch.topk(torch.softmax(rl, -1), K, -1)
+            y = torch.zeros_like(h)
+            for t in range(T):
+                for j in range(K):
+                    e = int(idx[t, j])
+                    pe = p + f"block_sparse_moe.experts.{e}."
+                    y[t] += w[t, j] * ((gelu(h[t] @ sd[pe + "w1.weight"].T) * (h[t] @ sd[pe + "w3.weight"].T)) @ sd[pe + "w2.weight"].T)
+            d = (gelu(h @ sd[p + "mlp.gate_proj.weight"].T) * (h @ sd[p + "mlp.up_proj.weight"].T)) @ sd[p + "mlp.down_proj.weight"].T
+            x = x + rms((y + d) / math.sqrt(2.0), sd[p + "post_moe_norm.weight"])
+        return (rms(x, sd["model.norm.weight"]) @ sd["lm_head.weight"].T) * 0.5
+
+    prompts = [[5, 9, 33, 7, 100, 2], [1, 2, 3]]
+    want = _dense_reference_generate(logits_of, prompts, 6)
+    assert _generate(path, prompts, n=6) == want
