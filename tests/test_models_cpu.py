@@ -302,3 +302,43 @@ def test_grok_matches_plain_torch_restatement(tmp_path):
     prompts = [[5, 9, 33, 7, 100, 2], [1, 2, 3]]
     want = _dense_reference_generate(logits_of, prompts, 6)
     assert _generate(path, prompts, n=6) == want
+
+
+def test_bailing_moe_is_glm4_moe_under_other_names(tmp_path):
+    """Ling checkpoints (fused `query_key_value`, `word_embeddings`, `expert_bias`) must produce
+    what the equivalent GLM-4-MoE checkpoint produces (which is checked against HF above)."""
+    from transformers import Glm4MoeConfig, Glm4MoeForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=3,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-5, rope_theta=10000.0,
+               vocab_size=512, tie_word_embeddings=False, max_position_embeddings=512, partial_rotary_factor=0.5,
+               n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, n_group=2, topk_group=1,
+               routed_scaling_factor=1.5, norm_topk_prob=True, first_k_dense_replace=1, use_qk_norm=True,
+               attention_bias=False)
+    hf = _init(Glm4MoeForCausalLM(Glm4MoeConfig(**cfg)))
+    for n, b in hf.named_buffers():
+        if "e_score_correction_bias" in n:
+            b.data.normal_(0, 0.1)
+    want = _hf_generate(hf, PROMPTS)
+
+    def rename(sd):
+        out = {}
+        qkv = {}
+        for k, v in sd.items():
+            k = k.replace("model.embed_tokens.", "model.word_embeddings.").replace(".self_attn.o_proj.", ".attention.dense.")
+            k = k.replace(".self_attn.q_norm.", ".attention.query_layernorm.").replace(".self_attn.k_norm.", ".attention.key_layernorm.")
+            k = k.replace(".mlp.gate.e_score_correction_bias", ".mlp.gate.expert_bias")
+            for p in ("q_proj", "k_proj", "v_proj"):
+                if f".self_attn.{p}.weight" in k:
+                    qkv.setdefault(k.split(".self_attn.")[0], {})[p] = v
+                    break
+            else:
+                out[k] = v
+        for head, d in qkv.items():
+            out[head + ".attention.query_key_value.weight"] = torch.cat([d["q_proj"], d["k_proj"], d["v_proj"]], 0)
+        return out
+
+    ling = dict(cfg, num_experts=8, num_shared_experts=1, score_function="sigmoid", moe_router_enable_expert_bias=True)
+    for k in ("n_routed_experts", "n_shared_experts"):
+        ling.pop(k)
+    path = _save(str(tmp_path / "ling"), hf, ling, "BailingMoeV2ForCausalLM", "bailing_moe", rename=rename)
+    assert _generate(path, PROMPTS) == want
