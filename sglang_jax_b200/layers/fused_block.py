@@ -17,7 +17,7 @@ from ..parallel import state as ps
 def row_linear_add_norm(lin, x, residual, norm):
     """Returns `(norm(lin(x) + residual), lin(x) + residual)`."""
     comm = ps.get_state().fused_comm
-    if comm is not None and lin.tp_size > 1 and lin.bias is None and lin.lora is None \
+    if comm is not None and lin.tp_size > 1 and lin.bias is None and lin.lora is None and lin.qweight is None \
             and comm.supports_gemm_ar_norm(x, lin.weight):
         return comm.gemm_allreduce_add_rmsnorm(x, lin.weight, residual, norm.weight,
                                                norm.variance_epsilon, norm.gemma)

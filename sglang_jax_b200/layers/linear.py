@@ -29,9 +29,18 @@ class LinearBase(nn.Module):
         self.weight = _param(out_features, in_features, dtype=dtype)
         self.bias = _param(out_features, dtype=dtype) if bias else None
         self.lora = None   # set by lora.layers.wrap_linear
+        self.qweight = None   # utils.quantization.QuantizedWeight once the layer is quantised
+
+    def set_quantized(self, qw):
+        """Replace the dense weight by quantised storage (the dense tensor is released)."""
+        self.qweight = qw
+        self.weight = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = ops.linear(x, self.weight, self.bias)
+        if self.qweight is not None:
+            y = self.qweight.linear(x, self.bias)
+        else:
+            y = ops.linear(x, self.weight, self.bias)
         if self.lora is not None:
             y = self.lora.apply(x, y)
         return y
@@ -160,3 +169,8 @@ class RowParallelLinear(LinearBase):
         if self.reduce_results and self.tp_size > 1:
             y = ps.all_reduce(y)
         return y
+
+
+# The reference has a separate `QuantizedLinear` class (`layers/linear.py:198`); here any linear
+# layer becomes quantised in place through `set_quantized`.
+QuantizedLinear = LinearBase

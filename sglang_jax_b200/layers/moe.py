@@ -66,6 +66,18 @@ class FusedMoE(nn.Module):
             src = w if self.expert_parallel or self.tp_size == 1 else w.narrow(1, self.tp_rank * I, I)
             param.data[local].copy_(src)
 
+    def quantize_(self, dtype, block_size=None):
+        """Round the expert weights through `dtype` with per-channel or block scales.  The values
+        are stored de-quantised in the compute dtype (the grouped GEMM runs in bf16), so this
+        reproduces the numerics of a quantised checkpoint without a separate kernel path."""
+        from ..utils.quantization import dequantize_tensor, quantize_tensor
+        gran = "block" if block_size else "per_channel"
+        for p in (self.w13_weight, self.w2_weight):
+            for e in range(p.shape[0]):
+                q, s = quantize_tensor(p.data[e], dtype, gran, block_size)
+                p.data[e].copy_(dequantize_tensor(q, s, block_size, p.dtype))
+        self.quantized = True
+
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 add: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         """Partial sum over this rank's experts / intermediate slice (`add` is folded in, e.g. the

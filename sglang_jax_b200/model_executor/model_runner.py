@@ -53,7 +53,10 @@ class ModelRunner:
         t0 = time.time()
         free_before = self._free_mem()
         loader = get_model_loader(server_args.load_format, seed=0)
-        self.model = loader.load_model(model_config, self.device)
+        from ..configs.quantization_config import QuantizationConfig
+        self.quant_config = QuantizationConfig.resolve(server_args.quantization, server_args.quantization_config_path,
+                                                       model_config.hf_config)
+        self.model = loader.load_model(model_config, self.device, self.quant_config)
         self.weight_bytes = sum(p.numel() * p.element_size() for p in self.model.parameters())
         logger.info("model loaded in %.1fs, %.2f GB weights on %s", time.time() - t0,
                     self.weight_bytes / 2 ** 30, self.device)

@@ -84,9 +84,13 @@ class DefaultModelLoader:
         with torch.device(device):
             model = cls(model_config.hf_config, dtype=model_config.dtype, quant_config=quant_config) \
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
-        it = self._iterator(model_config.model_path)
+        it = dequant_static_fp8(self._iterator(model_config.model_path), getattr(quant_config, "weight_block_size", None))
         loaded = model.load_weights(it)
         check_all_loaded(model, loaded)
+        if quant_config is not None and not quant_config.is_static_checkpoint:
+            from ..utils.quantization import apply_linear_quantization, apply_moe_quantization
+            n = apply_linear_quantization(model, quant_config) + apply_moe_quantization(model, quant_config)
+            logger.info("quantized %d modules with recipe %s", n, quant_config.name)
         return model.eval()
 
     def _iterator(self, path):
@@ -112,6 +116,44 @@ class DummyModelLoader:
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
         initialize_dummy_weights(model, self.seed)
         return model.eval()
+
+
+def dequant_static_fp8(weights, block_size=None):
+    """Static block-FP8 checkpoints (DeepSeek-V3 release format) ship `X.weight` in float8_e4m3fn
+    next to `X.weight_scale_inv` ([ceil(N/128), ceil(K/128)] fp32).  The pair is folded into one
+    bf16 tensor while streaming, whatever order the two arrive in; everything else passes
+    through.  (The matmuls then run on the bf16 tcgen05 kernel.)"""
+    from ..utils.quantization import dequantize_tensor
+    bs = tuple(block_size) if block_size else (128, 128)
+    pend_w: dict[str, torch.Tensor] = {}
+    pend_s: dict[str, torch.Tensor] = {}
+    fp8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+    for name, w in weights:
+        if name.endswith(".weight_scale_inv") or name.endswith(".weight_scale"):
+            base = name.rsplit(".", 1)[0] + ".weight"
+            inv = name.endswith("_inv")
+            if base in pend_w:
+                yield base, _fold(pend_w.pop(base), w, bs, inv, dequantize_tensor)
+            else:
+                pend_s[base] = (w, inv)
+            continue
+        if w.dtype in fp8:
+            if name in pend_s:
+                sc, inv = pend_s.pop(name)
+                yield name, _fold(w, sc, bs, inv, dequantize_tensor)
+            else:
+                pend_w[name] = w
+            continue
+        yield name, w
+    for name, w in pend_w.items():      # fp8 tensors without a scale: plain cast
+        yield name, w.to(torch.bfloat16)
+
+
+def _fold(w, scale, bs, inv, dequantize_tensor):
+    # both `weight_scale_inv` (DeepSeek) and `weight_scale` hold the multiplier that restores the weight
+    if scale.dim() == 1 and scale.numel() == w.shape[0]:
+        scale = scale.view(-1, 1)
+    return dequantize_tensor(w, scale.float(), bs, torch.bfloat16)
 
 
 def check_all_loaded(model, loaded):

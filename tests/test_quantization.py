@@ -1,0 +1,116 @@
+"""Quantisation helpers, presets, static-FP8 checkpoint ingestion and a quantised engine run
+(reference tests: `python/sgl_jax/test/quantization/`)."""
+
+import json
+import os
+
+import pytest
+import torch
+
+from sglang_jax_b200.configs.quantization_config import QuantizationConfig, presets
+from sglang_jax_b200.model_loader.loader import dequant_static_fp8
+from sglang_jax_b200.utils.quantization import (dequantize_tensor, quantize_activation, quantize_tensor)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float8_e4m3fn, 0.07), (torch.int8, 0.02)])
+@pytest.mark.parametrize("gran,bs", [("per_tensor", None), ("per_channel", None), ("block", (128, 128)), ("block", (64, 32))])
+def test_quantize_roundtrip(dtype, tol, gran, bs):
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(200, 300, generator=g) * torch.linspace(0.1, 3.0, 200).view(-1, 1)
+    q, s = quantize_tensor(w, dtype, gran, bs)
+    assert q.dtype == dtype and q.shape == w.shape
+    if gran == "block":
+        assert s.shape == (-(-200 // bs[0]), -(-300 // bs[1]))
+    back = dequantize_tensor(q, s, bs, torch.float32)
+    rel = (back - w).abs().max() / w.abs().max()
+    assert rel < tol, rel
+    if gran != "per_tensor":
+        # finer scales never do worse than one scale for the whole tensor
+        q0, s0 = quantize_tensor(w, dtype, "per_tensor")
+        assert (back - w).pow(2).mean() <= (dequantize_tensor(q0, s0, None, torch.float32) - w).pow(2).mean() * 1.01
+
+
+def test_activation_group_scales():
+    x = torch.randn(7, 300)
+    q, s = quantize_activation(x, torch.float8_e4m3fn, 128)
+    assert s.shape == (7, 3)
+    back = q.float() * s.repeat_interleave(128, 1)[:, :300]
+    assert (back - x).abs().max() / x.abs().max() < 0.07
+
+
+def test_presets_parse_and_rules():
+    names = presets()
+    assert {"fp8", "fp8_deepseek_v3", "int8", "fp8_block_128_dynamic", "int8_w8a8"} <= set(names)
+    for n in names:
+        cfg = QuantizationConfig.resolve(n)
+        assert cfg.linear_rules, n
+    ds = QuantizationConfig.resolve("fp8_deepseek_v3")
+    assert ds.is_static_checkpoint and ds.weight_block_size == (128, 128) and ds.granularity == "block"
+    q = QuantizationConfig.resolve("fp8_qwen3_30b_a3b")
+    assert q.rule_for("model.layers.0.mlp.gate") is None
+    assert q.rule_for("model.layers.0.self_attn.qkv_proj").weight_dtype == torch.float8_e4m3fn
+
+    class HF:
+        quantization_config = {"quant_method": "fp8", "weight_block_size": [128, 128]}
+    assert QuantizationConfig.resolve(None, None, HF()).is_static_checkpoint
+    with pytest.raises(ValueError):
+        QuantizationConfig.resolve("nope")
+
+
+def test_static_fp8_stream_is_folded_in_any_order():
+    w = torch.randn(256, 384)
+    q, s = quantize_tensor(w, torch.float8_e4m3fn, "block", (128, 128))
+    want = dequantize_tensor(q, s, (128, 128), torch.bfloat16)
+    plain = torch.randn(4, 4)
+    for order in ([("a.weight", q), ("a.weight_scale_inv", s), ("b.weight", plain)],
+                  [("a.weight_scale_inv", s), ("b.weight", plain), ("a.weight", q)]):
+        out = dict(dequant_static_fp8(iter(order)))
+        assert set(out) == {"a.weight", "b.weight"}
+        assert out["a.weight"].dtype == torch.bfloat16 and torch.equal(out["a.weight"], want)
+        assert torch.equal(out["b.weight"], plain)
+
+
+def test_engine_runs_static_fp8_checkpoint_and_dynamic_recipes(tmp_path):
+    """A block-FP8 copy of the tiny checkpoint must reproduce the run over its de-quantised weights
+    exactly; dynamic recipes must run and agree with the dense model on the first token."""
+    from safetensors.torch import save_file
+    from sglang_jax_b200.entrypoints.engine import Engine
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import TINY_QWEN3, tiny_qwen3_state_dict, write_config_only
+    sd = tiny_qwen3_state_dict(TINY_QWEN3, 0)
+    fp8_sd, deq_sd = {}, {}
+    for k, v in sd.items():
+        if v.dim() == 2 and "embed" not in k:
+            q, s = quantize_tensor(v, torch.float8_e4m3fn, "block", (128, 128))
+            fp8_sd[k] = q
+            fp8_sd[k + "_scale_inv"] = s
+            deq_sd[k] = dequantize_tensor(q, s, (128, 128), torch.float32)
+        else:
+            fp8_sd[k] = v
+            deq_sd[k] = v
+    paths = {}
+    for name, d, extra in (("fp8", fp8_sd, {"quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}}),
+                           ("deq", deq_sd, {}), ("dense", sd, {})):
+        p = write_config_only(str(tmp_path / name), dict(TINY_QWEN3, **extra))
+        save_file({k: v.contiguous() for k, v in d.items()}, os.path.join(p, "model.safetensors"))
+        paths[name] = p
+    prompts = [[3, 17, 42, 9, 5, 11, 8], [4, 4, 19, 23]]
+    sp = {"temperature": 0.0, "max_new_tokens": 8, "ignore_eos": True}
+
+    def run(path, **kw):
+        ps.reset_state()
+        eng = Engine(model_path=path, device="cpu", enable_single_process=True, page_size=4, skip_tokenizer_init=True,
+                     max_total_tokens=1024, dtype="float32", log_level="error", **kw)
+        try:
+            return [o["output_ids"] for o in eng.generate(input_ids=prompts, sampling_params=sp)]
+        finally:
+            eng.shutdown()
+
+    # bf16 rounding of the folded weights is the only difference between the two
+    a, b = run(paths["fp8"]), run(paths["deq"])
+    assert [x[:3] for x in a] == [x[:3] for x in b]
+    dense = run(paths["dense"])
+    for recipe in ("fp8", "int8", "fp8_block_128_dynamic"):
+        got = run(paths["dense"], quantization=recipe)
+        assert all(len(g) == 8 for g in got)
+        assert [g[0] for g in got] == [d[0] for d in dense], recipe
