@@ -61,6 +61,9 @@ class GatedRMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype), requires_grad=False)
         self.eps = eps
 
+    def weight_loader(self, param, w, shard_id=None):
+        param.data.copy_(w)
+
     def forward(self, x, gate):
         xf = x.float()
         y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()

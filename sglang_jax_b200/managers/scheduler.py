@@ -240,6 +240,12 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
     def init_memory_pool_and_cache(self):
         sa = self.server_args
         kv = self.token_to_kv_pool
+        lt = getattr(getattr(self.model_config, "hf_text_config", None), "layer_types", None) or []
+        if "linear_attention" in lt and not sa.disable_radix_cache:
+            # a shared prefix would also need the recurrent state at its end; without such
+            # checkpoints hybrid linear-attention models run without prefix sharing
+            logger.info("hybrid linear-attention model: prefix sharing is off")
+            sa.disable_radix_cache = True
         if kv is not None and hasattr(kv, "swa_pool"):
             # hybrid sliding-window model: dual allocator + window-aware prefix cache
             from ..mem_cache.allocator import SWATokenToKVPoolAllocator

@@ -1,0 +1,57 @@
+"""Per-request state of the linear-attention layers of hybrid models: the short-convolution
+window and the `[H, Dk, Dv]` recurrent matrix (reference
+`python/sgl_jax/srt/mem_cache/recurrent_state_pool.py:77`, `copy_slots` :230).
+
+A slot belongs to one request (`HybridReqToTokenPool` keeps the request -> slot ledger).  Slot 0 is
+a scratch slot used by padding rows.  `copy_slots` clones states (copy-on-write when a prefix with
+a recurrent checkpoint is shared)."""
+
+from __future__ import annotations
+
+import torch
+
+
+class RecurrentStatePool:
+    def __init__(self, size: int, num_layers: int, conv_dim: int, conv_kernel: int, num_heads: int, head_k_dim: int,
+                 head_v_dim: int, device: str = "cpu", conv_dtype=torch.bfloat16, state_dtype=torch.float32):
+        self.size = size
+        self.num_layers = num_layers
+        self.conv_state = torch.zeros((num_layers, size + 1, conv_dim, conv_kernel - 1), dtype=conv_dtype, device=device)
+        self.recurrent_state = torch.zeros((num_layers, size + 1, num_heads, head_k_dim, head_v_dim), dtype=state_dtype,
+                                           device=device)
+        self.free_slots = list(range(1, size + 1))
+        self.device = device
+
+    def available_size(self) -> int:
+        return len(self.free_slots)
+
+    def alloc(self, n: int) -> list[int] | None:
+        if n > len(self.free_slots):
+            return None
+        out, self.free_slots = self.free_slots[:n], self.free_slots[n:]
+        self.clear_slots(out)
+        return out
+
+    def free(self, slots) -> None:
+        self.free_slots.extend(int(s) for s in slots)
+
+    def clear_slots(self, slots) -> None:
+        idx = torch.as_tensor(list(slots), dtype=torch.long, device=self.conv_state.device)
+        if idx.numel():
+            self.conv_state[:, idx] = 0
+            self.recurrent_state[:, idx] = 0
+
+    def copy_slots(self, src, dst) -> None:
+        s = torch.as_tensor(list(src), dtype=torch.long, device=self.conv_state.device)
+        d = torch.as_tensor(list(dst), dtype=torch.long, device=self.conv_state.device)
+        self.conv_state[:, d] = self.conv_state[:, s]
+        self.recurrent_state[:, d] = self.recurrent_state[:, s]
+
+    def size_bytes(self) -> int:
+        return self.conv_state.numel() * self.conv_state.element_size() + \
+            self.recurrent_state.numel() * self.recurrent_state.element_size()
+
+    def clear(self) -> None:
+        self.free_slots = list(range(1, self.size + 1))
+        self.conv_state.zero_()
+        self.recurrent_state.zero_()

@@ -131,7 +131,8 @@ class CudaGraphRunner:
     # ------------------------------------------------------------------
     def can_run(self, batch: ModelWorkerBatch) -> bool:
         si = batch.sampling_info
-        return (self.enabled and not hasattr(self.runner.token_to_kv_pool, "swa_pool") and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
+        return (self.enabled and not hasattr(self.runner.token_to_kv_pool, "swa_pool")
+                and getattr(self.runner, "recurrent_pool", None) is None and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
                 and not batch.return_logprob and batch.capture_hidden_mode == 0 and batch.spec_info is None
                 and (si is None or (si.is_all_greedy and si.linear_penalty is None and si.vocab_mask is None
                                     and si.logit_bias is None))

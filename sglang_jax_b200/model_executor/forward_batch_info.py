@@ -139,6 +139,8 @@ class ForwardBatch:
             num_decode_in_mixed=batch.num_decode_in_mixed,
             h2d_bytes=total * 4,
         )
+        if getattr(runner, "recurrent_pool", None) is not None:
+            fb.extras["recurrent_pool"] = runner.recurrent_pool
         pool = runner.token_to_kv_pool
         if hasattr(pool, "swa_pool") and B:
             # sliding-window layers live in their own (smaller) pool: translate the rows' pages

@@ -143,6 +143,13 @@ class ModelRunner:
             # a few spare rows: requests being chunk-prefilled or retracted hold rows too
             req_to_token_pool = ReqToTokenPool(max_reqs + 8, ctx + 8, str(self.device), self.page_size)
         self.req_to_token_pool = req_to_token_pool
+        self.recurrent_pool = None
+        spec = getattr(self.model, "recurrent_spec", None)
+        if spec:
+            from ..mem_cache.recurrent_state_pool import RecurrentStatePool
+            # one state slot per request row (slot = row + 1)
+            self.recurrent_pool = RecurrentStatePool(req_to_token_pool.size, device=str(self.device),
+                                                     conv_dtype=self.dtype, **spec)
         n_layers = getattr(self.model, "num_kv_layers", None) or mc.num_hidden_layers
         if mc.attention_arch == AttentionArch.MLA:
             self.token_to_kv_pool = MLATokenToKVPool(self.max_total_num_tokens, self.page_size, self.kv_cache_dtype,

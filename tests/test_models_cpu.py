@@ -342,3 +342,32 @@ def test_bailing_moe_is_glm4_moe_under_other_names(tmp_path):
         ling.pop(k)
     path = _save(str(tmp_path / "ling"), hf, ling, "BailingMoeV2ForCausalLM", "bailing_moe", rename=rename)
     assert _generate(path, PROMPTS) == want
+
+
+@pytest.mark.parametrize("moe", [True, False])
+def test_qwen3_next_hybrid_gated_deltanet_matches_hf(tmp_path, moe):
+    """Linear-attention layers over the recurrent state pool (chunked prefill + recurrent decode,
+    state carried across prefill chunks) interleaved with gated softmax attention."""
+    from transformers import Qwen3NextConfig, Qwen3NextForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, vocab_size=512, tie_word_embeddings=False,
+               max_position_embeddings=512, partial_rotary_factor=0.25, linear_num_value_heads=4,
+               linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
+               num_experts=8 if moe else 0, num_experts_per_tok=2, moe_intermediate_size=64,
+               shared_expert_intermediate_size=64, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+               layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+               rope_parameters={"rope_theta": 10000.0, "rope_type": "default", "partial_rotary_factor": 0.25})
+    hf = _init(Qwen3NextForCausalLM(Qwen3NextConfig(**cfg)))
+    for n, p in hf.named_parameters():
+        if n.endswith("A_log"):
+            p.data.uniform_(-1.0, 1.0)
+        elif n.endswith("dt_bias"):
+            p.data.uniform_(0.5, 1.5)
+        elif "norm" in n:
+            p.data.normal_(0, 0.1)
+    path = _save(str(tmp_path / "q3n"), hf, dict(cfg, rope_theta=10000.0), "Qwen3NextForCausalLM", "qwen3_next")
+    prompts = [list(range(5, 90)), [9, 8, 7, 6, 5, 4, 3] * 5, [100, 200, 300]]
+    want = _hf_generate(hf, prompts, n=8)
+    assert _generate(path, prompts, n=8) == want
+    # prefill in chunks of 32 tokens: the conv window and the recurrent matrix cross chunk borders
+    assert _generate(path, prompts, n=8, chunked_prefill_size=32) == want
