@@ -420,6 +420,8 @@ class ModelWorkerBatch:
     launch_done: Any = None
     # ids of future-map slots the sampled tokens must be stored to (overlap mode)
     future_slots: np.ndarray | None = None
+    # [T, hidden] embeddings that replace the token embedding lookup (multimodal prefill)
+    input_embeds: Any = None
 
     @property
     def batch_size(self):

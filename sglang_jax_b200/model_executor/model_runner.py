@@ -231,6 +231,8 @@ class ModelRunner:
             per_req = batch.extend_seq_lens if batch.forward_mode.is_extend() else np.ones(len(batch.req_pool_indices), np.int64)
             with lora_batch(self.lora_manager.prepare_batch(batch.lora_ids, per_req)):
                 out = self.model(fb.input_ids, fb)
+        elif getattr(batch, "input_embeds", None) is not None:
+            out = self.model(fb.input_ids, fb, batch.input_embeds.to(self.device, self.dtype))
         else:
             out = self.model(fb.input_ids, fb)
         if skip_sample:

@@ -371,3 +371,25 @@ def test_qwen3_next_hybrid_gated_deltanet_matches_hf(tmp_path, moe):
     assert _generate(path, prompts, n=8) == want
     # prefill in chunks of 32 tokens: the conv window and the recurrent matrix cross chunk borders
     assert _generate(path, prompts, n=8, chunked_prefill_size=32) == want
+
+
+@pytest.mark.parametrize("kind", ["umt5", "t5"])
+def test_t5_family_encoder_matches_hf(tmp_path, kind):
+    import transformers
+    from sglang_jax_b200.models.umt5 import T5EncoderModel, UMT5EncoderModel
+    cfg_cls, hf_cls, mine = (transformers.UMT5Config, transformers.UMT5EncoderModel, UMT5EncoderModel) if kind == "umt5" \
+        else (transformers.T5Config, transformers.T5EncoderModel, T5EncoderModel)
+    cfg = cfg_cls(vocab_size=300, d_model=64, d_kv=16, d_ff=128, num_layers=3, num_heads=4,
+                  relative_attention_num_buckets=32, relative_attention_max_distance=128,
+                  feed_forward_proj="gated-gelu", dropout_rate=0.0)
+    hf = _init(hf_cls(cfg), 0.1)
+    model = mine(cfg, dtype=torch.float32)
+    loaded = model.load_weights(hf.state_dict().items())
+    assert loaded == {n for n, _ in model.named_parameters()}
+    ids = torch.randint(0, 300, (2, 23), generator=torch.Generator().manual_seed(0))
+    mask = torch.ones(2, 23, dtype=torch.long)
+    mask[1, 17:] = 0
+    with torch.no_grad():
+        want = hf(input_ids=ids, attention_mask=mask).last_hidden_state
+    got = model.encode(ids, mask)
+    assert torch.allclose(got[0], want[0], atol=2e-5) and torch.allclose(got[1, :17], want[1, :17], atol=2e-5)

@@ -1,0 +1,202 @@
+"""Multimodal pipeline on CPU: encoder / ViT parity with HF, solver behaviour, and whole
+pipelines (text -> DiT -> VAE, image -> ViT -> LLM) through the global scheduler and the HTTP
+layer (reference tests: `python/sgl_jax/test/multimodal/`)."""
+
+import base64
+import json
+import os
+import threading
+import time
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_qwen2_5_vl_vision_transformer_matches_hf():
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLVisionConfig
+    from transformers.models.qwen2_5_vl.modeling_qwen2_5_vl import Qwen2_5_VisionTransformerPretrainedModel
+    from sglang_jax_b200.multimodal.models.qwen2_5_vl_vit import Qwen2_5_VisionTransformer
+    cfg = Qwen2_5_VLVisionConfig(depth=4, hidden_size=64, intermediate_size=96, num_heads=4, in_channels=3,
+                                 patch_size=4, spatial_merge_size=2, temporal_patch_size=2, window_size=16,
+                                 fullatt_block_indexes=[1, 3], out_hidden_size=48)
+    torch.manual_seed(0)
+    hf = Qwen2_5_VisionTransformerPretrainedModel._from_config(cfg, attn_implementation="sdpa").float().eval()
+    for p in hf.parameters():
+        p.data.normal_(0, 0.08) if p.dim() > 1 else p.data.uniform_(0.5, 1.5)
+    mine = Qwen2_5_VisionTransformer(cfg, dtype=torch.float32)
+    loaded = mine.load_weights(hf.state_dict().items())
+    assert loaded == {n for n, _ in mine.named_parameters()}, set(dict(mine.named_parameters())) - loaded
+    grid = torch.tensor([[1, 6, 10], [1, 4, 4]])
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, 3 * 2 * 4 * 4)
+    with torch.no_grad():
+        want = hf(px, grid_thw=grid).pooler_output
+    got = mine(px, grid)
+    assert got.shape == want.shape == (n // 4, 48)
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+
+
+def test_flow_solvers_converge_on_a_known_velocity_field():
+    """With the exact velocity of a point mass at `x0` (v = (x - x0) / sigma) every flow solver must
+    land on x0, whatever the number of steps; the second-order solver is exact for this field too."""
+    from sglang_jax_b200.multimodal.models.diffusion_solvers import (FlowMatchEulerDiscreteScheduler,
+                                                                       UniPCMultistepScheduler, shifted_sigmas)
+    s = shifted_sigmas(8, 3.0)
+    assert s[0] == 1 and s[-1] == 0 and bool((s[:-1] > s[1:]).all())
+    x0 = torch.tensor([[1.5, -2.0, 0.25]])
+    for cls in (FlowMatchEulerDiscreteScheduler, UniPCMultistepScheduler):
+        for steps in (4, 16):
+            sch = cls(shift=3.0)
+            sch.set_timesteps(steps)
+            x = torch.randn(1, 3, generator=torch.Generator().manual_seed(1))
+            for i in range(steps):
+                sigma = sch.sigmas[i]
+                x = sch.step((x - x0) / sigma, x)
+            assert torch.allclose(x, x0, atol=1e-4), (cls.__name__, steps, x)
+    # a curved field: the multistep solver beats Euler at equal cost
+    def run(cls, steps):
+        sch = cls(shift=1.0)
+        sch.set_timesteps(steps)
+        x = torch.ones(1, 1) * 2.0
+        for i in range(steps):
+            sg = sch.sigmas[i]
+            x0_hat = torch.tanh(x) * (1 - sg) + 0.3            # a smooth, sigma-dependent denoiser
+            x = sch.step((x - x0_hat) / sg, x)
+        return x
+    ref = run(FlowMatchEulerDiscreteScheduler, 2000)
+    e_euler = (run(FlowMatchEulerDiscreteScheduler, 10) - ref).abs().item()
+    e_unipc = (run(UniPCMultistepScheduler, 10) - ref).abs().item()
+    assert e_unipc < e_euler, (e_unipc, e_euler)
+
+
+T5 = dict(vocab_size=259, d_model=32, d_kv=8, d_ff=64, num_layers=2, num_heads=4, relative_attention_num_buckets=32,
+          relative_attention_max_distance=128, layer_norm_epsilon=1e-6, is_gated_act=True, dense_act_fn="gelu_new")
+DIT = dict(in_channels=4, out_channels=4, patch_size=[1, 2, 2], num_attention_heads=2, attention_head_dim=24,
+           ffn_dim=96, num_layers=2, text_dim=32, freq_dim=32)
+VAE = dict(z_dim=4, base_dim=8, dim_mult=[4, 2, 1, 1], temporal_upsample=[True, True, False], out_channels=3,
+           scaling_factor=1.0)
+
+
+@pytest.fixture(scope="module")
+def wan_server():
+    from sglang_jax_b200.multimodal.entrypoint.http_server import MultimodalServer
+    srv = MultimodalServer("Wan-AI/Wan2.1-T2V-1.3B-Diffusers", None, config_overrides={0: T5, 1: DIT, 2: VAE})
+    yield srv
+    srv.shutdown()
+
+
+def test_text_to_video_pipeline_over_http(wan_server):
+    from fastapi.testclient import TestClient
+    from sglang_jax_b200.multimodal.entrypoint.http_server import build_app
+    with TestClient(build_app(wan_server)) as c:
+        h = c.get("/health").json()
+        assert [s["scheduler"] for s in h["stages"]] == ["text_encoder", "diffusion", "vae"]
+        body = {"prompt": "a red fox", "negative_prompt": "blurry", "size": "32x32", "num_frames": 5,
+                "num_inference_steps": 3, "guidance_scale": 3.0, "seed": 7}
+        r = c.post("/api/v1/videos/generation", json=body)
+        assert r.status_code == 200, r.text
+        d = r.json()["data"]
+        assert d["width"] == 32 and d["height"] == 32 and d["num_frames"] == 5
+        png = base64.b64decode(d["b64_png"][0])
+        assert png[:8] == bytes([0x89, 0x50, 0x4E, 0x47, 0x0D, 0x0A, 0x1A, 0x0A])
+        again = c.post("/api/v1/videos/generation", json=body).json()["data"]
+        assert again["b64_png"] == d["b64_png"]                          # seeded: bit-identical
+        other = c.post("/api/v1/videos/generation", json=dict(body, seed=8)).json()["data"]
+        assert other["b64_png"] != d["b64_png"]
+        img = c.post("/api/v1/images/generation", json={"prompt": "x", "size": "16x16", "num_inference_steps": 2})
+        assert img.status_code == 200 and img.json()["data"]["num_frames"] == 1
+        assert c.post("/v1/chat/completions", json={"input_ids": [1]}).status_code == 400     # no llm stage here
+        assert set(r.json()["meta"]["stage_times"]) == {"0", "1", "2"}
+
+
+def test_abort_reaches_the_stage_holding_the_request(wan_server):
+    from sglang_jax_b200.multimodal.manager.io_struct import GenerateMMReqInput
+    import asyncio
+    gs = wan_server.gs
+    diff = gs.stages[1].scheduler
+    orig = diff.model.forward
+    started = threading.Event()
+
+    def slow(*a, **k):
+        started.set()
+        time.sleep(0.05)
+        return orig(*a, **k)
+
+    diff.model.forward = slow
+    try:
+        async def go():
+            obj = GenerateMMReqInput(prompt="p", height=16, width=16, num_inference_steps=200, rid="abort-me")
+            task = asyncio.create_task(wan_server.tok.generate(obj))
+            while not started.is_set():
+                await asyncio.sleep(0.01)
+            assert gs.abort("abort-me")
+            return await asyncio.wait_for(task, 20)
+        before = diff.steps_run
+        out = asyncio.run(go())
+        assert out.error == "aborted" and diff.steps_run - before < 200
+        assert not gs.abort("abort-me")
+    finally:
+        diff.model.forward = orig
+
+
+def test_vision_language_pipeline(tmp_path):
+    """image patches -> ViT stage -> embeddings spliced over placeholder tokens -> LLM stage; the
+    answer must equal running the language model alone on the same spliced embeddings."""
+    from fastapi.testclient import TestClient
+    from sglang_jax_b200.multimodal.entrypoint.http_server import MultimodalServer, build_app
+    from sglang_jax_b200.utils.tiny_models import TINY_QWEN3, write_tiny_qwen3_checkpoint
+    llm = write_tiny_qwen3_checkpoint(str(tmp_path / "llm"), config=dict(TINY_QWEN3, tie_word_embeddings=False))
+    vit = dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+               spatial_merge_size=2, temporal_patch_size=2, window_size=16, fullatt_block_indexes=[1],
+               out_hidden_size=TINY_QWEN3["hidden_size"])
+    srv = MultimodalServer("Qwen/Qwen2.5-VL-7B-Instruct", None,
+                           config_overrides={0: vit, 1: {"model_path": llm, "image_token_id": 900}})
+    try:
+        grid = [[1, 4, 4]]
+        px = torch.randn(16, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(3))
+        ids = [5, 6] + [900] * 4 + [7, 8, 9]
+        with TestClient(build_app(srv)) as c:
+            r = c.post("/v1/chat/completions", json={"input_ids": ids, "pixel_values": px.tolist(),
+                                                     "image_grid_thw": grid, "max_tokens": 6})
+            assert r.status_code == 200, r.text
+            got = r.json()["choices"][0]["message"]["output_ids"]
+            bad = c.post("/v1/chat/completions", json={"input_ids": [5, 900, 7], "pixel_values": px.tolist(),
+                                                       "image_grid_thw": grid})
+            assert bad.status_code == 500 and "placeholder" in bad.json()["error"]["message"]
+        vit_model = srv.gs.stages[0].scheduler.model
+        llm_stage = srv.gs.stages[1].scheduler
+        emb = vit_model(px, torch.tensor(grid))
+        table = llm_stage.runner.model.get_embed_and_head()[0]
+        x = table[torch.tensor(ids)].clone()
+        x[2:6] = emb
+        want = llm_stage.gen.generate(ids, x, 6)
+        assert got == want and len(got) == 6
+        text_only = llm_stage.gen.generate(ids, None, 6)
+        assert text_only != got                               # the image really conditions the answer
+    finally:
+        srv.shutdown()
+
+
+def test_speech_pipeline_roundtrip(tmp_path):
+    from fastapi.testclient import TestClient
+    from sglang_jax_b200.multimodal.entrypoint.http_server import MultimodalServer, build_app
+    from sglang_jax_b200.utils.tiny_models import TINY_QWEN3, write_tiny_qwen3_checkpoint
+    llm = write_tiny_qwen3_checkpoint(str(tmp_path / "llm"))
+    codec = dict(sample_rate=8000, n_mels=20, d_model=32, heads=2, layers=1, num_quantizers=2, codebook_size=64, hop=80)
+    srv = MultimodalServer("XiaomiMiMo/MiMo-Audio", None, config_overrides={
+        0: codec, 1: {"model_path": llm, "audio_token_offset": 300, "codebook_size": 64, "num_quantizers": 2}, 2: codec})
+    try:
+        with TestClient(build_app(srv)) as c:
+            wave = np.sin(np.linspace(0, 200, 4000)).astype("<f4")
+            asr = c.post("/v1/audio/transcriptions", json={"audio_b64": base64.b64encode(wave.tobytes()).decode(),
+                                                           "max_new_tokens": 5})
+            assert asr.status_code == 200 and len(asr.json()["output_ids"]) == 5
+            tts = c.post("/v1/audio/speech", json={"input": "hello", "max_new_tokens": 6})
+            assert tts.status_code == 200 and tts.content[:4] == b"RIFF" and len(tts.content) > 44 + 100
+        tok = srv.gs.stages[0].scheduler.model
+        codes = tok.encode(torch.from_numpy(wave.copy()))
+        assert codes.shape[1] == 2 and int(codes.max()) < 64
+        assert torch.equal(codes, tok.encode(torch.from_numpy(wave.copy())))
+    finally:
+        srv.shutdown()
