@@ -55,6 +55,9 @@ def parse_args():
     ap.add_argument("--disable-fused-comm", action="store_true")
     ap.add_argument("--disable-overlap", action="store_true")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--log-level", default="error")
+    ap.add_argument("--hang-timeout", type=float, default=float(os.environ.get("SGLB_BENCH_HANG_TIMEOUT", "300")),
+                    help="seconds without progress after which every rank dumps its stacks and exits")
     return ap.parse_args()
 
 
@@ -148,6 +151,15 @@ def main():
             raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); "
                              f"WORLD_SIZE={world}")
     device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    # A stuck collective must not burn the whole time limit: without progress for `hang_timeout`
+    # seconds the process prints every thread's stack and exits non-zero.
+    import faulthandler
+
+    def arm():
+        if args.hang_timeout and args.hang_timeout > 0:
+            faulthandler.dump_traceback_later(args.hang_timeout, exit=True)
+
+    arm()
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29511")
     ps.init_distributed(rank, world, device, local_rank=local_rank, init_method="env://" if world > 1 else None)
@@ -166,12 +178,13 @@ def main():
         context_length=cfg["max_position_embeddings"], skip_tokenizer_init=True, enable_single_process=True,
         disable_cuda_graph=args.disable_cuda_graph, disable_fused_comm=args.disable_fused_comm,
         disable_overlap_schedule=args.disable_overlap, cuda_graph_max_bs=args.concurrency,
-        disable_radix_cache=False, log_level="error", watchdog_timeout=0, decode_log_interval=1 << 30,
+        disable_radix_cache=False, log_level=args.log_level, watchdog_timeout=0, decode_log_interval=1 << 30,
         mem_fraction_static=0.9)
 
     if rank != 0:
         from sglang_jax_b200.managers.tp_worker import run_tp_follower
-        run_tp_follower(sa)
+        run_tp_follower(sa, on_message=arm)
+        faulthandler.cancel_dump_traceback_later()
         ps.destroy()
         return 0
 
@@ -218,6 +231,7 @@ def main():
         if batch is None:
             return
         state["steps"] += 1
+        arm()
         now = time.perf_counter()
         if state["phase"] == "timed" and "last_t" in state:
             kind = "decode" if batch.forward_mode.is_decode() else "prefill"
@@ -256,6 +270,7 @@ def main():
     sched.step_hooks.append(hook)
     top_up(sched)
     state["done"].wait()
+    arm()
     clock_info = clocks.stop()
     ms = worker.elapsed_ms_max_over_ranks("t0", "t1")
     sched.step_hooks.remove(hook)
@@ -275,6 +290,7 @@ def main():
         kpg = getattr(gr, "kernels_per_graph", 0)
     gpu_launches = state.get("launches", 0) + state.get("replays", 0) * kpg
 
+    arm()
     # ---------------- phase 2: the same workload through the public API, wall clock
     e2e = None
     if not args.no_e2e:
@@ -324,6 +340,7 @@ def main():
     }
     if args.layers:
         out["invalid"] = "debug run with fewer layers than the named model"
+    faulthandler.cancel_dump_traceback_later()
     print(json.dumps(out), flush=True)
     engine.shutdown()
     ps.destroy()

@@ -192,12 +192,14 @@ def report_elapsed_max(worker: "ModelWorker", start_tag: str, end_tag: str) -> f
     return ms
 
 
-def run_tp_follower(server_args, worker: ModelWorker | None = None):
+def run_tp_follower(server_args, worker: ModelWorker | None = None, on_message=None):
     """Event loop of tensor ranks > 0: execute whatever rank 0 broadcasts."""
     worker = worker or ModelWorker(server_args)
     tp = ps.get_state().tp
     while True:
         msg = ps.broadcast_object(None, src=0, group=tp)
+        if on_message is not None:
+            on_message()          # liveness hook (e.g. re-arm a hang watchdog)
         if isinstance(msg, _Control):
             if msg.kind == "shutdown":
                 break

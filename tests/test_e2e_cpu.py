@@ -125,13 +125,15 @@ def _tp_rank(rank, world, port, ckpt, q):
     ps.destroy()
 
 
-def test_tensor_parallel_2_gloo_matches_oracle(ckpt, oracle):
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_gloo_matches_oracle(ckpt, oracle, world):
+    """world 4 exceeds the model's two KV heads: they are replicated across rank pairs."""
     import torch.multiprocessing as mp
     from sglang_jax_b200.utils.common import get_free_port
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = get_free_port()
-    procs = [ctx.Process(target=_tp_rank, args=(r, 2, port, ckpt, q)) for r in range(2)]
+    procs = [ctx.Process(target=_tp_rank, args=(r, world, port, ckpt, q)) for r in range(world)]
     for p in procs:
         p.start()
     try:
