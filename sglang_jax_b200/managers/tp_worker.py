@@ -13,6 +13,8 @@ import logging
 from dataclasses import dataclass
 from typing import Any
 
+import threading
+
 import numpy as np
 import torch
 
@@ -69,6 +71,10 @@ class ModelWorker:
         self.broadcast_batches = self.tp_size > 1 and self.tp_rank == 0 and not is_draft_worker
         self._pinned_ids = None
         self.marks: dict = {}
+        # Host collectives with the follower ranks are issued from the scheduler thread (batches)
+        # and from API threads (marks, reports, adapter loads): one transaction at a time, or two
+        # threads would interleave collectives on the same process group in different orders.
+        self._comm_lock = threading.RLock()
 
     # ------------------------------------------------------------------
     def get_worker_info(self):
@@ -90,7 +96,8 @@ class ModelWorker:
     def forward_batch_generation(self, batch: ModelWorkerBatch, launch_done=None, skip_sample: bool = False
                                  ) -> GenerationBatchResult:
         if self.broadcast_batches:
-            ps.broadcast_object(batch, src=0, group=ps.get_state().tp)
+            with self._comm_lock:
+                ps.broadcast_object(batch, src=0, group=ps.get_state().tp)
         out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
         res = GenerationBatchResult(out, ids, bid=batch.bid, forward_batch=fb)
         if ids is not None and self.device.type == "cuda":
@@ -116,7 +123,8 @@ class ModelWorker:
 
     def forward_batch_embedding(self, batch: ModelWorkerBatch):
         if self.broadcast_batches:
-            ps.broadcast_object(_Control("embed", batch), src=0, group=ps.get_state().tp)
+            with self._comm_lock:
+                ps.broadcast_object(_Control("embed", batch), src=0, group=ps.get_state().tp)
         batch.capture_hidden_mode = 1
         out, _, _ = self.model_runner.forward(batch, skip_sample=True)
         return out.hidden_states
@@ -127,7 +135,8 @@ class ModelWorker:
         if lm is None:
             return False, "LoRA is not enabled (--enable-lora)"
         if self.broadcast_batches:
-            ps.broadcast_object(_Control("load_lora", recv), src=0, group=ps.get_state().tp)
+            with self._comm_lock:
+                ps.broadcast_object(_Control("load_lora", recv), src=0, group=ps.get_state().tp)
         return lm.load_adapter(LoRARef(lora_id=recv.lora_id, lora_name=recv.lora_name, lora_path=recv.lora_path))
 
     def unload_lora_adapter(self, recv) -> tuple[bool, str]:
@@ -135,12 +144,14 @@ class ModelWorker:
         if lm is None:
             return False, "LoRA is not enabled (--enable-lora)"
         if self.broadcast_batches:
-            ps.broadcast_object(_Control("unload_lora", recv), src=0, group=ps.get_state().tp)
+            with self._comm_lock:
+                ps.broadcast_object(_Control("unload_lora", recv), src=0, group=ps.get_state().tp)
         return lm.unload_adapter(recv.lora_id)
 
     def send_control(self, kind: str, payload=None):
         if self.broadcast_batches:
-            ps.broadcast_object(_Control(kind, payload), src=0, group=ps.get_state().tp)
+            with self._comm_lock:
+                ps.broadcast_object(_Control(kind, payload), src=0, group=ps.get_state().tp)
 
     def flush(self):
         self.send_control("flush")
@@ -150,13 +161,15 @@ class ModelWorker:
 
     def mark(self, tag: str):
         """Record a timing event on this rank's stream and on every follower's."""
-        self.send_control("mark", tag)
-        _sync_all(self.device)
-        self.marks[tag] = _record_event(self.device)
+        with self._comm_lock:
+            self.send_control("mark", tag)
+            _sync_all(self.device)
+            self.marks[tag] = _record_event(self.device)
 
     def elapsed_ms_max_over_ranks(self, start_tag: str, end_tag: str) -> float:
-        self.send_control("report", (start_tag, end_tag))
-        return report_elapsed_max(self, start_tag, end_tag)
+        with self._comm_lock:
+            self.send_control("report", (start_tag, end_tag))
+            return report_elapsed_max(self, start_tag, end_tag)
 
 
 def _sync_all(device):
