@@ -46,7 +46,20 @@ class EngineBase:
 
 
 class Engine(EngineBase):
+    def __new__(cls, **kwargs):
+        # dp_size > 1: a set of replicas behind a router stands in for the engine
+        sa = kwargs.get("server_args")
+        dp = sa.dp_size if sa is not None else int(kwargs.get("dp_size", 1) or 1)
+        if dp > 1 and not kwargs.get("_replica"):
+            from ..managers.data_parallel_controller import DataParallelEngine
+            if sa is None:
+                kwargs.setdefault("log_level", "error")
+                sa = ServerArgs(**{k: v for k, v in kwargs.items() if k != "_replica"})
+            return DataParallelEngine(sa)
+        return super().__new__(cls)
+
     def __init__(self, **kwargs):
+        kwargs.pop("_replica", None)
         if "server_args" in kwargs:
             server_args = kwargs["server_args"]
         else:

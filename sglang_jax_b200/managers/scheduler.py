@@ -945,8 +945,11 @@ def run_scheduler_process(server_args, port_args, pipe_writer=None, rank: int = 
     kill_itself_when_parent_died()
     configure_logger(server_args, prefix=f" TP{rank}")
     try:
-        ps.init_distributed(rank, world_size, server_args.device, server_args.dp_size, server_args.ep_size,
-                            init_method=init_method, local_rank=rank, timeout_s=server_args.dist_timeout)
+        local = rank % max(world_size // max(server_args.nnodes, 1), 1)
+        if server_args.device_indexes:
+            local = server_args.device_indexes[local]
+        ps.init_distributed(rank, world_size, server_args.device, 1, server_args.ep_size,
+                            init_method=init_method, local_rank=local, timeout_s=server_args.dist_timeout)
         if rank != 0:
             from .tp_worker import run_tp_follower
             if pipe_writer is not None:

@@ -47,3 +47,38 @@ def test_eplb_replication_and_packing():
     assert len(set(phy[:, 0].tolist())) > 1          # the hot expert is spread over replicas
     w = torch.arange(8).float().view(8, 1)
     assert loc.physical_weights(w).view(-1).tolist() == [float(x) for x in loc.phy2log]
+
+
+def test_data_parallel_replicas_route_and_match_single_engine(tmp_path):
+    """dp_size=2: two replicas behind the router produce exactly the single-engine outputs, the
+    router spreads the requests, and a pinned `dp_rank` is honoured."""
+    import numpy as np
+    from sglang_jax_b200.entrypoints.engine import Engine
+    from sglang_jax_b200.managers.data_parallel_controller import DataParallelEngine
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import write_tiny_qwen3_checkpoint
+    ckpt = write_tiny_qwen3_checkpoint(str(tmp_path / "m"))
+    rng = np.random.RandomState(0)
+    prompts = [rng.randint(5, 1000, size=n).tolist() for n in (12, 30, 7, 19, 25, 9)]
+    sp = {"temperature": 0.0, "max_new_tokens": 6, "ignore_eos": True}
+    common = dict(model_path=ckpt, device="cpu", enable_single_process=True, page_size=4, skip_tokenizer_init=True,
+                  max_total_tokens=2048, dtype="float32", log_level="error")
+    ps.reset_state()
+    one = Engine(**common)
+    try:
+        want = [o["output_ids"] for o in one.generate(input_ids=prompts, sampling_params=sp)]
+    finally:
+        one.shutdown()
+    ps.reset_state()
+    eng = Engine(**common, dp_size=2, tp_size=2, dp_schedule_policy="round_robin")
+    try:
+        assert isinstance(eng, DataParallelEngine) and len(eng.replicas) == 2
+        outs = eng.generate(input_ids=prompts, sampling_params=sp)
+        assert [o["output_ids"] for o in outs] == want
+        assert [o["meta_info"]["dp_rank"] for o in outs] == [0, 1, 0, 1, 0, 1] and eng.routed == [3, 3]
+        pinned = eng.generate(input_ids=prompts[:2], sampling_params=sp, dp_rank=1)
+        assert [o["meta_info"]["dp_rank"] for o in pinned] == [1, 1]
+        assert eng.generate(input_ids=prompts[0], sampling_params=sp)["output_ids"] == want[0]
+        assert len(eng.get_server_info()["internal_states"]) == 2
+    finally:
+        eng.shutdown()
