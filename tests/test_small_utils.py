@@ -1,0 +1,90 @@
+"""Small utilities: template helpers, tiktoken adapter, trace diff, EPLB tools, named scopes."""
+
+import base64
+import json
+
+import numpy as np
+import pytest
+
+
+def test_template_content_format_and_processing():
+    from sglang_jax_b200.jinja_template_utils import (detect_template_content_format,
+                                                      process_content_for_template_format, render_template)
+    plain = "{% for m in messages %}{{ m.role }}: {{ m.content }}\n{% endfor %}"
+    rich = "{% for m in messages %}{% for c in m.content %}{% if c.type == 'text' %}{{ c.text }}{% endif %}{% endfor %}{% endfor %}"
+    assert detect_template_content_format(plain) == "string" and detect_template_content_format(rich) == "openai"
+    msg = {"role": "user", "content": [{"type": "text", "text": "look"}, {"type": "image_url", "image_url": {"url": "u"}},
+                                       {"type": "text", "text": "here"}]}
+    imgs = []
+    s = process_content_for_template_format(msg, "string", imgs)
+    assert s["content"] == "look here" and imgs == ["u"]
+    o = process_content_for_template_format(msg, "openai")
+    assert [c["type"] for c in o["content"]] == ["text", "image", "text"]
+    assert render_template(plain, messages=[{"role": "user", "content": "hi"}]) == "user: hi\n"
+    from sglang_jax_b200.conversation import Conversation
+    c = Conversation(system="be brief")
+    c.add_message("user", "hi")
+    assert c.get_prompt() == "system: be brief\nuser: hi\nassistant:"
+
+
+def test_tiktoken_adapter(tmp_path):
+    pytest.importorskip("tiktoken")
+    from sglang_jax_b200.utils.tiktoken_tokenizer import TiktokenTokenizer
+    path = tmp_path / "tok.tiktoken"
+    toks = [bytes([i]) for i in range(256)] + [b"he", b"ll", b"hell", b"hello", b" wor", b" world"]
+    path.write_bytes(b"\n".join(base64.b64encode(t) + b" " + str(i).encode() for i, t in enumerate(toks)))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(
+        {"chat_template": "{% for m in messages %}<{{ m.role }}>{{ m.content }}{% endfor %}"}))
+    t = TiktokenTokenizer(str(path))
+    ids = t.encode("hello world")
+    assert ids == [259, 261] and t.decode(ids) == "hello world"
+    assert t.decode(ids + [t.eos_token_id]) == "hello world" and t.vocab_size == 263
+    assert t.apply_chat_template([{"role": "user", "content": "hello"}], tokenize=False) == "<user>hello"
+
+
+def test_trace_diff_finds_first_divergence(tmp_path):
+    from sglang_jax_b200.utils.trace_diff import diff, load, main
+    a, b = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    recs = [{"forward": 0, "stage": "EXTEND", "name": "layer_residual", "layer": i, "mean": 0.1 * i, "std": 1.0,
+             "abs_max": 3.0} for i in range(4)]
+    a.write_text("\n".join(json.dumps(r) for r in recs))
+    recs[2]["std"] = 1.5
+    b.write_text("\n".join(json.dumps(r) for r in recs))
+    rows = diff(load(str(a)), load(str(b)))
+    assert [r["ok"] for r in rows] == [True, True, False, True]
+    assert main([str(a), str(a)]) == 0 and main([str(a), str(b)]) == 1
+
+
+def test_eplb_tools_report_improvement(tmp_path, capsys):
+    from sglang_jax_b200.eplb.tools import device_imbalance, hot_experts, main
+    rng = np.random.RandomState(0)
+    counts = rng.poisson(50, size=(3, 16)).astype(np.float64)
+    counts[:, 0] *= 20                                   # one very hot expert
+    p = tmp_path / "c.npy"
+    np.save(p, counts)
+    assert hot_experts(counts, 2)[0][0][0] == 0
+    assert device_imbalance(counts, 4).min() > 2.0
+    assert main(["rebalance", str(p), "--num-devices", "4", "--redundant", "4"]) == 0
+    out = capsys.readouterr().out
+    before = float(out.split("before: mean device max/mean ")[1].split()[0])
+    after = float(out.split("after : mean device max/mean ")[1].split()[0])
+    assert after < before
+    assert main(["inspect", str(p), "--topk", "3"]) == 0 and main(["hot", str(p), "--num-devices", "4"]) == 0
+
+
+def test_named_scope_and_timeit():
+    from sglang_jax_b200.utils.perf import multiple_iteration_timeit
+    from sglang_jax_b200.utils.profiling_utils import named_scope
+
+    @named_scope
+    def f(x):
+        return x + 1
+
+    @named_scope(name="g-scope")
+    def g(x):
+        return x * 2
+
+    with named_scope("block"):
+        assert f(1) == 2 and g(2) == 4
+    r = multiple_iteration_timeit(lambda: sum(range(1000)), warmup=1, iters=3, device="cpu")
+    assert r["iters"] == 3 and r["min_ms"] <= r["median_ms"]
