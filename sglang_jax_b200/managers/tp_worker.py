@@ -93,9 +93,16 @@ class ModelWorker:
         return self.model_config.sliding_window
 
     # ------------------------------------------------------------------
-    def forward_batch_generation(self, batch: ModelWorkerBatch, launch_done=None, skip_sample: bool = False
-                                 ) -> GenerationBatchResult:
+    def spec_broadcast(self, kind: str, payload) -> None:
+        """Ship one speculative step's host inputs to the follower ranks, which run the same
+        draft / verify sequence on their shards."""
         if self.broadcast_batches:
+            with self._comm_lock:
+                ps.broadcast_object(_Control(kind, payload), src=0, group=ps.get_state().tp)
+
+    def forward_batch_generation(self, batch: ModelWorkerBatch, launch_done=None, skip_sample: bool = False,
+                                 broadcast: bool = True) -> GenerationBatchResult:
+        if self.broadcast_batches and broadcast:
             with self._comm_lock:
                 ps.broadcast_object(batch, src=0, group=ps.get_state().tp)
         out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
@@ -209,6 +216,10 @@ def run_tp_follower(server_args, worker: ModelWorker | None = None, on_message=N
     """Event loop of tensor ranks > 0: execute whatever rank 0 broadcasts."""
     worker = worker or ModelWorker(server_args)
     tp = ps.get_state().tp
+    spec = None
+    if server_args.speculative_algorithm is not None:
+        from ..speculative.spec_info import create_spec_worker
+        spec = create_spec_worker(server_args, worker)
     while True:
         msg = ps.broadcast_object(None, src=0, group=tp)
         if on_message is not None:
@@ -226,6 +237,10 @@ def run_tp_follower(server_args, worker: ModelWorker | None = None, on_message=N
                 worker.marks[msg.payload] = _record_event(worker.device)
             elif msg.kind == "report":
                 report_elapsed_max(worker, *msg.payload)
+            elif msg.kind == "spec_prefill":
+                spec.prefill_core(*msg.payload)
+            elif msg.kind == "spec_decode":
+                spec.decode_core(*msg.payload)
             elif msg.kind == "load_lora":
                 from ..lora.lora_registry import LoRARef
                 r = msg.payload

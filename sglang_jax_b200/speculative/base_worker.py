@@ -71,6 +71,7 @@ class BaseSpecWorker:
         self.greedy_only = False
         self.accept_threshold_single = float(server_args.speculative_accept_threshold_single)
         self.accept_threshold_acc = float(server_args.speculative_accept_threshold_acc)
+        self.pending_deltas = None
         self.gen = torch.Generator(device="cpu")
         self.gen.manual_seed(int(server_args.random_seed or 0) + 7919)
 
@@ -79,7 +80,11 @@ class BaseSpecWorker:
                    extend_prefix_lens: np.ndarray | None, extend_seq_lens: np.ndarray | None,
                    spec: SpecInput, capture_hidden_mode: int, n_tokens: int,
                    input_ids: np.ndarray | None = None, positions: np.ndarray | None = None) -> ModelWorkerBatch:
-        d_rows, d_pos, d_ids = self.req_to_token_pool.take_page_deltas()
+        if self.pending_deltas is not None:
+            d_rows, d_pos, d_ids = self.pending_deltas       # shipped by tensor rank 0 with the step
+            self.pending_deltas = None
+        else:
+            d_rows, d_pos, d_ids = self.req_to_token_pool.take_page_deltas()
         return ModelWorkerBatch(
             bid=_next_bid(), forward_mode=mode,
             input_ids=input_ids if input_ids is not None else np.zeros(n_tokens, np.int32),

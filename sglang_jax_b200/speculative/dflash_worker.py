@@ -61,11 +61,15 @@ class DFlashWorker(EAGLEWorker):
         fb = ForwardBatch.init_new(batch, dw.runner)
         dw.model.materialize_kv(features, fb.positions, fb.out_cache_loc, fb)
 
-    @torch.inference_mode()
     def _prefill(self, batch: ScheduleBatch) -> GenerationBatchResult:
         mwb = batch.get_model_worker_batch()
+        self.target_worker.spec_broadcast("spec_prefill", (mwb, None, False))
+        return self.prefill_core(mwb, None, False)
+
+    @torch.inference_mode()
+    def prefill_core(self, mwb, chunk_next=None, want_hidden: bool = False) -> GenerationBatchResult:
         mwb.capture_hidden_mode = 2
-        res = self.target_worker.forward_batch_generation(mwb)
+        res = self.target_worker.forward_batch_generation(mwb, broadcast=False)
         out = res.logits_output
         feats = self._target_hidden(out)
         self._materialize(np.asarray(mwb.req_pool_indices), np.asarray(mwb.seq_lens), np.asarray(mwb.out_cache_loc),
@@ -78,10 +82,10 @@ class DFlashWorker(EAGLEWorker):
 
     # ------------------------------------------------------------------ decode
     @torch.inference_mode()
-    def _decode(self, batch: ScheduleBatch) -> GenerationBatchResult:
+    def decode_core(self, rows_np, L, tail, deltas, sinfo) -> GenerationBatchResult:
         dw = self.draft_worker
         dev = self.device
-        rows_np, L, tail = self._reserve(batch)
+        self.pending_deltas = deltas
         B, n = len(rows_np), self.block_size
         rows = torch.from_numpy(rows_np.astype(np.int64)).to(dev)
         anchor = dw.state_verified[rows]
@@ -106,7 +110,6 @@ class DFlashWorker(EAGLEWorker):
                              np.full(B, n, np.int32), vspec, 2, B * n)
         out, _, _ = self.target_runner.forward(vb, skip_sample=True)
         logits = out.next_token_logits.view(B, n, -1)
-        sinfo = batch.sampling_info_for_spec()
         if sinfo.is_all_greedy:
             accept, path, bonus = verify_tree_greedy(tokens, parent, logits.argmax(dim=-1), n - 1)
         else:

@@ -64,11 +64,6 @@ class EAGLEWorker(BaseSpecWorker):
     def _prefill(self, batch: ScheduleBatch) -> GenerationBatchResult:
         mwb = batch.get_model_worker_batch()
         assert mwb.num_decode_in_mixed == 0, "mixed chunks are not combined with speculative decoding"
-        want_hidden = batch.return_hidden_states
-        mwb.capture_hidden_mode = 2
-        res = self.target_worker.forward_batch_generation(mwb)
-        out = res.logits_output
-        full_hidden = self._target_hidden(out)
         # the token after a non-final chunk is the next prompt token
         chunk_next = np.full(len(batch.reqs), -1, np.int64)
         for i, r in enumerate(batch.reqs):
@@ -76,7 +71,16 @@ class EAGLEWorker(BaseSpecWorker):
             end = len(r.fill_ids)
             if end < full_len:
                 chunk_next[i] = (r.origin_input_ids + r.output_ids)[end]
-        self.draft_worker.draft_extend_for_prefill(mwb, res.next_token_ids, full_hidden, chunk_next)
+        self.target_worker.spec_broadcast("spec_prefill", (mwb, chunk_next, batch.return_hidden_states))
+        return self.prefill_core(mwb, chunk_next, batch.return_hidden_states)
+
+    @torch.inference_mode()
+    def prefill_core(self, mwb, chunk_next: np.ndarray, want_hidden: bool = False) -> GenerationBatchResult:
+        """Runs on every tensor rank with the same host inputs."""
+        mwb.capture_hidden_mode = 2
+        res = self.target_worker.forward_batch_generation(mwb, broadcast=False)
+        out = res.logits_output
+        self.draft_worker.draft_extend_for_prefill(mwb, res.next_token_ids, self._target_hidden(out), chunk_next)
         if want_hidden and out.hidden_states is not None:
             last = torch.from_numpy(np.cumsum(np.asarray(mwb.extend_seq_lens)) - 1).to(self.device).long()
             out.hidden_states = out.hidden_states[last]
@@ -103,11 +107,19 @@ class EAGLEWorker(BaseSpecWorker):
             r.kv_allocated_len = int(L[b]) + n
         return rows, L, tail
 
-    @torch.inference_mode()
     def _decode(self, batch: ScheduleBatch) -> GenerationBatchResult:
+        rows_np, L, tail = self._reserve(batch)
+        deltas = self.req_to_token_pool.take_page_deltas()
+        sinfo = batch.sampling_info_for_spec()
+        self.target_worker.spec_broadcast("spec_decode", (rows_np, L, tail, deltas, sinfo))
+        return self.decode_core(rows_np, L, tail, deltas, sinfo)
+
+    @torch.inference_mode()
+    def decode_core(self, rows_np, L, tail, deltas, sinfo) -> GenerationBatchResult:
+        """Runs on every tensor rank with the same host inputs (slots were reserved by rank 0)."""
         dw = self.draft_worker
         dev = self.device
-        rows_np, L, tail = self._reserve(batch)
+        self.pending_deltas = deltas
         B = len(rows_np)
         rows = torch.from_numpy(rows_np.astype(np.int64)).to(dev)
         S = self.num_steps
@@ -127,7 +139,6 @@ class EAGLEWorker(BaseSpecWorker):
                              np.full(B, n, np.int32), spec, 2, B * n)
         out, _, _ = self.target_runner.forward(vb, skip_sample=True)
         logits = out.next_token_logits.view(B, n, -1)
-        sinfo = batch.sampling_info_for_spec()
         if sinfo.is_all_greedy:
             target_ids = logits.argmax(dim=-1)
             accept, path, bonus = verify_tree_greedy(tokens, parent, target_ids, S)

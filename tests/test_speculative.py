@@ -193,3 +193,69 @@ def test_dflash_block_draft_keeps_greedy_output(tmp_path, page, block):
         speculative_algorithm="DFLASH", speculative_draft_model_path=draft, speculative_num_draft_tokens=block),
         page=page, chunked_prefill_size=8)
     assert [o["output_ids"] for o in outs] == ref
+
+
+def _spec_tp_rank(rank, world, port, target, draft, algo, q):
+    import os
+    import sys
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.server_args import ServerArgs
+    torch.set_num_threads(2)
+    ps.init_distributed(rank, world, "cpu", init_method=f"tcp://127.0.0.1:{port}", timeout_s=120)
+    sa = ServerArgs(model_path=target, device="cpu", dtype="float32", page_size=4, skip_tokenizer_init=True,
+                    max_total_tokens=2048, enable_single_process=True, tp_size=world, log_level="error",
+                    watchdog_timeout=0, chunked_prefill_size=16, speculative_algorithm=algo,
+                    speculative_draft_model_path=draft, speculative_num_steps=3, speculative_eagle_topk=2,
+                    speculative_num_draft_tokens=6)
+    if rank != 0:
+        from sglang_jax_b200.managers.tp_worker import run_tp_follower
+        run_tp_follower(sa)
+    else:
+        from sglang_jax_b200 import Engine
+        eng = Engine(server_args=sa)
+        prompts = [[3, 17, 42, 9, 5, 11, 8], [4, 4, 19, 23, 99, 100, 101, 102, 103] * 3]
+        outs = eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 16, "temperature": 0.0,
+                                                                 "ignore_eos": True})
+        sampled = eng.generate(input_ids=prompts[:1], sampling_params={"max_new_tokens": 8, "temperature": 0.9,
+                                                                       "ignore_eos": True})
+        q.put(([o["output_ids"] for o in outs], len(sampled[0]["output_ids"])))
+        eng.shutdown()
+    ps.destroy()
+
+
+@pytest.mark.parametrize("algo", ["EAGLE", "STANDALONE"])
+def test_speculative_under_tensor_parallel_2(tmp_path, algo):
+    """Follower ranks mirror every draft / verify forward from the host inputs rank 0 ships."""
+    import torch.multiprocessing as mp
+    from sglang_jax_b200.entrypoints.engine import Engine
+    from sglang_jax_b200.utils.common import get_free_port
+    from sglang_jax_b200.utils.tiny_models import write_tiny_eagle_checkpoint
+    target = _ckpt(tmp_path / "target", 0)
+    draft = write_tiny_eagle_checkpoint(str(tmp_path / "draft")) if algo == "EAGLE" else \
+        _ckpt(tmp_path / "draft", 1, num_hidden_layers=1)
+    prompts = [[3, 17, 42, 9, 5, 11, 8], [4, 4, 19, 23, 99, 100, 101, 102, 103] * 3]
+    _fresh()
+    plain = Engine(model_path=target, device="cpu", enable_single_process=True, page_size=4, skip_tokenizer_init=True,
+                   max_total_tokens=2048, dtype="float32", log_level="error")
+    try:
+        want = [o["output_ids"] for o in plain.generate(input_ids=prompts, sampling_params={
+            "max_new_tokens": 16, "temperature": 0.0, "ignore_eos": True})]
+    finally:
+        plain.shutdown()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = get_free_port()
+    procs = [ctx.Process(target=_spec_tp_rank, args=(r, 2, port, target, draft, algo, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        got, n_sampled = q.get(timeout=300)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    assert got == want and n_sampled == 8
