@@ -97,3 +97,146 @@ class GatedDeltaNet(nn.Module):
                 rec_all[sl[i]] = S
         out = self.norm(o.reshape(-1, self.dv), z.reshape(-1, self.dv)).reshape(T, self.value_dim)
         return self.out_proj(out)
+
+
+class _RecurrentMixer(nn.Module):
+    """Shared plumbing of the recurrent token mixers: per-request state lives in slot `row + 1` of the
+    runner's `RecurrentStatePool`; sequences of an extend batch are stepped one after another, a decode
+    batch in one go."""
+
+    layer_index: int
+
+    def _run(self, fb, T, per_seq, per_batch):
+        pool = fb.extras["recurrent_pool"]
+        conv_all, rec_all = pool.conv_state[self.layer_index], pool.recurrent_state[self.layer_index]
+        slots = fb.req_pool_indices.long() + 1
+        if fb.forward_mode.is_decode():
+            return per_batch(conv_all, rec_all, slots)
+        cu = fb.cu_q_lens.tolist()
+        pre = fb.extend_prefix_lens_cpu
+        outs = []
+        for i, s in enumerate(slots.tolist()):
+            if cu[i + 1] > cu[i]:
+                outs.append(per_seq(conv_all, rec_all, s, cu[i], cu[i + 1], int(pre[i]) == 0))
+        return torch.cat(outs, 0)
+
+
+class KimiDeltaAttention(_RecurrentMixer):
+    """KDA (reference `python/sgl_jax/srt/models/kimi_linear.py:74`, `layers/attention/linear/kda_backend.py`):
+    q/k/v projections followed by short causal convolutions, a per-channel forget gate from a low-rank
+    projection, a scalar write strength `beta`, the delta-rule recurrence and a low-rank output gate
+    through a gated RMSNorm."""
+
+    def __init__(self, config, linear_layer_index: int, dtype):
+        super().__init__()
+        lc = config.linear_attn_config
+        H = config.hidden_size
+        self.nh, self.hd = lc["num_heads"], lc["head_dim"]
+        self.conv_kernel = lc["short_conv_kernel_size"]
+        self.layer_index = linear_layer_index
+        P = self.nh * self.hd
+        self.conv_dim = 3 * P
+        self.q_proj = ReplicatedLinear(H, P, False, dtype)
+        self.k_proj = ReplicatedLinear(H, P, False, dtype)
+        self.v_proj = ReplicatedLinear(H, P, False, dtype)
+        self.q_conv1d_weight = nn.Parameter(torch.empty(P, self.conv_kernel, dtype=dtype), requires_grad=False)
+        self.k_conv1d_weight = nn.Parameter(torch.empty(P, self.conv_kernel, dtype=dtype), requires_grad=False)
+        self.v_conv1d_weight = nn.Parameter(torch.empty(P, self.conv_kernel, dtype=dtype), requires_grad=False)
+        self.A_log = nn.Parameter(torch.zeros(self.nh, dtype=torch.float32), requires_grad=False)
+        self.dt_bias = nn.Parameter(torch.zeros(P, dtype=torch.float32), requires_grad=False)
+        self.f_a_proj = ReplicatedLinear(H, self.hd, False, dtype)
+        self.f_b_proj = ReplicatedLinear(self.hd, P, False, dtype)
+        self.b_proj = ReplicatedLinear(H, self.nh, False, dtype)
+        self.g_a_proj = ReplicatedLinear(H, self.hd, False, dtype)
+        self.g_b_proj = ReplicatedLinear(self.hd, P, False, dtype)
+        self.o_norm = GatedRMSNorm(self.hd, config.rms_norm_eps, dtype)
+        self.o_norm.gate_act = "sigmoid"
+        self.o_proj = ReplicatedLinear(P, H, False, dtype)
+
+    def weight_loader(self, param, w, shard_id=None):
+        param.data.copy_((w.squeeze(1) if w.dim() == 3 else w).reshape(param.shape).to(param.dtype))
+
+    def forward(self, x, fb):
+        T = x.shape[0]
+        nh, hd = self.nh, self.hd
+        mixed = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], -1)
+        w = torch.cat([self.q_conv1d_weight, self.k_conv1d_weight, self.v_conv1d_weight], 0)
+        raw = self.f_b_proj(self.f_a_proj(x)).view(T, nh, hd).float() + self.dt_bias.view(nh, hd)
+        g = -self.A_log.float().exp().view(1, nh, 1) * torch.nn.functional.softplus(raw)
+        beta = torch.sigmoid(self.b_proj(x).float())
+
+        def split(y):
+            q, k, v = y.split(nh * hd, -1)
+            return q.reshape(-1, nh, hd), k.reshape(-1, nh, hd), v.reshape(-1, nh, hd)
+
+        def per_seq(conv_all, rec_all, s, a0, a1, fresh):
+            y, cs = la.causal_conv1d_prefill(mixed[a0:a1], w, None if fresh else conv_all[s])
+            conv_all[s] = cs.to(conv_all.dtype)
+            q, k, v = split(y)
+            init = torch.zeros_like(rec_all[s]) if fresh else rec_all[s]
+            o, S = la.kda_recurrent(q[None], k[None], v[None], g[None, a0:a1], beta[None, a0:a1], init[None])
+            rec_all[s] = S[0]
+            return o[0]
+
+        def per_batch(conv_all, rec_all, slots):
+            y, cs = la.causal_conv1d_update(mixed, conv_all[slots], w)
+            conv_all[slots] = cs.to(conv_all.dtype)
+            q, k, v = split(y)
+            o, S = la.kda_recurrent(q[:, None], k[:, None], v[:, None], g[:, None], beta[:, None], rec_all[slots])
+            rec_all[slots] = S
+            return o[:, 0]
+
+        o = self._run(fb, T, per_seq, per_batch)
+        gate = self.g_b_proj(self.g_a_proj(x)).view(T, nh, hd)
+        of = o.float()
+        y = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + self.o_norm.eps) * self.o_norm.weight.float()
+        y = (y * torch.sigmoid(gate.float())).to(x.dtype)
+        return self.o_proj(y.reshape(T, nh * hd))
+
+
+class LightningAttention(_RecurrentMixer):
+    """Lightning linear attention (reference `layers/attention/linear/lightning_backend.py:86`): SiLU'd
+    q/k/v from one fused projection, a fixed geometric per-head decay scaled by layer depth, RMS-normed
+    output gated by `sigmoid(g_proj(x))`."""
+
+    def __init__(self, config, linear_layer_index: int, layer_id: int, dtype):
+        super().__init__()
+        H = config.hidden_size
+        self.nh = config.num_attention_heads
+        self.hd = getattr(config, "head_dim", None) or H // self.nh
+        self.layer_index = linear_layer_index
+        self.conv_dim, self.conv_kernel = 1, 1
+        P = self.nh * self.hd
+        self.query_key_value = ReplicatedLinear(H, 3 * P, getattr(config, "use_qkv_bias", False), dtype)
+        self.g_proj = ReplicatedLinear(H, P, False, dtype)
+        self.g_norm = nn.Parameter(torch.ones(P, dtype=dtype), requires_grad=False)
+        self.dense = ReplicatedLinear(P, H, getattr(config, "use_bias", False), dtype)
+        n_layers = config.num_hidden_layers
+        scale = 1.0 - layer_id / max(n_layers - 1, 1) + 1e-5
+        self.register_buffer("slopes", la.alibi_slopes(self.nh) * scale, persistent=False)
+        self.eps = config.rms_norm_eps
+
+    def weight_loader(self, param, w, shard_id=None):
+        param.data.copy_(w.reshape(param.shape).to(param.dtype))
+
+    def forward(self, x, fb):
+        T = x.shape[0]
+        nh, hd = self.nh, self.hd
+        qkv = torch.nn.functional.silu(self.query_key_value(x)).view(T, nh, 3 * hd)
+        q, k, v = qkv.split(hd, -1)
+
+        def per_seq(conv_all, rec_all, s, a0, a1, fresh):
+            init = torch.zeros_like(rec_all[s]) if fresh else rec_all[s]
+            o, S = la.lightning_attention(q[None, a0:a1], k[None, a0:a1], v[None, a0:a1], self.slopes, init[None])
+            rec_all[s] = S[0]
+            return o[0]
+
+        def per_batch(conv_all, rec_all, slots):
+            o, S = la.lightning_attention(q[:, None], k[:, None], v[:, None], self.slopes, rec_all[slots])
+            rec_all[slots] = S
+            return o[:, 0]
+
+        o = self._run(fb, T, per_seq, per_batch).reshape(T, nh * hd).float()
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps) * self.g_norm.float()
+        o = (o * torch.sigmoid(self.g_proj(x).float())).to(x.dtype)
+        return self.dense(o)

@@ -80,9 +80,12 @@ class MLAAttention(nn.Module):
         latent = self.kv_a_proj_with_mqa(x)
         kv_c = self.kv_a_layernorm(latent[:, : self.kv_lora].contiguous())
         k_pe = latent[:, self.kv_lora:].unsqueeze(1)
-        cs = self.rotary_emb.cos_sin_cache
-        q_pe = reference.apply_rope(q_pe, fb.positions, cs, False)
-        k_pe = reference.apply_rope(k_pe, fb.positions, cs, False).squeeze(1)
+        if getattr(self, "skip_rope", False):          # position-free MLA (hybrids whose linear layers carry order)
+            k_pe = k_pe.squeeze(1)
+        else:
+            cs = self.rotary_emb.cos_sin_cache
+            q_pe = reference.apply_rope(q_pe, fb.positions, cs, False)
+            k_pe = reference.apply_rope(k_pe, fb.positions, cs, False).squeeze(1)
         pool = fb.token_to_kv_pool
         pool.set_kv_buffer(self.layer_id, fb.out_cache_loc, kv_c, k_pe)
         # absorbed query: [T, h, nope] x [h, nope, r] -> [T, h, r]

@@ -99,3 +99,51 @@ def recurrent_gated_delta_rule_step(q, k, v, g, beta, state):
     S = S + kf[..., None] * d[..., None, :]
     o = (S * qf[..., None]).sum(-2)
     return o.to(v.dtype), S
+
+
+def kda_recurrent(q, k, v, g, beta, state):
+    """Kimi Delta Attention for a batch of sequences stepped together.  `q,k [B, T, H, Dk]`,
+    `v [B, T, H, Dv]`, `g [B, T, H, Dk]` (per-channel log decay), `beta [B, T, H]`,
+    `state [B, H, Dk, Dv]` fp32.  Per step: `S <- diag(exp(g)) S;  S <- S + beta k (v - S^T k)^T;
+    o = S^T (q / sqrt(Dk))`.  q and k are L2-normalised.  Returns `(o [B, T, H, Dv], state)`."""
+    B, T, H, Dk = k.shape
+    qf = l2norm(q.float()) * Dk ** -0.5
+    kf = l2norm(k.float())
+    vf, gf, bf = v.float(), g.float(), beta.float()
+    S = state.float().clone()
+    out = torch.empty(B, T, H, v.shape[-1], dtype=torch.float32, device=v.device)
+    for t in range(T):
+        S = S * gf[:, t].exp().unsqueeze(-1)
+        resid = vf[:, t] - (S * kf[:, t].unsqueeze(-1)).sum(-2)
+        S = S + (bf[:, t, :, None] * kf[:, t]).unsqueeze(-1) * resid.unsqueeze(-2)
+        out[:, t] = (S * qf[:, t].unsqueeze(-1)).sum(-2)
+    return out.to(v.dtype), S
+
+
+def lightning_attention(q, k, v, slopes, state):
+    """Lightning (linear attention with a fixed per-head decay).  `q,k [B, T, H, D]`, `v [B, T, H, Dv]`,
+    `slopes [H]` (decay rate, gamma = exp(-slope)), `state [B, H, D, Dv]`:
+    `S <- gamma S + k v^T;  o = S^T q`."""
+    B, T, H, D = k.shape
+    gamma = torch.exp(-slopes.float()).view(1, H, 1, 1)
+    S = state.float().clone()
+    out = torch.empty(B, T, H, v.shape[-1], dtype=torch.float32, device=v.device)
+    qf, kf, vf = q.float(), k.float(), v.float()
+    for t in range(T):
+        S = S * gamma + kf[:, t].unsqueeze(-1) * vf[:, t].unsqueeze(-2)
+        out[:, t] = (S * qf[:, t].unsqueeze(-1)).sum(-2)
+    return out.to(v.dtype), S
+
+
+def alibi_slopes(num_heads: int) -> torch.Tensor:
+    """The geometric per-head slope sequence Lightning attention uses for its decay."""
+    import math
+
+    def pow2(n):
+        start = 2 ** (-(2 ** -(math.log2(n) - 3)))
+        return [start * start ** i for i in range(n)]
+
+    if math.log2(num_heads).is_integer():
+        return torch.tensor(pow2(num_heads))
+    c = 2 ** math.floor(math.log2(num_heads))
+    return torch.tensor(pow2(c) + pow2(2 * c)[0::2][: num_heads - c])

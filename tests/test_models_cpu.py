@@ -393,3 +393,68 @@ def test_t5_family_encoder_matches_hf(tmp_path, kind):
         want = hf(input_ids=ids, attention_mask=mask).last_hidden_state
     got = model.encode(ids, mask)
     assert torch.allclose(got[0], want[0], atol=2e-5) and torch.allclose(got[1, :17], want[1, :17], atol=2e-5)
+
+
+def _run_dummy(cfg: dict, tmp_path, name: str, prompts, n=6, **kw):
+    """Random-weight model: outputs must not depend on how the prompt was chunked or batched
+    (state hand-over between chunks / decode steps is exact) and must be deterministic."""
+    path = str(tmp_path / name)
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(dict(cfg, torch_dtype="float32"), f)
+    a = _generate(path, prompts, n=n, load_format="dummy", **kw)
+    b = _generate(path, prompts, n=n, load_format="dummy", chunked_prefill_size=32, **kw)
+    c = [_generate(path, [p], n=n, load_format="dummy", **kw)[0] for p in prompts]
+    assert a == b == c, (a, b, c)
+    return a
+
+
+def test_kimi_linear_kda_hybrid_is_chunk_and_batch_invariant(tmp_path):
+    cfg = dict(architectures=["KimiLinearForCausalLM"], model_type="kimi_linear", hidden_size=64, intermediate_size=96,
+               moe_intermediate_size=32, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=4,
+               rms_norm_eps=1e-5, vocab_size=256, max_position_embeddings=512, kv_lora_rank=32, q_lora_rank=None,
+               qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, mla_use_nope=True, num_experts=4,
+               num_experts_per_token=2, num_shared_experts=1, first_k_dense_replace=1, moe_layer_freq=1,
+               moe_router_activation_func="sigmoid", routed_scaling_factor=1.0, tie_word_embeddings=False,
+               linear_attn_config={"kda_layers": [1, 2, 3], "full_attn_layers": [4], "num_heads": 4, "head_dim": 16,
+                                   "short_conv_kernel_size": 4})
+    out = _run_dummy(cfg, tmp_path, "kimi", [list(range(5, 80)), [9, 8, 7, 6] * 3])
+    assert all(len(o) == 6 for o in out)
+
+
+def test_bailing_linear_lightning_hybrid_is_chunk_and_batch_invariant(tmp_path):
+    cfg = dict(architectures=["BailingMoeLinearForCausalLM"], model_type="bailing_moe_linear", hidden_size=64,
+               intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=4, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, vocab_size=256, max_position_embeddings=512,
+               num_experts=4, num_experts_per_tok=2, num_shared_experts=1, first_k_dense_replace=1, n_group=1,
+               topk_group=1, routed_scaling_factor=1.0, score_function="sigmoid", layer_group_size=4,
+               tie_word_embeddings=False, rope_theta=10000.0, partial_rotary_factor=0.5)
+    out = _run_dummy(cfg, tmp_path, "lingl", [list(range(5, 80)), [9, 8, 7, 6] * 3])
+    assert all(len(o) == 6 for o in out)
+
+
+def test_kda_and_lightning_ops_match_stepwise_recurrence():
+    from sglang_jax_b200.ops import linear_attention as la
+    g = torch.Generator().manual_seed(0)
+    B, T, H, D = 2, 9, 3, 8
+    q, k, v = (torch.randn(B, T, H, D, generator=g) for _ in range(3))
+    gate = -torch.rand(B, T, H, D, generator=g)
+    beta = torch.rand(B, T, H, generator=g)
+    S0 = torch.randn(B, H, D, D, generator=g) * 0.1
+    o_all, S_all = la.kda_recurrent(q, k, v, gate, beta, S0)
+    S, outs = S0, []
+    for t in range(T):                       # one step at a time == all steps at once
+        o, S = la.kda_recurrent(q[:, t:t + 1], k[:, t:t + 1], v[:, t:t + 1], gate[:, t:t + 1], beta[:, t:t + 1], S)
+        outs.append(o)
+    assert torch.allclose(torch.cat(outs, 1), o_all, atol=1e-5) and torch.allclose(S, S_all, atol=1e-5)
+    # with a zero gate and beta = 1 the delta rule stores exact key -> value associations
+    kk = torch.nn.functional.normalize(torch.eye(D)[None, :3, None, :].expand(1, 3, 1, D), dim=-1)
+    vv = torch.randn(1, 3, 1, D, generator=g)
+    _, S = la.kda_recurrent(kk, kk, vv, torch.zeros(1, 3, 1, D), torch.ones(1, 3, 1), torch.zeros(1, 1, D, D))
+    assert torch.allclose((S[0, 0] * kk[0, 1, 0].unsqueeze(-1)).sum(0), vv[0, 1, 0], atol=1e-5)
+    slopes = la.alibi_slopes(H)
+    o_all, S_all = la.lightning_attention(q, k, v, slopes, S0)
+    o1, S1 = la.lightning_attention(q[:, :4], k[:, :4], v[:, :4], slopes, S0)
+    o2, S2 = la.lightning_attention(q[:, 4:], k[:, 4:], v[:, 4:], slopes, S1)
+    assert torch.allclose(torch.cat([o1, o2], 1), o_all, atol=1e-5) and torch.allclose(S2, S_all, atol=1e-5)
+    assert la.alibi_slopes(6).shape == (6,)
