@@ -154,7 +154,8 @@ class ModelRunner:
         if mc.attention_arch == AttentionArch.MLA:
             self.token_to_kv_pool = MLATokenToKVPool(self.max_total_num_tokens, self.page_size, self.kv_cache_dtype,
                                                      mc.kv_lora_rank, mc.qk_rope_head_dim, n_layers, str(self.device))
-        elif getattr(self.model, "swa_layer_ids", None) and not sa.disable_hybrid_swa_memory:
+        elif getattr(self.model, "swa_layer_ids", None) and (not sa.disable_hybrid_swa_memory
+                                                            or hasattr(self.model, "swa_kv_shape")):
             swa_ids = self.model.swa_layer_ids
             full_ids = [i for i in range(mc.num_hidden_layers) if i not in set(swa_ids)]
             ratio = sa.swa_full_tokens_ratio
@@ -162,11 +163,11 @@ class ModelRunner:
             swa = max(int(full * ratio) // self.page_size * self.page_size, self.page_size)
             self.token_to_kv_pool = SWAKVPool(full, swa, self.page_size, self.kv_cache_dtype,
                                               mc.get_num_kv_heads(self.tp_size), mc.head_dim, swa_ids, full_ids,
-                                              str(self.device))
+                                              str(self.device), *getattr(self.model, "swa_kv_shape", ()))
         else:
+            heads, dim = getattr(self.model, "kv_shape", None) or (mc.get_num_kv_heads(self.tp_size), mc.head_dim)
             self.token_to_kv_pool = MHATokenToKVPool(self.max_total_num_tokens, self.page_size, self.kv_cache_dtype,
-                                                     mc.get_num_kv_heads(self.tp_size), mc.head_dim, n_layers,
-                                                     str(self.device))
+                                                     heads, dim, n_layers, str(self.device))
         logger.info("KV pool: %d tokens, %.2f GB, max_running_requests=%d", self.max_total_num_tokens,
                     self.token_to_kv_pool.get_kv_size_bytes() / 2 ** 30, max_reqs)
 

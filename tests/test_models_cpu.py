@@ -458,3 +458,24 @@ def test_kda_and_lightning_ops_match_stepwise_recurrence():
     o2, S2 = la.lightning_attention(q[:, 4:], k[:, 4:], v[:, 4:], slopes, S1)
     assert torch.allclose(torch.cat([o1, o2], 1), o_all, atol=1e-5) and torch.allclose(S2, S_all, atol=1e-5)
     assert la.alibi_slopes(6).shape == (6,)
+
+
+def test_mimo_v2_flash_hybrid_swa_sinks_and_narrow_values(tmp_path):
+    cfg = dict(architectures=["MiMoV2FlashForCausalLM"], model_type="mimo_v2_flash", hidden_size=64,
+               intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=4, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, v_head_dim=8, swa_num_attention_heads=4, swa_num_key_value_heads=4,
+               swa_head_dim=16, swa_v_head_dim=8, swa_rope_theta=10000.0, rope_theta=1000000.0,
+               sliding_window_size=24, hybrid_layer_pattern=[0, 1, 1, 0], moe_layer_freq=[0, 1, 1, 1],
+               add_swa_attention_sink_bias=True, add_full_attention_sink_bias=False, attention_value_scale=0.7,
+               partial_rotary_factor=0.5, n_routed_experts=4, num_experts_per_tok=2, scoring_func="sigmoid",
+               topk_method="noaux_tc", norm_topk_prob=True, layernorm_epsilon=1e-5, vocab_size=256,
+               max_position_embeddings=512, tie_word_embeddings=False)
+    out = _run_dummy(cfg, tmp_path, "mimo2", [list(range(5, 80)), [9, 8, 7, 6] * 3])
+    assert all(len(o) == 6 for o in out)
+    from sglang_jax_b200.models.mimo_v2_flash import MiMoV2FlashForCausalLM
+    from types import SimpleNamespace
+    m = MiMoV2FlashForCausalLM(SimpleNamespace(**cfg), dtype=torch.float32)
+    assert m.swa_layer_ids == [1, 2] and m.swa_kv_shape == (4, 16)
+    assert m.model.layers[1].self_attn.attention_sink_bias is not None
+    assert m.model.layers[0].self_attn.attention_sink_bias is None
+    assert m.model.layers[0].self_attn.o_proj.weight.shape[1] == 4 * 8

@@ -259,3 +259,26 @@ def test_speculative_under_tensor_parallel_2(tmp_path, algo):
             if p.is_alive():
                 p.kill()
     assert got == want and n_sampled == 8
+
+
+def test_mimo_v2_nextn_swa_draft_keeps_greedy_output(tmp_path):
+    """Random-weight MiMo-V2 target (hybrid SWA + MoE) with its sliding-window MTP layers as draft."""
+    import json
+    cfg = dict(architectures=["MiMoV2FlashForCausalLM"], model_type="mimo_v2_flash", hidden_size=64,
+               intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=3, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, v_head_dim=8, swa_num_attention_heads=4, swa_num_key_value_heads=4,
+               swa_head_dim=16, swa_v_head_dim=8, swa_rope_theta=10000.0, rope_theta=1000000.0,
+               sliding_window_size=16, hybrid_layer_pattern=[0, 1, 0], moe_layer_freq=[0, 1, 1],
+               add_swa_attention_sink_bias=True, n_routed_experts=4, num_experts_per_tok=2, scoring_func="sigmoid",
+               topk_method="noaux_tc", norm_topk_prob=True, layernorm_epsilon=1e-5, vocab_size=256,
+               max_position_embeddings=512, tie_word_embeddings=False, num_nextn_predict_layers=2,
+               torch_dtype="float32")
+    path = tmp_path / "mimo2"
+    path.mkdir()
+    (path / "config.json").write_text(json.dumps(cfg))
+    prompts = [list(range(3, 40)), [4, 4, 19, 23]]
+    sp = {"temperature": 0.0, "max_new_tokens": 16, "ignore_eos": True}
+    ref, outs = _plain_vs_spec(str(path), prompts, sp, dict(
+        speculative_algorithm="NEXTN", speculative_num_steps=3, speculative_eagle_topk=1,
+        speculative_num_draft_tokens=4), page=4, load_format="dummy")
+    assert [o["output_ids"] for o in outs] == ref
