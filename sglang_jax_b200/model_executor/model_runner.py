@@ -161,8 +161,8 @@ class ModelRunner:
             ratio = sa.swa_full_tokens_ratio
             full = self.max_total_num_tokens
             swa = max(int(full * ratio) // self.page_size * self.page_size, self.page_size)
-            self.token_to_kv_pool = SWAKVPool(full, swa, self.page_size, self.kv_cache_dtype,
-                                              mc.get_num_kv_heads(self.tp_size), mc.head_dim, swa_ids, full_ids,
+            fh, fd = getattr(self.model, "full_kv_shape", None) or (mc.get_num_kv_heads(self.tp_size), mc.head_dim)
+            self.token_to_kv_pool = SWAKVPool(full, swa, self.page_size, self.kv_cache_dtype, fh, fd, swa_ids, full_ids,
                                               str(self.device), *getattr(self.model, "swa_kv_shape", ()))
         else:
             heads, dim = getattr(self.model, "kv_shape", None) or (mc.get_num_kv_heads(self.tp_size), mc.head_dim)

@@ -479,3 +479,34 @@ def test_mimo_v2_flash_hybrid_swa_sinks_and_narrow_values(tmp_path):
     assert m.model.layers[1].self_attn.attention_sink_bias is not None
     assert m.model.layers[0].self_attn.attention_sink_bias is None
     assert m.model.layers[0].self_attn.o_proj.weight.shape[1] == 4 * 8
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_gemma4_text_matches_hf(tmp_path, moe):
+    """Sliding layers (narrow heads, plain RoPE) and global layers (wide heads, proportional RoPE,
+    values taken from the key projection), scale-free V norm, optional routed GeGLU block."""
+    from transformers.models.gemma4 import Gemma4ForCausalLM, Gemma4TextConfig
+    cfg = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, global_head_dim=32, num_global_key_value_heads=1,
+               attention_k_eq_v=True, rms_norm_eps=1e-6, vocab_size=300, tie_word_embeddings=True,
+               max_position_embeddings=512, sliding_window=16, final_logit_softcapping=30.0,
+               hidden_activation="gelu_pytorch_tanh", hidden_size_per_layer_input=0, num_kv_shared_layers=0,
+               layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+               vocab_size_per_layer_input=300)
+    if moe:
+        cfg.update(enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32)
+    hf = _init(Gemma4ForCausalLM(Gemma4TextConfig(**cfg, attn_implementation="eager")))
+    g = torch.Generator().manual_seed(1)
+    for n, b in list(hf.named_buffers()):
+        if n.endswith("layer_scalar"):
+            b.copy_(0.5 + torch.rand(1, generator=g))
+    for n, p in hf.named_parameters():
+        if n.endswith("per_expert_scale") or n.endswith("router.scale"):
+            p.data.copy_(0.5 + torch.rand(p.shape, generator=g))
+    full_cfg = Gemma4TextConfig(**cfg).to_dict()
+    full_cfg.pop("architectures", None)
+    path = _save(str(tmp_path / "gemma4"), hf, full_cfg, "Gemma4ForCausalLM", "gemma4_text")
+    prompts = [list(range(5, 60)), [9, 8, 7, 6, 5, 4, 3] * 5, [100, 200, 250]]
+    want = _hf_generate(hf, prompts, n=10)
+    assert _generate(path, prompts, n=10) == want
+    assert _generate(path, prompts, n=10, chunked_prefill_size=16) == want
