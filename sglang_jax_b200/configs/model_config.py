@@ -101,7 +101,7 @@ class ModelConfig:
         self.head_dim = getattr(c, "head_dim", None) or c.hidden_size // c.num_attention_heads
         self.vocab_size = c.vocab_size
         self.attention_arch = AttentionArch.MHA
-        if getattr(c, "kv_lora_rank", None) and any("Deepseek" in a or "DeepSeek" in a or "Kimi" in a or "Glm5" in a
+        if getattr(c, "kv_lora_rank", None) and any("Deepseek" in a or "DeepSeek" in a or "Kimi" in a or "Glm5" in a or "GlmMoeDsa" in a
                                                     for a in self.architectures):
             self.attention_arch = AttentionArch.MLA
             self.kv_lora_rank = c.kv_lora_rank

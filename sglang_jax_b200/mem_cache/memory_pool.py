@@ -257,7 +257,7 @@ class MLATokenToKVPool(KVCache):
     aligned so no padding is needed)."""
 
     def __init__(self, size, page_size, dtype, kv_lora_rank, qk_rope_head_dim, layer_num, device,
-                 start_layer: int = 0):
+                 start_layer: int = 0, index_head_dim: int = 0):
         super().__init__(size, page_size, dtype, layer_num, device, start_layer)
         self.kv_lora_rank = kv_lora_rank
         self.qk_rope_head_dim = qk_rope_head_dim
@@ -266,13 +266,23 @@ class MLATokenToKVPool(KVCache):
             torch.zeros((self.num_pages, page_size, self.kv_dim), dtype=dtype, device=device)
             for _ in range(layer_num)
         ]
+        # sparse-attention indexer keys (one `index_head_dim` row per token and layer), addressed
+        # by the same slot ids as the latent rows
+        self.index_head_dim = index_head_dim
+        self.index_k_buffer = [
+            torch.zeros((self.num_pages * page_size, index_head_dim), dtype=dtype, device=device)
+            for _ in range(layer_num)
+        ] if index_head_dim else None
 
     @staticmethod
-    def cell_size(kv_lora_rank, qk_rope_head_dim, layer_num, dtype) -> int:
-        return (kv_lora_rank + qk_rope_head_dim) * layer_num * torch.finfo(dtype).bits // 8
+    def cell_size(kv_lora_rank, qk_rope_head_dim, layer_num, dtype, index_head_dim: int = 0) -> int:
+        return (kv_lora_rank + qk_rope_head_dim + index_head_dim) * layer_num * torch.finfo(dtype).bits // 8
 
     def get_kv_size_bytes(self):
-        return sum(b.numel() * b.element_size() for b in self.kv_buffer)
+        return sum(b.numel() * b.element_size() for b in self.kv_buffer + (self.index_k_buffer or []))
+
+    def get_index_k_buffer(self, layer_id):
+        return self.index_k_buffer[layer_id - self.start_layer]
 
     def get_kv_buffer(self, layer_id):
         return self.kv_buffer[layer_id - self.start_layer]

@@ -98,7 +98,8 @@ class ModelRunner:
         kv_dtype = self.kv_cache_dtype
         n_layers = getattr(self.model, "num_kv_layers", None) or mc.num_hidden_layers
         if mc.attention_arch == AttentionArch.MLA:
-            return MLATokenToKVPool.cell_size(mc.kv_lora_rank, mc.qk_rope_head_dim, n_layers, kv_dtype)
+            return MLATokenToKVPool.cell_size(mc.kv_lora_rank, mc.qk_rope_head_dim, n_layers, kv_dtype,
+                                              getattr(self.model, "index_head_dim", 0))
         return MHATokenToKVPool.cell_size(mc.get_num_kv_heads(self.tp_size), mc.head_dim, n_layers, kv_dtype)
 
     def profile_max_num_token(self, free_before: int) -> int:
@@ -153,7 +154,8 @@ class ModelRunner:
         n_layers = getattr(self.model, "num_kv_layers", None) or mc.num_hidden_layers
         if mc.attention_arch == AttentionArch.MLA:
             self.token_to_kv_pool = MLATokenToKVPool(self.max_total_num_tokens, self.page_size, self.kv_cache_dtype,
-                                                     mc.kv_lora_rank, mc.qk_rope_head_dim, n_layers, str(self.device))
+                                                     mc.kv_lora_rank, mc.qk_rope_head_dim, n_layers, str(self.device),
+                                                     index_head_dim=getattr(self.model, "index_head_dim", 0))
         elif getattr(self.model, "swa_layer_ids", None) and (not sa.disable_hybrid_swa_memory
                                                             or hasattr(self.model, "swa_kv_shape")):
             swa_ids = self.model.swa_layer_ids

@@ -52,12 +52,15 @@ class MLAAttention(nn.Module):
         rs = getattr(config, "rope_scaling", None)
         if isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) == "yarn":
             rs = dict(rs, rope_type="deepseek_yarn")
+        # checkpoints store the rotary lanes interleaved; `rope_interleave=False` selects split-half
+        self.rope_neox = not getattr(config, "rope_interleave", True)
         self.rotary_emb = get_rope(self.rope_dim, self.rope_dim, config.max_position_embeddings,
-                                   getattr(config, "rope_theta", 10000.0), False, rs, dtype)
+                                   getattr(config, "rope_theta", 10000.0), self.rope_neox, rs, dtype)
         self.scaling = qk ** -0.5
         if isinstance(rs, dict) and rs.get("factor"):
             m = yarn_get_mscale(rs["factor"], rs.get("mscale_all_dim", 0.0) or 0.0)
             self.scaling = self.scaling * m * m
+        self.select_keys = None
         self.w_uk = None    # [heads, nope, kv_lora]
         self.w_uv = None    # [heads, kv_lora, v]
 
@@ -71,8 +74,10 @@ class MLAAttention(nn.Module):
         T = x.shape[0]
         if self.w_uk is None:
             self.absorb()
+        q_resid = None
         if self.q_lora:
-            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
+            q_resid = self.q_a_layernorm(self.q_a_proj(x))
+            q = self.q_b_proj(q_resid)
         else:
             q = self.q_proj(x)
         q = q.view(T, self.local_heads, self.nope + self.rope_dim)
@@ -84,20 +89,22 @@ class MLAAttention(nn.Module):
             k_pe = k_pe.squeeze(1)
         else:
             cs = self.rotary_emb.cos_sin_cache
-            q_pe = reference.apply_rope(q_pe, fb.positions, cs, False)
-            k_pe = reference.apply_rope(k_pe, fb.positions, cs, False).squeeze(1)
+            q_pe = reference.apply_rope(q_pe, fb.positions, cs, self.rope_neox)
+            k_pe = reference.apply_rope(k_pe, fb.positions, cs, self.rope_neox).squeeze(1)
         pool = fb.token_to_kv_pool
         pool.set_kv_buffer(self.layer_id, fb.out_cache_loc, kv_c, k_pe)
         # absorbed query: [T, h, nope] x [h, nope, r] -> [T, h, r]
         q_lat = torch.einsum("thn,hnr->thr", q_nope.float(), self.w_uk.float()).to(x.dtype)
         buf = pool.get_kv_buffer(self.layer_id)
+        # sparse attention (an indexer picks the keys each query may see); None = dense
+        allowed = self.select_keys(x, q_resid, fb) if self.select_keys is not None else None
         if fb.forward_mode.is_decode():
             o_lat = ops.mla_paged_attention(q_lat, q_pe.contiguous(), buf, fb.page_table, fb.req_pool_indices,
-                                            fb.seq_lens, fb.page_size, self.scaling, self.kv_lora)
+                                            fb.seq_lens, fb.page_size, self.scaling, self.kv_lora, allowed=allowed)
         else:
             o_lat = ops.mla_paged_attention(q_lat, q_pe.contiguous(), buf, fb.page_table, fb.req_pool_indices,
                                             fb.seq_lens, fb.page_size, self.scaling, self.kv_lora, fb.cu_q_lens,
-                                            fb.extend_prefix_lens)
+                                            fb.extend_prefix_lens, allowed=allowed)
         o = torch.einsum("thr,hrv->thv", o_lat.float(), self.w_uv.float()).to(x.dtype)
         return o.reshape(T, self.local_heads * self.v_dim)
 
@@ -129,10 +136,10 @@ class DeepseekMoE(nn.Module):
 
 
 class DeepseekDecoderLayer(nn.Module):
-    def __init__(self, config, layer_id, dtype):
+    def __init__(self, config, layer_id, dtype, attn_cls=None):
         super().__init__()
         eps = config.rms_norm_eps
-        self.self_attn = MLAAttention(config, layer_id, dtype)
+        self.self_attn = (attn_cls or MLAAttention)(config, layer_id, dtype)
         first_dense = getattr(config, "first_k_dense_replace", 0)
         freq = getattr(config, "moe_layer_freq", 1) or 1
         self.is_sparse = (getattr(config, "n_routed_experts", None) is not None and layer_id >= first_dense
@@ -153,10 +160,11 @@ class DeepseekDecoderLayer(nn.Module):
 
 
 class DeepseekModel(nn.Module):
-    def __init__(self, config, dtype):
+    def __init__(self, config, dtype, attn_cls=None):
         super().__init__()
         self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, dtype)
-        self.layers = nn.ModuleList([DeepseekDecoderLayer(config, i, dtype) for i in range(config.num_hidden_layers)])
+        self.layers = nn.ModuleList([DeepseekDecoderLayer(config, i, dtype, attn_cls)
+                                     for i in range(config.num_hidden_layers)])
         self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps, dtype)
 
     def forward(self, input_ids, fb, input_embeds=None):
@@ -172,12 +180,13 @@ class DeepseekModel(nn.Module):
 class DeepseekV3ForCausalLM(nn.Module):
     stacked = [(".gate_up_proj", ".gate_proj", 0), (".gate_up_proj", ".up_proj", 1)]
     optional_params = {"e_score_correction_bias"}
+    attn_cls = None
 
     def __init__(self, config, dtype=torch.bfloat16, quant_config=None):
         super().__init__()
         self.config = config
         self.dtype = dtype
-        self.model = DeepseekModel(config, dtype)
+        self.model = DeepseekModel(config, dtype, self.attn_cls)
         self.lm_head = ParallelLMHead(config.vocab_size, config.hidden_size, dtype)
         self.tie = bool(getattr(config, "tie_word_embeddings", False))
         self.logits_processor = LogitsProcessor(config.vocab_size)

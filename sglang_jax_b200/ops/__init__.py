@@ -115,9 +115,9 @@ def fused_experts(x, w13, w2, topk_weights, topk_ids, expert_start=0, workspace=
 
 
 def mla_paged_attention(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
-                        kv_lora_rank, cu_q_lens=None, prefix_lens=None):
+                        kv_lora_rank, cu_q_lens=None, prefix_lens=None, allowed=None):
     """Absorbed-MLA attention over the latent cache `[pages, P, kv_lora_rank + rope_dim]`."""
-    if use_native(q_latent) and kv_buffer.dtype == torch.bfloat16 and cu_q_lens is None:
+    if use_native(q_latent) and kv_buffer.dtype == torch.bfloat16 and cu_q_lens is None and allowed is None:
         try:
             from . import mla_native
         except ImportError:
@@ -126,4 +126,4 @@ def mla_paged_attention(q_latent, q_pe, kv_buffer, page_table, req_pool_indices,
             return mla_native.mla_decode(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens, page_size,
                                          scale, kv_lora_rank)
     return reference.mla_paged_attention(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens,
-                                         page_size, scale, kv_lora_rank, cu_q_lens, prefix_lens)
+                                         page_size, scale, kv_lora_rank, cu_q_lens, prefix_lens, allowed)

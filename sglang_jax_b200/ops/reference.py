@@ -297,10 +297,11 @@ def grouped_gemm(x, w, group_sizes):
 
 # ----------------------------------------------------------------------------- MLA
 def mla_paged_attention(q_nope_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens,
-                        page_size, scale, kv_lora_rank, cu_q_lens=None, prefix_lens=None):
+                        page_size, scale, kv_lora_rank, cu_q_lens=None, prefix_lens=None, allowed=None):
     """Absorbed MLA: every head attends over the shared latent cache
     `[pages, P, kv_lora_rank + rope_dim]`; logits = q_latent·c + q_pe·k_pe; output stays
-    latent `[T, H, kv_lora_rank]` (caller applies W_UV)."""
+    latent `[T, H, kv_lora_rank]` (caller applies W_UV).  `allowed[b]` (bool `[n_b, S_b]`) restricts
+    request b's queries to the keys a sparse-attention indexer selected."""
     T, H, R = q_nope_latent.shape
     out = torch.empty_like(q_nope_latent)
     B = len(req_pool_indices)
@@ -320,7 +321,10 @@ def mla_paged_attention(q_nope_latent, q_pe, kv_buffer, page_table, req_pool_ind
                   + torch.einsum("nhd,sd->hns", q_pe[q0:q1].float(), kpe)) * scale
         qpos = torch.arange(pre[b], pre[b] + n, device=logits.device).view(n, 1)
         kpos = torch.arange(S, device=logits.device).view(1, S)
-        logits = logits.masked_fill(~(kpos <= qpos).view(1, n, S), float("-inf"))
+        keep = kpos <= qpos
+        if allowed is not None and allowed[b] is not None:      # sparse attention: [n, S] selected keys
+            keep = keep & allowed[b]
+        logits = logits.masked_fill(~keep.view(1, n, S), float("-inf"))
         p = torch.softmax(logits, dim=-1)
         out[q0:q1] = torch.einsum("hns,sr->nhr", p, c).to(out.dtype)
     return out

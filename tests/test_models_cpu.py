@@ -510,3 +510,30 @@ def test_gemma4_text_matches_hf(tmp_path, moe):
     want = _hf_generate(hf, prompts, n=10)
     assert _generate(path, prompts, n=10) == want
     assert _generate(path, prompts, n=10, chunked_prefill_size=16) == want
+
+
+@pytest.mark.parametrize("topk", [8, 4096])
+def test_glm5_dsa_sparse_attention_matches_hf(tmp_path, topk):
+    """GLM-5: latent attention whose keys are picked by the per-layer indexer.  `topk=8` makes the
+    selection bite on every prompt longer than 8 tokens; `topk=4096` is the dense regime."""
+    from transformers.models.glm_moe_dsa import GlmMoeDsaConfig, GlmMoeDsaForCausalLM
+    cfg = dict(hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=3,
+               num_attention_heads=4, num_key_value_heads=4, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=32,
+               qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=3,
+               n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=2.5,
+               mlp_layer_types=["dense", "sparse", "sparse"], rms_norm_eps=1e-6, vocab_size=512,
+               tie_word_embeddings=False, max_position_embeddings=512, attention_bias=False,
+               index_topk=topk, index_head_dim=32, index_n_heads=4,
+               rope_parameters={"rope_type": "default", "rope_theta": 10000.0})
+    hf = _init(GlmMoeDsaForCausalLM(GlmMoeDsaConfig(**cfg, attn_implementation="eager")))
+    for n, b in hf.named_buffers():
+        if "e_score_correction_bias" in n:
+            b.data.normal_(0, 0.1)
+    for n, p in hf.named_parameters():
+        if n.endswith("k_norm.bias"):
+            p.data.normal_(0, 0.1)
+    # the HF port rotates split-half lanes in the main attention; released checkpoints interleave
+    path = _save(str(tmp_path / "glm5"), hf, dict(cfg, rope_interleave=False), "GlmMoeDsaForCausalLM", "glm_moe_dsa")
+    want = _hf_generate(hf, PROMPTS, n=8)
+    assert _generate(path, PROMPTS, n=8) == want
+    assert _generate(path, PROMPTS, n=8, chunked_prefill_size=16) == want
