@@ -200,3 +200,35 @@ def test_speech_pipeline_roundtrip(tmp_path):
         assert torch.equal(codes, tok.encode(torch.from_numpy(wave.copy())))
     finally:
         srv.shutdown()
+
+
+def test_clip_text_and_vision_towers_match_hf():
+    from transformers import CLIPTextConfig, CLIPTextModel as HFText, CLIPVisionConfig, CLIPVisionModel as HFVision
+    from sglang_jax_b200.multimodal.models.clip import CLIPTextModel, CLIPVisionModel
+    torch.manual_seed(0)
+    tc = CLIPTextConfig(vocab_size=120, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                        num_attention_heads=4, max_position_embeddings=32, eos_token_id=2, bos_token_id=1)
+    hf = HFText(tc).float().eval()
+    mine = CLIPTextModel(tc, dtype=torch.float32)
+    loaded = mine.load_weights(hf.state_dict().items())
+    assert loaded == {n for n, _ in mine.named_parameters()}
+    ids = torch.randint(3, 119, (2, 17))
+    ids[0, 9] = 119
+    ids[1, 16] = 119                      # the end-of-text token carries the largest id
+    with torch.no_grad():
+        want = hf(input_ids=ids)
+        got, pooled = mine(ids, return_pooled=True)
+    assert torch.allclose(got, want.last_hidden_state, atol=2e-5)
+    assert torch.allclose(pooled, want.pooler_output, atol=2e-5)
+    vc = CLIPVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                          image_size=32, patch_size=8)
+    hfv = HFVision(vc).float().eval()
+    mv = CLIPVisionModel(vc, dtype=torch.float32)
+    loaded = mv.load_weights(hfv.state_dict().items())
+    assert loaded == {n for n, _ in mv.named_parameters()}
+    px = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        want = hfv(pixel_values=px)
+        got, pooled = mv(px, return_pooled=True)
+    assert torch.allclose(got, want.last_hidden_state, atol=2e-5)
+    assert torch.allclose(pooled, want.pooler_output, atol=2e-5)
