@@ -16,7 +16,9 @@ class DiffusionScheduler(StageScheduler):
 
     def __init__(self, stage_config, devices, model_dir, dtype=torch.bfloat16, config_overrides=None, **kw):
         super().__init__(stage_config, devices, model_dir, dtype)
-        from ...models.dit import FluxTransformer2DModel, WanTransformer3DModel
+        from ...models.dit import WanTransformer3DModel
+        from ...models.flux import FluxTransformer2DModel
+        self._flux_cls = FluxTransformer2DModel
         classes = {"WanTransformer3DModel": WanTransformer3DModel, "FluxTransformer2DModel": FluxTransformer2DModel}
         sub = stage_config.stage_sub_dir or "transformer"
         cfg = load_stage_config(model_dir, sub, config_overrides)
@@ -39,10 +41,19 @@ class DiffusionScheduler(StageScheduler):
             pt, ph, pw = self.model.patch
             T, H, W = max(T // pt, 1) * pt, max(H // ph, 1) * ph, max(W // pw, 1) * pw
             g = torch.Generator().manual_seed(int(d["seed"]))
-            x = torch.randn(1, c.in_channels, T, H, W, generator=g).to(self.device, self.dtype)
+            flux = isinstance(self.model, self._flux_cls)
+            if flux:
+                T = 1                        # an image model: one frame, latents packed 2x2 inside the model
+            x = torch.randn(1, self.model.vae_channels if flux else c.in_channels, T, H, W,
+                            generator=g).to(self.device, self.dtype)
             solver = self.solver_cls(shift=self.shift)
             solver.set_timesteps(int(d["num_inference_steps"]), self.device)
             text = d["text_embeds"][None].to(self.device)
+            extra = {}
+            if flux:
+                if d.get("pooled_text_embeds") is not None:
+                    extra["pooled"] = d["pooled_text_embeds"][None].to(self.device)
+                extra["guidance"] = torch.full((1,), float(d.get("embedded_guidance", 3.5)), device=self.device)
             neg = d.get("negative_text_embeds")
             gs = float(d.get("guidance_scale", 1.0))
             for t in solver.timesteps:
@@ -50,12 +61,12 @@ class DiffusionScheduler(StageScheduler):
                     r.aborted = True
                     break
                 tt = t.reshape(1).to(self.device)
-                v = self.model(x, tt, text)
+                v = self.model(x, tt, text, **extra)
                 if neg is not None and gs != 1.0:
                     L = max(text.shape[1], neg.shape[0])
                     n = torch.zeros(1, L, neg.shape[-1], dtype=neg.dtype, device=self.device)
                     n[0, :neg.shape[0]] = neg
-                    vn = self.model(x, tt, n)
+                    vn = self.model(x, tt, n, **extra)
                     v = vn + gs * (v - vn)
                 x = solver.step(v, x)
                 self.steps_run += 1

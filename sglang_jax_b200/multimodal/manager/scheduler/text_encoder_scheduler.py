@@ -51,10 +51,12 @@ class TextEncoderScheduler(StageScheduler):
         emb = emb * mask.to(self.device)[..., None].to(emb.dtype)          # padded positions carry zeros
         if self.pooled_model is not None:
             for r in reqs:
-                cids = r.data.get("clip_input_ids")
-                if cids is not None:
-                    t = torch.as_tensor(cids, dtype=torch.long, device=self.device).view(1, -1)
-                    r.data["pooled_text_embeds"] = self.pooled_model(t, return_pooled=True)[1][0]
+                # ids from the pooled encoder's own tokenizer when the front end supplied them
+                cids = r.data.get("clip_input_ids") or r.data["input_ids"]
+                pc = self.pooled_model.cfg
+                t = torch.as_tensor(list(cids)[: pc.max_position_embeddings], dtype=torch.long, device=self.device)
+                t = t.clamp_max(pc.vocab_size - 1).view(1, -1)
+                r.data["pooled_text_embeds"] = self.pooled_model(t, return_pooled=True)[1][0]
         k = 0
         for r in reqs:
             r.data["text_embeds"] = emb[k]

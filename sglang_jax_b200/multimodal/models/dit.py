@@ -1,6 +1,6 @@
 """Diffusion transformers: the Wan-style video DiT (self-attention over the 3-D latent patch grid
 with rotary position in (t, h, w), cross-attention to the text tokens, adaLN modulation from the
-timestep) and the Flux-style image DiT (reference `multimodal/models/wan`, `multimodal/models/dits`).
+timestep; reference `multimodal/models/wan`).  The Flux image DiT lives in `flux.py`.
 
 Attention here is dense and bidirectional; projections and FFNs are `ops.linear`, i.e. the
 tcgen05 GEMM on a GPU."""
@@ -159,8 +159,4 @@ class WanTransformer3DModel(nn.Module):
         return loaded
 
 
-class FluxTransformer2DModel(WanTransformer3DModel):
-    """Image DiT: the same joint text-conditioned block stack run on a single-frame grid."""
-
-
-EntryClass = [WanTransformer3DModel, FluxTransformer2DModel]
+EntryClass = [WanTransformer3DModel]

@@ -232,3 +232,111 @@ def test_clip_text_and_vision_towers_match_hf():
         got, pooled = mv(px, return_pooled=True)
     assert torch.allclose(got, want.last_hidden_state, atol=2e-5)
     assert torch.allclose(pooled, want.pooler_output, atol=2e-5)
+
+
+FLUX = dict(in_channels=16, num_layers=2, num_single_layers=2, attention_head_dim=16, num_attention_heads=2,
+            joint_attention_dim=32, pooled_projection_dim=24, guidance_embeds=True, axes_dims_rope=[4, 6, 6])
+
+
+def test_flux_dit_structure():
+    from types import SimpleNamespace
+    from sglang_jax_b200.multimodal.model_executor.loading import init_dummy
+    from sglang_jax_b200.multimodal.models.flux import FluxTransformer2DModel, rope_nd
+    m = init_dummy(FluxTransformer2DModel(SimpleNamespace(**FLUX), dtype=torch.float32), seed=3, std=0.05).eval()
+    names = {n for n, _ in m.named_parameters()}
+    for n in ("x_embedder.weight", "context_embedder.bias", "time_text_embed.guidance_embedder.linear_2.weight",
+              "time_text_embed.text_embedder.linear_1.weight", "transformer_blocks.1.norm1_context.linear.weight",
+              "transformer_blocks.0.attn.norm_added_k.weight", "transformer_blocks.0.attn.to_add_out.bias",
+              "transformer_blocks.0.ff_context.net.0.proj.weight", "transformer_blocks.0.ff.net.2.bias",
+              "single_transformer_blocks.1.proj_mlp.weight", "single_transformer_blocks.0.attn.norm_q.weight",
+              "single_transformer_blocks.0.proj_out.weight", "norm_out.linear.weight", "proj_out.bias"):
+        assert n in names, n                                       # the published checkpoint's tensor names
+    assert m.single_transformer_blocks[0].proj_out.weight.shape == (32, 5 * 32)
+    g = torch.Generator().manual_seed(0)
+    lat = torch.randn(2, 4, 1, 8, 12, generator=g)
+    text = torch.randn(2, 5, 32, generator=g)
+    pooled = torch.randn(2, 24, generator=g)
+    t = torch.tensor([500.0, 20.0])
+    v = m(lat, t, text, pooled, torch.tensor([3.5, 1.0]))
+    assert v.shape == lat.shape and torch.isfinite(v).all()
+    # batch rows are independent and each conditioning input matters
+    v0 = m(lat[:1], t[:1], text[:1], pooled[:1], torch.tensor([3.5]))
+    assert torch.allclose(v0, v[:1], atol=1e-5)
+    assert not torch.allclose(m(lat[:1], t[:1], text[:1], pooled[1:], torch.tensor([3.5])), v0, atol=1e-4)
+    assert not torch.allclose(m(lat[:1], t[:1], text[:1], pooled[:1], torch.tensor([1.0])), v0, atol=1e-4)
+    assert not torch.allclose(m(lat[:1], t[:1], text[1:], pooled[:1], torch.tensor([3.5])), v0, atol=1e-4)
+    # text tokens sit at the rotary origin: their order only matters through the text weights, so
+    # permuting them permutes nothing in the image output
+    perm = torch.tensor([3, 0, 4, 1, 2])
+    assert torch.allclose(m(lat[:1], t[:1], text[:1, perm], pooled[:1], torch.tensor([3.5])), v0, atol=1e-5)
+    # zero output gates (adaLN-zero at initialisation) make every block the identity
+    saved = {}
+    for n, p in m.named_parameters():
+        if n.endswith("norm1.linear.weight") or n.endswith("norm1.linear.bias") or ".norm.linear." in n:
+            saved[n] = p.data.clone()
+            p.data.zero_()
+    x_only = m(lat[:1], t[:1], text[:1], pooled[:1], torch.tensor([3.5]))
+    other_text = m(lat[:1], t[:1], text[1:], pooled[:1], torch.tensor([3.5]))
+    assert torch.allclose(x_only, other_text, atol=1e-6)           # the image stream never saw the text
+    cos, sin = rope_nd(torch.tensor([[0., 0., 0.], [0., 2., 5.]]), (4, 6, 6))
+    assert cos.shape == (2, 8) and torch.allclose(cos[0], torch.ones(8)) and torch.allclose(sin[0], torch.zeros(8))
+    assert torch.allclose(cos[1, :2], torch.ones(2))               # first band follows axis 0, which is 0 here
+
+
+def test_flux_text_to_image_pipeline_with_pooled_clip_prompt(tmp_path):
+    import json
+    from fastapi.testclient import TestClient
+    from sglang_jax_b200.multimodal.entrypoint.http_server import MultimodalServer, build_app
+    (tmp_path / "text_encoder").mkdir()
+    (tmp_path / "text_encoder" / "config.json").write_text(json.dumps(dict(
+        vocab_size=300, hidden_size=24, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+        max_position_embeddings=16, layer_norm_eps=1e-5, hidden_act="quick_gelu", eos_token_id=2)))
+    t5 = dict(T5, d_model=32)
+    vae = dict(latent_channels=4, block_out_channels=[8, 16, 16, 16], layers_per_block=1, norm_num_groups=4,
+               scaling_factor=0.36, shift_factor=0.11)
+    srv = MultimodalServer("black-forest-labs/FLUX.1-dev", str(tmp_path), config_overrides={0: t5, 1: FLUX, 2: vae})
+    try:
+        assert srv.gs.stages[0].scheduler.pooled_model is not None
+        with TestClient(build_app(srv)) as c:
+            body = {"prompt": "a lighthouse at dusk", "size": "32x32", "num_inference_steps": 2, "seed": 3}
+            r = c.post("/api/v1/images/generation", json=body)
+            assert r.status_code == 200, r.text
+            d = r.json()["data"]
+            assert d["num_frames"] == 1 and d["width"] == 32
+            assert c.post("/api/v1/images/generation", json=body).json()["data"]["b64_png"] == d["b64_png"]
+            other = c.post("/api/v1/images/generation", json=dict(body, prompt="a harbour at dawn")).json()["data"]
+            assert other["b64_png"] != d["b64_png"]
+    finally:
+        srv.shutdown()
+
+
+def test_autoencoder_kl_names_shapes_and_roundtrip_scaling():
+    from types import SimpleNamespace
+    from sglang_jax_b200.multimodal.model_executor.loading import init_dummy
+    from sglang_jax_b200.multimodal.models.vae import AutoencoderKL
+    cfg = SimpleNamespace(latent_channels=4, block_out_channels=[8, 16, 32], layers_per_block=2, norm_num_groups=4,
+                          scaling_factor=0.5, shift_factor=0.25, use_quant_conv=True, use_post_quant_conv=True)
+    m = init_dummy(AutoencoderKL(cfg), seed=5, std=0.1).eval()
+    names = {n for n, _ in m.named_parameters()}
+    for n in ("encoder.conv_in.weight", "encoder.down_blocks.0.downsamplers.0.conv.weight",
+              "encoder.down_blocks.1.resnets.0.conv_shortcut.weight", "encoder.mid_block.attentions.0.to_q.weight",
+              "encoder.mid_block.attentions.0.group_norm.weight", "encoder.conv_out.bias", "quant_conv.weight",
+              "post_quant_conv.bias", "decoder.up_blocks.0.resnets.2.conv2.weight",
+              "decoder.up_blocks.1.upsamplers.0.conv.weight", "decoder.up_blocks.2.resnets.0.conv_shortcut.weight",
+              "decoder.mid_block.resnets.1.norm2.weight", "decoder.conv_norm_out.weight"):
+        assert n in names, n
+    assert "encoder.down_blocks.2.downsamplers.0.conv.weight" not in names       # the last level keeps its size
+    px = torch.rand(2, 3, 32, 24) * 2 - 1
+    z = m.encode(px)
+    assert z.shape == (2, 4, 8, 6) and m.spatial_factor == 4
+    out = m.decode(z)
+    assert out.shape == (2, 3, 32, 24) and out.abs().max() <= 1
+    # scaling: decode undoes (x - shift) * scale before the decoder sees the latent
+    raw = (z / 0.5 + 0.25)
+    assert torch.allclose(m.decoder(m.post_quant_conv(raw)).clamp(-1, 1), out, atol=1e-6)
+    vid = m.decode(torch.stack([z, z], dim=2))                                  # frames decode independently
+    assert vid.shape == (2, 3, 2, 32, 24) and torch.allclose(vid[:, :, 0], out, atol=1e-6)
+    sd = {k.replace(".to_q.", ".query."): v for k, v in m.state_dict().items()}
+    m2 = AutoencoderKL(cfg)
+    assert m2.load_weights(sd.items()) == names
+    assert torch.allclose(m2.decode(z), out, atol=1e-6)
