@@ -42,6 +42,19 @@ class RadixAttention(nn.Module):
         rope = ops.rope_qknorm_kvwrite if not native_backend else reference.rope_qknorm_kvwrite
         attn = ops.paged_attention if not native_backend else reference.paged_attention
         eps = q_norm.variance_epsilon if q_norm is not None else 1e-6
+        mpos = fb.extras.get("mrope_positions") if hasattr(rotary_emb, "mrope_section") else None
+        if mpos is not None:
+            # multimodal rotary: the frequency lanes are driven by three position streams, so the
+            # rotation is applied here and the fused kernel only normalises and writes the cache
+            qs, ks = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+            q3 = qkv[:, :qs].reshape(-1, self.num_heads, self.head_dim)
+            k3 = qkv[:, qs:qs + ks].reshape(-1, self.num_kv_heads, self.head_dim)
+            if q_norm is not None:
+                q3, k3 = q_norm(q3), k_norm(k3)
+                q_norm = k_norm = None
+            q3, k3 = rotary_emb(mpos, q3, k3)
+            qkv = torch.cat([q3.flatten(1), k3.flatten(1), qkv[:, qs + ks:]], dim=-1)
+            rotary_emb = None
         q = rope(qkv, fb.positions,
                  rotary_emb.cos_sin_cache if rotary_emb is not None else None,
                  q_norm.weight if q_norm is not None else None,

@@ -39,6 +39,9 @@ class GenerateReqInput:
     image_data: Any = None
     video_data: Any = None
     audio_data: Any = None
+    # per request: {"input_embedding": [prompt_len, hidden], "mrope_positions": [3, prompt_len],
+    # "mrope_position_delta": int} produced by an encoder stage (one dict, or a list for a batch)
+    mm_inputs: list[dict] | dict | None = None
     sampling_params: list[dict] | dict | None = None
     rid: list[str] | str | None = None
     return_logprob: list[bool] | bool | None = None
@@ -140,6 +143,7 @@ class GenerateReqInput:
         else:
             self.token_ids_logprob = per_item(self.token_ids_logprob, None)
         self.lora_path = per_item(self.lora_path, None)
+        self.mm_inputs = per_item(self.mm_inputs, None)
         self.lora_id = per_item(self.lora_id, None)
         self.extra_key = per_item(self.extra_key, None)
         self.return_routed_experts = per_item(self.return_routed_experts, False)
@@ -158,6 +162,7 @@ class GenerateReqInput:
             text=self.text[i] if self.text is not None else None,
             input_ids=self.input_ids[i] if self.input_ids is not None else None,
             input_embeds=self.input_embeds[i] if self.input_embeds is not None else None,
+            mm_inputs=g(self.mm_inputs),
             sampling_params=self.sampling_params[i],
             rid=self.rid[i],
             return_logprob=g(self.return_logprob),

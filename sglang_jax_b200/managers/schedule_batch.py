@@ -126,8 +126,11 @@ class Req:
                  return_hidden_states: bool = False, return_routed_experts: bool = False,
                  return_output_logprob_only: bool = False, logprob_start_len: int = -1,
                  session_id: str | None = None, bootstrap_host=None, bootstrap_port=None,
-                 bootstrap_room=None):
+                 bootstrap_room=None, mm_inputs: dict | None = None):
         self.rid = rid
+        # encoder-stage products: "input_embedding" [prompt_len, hidden], "mrope_positions"
+        # [3, prompt_len], "mrope_position_delta" (3-D position minus token index after the prompt)
+        self.mm_inputs = mm_inputs
         self.origin_input_text = origin_input_text
         self.origin_input_ids = list(origin_input_ids)
         self.origin_input_ids_unpadded = origin_input_ids_unpadded or self.origin_input_ids
@@ -420,8 +423,12 @@ class ModelWorkerBatch:
     launch_done: Any = None
     # ids of future-map slots the sampled tokens must be stored to (overlap mode)
     future_slots: np.ndarray | None = None
-    # [T, hidden] embeddings that replace the token embedding lookup (multimodal prefill)
+    # [T, hidden] embeddings that replace the token embedding lookup (multimodal prefill);
+    # with `input_embeds_rows` (bool [T]) only the marked rows are replaced
     input_embeds: Any = None
+    input_embeds_rows: np.ndarray | None = None
+    # i32 [3, T] (temporal, height, width) positions for multimodal rotary embeddings
+    mrope_positions: np.ndarray | None = None
 
     @property
     def batch_size(self):
@@ -795,6 +802,7 @@ class ScheduleBatch:
             pre = ext = None
             positions = (self.seq_lens - 1).astype(np.int32)
         rows, pos, ids = self.req_to_token_pool.take_page_deltas()
+        mm_embeds, mm_rows, mrope = self._multimodal_inputs(positions)
         sinfo = ModelWorkerSamplingInfo.from_reqs(self.reqs, self.vocab_size)
         if self.penalizer is not None:
             sinfo.linear_penalty = self.penalizer.linear_penalty(self.reqs)
@@ -814,7 +822,47 @@ class ScheduleBatch:
             num_decode_in_mixed=self.num_decode_in_mixed,
             spec_info=self.spec_info, spec_algorithm=self.spec_algorithm,
             dp_rank=self.dp_rank, real_bs=len(self.reqs),
+            input_embeds=mm_embeds, input_embeds_rows=mm_rows, mrope_positions=mrope,
         )
+
+    def _multimodal_inputs(self, positions: np.ndarray):
+        """Per-token encoder embeddings and 3-D rotary positions of the requests that carry
+        `mm_inputs` (reference `schedule_batch.py:2139-2230`).  Prompt tokens take their slice of
+        the request's arrays; generated tokens advance all three position streams together from
+        `token index + mrope_position_delta`."""
+        if not any(getattr(r, "mm_inputs", None) for r in self.reqs):
+            return None, None, None
+        import torch
+        T = len(positions)
+        mrope = np.repeat(positions[None, :].astype(np.int32), 3, axis=0)
+        embeds, rows = None, np.zeros(T, bool)
+        if self.forward_mode.is_extend():
+            offs = np.concatenate([[0], np.cumsum(self.extend_lens)]).astype(int)
+            spans = [(int(offs[i]), int(self.prefix_lens[i]), int(self.extend_lens[i])) for i in range(len(self.reqs))]
+        else:
+            spans = [(i, int(self.seq_lens[i]) - 1, 1) for i in range(len(self.reqs))]
+        for r, (off, start, n) in zip(self.reqs, spans):
+            mm = getattr(r, "mm_inputs", None)
+            if not mm:
+                continue
+            plen = len(r.origin_input_ids)
+            mp = mm.get("mrope_positions")
+            delta = int(mm.get("mrope_position_delta", 0) or 0)
+            for j in range(n):
+                p = start + j
+                if mp is not None and p < plen:
+                    mrope[:, off + j] = np.asarray(mp)[:, p]
+                else:
+                    mrope[:, off + j] = p + delta
+            emb = mm.get("input_embedding")
+            if emb is not None and start < plen and self.forward_mode.is_extend():
+                emb = torch.as_tensor(emb)
+                m = min(n, plen - start)
+                if embeds is None:
+                    embeds = torch.zeros(T, emb.shape[-1], dtype=emb.dtype)
+                embeds[off:off + m] = emb[start:start + m]
+                rows[off:off + m] = True
+        return embeds, (rows if embeds is not None else None), mrope
 
     def copy(self) -> "ScheduleBatch":
         """Shallow snapshot used by the overlap loop to process results one step late."""

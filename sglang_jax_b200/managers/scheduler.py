@@ -391,7 +391,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                   return_output_logprob_only=bool(recv.return_output_logprob_only),
                   logprob_start_len=recv.logprob_start_len if recv.logprob_start_len is not None else -1,
                   session_id=recv.session_id, bootstrap_host=recv.bootstrap_host,
-                  bootstrap_port=recv.bootstrap_port, bootstrap_room=recv.bootstrap_room)
+                  bootstrap_port=recv.bootstrap_port, bootstrap_room=recv.bootstrap_room,
+                  mm_inputs=recv.mm_inputs)
         req.tokenizer = self.tokenizer
         if req.lora_id is not None and not self.server_args.enable_lora:
             return self._reject(req, "LoRA is not enabled on this server (--enable-lora).")

@@ -222,7 +222,7 @@ class TokenizerManager:
             return_routed_experts=bool(obj.return_routed_experts), return_hidden_states=obj.return_hidden_states,
             dp_rank=obj.dp_rank, bootstrap_host=obj.bootstrap_host, bootstrap_port=obj.bootstrap_port,
             bootstrap_room=obj.bootstrap_room, disagg_prefill_dp_rank=obj.disagg_prefill_dp_rank,
-            disagg_transfer_id=obj.disagg_transfer_id)
+            disagg_transfer_id=obj.disagg_transfer_id, mm_inputs=obj.mm_inputs)
 
     def _send_one_request(self, obj, tokenized, created) -> ReqState:
         state = ReqState([], False, asyncio.Event(), obj, created)

@@ -137,7 +137,7 @@ class CudaGraphRunner:
                 and (si is None or (si.is_all_greedy and si.linear_penalty is None and si.vocab_mask is None
                                     and si.logit_bias is None))
                 and (batch.page_delta_rows is None or len(batch.page_delta_rows) <= MAX_PAGE_DELTAS)
-                and not any(batch.lora_ids or []))
+                and not any(batch.lora_ids or []) and getattr(batch, "mrope_positions", None) is None)
 
     def replay(self, batch: ModelWorkerBatch):
         r = self.runner

@@ -141,6 +141,9 @@ class ForwardBatch:
         )
         if getattr(runner, "recurrent_pool", None) is not None:
             fb.extras["recurrent_pool"] = runner.recurrent_pool
+        if getattr(batch, "mrope_positions", None) is not None:
+            fb.extras["mrope_positions"] = torch.from_numpy(np.ascontiguousarray(batch.mrope_positions)).to(
+                runner.device, non_blocking=True)
         pool = runner.token_to_kv_pool
         if hasattr(pool, "swa_pool") and B:
             # sliding-window layers live in their own (smaller) pool: translate the rows' pages

@@ -235,7 +235,13 @@ class ModelRunner:
             with lora_batch(self.lora_manager.prepare_batch(batch.lora_ids, per_req)):
                 out = self.model(fb.input_ids, fb)
         elif getattr(batch, "input_embeds", None) is not None:
-            out = self.model(fb.input_ids, fb, batch.input_embeds.to(self.device, self.dtype))
+            emb = batch.input_embeds.to(self.device, self.dtype)
+            if getattr(batch, "input_embeds_rows", None) is not None and not batch.input_embeds_rows.all():
+                # rows without encoder embeddings (other requests of the batch) use the token table
+                embed = getattr(self.model, "embed_input_ids", None) or self.model.model.embed_tokens
+                rows = torch.from_numpy(batch.input_embeds_rows).to(self.device)
+                emb = torch.where(rows[:, None], emb, embed(fb.input_ids).to(emb.dtype))
+            out = self.model(fb.input_ids, fb, emb)
         else:
             out = self.model(fb.input_ids, fb)
         if skip_sample:

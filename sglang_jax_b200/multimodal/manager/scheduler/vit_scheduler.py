@@ -49,6 +49,7 @@ class LLMStageScheduler(StageScheduler):
         from ....server_args import ServerArgs
         ov = dict(config_overrides or {})
         self.image_token_id = int(ov.pop("image_token_id", 151655))
+        self.spatial_merge_size = int(ov.pop("spatial_merge_size", 2))
         path = ov.pop("model_path", None) or model_dir
         if not ps.get_state().initialized:
             ps.init_distributed(0, 1, str(self.device))
@@ -59,6 +60,8 @@ class LLMStageScheduler(StageScheduler):
         self.runner = ModelRunner(ModelConfig.from_server_args(sa), sa, self.device)
         from ...model_executor.llm_runner import EmbedsGenerator
         self.gen = EmbedsGenerator(self.runner)
+        # a language model with multimodal rotary embeddings wants 3-D positions for image tokens
+        self.uses_mrope = any(hasattr(m, "mrope_section") for m in self.runner.model.modules())
 
     @torch.inference_mode()
     def run_batch(self, reqs):
@@ -75,5 +78,12 @@ class LLMStageScheduler(StageScheduler):
                     raise ValueError(f"{where.numel()} image placeholder tokens for {img.shape[0]} image embeddings")
                 x[where] = img.to(x.dtype).to(x.device)
             sp = r.data.get("sampling_params") or {}
+            mpos, delta = None, 0
+            if img is not None and self.uses_mrope and r.data.get("image_grid_thw") is not None:
+                from ..mrope_utils import get_rope_index
+                mpos, delta = get_rope_index(ids, image_grid_thw=r.data["image_grid_thw"],
+                                             image_token_id=self.image_token_id,
+                                             spatial_merge_size=self.spatial_merge_size)
             r.data["output_ids"] = self.gen.generate(ids, x, int(sp.get("max_new_tokens", 16)),
-                                                     float(sp.get("temperature", 0.0)))
+                                                     float(sp.get("temperature", 0.0)), mrope_positions=mpos,
+                                                     mrope_delta=delta)

@@ -40,7 +40,8 @@ class EmbedsGenerator:
 
     @torch.inference_mode()
     def generate(self, input_ids: list[int], input_embeds: torch.Tensor | None, max_new_tokens: int = 16,
-                 temperature: float = 0.0, eos_ids: set[int] | None = None) -> list[int]:
+                 temperature: float = 0.0, eos_ids: set[int] | None = None,
+                 mrope_positions: np.ndarray | None = None, mrope_delta: int = 0) -> list[int]:
         r = self.runner
         row = 0
         self.next_page = 1
@@ -56,7 +57,8 @@ class EmbedsGenerator:
             positions=np.arange(n, dtype=np.int32), extend_prefix_lens=np.zeros(1, np.int32),
             extend_seq_lens=np.asarray([n], np.int32), extend_logprob_start_lens=np.zeros(1, np.int32),
             page_delta_rows=rows, page_delta_pos=pos, page_delta_ids=ids, sampling_info=self._sinfo(temperature),
-            input_embeds=input_embeds)
+            input_embeds=input_embeds,
+            mrope_positions=None if mrope_positions is None else np.asarray(mrope_positions, np.int32))
         _, tok, _ = r.forward(batch)
         out = [int(tok[0])]
         eos_ids = eos_ids or set()
@@ -68,7 +70,8 @@ class EmbedsGenerator:
                 bid=2, forward_mode=ForwardMode.DECODE, input_ids=np.asarray([out[-1]], np.int32),
                 req_pool_indices=np.asarray([row], np.int32), seq_lens=np.asarray([cur + 1], np.int32),
                 out_cache_loc=loc, positions=np.asarray([cur], np.int32), page_delta_rows=rows, page_delta_pos=pos,
-                page_delta_ids=ids, sampling_info=self._sinfo(temperature))
+                page_delta_ids=ids, sampling_info=self._sinfo(temperature),
+                mrope_positions=None if mrope_positions is None else np.full((3, 1), cur + mrope_delta, np.int32))
             _, tok, _ = r.forward(batch)
             out.append(int(tok[0]))
         return out

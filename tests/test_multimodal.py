@@ -340,3 +340,67 @@ def test_autoencoder_kl_names_shapes_and_roundtrip_scaling():
     m2 = AutoencoderKL(cfg)
     assert m2.load_weights(sd.items()) == names
     assert torch.allclose(m2.decode(z), out, atol=1e-6)
+
+
+def test_qwen2_5_vl_image_prompt_matches_hf_through_the_engine(tmp_path):
+    """ViT embeddings spliced over the image placeholders + 3-D rotary positions, served by the
+    main scheduler (chunked prefill, a text-only request in the same batch) == HF generate."""
+    from safetensors.torch import save_file
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration as HF
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.multimodal.manager.mrope_utils import get_rope_index
+    from sglang_jax_b200.multimodal.models.qwen2_5_vl_vit import Qwen2_5_VisionTransformer
+    from sglang_jax_b200.parallel import state as ps
+    IMG, VS, VE = 290, 291, 292
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=2, vocab_size=300, max_position_embeddings=512, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, rope_parameters={"rope_type": "default", "mrope_section": [2, 3, 3],
+                                                            "rope_theta": 10000.0})
+    vis = dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+               spatial_merge_size=2, temporal_patch_size=2, window_size=16, fullatt_block_indexes=[1],
+               out_hidden_size=64, tokens_per_second=1)
+    cfg = Qwen2_5_VLConfig(text_config=text, vision_config=vis, image_token_id=IMG, video_token_id=293,
+                           vision_start_token_id=VS, vision_end_token_id=VE, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = HF(cfg).float().eval()
+    for p in hf.parameters():
+        p.data.normal_(0, 0.08) if p.dim() > 1 else p.data.uniform_(0.8, 1.2)
+    path = tmp_path / "qwen25vl"
+    path.mkdir()
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(path / "model.safetensors"))
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen2_5_VLForConditionalGeneration"]
+    d["torch_dtype"] = "float32"
+    (path / "config.json").write_text(json.dumps(d))
+    grid = torch.tensor([[1, 4, 6]])                       # 24 patches -> 6 merged tokens
+    px = torch.randn(24, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    ids = [5, 9, 33, VS] + [IMG] * 6 + [VE, 41, 42, 7, 8]
+    n_new = 8
+    with torch.no_grad():
+        want = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, image_grid_thw=grid,
+                           max_new_tokens=n_new, do_sample=False)[0, len(ids):].tolist()
+        want_text = hf.generate(input_ids=torch.tensor([[3, 4, 5, 6, 7, 8, 9]]), max_new_tokens=n_new,
+                                do_sample=False)[0, 7:].tolist()
+    vit = Qwen2_5_VisionTransformer(cfg.vision_config, dtype=torch.float32)
+    vit.load_weights(hf.state_dict().items())
+    img = vit(px, grid)
+    assert img.shape == (6, 64)
+    table = hf.state_dict()["model.language_model.embed_tokens.weight"]
+    emb = table[torch.tensor(ids)].clone()
+    emb[torch.tensor(ids) == IMG] = img
+    pos, delta = get_rope_index(ids, image_grid_thw=grid, image_token_id=IMG, spatial_merge_size=2)
+    assert pos[:, 3].tolist() == [3, 3, 3] and pos[:, 4].tolist() == [4, 4, 4] and pos[:, 9].tolist() == [4, 5, 6]
+    assert pos[:, 10].tolist() == [7, 7, 7] and delta == 7 + 5 - len(ids)
+    mm = {"input_embedding": emb, "mrope_positions": pos, "mrope_position_delta": delta}
+    sp = {"max_new_tokens": n_new, "temperature": 0, "ignore_eos": True}
+    for chunk in (None, 8):
+        ps.reset_state()
+        eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=4, skip_tokenizer_init=True,
+                     max_total_tokens=1024, enable_single_process=True, chunked_prefill_size=chunk,
+                     disable_radix_cache=True)
+        try:
+            outs = eng.generate(input_ids=[ids, [3, 4, 5, 6, 7, 8, 9]], sampling_params=sp, mm_inputs=[mm, None])
+            assert outs[0]["output_ids"] == want, (chunk, outs[0]["output_ids"], want)
+            assert outs[1]["output_ids"] == want_text
+        finally:
+            eng.shutdown()
