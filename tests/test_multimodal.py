@@ -404,3 +404,64 @@ def test_qwen2_5_vl_image_prompt_matches_hf_through_the_engine(tmp_path):
             assert outs[1]["output_ids"] == want_text
         finally:
             eng.shutdown()
+
+
+def test_qwen3_omni_audio_encoder_matches_hf():
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeAudioEncoderConfig
+    from transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe import Qwen3OmniMoeAudioEncoder as HF
+    from sglang_jax_b200.multimodal.models.qwen3_omni.audio_encoder import Qwen3OmniMoeAudioEncoder, feat_lengths
+    cfg = Qwen3OmniMoeAudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=2, encoder_attention_heads=4,
+                                         encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=24,
+                                         max_source_positions=64, n_window=50, n_window_infer=200, conv_chunksize=4)
+    torch.manual_seed(0)
+    hf = HF._from_config(cfg, attn_implementation="eager").float().eval()
+    for p in hf.parameters():
+        p.data.normal_(0, 0.1) if p.dim() > 1 else p.data.uniform_(-0.2, 0.2)
+    mine = Qwen3OmniMoeAudioEncoder(cfg, dtype=torch.float32).eval()
+    assert mine.load_weights(hf.state_dict().items()) == {n for n, _ in mine.named_parameters()}
+    # the HF port only windows its attention on the flash-attention path; one clip inside one window
+    # is where its eager path and the windowed model agree
+    lens = torch.tensor([157])
+    feats = torch.randn(16, 157, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(feats, feature_lens=lens).last_hidden_state
+    got = mine(feats, lens)
+    assert got.shape == want.shape == (int(feat_lengths(lens).sum()), 24)
+    assert torch.allclose(got, want, atol=2e-5), (got - want).abs().max()
+    # clips packed together do not see each other, and a long clip attends within its windows
+    lens2 = torch.tensor([157, 330])
+    feats2 = torch.cat([feats, torch.randn(16, 330, generator=torch.Generator().manual_seed(2))], dim=1)
+    both = mine(feats2, lens2)
+    assert both.shape[0] == int(feat_lengths(lens2).sum())
+    assert torch.allclose(both[: got.shape[0]], got, atol=1e-5)
+    long_alone = mine(feats2[:, 157:], lens2[1:])
+    assert torch.allclose(both[got.shape[0]:], long_alone, atol=1e-5)
+    first_window = mine(feats2[:, 157:357], torch.tensor([200]))           # 200 frames = one attention window
+    assert torch.allclose(long_alone[:26], first_window, atol=1e-5)
+
+
+def test_qwen3_omni_vision_encoder_matches_hf():
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeVisionEncoderConfig
+    from transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe import Qwen3OmniMoeVisionEncoder as HF
+    from sglang_jax_b200.multimodal.models.qwen3_omni.vision_encoder import Qwen3OmniMoeVisionEncoder
+    cfg = Qwen3OmniMoeVisionEncoderConfig(depth=3, hidden_size=32, intermediate_size=48, num_heads=4, in_channels=3,
+                                          patch_size=4, spatial_merge_size=2, temporal_patch_size=2,
+                                          out_hidden_size=40, num_position_embeddings=36,
+                                          deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh")
+    torch.manual_seed(0)
+    hf = HF._from_config(cfg, attn_implementation="sdpa").float().eval()
+    for p in hf.parameters():
+        p.data.normal_(0, 0.08) if p.dim() > 1 else p.data.uniform_(-0.3, 0.3)
+    mine = Qwen3OmniMoeVisionEncoder(cfg, dtype=torch.float32).eval()
+    assert mine.load_weights(hf.state_dict().items()) == {n for n, _ in mine.named_parameters()}
+    grid = torch.tensor([[1, 6, 10], [2, 4, 4]])               # an image and a two-frame clip
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(px, grid_thw=grid)
+    got, deep = mine(px, grid, return_deepstack=True)
+    assert got.shape == want.pooler_output.shape == (n // 4, 40)
+    assert torch.allclose(got, want.pooler_output, atol=2e-4), (got - want.pooler_output).abs().max()
+    assert len(deep) == 2
+    for a, b in zip(deep, want.deepstack_features):
+        assert torch.allclose(a, b, atol=2e-4)
