@@ -198,8 +198,12 @@ class MRotaryEmbedding(RotaryEmbedding):
     the frequency lanes are partitioned into `mrope_section` groups, each driven by one of the
     three position streams."""
 
-    def __init__(self, head_size, rotary_dim, max_pos, base, is_neox_style, dtype, mrope_section):
+    def __init__(self, head_size, rotary_dim, max_pos, base, is_neox_style, dtype, mrope_section,
+                 interleaved: bool = False):
         self.mrope_section = mrope_section
+        # interleaved layout (Qwen3-VL / Qwen3-Omni): lanes cycle T, H, W, T, H, W, ... while a
+        # stream still has lanes left in its section; the remainder follows the temporal stream
+        self.mrope_interleaved = interleaved
         super().__init__(head_size, rotary_dim, max_pos, base, is_neox_style, dtype)
 
     def forward(self, positions, q, k):
@@ -208,12 +212,19 @@ class MRotaryEmbedding(RotaryEmbedding):
         cs = self.cos_sin_cache[positions.long()]            # [3, T, rd]
         half = self.rotary_dim // 2
         cos, sin = cs[..., :half], cs[..., half:]
-        parts_c, parts_s, o = [], [], 0
-        for i, n in enumerate(self.mrope_section):
-            parts_c.append(cos[i, :, o:o + n])
-            parts_s.append(sin[i, :, o:o + n])
-            o += n
-        cos, sin = torch.cat(parts_c, -1).unsqueeze(1), torch.cat(parts_s, -1).unsqueeze(1)
+        if self.mrope_interleaved:
+            cos, sin = cos[0].clone(), sin[0].clone()
+            for i, off in ((1, 1), (2, 2)):
+                sl = slice(off, self.mrope_section[i] * 3, 3)
+                cos[:, sl], sin[:, sl] = cs[i, :, :half][:, sl], cs[i, :, half:][:, sl]
+            cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+        else:
+            parts_c, parts_s, o = [], [], 0
+            for i, n in enumerate(self.mrope_section):
+                parts_c.append(cos[i, :, o:o + n])
+                parts_s.append(sin[i, :, o:o + n])
+                o += n
+            cos, sin = torch.cat(parts_c, -1).unsqueeze(1), torch.cat(parts_s, -1).unsqueeze(1)
 
         def rot(x):
             xf = x[..., : self.rotary_dim].float()
@@ -244,7 +255,8 @@ def get_rope(head_size, rotary_dim, max_position, base, is_neox_style=True, rope
             rope = ProportionalRotaryEmbedding(head_size, rotary_dim, max_position, base, is_neox_style, dtype,
                                                partial_rotary_factor)
         elif "mrope_section" in rs:
-            rope = MRotaryEmbedding(head_size, rotary_dim, max_position, base, is_neox_style, dtype, rs["mrope_section"])
+            rope = MRotaryEmbedding(head_size, rotary_dim, max_position, base, is_neox_style, dtype, rs["mrope_section"],
+                                    bool(rs.get("mrope_interleaved", False)))
         else:
             rope = RotaryEmbedding(head_size, rotary_dim, max_position, base, is_neox_style, dtype)
     elif kind == "llama3":

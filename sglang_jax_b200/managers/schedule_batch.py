@@ -429,6 +429,8 @@ class ModelWorkerBatch:
     input_embeds_rows: np.ndarray | None = None
     # i32 [3, T] (temporal, height, width) positions for multimodal rotary embeddings
     mrope_positions: np.ndarray | None = None
+    # [L, T, hidden]: vision features added to the residual stream after each of the first L layers
+    deepstack_embeds: Any = None
 
     @property
     def batch_size(self):
@@ -802,7 +804,7 @@ class ScheduleBatch:
             pre = ext = None
             positions = (self.seq_lens - 1).astype(np.int32)
         rows, pos, ids = self.req_to_token_pool.take_page_deltas()
-        mm_embeds, mm_rows, mrope = self._multimodal_inputs(positions)
+        mm_embeds, mm_rows, mrope, deepstack = self._multimodal_inputs(positions)
         sinfo = ModelWorkerSamplingInfo.from_reqs(self.reqs, self.vocab_size)
         if self.penalizer is not None:
             sinfo.linear_penalty = self.penalizer.linear_penalty(self.reqs)
@@ -822,7 +824,7 @@ class ScheduleBatch:
             num_decode_in_mixed=self.num_decode_in_mixed,
             spec_info=self.spec_info, spec_algorithm=self.spec_algorithm,
             dp_rank=self.dp_rank, real_bs=len(self.reqs),
-            input_embeds=mm_embeds, input_embeds_rows=mm_rows, mrope_positions=mrope,
+            input_embeds=mm_embeds, input_embeds_rows=mm_rows, mrope_positions=mrope, deepstack_embeds=deepstack,
         )
 
     def _multimodal_inputs(self, positions: np.ndarray):
@@ -831,9 +833,10 @@ class ScheduleBatch:
         the request's arrays; generated tokens advance all three position streams together from
         `token index + mrope_position_delta`."""
         if not any(getattr(r, "mm_inputs", None) for r in self.reqs):
-            return None, None, None
+            return None, None, None, None
         import torch
         T = len(positions)
+        deep = None
         mrope = np.repeat(positions[None, :].astype(np.int32), 3, axis=0)
         embeds, rows = None, np.zeros(T, bool)
         if self.forward_mode.is_extend():
@@ -862,7 +865,13 @@ class ScheduleBatch:
                     embeds = torch.zeros(T, emb.shape[-1], dtype=emb.dtype)
                 embeds[off:off + m] = emb[start:start + m]
                 rows[off:off + m] = True
-        return embeds, (rows if embeds is not None else None), mrope
+                ds = mm.get("deepstack")                  # [L, prompt_len, hidden], zero off the vision tokens
+                if ds is not None:
+                    ds = torch.as_tensor(ds)
+                    if deep is None:
+                        deep = torch.zeros(ds.shape[0], T, ds.shape[-1], dtype=ds.dtype)
+                    deep[:, off:off + m] = ds[:, start:start + m]
+        return embeds, (rows if embeds is not None else None), mrope, deep
 
     def copy(self) -> "ScheduleBatch":
         """Shallow snapshot used by the overlap loop to process results one step late."""

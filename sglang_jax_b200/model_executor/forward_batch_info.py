@@ -141,6 +141,8 @@ class ForwardBatch:
         )
         if getattr(runner, "recurrent_pool", None) is not None:
             fb.extras["recurrent_pool"] = runner.recurrent_pool
+        if getattr(batch, "deepstack_embeds", None) is not None:
+            fb.extras["deepstack"] = batch.deepstack_embeds.to(runner.device, runner.dtype)
         if getattr(batch, "mrope_positions", None) is not None:
             fb.extras["mrope_positions"] = torch.from_numpy(np.ascontiguousarray(batch.mrope_positions)).to(
                 runner.device, non_blocking=True)

@@ -114,6 +114,11 @@ class DenseModel(nn.Module):
                 aux.append(residual)
             nxt = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
             h, residual = layer(h, residual, forward_batch, nxt)
+            deep = forward_batch.extras.get("deepstack")
+            if deep is not None and i < deep.shape[0]:
+                # vision features join the residual stream after the first layers (deep-stack)
+                residual = residual + deep[i].to(residual.dtype)
+                h = nxt(residual)
             if tracing:
                 precision_tracer.record(residual, "layer_residual", forward_batch.forward_mode.name, i)
                 precision_tracer.record(h, "layer_output_normed", forward_batch.forward_mode.name, i)

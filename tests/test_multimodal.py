@@ -465,3 +465,79 @@ def test_qwen3_omni_vision_encoder_matches_hf():
     assert len(deep) == 2
     for a, b in zip(deep, want.deepstack_features):
         assert torch.allclose(a, b, atol=2e-4)
+
+
+def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
+    """Audio + image + text prompt: my encoders feed the MoE language model (interleaved 3-stream
+    rotary, deep-stack features after the first layers) through the engine == HF thinker generate."""
+    from safetensors.torch import save_file
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeThinkerConfig
+    from transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe import (
+        Qwen3OmniMoeThinkerForConditionalGeneration as HF)
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.multimodal.models.qwen3_omni.audio_encoder import Qwen3OmniMoeAudioEncoder, feat_lengths
+    from sglang_jax_b200.multimodal.models.qwen3_omni.vision_encoder import Qwen3OmniMoeVisionEncoder
+    from sglang_jax_b200.parallel import state as ps
+    IMG, AUD = 290, 291
+    text = dict(hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=16, vocab_size=300, num_experts=4,
+                num_experts_per_tok=2, norm_topk_prob=True, max_position_embeddings=512, rms_norm_eps=1e-6,
+                rope_parameters={"rope_type": "default", "mrope_section": [3, 3, 2], "rope_theta": 10000.0,
+                                 "mrope_interleaved": True})
+    vis = dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=4, in_channels=3, patch_size=4,
+               spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=64, num_position_embeddings=36,
+               deepstack_visual_indexes=[0, 1])
+    aud = dict(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=4, encoder_ffn_dim=64,
+               downsample_hidden_size=8, output_dim=64, max_source_positions=64, n_window=50, n_window_infer=200)
+    cfg = Qwen3OmniMoeThinkerConfig(text_config=text, vision_config=vis, audio_config=aud, image_token_id=IMG,
+                                    audio_token_id=AUD, video_token_id=292, audio_start_token_id=293,
+                                    vision_start_token_id=294, position_id_per_seconds=25)
+    torch.manual_seed(0)
+    hf = HF._from_config(cfg, attn_implementation="eager").float().eval()
+    for p in hf.parameters():
+        p.data.normal_(0, 0.08) if p.dim() > 1 else p.data.uniform_(0.8, 1.2)
+    path = tmp_path / "omni"
+    path.mkdir()
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(path / "model.safetensors"))
+    d = cfg.to_dict()
+    d.update(architectures=["Qwen3OmniMoeThinkerForConditionalGeneration"], torch_dtype="float32")
+    (path / "config.json").write_text(json.dumps(d))
+    grid = torch.tensor([[1, 4, 6]])
+    px = torch.randn(24, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    n_frames = 157
+    n_aud = int(feat_lengths(torch.tensor([n_frames])))
+    feats = torch.randn(1, 16, n_frames, generator=torch.Generator().manual_seed(2))
+    ids = [5, 9, 293] + [AUD] * n_aud + [33, 294] + [IMG] * 6 + [41, 42, 7]
+    n_new = 6
+    inp = torch.tensor([ids])
+    kw = dict(input_ids=inp, attention_mask=torch.ones_like(inp), pixel_values=px, image_grid_thw=grid,
+              input_features=feats, feature_attention_mask=torch.ones(1, n_frames, dtype=torch.long))
+    with torch.no_grad():
+        want = hf.generate(**kw, max_new_tokens=n_new, do_sample=False)[0, len(ids):].tolist()
+        pos, delta = hf.get_rope_index(inp, grid, None, torch.ones_like(inp), False, torch.tensor([n_frames]), None)
+    sd = hf.state_dict()
+    vit = Qwen3OmniMoeVisionEncoder(cfg.vision_config, dtype=torch.float32)
+    vit.load_weights(sd.items())
+    enc = Qwen3OmniMoeAudioEncoder(cfg.audio_config, dtype=torch.float32)
+    enc.load_weights(sd.items())
+    img, deep = vit(px, grid, return_deepstack=True)
+    audio = enc(feats[0], torch.tensor([n_frames]))
+    t = torch.tensor(ids)
+    emb = sd["model.embed_tokens.weight"][t].clone()
+    emb[t == IMG], emb[t == AUD] = img, audio
+    ds = torch.zeros(len(deep), len(ids), 64)
+    for i, f in enumerate(deep):
+        ds[i, t == IMG] = f
+    mm = {"input_embedding": emb, "mrope_positions": pos[:, 0].numpy(), "mrope_position_delta": int(delta[0]),
+          "deepstack": ds}
+    sp = {"max_new_tokens": n_new, "temperature": 0, "ignore_eos": True}
+    for chunk in (None, 16):
+        ps.reset_state()
+        eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=4, skip_tokenizer_init=True,
+                     max_total_tokens=1024, enable_single_process=True, chunked_prefill_size=chunk,
+                     disable_radix_cache=True)
+        try:
+            out = eng.generate(input_ids=ids, sampling_params=sp, mm_inputs=mm)
+            assert out["output_ids"] == want, (chunk, out["output_ids"], want)
+        finally:
+            eng.shutdown()
