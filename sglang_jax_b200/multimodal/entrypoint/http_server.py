@@ -122,14 +122,15 @@ def build_app(server: MultimodalServer) -> FastAPI:
 
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
-        if (r := need("llm")) is not None:
+        if "auto_regressive" not in server.kinds and (r := need("llm")) is not None:
             return r
         b = await request.json()
         rid = b.get("rid") or uuid.uuid4().hex
         sp = {"max_new_tokens": int(b.get("max_tokens", 16)), "temperature": float(b.get("temperature", 0.0))}
         out = await server._await(rid, lambda: server.gs.submit(TokenizedGenerateOmniReqInput(
             rid, list(b["input_ids"]), np.asarray(b["pixel_values"], np.float32) if b.get("pixel_values") is not None else None,
-            np.asarray(b["image_grid_thw"]) if b.get("image_grid_thw") is not None else None, None, sp)))
+            np.asarray(b["image_grid_thw"]) if b.get("image_grid_thw") is not None else None,
+            np.asarray(b["audio_features"], np.float32) if b.get("audio_features") is not None else None, sp)))
         if out.error:
             return fail(out)
         return {"id": out.rid, "object": "chat.completion",

@@ -41,10 +41,12 @@ def _build_scheduler(stage_cfg, devices, model_dir, overrides):
     from .scheduler.vae_scheduler import VaeScheduler
     from .scheduler.vit_scheduler import LLMStageScheduler, VitScheduler
     from .scheduler.audio_scheduler import AudioBackboneScheduler, AudioDecoderScheduler, AudioEncoderScheduler
+    from .scheduler.omni_scheduler import AutoRegressiveStageScheduler, EmbeddingStageScheduler
     table = {"text_encoder": TextEncoderScheduler, "encoder": TextEncoderScheduler, "diffusion": DiffusionScheduler,
              "vae": VaeScheduler, "vit": VitScheduler, "llm": LLMStageScheduler, "embed": VitScheduler,
              "audio_encoder": AudioEncoderScheduler, "audio_backbone": AudioBackboneScheduler,
-             "audio_decoder": AudioDecoderScheduler, "audio": AudioEncoderScheduler}
+             "audio_decoder": AudioDecoderScheduler, "audio": AudioEncoderScheduler,
+             "embedding": EmbeddingStageScheduler, "auto_regressive": AutoRegressiveStageScheduler}
     if stage_cfg.scheduler not in table:
         raise ValueError(f"unknown stage scheduler {stage_cfg.scheduler!r}")
     return table[stage_cfg.scheduler](stage_cfg, devices, model_dir,
@@ -103,7 +105,9 @@ class GlobalScheduler:
 
     def convert_omni_request(self, t: TokenizedGenerateOmniReqInput):
         self._enter(MMReq(t.rid, "omni", dataclasses.asdict(t) | {"pixel_values": t.pixel_values,
-                                                                 "image_grid_thw": t.image_grid_thw}))
+                                                                 "image_grid_thw": t.image_grid_thw,
+                                                                 "audio_features": t.audio_features,
+                                                                 "audio_feature_lens": t.audio_feature_lens}))
 
     def convert_audio_request(self, t: TokenizedGenerateAudioReqInput):
         self._enter(MMReq(t.rid, "audio", dataclasses.asdict(t) | {"audio": t.audio}))

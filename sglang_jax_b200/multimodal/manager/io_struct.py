@@ -44,8 +44,9 @@ class TokenizedGenerateOmniReqInput:
     input_ids: list[int]
     pixel_values: Any = None            # [num_patches, patch_dim]
     image_grid_thw: Any = None          # [num_images, 3]
-    audio_features: Any = None
+    audio_features: Any = None          # log-mel spectrogram [num_mel_bins, frames]
     sampling_params: dict = dataclasses.field(default_factory=dict)
+    audio_feature_lens: Any = None      # frames per clip when several clips are concatenated
 
 
 @dataclasses.dataclass

@@ -32,6 +32,8 @@ class Stage:
     def stop(self):
         self.in_queue.put(None)
         self._thread.join(timeout=10)
+        if hasattr(self.scheduler, "shutdown"):
+            self.scheduler.shutdown()
 
     def abort(self, rid: str):
         with self._lock:

@@ -530,6 +530,10 @@ def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
         ds[i, t == IMG] = f
     mm = {"input_embedding": emb, "mrope_positions": pos[:, 0].numpy(), "mrope_position_delta": int(delta[0]),
           "deepstack": ds}
+    from sglang_jax_b200.multimodal.manager.mrope_utils import get_rope_index
+    my_pos, my_delta = get_rope_index(ids, image_grid_thw=grid, image_token_id=IMG, video_token_id=292,
+                                      spatial_merge_size=2, tokens_per_second=25)
+    assert (my_pos == pos[:, 0].long().numpy()).all() and my_delta == int(delta[0])
     sp = {"max_new_tokens": n_new, "temperature": 0, "ignore_eos": True}
     for chunk in (None, 16):
         ps.reset_state()
@@ -541,3 +545,19 @@ def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
             assert out["output_ids"] == want, (chunk, out["output_ids"], want)
         finally:
             eng.shutdown()
+    # the same request through the two-stage pipeline (embedding stage -> serving engine) over HTTP
+    from fastapi.testclient import TestClient
+    from sglang_jax_b200.multimodal.entrypoint.http_server import MultimodalServer, build_app
+    ps.reset_state()
+    srv = MultimodalServer("Qwen/Qwen3-Omni-30B-A3B-Instruct", str(path),
+                           config_overrides={1: dict(page_size=4, max_total_tokens=1024, tp_size=1)})
+    try:
+        with TestClient(build_app(srv)) as c:
+            assert [s["scheduler"] for s in c.get("/health").json()["stages"]] == ["embedding", "auto_regressive"]
+            r = c.post("/v1/chat/completions", json={
+                "input_ids": ids, "pixel_values": px.tolist(), "image_grid_thw": grid.tolist(),
+                "audio_features": feats[0].tolist(), "max_tokens": n_new})
+            assert r.status_code == 200, r.text
+            assert r.json()["choices"][0]["message"]["output_ids"] == want
+    finally:
+        srv.shutdown()
