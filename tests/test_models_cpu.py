@@ -537,3 +537,28 @@ def test_glm5_dsa_sparse_attention_matches_hf(tmp_path, topk):
     want = _hf_generate(hf, PROMPTS, n=8)
     assert _generate(path, PROMPTS, n=8) == want
     assert _generate(path, PROMPTS, n=8, chunked_prefill_size=16) == want
+
+
+def test_kimi_k25_language_model_loads_under_language_model_prefix(tmp_path):
+    """The checkpoint nests the DeepSeek-V3 decoder under `language_model.` beside the vision tower."""
+    from safetensors.torch import save_file
+    from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+    text = dict(hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=2,
+                num_attention_heads=4, num_key_value_heads=4, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=32,
+                qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=4, n_shared_experts=1, num_experts_per_tok=2,
+                n_group=1, topk_group=1, scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True,
+                routed_scaling_factor=2.5, first_k_dense_replace=1, moe_layer_freq=1, rms_norm_eps=1e-6,
+                rope_theta=10000.0, vocab_size=512, tie_word_embeddings=False, max_position_embeddings=512,
+                rope_scaling=None, attention_bias=False)
+    hf = _init(DeepseekV3ForCausalLM(DeepseekV3Config(**text)))
+    path = tmp_path / "k25"
+    path.mkdir()
+    sd = {"language_model." + k: v.contiguous() for k, v in hf.state_dict().items()}
+    sd["vision_tower.patch_embed.proj.bias"] = torch.zeros(8)
+    sd["mm_projector.proj.0.bias"] = torch.zeros(8)
+    save_file(sd, str(path / "model.safetensors"))
+    cfg = dict(architectures=["KimiK25ForConditionalGeneration"], model_type="kimi_k25", torch_dtype="float32",
+               text_config=dict(text, model_type="deepseek_v3", quantization_config={"format": "pack-quantized"}),
+               vision_config={"vt_hidden_size": 8}, media_placeholder_token_id=500)
+    (path / "config.json").write_text(json.dumps(cfg))
+    assert _generate(str(path), PROMPTS, n=6) == _hf_generate(hf, PROMPTS, n=6)

@@ -561,3 +561,45 @@ def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
             assert r.json()["choices"][0]["message"]["output_ids"] == want
     finally:
         srv.shutdown()
+
+
+def test_kimi_k25_vision_tower_properties():
+    from types import SimpleNamespace
+    from sglang_jax_b200.multimodal.model_executor.loading import init_dummy
+    from sglang_jax_b200.multimodal.models.kimi_k25.kimi_k25_vit import (KimiK25VisionModel, apply_rope_interleaved,
+                                                                           rope_2d)
+    cfg = SimpleNamespace(patch_size=4, in_channels=3, vt_hidden_size=32, vt_num_attention_heads=4,
+                          vt_intermediate_size=48, vt_num_hidden_layers=2, init_pos_emb_height=6, init_pos_emb_width=6,
+                          init_pos_emb_time=4, merge_kernel_size=[2, 2], text_hidden_size=40)
+    m = init_dummy(KimiK25VisionModel(cfg, dtype=torch.float32), seed=2, std=0.1).eval()
+    names = {n for n, _ in m.named_parameters()}
+    for n in ("vision_tower.patch_embed.pos_emb.weight", "vision_tower.patch_embed.proj.bias",
+              "vision_tower.encoder.blocks.1.wqkv.weight", "vision_tower.encoder.blocks.0.wo.bias",
+              "vision_tower.encoder.blocks.0.mlp.fc0.weight", "vision_tower.encoder.blocks.0.norm1.weight",
+              "vision_tower.encoder.final_layernorm.bias", "mm_projector.pre_norm.weight",
+              "mm_projector.proj.0.weight", "mm_projector.proj.2.bias"):
+        assert n in names, n
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(1 * 6 * 6, 3, 4, 4, generator=g)           # an image on the native grid
+    b = torch.randn(2 * 4 * 8, 3, 4, 4, generator=g)           # a two-frame clip on a resized grid
+    ya, yb = m(a, [[1, 6, 6]]), m(b, [[2, 4, 8]])
+    assert ya.shape == (9, 40) and yb.shape == (8, 40)         # frames pooled, 2x2 patches merged
+    both = m(torch.cat([a, b]), [[1, 6, 6], [2, 4, 8]])
+    assert torch.allclose(both, torch.cat([ya, yb]), atol=1e-5)             # items never see each other
+    assert torch.equal(m._abs_pos(1, 6, 6), m.vision_tower.patch_embed.pos_emb.weight.reshape(36, -1))
+    assert m._abs_pos(2, 4, 8).shape == (64, 32)
+    with pytest.raises(ValueError):
+        m(torch.randn(5 * 4, 3, 4, 4), [[5, 2, 2]])
+    # rotary: the origin is the identity, and q.k depends only on the (row, column) offset
+    cos, sin = rope_2d(5, 7, 8)
+    x = torch.randn(35, 1, 8, generator=g)
+    assert torch.allclose(apply_rope_interleaved(x, cos, sin)[0], x[0])
+    q, k = torch.randn(1, 1, 8, generator=g).expand(35, 1, 8), torch.randn(1, 1, 8, generator=g).expand(35, 1, 8)
+    rq, rk = apply_rope_interleaved(q, cos, sin)[:, 0], apply_rope_interleaved(k, cos, sin)[:, 0]
+    at = lambda r, c: r * 7 + c
+    assert torch.allclose((rq[at(1, 2)] * rk[at(3, 5)]).sum(), (rq[at(2, 1)] * rk[at(4, 4)]).sum(), atol=1e-5)
+    assert not torch.allclose((rq[at(1, 2)] * rk[at(3, 5)]).sum(), (rq[at(1, 2)] * rk[at(3, 6)]).sum(), atol=1e-4)
+    sd = dict(m.state_dict())
+    m2 = KimiK25VisionModel(cfg, dtype=torch.float32)
+    assert m2.load_weights(sd.items()) == names
+    assert torch.allclose(m2(a, [[1, 6, 6]]), ya)
