@@ -38,40 +38,62 @@ class EmbedsGenerator:
                                        np.full(1, 1 if greedy else 1 << 30, np.int32), np.zeros(1, np.float32), None,
                                        greedy, False, False, False)
 
-    @torch.inference_mode()
-    def generate(self, input_ids: list[int], input_embeds: torch.Tensor | None, max_new_tokens: int = 16,
-                 temperature: float = 0.0, eos_ids: set[int] | None = None,
-                 mrope_positions: np.ndarray | None = None, mrope_delta: int = 0) -> list[int]:
+    # ------------------------------------------------------------------ stepwise API
+    def begin(self, total_len: int):
+        """Start a new sequence (the generator serves one at a time) that will grow to `total_len`."""
         r = self.runner
-        row = 0
-        self.next_page = 1
-        n = len(input_ids)
-        total = n + max_new_tokens
-        if total > r.req_to_token_pool.max_context_len or total > r.max_total_num_tokens:
+        if total_len > r.req_to_token_pool.max_context_len or total_len > r.max_total_num_tokens:
             raise ValueError("request does not fit the stage's KV pool")
-        loc = self._alloc(row, 0, n)
+        self.next_page = 1
+        self.length = 0
+        self.temperature = 0.0
+
+    @torch.inference_mode()
+    def extend(self, input_ids: list[int], input_embeds: torch.Tensor | None = None, capture_hidden: bool = False,
+               mrope_positions: np.ndarray | None = None):
+        """Prefill `len(input_ids)` positions; returns (sampled token, last hidden state or None)."""
+        r, row, n, start = self.runner, 0, len(input_ids), self.length
+        loc = self._alloc(row, start, n)
         rows, pos, ids = r.req_to_token_pool.take_page_deltas()
         batch = ModelWorkerBatch(
             bid=1, forward_mode=ForwardMode.EXTEND, input_ids=np.asarray(input_ids, np.int32),
-            req_pool_indices=np.asarray([row], np.int32), seq_lens=np.asarray([n], np.int32), out_cache_loc=loc,
-            positions=np.arange(n, dtype=np.int32), extend_prefix_lens=np.zeros(1, np.int32),
+            req_pool_indices=np.asarray([row], np.int32), seq_lens=np.asarray([start + n], np.int32), out_cache_loc=loc,
+            positions=np.arange(start, start + n, dtype=np.int32), extend_prefix_lens=np.asarray([start], np.int32),
             extend_seq_lens=np.asarray([n], np.int32), extend_logprob_start_lens=np.zeros(1, np.int32),
-            page_delta_rows=rows, page_delta_pos=pos, page_delta_ids=ids, sampling_info=self._sinfo(temperature),
-            input_embeds=input_embeds,
+            page_delta_rows=rows, page_delta_pos=pos, page_delta_ids=ids, sampling_info=self._sinfo(self.temperature),
+            input_embeds=input_embeds, capture_hidden_mode=1 if capture_hidden else 0,
             mrope_positions=None if mrope_positions is None else np.asarray(mrope_positions, np.int32))
-        _, tok, _ = r.forward(batch)
-        out = [int(tok[0])]
+        out, tok, _ = r.forward(batch)
+        self.length = start + n
+        return int(tok[0]), (out.hidden_states if capture_hidden else None)
+
+    @torch.inference_mode()
+    def step(self, token_id: int, input_embed: torch.Tensor | None = None, capture_hidden: bool = False,
+             mrope_delta: int | None = None):
+        """Decode one position whose input is `token_id` (or `input_embed [1, hidden]`)."""
+        r, row, cur = self.runner, 0, self.length
+        loc = self._alloc(row, cur, 1)
+        rows, pos, ids = r.req_to_token_pool.take_page_deltas()
+        batch = ModelWorkerBatch(
+            bid=2, forward_mode=ForwardMode.DECODE, input_ids=np.asarray([token_id], np.int32),
+            req_pool_indices=np.asarray([row], np.int32), seq_lens=np.asarray([cur + 1], np.int32),
+            out_cache_loc=loc, positions=np.asarray([cur], np.int32), page_delta_rows=rows, page_delta_pos=pos,
+            page_delta_ids=ids, sampling_info=self._sinfo(self.temperature), input_embeds=input_embed,
+            capture_hidden_mode=1 if capture_hidden else 0,
+            mrope_positions=None if mrope_delta is None else np.full((3, 1), cur + mrope_delta, np.int32))
+        out, tok, _ = r.forward(batch)
+        self.length = cur + 1
+        return int(tok[0]), (out.hidden_states if capture_hidden else None)
+
+    def generate(self, input_ids: list[int], input_embeds: torch.Tensor | None, max_new_tokens: int = 16,
+                 temperature: float = 0.0, eos_ids: set[int] | None = None,
+                 mrope_positions: np.ndarray | None = None, mrope_delta: int = 0) -> list[int]:
+        self.begin(len(input_ids) + max_new_tokens)
+        self.temperature = temperature
+        tok, _ = self.extend(input_ids, input_embeds, mrope_positions=mrope_positions)
+        out = [tok]
         eos_ids = eos_ids or set()
         while len(out) < max_new_tokens and out[-1] not in eos_ids:
-            cur = n + len(out) - 1
-            loc = self._alloc(row, cur, 1)
-            rows, pos, ids = r.req_to_token_pool.take_page_deltas()
-            batch = ModelWorkerBatch(
-                bid=2, forward_mode=ForwardMode.DECODE, input_ids=np.asarray([out[-1]], np.int32),
-                req_pool_indices=np.asarray([row], np.int32), seq_lens=np.asarray([cur + 1], np.int32),
-                out_cache_loc=loc, positions=np.asarray([cur], np.int32), page_delta_rows=rows, page_delta_pos=pos,
-                page_delta_ids=ids, sampling_info=self._sinfo(temperature),
-                mrope_positions=None if mrope_positions is None else np.full((3, 1), cur + mrope_delta, np.int32))
-            _, tok, _ = r.forward(batch)
-            out.append(int(tok[0]))
+            tok, _ = self.step(out[-1], mrope_delta=mrope_delta if mrope_positions is not None else None)
+            out.append(tok)
         return out

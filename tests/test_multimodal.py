@@ -603,3 +603,71 @@ def test_kimi_k25_vision_tower_properties():
     m2 = KimiK25VisionModel(cfg, dtype=torch.float32)
     assert m2.load_weights(sd.items()) == names
     assert torch.allclose(m2(a, [[1, 6, 6]]), ya)
+
+
+MIMO_LOCAL = dict(group_size=2, audio_channels=2, local_dim=24, local_layers=1, local_attn_heads=2, local_head_dim=8,
+                  local_ffn_dim=32, input_local_layers=1, input_local_dim=24, input_full_attention=True,
+                  speech_vocab_sizes=[65, 65], speech_empty_ids=[64, 64], delay_pattern=[0, 1], attention_bias=True,
+                  rope_theta=10000.0, rms_norm_eps=1e-6)
+
+
+def test_mimo_audio_local_transformers():
+    from types import SimpleNamespace
+    from sglang_jax_b200.multimodal.model_executor.loading import init_dummy
+    from sglang_jax_b200.multimodal.models.mimo_audio_backbone import MiMoAudioLocalModules
+    m = init_dummy(MiMoAudioLocalModules(SimpleNamespace(hidden_size=32, **MIMO_LOCAL), dtype=torch.float32), 3, 0.2).eval()
+    names = {n for n, _ in m.named_parameters()}
+    for n in ("local_transformer.layers.0.self_attn.q_proj.bias", "input_local_transformer.layers.0.mlp.down_proj.weight",
+              "local_transformer.norm.weight", "speech_embeddings.1.weight", "local_transformer_lm_heads.0.weight",
+              "speech_group_downcast.weight", "hidden_states_downcast.weight"):
+        assert n in names, n
+    ids = torch.tensor([[[3, 4], [5, 6]], [[7, 8], [9, 10]], [[64, 64], [64, 64]]])
+    e = m.group_embeds(ids, torch.tensor([True, True, False]))
+    assert e.shape == (3, 32) and bool((e[2] == 0).all()) and not torch.allclose(e[0], e[1])
+    # the patch encoder is bidirectional: the second frame changes the first frame's contribution
+    swapped = m.group_embeds(ids[:1].flip(1), torch.tensor([True]))
+    assert not torch.allclose(swapped, e[:1])
+    # groups are independent of one another
+    assert torch.allclose(m.group_embeds(ids[1:2], torch.tensor([True])), e[1:2], atol=1e-6)
+    h = torch.randn(2, 32, generator=torch.Generator().manual_seed(0))
+    codes = m.patch_decode(h)
+    assert codes.shape == (2, 2, 2) and int(codes.max()) < 64                    # never the `empty` code
+    assert torch.equal(codes, m.patch_decode(h)) and torch.equal(m.patch_decode(h[:1]), codes[:1])
+    # the decoder's cache matters: with the delay pattern, channel 1 of frame 0 is produced at local step 1
+    # and must depend on channel 0 of frame 0 (fed back at step 1) — change that embedding and it moves
+    before = m.patch_decode(h[:1])
+    m.speech_embeddings[0].weight.data[int(before[0, 0, 0])] += 5.0
+    after = m.patch_decode(h[:1])
+    assert int(after[0, 0, 0]) == int(before[0, 0, 0])
+    assert not torch.equal(after[0, :, 1], before[0, :, 1]) or not torch.equal(after[0, 1], before[0, 1])
+
+
+def test_mimo_audio_grouped_backbone_pipeline(tmp_path):
+    """audio -> codec tokens -> grouped MiMo backbone (patch encoder in, patch decoder out) -> codec -> wave."""
+    from fastapi.testclient import TestClient
+    from sglang_jax_b200.multimodal.entrypoint.http_server import MultimodalServer, build_app
+    llm_cfg = dict(architectures=["MiMoAudioForCausalLM"], model_type="qwen2", hidden_size=32, intermediate_size=64,
+                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=320,
+                   max_position_embeddings=256, tie_word_embeddings=False, torch_dtype="float32", **MIMO_LOCAL)
+    path = tmp_path / "mimo_audio"
+    path.mkdir()
+    (path / "config.json").write_text(json.dumps(llm_cfg))
+    codec = dict(sample_rate=8000, n_mels=20, d_model=32, heads=2, layers=1, num_quantizers=2, codebook_size=64, hop=80)
+    srv = MultimodalServer("XiaomiMiMo/MiMo-Audio", None, config_overrides={
+        0: codec, 1: {"model_path": str(path), "load_format": "dummy", "empty_idx": 300}, 2: codec})
+    try:
+        bb = srv.gs.stages[1].scheduler
+        assert bb.local is not None and bb.local.group == 2
+        with TestClient(build_app(srv)) as c:
+            wave = np.sin(np.linspace(0, 200, 4000)).astype("<f4")
+            asr = c.post("/v1/audio/transcriptions", json={"audio_b64": base64.b64encode(wave.tobytes()).decode(),
+                                                           "max_new_tokens": 5})
+            assert asr.status_code == 200, asr.text
+            tts = c.post("/v1/audio/speech", json={"input": "hello", "max_new_tokens": 6})
+            assert tts.status_code == 200 and tts.content[:4] == b"RIFF"
+            again = c.post("/v1/audio/speech", json={"input": "hello", "max_new_tokens": 6})
+            assert again.content == tts.content
+            longer = c.post("/v1/audio/speech", json={"input": "hello", "max_new_tokens": 9})
+            assert len(longer.content) > len(tts.content)            # 2 frames of audio per generated group
+    finally:
+        srv.shutdown()
