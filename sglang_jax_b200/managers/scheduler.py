@@ -255,10 +255,9 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                                             self.model_config.sliding_window or 4096, self.page_size,
                                             disable=sa.disable_radix_cache)
             return
-        if self.page_size == 1:
-            self.token_to_kv_pool_allocator = TokenToKVPoolAllocator(self.max_total_num_tokens, kvcache=kv)
-        else:
-            self.token_to_kv_pool_allocator = PagedTokenToKVPoolAllocator(self.max_total_num_tokens, self.page_size, kvcache=kv)
+        # C++ free list / radix tree when the extension is built (`csrc/sched`), Python otherwise
+        from ..mem_cache import native as native_sched
+        self.token_to_kv_pool_allocator = native_sched.make_allocator(self.max_total_num_tokens, self.page_size, kv)
         if sa.disable_radix_cache:
             self.tree_cache = ChunkCache(self.req_to_token_pool, self.token_to_kv_pool_allocator, self.page_size)
         elif sa.hicache_storage != "disable" and kv is not None:
@@ -267,7 +266,7 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
                                            kv, sa.hicache_ratio, sa.hicache_write_policy,
                                            sa.hicache_write_through_threshold)
         else:
-            self.tree_cache = RadixCache(self.req_to_token_pool, self.token_to_kv_pool_allocator, self.page_size,
+            self.tree_cache = native_sched.make_radix_cache(self.req_to_token_pool, self.token_to_kv_pool_allocator, self.page_size,
                                          enable_kv_cache_events=bool(sa.kv_events_config),
                                          is_eagle=self.spec_algorithm in ("EAGLE", "EAGLE3"))
 
