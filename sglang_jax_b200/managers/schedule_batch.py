@@ -431,6 +431,8 @@ class ModelWorkerBatch:
     mrope_positions: np.ndarray | None = None
     # [L, T, hidden]: vision features added to the residual stream after each of the first L layers
     deepstack_embeds: Any = None
+    # (src, dst) recurrent-state slot copies to run, in order, before this forward
+    recurrent_copies: list | None = None
 
     @property
     def batch_size(self):
@@ -538,6 +540,8 @@ class ScheduleBatch:
             if fresh_row or r.kv_allocated_len < pre:
                 # matched (or re-matched) prefix: publish the shared slots in the request's row
                 pool.write(r.req_pool_idx, 0, r.prefix_indices)
+            if fresh_row and hasattr(self.tree_cache, "on_request_scheduled"):
+                self.tree_cache.on_request_scheduled(r)        # clone the prefix's recurrent state
             seq = len(r.fill_ids)
             input_ids.extend(r.fill_ids[pre:])
             prefix_lens.append(pre)
@@ -825,6 +829,8 @@ class ScheduleBatch:
             spec_info=self.spec_info, spec_algorithm=self.spec_algorithm,
             dp_rank=self.dp_rank, real_bs=len(self.reqs),
             input_embeds=mm_embeds, input_embeds_rows=mm_rows, mrope_positions=mrope, deepstack_embeds=deepstack,
+            recurrent_copies=(self.tree_cache.take_recurrent_copies()
+                              if hasattr(self.tree_cache, "take_recurrent_copies") else None) or None,
         )
 
     def _multimodal_inputs(self, positions: np.ndarray):

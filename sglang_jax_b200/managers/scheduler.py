@@ -238,37 +238,15 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
 
     # ------------------------------------------------------------------ memory
     def init_memory_pool_and_cache(self):
-        sa = self.server_args
-        kv = self.token_to_kv_pool
-        lt = getattr(getattr(self.model_config, "hf_text_config", None), "layer_types", None) or []
-        if "linear_attention" in lt and not sa.disable_radix_cache:
-            # a shared prefix would also need the recurrent state at its end; without such
-            # checkpoints hybrid linear-attention models run without prefix sharing
-            logger.info("hybrid linear-attention model: prefix sharing is off")
-            sa.disable_radix_cache = True
-        if kv is not None and hasattr(kv, "swa_pool"):
-            # hybrid sliding-window model: dual allocator + window-aware prefix cache
-            from ..mem_cache.allocator import SWATokenToKVPoolAllocator
-            from ..mem_cache.swa_radix_cache import SWARadixCache
-            self.token_to_kv_pool_allocator = SWATokenToKVPoolAllocator(kv.size, kv.size_swa, self.page_size, kvcache=kv)
-            self.tree_cache = SWARadixCache(self.req_to_token_pool, self.token_to_kv_pool_allocator,
-                                            self.model_config.sliding_window or 4096, self.page_size,
-                                            disable=sa.disable_radix_cache)
-            return
-        # C++ free list / radix tree when the extension is built (`csrc/sched`), Python otherwise
-        from ..mem_cache import native as native_sched
-        self.token_to_kv_pool_allocator = native_sched.make_allocator(self.max_total_num_tokens, self.page_size, kv)
-        if sa.disable_radix_cache:
-            self.tree_cache = ChunkCache(self.req_to_token_pool, self.token_to_kv_pool_allocator, self.page_size)
-        elif sa.hicache_storage != "disable" and kv is not None:
-            from ..mem_cache.hiradix_cache import HiRadixCache
-            self.tree_cache = HiRadixCache(self.req_to_token_pool, self.token_to_kv_pool_allocator, self.page_size,
-                                           kv, sa.hicache_ratio, sa.hicache_write_policy,
-                                           sa.hicache_write_through_threshold)
-        else:
-            self.tree_cache = native_sched.make_radix_cache(self.req_to_token_pool, self.token_to_kv_pool_allocator, self.page_size,
-                                         enable_kv_cache_events=bool(sa.kv_events_config),
-                                         is_eagle=self.spec_algorithm in ("EAGLE", "EAGLE3"))
+        from ..mem_cache.registry import TreeCacheBuildContext, create_tree_cache
+        rp = getattr(getattr(self.tp_worker, "model_runner", None), "recurrent_pool", None)
+        built = create_tree_cache(TreeCacheBuildContext(
+            self.server_args, self.model_config, self.req_to_token_pool, self.token_to_kv_pool,
+            self.max_total_num_tokens, self.page_size, self.spec_algorithm, rp))
+        self.token_to_kv_pool_allocator, self.tree_cache = built.allocator, built.tree_cache
+        if built.needs_sequential_schedule:
+            self.enable_overlap = False
+            self.server_args.disable_overlap_schedule = True
 
     @property
     def _hicache(self) -> bool:

@@ -13,11 +13,16 @@ import torch
 
 class RecurrentStatePool:
     def __init__(self, size: int, num_layers: int, conv_dim: int, conv_kernel: int, num_heads: int, head_k_dim: int,
-                 head_v_dim: int, device: str = "cpu", conv_dtype=torch.bfloat16, state_dtype=torch.float32):
+                 head_v_dim: int, device: str = "cpu", conv_dtype=torch.bfloat16, state_dtype=torch.float32,
+                 snapshot_slots: int = 0):
         self.size = size
         self.num_layers = num_layers
-        self.conv_state = torch.zeros((num_layers, size + 1, conv_dim, conv_kernel - 1), dtype=conv_dtype, device=device)
-        self.recurrent_state = torch.zeros((num_layers, size + 1, num_heads, head_k_dim, head_v_dim), dtype=state_dtype,
+        # slots 1..size belong to request rows; `snapshot_slots` more hold prefix-cache checkpoints
+        # (owned by the scheduler's unified radix cache)
+        self.snapshot_slots = snapshot_slots
+        n = size + 1 + snapshot_slots
+        self.conv_state = torch.zeros((num_layers, n, conv_dim, conv_kernel - 1), dtype=conv_dtype, device=device)
+        self.recurrent_state = torch.zeros((num_layers, n, num_heads, head_k_dim, head_v_dim), dtype=state_dtype,
                                            device=device)
         self.free_slots = list(range(1, size + 1))
         self.device = device
@@ -40,6 +45,12 @@ class RecurrentStatePool:
         if idx.numel():
             self.conv_state[:, idx] = 0
             self.recurrent_state[:, idx] = 0
+
+    def copy_sequence(self, pairs) -> None:
+        """Run `(src, dst)` copies in order (a later copy may read what an earlier one wrote)."""
+        for s, d in pairs:
+            self.conv_state[:, d] = self.conv_state[:, s]
+            self.recurrent_state[:, d] = self.recurrent_state[:, s]
 
     def copy_slots(self, src, dst) -> None:
         s = torch.as_tensor(list(src), dtype=torch.long, device=self.conv_state.device)

@@ -1,0 +1,154 @@
+"""Prefix cache for hybrid models whose linear-attention layers carry a recurrent state
+(reference `python/sgl_jax/srt/mem_cache/unified_radix_cache.py`,
+`unified_cache_components/{tree,full,recurrent}_component.py`).
+
+A shared prefix is only usable if, besides its KV slots (the FULL component), the recurrent state
+at its *end* is available (the RECURRENT component).  Nodes therefore may carry a *snapshot*: a
+slot of the `RecurrentStatePool` snapshot area holding the conv window and state matrix after the
+node's last token.  Matching walks the tree as usual but stops at the deepest node that has a
+snapshot; the request then starts from a copy of it (copy-on-write into its own slot) and
+recomputes the rest.  A finished request commits its final state to the node that ends exactly
+at its last cached token.
+
+Differences from the reference's component design, chosen for this runtime: snapshots may sit on
+internal nodes too (the reference keeps them on leaves and drops one when its node gains a
+child), and they have their own LRU over a fixed number of snapshot slots instead of riding leaf
+eviction — a node can lose its snapshot and keep its KV.  State copies are not executed here:
+the tree runs in the scheduler, the pools live in every tensor rank, so copies are queued
+(`take_recurrent_copies`) and travel with the next batch to all ranks, in order.
+"""
+
+from __future__ import annotations
+
+from collections import OrderedDict
+from enum import IntEnum
+
+import numpy as np
+
+from .base_prefix_cache import MatchResult
+from .radix_cache import RadixCache, RadixKey, TreeNode
+
+
+class ComponentType(IntEnum):
+    FULL = 0
+    RECURRENT = 1
+
+
+class UnifiedRadixCache(RadixCache):
+    def __init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size: int = 1, disable: bool = False,
+                 num_request_slots: int = 0, num_snapshot_slots: int = 0, enable_kv_cache_events: bool = False):
+        self.components = (ComponentType.FULL, ComponentType.RECURRENT)
+        self.snapshot_base = num_request_slots + 1          # request row r owns state slot r + 1
+        self.num_snapshot_slots = num_snapshot_slots
+        super().__init__(req_to_token_pool, token_to_kv_pool_allocator, page_size, disable, enable_kv_cache_events)
+
+    # ---------------------------------------------------------------- state
+    def reset(self):
+        super().reset()
+        self._snap: dict[int, int] = {}                     # node id -> snapshot slot
+        self._nodes: dict[int, TreeNode] = {}               # node id -> node, for snapshot holders
+        self._lru: OrderedDict[int, None] = OrderedDict()   # node ids, least recently used first
+        self._free_snap = list(range(self.snapshot_base, self.snapshot_base + self.num_snapshot_slots))
+        self._copies: list[tuple[int, int]] = []
+
+    def supports_recurrent(self) -> bool:
+        return True
+
+    def take_recurrent_copies(self) -> list[tuple[int, int]]:
+        """(src slot, dst slot) state copies to run, in order, before the next forward."""
+        c, self._copies = self._copies, []
+        return c
+
+    def queue_copy(self, src: int, dst: int):
+        self._copies.append((int(src), int(dst)))
+
+    def recurrent_evictable_size(self) -> int:
+        return sum(1 for i in self._snap if self._nodes[i].lock_ref == 0)
+
+    def snapshot_slots_in_use(self) -> int:
+        return len(self._snap)
+
+    def assert_recurrent_slot_ledger(self):
+        used = sorted(self._snap.values())
+        assert len(set(used)) == len(used), "a snapshot slot is owned twice"
+        assert sorted(used + self._free_snap) == list(range(self.snapshot_base,
+                                                            self.snapshot_base + self.num_snapshot_slots)), \
+            "snapshot slots leaked"
+        return len(used)
+
+    # ---------------------------------------------------------------- match
+    def match_prefix(self, key: RadixKey, req=None, **kw) -> MatchResult:
+        res = super().match_prefix(key)
+        node = res.last_device_node
+        if self.disable or node is self.root_node:
+            if req is not None:
+                req.recurrent_cow_src = None
+            return MatchResult(np.empty(0, np.int32), self.root_node, self.root_node)
+        total = len(res.device_indices)
+        # deepest node on the matched path that also has the recurrent state at its end
+        while node is not self.root_node and node.id not in self._snap:
+            total -= len(node.key)
+            node = node.parent
+        if node is self.root_node:
+            if req is not None:
+                req.recurrent_cow_src = None
+            return MatchResult(np.empty(0, np.int32), self.root_node, self.root_node)
+        self._lru.move_to_end(node.id)
+        if req is not None:
+            req.recurrent_cow_src = self._snap[node.id]
+        return MatchResult(res.device_indices[:total], node, node)
+
+    # ---------------------------------------------------------------- request hooks
+    def cache_finished_req(self, req, is_insert: bool = True, **kw):
+        kv_len = req.committed_kv_len()
+        tokens = (req.origin_input_ids + req.output_ids)[:kv_len]
+        row = req.req_pool_idx
+        super().cache_finished_req(req, is_insert, **kw)
+        if self.disable or not is_insert or kv_len == 0 or kv_len % self.page_size:
+            return          # the state belongs to position kv_len; only a node ending there can own it
+        dp = getattr(req, "dp_rank", 0) or 0
+        values, node = self._match(tokens, RadixKey(tokens, req.extra_key, dp).namespace)
+        if node is self.root_node or sum(len(v) for v in values) != kv_len or node.id in self._snap:
+            return
+        slot = self._alloc_snapshot()
+        if slot is None:
+            return
+        self._snap[node.id] = slot
+        self._nodes[node.id] = node
+        self._lru[node.id] = None
+        self.queue_copy(row + 1, slot)
+
+    def cache_unfinished_req(self, req, chunked: bool = False, **kw):
+        # the state of an in-flight prefill is only in the request's own slot: nothing to share yet
+        kv_len = len(req.fill_ids)
+        req.prefix_indices = self.req_to_token_pool.read(req.req_pool_idx, kv_len).copy()
+
+    def on_request_scheduled(self, req):
+        """First prefill of a request that matched a snapshot: clone it into the request's slot."""
+        src = getattr(req, "recurrent_cow_src", None)
+        if src is not None and len(req.prefix_indices) > 0:
+            self.queue_copy(src, req.req_pool_idx + 1)
+        req.recurrent_cow_src = None
+
+    # ---------------------------------------------------------------- snapshots
+    def _alloc_snapshot(self) -> int | None:
+        if self._free_snap:
+            return self._free_snap.pop()
+        for nid in self._lru:                    # least recently used, not pinned by a running request
+            if self._nodes[nid].lock_ref == 0:
+                return self._release_snapshot(nid, reuse=True)
+        return None
+
+    def _release_snapshot(self, nid: int, reuse: bool = False):
+        slot = self._snap.pop(nid)
+        self._nodes.pop(nid, None)
+        self._lru.pop(nid, None)
+        if reuse:
+            return slot
+        self._free_snap.append(slot)
+        return None
+
+    def _drop(self, n: TreeNode):
+        if n.id in self._snap:
+            self._release_snapshot(n.id)
+        super()._drop(n)

@@ -149,8 +149,9 @@ class ModelRunner:
         if spec:
             from ..mem_cache.recurrent_state_pool import RecurrentStatePool
             # one state slot per request row (slot = row + 1)
+            snap = 0 if sa.disable_radix_cache else int(sa.recurrent_snapshot_slots)
             self.recurrent_pool = RecurrentStatePool(req_to_token_pool.size, device=str(self.device),
-                                                     conv_dtype=self.dtype, **spec)
+                                                     conv_dtype=self.dtype, snapshot_slots=snap, **spec)
         n_layers = getattr(self.model, "num_kv_layers", None) or mc.num_hidden_layers
         if mc.attention_arch == AttentionArch.MLA:
             self.token_to_kv_pool = MLATokenToKVPool(self.max_total_num_tokens, self.page_size, self.kv_cache_dtype,
@@ -223,6 +224,8 @@ class ModelRunner:
                 fb.last_token_indices = None
         if self.server_args is not None and not self.server_args.disable_overlap_schedule:
             fb.input_ids = self.resolve_future_token_ids(fb.input_ids)
+        if getattr(batch, "recurrent_copies", None) and self.recurrent_pool is not None:
+            self.recurrent_pool.copy_sequence(batch.recurrent_copies)      # prefix-cache checkpoints / clones
         comm = ps.get_state().fused_comm
         si = batch.sampling_info
         if (comm is not None and not skip_sample and not batch.return_logprob and si is not None and si.is_all_greedy

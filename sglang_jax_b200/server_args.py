@@ -74,6 +74,8 @@ class ServerArgs:
     schedule_conservativeness: float = 1.0
     page_size: int = 1
     swa_full_tokens_ratio: float = 0.8
+    # hybrid linear-attention models: recurrent-state checkpoints kept for shared prefixes (0 = no sharing)
+    recurrent_snapshot_slots: int = 32
     recurrent_state_memory_ratio: float = 0.9
     max_recurrent_state_size: int | None = None
     recurrent_track_interval: int | None = None

@@ -562,3 +562,60 @@ def test_kimi_k25_language_model_loads_under_language_model_prefix(tmp_path):
                vision_config={"vt_hidden_size": 8}, media_placeholder_token_id=500)
     (path / "config.json").write_text(json.dumps(cfg))
     assert _generate(str(path), PROMPTS, n=6) == _hf_generate(hf, PROMPTS, n=6)
+
+
+def test_hybrid_recurrent_prefix_sharing_reuses_state_checkpoints(tmp_path):
+    """Qwen3-Next-style hybrid with the unified radix cache: a later request that extends a finished
+    one starts from the finished request's recurrent-state checkpoint and must produce exactly the
+    tokens of a run without any sharing."""
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    cfg = dict(architectures=["Qwen3NextForCausalLM"], model_type="qwen3_next", hidden_size=64, intermediate_size=96,
+               num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6,
+               vocab_size=256, max_position_embeddings=512, full_attention_interval=2, linear_num_key_heads=2,
+               linear_num_value_heads=4, linear_key_head_dim=8, linear_value_head_dim=8, linear_conv_kernel_dim=4,
+               partial_rotary_factor=0.5, num_experts=0, tie_word_embeddings=False, torch_dtype="float32",
+               layer_types=["linear_attention", "full_attention"] * 2)
+    path = tmp_path / "q3n"
+    path.mkdir()
+    (path / "config.json").write_text(json.dumps(cfg))
+    base = list(range(5, 45))
+    sp = {"max_new_tokens": 6, "temperature": 0, "ignore_eos": True}
+
+    def run(**kw):
+        ps.reset_state()
+        eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=1, skip_tokenizer_init=True,
+                     max_total_tokens=1024, enable_single_process=True, load_format="dummy", **kw)
+        try:
+            first = eng.generate(input_ids=base, sampling_params=sp)
+            cont = base + first["output_ids"][:5]                      # exactly the first request's cached tokens
+            second = eng.generate(input_ids=cont + [77, 78, 79], sampling_params=sp)
+            third = eng.generate(input_ids=[cont + [90, 91], base[:30] + [3, 3]], sampling_params=sp)
+            tc = eng.scheduler.tree_cache
+            if hasattr(tc, "assert_recurrent_slot_ledger"):
+                tc.assert_recurrent_slot_ledger()
+            eng.scheduler.check_memory()
+            return (type(tc).__name__, first["output_ids"], second["output_ids"], [o["output_ids"] for o in third],
+                    second["meta_info"]["cached_tokens"], [o["meta_info"]["cached_tokens"] for o in third],
+                    getattr(tc, "snapshot_slots_in_use", lambda: 0)())
+        finally:
+            eng.shutdown()
+
+    shared = run()
+    plain = run(disable_radix_cache=True)
+    assert shared[0] == "UnifiedRadixCache" and plain[0] == "ChunkCache"
+    assert shared[1:4] == plain[1:4]
+    assert shared[4] == len(base) + 5                   # the second request started from the checkpoint
+    assert shared[5][0] == len(base) + 5 and shared[5][1] == 0      # a prefix without a checkpoint is recomputed
+    assert plain[4] == 0 and shared[6] >= 3
+    # two snapshot slots only: checkpoints are recycled least-recently-used first and nothing leaks
+    tight = run(recurrent_snapshot_slots=2)
+    assert tight[1:4] == plain[1:4] and tight[6] <= 2
+    # page size > 1 turns sharing off for these models
+    ps.reset_state()
+    eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=4, skip_tokenizer_init=True,
+                 max_total_tokens=1024, enable_single_process=True, load_format="dummy")
+    try:
+        assert type(eng.scheduler.tree_cache).__name__ == "ChunkCache"
+    finally:
+        eng.shutdown()
