@@ -88,3 +88,48 @@ def test_named_scope_and_timeit():
         assert f(1) == 2 and g(2) == 4
     r = multiple_iteration_timeit(lambda: sum(range(1000)), warmup=1, iters=3, device="cpu")
     assert r["iters"] == 3 and r["min_ms"] <= r["median_ms"]
+
+
+def test_accuracy_evals_score_known_samplers(tmp_path):
+    """MMLU / GSM8K harness: an oracle sampler scores 1, a wrong one 0, a half-right one 0.5."""
+    import csv
+    import json
+    from sglang_jax_b200.test.eval.simple_eval_common import SamplerBase, make_report, normalize_number
+    from sglang_jax_b200.test.eval.simple_eval_gsm8k import GSM8KEval
+    from sglang_jax_b200.test.eval.simple_eval_mmlu import MMLUEval
+    rows = [dict(Question=f"q{i}?", A="a", B="b", C="c", D="d", Answer="ABCD"[i % 4],
+                 Subject=["abstract_algebra", "philosophy"][i % 2]) for i in range(8)]
+    p = tmp_path / "mmlu.csv"
+    with open(p, "w", newline="") as f:
+        w = csv.DictWriter(f, fieldnames=list(rows[0]))
+        w.writeheader()
+        w.writerows(rows)
+
+    class Oracle(SamplerBase):
+        def __init__(self, right):
+            self.right = right
+
+        def __call__(self, messages):
+            q = messages[-1]["content"]
+            i = int(q.split("q")[-1].split("?")[0]) if "?" in q else 0
+            return f"thinking...\nAnswer: {'ABCD'[i % 4] if self.right(i) else 'ABCD'[(i + 1) % 4]}"
+
+    assert MMLUEval(str(p), num_threads=2)(Oracle(lambda i: True)).score == 1.0
+    assert MMLUEval(str(p), num_threads=1)(Oracle(lambda i: False)).score == 0.0
+    half = MMLUEval(str(p))(Oracle(lambda i: i % 2 == 0))
+    assert half.score == 0.5 and half.metrics["stem"] == 1.0 and half.metrics["humanities"] == 0.0
+    assert "score: 0.5" in make_report(half)
+    g = tmp_path / "gsm.jsonl"
+    with open(g, "w") as f:
+        for i in range(9):
+            f.write(json.dumps({"question": f"what is {i}+{i}?", "answer": f"work\n#### {2 * i:,}"}) + "\n")
+
+    class Adder(SamplerBase):
+        def __call__(self, messages):
+            a = int(messages[-1]["content"].rsplit("what is ", 1)[1].split("+")[0])
+            assert messages[-1]["content"].count("Question:") == 4            # 3 shots + the question
+            return f"{a}+{a}\nAnswer: ${2 * a}.0"
+
+    ev = GSM8KEval(str(g), num_shots=3, num_threads=2)
+    assert len(ev.examples) == 6 and ev(Adder()).score == 1.0
+    assert normalize_number("1,234.0") == "1234" and normalize_number("about 12 apples") == "12"
