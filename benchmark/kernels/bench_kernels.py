@@ -86,7 +86,8 @@ def bench_attention():
     hbm, tf, src = peaks()
     print(f"{'case':>40} {'ms':>9} {'GB/s':>8} {'of hbm':>7}")
     D, P = 128, 64
-    for B, Hq, Hkv, S in [(128, 64, 8, 1400), (128, 8, 1, 1400), (128, 64, 8, 2300), (32, 64, 8, 4096), (256, 8, 1, 1400)]:
+    for B, Hq, Hkv, S in [(128, 64, 8, 1400), (128, 32, 4, 1400), (128, 16, 2, 1400), (128, 8, 1, 1400), (128, 64, 8, 2300),
+                          (32, 64, 8, 4096), (256, 8, 1, 1400), (16, 64, 8, 1400)]:
         pages_per = (S + P - 1) // P
         num_pages = B * pages_per + 1
         cache = torch.randn(num_pages, 2, Hkv, P, D, device="cuda").bfloat16()
