@@ -396,7 +396,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 constexpr int BQ = 64;   // query rows per CTA (16 per consumer warp)
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, int stages) {
   using S = Stage<D>;
   extern __shared__ uint8_t smem_raw[];
