@@ -19,6 +19,7 @@
 //
 // The reference project has no counterpart kernel: its dense projections are
 // `lax.dot_general` calls lowered by XLA (python/sgl_jax/srt/layers/linear.py:102).
+#include <cstdlib>
 #include <stdio.h>
 #include <stdlib.h>
 
@@ -74,6 +75,7 @@ struct Params {
   __nv_bfloat16* rs_peer[8];
   int rs_world, rs_rank, rs_rows_per;
   unsigned long long* debug_stamps;   // optional [16] globaltimer stamps of CTA 0 (profiling aid)
+  int l2_hints;                       // decode mode: stream weights evict-first, keep the token tile evict-last
 };
 
 __device__ __forceinline__ __nv_bfloat16* out_ptr(const Params& p, int tok, int gn) {
@@ -267,6 +269,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       SegIter<BN, MODE> iter(p);
       Seg sg;
+      // decode mode: operand A is the weight matrix, read exactly once by the whole grid; operand B is
+      // the token tile every CTA re-reads for each k-block
+      const uint64_t pol_a = l2_policy_evict_first(), pol_b = l2_policy_evict_last();
       while (!*abort_flag && iter.next(p, sg)) {
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
@@ -277,8 +282,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t fb = smem_u32(&full_bar[stage]);
           mbar_expect_tx(fb, C::kStageBytes);
           uint8_t* sa = stage_base + stage * C::kStageBytes;
-          tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * BK, sg.a_row);
-          tma_load_2d(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, sg.b_row);
+          if (MODE == 1 && p.l2_hints) {
+            tma_load_2d_hint(smem_u32(sa), &tmap_a, fb, kb * BK, sg.a_row, pol_a);
+            tma_load_2d_hint(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, sg.b_row, pol_b);
+          } else {
+            tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * BK, sg.a_row);
+            tma_load_2d(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, sg.b_row);
+          }
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1;
@@ -657,6 +667,13 @@ int sglb_gemm_bf16_rs(const void* x, const void* w, int M, int N, int K, void* w
 }
 
 static unsigned long long* g_debug_stamps = nullptr;
+
+// Decode-mode loads carry L2 eviction hints (weights evict-first, token tile evict-last): measured
+// 278 -> 248 us for the four GEMMs of a Qwen3-32B layer at 128 tokens.  SGLB_GEMM_L2_HINTS=0 turns them off.
+static int gemm_l2_hints() {
+  static const int v = [] { const char* e = getenv("SGLB_GEMM_L2_HINTS"); return e ? atoi(e) : 1; }();
+  return v;
+}
 // Profiling aid: when set, CTA 0 of every dense GEMM launch writes globaltimer stamps (kernel start,
 // after set-up barrier, producer done, MMA issue done, first accumulator ready, epilogue done,
 // teardown barrier, TMEM freed) into this device buffer of 16 u64.
@@ -692,6 +709,7 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
   p.kb_total = kb_total;
   p.splits = 1;
   p.debug_stamps = g_debug_stamps;
+  p.l2_hints = gemm_l2_hints();
   if (rs_world > 0) {
     p.rs_world = rs_world;
     p.rs_rank = rs_rank;
@@ -868,6 +886,7 @@ int sglb_gemm_bf16_noalloc(const void* x, const void* w, const void* bias, void*
   if (e != cudaSuccess) return fail(static_cast<int>(e), "cudaMemsetAsync failed (code %lld)", e);
 
   Params p{};
+  p.l2_hints = gemm_l2_hints();
   p.out = static_cast<__nv_bfloat16*>(out);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.status = reinterpret_cast<Status*>(scratch);
@@ -937,6 +956,7 @@ extern "C" int sglb_grouped_gemm_bf16(const void* x, const void* w, void* out, c
   const int kb_total = (K + BK - 1) / BK;
   const int sms = sm_count();
   Params p{};
+  p.l2_hints = gemm_l2_hints();
   p.out = static_cast<__nv_bfloat16*>(out);
   p.workspace = static_cast<float*>(workspace);
   p.counters = counters;
