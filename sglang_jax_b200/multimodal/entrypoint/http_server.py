@@ -31,6 +31,8 @@ class MultimodalServer:
         self.tok = MultimodalTokenizer(self.gs, tokenizer)
         self.detok = MultimodalDetokenizer()
         self.kinds = {s.scheduler for s in self.pipeline.stages}
+        from ..manager.multimodal_tokenizer import MediaPreprocessor
+        self.media = MediaPreprocessor(model_dir, (config_overrides or {}).get("media"))
 
     async def _await(self, rid: str, submit) -> MMOutput:
         loop = asyncio.get_running_loop()
@@ -127,10 +129,24 @@ def build_app(server: MultimodalServer) -> FastAPI:
         b = await request.json()
         rid = b.get("rid") or uuid.uuid4().hex
         sp = {"max_new_tokens": int(b.get("max_tokens", 16)), "temperature": float(b.get("temperature", 0.0))}
-        out = await server._await(rid, lambda: server.gs.submit(TokenizedGenerateOmniReqInput(
-            rid, list(b["input_ids"]), np.asarray(b["pixel_values"], np.float32) if b.get("pixel_values") is not None else None,
-            np.asarray(b["image_grid_thw"]) if b.get("image_grid_thw") is not None else None,
-            np.asarray(b["audio_features"], np.float32) if b.get("audio_features") is not None else None, sp)))
+        if b.get("images") or b.get("audios"):
+            # raw media (base64 / data-URI images, PCM sample lists): preprocess here and expand the
+            # single placeholder tokens of the prompt
+            try:
+                audios = [np.frombuffer(base64.b64decode(a), dtype="<f4") if isinstance(a, str) else a
+                          for a in (b.get("audios") or [])]
+                m = server.media(list(b["input_ids"]), b.get("images"), audios)
+            except (ValueError, KeyError) as e:
+                return JSONResponse({"error": {"message": str(e), "code": 400}}, status_code=400)
+            req = TokenizedGenerateOmniReqInput(rid, m["input_ids"], m.get("pixel_values"), m.get("image_grid_thw"),
+                                                m.get("audio_features"), sp, m.get("audio_feature_lens"))
+        else:
+            req = TokenizedGenerateOmniReqInput(
+                rid, list(b["input_ids"]),
+                np.asarray(b["pixel_values"], np.float32) if b.get("pixel_values") is not None else None,
+                np.asarray(b["image_grid_thw"]) if b.get("image_grid_thw") is not None else None,
+                np.asarray(b["audio_features"], np.float32) if b.get("audio_features") is not None else None, sp)
+        out = await server._await(rid, lambda: server.gs.submit(req))
         if out.error:
             return fail(out)
         return {"id": out.rid, "object": "chat.completion",

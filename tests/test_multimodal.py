@@ -3,6 +3,7 @@ pipelines (text -> DiT -> VAE, image -> ViT -> LLM) through the global scheduler
 layer (reference tests: `python/sgl_jax/test/multimodal/`)."""
 
 import base64
+import io
 import json
 import os
 import threading
@@ -550,7 +551,8 @@ def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
     from sglang_jax_b200.multimodal.entrypoint.http_server import MultimodalServer, build_app
     ps.reset_state()
     srv = MultimodalServer("Qwen/Qwen3-Omni-30B-A3B-Instruct", str(path),
-                           config_overrides={1: dict(page_size=4, max_total_tokens=1024, tp_size=1)})
+                           config_overrides={1: dict(page_size=4, max_total_tokens=1024, tp_size=1),
+                                             "media": dict(min_pixels=64, max_pixels=4096)})
     try:
         with TestClient(build_app(srv)) as c:
             assert [s["scheduler"] for s in c.get("/health").json()["stages"]] == ["embedding", "auto_regressive"]
@@ -559,6 +561,21 @@ def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
                 "audio_features": feats[0].tolist(), "max_tokens": n_new})
             assert r.status_code == 200, r.text
             assert r.json()["choices"][0]["message"]["output_ids"] == want
+            # raw media: a PNG and PCM samples are preprocessed by the server, placeholders expanded
+            from PIL import Image
+            img = np.random.RandomState(0).randint(0, 255, (16, 24, 3), dtype=np.uint8)
+            buf = io.BytesIO()
+            Image.fromarray(img).save(buf, format="PNG")
+            pcm = (np.sin(np.linspace(0, 300, 16000)) * 0.2).astype("<f4")
+            short = [5, 9, 293, AUD, 33, 294, IMG, 41, 42, 7]
+            r2 = c.post("/v1/chat/completions", json={
+                "input_ids": short, "images": ["data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()],
+                "audios": [base64.b64encode(pcm.tobytes()).decode()], "max_tokens": 4})
+            assert r2.status_code == 200, r2.text
+            assert len(r2.json()["choices"][0]["message"]["output_ids"]) == 4
+            bad = c.post("/v1/chat/completions", json={"input_ids": [5, 9], "images": ["data:image/png;base64," +
+                                                       base64.b64encode(buf.getvalue()).decode()]})
+            assert bad.status_code == 400
     finally:
         srv.shutdown()
 
@@ -671,3 +688,38 @@ def test_mimo_audio_grouped_backbone_pipeline(tmp_path):
             assert len(longer.content) > len(tts.content)            # 2 frames of audio per generated group
     finally:
         srv.shutdown()
+
+
+def test_media_preprocessing_matches_hf_processors():
+    from PIL import Image
+    from transformers import WhisperFeatureExtractor
+    from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
+    from sglang_jax_b200.multimodal.manager.processors import (expand_placeholders, frames_to_patches, load_image,
+                                                                 log_mel_spectrogram, smart_resize)
+    rng = np.random.RandomState(0)
+    img = rng.randint(0, 255, (75, 131, 3), dtype=np.uint8)
+    hf = Qwen2VLImageProcessor(patch_size=14, merge_size=2, temporal_patch_size=2, min_pixels=56 * 56,
+                               max_pixels=28 * 28 * 64)
+    want = hf(images=[Image.fromarray(img)], return_tensors="np")
+    px, grid = frames_to_patches(img[None], 14, 2, 2, min_pixels=56 * 56, max_pixels=28 * 28 * 64)
+    assert list(grid) == want["image_grid_thw"][0].tolist()
+    assert px.shape == want["pixel_values"].shape
+    assert np.abs(px - want["pixel_values"]).max() < 0.03               # bicubic resampling rounds pixels differently
+    exact = rng.randint(0, 255, (56, 84, 3), dtype=np.uint8)            # already on the patch grid: no resampling
+    w2 = hf(images=[Image.fromarray(exact)], return_tensors="np")
+    p2, g2 = frames_to_patches(exact[None], 14, 2, 2, min_pixels=56 * 56, max_pixels=28 * 28 * 64)
+    assert list(g2) == [1, 4, 6] and np.allclose(p2, w2["pixel_values"], atol=1e-5)
+    assert smart_resize(75, 131, 28, 56 * 56, 28 * 28 * 64) == (84, 140)
+    buf = io.BytesIO()
+    Image.fromarray(exact).save(buf, format="PNG")
+    uri = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    assert np.array_equal(load_image(uri), exact)
+    wave = (np.sin(np.linspace(0, 900, 16000 * 2)) * 0.3 + rng.randn(32000) * 0.01).astype(np.float32)
+    fe = WhisperFeatureExtractor(feature_size=128, sampling_rate=16000, hop_length=160, n_fft=400)
+    ref = fe(wave, sampling_rate=16000, return_tensors="np", padding="do_not_pad" if False else "longest")["input_features"][0]
+    got = log_mel_spectrogram(wave, 16000, 400, 160, 128).numpy()
+    n = got.shape[1]
+    assert n == 200 and np.abs(got - ref[:, :n]).max() < 2e-3
+    assert expand_placeholders([1, 9, 2, 9, 3], 9, [3, 1]) == [1, 9, 9, 9, 2, 9, 3]
+    with pytest.raises(ValueError):
+        expand_placeholders([1, 9], 9, [1, 2])
