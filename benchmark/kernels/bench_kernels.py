@@ -98,6 +98,16 @@ def bench_attention():
         t = timeit(lambda: native.paged_attention(q, cache, pt, rows, sl, P, D ** -0.5, max_seq_len=S))
         byts = B * S * 2 * Hkv * D * 2
         print(f"{f'decode B={B} Hq={Hq} Hkv={Hkv} S={S}':>40} {t:9.4f} {byts / t / 1e6:8.0f} {100 * byts / t / 1e6 / hbm:6.1f}%")
+    for B, H, S in [(128, 16, 1400), (128, 128, 1400), (32, 16, 8192), (256, 16, 1400)]:   # absorbed MLA (latent 512 + 64)
+        pages_per = (S + P - 1) // P
+        cache = torch.randn(B * pages_per + 1, P, 576, device="cuda").bfloat16()
+        pt = (torch.arange(B * pages_per, device="cuda", dtype=torch.int32) + 1).view(B, pages_per).contiguous()
+        rows = torch.arange(B, device="cuda", dtype=torch.int32)
+        sl = torch.full((B,), S, device="cuda", dtype=torch.int32)
+        ql, qp = torch.randn(B, H, 512, device="cuda").bfloat16(), torch.randn(B, H, 64, device="cuda").bfloat16()
+        t = timeit(lambda: native.mla_decode(ql, qp, cache, pt, rows, sl, P, 192 ** -0.5, max_seq_len=S))
+        byts = B * S * 576 * 2
+        print(f"{f'mla decode B={B} H={H} S={S}':>40} {t:9.4f} {byts / t / 1e6:8.0f} {100 * byts / t / 1e6 / hbm:6.1f}%")
     print(f"{'case':>40} {'ms':>9} {'TFLOP/s':>8}")
     for B, Hq, Hkv, S in [(4, 64, 8, 2048), (8, 8, 1, 1024), (1, 64, 8, 8192)]:
         pages_per = (S + P - 1) // P

@@ -100,7 +100,8 @@ class MLAAttention(nn.Module):
         allowed = self.select_keys(x, q_resid, fb) if self.select_keys is not None else None
         if fb.forward_mode.is_decode():
             o_lat = ops.mla_paged_attention(q_lat, q_pe.contiguous(), buf, fb.page_table, fb.req_pool_indices,
-                                            fb.seq_lens, fb.page_size, self.scaling, self.kv_lora, allowed=allowed)
+                                            fb.seq_lens, fb.page_size, self.scaling, self.kv_lora, allowed=allowed,
+                                            max_seq_len=fb.max_seq_len)
         else:
             o_lat = ops.mla_paged_attention(q_lat, q_pe.contiguous(), buf, fb.page_table, fb.req_pool_indices,
                                             fb.seq_lens, fb.page_size, self.scaling, self.kv_lora, fb.cu_q_lens,

@@ -115,15 +115,11 @@ def fused_experts(x, w13, w2, topk_weights, topk_ids, expert_start=0, workspace=
 
 
 def mla_paged_attention(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale,
-                        kv_lora_rank, cu_q_lens=None, prefix_lens=None, allowed=None):
+                        kv_lora_rank, cu_q_lens=None, prefix_lens=None, allowed=None, max_seq_len=0):
     """Absorbed-MLA attention over the latent cache `[pages, P, kv_lora_rank + rope_dim]`."""
-    if use_native(q_latent) and kv_buffer.dtype == torch.bfloat16 and cu_q_lens is None and allowed is None:
-        try:
-            from . import mla_native
-        except ImportError:
-            mla_native = None
-        if mla_native is not None and mla_native.supported(q_latent, q_pe, kv_lora_rank, page_size):
-            return mla_native.mla_decode(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens, page_size,
-                                         scale, kv_lora_rank)
+    if use_native(q_latent) and cu_q_lens is None and allowed is None and req_pool_indices.dtype == torch.int32 \
+            and _native().mla_decode_supported(q_latent, q_pe, kv_buffer, kv_lora_rank, page_size):
+        return _native().mla_decode(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens, page_size,
+                                    scale, max_seq_len)
     return reference.mla_paged_attention(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens,
                                          page_size, scale, kv_lora_rank, cu_q_lens, prefix_lens, allowed)

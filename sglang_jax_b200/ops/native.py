@@ -52,6 +52,8 @@ def lib():
     L.sglb_page_table_scatter.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     L.sglb_resolve_future.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
     L.sglb_decode_num_splits.argtypes = [c_int, c_int, c_int]
+    L.sglb_mla_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]
     L.sglb_paged_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_int, c_void_p,
                                     c_void_p, c_void_p]
@@ -248,6 +250,31 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    _p(req_pool_indices), _p(seq_lens), _p(prefix_lens), _p(cu_q_lens), B, bound, Hq,
                                    Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
                                    _stream()), "paged_extend")
+    return out
+
+
+def mla_decode_supported(q_latent, q_pe, kv_buffer, kv_lora_rank, page_size) -> bool:
+    return (q_latent.dtype == torch.bfloat16 and kv_buffer.dtype == torch.bfloat16 and kv_lora_rank == 512
+            and q_pe.shape[-1] == 64 and kv_buffer.shape[-1] == 576
+            and ((64 % page_size == 0) if page_size < 64 else (page_size % 64 == 0)))
+
+
+def mla_decode(q_latent, q_pe, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale, max_seq_len=0,
+               num_splits=None):
+    """Absorbed-MLA decode: `q_latent [B, H, 512]`, `q_pe [B, H, 64]`, latent cache
+    `[pages, P, 576]` -> latent output `[B, H, 512]` (the caller applies W_UV)."""
+    B, H, R = q_latent.shape
+    q_latent, q_pe = q_latent.contiguous(), q_pe.contiguous()
+    out = torch.empty_like(q_latent)
+    if num_splits is None:
+        num_splits = decode_num_splits(B, (H + 15) // 16, max_seq_len or page_table.shape[1] * page_size)
+    part_o = part_lse = None
+    if num_splits > 1:
+        part_o = torch.empty((B, H, num_splits, R), dtype=torch.float32, device=q_latent.device)
+        part_lse = torch.empty((B, H, num_splits), dtype=torch.float32, device=q_latent.device)
+    _check(lib().sglb_mla_decode(_p(q_latent), _p(q_pe), _p(out), _p(kv_buffer), kv_buffer.shape[0], _p(page_table),
+                                 page_table.shape[1], _p(req_pool_indices), _p(seq_lens), B, H, R, q_pe.shape[-1],
+                                 page_size, scale, num_splits, _p(part_o), _p(part_lse), _stream()), "mla_decode")
     return out
 
 

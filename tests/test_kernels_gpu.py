@@ -318,3 +318,37 @@ def test_kv_page_copy_device_host_roundtrip(native):
     for layer, b in enumerate(ref_bufs):
         assert torch.equal(pool.kv_buffer[layer][new_pages], b[dev_pages])
         assert pool.kv_buffer[layer][20].abs().sum() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("P", [16, 64, 128])
+@pytest.mark.parametrize("H", [16, 8, 40])
+def test_mla_decode(native, P, H):
+    """Absorbed-MLA decode kernel vs the fp32 PyTorch statement (ragged lengths, split-KV, head
+    groups that are not full, page sizes below / at / above the tile)."""
+    seqs = [1, 17, 64, 65, 300, 1000, 129, 1537]
+    B = len(seqs)
+    pages_per = [(s + P - 1) // P for s in seqs]
+    num_pages = sum(pages_per) + 3
+    g = torch.Generator(device="cuda").manual_seed(50)
+    cache = (torch.randn(num_pages, P, 576, device="cuda", generator=g) * 0.5).bfloat16()
+    pt = torch.zeros(B + 3, max(pages_per) + 2, dtype=torch.int32, device="cuda")
+    perm = (torch.randperm(num_pages - 1, device="cuda") + 1).to(torch.int32)
+    rows = torch.randperm(B + 2, device="cuda")[:B].to(torch.int32)
+    o = 0
+    for b in range(B):
+        pt[rows[b], :pages_per[b]] = perm[o:o + pages_per[b]]
+        o += pages_per[b]
+    q_lat, q_pe = _bf16(B, H, 512, seed=51), _bf16(B, H, 64, seed=52)
+    sl = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    scale = 192 ** -0.5
+    expect = ref.mla_paged_attention(q_lat.float(), q_pe.float(), cache.float(), pt, rows, sl, P, scale, 512)
+    assert native.mla_decode_supported(q_lat, q_pe, cache, 512, P)
+    for splits in (1, 3, None):
+        got = native.mla_decode(q_lat, q_pe, cache, pt, rows, sl, P, scale, max_seq_len=max(seqs), num_splits=splits)
+        torch.cuda.synchronize()
+        native.check_status()
+        _close(got, expect, 2e-2, 2e-2)
+    from sglang_jax_b200 import ops
+    got = ops.mla_paged_attention(q_lat, q_pe, cache, pt, rows, sl, P, scale, 512, max_seq_len=max(seqs))
+    _close(got, expect, 2e-2, 2e-2)
