@@ -199,3 +199,53 @@ def test_speculative_decoding_gpu(tiny_path, algo, topk, steps, ndraft, page):
         # the target drafting for itself is mostly accepted
         steps_used = sum(x["meta_info"]["spec_verify_ct"] for x in outs)
         assert steps_used < 24 * len(prompts) * 0.8, steps_used
+
+
+def test_deepseek_mla_decode_kernel_in_model(tmp_path):
+    """A DeepSeek-shaped model (latent 512 + 64 rotary lanes, MoE) on the GPU: decode with the MLA
+    kernel (eager and under the CUDA graph) against the same step through the PyTorch statements."""
+    import json
+    from sglang_jax_b200 import ops
+    from sglang_jax_b200.ops import native
+    cfg = dict(architectures=["DeepseekV3ForCausalLM"], model_type="deepseek_v3", hidden_size=512,
+               intermediate_size=1024, moe_intermediate_size=256, num_hidden_layers=2, num_attention_heads=16,
+               num_key_value_heads=16, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64,
+               v_head_dim=128, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, n_group=1, topk_group=1,
+               scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, routed_scaling_factor=2.5,
+               first_k_dense_replace=1, moe_layer_freq=1, rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=1024,
+               tie_word_embeddings=False, max_position_embeddings=4096, torch_dtype="bfloat16")
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    lens = [5, 64, 130, 700]
+    runner, _ = _runner(str(tmp_path), load_format="dummy", cuda_graph_max_bs=8)
+    assert runner.cuda_graph_runner is not None and runner.cuda_graph_runner.graphs
+    batch = _extend_batch(runner, lens)
+    out, ids, _ = runner.forward(batch)
+    toks = ids.tolist()
+    dbatch = _decode_batch(runner, lens, toks)
+    assert runner.cuda_graph_runner.can_run(dbatch)
+    _, g_ids, _ = runner.forward(dbatch)                       # replayed graph with the MLA kernel inside
+    g_ids = g_ids.clone()
+    runner.cuda_graph_runner.enabled = False
+    calls = {"n": 0}
+    orig = native.mla_decode
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+
+    native.mla_decode = counted
+    try:
+        d_n, e_ids, _ = runner.forward(dbatch, skip_sample=False)
+        d_n, _, _ = runner.forward(dbatch, skip_sample=True)
+        assert calls["n"] == 4                                 # one launch per layer and forward
+    finally:
+        native.mla_decode = orig
+    ops.set_force_reference(True)
+    try:
+        d_r, _, _ = runner.forward(dbatch, skip_sample=True)
+    finally:
+        ops.set_force_reference(False)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert g_ids.tolist() == e_ids.tolist()
+    assert _rel(d_n.next_token_logits, d_r.next_token_logits) < 4e-2
