@@ -16,6 +16,14 @@ from .layernorm import GatedRMSNorm
 from .linear import ReplicatedLinear
 
 
+def _native_step_ok(x, conv_all, rec_all, dk: int, dv: int) -> bool:
+    """Whether a decode step can run the in-place CUDA kernels (`csrc/linear_attn.cu`)."""
+    from .. import ops
+    return (ops.use_native(x) and rec_all.dtype == torch.float32 and conv_all.dtype in (torch.bfloat16, torch.float32)
+            and rec_all.is_contiguous() and conv_all.is_contiguous() and dk <= 256 and dv <= 256 and dv % 32 == 0
+            and conv_all.shape[-1] + 1 <= 8)
+
+
 class GatedDeltaNet(nn.Module):
     def __init__(self, config, linear_layer_index: int, dtype):
         super().__init__()
@@ -71,7 +79,14 @@ class GatedDeltaNet(nn.Module):
                 qq, kk = qq.repeat_interleave(r, 1), kk.repeat_interleave(r, 1)
             return qq, kk, vv.reshape(-1, self.nv, self.dv)
 
-        if fb.forward_mode.is_decode():
+        if fb.forward_mode.is_decode() and _native_step_ok(x, conv_all, rec_all, self.dk, self.dv):
+            # sm_100a path: the convolution window and the state matrix are updated in place in their pools
+            from ..ops import native
+            y = native.conv1d_update(mixed, conv_all, self.conv1d_weight, slots)
+            qq, kk, vv = torch.split(y, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
+            o = native.delta_rule_step(qq.reshape(T, self.nk, self.dk), kk.reshape(T, self.nk, self.dk),
+                                       vv.reshape(T, self.nv, self.dv), g, beta, rec_all, slots)
+        elif fb.forward_mode.is_decode():
             y, new_conv = la.causal_conv1d_update(mixed, conv_all[slots], self.conv1d_weight)
             conv_all[slots] = new_conv.to(conv_all.dtype)
             qq, kk, vv = heads(y)
@@ -179,6 +194,10 @@ class KimiDeltaAttention(_RecurrentMixer):
             return o[0]
 
         def per_batch(conv_all, rec_all, slots):
+            if _native_step_ok(x, conv_all, rec_all, hd, hd):
+                from ..ops import native
+                q, k, v = split(native.conv1d_update(mixed, conv_all, w, slots))
+                return native.delta_rule_step(q, k, v, g, beta, rec_all, slots, gate_per_channel=True)
             y, cs = la.causal_conv1d_update(mixed, conv_all[slots], w)
             conv_all[slots] = cs.to(conv_all.dtype)
             q, k, v = split(y)

@@ -52,6 +52,10 @@ def lib():
     L.sglb_page_table_scatter.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     L.sglb_resolve_future.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
     L.sglb_decode_num_splits.argtypes = [c_int, c_int, c_int]
+    L.sglb_delta_rule_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    L.sglb_conv1d_update.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                     c_void_p]
     L.sglb_mla_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]
     L.sglb_paged_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
@@ -251,6 +255,33 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
                                    _stream()), "paged_extend")
     return out
+
+
+def delta_rule_step(q, k, v, g, beta, state_pool, slots, gate_per_channel=False, l2norm=True):
+    """One recurrent step per request, state updated in place.  `q, k [B, Hqk, Dk]`, `v [B, H, Dv]` bf16,
+    `g [B, H]` (or `[B, H, Dk]`) and `beta [B, H]` fp32, `state_pool [slots, H, Dk, Dv]` fp32,
+    `slots [B]` int64 -> `o [B, H, Dv]` bf16."""
+    B, H, Dv = v.shape
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    g, beta = g.float().contiguous(), beta.float().contiguous()
+    assert state_pool.dtype == torch.float32 and state_pool.is_contiguous() and slots.dtype == torch.int64
+    out = torch.empty_like(v)
+    _check(lib().sglb_delta_rule_step(_p(q), _p(k), _p(v), _p(g), _p(beta), _p(state_pool), _p(slots), _p(out), B, H,
+                                      q.shape[1], q.shape[2], Dv, int(gate_per_channel), int(l2norm), _stream()),
+           "delta_rule_step")
+    return out
+
+
+def conv1d_update(x, state_pool, weight, slots, silu=True):
+    """Short causal convolution of one new input per request; `state_pool [slots, C, K-1]` (bf16 or fp32)
+    is shifted in place.  `x [B, C]` bf16, `weight [C, K]` bf16 -> `y [B, C]` bf16."""
+    B, C = x.shape
+    x, weight = x.contiguous(), weight.contiguous()
+    assert state_pool.is_contiguous() and state_pool.dtype in (torch.bfloat16, torch.float32) and slots.dtype == torch.int64
+    y = torch.empty_like(x)
+    _check(lib().sglb_conv1d_update(_p(x), _p(state_pool), _p(weight), _p(slots), _p(y), B, C, weight.shape[1],
+                                    int(silu), int(state_pool.dtype == torch.bfloat16), _stream()), "conv1d_update")
+    return y
 
 
 def mla_decode_supported(q_latent, q_pe, kv_buffer, kv_lora_rank, page_size) -> bool:

@@ -352,3 +352,44 @@ def test_mla_decode(native, P, H):
     from sglang_jax_b200 import ops
     got = ops.mla_paged_attention(q_lat, q_pe, cache, pt, rows, sl, P, scale, 512, max_seq_len=max(seqs))
     _close(got, expect, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("Dk,Dv,H,Hqk,per_channel", [(128, 128, 8, 4, False), (64, 128, 4, 4, False), (128, 128, 4, 4, True),
+                                                        (96, 64, 6, 2, True)])
+def test_delta_rule_step_and_conv_update(native, Dk, Dv, H, Hqk, per_channel):
+    """In-place recurrent decode kernels vs the fp32 PyTorch statements (GDN scalar gate with shared q/k
+    heads, KDA per-channel gate), slots scattered through the pool, untouched slots left alone."""
+    from sglang_jax_b200.ops import linear_attention as la
+    B, n_slots = 5, 9
+    g0 = torch.Generator(device="cuda").manual_seed(60)
+    q, k, v = _bf16(B, Hqk, Dk, seed=61), _bf16(B, Hqk, Dk, seed=62), _bf16(B, H, Dv, seed=63)
+    gate = -torch.rand((B, H, Dk) if per_channel else (B, H), device="cuda", generator=g0)
+    beta = torch.rand(B, H, device="cuda", generator=g0)
+    pool = torch.randn(n_slots, H, Dk, Dv, device="cuda", generator=g0) * 0.1
+    slots = torch.tensor([7, 2, 5, 1, 8], device="cuda")
+    before = pool.clone()
+    r = H // Hqk
+    qe, ke = q.repeat_interleave(r, 1), k.repeat_interleave(r, 1)
+    if per_channel:
+        want_o, want_S = la.kda_recurrent(qe[:, None], ke[:, None], v[:, None], gate[:, None], beta[:, None], before[slots])
+        want_o = want_o[:, 0]
+    else:
+        want_o, want_S = la.recurrent_gated_delta_rule_step(qe, ke, v, gate, beta, before[slots])
+    got = native.delta_rule_step(q, k, v, gate, beta, pool, slots, gate_per_channel=per_channel)
+    torch.cuda.synchronize()
+    _close(got, want_o, 2e-2, 2e-2)
+    assert torch.allclose(pool[slots], want_S, atol=2e-3, rtol=2e-3)
+    rest = [i for i in range(n_slots) if i not in slots.tolist()]
+    assert torch.equal(pool[rest], before[rest])
+    # short convolution
+    C, K = 3 * Hqk * Dk, 4
+    x, w = _bf16(B, C, seed=64), _bf16(C, K, seed=65)
+    for dt in (torch.bfloat16, torch.float32):
+        cpool = (torch.randn(n_slots, C, K - 1, device="cuda", generator=g0)).to(dt)
+        cb = cpool.clone()
+        want_y, want_state = la.causal_conv1d_update(x, cb[slots], w)
+        y = native.conv1d_update(x, cpool, w, slots)
+        torch.cuda.synchronize()
+        _close(y, want_y, 2e-2, 2e-2)
+        assert torch.allclose(cpool[slots].float(), want_state.to(dt).float(), atol=1e-2)
+        assert torch.equal(cpool[rest], cb[rest])

@@ -249,3 +249,50 @@ def test_deepseek_mla_decode_kernel_in_model(tmp_path):
     native.check_status()
     assert g_ids.tolist() == e_ids.tolist()
     assert _rel(d_n.next_token_logits, d_r.next_token_logits) < 4e-2
+
+
+def test_qwen3_next_decode_with_recurrent_kernels(tmp_path):
+    """Hybrid Gated-DeltaNet model on the GPU: a decode step through the in-place recurrent kernels
+    equals the same step through the PyTorch statements, including the updated state pools."""
+    import json
+    from sglang_jax_b200 import ops
+    from sglang_jax_b200.ops import native
+    cfg = dict(architectures=["Qwen3NextForCausalLM"], model_type="qwen3_next", hidden_size=512, intermediate_size=1024,
+               num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+               vocab_size=1024, max_position_embeddings=4096, full_attention_interval=2, linear_num_key_heads=2,
+               linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128, linear_conv_kernel_dim=4,
+               partial_rotary_factor=0.25, num_experts=0, tie_word_embeddings=False, torch_dtype="bfloat16",
+               layer_types=["linear_attention", "full_attention"] * 2)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    runner, _ = _runner(str(tmp_path), load_format="dummy", disable_cuda_graph=True, disable_radix_cache=True)
+    lens = [5, 64, 130]
+    out, ids, _ = runner.forward(_extend_batch(runner, lens))
+    toks = ids.tolist()
+    pool = runner.recurrent_pool
+    conv0, rec0 = pool.conv_state.clone(), pool.recurrent_state.clone()
+    calls = {"n": 0}
+    orig = native.delta_rule_step
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+
+    native.delta_rule_step = counted
+    try:
+        dbatch = _decode_batch(runner, lens, toks)
+        d_n, _, _ = runner.forward(dbatch, skip_sample=True)
+    finally:
+        native.delta_rule_step = orig
+    assert calls["n"] == 2                                     # the two linear-attention layers
+    conv_n, rec_n = pool.conv_state.clone(), pool.recurrent_state.clone()
+    pool.conv_state.copy_(conv0)
+    pool.recurrent_state.copy_(rec0)
+    ops.set_force_reference(True)
+    try:
+        d_r, _, _ = runner.forward(dbatch, skip_sample=True)
+    finally:
+        ops.set_force_reference(False)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert _rel(d_n.next_token_logits, d_r.next_token_logits) < 4e-2
+    assert _rel(rec_n, pool.recurrent_state) < 2e-2 and _rel(conv_n, pool.conv_state) < 2e-2
