@@ -77,6 +77,18 @@ def bench_gemm():
         gbs = byts / t / 1e6
         roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3   # ms at the roofline
         print(f"{f'{M}x{N}x{K}':>28} {label:>22} {t:9.4f} {tfl:9.1f} {gbs:8.0f} {100 * roof / t:6.1f}% {tt:9.4f} {tt / t:8.2f}")
+    print(f"{'fp8 e4m3 (per-token x per-channel scales)':>51} {'fp8 ms':>9} {'TFLOP/s':>9} {'GB/s':>8} {'bf16 ms':>9}")
+    for M, N, K, label in [(8192, 10240, 5120, "qkv prefill tp1"), (8192, 51200, 5120, "gate_up prefill tp1"),
+                           (128, 10240, 5120, "qkv decode tp1"), (128, 51200, 5120, "gate_up decode tp1"),
+                           (128, 5120, 25600, "down decode tp1"), (16, 51200, 5120, "gate_up bs16")]:
+        xq = torch.randn(M, K, device="cuda").to(torch.float8_e4m3fn)
+        wq = (torch.randn(N, K, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+        sx, sw = torch.rand(M, device="cuda") + 0.5, torch.rand(N, device="cuda") + 0.5
+        x, w = xq.to(torch.bfloat16), wq.to(torch.bfloat16)
+        t = timeit(lambda: native.gemm_fp8(xq, wq, sx, sw))
+        tb = timeit(lambda: native.linear(x, w))
+        byts = 1.0 * (M * K + N * K) + 2.0 * M * N
+        print(f"{f'{M}x{N}x{K}':>28} {label:>22} {t:9.4f} {2.0 * M * N * K / t / 1e9:9.1f} {byts / t / 1e6:8.0f} {tb:9.4f}")
     torch.cuda.synchronize()
     native.check_status()
     print(f"(roofline = slower of FLOPs / {tf} TFLOP/s and bytes / {hbm} GB/s, {src})")

@@ -76,6 +76,8 @@ struct Params {
   int rs_world, rs_rank, rs_rows_per;
   unsigned long long* debug_stamps;   // optional [16] globaltimer stamps of CTA 0 (profiling aid)
   int l2_hints;                       // decode mode: stream weights evict-first, keep the token tile evict-last
+  const float* scale_x;               // fp8: per-token activation scale [M]
+  const float* scale_w;               // fp8: per-output-channel weight scale [N]
 };
 
 __device__ __forceinline__ __nv_bfloat16* out_ptr(const Params& p, int tok, int gn) {
@@ -211,11 +213,15 @@ struct SegIter {
   }
 };
 
-template <int BN, int MODE>
+// FP8: both operands are e4m3 bytes (128 per swizzle row instead of 64 bf16, so the byte layout of a
+// stage is unchanged), `tcgen05.mma.kind::f8f6f4` accumulates in fp32 and the epilogue multiplies by
+// `scale_x[token] * scale_w[channel]` (per-token activation scale, per-channel weight scale).
+template <int BN, int MODE, bool FP8 = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const Params p) {
   using C = Cfg<BN>;
+  constexpr int kBKE = FP8 ? 2 * BK : BK;       // elements per K block (128 bytes either way)
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -283,11 +289,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           mbar_expect_tx(fb, C::kStageBytes);
           uint8_t* sa = stage_base + stage * C::kStageBytes;
           if (MODE == 1 && p.l2_hints) {
-            tma_load_2d_hint(smem_u32(sa), &tmap_a, fb, kb * BK, sg.a_row, pol_a);
-            tma_load_2d_hint(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, sg.b_row, pol_b);
+            tma_load_2d_hint(smem_u32(sa), &tmap_a, fb, kb * kBKE, sg.a_row, pol_a);
+            tma_load_2d_hint(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * kBKE, sg.b_row, pol_b);
           } else {
-            tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * BK, sg.a_row);
-            tma_load_2d(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * BK, sg.b_row);
+            tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * kBKE, sg.a_row);
+            tma_load_2d(smem_u32(sa + C::kStageBytesA), &tmap_b, fb, kb * kBKE, sg.b_row);
           }
           if (++stage == C::kStages) {
             stage = 0;
@@ -300,7 +306,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1);
+      constexpr uint32_t idesc = FP8 ? make_idesc(BM, BN, 0, 0) : make_idesc(BM, BN, 1, 1);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -331,7 +337,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // advance 16 bf16 = 32 bytes along K inside the swizzle row: +2 in 16-byte units
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if constexpr (FP8) umma_f8(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty_bar[stage]));
           if (++stage == C::kStages) {
@@ -365,12 +372,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // are 16-byte vectors covering whole 64-byte row segments
         const int gm0 = sg.m0 + q * 32;
         const int gn0 = sg.n0 + c0;
+        float sx = 1.f;
+        if constexpr (FP8) sx = (gm0 + lane) < sg.m_limit ? p.scale_x[gm0 + lane] : 0.f;
 #pragma unroll
         for (int j = 0; j < C::CW / 8; ++j) {
           float g[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             g[e] = f[j * 8 + e];
+            if constexpr (FP8) {
+              const int gn = gn0 + j * 8 + e;
+              g[e] *= sx * (gn < p.N ? p.scale_w[gn] : 0.f);
+            }
             if (p.bias != nullptr) {
               const int gn = gn0 + j * 8 + e;
               if (gn < p.N) g[e] += __bfloat162float(p.bias[gn]);
@@ -404,8 +417,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(staging);
         const int gn_row = sg.n0 + row;
         const float b = (p.bias != nullptr && gn_row < p.N) ? __bfloat162float(p.bias[gn_row]) : 0.f;
+        if constexpr (FP8) {
+          const float sw = gn_row < p.N ? p.scale_w[gn_row] : 0.f;
 #pragma unroll
-        for (int e = 0; e < C::CW; ++e) st[e * BM + row] = __float2bfloat16(f[e] + b);
+          for (int e = 0; e < C::CW; ++e) {
+            const int tok = sg.m0 + c0 + e;
+            st[e * BM + row] = __float2bfloat16(f[e] * sw * (tok < sg.m_limit ? p.scale_x[tok] : 0.f) + b);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < C::CW; ++e) st[e * BM + row] = __float2bfloat16(f[e] + b);
+        }
         named_bar_sync(2, kEpiThreads);
 #pragma unroll
         for (int v = 0; v < C::CW * (BM / 8) / kEpiThreads; ++v) {
@@ -603,10 +625,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool FP8 = false>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN>;
-  auto* kern = gemm_bf16_kernel<BN, MODE>;
+  auto* kern = gemm_bf16_kernel<BN, MODE, FP8>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -647,7 +669,18 @@ int sglb_gemm_max_counters(int N) { return (N + 127) / 128 + 8; }
 // force_mode: -1 auto, 0 tokens-on-M, 1 weights-on-M.  force_splits: 0 auto.
 int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
                         void* workspace, size_t workspace_bytes, int* counters, int force_mode, int force_splits,
-                        void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream);
+                        void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream,
+                        const float* scale_x = nullptr, const float* scale_w = nullptr);
+
+// out[M,N] (bf16) = (x_q[M,K] . w_q[N,K]^T) * scale_x[M] * scale_w[N] + bias with e4m3 operands
+// (per-token activation scales, per-output-channel weight scales; K a multiple of 16).
+int sglb_gemm_fp8(const void* x_q, const void* w_q, const float* scale_x, const float* scale_w, const void* bias,
+                  void* out, int M, int N, int K, void* workspace, size_t workspace_bytes, int* counters,
+                  cudaStream_t stream) {
+  if (scale_x == nullptr || scale_w == nullptr || K % 16 != 0) return -sglb::kBadArgument;
+  return sglb_gemm_bf16_impl(x_q, w_q, bias, out, M, N, K, workspace, workspace_bytes, counters, -1, 0, nullptr, 0, 0,
+                             stream, scale_x, scale_w);
+}
 
 int sglb_gemm_bf16(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, void* workspace,
                    size_t workspace_bytes, int* counters, int force_mode, int force_splits, cudaStream_t stream) {
@@ -681,11 +714,15 @@ void sglb_gemm_set_debug_stamps(void* dev_ptr) { g_debug_stamps = static_cast<un
 
 int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
                         void* workspace, size_t workspace_bytes, int* counters, int force_mode, int force_splits,
-                        void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream) {
+                        void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream,
+                        const float* scale_x, const float* scale_w) {
   using namespace sglb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (N % 8)) return -kBadArgument;
-  const int kb_total = (K + BK - 1) / BK;
+  const bool fp8 = scale_x != nullptr;
+  const int eb = fp8 ? 1 : 2;                          // operand element bytes
+  const int bke = fp8 ? 2 * BK : BK;                   // elements per 128-byte K block
+  const int kb_total = (K + bke - 1) / bke;
   const int sms = sm_count();
   // Decode-sized batches: both operand assignments stream the weights once; they differ in how many
   // activation bytes each K block re-reads from L2 per weight byte (tokens-on-M with 256 weight rows
@@ -710,6 +747,8 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
   p.splits = 1;
   p.debug_stamps = g_debug_stamps;
   p.l2_hints = gemm_l2_hints();
+  p.scale_x = scale_x;
+  p.scale_w = scale_w;
   if (rs_world > 0) {
     p.rs_world = rs_world;
     p.rs_rank = rs_rank;
@@ -724,8 +763,8 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
                        ? 256 : 128;
     p.tiles_a = (M + BM - 1) / BM;
     p.tiles_b = (N + bn - 1) / bn;
-    if (!encode_tmap_2d(&ta, x, K, M, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
-    if (!encode_tmap_2d(&tb, w, K, N, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
+    if (!encode_tmap_2d(&ta, x, K, M, static_cast<uint64_t>(K) * eb, bke, BM, eb)) return -100;
+    if (!encode_tmap_2d(&tb, w, K, N, static_cast<uint64_t>(K) * eb, bke, bn, eb)) return -101;
     int grid = min(p.tiles_a * p.tiles_b, sms);
     if (M <= 256 && force_splits <= 0 && workspace != nullptr && counters != nullptr) {
       // decode-sized: stream-K so that every SM streams the same number of weight bytes
@@ -742,7 +781,8 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
         grid = (total + upc - 1) / upc;
       }
     }
-    err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
+    if (fp8) err = bn == 256 ? launch<256, 0, true>(ta, tb, p, grid, stream) : launch<128, 0, true>(ta, tb, p, grid, stream);
+    else err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
   } else {
     const int bn = pick_bn_tokens(M);
     p.tiles_a = (N + BM - 1) / BM;
@@ -776,14 +816,24 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
       grid = min(p.tiles_a * splits, sms);
     }
     p.splits = splits;
-    if (!encode_tmap_2d(&ta, w, K, N, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
-    if (!encode_tmap_2d(&tb, x, K, M, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
-    switch (bn) {
-      case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
-      case 32: err = launch<32, 1>(ta, tb, p, grid, stream); break;
-      case 64: err = launch<64, 1>(ta, tb, p, grid, stream); break;
-      case 128: err = launch<128, 1>(ta, tb, p, grid, stream); break;
-      default: err = launch<256, 1>(ta, tb, p, grid, stream); break;
+    if (!encode_tmap_2d(&ta, w, K, N, static_cast<uint64_t>(K) * eb, bke, BM, eb)) return -100;
+    if (!encode_tmap_2d(&tb, x, K, M, static_cast<uint64_t>(K) * eb, bke, bn, eb)) return -101;
+    if (fp8) {
+      switch (bn) {
+        case 16: err = launch<16, 1, true>(ta, tb, p, grid, stream); break;
+        case 32: err = launch<32, 1, true>(ta, tb, p, grid, stream); break;
+        case 64: err = launch<64, 1, true>(ta, tb, p, grid, stream); break;
+        case 128: err = launch<128, 1, true>(ta, tb, p, grid, stream); break;
+        default: err = launch<256, 1, true>(ta, tb, p, grid, stream); break;
+      }
+    } else {
+      switch (bn) {
+        case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
+        case 32: err = launch<32, 1>(ta, tb, p, grid, stream); break;
+        case 64: err = launch<64, 1>(ta, tb, p, grid, stream); break;
+        case 128: err = launch<128, 1>(ta, tb, p, grid, stream); break;
+        default: err = launch<256, 1>(ta, tb, p, grid, stream); break;
+      }
     }
   }
   return err == cudaSuccess ? 0 : static_cast<int>(err);

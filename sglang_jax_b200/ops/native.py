@@ -52,6 +52,8 @@ def lib():
     L.sglb_page_table_scatter.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     L.sglb_resolve_future.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
     L.sglb_decode_num_splits.argtypes = [c_int, c_int, c_int]
+    L.sglb_gemm_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                c_size_t, c_void_p, c_void_p]
     L.sglb_delta_rule_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     L.sglb_conv1d_update.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -255,6 +257,30 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
                                    _stream()), "paged_extend")
     return out
+
+
+def gemm_fp8_supported(xq, wq) -> bool:
+    return (xq.dtype == torch.float8_e4m3fn and wq.dtype == torch.float8_e4m3fn and xq.shape[-1] % 16 == 0
+            and wq.shape[0] % 8 == 0 and wq.is_contiguous() and wq.data_ptr() % 16 == 0)
+
+
+def gemm_fp8(xq, wq, scale_x, scale_w, bias=None, out_dtype=torch.bfloat16):
+    """`(xq [M, K] . wq [N, K]^T) * scale_x [M] * scale_w [N] + bias` with e4m3 operands on the tcgen05
+    `kind::f8f6f4` path (fp32 accumulation), bf16 result."""
+    assert out_dtype == torch.bfloat16
+    K, N = xq.shape[-1], wq.shape[0]
+    x2 = xq.reshape(-1, K).contiguous()
+    M = x2.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
+    if M == 0:
+        return out.view(*xq.shape[:-1], N)
+    sx = scale_x.reshape(-1).float().contiguous()
+    sw = scale_w.reshape(-1).float().contiguous()
+    assert sx.numel() == M and sw.numel() == N
+    sc = gemm_scratch(xq.device)
+    _check(lib().sglb_gemm_fp8(_p(x2), _p(wq), _p(sx), _p(sw), _p(bias), _p(out), M, N, K, _p(sc.workspace), sc.bytes,
+                               _p(sc.counters), _stream()), "gemm_fp8")
+    return out.view(*xq.shape[:-1], N)
 
 
 def delta_rule_step(q, k, v, g, beta, state_pool, slots, gate_per_channel=False, l2norm=True):

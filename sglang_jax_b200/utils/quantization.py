@@ -93,6 +93,15 @@ class QuantizedWeight(nn.Module):
     def linear(self, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
         """`x @ W^T` with the activation rounded through the recipe's activation dtype, fp32 accumulate."""
         from .. import ops
+        if (self.act_dtype == torch.float8_e4m3fn and self.qweight.dtype == torch.float8_e4m3fn and self.block_size is None
+                and self.scale.numel() == self.qweight.shape[0] and x.is_cuda and self.out_dtype == torch.bfloat16
+                and not ops._FORCE_REFERENCE):
+            # W8A8 e4m3 with per-channel weight scales and per-token activation scales: fp8 tensor-core GEMM
+            native = ops._native()
+            if native.gemm_fp8_supported(self.qweight, self.qweight) and x.shape[-1] % 16 == 0:
+                xq, xs = quantize_activation(x.reshape(-1, x.shape[-1]), self.act_dtype, None)
+                y = native.gemm_fp8(xq, self.qweight, xs, self.scale, bias)
+                return y.view(*x.shape[:-1], self.qweight.shape[0])
         if self.act_dtype is not None and self.act_dtype in _QMAX:
             xq, xs = quantize_activation(x.reshape(-1, x.shape[-1]), self.act_dtype,
                                          self.block_size[1] if self.block_size else None)

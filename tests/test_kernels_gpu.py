@@ -393,3 +393,23 @@ def test_delta_rule_step_and_conv_update(native, Dk, Dv, H, Hqk, per_channel):
         _close(y, want_y, 2e-2, 2e-2)
         assert torch.allclose(cpool[slots].float(), want_state.to(dt).float(), atol=1e-2)
         assert torch.equal(cpool[rest], cb[rest])
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 1024, 512), (5, 256, 4096), (300, 384, 1040), (1, 5120, 5120), (1024, 2048, 2048)])
+def test_gemm_fp8_per_token_per_channel(native, M, N, K):
+    """e4m3 x e4m3 tcgen05 GEMM with per-token / per-channel scales vs the fp32 product of the same
+    quantised operands (decode and prefill tilings, ragged M, K not a multiple of the 128-byte block)."""
+    from sglang_jax_b200.utils.quantization import quantize_activation, quantize_tensor
+    g = torch.Generator(device="cuda").manual_seed(70)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    bias = _bf16(N, seed=71)
+    xq, xs = quantize_activation(x, torch.float8_e4m3fn)
+    wq, ws = quantize_tensor(w, torch.float8_e4m3fn, "per_channel")
+    want = (xq.float() @ wq.float().t()) * xs * ws.t() + bias.float()
+    got = native.gemm_fp8(xq, wq.contiguous(), xs, ws, bias)
+    torch.cuda.synchronize()
+    native.check_status()
+    _close(got, want, 2e-2, 2e-2)
+    full = x @ w.t() + bias.float()
+    assert ((got.float() - full).norm() / full.norm()).item() < 0.08       # and close to the unquantised product
