@@ -359,10 +359,20 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             sp = SamplingParams()
         if not getattr(sp, "stop_strs", None) and sp.stop_strs is None:
             sp.normalize(self.tokenizer)
+        extra_key = recv.extra_key
+        if recv.mm_inputs and recv.mm_inputs.get("input_embedding") is not None:
+            # placeholder tokens look the same for every image / clip: key the prefix cache by the media too
+            tag = recv.mm_inputs.get("hash")
+            if tag is None:
+                import hashlib
+                import torch as _t
+                emb = _t.as_tensor(recv.mm_inputs["input_embedding"]).detach().cpu().contiguous()
+                tag = hashlib.sha1(emb.view(_t.uint8).numpy().tobytes()).hexdigest()[:16]
+            extra_key = f"{extra_key or ''}|mm:{tag}"
         req = Req(recv.rid, recv.text, recv.input_ids, sp, return_logprob=bool(recv.return_logprob),
                   top_logprobs_num=recv.top_logprobs_num or 0, token_ids_logprob=recv.token_ids_logprob,
                   stream=recv.stream, lora_id=recv.lora_id, eos_token_ids=self.model_config.hf_eos_token_id,
-                  vocab_size=self.vocab_size, extra_key=recv.extra_key, dp_rank=recv.dp_rank,
+                  vocab_size=self.vocab_size, extra_key=extra_key, dp_rank=recv.dp_rank,
                   return_hidden_states=recv.return_hidden_states,
                   return_routed_experts=bool(recv.return_routed_experts),
                   return_output_logprob_only=bool(recv.return_output_logprob_only),

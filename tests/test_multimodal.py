@@ -364,8 +364,14 @@ def test_qwen2_5_vl_image_prompt_matches_hf_through_the_engine(tmp_path):
                            vision_start_token_id=VS, vision_end_token_id=VE, tie_word_embeddings=False)
     torch.manual_seed(0)
     hf = HF(cfg).float().eval()
-    for p in hf.parameters():
-        p.data.normal_(0, 0.08) if p.dim() > 1 else p.data.uniform_(0.8, 1.2)
+    for n, p in hf.named_parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.08)
+        elif n.endswith("bias"):
+            p.data.normal_(0, 0.02)
+        else:
+            p.data.uniform_(0.8, 1.2)
+    hf.lm_head.weight.data.normal_(0, 0.5)                 # spread the logits so that greedy tokens vary
     path = tmp_path / "qwen25vl"
     path.mkdir()
     save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(path / "model.safetensors"))
@@ -378,8 +384,13 @@ def test_qwen2_5_vl_image_prompt_matches_hf_through_the_engine(tmp_path):
     ids = [5, 9, 33, VS] + [IMG] * 6 + [VE, 41, 42, 7, 8]
     n_new = 8
     with torch.no_grad():
+        # `mm_token_type_ids` is what makes the HF model compute the 3-D rotary positions itself
         want = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, image_grid_thw=grid,
+                           mm_token_type_ids=(torch.tensor([ids]) == IMG).int(),
                            max_new_tokens=n_new, do_sample=False)[0, len(ids):].tolist()
+        flat = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, image_grid_thw=grid,
+                           max_new_tokens=n_new, do_sample=False)[0, len(ids):].tolist()
+        assert flat != want                                   # the positions matter for this model
         want_text = hf.generate(input_ids=torch.tensor([[3, 4, 5, 6, 7, 8, 9]]), max_new_tokens=n_new,
                                 do_sample=False)[0, 7:].tolist()
     vit = Qwen2_5_VisionTransformer(cfg.vision_config, dtype=torch.float32)
@@ -397,12 +408,19 @@ def test_qwen2_5_vl_image_prompt_matches_hf_through_the_engine(tmp_path):
     for chunk in (None, 8):
         ps.reset_state()
         eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=4, skip_tokenizer_init=True,
-                     max_total_tokens=1024, enable_single_process=True, chunked_prefill_size=chunk,
-                     disable_radix_cache=True)
+                     max_total_tokens=1024, enable_single_process=True, chunked_prefill_size=chunk)
         try:
             outs = eng.generate(input_ids=[ids, [3, 4, 5, 6, 7, 8, 9]], sampling_params=sp, mm_inputs=[mm, None])
             assert outs[0]["output_ids"] == want, (chunk, outs[0]["output_ids"], want)
             assert outs[1]["output_ids"] == want_text
+            # the prefix cache is keyed by the media: the same image hits, another image (same token ids) does not
+            again = eng.generate(input_ids=ids, sampling_params=sp, mm_inputs=mm)
+            assert again["output_ids"] == want and again["meta_info"]["cached_tokens"] >= 12
+            emb2 = emb.clone()
+            emb2[torch.tensor(ids) == IMG] = img.flip(0)
+            other = eng.generate(input_ids=ids, sampling_params=sp, mm_inputs=dict(mm, input_embedding=emb2))
+            assert other["meta_info"]["cached_tokens"] == 0 and other["output_ids"] != want
+            assert len(set(want)) >= 2
         finally:
             eng.shutdown()
 
@@ -495,8 +513,14 @@ def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
                                     vision_start_token_id=294, position_id_per_seconds=25)
     torch.manual_seed(0)
     hf = HF._from_config(cfg, attn_implementation="eager").float().eval()
-    for p in hf.parameters():
-        p.data.normal_(0, 0.08) if p.dim() > 1 else p.data.uniform_(0.8, 1.2)
+    for n, p in hf.named_parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.08)
+        elif n.endswith("bias"):
+            p.data.normal_(0, 0.02)
+        else:
+            p.data.uniform_(0.8, 1.2)
+    hf.lm_head.weight.data.normal_(0, 0.5)                 # spread the logits so that greedy tokens vary
     path = tmp_path / "omni"
     path.mkdir()
     save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(path / "model.safetensors"))
@@ -516,6 +540,7 @@ def test_qwen3_omni_thinker_image_and_audio_prompt_matches_hf(tmp_path):
     with torch.no_grad():
         want = hf.generate(**kw, max_new_tokens=n_new, do_sample=False)[0, len(ids):].tolist()
         pos, delta = hf.get_rope_index(inp, grid, None, torch.ones_like(inp), False, torch.tensor([n_frames]), None)
+    assert len(set(want)) >= 2
     sd = hf.state_dict()
     vit = Qwen3OmniMoeVisionEncoder(cfg.vision_config, dtype=torch.float32)
     vit.load_weights(sd.items())
