@@ -406,6 +406,7 @@ def _run_dummy(cfg: dict, tmp_path, name: str, prompts, n=6, **kw):
     b = _generate(path, prompts, n=n, load_format="dummy", chunked_prefill_size=32, **kw)
     c = [_generate(path, [p], n=n, load_format="dummy", **kw)[0] for p in prompts]
     assert a == b == c, (a, b, c)
+    assert len({t for o in a for t in o}) > 2, a          # a collapsed model would pass the invariance trivially
     return a
 
 
