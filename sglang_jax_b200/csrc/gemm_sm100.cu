@@ -94,6 +94,7 @@ struct Seg {
   int a_row, b_row;     // TMA row coordinates of the A / B operand tiles
   int m0, m_limit;      // first output token row of the tile, exclusive bound of valid token rows
   int n0;               // first output column of the tile
+  int w_off;            // offset of this tile's weight rows in `scale_w` (grouped: group * N)
 };
 
 // Two decompositions share the kernel:
@@ -124,6 +125,7 @@ struct SegIter {
       s.n0 = s.ta * BM;
     }
     s.m_limit = p.M;
+    s.w_off = 0;
   }
   __device__ bool next(const Params& p, Seg& s) {
     if (p.group_offsets != nullptr) return MODE == 0 ? next_grouped_tokens_on_m(p, s) : next_grouped_weights_on_m(p, s);
@@ -181,6 +183,7 @@ struct SegIter {
       s.slot = blockIdx.x - first_cta;
       s.n_contrib = last_cta - first_cta + 1;
       s.a_row = g * p.N + s.ta * BM;
+      s.w_off = g * p.N;
       s.b_row = row_lo;
       s.m0 = row_lo;
       s.m_limit = min(row_hi, row_lo + BN);
@@ -206,6 +209,7 @@ struct SegIter {
     s.n_contrib = 1;
     s.a_row = row0;
     s.b_row = g * p.N + s.tb * BN;
+    s.w_off = g * p.N;
     s.m0 = row0;
     s.m_limit = min(p.group_offsets[g + 1], row0 + BM);
     s.n0 = s.tb * BN;
@@ -382,7 +386,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             g[e] = f[j * 8 + e];
             if constexpr (FP8) {
               const int gn = gn0 + j * 8 + e;
-              g[e] *= sx * (gn < p.N ? p.scale_w[gn] : 0.f);
+              g[e] *= sx * (gn < p.N ? p.scale_w[sg.w_off + gn] : 0.f);
             }
             if (p.bias != nullptr) {
               const int gn = gn0 + j * 8 + e;
@@ -418,7 +422,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int gn_row = sg.n0 + row;
         const float b = (p.bias != nullptr && gn_row < p.N) ? __bfloat162float(p.bias[gn_row]) : 0.f;
         if constexpr (FP8) {
-          const float sw = gn_row < p.N ? p.scale_w[gn_row] : 0.f;
+          const float sw = gn_row < p.N ? p.scale_w[sg.w_off + gn_row] : 0.f;
 #pragma unroll
           for (int e = 0; e < C::CW; ++e) {
             const int tok = sg.m0 + c0 + e;
@@ -996,17 +1000,23 @@ int sglb_gemm_bf16_noalloc_status(int* out4) {
 // The reference's counterpart is the Megablox grouped matmul
 // (python/sgl_jax/srt/kernels/gmm/megablox_gmm_kernel/gmm.py:311).
 // ---------------------------------------------------------------------------------------------
-extern "C" int sglb_grouped_gemm_bf16(const void* x, const void* w, void* out, const int* group_offsets,
-                                       const int* tile_group, const int* tile_row0, const int* num_token_tiles,
-                                       int rows, int N, int K, int groups, void* workspace, size_t workspace_bytes,
-                                       int* counters, cudaStream_t stream) {
+static int grouped_gemm_impl(const void* x, const void* w, void* out, const int* group_offsets, const int* tile_group,
+                             const int* tile_row0, const int* num_token_tiles, int rows, int N, int K, int groups,
+                             void* workspace, size_t workspace_bytes, int* counters, cudaStream_t stream,
+                             const float* scale_x, const float* scale_w) {
   using namespace sglb;
   if (rows <= 0 || groups <= 0) return 0;
   if ((K % 8) || (N % 8)) return -kBadArgument;
-  const int kb_total = (K + BK - 1) / BK;
+  const bool fp8 = scale_x != nullptr;
+  const int eb = fp8 ? 1 : 2;
+  const int bke = fp8 ? 2 * BK : BK;
+  if (fp8 && K % 16) return -kBadArgument;
+  const int kb_total = (K + bke - 1) / bke;
   const int sms = sm_count();
   Params p{};
   p.l2_hints = gemm_l2_hints();
+  p.scale_x = scale_x;
+  p.scale_w = scale_w;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.workspace = static_cast<float*>(workspace);
   p.counters = counters;
@@ -1041,14 +1051,24 @@ extern "C" int sglb_grouped_gemm_bf16(const void* x, const void* w, void* out, c
     const int grid = (total + upc - 1) / upc;
     // weights [groups*N, K] on the A operand; when N is not a multiple of 128 the last tile of a
     // group reads rows of the next group, which are masked at the store (gn < N).
-    if (!encode_tmap_2d(&ta, w, K, static_cast<uint64_t>(groups) * N, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
-    if (!encode_tmap_2d(&tb, x, K, rows, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
-    switch (bn) {
-      case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
-      case 32: err = launch<32, 1>(ta, tb, p, grid, stream); break;
-      case 64: err = launch<64, 1>(ta, tb, p, grid, stream); break;
-      case 128: err = launch<128, 1>(ta, tb, p, grid, stream); break;
-      default: err = launch<256, 1>(ta, tb, p, grid, stream); break;
+    if (!encode_tmap_2d(&ta, w, K, static_cast<uint64_t>(groups) * N, static_cast<uint64_t>(K) * eb, bke, BM, eb)) return -100;
+    if (!encode_tmap_2d(&tb, x, K, rows, static_cast<uint64_t>(K) * eb, bke, bn, eb)) return -101;
+    if (fp8) {
+      switch (bn) {
+        case 16: err = launch<16, 1, true>(ta, tb, p, grid, stream); break;
+        case 32: err = launch<32, 1, true>(ta, tb, p, grid, stream); break;
+        case 64: err = launch<64, 1, true>(ta, tb, p, grid, stream); break;
+        case 128: err = launch<128, 1, true>(ta, tb, p, grid, stream); break;
+        default: err = launch<256, 1, true>(ta, tb, p, grid, stream); break;
+      }
+    } else {
+      switch (bn) {
+        case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
+        case 32: err = launch<32, 1>(ta, tb, p, grid, stream); break;
+        case 64: err = launch<64, 1>(ta, tb, p, grid, stream); break;
+        case 128: err = launch<128, 1>(ta, tb, p, grid, stream); break;
+        default: err = launch<256, 1>(ta, tb, p, grid, stream); break;
+      }
     }
   } else {
     if (tile_group == nullptr || tile_row0 == nullptr || num_token_tiles == nullptr) return -kBadArgument;
@@ -1058,10 +1078,30 @@ extern "C" int sglb_grouped_gemm_bf16(const void* x, const void* w, void* out, c
     p.num_token_tiles = num_token_tiles;
     p.tiles_a = rows / BM + groups;       // upper bound of token tiles
     p.tiles_b = (N + bn - 1) / bn;
-    if (!encode_tmap_2d(&ta, x, K, rows, static_cast<uint64_t>(K) * 2, BK, BM, 2)) return -100;
-    if (!encode_tmap_2d(&tb, w, K, static_cast<uint64_t>(groups) * N, static_cast<uint64_t>(K) * 2, BK, bn, 2)) return -101;
+    if (!encode_tmap_2d(&ta, x, K, rows, static_cast<uint64_t>(K) * eb, bke, BM, eb)) return -100;
+    if (!encode_tmap_2d(&tb, w, K, static_cast<uint64_t>(groups) * N, static_cast<uint64_t>(K) * eb, bke, bn, eb)) return -101;
     const int grid = min(p.tiles_a * p.tiles_b, sms);
-    err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
+    if (fp8) err = bn == 256 ? launch<256, 0, true>(ta, tb, p, grid, stream) : launch<128, 0, true>(ta, tb, p, grid, stream);
+    else err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
   }
   return err == cudaSuccess ? 0 : static_cast<int>(err);
+}
+
+extern "C" int sglb_grouped_gemm_bf16(const void* x, const void* w, void* out, const int* group_offsets,
+                                       const int* tile_group, const int* tile_row0, const int* num_token_tiles,
+                                       int rows, int N, int K, int groups, void* workspace, size_t workspace_bytes,
+                                       int* counters, cudaStream_t stream) {
+  return grouped_gemm_impl(x, w, out, group_offsets, tile_group, tile_row0, num_token_tiles, rows, N, K, groups,
+                           workspace, workspace_bytes, counters, stream, nullptr, nullptr);
+}
+
+// e4m3 operands: `x_q [rows, K]` with per-row scales `scale_x [rows]`, `w_q [groups * N, K]` with per-row
+// (= per expert output channel) scales `scale_w [groups * N]`; bf16 output.
+extern "C" int sglb_grouped_gemm_fp8(const void* x_q, const void* w_q, const float* scale_x, const float* scale_w,
+                                      void* out, const int* group_offsets, const int* tile_group, const int* tile_row0,
+                                      const int* num_token_tiles, int rows, int N, int K, int groups, void* workspace,
+                                      size_t workspace_bytes, int* counters, cudaStream_t stream) {
+  if (scale_x == nullptr || scale_w == nullptr) return -sglb::kBadArgument;
+  return grouped_gemm_impl(x_q, w_q, out, group_offsets, tile_group, tile_row0, num_token_tiles, rows, N, K, groups,
+                           workspace, workspace_bytes, counters, stream, scale_x, scale_w);
 }

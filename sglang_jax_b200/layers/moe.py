@@ -52,6 +52,8 @@ class FusedMoE(nn.Module):
                                       requires_grad=False)
         self.workspace = None
         self.routed_experts_capturer = None
+        self.dtype = dtype
+        self.fp8 = False
 
     def weight_loader(self, param, w, shard_id: str, expert_id: int):
         """`shard_id` in {"gate", "up", "down"}; `w` is the full `[out, in]` tensor of one expert."""
@@ -66,17 +68,44 @@ class FusedMoE(nn.Module):
             src = w if self.expert_parallel or self.tp_size == 1 else w.narrow(1, self.tp_rank * I, I)
             param.data[local].copy_(src)
 
-    def quantize_(self, dtype, block_size=None):
-        """Round the expert weights through `dtype` with per-channel or block scales.  The values
-        are stored de-quantised in the compute dtype (the grouped GEMM runs in bf16), so this
-        reproduces the numerics of a quantised checkpoint without a separate kernel path."""
+    def quantize_(self, dtype, block_size=None, activation_dtype=None):
+        """Quantise the expert weights to `dtype` with per-channel or block scales.
+
+        W8A8 e4m3 with per-channel scales keeps real fp8 storage (`w13_q`, `w2_q` + fp32 scales): the
+        bf16 tensors are released and the forward runs the grouped fp8 tensor-core GEMMs with dynamic
+        per-token activation scales.  Every other recipe stores the values de-quantised in the compute
+        dtype, which reproduces the numerics of a quantised checkpoint on the bf16 grouped GEMM."""
         from ..utils.quantization import dequantize_tensor, quantize_tensor
         gran = "block" if block_size else "per_channel"
-        for p in (self.w13_weight, self.w2_weight):
-            for e in range(p.shape[0]):
-                q, s = quantize_tensor(p.data[e], dtype, gran, block_size)
-                p.data[e].copy_(dequantize_tensor(q, s, block_size, p.dtype))
+        fp8_storage = (dtype == torch.float8_e4m3fn and activation_dtype == torch.float8_e4m3fn and not block_size
+                       and self.w13_weight.dtype == torch.bfloat16 and self.activation == "silu"
+                       and self.w13_weight.shape[-1] % 16 == 0 and self.w2_weight.shape[-1] % 16 == 0)
+        if fp8_storage:
+            for name in ("w13", "w2"):
+                p = getattr(self, f"{name}_weight")
+                q = torch.empty(p.shape, dtype=dtype, device=p.device)
+                sc = torch.empty(p.shape[:2], dtype=torch.float32, device=p.device)
+                for e in range(p.shape[0]):
+                    qe, se = quantize_tensor(p.data[e], dtype, "per_channel")
+                    q[e].copy_(qe)
+                    sc[e].copy_(se.view(-1))
+                setattr(self, f"{name}_q", nn.Parameter(q, requires_grad=False))
+                setattr(self, f"{name}_scale", nn.Parameter(sc, requires_grad=False))
+                setattr(self, f"{name}_weight", None)
+            self.fp8 = True
+        else:
+            for p in (self.w13_weight, self.w2_weight):
+                for e in range(p.shape[0]):
+                    q, s = quantize_tensor(p.data[e], dtype, gran, block_size)
+                    p.data[e].copy_(dequantize_tensor(q, s, block_size, p.dtype))
         self.quantized = True
+
+    def _bf16_weights(self):
+        """Expert weights in the compute dtype (de-quantised on the fly under fp8 storage)."""
+        if not self.fp8:
+            return self.w13_weight, self.w2_weight
+        return ((self.w13_q.float() * self.w13_scale[..., None]).to(self.dtype),
+                (self.w2_q.float() * self.w2_scale[..., None]).to(self.dtype))
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 add: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -89,21 +118,50 @@ class FusedMoE(nn.Module):
             pairs = x.shape[0] * topk_ids.shape[1]
             if self.workspace is None or self.workspace.max_pairs < pairs:
                 self.workspace = moe_native.MoeWorkspace(max(pairs, 2048), self.num_local_experts, x.device)
+            if self.fp8:
+                return moe_native.fused_experts_fp8(x, self.w13_q, self.w13_scale, self.w2_q, self.w2_scale,
+                                                    topk_weights, topk_ids, self.expert_start, self.workspace, add,
+                                                    out)
             return moe_native.fused_experts(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids,
                                             self.expert_start, self.workspace, add, out)
-        if self.activation == "silu":
+        if self.fp8:
+            y = _fp8_reference_experts(x, self, topk_weights, topk_ids)
+            if add is not None:
+                y = (y.float() + add.float()).to(y.dtype)
+        elif self.activation == "silu":
             y = ops.fused_experts(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids, self.expert_start, None,
                                   add)
         else:
             from ..ops import reference
-            y = reference.moe_forward(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids, self.expert_start,
-                                      act=self.activation)
+            y = reference.moe_forward(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids, self.expert_start, act=self.activation)
             if add is not None:
                 y = (y.float() + add.float()).to(y.dtype)
         if out is not None:
             out.copy_(y)
             return out
         return y
+
+
+def _fp8_reference_experts(x, moe: "FusedMoE", topk_weights, topk_ids):
+    """Plain PyTorch statement of the W8A8 expert FFN (per-token activation scales, per-channel weight
+    scales, fp32 accumulation): the oracle of the fp8 kernels and the CPU path of fp8-stored experts."""
+    from ..utils.quantization import quantize_activation
+    T, H = x.shape
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    I = moe.local_intermediate
+    for e in range(moe.num_local_experts):
+        tok, slot = (topk_ids == e + moe.expert_start).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xq, sx = quantize_activation(x[tok], torch.float8_e4m3fn)
+        h = (xq.float() @ moe.w13_q[e].float().t()) * sx * moe.w13_scale[e][None, :]
+        h = h.to(x.dtype).float()
+        a = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
+        aq, sa = quantize_activation(a, torch.float8_e4m3fn)
+        y = (aq.float() @ moe.w2_q[e].float().t()) * sa * moe.w2_scale[e][None, :]
+        y = y.to(x.dtype).float()
+        out.index_add_(0, tok, y * topk_weights[tok, slot].float()[:, None])
+    return out.to(x.dtype)
 
 
 EPMoE = FusedMoE

@@ -23,6 +23,9 @@ def _lib():
         L.sglb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         L.sglb_grouped_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
+        L.sglb_grouped_gemm_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                                            c_void_p, c_void_p]
         _bound = True
     return L
 
@@ -88,6 +91,44 @@ def grouped_gemm(x_sorted, w, ws: MoeWorkspace, rows: int):
                                        sc.counters.data_ptr(), native._stream())
     native._check(rc, "grouped_gemm")
     return out
+
+
+def grouped_gemm_fp8(xq_sorted, scale_x, wq, scale_w, ws: MoeWorkspace, rows: int):
+    """e4m3 grouped GEMM on the tcgen05 `kind::f8f6f4` path: `xq_sorted [rows, K]` with per-row scales
+    `scale_x [rows]`, `wq [E_local, N, K]` with per-output-channel scales `scale_w [E_local, N]` -> bf16 `[rows, N]`."""
+    E, N, K = wq.shape
+    assert xq_sorted.dtype == torch.float8_e4m3fn and wq.dtype == torch.float8_e4m3fn
+    assert scale_x.dtype == torch.float32 and scale_w.dtype == torch.float32
+    assert scale_x.numel() >= rows and scale_w.numel() == E * N and K % 16 == 0
+    out = torch.empty((rows, N), dtype=torch.bfloat16, device=xq_sorted.device)
+    sc = native.gemm_scratch(xq_sorted.device)
+    rc = _lib().sglb_grouped_gemm_fp8(xq_sorted.data_ptr(), wq.data_ptr(), scale_x.data_ptr(), scale_w.data_ptr(),
+                                      out.data_ptr(), ws.offsets.data_ptr(), ws.tile_group.data_ptr(),
+                                      ws.tile_row0.data_ptr(), ws.counts.data_ptr() + 4, rows, N, K, E,
+                                      sc.workspace.data_ptr(), sc.bytes, sc.counters.data_ptr(), native._stream())
+    native._check(rc, "grouped_gemm_fp8")
+    return out
+
+
+def fused_experts_fp8(x, w13_q, w13_scale, w2_q, w2_scale, topk_weights, topk_ids, expert_start: int = 0,
+                      ws: MoeWorkspace | None = None, add=None, out=None):
+    """W8A8 e4m3 routed-expert FFN: align -> gather -> per-token quantise -> grouped fp8 GEMM (gate|up) ->
+    fused SiLU*mul + per-token quantise -> grouped fp8 GEMM (down) -> weighted combine.  Weights are per-channel
+    quantised (`w13_q [E_local, 2I, H]`, `w13_scale [E_local, 2I]`, `w2_q [E_local, H, I]`, `w2_scale [E_local, H]`)."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E_local = w13_q.shape[0]
+    pairs = T * k
+    if ws is None or ws.max_pairs < pairs:
+        ws = MoeWorkspace(pairs, E_local, x.device)
+    moe_align(topk_ids, expert_start, E_local, ws)
+    xs = moe_gather(x, ws, pairs)
+    valid = ws.counts[0:1]
+    xq, sx = native.quant_fp8_rows(xs, valid_rows=valid)
+    h = grouped_gemm_fp8(xq, sx, w13_q, w13_scale, ws, pairs)
+    aq, sa = native.quant_fp8_rows(h, gated=True, valid_rows=valid)
+    y = grouped_gemm_fp8(aq, sa, w2_q, w2_scale, ws, pairs)
+    return moe_combine(y, topk_weights, ws, T, add=add, out=out)
 
 
 def moe_combine(y_sorted, topk_weights, ws: MoeWorkspace, T: int, add=None, out=None):

@@ -54,6 +54,7 @@ def lib():
     L.sglb_decode_num_splits.argtypes = [c_int, c_int, c_int]
     L.sglb_gemm_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                 c_size_t, c_void_p, c_void_p]
+    L.sglb_quant_fp8_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p]
     L.sglb_delta_rule_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     L.sglb_conv1d_update.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -257,6 +258,22 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
                                    _stream()), "paged_extend")
     return out
+
+
+def quant_fp8_rows(x, gated: bool = False, valid_rows=None):
+    """Per-token dynamic e4m3 quantisation of `x [T, K]` bf16 -> `(q [T, K], scale [T])`.  `gated`: `x` is
+    `[T, 2K]` and `silu(x[:, :K]) * x[:, K:]` is quantised.  `valid_rows`: device int32 scalar; rows at or
+    past it are skipped (their outputs stay uninitialised)."""
+    assert x.dtype == torch.bfloat16
+    x = x.contiguous()
+    K = x.shape[-1] // (2 if gated else 1)
+    T = x.numel() // x.shape[-1]
+    q = torch.empty((*x.shape[:-1], K), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    _check(lib().sglb_quant_fp8_rows(_p(q), _p(s), _p(x), T, K, int(gated),
+                                     valid_rows.data_ptr() if valid_rows is not None else None, _stream()),
+           "quant_fp8_rows")
+    return q, s
 
 
 def gemm_fp8_supported(xq, wq) -> bool:

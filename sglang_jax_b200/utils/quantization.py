@@ -99,7 +99,11 @@ class QuantizedWeight(nn.Module):
             # W8A8 e4m3 with per-channel weight scales and per-token activation scales: fp8 tensor-core GEMM
             native = ops._native()
             if native.gemm_fp8_supported(self.qweight, self.qweight) and x.shape[-1] % 16 == 0:
-                xq, xs = quantize_activation(x.reshape(-1, x.shape[-1]), self.act_dtype, None)
+                x2 = x.reshape(-1, x.shape[-1])
+                if x2.dtype == torch.bfloat16 and x2.shape[-1] % 8 == 0:
+                    xq, xs = native.quant_fp8_rows(x2)
+                else:
+                    xq, xs = quantize_activation(x2, self.act_dtype, None)
                 y = native.gemm_fp8(xq, self.qweight, xs, self.scale, bias)
                 return y.view(*x.shape[:-1], self.qweight.shape[0])
         if self.act_dtype is not None and self.act_dtype in _QMAX:
@@ -140,7 +144,7 @@ def apply_moe_quantization(model: nn.Module, cfg: QuantizationConfig) -> int:
     n = 0
     for _, mod in model.named_modules():
         if isinstance(mod, FusedMoE) and not getattr(mod, "quantized", False):
-            mod.quantize_(cfg.moe_weight_dtype, cfg.moe_weight_block_size)
+            mod.quantize_(cfg.moe_weight_dtype, cfg.moe_weight_block_size, cfg.moe_activation_dtype)
             n += 1
     return n
 

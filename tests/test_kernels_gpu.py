@@ -208,6 +208,54 @@ def test_fused_experts(native, T, E, E_local, e0, k, H, I):
     _close(got, exp, 3e-2, 3e-2)
 
 
+@pytest.mark.parametrize("T,K,gated", [(7, 512, False), (130, 5120, False), (33, 768, True), (3, 25600, False), (64, 2048, True)])
+def test_quant_fp8_rows(native, T, K, gated):
+    """Per-token e4m3 quantisation kernel (plain and fused SiLU-gate) vs the PyTorch statement."""
+    from sglang_jax_b200.utils.quantization import quantize_activation
+    x = _bf16(T, 2 * K if gated else K, scale=3.0, seed=72)
+    x[0, :8] = 0.0
+    a = torch.nn.functional.silu(x[:, :K].float()) * x[:, K:].float() if gated else x.float()
+    q, s = native.quant_fp8_rows(x, gated=gated)
+    torch.cuda.synchronize()
+    eq, es = quantize_activation(a, torch.float8_e4m3fn)
+    torch.testing.assert_close(s, es.view(-1), rtol=2e-3 if gated else 1e-6, atol=0)
+    back, want = q.float() * s[:, None], eq.float() * es
+    assert q.dtype == torch.float8_e4m3fn and torch.isfinite(back).all()
+    # one e4m3 step (2^-3 relative) at most where a rounding boundary fell the other way
+    assert ((back - want).abs() <= 0.126 * want.abs() + 1e-6 + s[:, None] * 2 ** -9).all()
+    assert ((back - want).abs() > 1e-6).float().mean().item() < (0.02 if gated else 1e-3)
+    valid = torch.tensor([T // 2], dtype=torch.int32, device="cuda")
+    q2, s2 = native.quant_fp8_rows(x, gated=gated, valid_rows=valid)
+    assert torch.equal(q2[: T // 2].view(torch.uint8), q[: T // 2].view(torch.uint8))
+
+
+@pytest.mark.parametrize("T,E,E_local,e0,k,H,I", [
+    (5, 16, 16, 0, 2, 256, 128), (40, 32, 8, 8, 4, 512, 384), (128, 128, 16, 32, 8, 2048, 768),
+    (700, 32, 32, 0, 4, 512, 256), (1500, 64, 16, 16, 8, 1024, 768),
+])
+def test_fused_experts_fp8(native, T, E, E_local, e0, k, H, I):
+    """W8A8 e4m3 expert FFN (grouped fp8 tcgen05 GEMMs, decode and prefill tilings, expert-parallel slices)
+    vs the PyTorch statement on the same quantised weights, and near the unquantised bf16 result."""
+    from sglang_jax_b200.layers.moe import FusedMoE, _fp8_reference_experts
+    moe = FusedMoE(E, H, I, tp_size=E // E_local, tp_rank=e0 // E_local, ep_size=E // E_local).cuda()
+    assert moe.num_local_experts == E_local and moe.expert_start == e0
+    moe.w13_weight.data.copy_(_bf16(E_local, 2 * I, H, scale=0.05, seed=51))
+    moe.w2_weight.data.copy_(_bf16(E_local, H, I, scale=0.05, seed=52))
+    x = _bf16(T, H, seed=50)
+    logits = torch.randn(T, E, device="cuda", generator=torch.Generator(device="cuda").manual_seed(53))
+    tw, ids = ref.topk_route(logits, k)
+    full = ref.moe_forward(x.float(), moe.w13_weight.float(), moe.w2_weight.float(), tw, ids, e0)
+    moe.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)
+    assert moe.fp8 and moe.w13_weight is None and moe.w13_q.dtype == torch.float8_e4m3fn
+    got = moe(x, tw, ids)
+    torch.cuda.synchronize()
+    native.check_status()
+    want = _fp8_reference_experts(x, moe, tw, ids)
+    assert ((got.float() - want.float()).norm() / want.float().norm()).item() < 0.02
+    _close(got, want, 6e-2, 6e-2)
+    assert ((got.float() - full).norm() / full.norm()).item() < 0.1
+
+
 def test_argmax_unaligned_rows(native):
     logits = torch.randn(7, 1003, device="cuda").to(torch.bfloat16)     # odd rows start off a 16-byte boundary
     assert torch.equal(native.argmax(logits).long(), torch.argmax(logits.float(), dim=-1))

@@ -130,3 +130,32 @@ def test_quantized_linear_is_close_to_dense():
         y = QuantizedWeight(q, s, bs, act, torch.float32).linear(x)
         rel = (y - want).norm() / want.norm()
         assert rel < 0.06, (dtype, gran, rel)
+
+
+def test_fused_moe_fp8_storage_keeps_only_quantised_experts():
+    """A W8A8 e4m3 per-channel recipe replaces the expert tensors with fp8 storage + fp32 scales and the
+    forward stays close to the unquantised experts; block recipes keep de-quantised compute-dtype storage."""
+    from sglang_jax_b200.layers.moe import FusedMoE
+    from sglang_jax_b200.ops import reference
+    torch.manual_seed(0)
+    moe = FusedMoE(4, 64, 32, tp_size=1, tp_rank=0, ep_size=1)
+    moe.w13_weight.data.normal_(0, 0.1)
+    moe.w2_weight.data.normal_(0, 0.1)
+    x = torch.randn(12, 64).bfloat16()
+    ids = torch.stack([torch.randperm(4)[:2] for _ in range(12)]).int()
+    w = torch.rand(12, 2)
+    add = torch.randn(12, 64).bfloat16()
+    want = reference.moe_forward(x, moe.w13_weight, moe.w2_weight, w, ids, 0).float() + add.float()
+    blocky = FusedMoE(4, 64, 32, tp_size=1, tp_rank=0, ep_size=1)
+    blocky.load_state_dict(moe.state_dict())
+    blocky.quantize_(torch.float8_e4m3fn, (16, 16), torch.float8_e4m3fn)
+    assert not blocky.fp8 and blocky.w13_weight.dtype == torch.bfloat16
+    moe.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)
+    assert moe.fp8 and moe.w13_weight is None and moe.w2_weight is None
+    assert sorted(n for n, _ in moe.named_parameters()) == ["w13_q", "w13_scale", "w2_q", "w2_scale"]
+    assert moe.w13_q.dtype == torch.float8_e4m3fn and moe.w13_scale.shape == (4, 64) and moe.w2_scale.shape == (4, 64)
+    got = moe(x, w, ids, add=add).float()
+    assert got.std() > 0.05
+    assert ((got - want).norm() / want.norm()).item() < 0.08
+    w13, w2 = moe._bf16_weights()
+    assert w13.shape == (4, 64, 64) and w2.dtype == torch.bfloat16
