@@ -3,7 +3,7 @@
 `benchmark/kernels/*`): CUDA-event timing after warm-up, L2 flushed between iterations,
 achieved TFLOP/s or GB/s and the fraction of the measured peaks in MEASURED_PEAKS.json.
 
-    python benchmark/kernels/bench_kernels.py gemm attention elementwise
+    python benchmark/kernels/bench_kernels.py gemm attention elementwise moe sampling
 """
 
 from __future__ import annotations
@@ -138,6 +138,52 @@ def bench_attention():
     native.check_status()
 
 
+def bench_moe():
+    """Routed-expert FFN (align, gather, two grouped GEMMs, activation, combine): bf16 vs W8A8 e4m3."""
+    from sglang_jax_b200.layers.moe import FusedMoE
+    from sglang_jax_b200.ops import reference
+    hbm, tf, src = peaks()
+    print(f"{'case':>44} {'bf16 ms':>9} {'fp8 ms':>9} {'bf16 TFLOP/s':>13} {'fp8 TFLOP/s':>12} {'fp8 GB/s':>9}")
+    for T, E, k, H, I, label in [(128, 128, 8, 2048, 768, "qwen3-30b-a3b decode"), (8192, 128, 8, 2048, 768, "qwen3-30b-a3b prefill"),
+                                 (128, 32, 8, 7168, 2048, "deepseek-v3 ep8 decode"), (8192, 32, 8, 7168, 2048, "deepseek-v3 ep8 prefill")]:
+        moe = FusedMoE(E, H, I, tp_size=1, tp_rank=0, ep_size=1).cuda()
+        moe.w13_weight.data.normal_(0, 0.02)
+        moe.w2_weight.data.normal_(0, 0.02)
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        tw, ids = reference.topk_route(torch.randn(T, E, device="cuda"), k)
+        ids = ids.int()
+        tb = timeit(lambda: moe(x, tw, ids))
+        moe.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)
+        t8 = timeit(lambda: moe(x, tw, ids))
+        flops = 2.0 * T * k * 3 * I * H
+        touched = min(E, T * k)
+        byts = touched * 3.0 * I * H
+        print(f"{f'T={T} E={E} k={k} H={H} I={I} {label}':>44} {tb:9.4f} {t8:9.4f} {flops / tb / 1e9:13.1f} {flops / t8 / 1e9:12.1f} {byts / t8 / 1e6:9.0f}")
+        del moe
+    torch.cuda.synchronize()
+    native.check_status()
+
+
+def bench_sampling():
+    """Filtered sampling at the Qwen3 vocabulary: one radix-select kernel vs the sort-based PyTorch statement."""
+    from sglang_jax_b200.ops import reference
+    print(f"{'case':>44} {'kernel ms':>10} {'torch ms':>9}")
+    V = 151936
+    for B, k, p, mp, label in [(128, 50, 0.95, 0.0, "top-k 50 top-p .95"), (128, V, 0.9, 0.0, "top-p .9"),
+                               (128, V, 1.0, 0.0, "temperature only"), (128, 20, 1.0, 0.05, "top-k 20 min-p .05"),
+                               (16, 50, 0.95, 0.0, "top-k 50 top-p .95")]:
+        logits = torch.randn(B, V, device="cuda") * 2
+        one = lambda v, dt=torch.float32: torch.full((B,), v, device="cuda", dtype=dt)
+        t, ks, ps, mps = one(0.7), one(k, torch.int32), one(p), one(mp)
+        seeds, pos = torch.arange(B, device="cuda", dtype=torch.int32), torch.arange(B, device="cuda", dtype=torch.int32)
+        tk = timeit(lambda: native.sample_filtered(logits, t, ks, ps, mps, seeds, pos), flush=False)
+        tt = timeit(lambda: reference.multinomial_with_seed(
+            reference.top_k_top_p_min_p_probs(logits, t, ks.long(), ps, mps), seeds, pos), iters=5, flush=False)
+        print(f"{f'B={B} V={V} {label}':>44} {tk:10.4f} {tt:9.4f}")
+    torch.cuda.synchronize()
+    native.check_status()
+
+
 def bench_elementwise():
     hbm, tf, src = peaks()
     T, H, I = 8192, 5120, 25600
@@ -155,4 +201,4 @@ if __name__ == "__main__":
     which = sys.argv[1:] or ["gemm", "attention", "elementwise"]
     torch.manual_seed(0)
     for w in which:
-        {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[w]()
+        {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "moe": bench_moe, "sampling": bench_sampling}[w]()

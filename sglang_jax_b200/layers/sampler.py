@@ -93,24 +93,54 @@ class Sampler(nn.Module):
             ids = ops.argmax(logits)
             probs_for_lp = None
         else:
-            lf = logits.float()
-            if meta.need_filter:
-                probs = reference.top_k_top_p_min_p_probs(lf, meta.temperatures, meta.top_ks, meta.top_ps, meta.min_ps)
+            if ops.use_native_sampling(logits):
+                ids = self._sample_native(logits, meta)
             else:
-                probs = torch.softmax(lf / meta.temperatures.view(-1, 1).clamp_min(1e-6), dim=-1)
-            if meta.sampling_seeds is not None or self.enable_deterministic:
-                seeds = meta.sampling_seeds if meta.sampling_seeds is not None else \
-                    torch.full((probs.shape[0],), 42, dtype=torch.int32, device=probs.device)
-                ids = reference.multinomial_with_seed(probs, seeds, meta.positions)
-            else:
-                ids = torch.multinomial(probs, 1, generator=self._generator(probs.device)).squeeze(1)
-            greedy_rows = meta.top_ks <= 1
-            if bool(greedy_rows.any()):
-                ids = torch.where(greedy_rows, torch.argmax(lf, dim=-1), ids)
+                ids = self._sample_reference(logits, meta)
             ids = ids.to(torch.int32)
         self.step += 1
         if meta.return_logprob:
             self.compute_logprobs(logits, ids, logits_output, meta)
+        return ids
+
+    def _seeds_and_positions(self, meta: SamplingMetadata, B: int, device):
+        """Per-row (seed, position) of the hashed Gumbel draw: the request's own seed, a fixed one under
+        `enable_deterministic`, otherwise fresh seeds from this sampler's generator."""
+        if meta.sampling_seeds is not None:
+            seeds = meta.sampling_seeds
+        elif self.enable_deterministic:
+            seeds = torch.full((B,), 42, dtype=torch.int32, device=device)
+        else:
+            seeds = torch.randint(0, 2 ** 31 - 1, (B,), dtype=torch.int32, device=device,
+                                  generator=self._generator(device))
+        positions = meta.positions if meta.positions is not None else \
+            torch.full((B,), self.step, dtype=torch.int32, device=device)
+        return seeds, positions
+
+    def _sample_native(self, logits, meta: SamplingMetadata) -> torch.Tensor:
+        """One kernel: temperature, top-k / top-p / min-p (sort-free radix select) and the hashed Gumbel-max
+        draw; rows with `top_k <= 1` come back as the argmax."""
+        seeds, positions = self._seeds_and_positions(meta, logits.shape[0], logits.device)
+        if logits.stride(-1) != 1:
+            logits = logits.contiguous()
+        seeded = meta.sampling_seeds is not None or self.enable_deterministic
+        return ops._native().sample_filtered(logits, meta.temperatures, meta.top_ks, meta.top_ps, meta.min_ps, seeds,
+                                             positions, request_seeded=seeded)
+
+    def _sample_reference(self, logits, meta: SamplingMetadata) -> torch.Tensor:
+        lf = logits.float()
+        if meta.need_filter:
+            probs = reference.top_k_top_p_min_p_probs(lf, meta.temperatures, meta.top_ks, meta.top_ps, meta.min_ps)
+        else:
+            probs = torch.softmax(lf / meta.temperatures.view(-1, 1).clamp_min(1e-6), dim=-1)
+        if meta.sampling_seeds is not None or self.enable_deterministic:
+            seeds, positions = self._seeds_and_positions(meta, probs.shape[0], probs.device)
+            ids = reference.multinomial_with_seed(probs, seeds, positions)
+        else:
+            ids = torch.multinomial(probs, 1, generator=self._generator(probs.device)).squeeze(1)
+        greedy_rows = meta.top_ks <= 1
+        if bool(greedy_rows.any()):
+            ids = torch.where(greedy_rows, torch.argmax(lf, dim=-1), ids)
         return ids
 
     @staticmethod

@@ -75,6 +75,15 @@ def hash_name(name: str) -> int:
     return h
 
 
+def _apply_dynamic_quantization(model, quant_config):
+    """Dynamic recipes quantise the loaded (or dummy-initialised) bf16 weights in place."""
+    if quant_config is None or quant_config.is_static_checkpoint:
+        return
+    from ..utils.quantization import apply_linear_quantization, apply_moe_quantization
+    n = apply_linear_quantization(model, quant_config) + apply_moe_quantization(model, quant_config)
+    logger.info("quantized %d modules with recipe %s", n, quant_config.name)
+
+
 class DefaultModelLoader:
     def __init__(self, load_format: str = "auto"):
         self.load_format = load_format
@@ -87,10 +96,7 @@ class DefaultModelLoader:
         it = dequant_static_fp8(self._iterator(model_config.model_path), getattr(quant_config, "weight_block_size", None))
         loaded = model.load_weights(it)
         check_all_loaded(model, loaded)
-        if quant_config is not None and not quant_config.is_static_checkpoint:
-            from ..utils.quantization import apply_linear_quantization, apply_moe_quantization
-            n = apply_linear_quantization(model, quant_config) + apply_moe_quantization(model, quant_config)
-            logger.info("quantized %d modules with recipe %s", n, quant_config.name)
+        _apply_dynamic_quantization(model, quant_config)
         return model.eval()
 
     def _iterator(self, path):
@@ -115,6 +121,7 @@ class DummyModelLoader:
             model = cls(model_config.hf_config, dtype=model_config.dtype, quant_config=quant_config) \
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
         initialize_dummy_weights(model, self.seed)
+        _apply_dynamic_quantization(model, quant_config)
         return model.eval()
 
 

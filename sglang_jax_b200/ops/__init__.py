@@ -27,6 +27,11 @@ def use_native(x: torch.Tensor) -> bool:
     return (not _FORCE_REFERENCE) and x.is_cuda and x.dtype == torch.bfloat16
 
 
+def use_native_sampling(logits: torch.Tensor) -> bool:
+    return (not _FORCE_REFERENCE) and logits.is_cuda and logits.dim() == 2 \
+        and logits.dtype in (torch.float32, torch.bfloat16)
+
+
 def _native():
     from . import native
     return native

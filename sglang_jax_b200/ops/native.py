@@ -54,6 +54,8 @@ def lib():
     L.sglb_decode_num_splits.argtypes = [c_int, c_int, c_int]
     L.sglb_gemm_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                 c_size_t, c_void_p, c_void_p]
+    L.sglb_sample_filtered.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     L.sglb_quant_fp8_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p]
     L.sglb_delta_rule_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
@@ -258,6 +260,29 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                    Hkv, D, page_size, scale, int(sliding_window or 0), float(soft_cap or 0.0),
                                    _stream()), "paged_extend")
     return out
+
+
+def sample_filtered(logits, temperatures, top_ks, top_ps, min_ps, seeds, positions, return_probs: bool = False,
+                    request_seeded: bool = True):
+    """Temperature / top-k / top-p / min-p filtering and hashed Gumbel-max sampling of `logits [B, V]` (fp32 or
+    bf16, unit stride inside a row) in one kernel -> int32 `[B]` ids (and, with `return_probs`, the filtered
+    renormalised fp32 probabilities).  `request_seeded` keeps the reference's (seed, position, column) hash bit
+    for bit; without it the uniforms come from an avalanche mix of the same inputs."""
+    assert logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
+    B, V = logits.shape
+    dev = logits.device
+    f32 = lambda t: t.to(device=dev, dtype=torch.float32).reshape(-1).contiguous()
+    i32 = lambda t: t.to(device=dev, dtype=torch.int32).reshape(-1).contiguous()
+    temperatures, top_ps, min_ps = f32(temperatures), f32(top_ps), f32(min_ps)
+    top_ks, seeds, positions = i32(top_ks.clamp(max=2 ** 31 - 1)), i32(seeds), i32(positions)
+    for t in (temperatures, top_ps, min_ps, top_ks, seeds, positions):
+        assert t.numel() == B
+    out = torch.empty(B, dtype=torch.int32, device=dev)
+    probs = torch.empty((B, V), dtype=torch.float32, device=dev) if return_probs else None
+    _check(lib().sglb_sample_filtered(_p(out), _p(probs), _p(logits), B, V, logits.stride(0), logits.element_size(),
+                                      _p(temperatures), _p(top_ks), _p(top_ps), _p(min_ps), _p(seeds), _p(positions),
+                                      0 if request_seeded else 1, _stream()), "sample_filtered")
+    return (out, probs) if return_probs else out
 
 
 def quant_fp8_rows(x, gated: bool = False, valid_rows=None):

@@ -256,6 +256,119 @@ def test_fused_experts_fp8(native, T, E, E_local, e0, k, H, I):
     assert ((got.float() - full).norm() / full.norm()).item() < 0.1
 
 
+def _filtered_probs_f64(logits, temps, ks, ps, mps):
+    """Sort-based statement of temperature / top-k / top-p / min-p in float64 (fp32 cumulative sums over a
+    150k vocabulary drift by more than the spacing of the top-p boundary)."""
+    x = logits.double() / temps.double().view(-1, 1).clamp_min(1e-6)
+    probs = torch.softmax(x, dim=-1)
+    sp, si = probs.sort(dim=-1, descending=True)
+    V = probs.shape[-1]
+    keep = torch.arange(V, device=probs.device).view(1, -1) < ks.long().view(-1, 1).clamp(max=V)
+    keep &= (sp.cumsum(-1) - sp) < ps.double().view(-1, 1)
+    keep &= sp >= sp[:, :1] * mps.double().view(-1, 1)
+    keep[:, 0] = True
+    sp = sp * keep
+    sp = sp / sp.sum(-1, keepdim=True)
+    return torch.zeros_like(probs).scatter_(1, si, sp).float()
+
+
+@pytest.mark.parametrize("B,V,dtype", [(24, 151936, torch.float32), (16, 5003, torch.float32), (12, 32000, torch.bfloat16)])
+def test_sample_filtered_matches_sorted_reference(native, B, V, dtype):
+    """Radix-select top-k / top-p / min-p + hashed Gumbel draw vs the sort-based PyTorch statement: same kept
+    set and probabilities, same seeded draw, greedy rows return the argmax."""
+    g = torch.Generator(device="cuda").manual_seed(80)
+    logits = (torch.randn(B, V, device="cuda", generator=g) * 3).to(dtype)
+    temps = torch.rand(B, device="cuda", generator=g) + 0.5
+    ks = torch.randint(2, 300, (B,), device="cuda", generator=g, dtype=torch.int32)
+    ks[::4] = V + 7                                         # top-k off
+    ks[5] = 1                                               # greedy row
+    ps = torch.rand(B, device="cuda", generator=g) * 0.8 + 0.2
+    ps[1::4] = 1.0                                          # top-p off
+    mps = torch.rand(B, device="cuda", generator=g) * 0.05
+    mps[::2] = 0.0
+    ks[2], ps[2], mps[2] = V, 1.0, 0.0                      # no filter at all
+    ks[3], ps[3], mps[3] = V, 1.0, 0.02                     # min-p alone
+    seeds = torch.randint(0, 2 ** 31 - 1, (B,), device="cuda", generator=g, dtype=torch.int32)
+    pos = torch.randint(0, 4096, (B,), device="cuda", generator=g, dtype=torch.int32)
+    ids, probs = native.sample_filtered(logits, temps, ks, ps, mps, seeds, pos, return_probs=True)
+    torch.cuda.synchronize()
+    want = _filtered_probs_f64(logits, temps, ks, ps, mps)
+    live = ks > 1
+    assert torch.equal(ids[~live].long(), logits[~live].float().argmax(-1))
+    torch.testing.assert_close(probs[live].sum(-1), torch.ones(int(live.sum()), device="cuda"), rtol=1e-4, atol=1e-4)
+    if dtype == torch.float32:
+        # a top-p close to 1 puts the boundary among tokens of ~1e-9 probability, where the last bits of the
+        # kernel's fast exp move it by many (negligible) tokens: compare by mass, and exactly on the small vocabulary
+        flips = (probs[live] > 0) != (want[live] > 0)
+        assert float(((probs[live] + want[live]) * flips).sum(-1).max()) < 2e-5
+        assert float((probs[live] - want[live]).abs().sum(-1).max()) < 2e-4
+        same = flips.sum(-1) == 0
+        torch.testing.assert_close(probs[live][same], want[live][same], rtol=2e-3, atol=1e-7)
+        if V < 10000:
+            assert bool(same.all())
+    else:                                                   # bf16 rows are full of ties: all of them are kept
+        assert bool(((want[live] > 0) <= (probs[live] > 0)).all())
+        tie_free = (probs[live] > 0).sum(-1) == (want[live] > 0).sum(-1)
+        torch.testing.assert_close(probs[live][tie_free], want[live][tie_free], rtol=2e-3, atol=1e-7)
+    assert bool((probs[live].gather(1, ids[live].long().view(-1, 1)) > 0).all())
+    drawn = ref.multinomial_with_seed(probs, seeds, pos)
+    assert (drawn[live] == ids[live].long()).float().mean().item() >= 0.9
+    again = native.sample_filtered(logits, temps, ks, ps, mps, seeds, pos)
+    assert torch.equal(again, ids)                          # bit-reproducible
+    other = native.sample_filtered(logits, temps, ks, ps, mps, seeds + 1, pos)
+    assert not torch.equal(other[live], ids[live])
+
+
+def test_sample_filtered_follows_the_distribution(native):
+    """Many rows of one small distribution with different seeds, unseeded-request hash: empirical frequencies
+    match the filtered probabilities (top-p removes the tail)."""
+    base = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -3.0, -3.5, -8.0], device="cuda")
+    B = 20000
+    logits = base.repeat(B, 1)
+    one = lambda v, dt=torch.float32: torch.full((B,), v, device="cuda", dtype=dt)
+    seeds = torch.arange(B, device="cuda", dtype=torch.int32) * 7919 + 13
+    pos = torch.arange(B, device="cuda", dtype=torch.int32) % 97
+    ids = native.sample_filtered(logits, one(0.8), one(8, torch.int32), one(0.9), one(0.0), seeds, pos,
+                                 request_seeded=False)
+    want = ref.top_k_top_p_min_p_probs(base.view(1, -1), one(0.8)[:1], one(8, torch.int64)[:1], one(0.9)[:1], one(0.0)[:1])[0]
+    freq = torch.bincount(ids.long(), minlength=8).float() / B
+    assert bool((freq[want == 0] == 0).all()) and int((want > 0).sum()) < 8
+    torch.testing.assert_close(freq, want, rtol=0.0, atol=0.015)
+
+
+def test_sampler_module_uses_the_sampling_kernel(native):
+    """`Sampler.forward` on the GPU: seeded requests reproduce the PyTorch statement of the same draw, unseeded
+    ones are reproducible per sampler seed, vary between steps and stay inside the top-k set."""
+    from types import SimpleNamespace
+    from sglang_jax_b200 import ops
+    from sglang_jax_b200.layers.sampler import Sampler, SamplingMetadata
+    B, V = 32, 4096
+    g = torch.Generator(device="cuda").manual_seed(90)
+    logits = torch.randn(B, V, device="cuda", generator=g) * 2
+    ks = torch.full((B,), 5, device="cuda", dtype=torch.int32)
+    ks[7] = 1
+    meta = SamplingMetadata(temperatures=torch.full((B,), 0.9, device="cuda"), top_ks=ks,
+                            top_ps=torch.full((B,), 0.95, device="cuda"), min_ps=torch.zeros(B, device="cuda"),
+                            is_all_greedy=False, need_filter=True,
+                            sampling_seeds=torch.arange(B, device="cuda", dtype=torch.int32) + 100,
+                            positions=torch.arange(B, device="cuda", dtype=torch.int32))
+    out = SimpleNamespace(next_token_logits=logits)
+    ids = Sampler()(out, meta)
+    ops.set_force_reference(True)
+    try:
+        want = Sampler()(out, meta)
+    finally:
+        ops.set_force_reference(False)
+    assert ids.dtype == torch.int32 and (ids == want).float().mean().item() >= 0.9   # fast log vs libm at near-ties
+    assert int(ids[7]) == int(logits[7].argmax())
+    meta.sampling_seeds = None
+    a, b = Sampler(rng_seed=3), Sampler(rng_seed=3)
+    first, second = a(out, meta), a(out, meta)
+    assert torch.equal(first, b(out, meta)) and not torch.equal(first, second)
+    top5 = logits.topk(5, dim=-1).indices
+    assert bool((top5 == first.long().view(-1, 1)).any(-1).all())
+
+
 def test_argmax_unaligned_rows(native):
     logits = torch.randn(7, 1003, device="cuda").to(torch.bfloat16)     # odd rows start off a 16-byte boundary
     assert torch.equal(native.argmax(logits).long(), torch.argmax(logits.float(), dim=-1))

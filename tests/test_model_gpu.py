@@ -251,6 +251,61 @@ def test_deepseek_mla_decode_kernel_in_model(tmp_path):
     assert _rel(d_n.next_token_logits, d_r.next_token_logits) < 4e-2
 
 
+def test_qwen3_moe_fp8_recipe_runs_on_grouped_fp8_gemm(tmp_path):
+    """A Qwen3-MoE-shaped model under the dynamic fp8 recipe: experts keep fp8 storage, every MoE layer runs
+    the grouped fp8 GEMM path (prefill eager, decode inside the CUDA graph) and one expert layer in isolation
+    agrees with the PyTorch statement of the same quantised experts."""
+    import json
+    from sglang_jax_b200 import ops
+    from sglang_jax_b200.layers.moe import FusedMoE
+    from sglang_jax_b200.ops import moe_native, native
+    cfg = dict(architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", hidden_size=512, intermediate_size=1024,
+               moe_intermediate_size=256, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+               head_dim=128, num_experts=16, num_experts_per_tok=4, norm_topk_prob=True, decoder_sparse_step=1,
+               mlp_only_layers=[], rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=1024, tie_word_embeddings=False,
+               max_position_embeddings=4096, torch_dtype="bfloat16")
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    runner, _ = _runner(str(tmp_path), load_format="dummy", cuda_graph_max_bs=8, quantization="fp8_qwen3_30b_a3b")
+    moes = [m for m in runner.model.modules() if isinstance(m, FusedMoE)]
+    assert len(moes) == 2 and all(m.fp8 and m.w13_weight is None for m in moes)
+    calls = {"n": 0}
+    orig = moe_native.fused_experts_fp8
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+
+    moe_native.fused_experts_fp8 = counted
+    lens = [5, 64, 130, 300]
+    try:
+        batch = _extend_batch(runner, lens)
+        out, ids, _ = runner.forward(batch)
+        assert calls["n"] == 2
+        dbatch = _decode_batch(runner, lens, ids.tolist())
+        assert runner.cuda_graph_runner.can_run(dbatch)
+        _, g_ids, _ = runner.forward(dbatch)
+        g_ids = g_ids.clone()
+        runner.cuda_graph_runner.enabled = False
+        _, e_ids, _ = runner.forward(dbatch)
+        assert calls["n"] == 4
+    finally:
+        moe_native.fused_experts_fp8 = orig
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.isfinite(out.next_token_logits).all() and out.next_token_logits.float().std() > 1e-3
+    assert g_ids.tolist() == e_ids.tolist()
+    moe = moes[0]
+    x = (torch.randn(77, 512, device="cuda") * 0.5).bfloat16()
+    tw, tid = ops.topk_route(torch.randn(77, 16, device="cuda"), 4)
+    y_n = moe(x, tw, tid)
+    ops.set_force_reference(True)
+    try:
+        y_r = moe(x, tw, tid)
+    finally:
+        ops.set_force_reference(False)
+    assert y_r.float().std() > 0 and _rel(y_n, y_r) < 2e-2
+
+
 def test_qwen3_next_decode_with_recurrent_kernels(tmp_path):
     """Hybrid Gated-DeltaNet model on the GPU: a decode step through the in-place recurrent kernels
     equals the same step through the PyTorch statements, including the updated state pools."""
