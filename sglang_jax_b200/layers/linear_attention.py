@@ -16,6 +16,13 @@ from .layernorm import GatedRMSNorm
 from .linear import ReplicatedLinear
 
 
+def recurrent_slots(fb) -> torch.Tensor:
+    """State slot of every row of the batch: request row + 1 (slot 0 is scratch).  A captured decode step
+    supplies them itself so that its padding rows land on the scratch slot."""
+    slots = fb.extras.get("recurrent_slots")
+    return slots if slots is not None else fb.req_pool_indices.long() + 1
+
+
 def _native_step_ok(x, conv_all, rec_all, dk: int, dv: int) -> bool:
     """Whether a decode step can run the in-place CUDA kernels (`csrc/linear_attn.cu`)."""
     from .. import ops
@@ -67,7 +74,7 @@ class GatedDeltaNet(nn.Module):
         mixed = torch.cat([q, k, v], dim=-1)                             # [T, conv_dim]
         beta = torch.sigmoid(b.float())
         g = -self.A_log.float().exp() * torch.nn.functional.softplus(a.float() + self.dt_bias)
-        slots = fb.req_pool_indices.long() + 1
+        slots = recurrent_slots(fb)
         r = self.nv // self.nk
         T = x.shape[0]
 
@@ -124,7 +131,7 @@ class _RecurrentMixer(nn.Module):
     def _run(self, fb, T, per_seq, per_batch):
         pool = fb.extras["recurrent_pool"]
         conv_all, rec_all = pool.conv_state[self.layer_index], pool.recurrent_state[self.layer_index]
-        slots = fb.req_pool_indices.long() + 1
+        slots = recurrent_slots(fb)
         if fb.forward_mode.is_decode():
             return per_batch(conv_all, rec_all, slots)
         cu = fb.cu_q_lens.tolist()

@@ -806,6 +806,7 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             "total_retracted_reqs": self.total_retracted_reqs,
             "forward_ct": self.forward_ct,
             "cuda_graph_recaptures": self.graph_recapture_count(),
+            "cuda_graph_replays": getattr(getattr(self.tp_worker, "model_runner", None), "graph_replays", 0),
             "precision_tracer": dict(self.precision_tracer_state),
         })
         if self.spec_algorithm is not None and self.spec_num_total_forward_ct:

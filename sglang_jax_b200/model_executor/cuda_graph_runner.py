@@ -48,6 +48,7 @@ class CudaGraphRunner:
         self.copy_event: torch.cuda.Event | None = None
         self.enabled = True
         self.kernels_per_graph = 0
+        self.swa_page_table: torch.Tensor | None = None
         if not sa.disable_precompile:
             self.capture_all()
 
@@ -75,6 +76,23 @@ class CudaGraphRunner:
             page_table=r.req_to_token_pool.page_table, page_size=r.page_size,
             max_seq_len=r.model_config.context_len, token_to_kv_pool=r.token_to_kv_pool,
             attn_backend=r.attn_backend, in_graph=True)
+        if getattr(r, "recurrent_pool", None) is not None:
+            # hybrid linear-attention models: states are updated in place in slot row + 1; padding rows use the
+            # scratch slot 0 (their page-table row index is one past the last request row)
+            rows = v["req_pool_indices"].long()
+            fb.extras["recurrent_pool"] = r.recurrent_pool
+            fb.extras["recurrent_slots"] = torch.where(rows < self.pad_row, rows + 1, torch.zeros_like(rows))
+        pool = r.token_to_kv_pool
+        if hasattr(pool, "swa_pool"):
+            # hybrid sliding-window models: the window layers' page table is derived from the (just updated)
+            # full one through the full -> window slot mapping, rows of this batch only
+            P = r.page_size
+            pt = r.req_to_token_pool.page_table
+            rows = v["req_pool_indices"].long()
+            if self.swa_page_table is None:
+                self.swa_page_table = torch.zeros_like(pt)
+            self.swa_page_table[rows] = (pool.full_to_swa_index_mapping[pt[rows].long() * P] // P).to(pt.dtype)
+            fb.extras["swa_page_table"] = self.swa_page_table
         from ..parallel import state as ps
         comm = ps.get_state().fused_comm
         if comm is not None:
@@ -131,8 +149,7 @@ class CudaGraphRunner:
     # ------------------------------------------------------------------
     def can_run(self, batch: ModelWorkerBatch) -> bool:
         si = batch.sampling_info
-        return (self.enabled and not hasattr(self.runner.token_to_kv_pool, "swa_pool")
-                and getattr(self.runner, "recurrent_pool", None) is None and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
+        return (self.enabled and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
                 and not batch.return_logprob and batch.capture_hidden_mode == 0 and batch.spec_info is None
                 and (si is None or (si.is_all_greedy and si.linear_penalty is None and si.vocab_mask is None
                                     and si.logit_bias is None))

@@ -208,6 +208,8 @@ class ModelRunner:
         self.forward_ct += 1
         if batch.forward_mode.is_idle():
             return None, torch.empty(0, dtype=torch.int32, device=self.device), None
+        if getattr(batch, "recurrent_copies", None) and self.recurrent_pool is not None:
+            self.recurrent_pool.copy_sequence(batch.recurrent_copies)      # prefix-cache checkpoints / clones
         gr = self.cuda_graph_runner
         if gr is not None and gr.can_run(batch):
             return gr.replay(batch)
@@ -224,8 +226,6 @@ class ModelRunner:
                 fb.last_token_indices = None
         if self.server_args is not None and not self.server_args.disable_overlap_schedule:
             fb.input_ids = self.resolve_future_token_ids(fb.input_ids)
-        if getattr(batch, "recurrent_copies", None) and self.recurrent_pool is not None:
-            self.recurrent_pool.copy_sequence(batch.recurrent_copies)      # prefix-cache checkpoints / clones
         comm = ps.get_state().fused_comm
         si = batch.sampling_info
         if (comm is not None and not skip_sample and not batch.return_logprob and si is not None and si.is_all_greedy

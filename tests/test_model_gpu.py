@@ -353,6 +353,57 @@ def test_qwen3_next_decode_with_recurrent_kernels(tmp_path):
     assert _rel(rec_n, pool.recurrent_state) < 2e-2 and _rel(conv_n, pool.conv_state) < 2e-2
 
 
+_QWEN3_NEXT_TINY = dict(
+    architectures=["Qwen3NextForCausalLM"], model_type="qwen3_next", hidden_size=512, intermediate_size=1024,
+    num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+    vocab_size=1024, max_position_embeddings=4096, full_attention_interval=2, linear_num_key_heads=2,
+    linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128, linear_conv_kernel_dim=4,
+    partial_rotary_factor=0.25, num_experts=0, tie_word_embeddings=False, torch_dtype="bfloat16",
+    layer_types=["linear_attention", "full_attention"] * 2)
+_GEMMA2_TINY = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2", hidden_size=512, intermediate_size=1024,
+    num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+    rope_theta=10000.0, vocab_size=1024, tie_word_embeddings=True, max_position_embeddings=4096, sliding_window=48,
+    query_pre_attn_scalar=128, attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
+    hidden_activation="gelu_pytorch_tanh", torch_dtype="bfloat16")
+
+
+@pytest.mark.parametrize("name,cfg,extra", [("qwen3_next", _QWEN3_NEXT_TINY, dict(disable_radix_cache=True)),
+                                            ("gemma2", _GEMMA2_TINY, dict())])
+def test_hybrid_models_decode_inside_cuda_graphs(tmp_path, name, cfg, extra):
+    """Hybrid linear-attention (recurrent state pool) and hybrid sliding-window (dual KV pool) models decode
+    through captured CUDA graphs: the graphs are replayed, nothing is recaptured and greedy output equals the
+    eager engine's, including sequences that run past the window."""
+    import json
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.ops import native
+    from sglang_jax_b200.parallel import state as ps
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    prompts = [list(range(1, 40)), list(range(3, 150)), [7, 9, 11] * 9]
+    outs = {}
+    for graphs in (True, False):
+        ps.reset_state()
+        eng = Engine(model_path=str(tmp_path), device="cuda", dtype="bfloat16", page_size=16, skip_tokenizer_init=True,
+                     max_total_tokens=8192, max_running_requests=8, enable_single_process=True, load_format="dummy",
+                     cuda_graph_max_bs=8, disable_cuda_graph=not graphs, disable_overlap_schedule=True, **extra)
+        try:
+            o = eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 24, "temperature": 0.0,
+                                                                 "ignore_eos": True})
+            outs[graphs] = [x["output_ids"] for x in o]
+            info = eng.get_server_info()["internal_states"][0]
+            assert info["cuda_graph_recaptures"] == 0
+            assert (info["cuda_graph_replays"] >= 20) if graphs else (info["cuda_graph_replays"] == 0)
+        finally:
+            eng.shutdown()
+    torch.cuda.synchronize()
+    native.check_status()
+    assert all(len(x) == 24 for x in outs[True])
+    assert len({t for o in outs[True] for t in o}) > 3
+    # the captured step sizes its attention splits for the longest context, so late tokens may round differently
+    assert all(a[:8] == b[:8] for a, b in zip(outs[True], outs[False])), outs
+    assert sum(a == b for a, b in zip(outs[True], outs[False])) >= 2, outs
+
+
 def test_fp8_recipe_runs_on_the_fp8_gemm(tiny_path):
     """`--quantization fp8` (per-channel e4m3 weights, per-token e4m3 activations): the projections go
     through the fp8 tensor-core GEMM and agree with the same quantised model evaluated in PyTorch."""
