@@ -4,8 +4,9 @@ The reference avoids per-step compilation by padding batches to shape buckets an
 pre-compiling one XLA executable per bucket (`python/sgl_jax/srt/model_executor/
 compilation_manager.py:69-128`), and asserts zero recompiles at serving time.  The B200
 equivalent: one captured CUDA graph per batch-size bucket holding the whole decode step
-(future-token resolve, page-table delta scatter, all layers, LM head, greedy sample,
-future-map store).  A step copies its few integers into the graph's static input buffers
+(future-token resolve, page-table delta scatter, all layers, LM head, sampling,
+future-map store) in two variants: greedy (argmax, reduced across tensor ranks as (max, index) pairs) and
+sampled (temperature / top-k / top-p / min-p through the sampling kernel on the gathered logits).  A step copies its few integers into the graph's static input buffers
 and replays; nothing is captured after warm-up (`graph_recaptures` stays 0 and is
 reported to clients as `cache_miss_count`).
 """
@@ -38,11 +39,19 @@ class CudaGraphRunner:
         dev = runner.device
         self.pad_row = runner.req_to_token_pool.size   # all-zero page-table row -> dummy page 0
         n = self.max_bs
-        # static inputs: ids | positions | out_cache_loc | req_pool | seq_lens | future_slots | delta rows,pos,ids | n_delta
-        self.buf = torch.zeros(6 * n + 3 * MAX_PAGE_DELTAS, dtype=torch.int32, device=dev)
-        self.host = torch.zeros(6 * n + 3 * MAX_PAGE_DELTAS, dtype=torch.int32, pin_memory=True)
-        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
-        self.outputs: dict[int, torch.Tensor] = {}
+        # static inputs: ids | positions | out_cache_loc | req_pool | seq_lens | future_slots | delta rows,pos,ids |
+        # sampling: top_ks | seeds | sample positions | temperatures | top_ps | min_ps (the last three are float bits)
+        self.samp0 = 6 * n + 3 * MAX_PAGE_DELTAS
+        self.buf = torch.zeros(self.samp0 + 6 * n, dtype=torch.int32, device=dev)
+        self.host = torch.zeros(self.samp0 + 6 * n, dtype=torch.int32, pin_memory=True)
+        # keys: batch-size bucket (greedy step) or (bucket, "sampled")
+        self.graphs: dict = {}
+        self.outputs: dict = {}
+        self.seed_rng = np.random.default_rng(int(getattr(sa, "random_seed", 0) or 0) + 7919)
+        # sampled steps gather the vocabulary shards with a library all-gather; that variant is captured for
+        # single-GPU engines only (tensor-parallel engines sample eagerly)
+        from ..parallel import state as ps
+        self.sample_in_graph = ps.tp_size() == 1
         self.pool = None
         self.stream = torch.cuda.Stream(device=dev)
         self.copy_event: torch.cuda.Event | None = None
@@ -61,9 +70,14 @@ class CudaGraphRunner:
                     future_slots=b[5 * n:5 * n + bs],
                     d_rows=b[6 * n:6 * n + MAX_PAGE_DELTAS],
                     d_pos=b[6 * n + MAX_PAGE_DELTAS:6 * n + 2 * MAX_PAGE_DELTAS],
-                    d_ids=b[6 * n + 2 * MAX_PAGE_DELTAS:6 * n + 3 * MAX_PAGE_DELTAS])
+                    d_ids=b[6 * n + 2 * MAX_PAGE_DELTAS:6 * n + 3 * MAX_PAGE_DELTAS],
+                    top_ks=b[self.samp0:self.samp0 + bs], seeds=b[self.samp0 + n:self.samp0 + n + bs],
+                    sample_pos=b[self.samp0 + 2 * n:self.samp0 + 2 * n + bs],
+                    temperatures=b[self.samp0 + 3 * n:self.samp0 + 3 * n + bs].view(torch.float32),
+                    top_ps=b[self.samp0 + 4 * n:self.samp0 + 4 * n + bs].view(torch.float32),
+                    min_ps=b[self.samp0 + 5 * n:self.samp0 + 5 * n + bs].view(torch.float32))
 
-    def _step(self, bs: int) -> torch.Tensor:
+    def _step(self, bs: int, sampled: bool = False) -> torch.Tensor:
         r = self.runner
         v = self._views(bs)
         from ..ops import native
@@ -95,10 +109,15 @@ class CudaGraphRunner:
             fb.extras["swa_page_table"] = self.swa_page_table
         from ..parallel import state as ps
         comm = ps.get_state().fused_comm
-        if comm is not None:
+        if comm is not None and not sampled:
             fb.extras["skip_logits_gather"] = True
         out = r.model(ids, fb)
-        if "vocab_shard" in out.extras:
+        if sampled:
+            # unseeded requests: fresh per-row seeds arrive with the step's inputs; every tensor rank holds the
+            # same gathered logits and the same seeds, so all ranks draw the same tokens
+            tok = native.sample_filtered(out.next_token_logits, v["temperatures"], v["top_ks"], v["top_ps"],
+                                         v["min_ps"], v["seeds"], v["sample_pos"], request_seeded=False)
+        elif "vocab_shard" in out.extras:
             start, vocab = out.extras["vocab_shard"]
             tok = comm.argmax_gather(out.next_token_logits, start, vocab)
         else:
@@ -112,25 +131,28 @@ class CudaGraphRunner:
         # make the padded inputs valid before the warm-up runs
         self._fill_padding(0, self.max_bs)
         with torch.inference_mode():
-            for bs in reversed(self.buckets):
-                torch.cuda.synchronize()
-                s = self.stream
-                s.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(s):
-                    for _ in range(2):
-                        self._step(bs)     # warm-up: lazy inits (function attributes, scratch) happen here
-                torch.cuda.current_stream().wait_stream(s)
-                torch.cuda.synchronize()
-                g = torch.cuda.CUDAGraph()
-                from ..ops import native
-                n0 = native.launch_count
-                with torch.cuda.graph(g, pool=self.pool, stream=s):
-                    out = self._step(bs)
-                # kernels of this library inside one replay (torch's own small ops not counted)
-                self.kernels_per_graph = native.launch_count - n0
-                self.pool = self.pool or g.pool()
-                self.graphs[bs] = g
-                self.outputs[bs] = out
+            for sampled in ((False, True) if self.sample_in_graph else (False,)):
+                for bs in reversed(self.buckets):
+                    torch.cuda.synchronize()
+                    s = self.stream
+                    s.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(s):
+                        for _ in range(2):
+                            self._step(bs, sampled)     # warm-up: lazy inits (function attributes, scratch) happen here
+                    torch.cuda.current_stream().wait_stream(s)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    from ..ops import native
+                    n0 = native.launch_count
+                    with torch.cuda.graph(g, pool=self.pool, stream=s):
+                        out = self._step(bs, sampled)
+                    if not sampled:
+                        # kernels of this library inside one replay (torch's own small ops not counted)
+                        self.kernels_per_graph = native.launch_count - n0
+                    self.pool = self.pool or g.pool()
+                    key = (bs, "sampled") if sampled else bs
+                    self.graphs[key] = g
+                    self.outputs[key] = out
         torch.cuda.synchronize()
 
     def _fill_padding(self, lo: int, hi: int):
@@ -143,27 +165,50 @@ class CudaGraphRunner:
         h[4 * n + lo:4 * n + hi] = 1
         h[5 * n + lo:5 * n + hi] = 0
         h[6 * n:6 * n + MAX_PAGE_DELTAS] = self.pad_row
-        h[6 * n + MAX_PAGE_DELTAS:] = 0
+        h[6 * n + MAX_PAGE_DELTAS:self.samp0] = 0
+        self._fill_sampling_padding(lo, hi)
         self.buf.copy_(self.host, non_blocking=False)
+
+    def _fill_sampling_padding(self, lo: int, hi: int):
+        """Padding rows sample greedily (top_k 1): the cheapest path of the kernel."""
+        n, s0 = self.max_bs, self.samp0
+        h = self.host.numpy()
+        f = h.view(np.float32)
+        h[s0 + lo:s0 + hi] = 1
+        h[s0 + n + lo:s0 + n + hi] = 0
+        h[s0 + 2 * n + lo:s0 + 2 * n + hi] = 0
+        f[s0 + 3 * n + lo:s0 + 3 * n + hi] = 1.0
+        f[s0 + 4 * n + lo:s0 + 4 * n + hi] = 1.0
+        f[s0 + 5 * n + lo:s0 + 5 * n + hi] = 0.0
 
     # ------------------------------------------------------------------
     def can_run(self, batch: ModelWorkerBatch) -> bool:
         si = batch.sampling_info
         return (self.enabled and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
                 and not batch.return_logprob and batch.capture_hidden_mode == 0 and batch.spec_info is None
-                and (si is None or (si.is_all_greedy and si.linear_penalty is None and si.vocab_mask is None
-                                    and si.logit_bias is None))
+                and (si is None or (si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None
+                                    and (si.is_all_greedy or self._can_sample_in_graph(si))))
                 and (batch.page_delta_rows is None or len(batch.page_delta_rows) <= MAX_PAGE_DELTAS)
                 and not any(batch.lora_ids or []) and getattr(batch, "mrope_positions", None) is None)
+
+    def _can_sample_in_graph(self, si) -> bool:
+        """Sampled steps run in a graph when no request carries its own seed (seeded and deterministic runs keep
+        the reference's hash, which the eager sampler applies) and the logits are fp32 / bf16 on this device."""
+        sa = self.runner.server_args
+        return (self.sample_in_graph and si.sampling_seeds is None
+                and not getattr(sa, "enable_deterministic_sampling", False) and si.positions is not None)
 
     def replay(self, batch: ModelWorkerBatch):
         r = self.runner
         bs = len(batch.req_pool_indices)
         bucket = self.buckets[bisect.bisect_left(self.buckets, bs)]
-        if bucket not in self.graphs:
+        si = batch.sampling_info
+        sampled = si is not None and not si.is_all_greedy
+        key = (bucket, "sampled") if sampled else bucket
+        if key not in self.graphs:
             # capture on demand (only when precompile was disabled); counted like a jit cache miss
             r.graph_recaptures += 1
-            self._capture_one(bucket)
+            self._capture_one(bucket, sampled)
         n = self.max_bs
         if self.copy_event is not None:
             self.copy_event.synchronize()     # the previous step's H2D has consumed the pinned buffer
@@ -189,26 +234,38 @@ class CudaGraphRunner:
             h[d0:d0 + nd] = batch.page_delta_rows
             h[d0 + MAX_PAGE_DELTAS:d0 + MAX_PAGE_DELTAS + nd] = batch.page_delta_pos
             h[d0 + 2 * MAX_PAGE_DELTAS:d0 + 2 * MAX_PAGE_DELTAS + nd] = batch.page_delta_ids
+        if sampled:
+            s0 = self.samp0
+            f = h.view(np.float32)
+            h[s0:s0 + bs] = si.top_ks
+            h[s0 + n:s0 + n + bs] = self.seed_rng.integers(0, 2 ** 31 - 1, size=bs, dtype=np.int32)
+            h[s0 + 2 * n:s0 + 2 * n + bs] = si.positions
+            f[s0 + 3 * n:s0 + 3 * n + bs] = si.temperatures
+            f[s0 + 4 * n:s0 + 4 * n + bs] = si.top_ps
+            f[s0 + 5 * n:s0 + 5 * n + bs] = si.min_ps
+            if bucket > bs:
+                self._fill_sampling_padding(bs, bucket)
         self.buf.copy_(self.host, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.copy_event = ev
-        self.graphs[bucket].replay()
+        self.graphs[key].replay()
         r.graph_replays += 1
         r.h2d_bytes_total += self.host.numel() * 4
-        return None, self.outputs[bucket][:bs], None
+        return None, self.outputs[key][:bs], None
 
-    def _capture_one(self, bs: int):
+    def _capture_one(self, bs: int, sampled: bool = False):
         with torch.inference_mode():
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             s = self.stream
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
-                self._step(bs)
+                self._step(bs, sampled)
             torch.cuda.current_stream().wait_stream(s)
             with torch.cuda.graph(g, pool=self.pool, stream=s):
-                out = self._step(bs)
+                out = self._step(bs, sampled)
             self.pool = self.pool or g.pool()
-            self.graphs[bs] = g
-            self.outputs[bs] = out
+            key = (bs, "sampled") if sampled else bs
+            self.graphs[key] = g
+            self.outputs[key] = out

@@ -404,6 +404,48 @@ def test_hybrid_models_decode_inside_cuda_graphs(tmp_path, name, cfg, extra):
     assert sum(a == b for a, b in zip(outs[True], outs[False])) >= 2, outs
 
 
+def test_sampled_decode_runs_inside_cuda_graphs(tiny_path):
+    """Temperature / top-k / top-p requests without their own seed decode through the sampled graph variant
+    (sampling kernel inside the graph): graphs are replayed, nothing is recaptured, two engines with the same
+    seed agree token for token, equal prompts in one batch draw different continuations, and every token lies in
+    the top-k set of an eager forward of its prefix."""
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.ops import native
+    from sglang_jax_b200.parallel import state as ps
+    prompts = [list(range(1, 50)), list(range(1, 50)), [7, 9, 11] * 9, list(range(3, 120))]
+    sp = {"max_new_tokens": 16, "temperature": 1.5, "top_k": 8, "top_p": 0.95, "ignore_eos": True}
+    runs = []
+    for _ in range(2):
+        ps.reset_state()
+        eng = Engine(model_path=tiny_path, device="cuda", dtype="bfloat16", page_size=16, skip_tokenizer_init=True,
+                     max_total_tokens=8192, max_running_requests=8, enable_single_process=True, cuda_graph_max_bs=8,
+                     random_seed=11)
+        try:
+            o = eng.generate(input_ids=prompts, sampling_params=sp)
+            runs.append([x["output_ids"] for x in o])
+            info = eng.get_server_info()["internal_states"][0]
+            assert info["cuda_graph_recaptures"] == 0 and info["cuda_graph_replays"] >= 14
+            greedy = eng.generate(input_ids=prompts[:1], sampling_params={"max_new_tokens": 16, "temperature": 0.0,
+                                                                          "ignore_eos": True})[0]["output_ids"]
+        finally:
+            eng.shutdown()
+    torch.cuda.synchronize()
+    native.check_status()
+    assert runs[0] == runs[1]
+    assert all(len(x) == 16 for x in runs[0])
+    assert runs[0][0] != runs[0][1]                          # same prompt, different per-row seeds
+    assert runs[0][0] != greedy and runs[0][1] != greedy
+    # the last drawn token lies in the top-k set of an eager forward of everything before it (a few ranks of
+    # slack for bf16 rounding between the chunked prefill here and the decode steps there)
+    runner, _ = _runner(tiny_path, disable_cuda_graph=True)
+    for p, o in zip(prompts[2:], runs[0][2:]):
+        seq = p + o[:-1]
+        batch = _extend_batch(runner, [len(seq)])
+        batch.input_ids = np.asarray(seq, np.int32)
+        out, _, _ = runner.forward(batch, skip_sample=True)
+        assert o[-1] in out.next_token_logits[-1].float().topk(12).indices.tolist()
+
+
 def test_fp8_recipe_runs_on_the_fp8_gemm(tiny_path):
     """`--quantization fp8` (per-channel e4m3 weights, per-token e4m3 activations): the projections go
     through the fp8 tensor-core GEMM and agree with the same quantised model evaluated in PyTorch."""
