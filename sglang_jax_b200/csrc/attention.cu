@@ -242,6 +242,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
   const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
+  pdl_wait();
   const int seq = p.seq_lens[b];
   const int* pt_row = p.page_table + static_cast<size_t>(p.req_pool_indices[b]) * p.max_pages;
 
@@ -380,6 +381,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
 template <int D>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                       __nv_bfloat16* __restrict__ out, int num_splits) {
+  pdl_wait();
   const int row = blockIdx.x;   // b * Hq + h
   const float* lse = part_lse + static_cast<size_t>(row) * num_splits;
   float mmax = -INFINITY;
@@ -643,20 +645,20 @@ int sglb_paged_decode(const void* q, void* out, const void* kv_buffer, long long
     static bool cfg = false;
     const int sm = smem_bytes<128>(stages);
     if (!cfg) { cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); cfg = true; }
-    paged_decode_kernel<128><<<grid, kThreads, sm, stream>>>(tm, p, stages);
+    launch_pdl(paged_decode_kernel<128>, grid, dim3(kThreads), sm, stream, tm, p, stages);
     e = cudaGetLastError();
     if (e == cudaSuccess && p.num_splits > 1) {
-      decode_combine_kernel<128><<<B * Hq, 128, 0, stream>>>(part_o, part_lse, p.out, p.num_splits);
+      launch_pdl(decode_combine_kernel<128>, dim3(B * Hq), dim3(128), 0, stream, part_o, part_lse, p.out, p.num_splits);
       e = cudaGetLastError();
     }
   } else {
     static bool cfg = false;
     const int sm = smem_bytes<64>(stages);
     if (!cfg) { cudaFuncSetAttribute(paged_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm); cfg = true; }
-    paged_decode_kernel<64><<<grid, kThreads, sm, stream>>>(tm, p, stages);
+    launch_pdl(paged_decode_kernel<64>, grid, dim3(kThreads), sm, stream, tm, p, stages);
     e = cudaGetLastError();
     if (e == cudaSuccess && p.num_splits > 1) {
-      decode_combine_kernel<64><<<B * Hq, 64, 0, stream>>>(part_o, part_lse, p.out, p.num_splits);
+      launch_pdl(decode_combine_kernel<64>, dim3(B * Hq), dim3(64), 0, stream, part_o, part_lse, p.out, p.num_splits);
       e = cudaGetLastError();
     }
   }

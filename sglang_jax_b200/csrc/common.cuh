@@ -253,8 +253,33 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 
 }  // namespace sglb
 
+// Programmatic dependent launch: a kernel launched with `launch_pdl` may be scheduled while its predecessor
+// on the stream is still draining; everything it does before `pdl_wait()` (barrier init, TMEM allocation,
+// descriptor prefetch: nothing that touches global memory another kernel writes) overlaps that tail.
+// `pdl_wait()` returns once the predecessor grid has completed and its writes are visible, and is a no-op in
+// a kernel launched the ordinary way.
+namespace sglb {
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+}  // namespace sglb
+
 // Host-side: status access and tensor-map encoding (implemented in runtime.cu).
 namespace sglb {
+bool pdl_enabled();                            // SGLB_PDL=0 turns programmatic dependent launch off
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 Status* device_status();                       // device pointer of this device's status word
 bool encode_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner_elems, uint64_t rows, uint64_t row_stride_bytes,
                     uint32_t box_inner, uint32_t box_rows, int elem_bytes);

@@ -54,6 +54,7 @@ __global__ void rmsnorm_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat1
                                __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w, int H,
                                float eps, int gemma) {
   __shared__ float red[32];
+  pdl_wait();
   const size_t row = blockIdx.x;
   const uint4* xv = reinterpret_cast<const uint4*>(x + row * H);
   uint4* rv = ADD ? reinterpret_cast<uint4*>(residual + row * H) : nullptr;
@@ -98,6 +99,7 @@ __global__ void rmsnorm_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat1
 // out[t, i] = silu(x[t, i]) * x[t, I + i]
 __global__ void silu_mul_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, long long T,
                                 int I) {
+  pdl_wait();
   const int nvec = I >> 3;
   const long long total = T * nvec;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -118,6 +120,7 @@ __global__ void silu_mul_kernel(__nv_bfloat16* __restrict__ out, const __nv_bflo
 __global__ void embedding_kernel(__nv_bfloat16* __restrict__ out, const int* __restrict__ ids,
                                  const __nv_bfloat16* __restrict__ table, int H, int rows, int vocab_start,
                                  int masked) {
+  pdl_wait();
   const size_t t = blockIdx.x;
   int id = ids[t] - vocab_start;
   const bool ok = id >= 0 && id < rows;
@@ -131,6 +134,7 @@ __global__ void embedding_kernel(__nv_bfloat16* __restrict__ out, const int* __r
 // first maximal index per row
 template <typename T>
 __global__ void argmax_kernel(int* __restrict__ out, const T* __restrict__ logits, int V, long long row_stride) {
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const T* row = logits + blockIdx.x * row_stride;
@@ -222,6 +226,7 @@ __global__ void rope_qknorm_kvwrite_kernel(__nv_bfloat16* __restrict__ q_out, co
                                            float eps, long long T, int Hq, int Hkv, int rd,
                                            __nv_bfloat16* __restrict__ kv, const int* __restrict__ loc, int page_size,
                                            int is_neox) {
+  pdl_wait();
   constexpr int E = D / 32;
   const int heads = Hq + 2 * Hkv;
   const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
@@ -329,10 +334,10 @@ int sglb_rmsnorm(void* y, const void* x, const void* w, long long T, int H, floa
   auto* xx = static_cast<const __nv_bfloat16*>(x);
   auto* ww = static_cast<const __nv_bfloat16*>(w);
   switch (vpt) {
-    case 1: rmsnorm_kernel<false, 1><<<T, threads, 0, s>>>(yy, xx, nullptr, ww, H, eps, gemma); break;
-    case 2: rmsnorm_kernel<false, 2><<<T, threads, 0, s>>>(yy, xx, nullptr, ww, H, eps, gemma); break;
-    case 4: rmsnorm_kernel<false, 4><<<T, threads, 0, s>>>(yy, xx, nullptr, ww, H, eps, gemma); break;
-    default: rmsnorm_kernel<false, 8><<<T, threads, 0, s>>>(yy, xx, nullptr, ww, H, eps, gemma); break;
+    case 1: launch_pdl(rmsnorm_kernel<false, 1>, dim3(T), dim3(threads), 0, s, yy, xx, nullptr, ww, H, eps, gemma); break;
+    case 2: launch_pdl(rmsnorm_kernel<false, 2>, dim3(T), dim3(threads), 0, s, yy, xx, nullptr, ww, H, eps, gemma); break;
+    case 4: launch_pdl(rmsnorm_kernel<false, 4>, dim3(T), dim3(threads), 0, s, yy, xx, nullptr, ww, H, eps, gemma); break;
+    default: launch_pdl(rmsnorm_kernel<false, 8>, dim3(T), dim3(threads), 0, s, yy, xx, nullptr, ww, H, eps, gemma); break;
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -352,10 +357,10 @@ int sglb_fused_add_rmsnorm(void* y, const void* x, void* residual, const void* w
   auto* rr = static_cast<__nv_bfloat16*>(residual);
   auto* ww = static_cast<const __nv_bfloat16*>(w);
   switch (vpt) {
-    case 1: rmsnorm_kernel<true, 1><<<T, threads, 0, s>>>(yy, xx, rr, ww, H, eps, gemma); break;
-    case 2: rmsnorm_kernel<true, 2><<<T, threads, 0, s>>>(yy, xx, rr, ww, H, eps, gemma); break;
-    case 4: rmsnorm_kernel<true, 4><<<T, threads, 0, s>>>(yy, xx, rr, ww, H, eps, gemma); break;
-    default: rmsnorm_kernel<true, 8><<<T, threads, 0, s>>>(yy, xx, rr, ww, H, eps, gemma); break;
+    case 1: launch_pdl(rmsnorm_kernel<true, 1>, dim3(T), dim3(threads), 0, s, yy, xx, rr, ww, H, eps, gemma); break;
+    case 2: launch_pdl(rmsnorm_kernel<true, 2>, dim3(T), dim3(threads), 0, s, yy, xx, rr, ww, H, eps, gemma); break;
+    case 4: launch_pdl(rmsnorm_kernel<true, 4>, dim3(T), dim3(threads), 0, s, yy, xx, rr, ww, H, eps, gemma); break;
+    default: launch_pdl(rmsnorm_kernel<true, 8>, dim3(T), dim3(threads), 0, s, yy, xx, rr, ww, H, eps, gemma); break;
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -368,7 +373,7 @@ int sglb_silu_and_mul(void* out, const void* x, long long T, int I, cudaStream_t
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
-  silu_mul_kernel<<<static_cast<int>(blocks), threads, 0, s>>>(static_cast<__nv_bfloat16*>(out),
+  launch_pdl(silu_mul_kernel, dim3(static_cast<int>(blocks)), dim3(threads), 0, s, static_cast<__nv_bfloat16*>(out),
                                                                static_cast<const __nv_bfloat16*>(x), T, I);
   return static_cast<int>(cudaGetLastError());
 }
@@ -379,7 +384,7 @@ int sglb_embedding(void* out, const int* ids, const void* table, long long T, in
   if (T <= 0) return 0;
   if (H % 8) return -kBadArgument;
   int threads = H / 8 < 256 ? ((H / 8 + 31) / 32) * 32 : 256;
-  embedding_kernel<<<T, threads, 0, s>>>(static_cast<__nv_bfloat16*>(out), ids,
+  launch_pdl(embedding_kernel, dim3(T), dim3(threads), 0, s, static_cast<__nv_bfloat16*>(out), ids,
                                          static_cast<const __nv_bfloat16*>(table), H, rows, vocab_start, masked);
   return static_cast<int>(cudaGetLastError());
 }
@@ -388,8 +393,8 @@ int sglb_embedding(void* out, const int* ids, const void* table, long long T, in
 int sglb_argmax(int* out, const void* logits, int B, int V, long long row_stride, int dtype_bytes, cudaStream_t s) {
   using namespace sglb;
   if (B <= 0) return 0;
-  if (dtype_bytes == 4) argmax_kernel<float><<<B, 1024, 0, s>>>(out, static_cast<const float*>(logits), V, row_stride);
-  else argmax_kernel<__nv_bfloat16><<<B, 1024, 0, s>>>(out, static_cast<const __nv_bfloat16*>(logits), V, row_stride);
+  if (dtype_bytes == 4) launch_pdl(argmax_kernel<float>, dim3(B), dim3(1024), 0, s, out, static_cast<const float*>(logits), V, row_stride);
+  else launch_pdl(argmax_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, s, out, static_cast<const __nv_bfloat16*>(logits), V, row_stride);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -409,15 +414,15 @@ int sglb_rope_qknorm_kvwrite(void* q_out, const void* qkv, const int* positions,
   auto* kv = static_cast<__nv_bfloat16*>(kv_buffer);
   switch (D) {
     case 64:
-      rope_qknorm_kvwrite_kernel<64><<<blocks, threads, 0, s>>>(qo, in, positions, cos_sin, qw, kw, eps, T, Hq, Hkv,
+      launch_pdl(rope_qknorm_kvwrite_kernel<64>, dim3(blocks), dim3(threads), 0, s, qo, in, positions, cos_sin, qw, kw, eps, T, Hq, Hkv,
                                                                 rotary_dim, kv, loc, page_size, is_neox);
       break;
     case 128:
-      rope_qknorm_kvwrite_kernel<128><<<blocks, threads, 0, s>>>(qo, in, positions, cos_sin, qw, kw, eps, T, Hq, Hkv,
+      launch_pdl(rope_qknorm_kvwrite_kernel<128>, dim3(blocks), dim3(threads), 0, s, qo, in, positions, cos_sin, qw, kw, eps, T, Hq, Hkv,
                                                                  rotary_dim, kv, loc, page_size, is_neox);
       break;
     case 256:
-      rope_qknorm_kvwrite_kernel<256><<<blocks, threads, 0, s>>>(qo, in, positions, cos_sin, qw, kw, eps, T, Hq, Hkv,
+      launch_pdl(rope_qknorm_kvwrite_kernel<256>, dim3(blocks), dim3(threads), 0, s, qo, in, positions, cos_sin, qw, kw, eps, T, Hq, Hkv,
                                                                  rotary_dim, kv, loc, page_size, is_neox);
       break;
     default:

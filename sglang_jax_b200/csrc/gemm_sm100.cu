@@ -270,6 +270,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above is CTA-local; operands, counters and the tile lists may come from the previous kernel
+  pdl_wait();
   if (threadIdx.x == 0) stamp(1);
 
   if (warp == 0) {
@@ -639,8 +641,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  kern<<<grid, kNumThreads, C::kSmemBytes, stream>>>(ta, tb, p);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(grid), dim3(kNumThreads), C::kSmemBytes, stream, ta, tb, p);
 }
 
 inline int pick_bn_tokens(int M) {

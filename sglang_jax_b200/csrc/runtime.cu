@@ -46,6 +46,14 @@ Status* device_status() {
   return g_status[dev];
 }
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SGLB_PDL");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
+}
+
 int sm_count() {
   int dev = 0;
   cudaGetDevice(&dev);
