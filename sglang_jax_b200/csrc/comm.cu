@@ -274,6 +274,38 @@ argmax_gather_kernel(int* __restrict__ out, const T* __restrict__ logits, int V,
   rank_barrier(flags, epochs, rank, world, st, 4);
 }
 
+// Vocabulary-parallel logits gather by peer stores: rank r's shard `[B, Vp]` lands in columns
+// [r * Vp, (r + 1) * Vp) of every rank's `[B, world * Vp]` symmetric buffer.  The first barrier holds the
+// pushes back until every rank has consumed the previous contents (its sampling kernels precede this launch
+// on its stream), the second returns once every peer's pushes into this rank's buffer are visible.
+template <typename T>
+__global__ void __launch_bounds__(1024, 1)
+logits_gather_kernel(const T* __restrict__ logits, int Vp, long long row_stride, const Peers out, const Peers flags,
+                     uint32_t* epochs, int B, int rank, int world, Status* st) {
+  if (!rank_barrier(flags, epochs, rank, world, st, 5)) return;
+  const long long full = static_cast<long long>(world) * Vp;
+  const bool vec = (Vp * sizeof(T)) % 16 == 0 && (row_stride * sizeof(T)) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  for (int row = blockIdx.x; row < B; row += gridDim.x) {
+    const T* src = logits + row * row_stride;
+    const long long dst_off = row * full + static_cast<long long>(rank) * Vp;
+    if (vec) {
+      const int nvec = static_cast<int>(Vp * sizeof(T) / 16);
+      const uint4* sv = reinterpret_cast<const uint4*>(src);
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        const uint4 v = sv[i];
+        for (int p = 0; p < world; ++p) reinterpret_cast<uint4*>(static_cast<T*>(out.p[p]) + dst_off)[i] = v;
+      }
+    } else {
+      for (int i = threadIdx.x; i < Vp; i += blockDim.x) {
+        const T v = src[i];
+        for (int p = 0; p < world; ++p) (static_cast<T*>(out.p[p]) + dst_off)[i] = v;
+      }
+    }
+  }
+  rank_barrier(flags, epochs, rank, world, st, 6);
+}
+
 __global__ void barrier_only_kernel(const Peers flags, uint32_t* epochs, int rank, int world, Status* st) {
   rank_barrier(flags, epochs, rank, world, st, 9);
 }
@@ -340,6 +372,26 @@ int sglb_argmax_gather(int* out, const void* logits, int B, int V, long long row
     argmax_gather_kernel<__nv_bfloat16><<<blocks, 1024, 0, stream>>>(out, static_cast<const __nv_bfloat16*>(logits), V,
                                                                       row_stride, vocab_start, vocab_limit, cp, fp, ep,
                                                                       B, rank, world, st);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// logits: this rank's shard [B, Vp] (dtype_bytes 4 = fp32, 2 = bf16); out_ptrs: every rank's [B, world * Vp]
+// symmetric buffer of the same dtype.
+int sglb_logits_gather(const void* logits, int B, int Vp, long long row_stride, int dtype_bytes, void* const* out_ptrs,
+                       void* const* flag_ptrs, void* epochs, int rank, int world, cudaStream_t stream) {
+  using namespace sglb;
+  if (B <= 0) return 0;
+  if (world < 1 || world > kMaxWorld || Vp <= 0 || (dtype_bytes != 2 && dtype_bytes != 4)) return -kBadArgument;
+  Peers op = make_peers(out_ptrs, world), fp = make_peers(flag_ptrs, world);
+  const int blocks = B < kMaxBlocks ? B : kMaxBlocks;
+  auto* ep = static_cast<uint32_t*>(epochs);
+  Status* st = device_status();
+  if (dtype_bytes == 4)
+    logits_gather_kernel<float><<<blocks, 1024, 0, stream>>>(static_cast<const float*>(logits), Vp, row_stride, op, fp,
+                                                              ep, B, rank, world, st);
+  else
+    logits_gather_kernel<__nv_bfloat16><<<blocks, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), Vp,
+                                                                      row_stride, op, fp, ep, B, rank, world, st);
   return static_cast<int>(cudaGetLastError());
 }
 

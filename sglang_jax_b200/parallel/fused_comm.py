@@ -10,6 +10,8 @@ exchanges the peer mappings) and launches the kernels of `csrc/comm.cu` on them:
   dataflow the reference reaches with `--enable-sequence-parallel`
   (`python/sgl_jax/srt/utils/parallel_utils.py:8-51`).
 * `argmax_gather`: vocab-parallel greedy sampling without gathering logits.
+* `logits_gather`: vocab-parallel logits gather by peer stores (sampling with temperature / top-k / top-p
+  needs the whole row), reference `python/sgl_jax/srt/layers/logits_processor.py:523`.
 
 NCCL (`parallel/state.py`) remains the fallback for every op, and the A/B baseline.
 """
@@ -60,6 +62,9 @@ class FusedComm:
         L.sglb_argmax_gather.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        L.sglb_logits_gather.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_longlong, ctypes.c_int,
+                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                         ctypes.c_void_p]
         L.sglb_comm_barrier.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                         ctypes.c_void_p]
         self.L = L
@@ -80,6 +85,11 @@ class FusedComm:
         self.cand = _Symm(2 * self.world * 1024, torch.int32, self.device, group)   # (value, index) x world x B
         self.epochs = torch.zeros(L.sglb_comm_max_blocks(), dtype=torch.int32, device=self.device)
         self.epochs2 = torch.zeros(L.sglb_comm_max_blocks(), dtype=torch.int32, device=self.device)
+        self.flags3 = _Symm(L.sglb_comm_flag_bytes() // 4, torch.int32, self.device, group)
+        self.epochs3 = torch.zeros(L.sglb_comm_max_blocks(), dtype=torch.int32, device=self.device)
+        self.group = group
+        self.logits_full: _Symm | None = None       # [LOGITS_GATHER_ROWS, world * shard] of the logits dtype, on demand
+        self.logits_full_key = None
         torch.cuda.synchronize(self.device)
         import torch.distributed as dist
         dist.barrier(group=state.tp.cpu_group)
@@ -139,8 +149,36 @@ class FusedComm:
         native._check(rc, "argmax_gather")
         return out
 
+    LOGITS_GATHER_ROWS = 256
+
     def supports_logits_gather(self, logits) -> bool:
-        return False
+        """Decode-sized batches of bf16 / fp32 shards.  The symmetric result buffer is allocated by the first call
+        (a collective over the group: every rank reaches it in the same step), never inside a graph capture."""
+        if not (logits.is_cuda and logits.dim() == 2 and logits.shape[0] <= self.LOGITS_GATHER_ROWS
+                and logits.stride(1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)):
+            return False
+        key = (logits.shape[1], logits.dtype)
+        if self.logits_full_key == key:
+            return True
+        return self.logits_full_key is None and not torch.cuda.is_current_stream_capturing()
+
+    def logits_gather(self, local_logits: torch.Tensor) -> torch.Tensor:
+        """`[B, Vp]` shard of every rank -> `[B, world * Vp]` (rank r's columns at `r * Vp`), a view of this rank's
+        symmetric buffer: valid until the next call."""
+        B, Vp = local_logits.shape
+        key = (Vp, local_logits.dtype)
+        if self.logits_full is None:
+            self.logits_full = _Symm(self.LOGITS_GATHER_ROWS * self.world * Vp, local_logits.dtype, self.device,
+                                     self.group)
+            self.logits_full_key = key
+            torch.cuda.synchronize(self.device)
+        assert self.logits_full_key == key
+        rc = self.L.sglb_logits_gather(local_logits.data_ptr(), B, Vp, local_logits.stride(0),
+                                       local_logits.element_size(), self.logits_full.ptrs, self.flags3.ptrs,
+                                       self.epochs3.data_ptr(), self.rank, self.world,
+                                       torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "logits_gather")
+        return self.logits_full.tensor[: B * self.world * Vp].view(B, self.world * Vp)
 
     def barrier(self, blocks: int = 1):
         rc = self.L.sglb_comm_barrier(self.flags.ptrs, self.epochs.data_ptr(), self.rank, self.world, blocks,

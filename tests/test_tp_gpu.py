@@ -122,6 +122,20 @@ def _kernels(rank, world):
     native.check_status()
     exp = torch.argmax(full[:, : V * world - 5], dim=-1)
     assert ids.long().tolist() == exp.tolist()
+    # vocab-parallel logits gather by peer stores: repeated calls reuse one symmetric buffer, so each call has to
+    # wait for every rank to be done with the previous contents
+    Vp = 1000
+    for it, Bg in enumerate((37, 128, 5)):
+        gg = torch.Generator(device=dev).manual_seed(50 + it)
+        full = torch.randn(Bg, Vp * world, device=dev, generator=gg).to(torch.bfloat16)
+        local = full[:, rank * Vp:(rank + 1) * Vp].contiguous()
+        assert comm.supports_logits_gather(local)
+        got = comm.logits_gather(local)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert got.shape == (Bg, Vp * world) and torch.equal(got, full), ("logits_gather", it)
+    assert not comm.supports_logits_gather(torch.zeros(4, 1008, device=dev, dtype=torch.bfloat16))   # other shard width
+    assert not comm.supports_logits_gather(torch.zeros(1000, Vp, device=dev, dtype=torch.bfloat16))  # too many rows
     return report
 
 
