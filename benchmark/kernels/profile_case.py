@@ -2,7 +2,7 @@
 """One small, self-terminating case per kernel for `ncu` captures (inputs larger than L2, a few
 hundred MB on the device, a handful of launches).
 
-    python benchmark/kernels/profile_case.py gemm_prefill|gemm_decode|attn_decode|attn_extend|ar_norm
+    python benchmark/kernels/profile_case.py gemm_prefill|gemm_decode|attn_decode|attn_extend|sampling|gemm_fp8|moe_fp8
 """
 
 import os
@@ -48,6 +48,33 @@ def main():
         q = torch.randn(B * S, Hq, D, device="cuda").bfloat16()
         for _ in range(n):
             native.paged_attention(q, cache, pt, rows, sl, P, D ** -0.5, cu, pl)
+    elif case == "sampling":
+        B, V = 256, 151936                                   # 155 MB of fp32 logits: larger than L2
+        logits = torch.randn(B, V, device="cuda") * 2
+        one = lambda v, dt=torch.float32: torch.full((B,), v, device="cuda", dtype=dt)
+        seeds = torch.arange(B, device="cuda", dtype=torch.int32)
+        for _ in range(n):
+            native.sample_filtered(logits, one(0.7), one(50, torch.int32), one(0.95), one(0.0), seeds, seeds)
+    elif case == "gemm_fp8":
+        M, N, K = 4096, 10240, 5120
+        xq = torch.randn(M, K, device="cuda").to(torch.float8_e4m3fn)
+        wq = (torch.randn(N, K, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+        sx, sw = torch.rand(M, device="cuda") + 0.5, torch.rand(N, device="cuda") + 0.5
+        for _ in range(n):
+            native.gemm_fp8(xq, wq, sx, sw)
+    elif case == "moe_fp8":
+        from sglang_jax_b200.layers.moe import FusedMoE
+        from sglang_jax_b200.ops import reference
+        T, E, k, H, I = 2048, 32, 8, 7168, 2048
+        moe = FusedMoE(E, H, I, tp_size=1, tp_rank=0, ep_size=1).cuda()
+        moe.w13_weight.data.normal_(0, 0.02)
+        moe.w2_weight.data.normal_(0, 0.02)
+        moe.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        tw, ids = reference.topk_route(torch.randn(T, E, device="cuda"), k)
+        ids = ids.int()
+        for _ in range(n):
+            moe(x, tw, ids)
     else:
         raise SystemExit(f"unknown case {case}")
     torch.cuda.synchronize()
