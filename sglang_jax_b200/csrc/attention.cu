@@ -48,6 +48,7 @@ struct AttnParams {
   // extend only: visibility inside the last `tail_len` keys, [B, mask_rows, tail_len] bytes (null = causal)
   const uint8_t* tail_mask;
   int tail_len, mask_rows;
+  int bidirectional;            // extend only: every query row sees every key of its sequence (encoders)
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -441,7 +442,7 @@ paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
   const int seq = p.seq_lens[b];
   const int q0 = tile_in_seq * BQ;                         // first query row (within the sequence's new tokens)
   const int q_hi = min(q0 + BQ, q_len);
-  const bool masked = p.tail_mask != nullptr;
+  const bool masked = p.tail_mask != nullptr || p.bidirectional != 0;
   const int kv_end = masked ? seq : min(seq, prefix + q_hi);   // causal upper bound for this tile
   int first_tok = 0;
   if (p.window > 0) first_tok = max(0, prefix + q0 - p.window + 1);
@@ -500,7 +501,7 @@ paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
   }
   const int kmax[2] = {masked ? seq - 1 : min(prefix + r_lo, seq - 1), masked ? seq - 1 : min(prefix + r_hi, seq - 1)};
   const uint8_t* mask_row[2] = {nullptr, nullptr};
-  if (masked) {
+  if (p.tail_mask != nullptr) {
     const uint8_t* mb = p.tail_mask + static_cast<size_t>(b) * p.mask_rows * p.tail_len;
     if (r_lo < q_len && r_lo < p.mask_rows) mask_row[0] = mb + static_cast<size_t>(r_lo) * p.tail_len;
     if (r_hi < q_len && r_hi < p.mask_rows) mask_row[1] = mb + static_cast<size_t>(r_hi) * p.tail_len;
@@ -709,6 +710,7 @@ int sglb_paged_extend_masked(const void* q, void* out, const void* kv_buffer, lo
   p.tail_mask = static_cast<const uint8_t*>(tail_mask);
   p.tail_len = tail_mask ? tail_len : 0;
   p.mask_rows = mask_rows;
+  p.bidirectional = (tail_mask == nullptr && mask_rows < 0) ? 1 : 0;   // mask_rows -1 without a mask: no causal rule
   const int stages = 3;
   dim3 grid(num_q_tiles_bound, Hq, 1);
   cudaError_t e;

@@ -4,7 +4,8 @@ alternate windowed and full attention over a window-major token order, RMSNorm +
 MLP, and a 2x2 spatial merger that emits one LLM-width embedding per merged patch.
 
 Attention runs over packed variable-length segments (whole images for the full-attention blocks,
-windows otherwise); segments are expressed as a block-diagonal mask over the packed sequence."""
+windows otherwise): on the GPU through the varlen attention kernel, elsewhere as a block-diagonal
+mask over the packed sequence."""
 
 from __future__ import annotations
 
@@ -21,6 +22,21 @@ def _rms(x, w, eps=1e-6):
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
 
+
+class Segments:
+    """Contiguous attention segments of a packed sequence: lengths for the varlen kernel, and the
+    block-diagonal mask (built on first use) for the PyTorch path."""
+
+    def __init__(self, cu: torch.Tensor, n: int, device):
+        self.cu, self.n, self.device = cu, n, device
+        self.lens = (cu[1:] - cu[:-1]).tolist()
+        self._mask = None
+
+    def mask(self) -> torch.Tensor:
+        if self._mask is None:
+            seg = torch.bucketize(torch.arange(self.n), self.cu[1:], right=True)
+            self._mask = (seg[:, None] == seg[None, :]).to(self.device)
+        return self._mask
 
 class _Lin(nn.Module):
     def __init__(self, i, o, dtype, bias=True):
@@ -57,9 +73,14 @@ class VisionBlock(nn.Module):
             rh = torch.cat([-tf[..., half:], tf[..., :half]], -1)
             return (tf * cos[:, None] + rh * sin[:, None]).to(t.dtype)
 
-        a = F.scaled_dot_product_attention(rot(q).transpose(0, 1)[None], rot(k).transpose(0, 1)[None],
-                                           v.transpose(0, 1)[None], attn_mask=seg_mask[None, None])
-        x = x + self.proj(a[0].transpose(0, 1).reshape(N, D))
+        if ops.use_native(x):
+            # packed segments through the paged extend kernel with the causal rule off: no N x N mask
+            a = ops.varlen_attention(rot(q), rot(k), v.contiguous(), seg_mask.lens, (D // H) ** -0.5).reshape(N, D)
+        else:
+            a = F.scaled_dot_product_attention(rot(q).transpose(0, 1)[None], rot(k).transpose(0, 1)[None],
+                                               v.transpose(0, 1)[None], attn_mask=seg_mask.mask()[None, None])
+            a = a[0].transpose(0, 1).reshape(N, D)
+        x = x + self.proj(a)
         h = _rms(x, self.norm2)
         return x + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h))
 
@@ -113,9 +134,8 @@ class Qwen2_5_VisionTransformer(nn.Module):
         return torch.cat(index), cu_t
 
     @staticmethod
-    def _segment_mask(cu: torch.Tensor, n: int, device) -> torch.Tensor:
-        seg = torch.bucketize(torch.arange(n), cu[1:], right=True)
-        return (seg[:, None] == seg[None, :]).to(device)
+    def _segment_mask(cu: torch.Tensor, n: int, device) -> "Segments":
+        return Segments(cu, n, device)
 
     # ------------------------------------------------------------------ forward
     @torch.inference_mode()

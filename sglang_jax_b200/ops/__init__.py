@@ -27,6 +27,14 @@ def use_native(x: torch.Tensor) -> bool:
     return (not _FORCE_REFERENCE) and x.is_cuda and x.dtype == torch.bfloat16
 
 
+def varlen_attention(q, k, v, seq_lens, scale: float):
+    """Bidirectional attention over packed sequences (encoders, diffusion transformers)."""
+    if use_native(q) and q.shape[-1] <= 128 and q.shape[1] % k.shape[1] == 0 and q.shape[1] // k.shape[1] <= 16 \
+            and k.dtype == q.dtype and v.dtype == q.dtype:
+        return _native().varlen_attention(q, k, v, seq_lens, scale)
+    return reference.varlen_attention(q, k, v, seq_lens, scale)
+
+
 def use_native_sampling(logits: torch.Tensor) -> bool:
     return (not _FORCE_REFERENCE) and logits.is_cuda and logits.dim() == 2 \
         and logits.dtype in (torch.float32, torch.bfloat16)

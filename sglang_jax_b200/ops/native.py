@@ -268,6 +268,58 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
     return out
 
 
+def pack_varlen_pages(k, v, lens, page_size: int = 64):
+    """`k, v [T, H, D]` of sequences with lengths `lens`, packed along T -> a paged cache
+    `[pages, 2, H, page_size, D]` in which every sequence starts on a page boundary (page 0 is an all-zero dummy),
+    its page table `[B, max_pages]`, `lens` and their running sum as int32 device tensors, and the two counts."""
+    T, H, D = k.shape
+    dev, P, B = k.device, page_size, len(lens)
+    pages = [(n + P - 1) // P for n in lens]
+    max_pages = max(max(pages, default=0), 1)
+    base, table = 1, []
+    for np_ in pages:
+        table.append([base + i for i in range(np_)] + [0] * (max_pages - np_))
+        base += np_
+    i32 = dict(dtype=torch.int32, device=dev)
+    lens_t = torch.tensor(lens, **i32)
+    cu = torch.zeros(B + 1, **i32)
+    cu[1:] = torch.cumsum(lens_t, 0)
+    pos = torch.arange(T, device=dev) - torch.repeat_interleave(cu[:-1].long(), lens_t.long())
+    first_page = torch.tensor([row[0] for row in table], device=dev, dtype=torch.long)
+    page_of = torch.repeat_interleave(first_page, lens_t.long()) + pos // P
+    cache = torch.zeros((base, 2, H, P, D), dtype=k.dtype, device=dev)
+    cache[page_of, 0, :, pos % P] = k
+    cache[page_of, 1, :, pos % P] = v
+    return cache, torch.tensor(table, **i32), lens_t, cu, base, max_pages
+
+
+def varlen_attention(q, k, v, seq_lens, scale: float):
+    """Bidirectional attention over a ragged batch of sequences packed along the token axis (vision / audio
+    encoders, diffusion transformers): `q [T, Hq, D]`, `k, v [T, Hkv, D]`, `seq_lens` host ints summing to T.
+    K / V are laid out as 64-token pages (one gather-friendly copy) and the paged extend kernel runs with the
+    causal rule switched off; head dims that are not 64 / 128 are zero-padded to the next of the two
+    (reference kernel: `python/sgl_jax/srt/multimodal/kernels/varlen_attention.py`)."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    lens = [int(x) for x in seq_lens]
+    assert sum(lens) == T and q.dtype == torch.bfloat16 and Hq % Hkv == 0 and Hq // Hkv <= 16 and D <= 128
+    Dp = 64 if D <= 64 else 128
+    if Dp != D:
+        pad = lambda t: torch.nn.functional.pad(t, (0, Dp - D))
+        q, k, v = pad(q), pad(k), pad(v)
+    P, B = 64, len(lens)
+    cache, pt, lens_t, cu, base, max_pages = pack_varlen_pages(k, v, lens, P)
+    i32 = dict(dtype=torch.int32, device=q.device)
+    rows = torch.arange(B, **i32)
+    prefix = torch.zeros(B, **i32)
+    qc = q.contiguous()
+    out = torch.empty_like(qc)
+    _check(lib().sglb_paged_extend_masked(_p(qc), _p(out), _p(cache), base, _p(pt), max_pages, _p(rows), _p(lens_t),
+                                          _p(prefix), _p(cu), B, T // 64 + B, Hq, Hkv, Dp, P,
+                                          float(scale), 0, 0.0, None, 0, -1, _stream()), "varlen_attention")
+    return out[..., :D] if Dp != D else out
+
+
 def sample_filtered(logits, temperatures, top_ks, top_ps, min_ps, seeds, positions, return_probs: bool = False,
                     request_seeded: bool = True):
     """Temperature / top-k / top-p / min-p filtering and hashed Gumbel-max sampling of `logits [B, V]` (fp32 or

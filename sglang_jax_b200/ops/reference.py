@@ -218,6 +218,24 @@ def top_k_top_p_min_p_probs(logits, temperatures, top_ks, top_ps, min_ps):
     return out
 
 
+def varlen_attention(q, k, v, seq_lens, scale: float):
+    """Bidirectional attention inside each sequence of a packed ragged batch: `q [T, Hq, D]`, `k, v [T, Hkv, D]`,
+    `seq_lens` host ints.  fp32 softmax."""
+    out = torch.empty_like(q)
+    g = q.shape[1] // k.shape[1]
+    o = 0
+    for n in (int(x) for x in seq_lens):
+        if n == 0:
+            continue
+        qq = q[o:o + n].float().transpose(0, 1)                                  # [Hq, n, D]
+        kk = k[o:o + n].float().transpose(0, 1).repeat_interleave(g, 0)
+        vv = v[o:o + n].float().transpose(0, 1).repeat_interleave(g, 0)
+        p = torch.softmax(qq @ kk.transpose(1, 2) * scale, dim=-1)
+        out[o:o + n] = (p @ vv).transpose(0, 1).to(q.dtype)
+        o += n
+    return out
+
+
 def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0, masked: bool = False) -> torch.Tensor:
     """Row lookup.  With `masked` (vocab-parallel shard) ids outside
     `[vocab_start, vocab_start + rows)` produce zero rows so an all-reduce completes them."""

@@ -369,6 +369,21 @@ def test_sampler_module_uses_the_sampling_kernel(native):
     assert bool((top5 == first.long().view(-1, 1)).any(-1).all())
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,lens", [(4, 4, 128, [5, 64, 130, 0, 700]), (16, 16, 80, [37, 256, 100]),
+                                            (8, 2, 64, [1, 63, 65, 129]), (6, 6, 72, [300])])
+def test_varlen_bidirectional_attention(native, Hq, Hkv, D, lens):
+    """Packed encoder attention (no causal rule) through the paged extend kernel, head dims padded to 64 / 128,
+    vs an fp32 softmax per sequence."""
+    T = sum(lens)
+    q, k, v = _bf16(T, Hq, D, seed=91), _bf16(T, Hkv, D, seed=92), _bf16(T, Hkv, D, seed=93)
+    got = native.varlen_attention(q, k, v, lens, D ** -0.5)
+    torch.cuda.synchronize()
+    native.check_status()
+    want = ref.varlen_attention(q.float(), k.float(), v.float(), lens, D ** -0.5)
+    assert got.shape == q.shape
+    _close(got, want, 2e-2, 2e-2)
+
+
 def test_argmax_unaligned_rows(native):
     logits = torch.randn(7, 1003, device="cuda").to(torch.bfloat16)     # odd rows start off a 16-byte boundary
     assert torch.equal(native.argmax(logits).long(), torch.argmax(logits.float(), dim=-1))
