@@ -486,3 +486,44 @@ def test_fp8_recipe_runs_on_the_fp8_gemm(tiny_path):
     finally:
         ops.set_force_reference(False)
     assert _rel(y_n, y_r) < 2e-2
+
+
+def test_qwen2_5_vl_vision_tower_uses_varlen_attention_on_gpu():
+    """The vision tower on the GPU (windowed and full-attention blocks as packed segments through the varlen
+    kernel, head dim 80 padded to 128) agrees with the same weights through the PyTorch path."""
+    from types import SimpleNamespace
+    from sglang_jax_b200 import ops
+    from sglang_jax_b200.multimodal.models.qwen2_5_vl_vit import Qwen2_5_VisionTransformer
+    from sglang_jax_b200.ops import native
+    cfg = SimpleNamespace(depth=4, hidden_size=320, intermediate_size=512, num_heads=4, in_channels=3, patch_size=14,
+                          spatial_merge_size=2, temporal_patch_size=2, window_size=112, fullatt_block_indexes=[1, 3],
+                          out_hidden_size=256, hidden_act="silu")
+    torch.manual_seed(0)
+    vit = Qwen2_5_VisionTransformer(cfg, dtype=torch.bfloat16).cuda()
+    for p in vit.parameters():
+        p.data.normal_(0, 0.05) if p.dim() > 1 else p.data.uniform_(0.5, 1.5)
+    grid = torch.tensor([[1, 12, 20], [1, 8, 8], [2, 4, 6]])
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, 3 * 2 * 14 * 14, device="cuda").bfloat16()
+    calls = {"n": 0}
+    orig = native.varlen_attention
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+
+    native.varlen_attention = counted
+    try:
+        got = vit(px, grid)
+    finally:
+        native.varlen_attention = orig
+    assert calls["n"] == 4
+    ops.set_force_reference(True)
+    try:
+        want = vit(px, grid)
+    finally:
+        ops.set_force_reference(False)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert got.shape == want.shape == (n // 4, 256) and want.float().std() > 1e-3
+    assert _rel(got, want) < 3e-2
