@@ -21,6 +21,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .... import ops
+from ..segments import PackedSegments
 
 
 def _lin(x, lin):
@@ -58,9 +59,7 @@ class KimiVisionBlock(nn.Module):
         T, D = x.shape
         q, k, v = _lin(self.norm0(x), self.wqkv).view(T, 3, self.heads, -1).unbind(1)
         q, k = apply_rope_interleaved(q, cos, sin), apply_rope_interleaved(k, cos, sin)
-        o = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
-                                           attn_mask=mask)[0]
-        x = x + _lin(o.transpose(0, 1).reshape(T, D), self.wo)
+        x = x + _lin(mask.attend(q, k, v), self.wo)
         return x + _lin(F.gelu(_lin(self.norm1(x), self.mlp.fc0), approximate="tanh"), self.mlp.fc1)
 
 
@@ -119,10 +118,10 @@ class KimiK25VisionModel(nn.Module):
             c, s = rope_2d(h, wd, hd, device=x.device)
             cos.append(c.repeat(t, 1))
             sin.append(s.repeat(t, 1))
-            ids.append(torch.full((t * h * wd,), i, device=x.device))
+            ids.append(t * h * wd)
         x = x + torch.cat(pos).to(x.dtype)
-        cos, sin, ids = torch.cat(cos), torch.cat(sin), torch.cat(ids)
-        mask = (ids[:, None] == ids[None, :])[None, None]
+        cos, sin = torch.cat(cos), torch.cat(sin)
+        mask = PackedSegments(ids, x.device)                       # one attention segment per item
         for blk in vt.encoder.blocks:
             x = blk(x, cos, sin, mask)
         x = vt.encoder.final_layernorm(x)

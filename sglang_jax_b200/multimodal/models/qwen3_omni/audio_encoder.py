@@ -18,6 +18,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .... import ops
+from ..segments import PackedSegments
 
 
 def feat_lengths(n: torch.Tensor) -> torch.Tensor:
@@ -54,9 +55,8 @@ class AudioEncoderLayer(nn.Module):
         T, D = x.shape
         h = self.self_attn_layer_norm(x)
         a = self.self_attn
-        q, k, v = (_lin(h, p).view(T, self.heads, -1).transpose(0, 1) for p in (a.q_proj, a.k_proj, a.v_proj))
-        o = F.scaled_dot_product_attention(q[None], k[None], v[None], attn_mask=mask)[0]
-        x = x + _lin(o.transpose(0, 1).reshape(T, D), a.out_proj)
+        q, k, v = (_lin(h, p).view(T, self.heads, -1) for p in (a.q_proj, a.k_proj, a.v_proj))
+        x = x + _lin(mask.attend(q, k, v), a.out_proj)
         return x + _lin(self.act(_lin(self.final_layer_norm(x), self.fc1)), self.fc2)
 
 
@@ -111,8 +111,7 @@ class Qwen3OmniMoeAudioEncoder(nn.Module):
         seg = []
         for n in feat_lengths(feature_lens).tolist():
             seg += [window] * (n // window) + ([n % window] if n % window else [])
-        ids = torch.repeat_interleave(torch.arange(len(seg)), torch.tensor(seg)).to(h.device)
-        mask = (ids[:, None] == ids[None, :])[None, None]
+        mask = PackedSegments(seg, h.device)
         for layer in self.layers:
             h = layer(h, mask)
         return _lin(self.act(_lin(self.ln_post(h), self.proj1)), self.proj2)

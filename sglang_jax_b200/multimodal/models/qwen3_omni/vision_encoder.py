@@ -17,6 +17,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .... import ops
+from ..segments import PackedSegments
 
 
 def _lin(x, lin):
@@ -51,9 +52,7 @@ class VisionBlock(nn.Module):
             return (tf * cos + torch.cat([-tf[..., h:], tf[..., :h]], -1) * sin).to(t.dtype)
 
         q, k = rot(q), rot(k)
-        o = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
-                                           attn_mask=mask)[0]
-        x = x + _lin(o.transpose(0, 1).reshape(T, D), self.attn.proj)
+        x = x + _lin(mask.attend(q, k, v), self.attn.proj)
         return x + _lin(self.act(_lin(self.norm2(x), self.mlp.linear_fc1)), self.mlp.linear_fc2)
 
 
@@ -133,8 +132,7 @@ class Qwen3OmniMoeVisionEncoder(nn.Module):
         ang = torch.cat([ang, ang], dim=-1)
         cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
         frames = torch.repeat_interleave(grid_thw[:, 1] * grid_thw[:, 2], grid_thw[:, 0])
-        ids = torch.repeat_interleave(torch.arange(len(frames)), frames).to(x.device)
-        mask = (ids[:, None] == ids[None, :])[None, None]
+        mask = PackedSegments(frames.tolist(), x.device)          # one attention segment per frame
         deep = []
         for i, blk in enumerate(self.blocks):
             x = blk(x, cos, sin, mask)

@@ -527,3 +527,61 @@ def test_qwen2_5_vl_vision_tower_uses_varlen_attention_on_gpu():
     native.check_status()
     assert got.shape == want.shape == (n // 4, 256) and want.float().std() > 1e-3
     assert _rel(got, want) < 3e-2
+
+
+def test_encoders_use_varlen_attention_on_gpu():
+    """Qwen3-Omni vision and audio encoders and the Kimi-K2.5 vision tower on the GPU: frames / windows / items as
+    packed segments through the varlen kernel (head dims 72, 64, 72) agree with the PyTorch path of the same weights."""
+    from types import SimpleNamespace
+    from sglang_jax_b200 import ops
+    from sglang_jax_b200.multimodal.model_executor.loading import init_dummy
+    from sglang_jax_b200.multimodal.models.kimi_k25.kimi_k25_vit import KimiK25VisionModel
+    from sglang_jax_b200.multimodal.models.qwen3_omni.audio_encoder import Qwen3OmniMoeAudioEncoder
+    from sglang_jax_b200.multimodal.models.qwen3_omni.vision_encoder import Qwen3OmniMoeVisionEncoder
+    from sglang_jax_b200.ops import native
+    bf = torch.bfloat16
+    g = torch.Generator().manual_seed(0)
+    vcfg = SimpleNamespace(depth=3, hidden_size=288, intermediate_size=384, num_heads=4, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=144,
+                           deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh")
+    vis = init_dummy(Qwen3OmniMoeVisionEncoder(vcfg, dtype=bf), seed=1, std=0.05).cuda().eval()
+    grid = torch.tensor([[1, 12, 20], [2, 8, 8]])
+    px = torch.randn(int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 4 * 4, generator=g).cuda().to(bf)
+    acfg = SimpleNamespace(num_mel_bins=16, d_model=256, encoder_layers=2, encoder_attention_heads=4,
+                           encoder_ffn_dim=512, downsample_hidden_size=8, output_dim=64, max_source_positions=64,
+                           n_window=50, n_window_infer=200, conv_chunksize=4, activation_function="gelu",
+                           scale_embedding=False)
+    aud = init_dummy(Qwen3OmniMoeAudioEncoder(acfg, dtype=bf), seed=2, std=0.05).cuda().eval()
+    feats, flens = torch.randn(16, 157 + 330, generator=g).cuda().to(bf), torch.tensor([157, 330])
+    kcfg = SimpleNamespace(patch_size=4, in_channels=3, vt_hidden_size=288, vt_num_attention_heads=4,
+                           vt_intermediate_size=384, vt_num_hidden_layers=2, init_pos_emb_height=6, init_pos_emb_width=6,
+                           init_pos_emb_time=4, merge_kernel_size=[2, 2], text_hidden_size=64)
+    kimi = init_dummy(KimiK25VisionModel(kcfg, dtype=bf), seed=3, std=0.05).cuda().eval()
+    kpx = torch.randn(36 + 64, 3, 4, 4, generator=g).cuda().to(bf)
+    runs = [lambda: vis(px, grid), lambda: aud(feats, flens), lambda: kimi(kpx, [[1, 6, 6], [2, 4, 8]])]
+    calls = {"n": 0}
+    orig = native.varlen_attention
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+
+    for run, layers in zip(runs, (3, 2, 2)):
+        calls["n"] = 0
+        native.varlen_attention = counted
+        try:
+            with torch.inference_mode():
+                got = run()
+        finally:
+            native.varlen_attention = orig
+        assert calls["n"] == layers
+        ops.set_force_reference(True)
+        try:
+            with torch.inference_mode():
+                want = run()
+        finally:
+            ops.set_force_reference(False)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert got.shape == want.shape and want.float().std() > 1e-3
+        assert _rel(got, want) < 4e-2
