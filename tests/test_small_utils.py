@@ -133,3 +133,35 @@ def test_accuracy_evals_score_known_samplers(tmp_path):
     ev = GSM8KEval(str(g), num_shots=3, num_threads=2)
     assert len(ev.examples) == 6 and ev(Adder()).score == 1.0
     assert normalize_number("1,234.0") == "1234" and normalize_number("about 12 apples") == "12"
+
+
+def test_varlen_page_packing_and_reference_attention():
+    """The page layout the varlen attention kernel reads (every sequence on its own pages, page 0 a zero dummy) and
+    the PyTorch statement of bidirectional packed attention (sequences do not see each other)."""
+    import torch
+    from sglang_jax_b200 import ops
+    from sglang_jax_b200.ops.native import pack_varlen_pages
+    torch.manual_seed(0)
+    lens = [5, 64, 130, 0, 1]
+    T = sum(lens)
+    k, v = torch.randn(T, 2, 8), torch.randn(T, 2, 8)
+    cache, pt, lens_t, cu, n_pages, max_pages = pack_varlen_pages(k, v, lens, 64)
+    assert cache.shape == (7, 2, 2, 64, 8) and n_pages == 7 and max_pages == 3
+    assert pt.tolist() == [[1, 0, 0], [2, 0, 0], [3, 4, 5], [0, 0, 0], [6, 0, 0]]
+    assert cu.tolist() == [0, 5, 69, 199, 199, 200] and lens_t.tolist() == lens
+    assert not cache[0].any()
+    o = 0
+    for b, n in enumerate(lens):
+        if n:
+            pages = pt[b, : (n + 63) // 64].long()
+            assert torch.equal(cache[pages, 0].permute(0, 2, 1, 3).reshape(-1, 2, 8)[:n], k[o:o + n])
+            assert torch.equal(cache[pages, 1].permute(0, 2, 1, 3).reshape(-1, 2, 8)[:n], v[o:o + n])
+        o += n
+    q = torch.randn(T, 4, 8)
+    out = ops.varlen_attention(q, k, v, lens, 8 ** -0.5)
+    alone = ops.varlen_attention(q[5:69], k[5:69], v[5:69], [64], 8 ** -0.5)
+    assert torch.allclose(out[5:69], alone, atol=1e-6)
+    sd = torch.nn.functional.scaled_dot_product_attention(
+        q[5:69].transpose(0, 1)[None], k[5:69].transpose(0, 1).repeat_interleave(2, 0)[None],
+        v[5:69].transpose(0, 1).repeat_interleave(2, 0)[None])[0].transpose(0, 1)
+    assert torch.allclose(alone, sd, atol=1e-5)
