@@ -16,11 +16,28 @@ align -> gather -> grouped tcgen05 GEMM -> SiLU*mul -> grouped GEMM -> weighted 
 
 from __future__ import annotations
 
+import contextlib
+
 import torch
 from torch import nn
 
 from .. import ops
 from ..parallel import state as ps
+
+
+_EXPERT_STORAGE = None
+
+
+@contextlib.contextmanager
+def expert_storage(dtype):
+    """Experts constructed inside the block store their weights in `dtype` (only `torch.float8_e4m3fn` changes
+    anything) instead of the compute dtype."""
+    global _EXPERT_STORAGE
+    prev, _EXPERT_STORAGE = _EXPERT_STORAGE, dtype
+    try:
+        yield
+    finally:
+        _EXPERT_STORAGE = prev
 
 
 class FusedMoE(nn.Module):
@@ -46,14 +63,33 @@ class FusedMoE(nn.Module):
             self.expert_start = 0
             self.local_intermediate = intermediate_size // self.tp_size
         I = self.local_intermediate
-        self.w13_weight = nn.Parameter(torch.empty(self.num_local_experts, 2 * I, hidden_size, dtype=dtype),
-                                       requires_grad=False)
-        self.w2_weight = nn.Parameter(torch.empty(self.num_local_experts, hidden_size, I, dtype=dtype),
-                                      requires_grad=False)
         self.workspace = None
         self.routed_experts_capturer = None
         self.dtype = dtype
-        self.fp8 = False
+        # e4m3 storage from the start (set by the loader for W8A8 per-channel recipes): the bf16 experts of a large
+        # model never exist on the device; each expert is quantised as its checkpoint tensor arrives
+        self.fp8 = (_EXPERT_STORAGE == torch.float8_e4m3fn and self._fp8_capable(dtype, activation, hidden_size, I))
+        store = torch.float8_e4m3fn if self.fp8 else dtype
+        self.w13_weight = nn.Parameter(torch.empty(self.num_local_experts, 2 * I, hidden_size, dtype=store),
+                                       requires_grad=False)
+        self.w2_weight = nn.Parameter(torch.empty(self.num_local_experts, hidden_size, I, dtype=store),
+                                      requires_grad=False)
+        if self.fp8:
+            self._register_scales(self.w13_weight.device)
+            self.quantized = True
+
+    @staticmethod
+    def _fp8_capable(dtype, activation, hidden_size, intermediate) -> bool:
+        return dtype == torch.bfloat16 and activation == "silu" and hidden_size % 16 == 0 and intermediate % 16 == 0
+
+    def _register_scales(self, device, w13_scale=None, w2_scale=None):
+        """Per-expert, per-output-channel fp32 scales (buffers: they follow the module across devices and are
+        not checkpoint parameters).  The default 0.02 gives dummy-initialised e4m3 values the usual weight scale."""
+        E, I2, H = self.w13_weight.shape
+        self.register_buffer("w13_scale", w13_scale if w13_scale is not None
+                             else torch.full((E, I2), 0.02, dtype=torch.float32, device=device))
+        self.register_buffer("w2_scale", w2_scale if w2_scale is not None
+                             else torch.full((E, H), 0.02, dtype=torch.float32, device=device))
 
     def weight_loader(self, param, w, shard_id: str, expert_id: int):
         """`shard_id` in {"gate", "up", "down"}; `w` is the full `[out, in]` tensor of one expert."""
@@ -63,24 +99,37 @@ class FusedMoE(nn.Module):
         I = self.local_intermediate
         if shard_id in ("gate", "up"):
             src = w if self.expert_parallel or self.tp_size == 1 else w.narrow(0, self.tp_rank * I, I)
-            param.data[local].narrow(0, 0 if shard_id == "gate" else I, I).copy_(src)
+            row0 = 0 if shard_id == "gate" else I
         else:
             src = w if self.expert_parallel or self.tp_size == 1 else w.narrow(1, self.tp_rank * I, I)
-            param.data[local].copy_(src)
+            row0 = 0
+        dst = param.data[local].narrow(0, row0, src.shape[0])
+        if self.fp8:
+            from ..utils.quantization import quantize_tensor
+            q, sc = quantize_tensor(src.to(dst.device), torch.float8_e4m3fn, "per_channel")
+            dst.copy_(q)
+            scale = self.w2_scale if shard_id == "down" else self.w13_scale
+            scale[local].narrow(0, row0, src.shape[0]).copy_(sc.view(-1))
+        else:
+            dst.copy_(src)
 
     def quantize_(self, dtype, block_size=None, activation_dtype=None):
         """Quantise the expert weights to `dtype` with per-channel or block scales.
 
-        W8A8 e4m3 with per-channel scales keeps real fp8 storage (`w13_q`, `w2_q` + fp32 scales): the
-        bf16 tensors are released and the forward runs the grouped fp8 tensor-core GEMMs with dynamic
-        per-token activation scales.  Every other recipe stores the values de-quantised in the compute
-        dtype, which reproduces the numerics of a quantised checkpoint on the bf16 grouped GEMM."""
+        W8A8 e4m3 with per-channel scales keeps real fp8 storage (`w13_weight` / `w2_weight` become e4m3, with
+        fp32 `w13_scale` / `w2_scale` buffers): the bf16 tensors are released and the forward runs the grouped
+        fp8 tensor-core GEMMs with dynamic per-token activation scales.  Every other recipe stores the values
+        de-quantised in the compute dtype, which reproduces the numerics of a quantised checkpoint on the bf16
+        grouped GEMM."""
         from ..utils.quantization import dequantize_tensor, quantize_tensor
+        if self.fp8:
+            return                                            # built in fp8 storage: quantised while loading
         gran = "block" if block_size else "per_channel"
+        E, I2, H = self.w13_weight.shape
         fp8_storage = (dtype == torch.float8_e4m3fn and activation_dtype == torch.float8_e4m3fn and not block_size
-                       and self.w13_weight.dtype == torch.bfloat16 and self.activation == "silu"
-                       and self.w13_weight.shape[-1] % 16 == 0 and self.w2_weight.shape[-1] % 16 == 0)
+                       and self._fp8_capable(self.w13_weight.dtype, self.activation, H, I2 // 2))
         if fp8_storage:
+            scales = {}
             for name in ("w13", "w2"):
                 p = getattr(self, f"{name}_weight")
                 q = torch.empty(p.shape, dtype=dtype, device=p.device)
@@ -89,9 +138,9 @@ class FusedMoE(nn.Module):
                     qe, se = quantize_tensor(p.data[e], dtype, "per_channel")
                     q[e].copy_(qe)
                     sc[e].copy_(se.view(-1))
-                setattr(self, f"{name}_q", nn.Parameter(q, requires_grad=False))
-                setattr(self, f"{name}_scale", nn.Parameter(sc, requires_grad=False))
-                setattr(self, f"{name}_weight", None)
+                setattr(self, f"{name}_weight", nn.Parameter(q, requires_grad=False))
+                scales[name] = sc
+            self._register_scales(self.w13_weight.device, scales["w13"], scales["w2"])
             self.fp8 = True
         else:
             for p in (self.w13_weight, self.w2_weight):
@@ -104,8 +153,8 @@ class FusedMoE(nn.Module):
         """Expert weights in the compute dtype (de-quantised on the fly under fp8 storage)."""
         if not self.fp8:
             return self.w13_weight, self.w2_weight
-        return ((self.w13_q.float() * self.w13_scale[..., None]).to(self.dtype),
-                (self.w2_q.float() * self.w2_scale[..., None]).to(self.dtype))
+        return ((self.w13_weight.float() * self.w13_scale[..., None]).to(self.dtype),
+                (self.w2_weight.float() * self.w2_scale[..., None]).to(self.dtype))
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 add: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -119,7 +168,7 @@ class FusedMoE(nn.Module):
             if self.workspace is None or self.workspace.max_pairs < pairs:
                 self.workspace = moe_native.MoeWorkspace(max(pairs, 2048), self.num_local_experts, x.device)
             if self.fp8:
-                return moe_native.fused_experts_fp8(x, self.w13_q, self.w13_scale, self.w2_q, self.w2_scale,
+                return moe_native.fused_experts_fp8(x, self.w13_weight, self.w13_scale, self.w2_weight, self.w2_scale,
                                                     topk_weights, topk_ids, self.expert_start, self.workspace, add,
                                                     out)
             return moe_native.fused_experts(x, self.w13_weight, self.w2_weight, topk_weights, topk_ids,
@@ -154,11 +203,11 @@ def _fp8_reference_experts(x, moe: "FusedMoE", topk_weights, topk_ids):
         if tok.numel() == 0:
             continue
         xq, sx = quantize_activation(x[tok], torch.float8_e4m3fn)
-        h = (xq.float() @ moe.w13_q[e].float().t()) * sx * moe.w13_scale[e][None, :]
+        h = (xq.float() @ moe.w13_weight[e].float().t()) * sx * moe.w13_scale[e][None, :]
         h = h.to(x.dtype).float()
         a = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
         aq, sa = quantize_activation(a, torch.float8_e4m3fn)
-        y = (aq.float() @ moe.w2_q[e].float().t()) * sa * moe.w2_scale[e][None, :]
+        y = (aq.float() @ moe.w2_weight[e].float().t()) * sa * moe.w2_scale[e][None, :]
         y = y.to(x.dtype).float()
         out.index_add_(0, tok, y * topk_weights[tok, slot].float()[:, None])
     return out.to(x.dtype)

@@ -75,6 +75,17 @@ def hash_name(name: str) -> int:
     return h
 
 
+def _expert_storage_for(quant_config):
+    """Dynamic W8A8 e4m3 per-channel recipes build the routed experts directly in e4m3 storage, so a model whose
+    bf16 experts would not fit on the device can still be loaded (each expert is quantised as it arrives)."""
+    from ..layers.moe import expert_storage
+    fp8 = torch.float8_e4m3fn
+    native = (quant_config is not None and not quant_config.is_static_checkpoint
+              and quant_config.moe_weight_dtype == fp8 and quant_config.moe_activation_dtype == fp8
+              and not quant_config.moe_weight_block_size)
+    return expert_storage(fp8 if native else None)
+
+
 def _apply_dynamic_quantization(model, quant_config):
     """Dynamic recipes quantise the loaded (or dummy-initialised) bf16 weights in place."""
     if quant_config is None or quant_config.is_static_checkpoint:
@@ -90,7 +101,7 @@ class DefaultModelLoader:
 
     def load_model(self, model_config, device, quant_config=None) -> torch.nn.Module:
         cls = get_model_class(model_config.architectures)
-        with torch.device(device):
+        with torch.device(device), _expert_storage_for(quant_config):
             model = cls(model_config.hf_config, dtype=model_config.dtype, quant_config=quant_config) \
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
         it = dequant_static_fp8(self._iterator(model_config.model_path), getattr(quant_config, "weight_block_size", None))
@@ -117,7 +128,7 @@ class DummyModelLoader:
 
     def load_model(self, model_config, device, quant_config=None) -> torch.nn.Module:
         cls = get_model_class(model_config.architectures)
-        with torch.device(device):
+        with torch.device(device), _expert_storage_for(quant_config):
             model = cls(model_config.hf_config, dtype=model_config.dtype, quant_config=quant_config) \
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
         initialize_dummy_weights(model, self.seed)

@@ -41,7 +41,7 @@ def load_sparse_weights(model, weights: Iterable[tuple[str, torch.Tensor]], rena
             pname = f"{head}." + ("w2_weight" if shard == "down" else "w13_weight")
             if pname in params:
                 p = params[pname]
-                modules[head].weight_loader(p, w.to(p.dtype), shard, e)
+                modules[head].weight_loader(p, w, shard, e)
                 loaded.add(pname)
             continue
         if name.endswith(".experts.gate_up_proj") or name.endswith(".experts.down_proj"):
@@ -51,13 +51,13 @@ def load_sparse_weights(model, weights: Iterable[tuple[str, torch.Tensor]], rena
                 p = params[f"{head}.w13_weight"]
                 half = w.shape[1] // 2
                 for e in range(w.shape[0]):
-                    mod.weight_loader(p, w[e, :half].to(p.dtype), "gate", e)
-                    mod.weight_loader(p, w[e, half:].to(p.dtype), "up", e)
+                    mod.weight_loader(p, w[e, :half], "gate", e)
+                    mod.weight_loader(p, w[e, half:], "up", e)
                 loaded.add(f"{head}.w13_weight")
             else:
                 p = params[f"{head}.w2_weight"]
                 for e in range(w.shape[0]):
-                    mod.weight_loader(p, w[e].to(p.dtype), "down", e)
+                    mod.weight_loader(p, w[e], "down", e)
                 loaded.add(f"{head}.w2_weight")
             continue
         if name.endswith("e_score_correction_bias"):

@@ -104,7 +104,7 @@ class Qwen3MoeForCausalLM(LlamaForCausalLM):
                     pname = f"{head}.mlp.experts." + ("w2_weight" if shard == "down" else "w13_weight")
                     if pname in params:
                         p = params[pname]
-                        modules[f"{head}.mlp.experts"].weight_loader(p, w.to(p.dtype), shard, int(e_str))
+                        modules[f"{head}.mlp.experts"].weight_loader(p, w, shard, int(e_str))
                         self._loaded_extra.add(pname)
                     continue
                 if name.endswith(".mlp.experts.gate_up_proj") or name.endswith(".mlp.experts.down_proj"):
@@ -115,13 +115,13 @@ class Qwen3MoeForCausalLM(LlamaForCausalLM):
                         p = params[f"{head}.mlp.experts.w13_weight"]
                         I = w.shape[1] // 2
                         for e in range(w.shape[0]):
-                            mod.weight_loader(p, w[e, :I].to(p.dtype), "gate", e)
-                            mod.weight_loader(p, w[e, I:].to(p.dtype), "up", e)
+                            mod.weight_loader(p, w[e, :I], "gate", e)
+                            mod.weight_loader(p, w[e, I:], "up", e)
                         self._loaded_extra.add(f"{head}.mlp.experts.w13_weight")
                     else:
                         p = params[f"{head}.mlp.experts.w2_weight"]
                         for e in range(w.shape[0]):
-                            mod.weight_loader(p, w[e].to(p.dtype), "down", e)
+                            mod.weight_loader(p, w[e], "down", e)
                         self._loaded_extra.add(f"{head}.mlp.experts.w2_weight")
                     continue
                 yield name, w

@@ -246,7 +246,7 @@ def test_fused_experts_fp8(native, T, E, E_local, e0, k, H, I):
     tw, ids = ref.topk_route(logits, k)
     full = ref.moe_forward(x.float(), moe.w13_weight.float(), moe.w2_weight.float(), tw, ids, e0)
     moe.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)
-    assert moe.fp8 and moe.w13_weight is None and moe.w13_q.dtype == torch.float8_e4m3fn
+    assert moe.fp8 and moe.w13_weight.dtype == torch.float8_e4m3fn and moe.w13_scale.shape == (E_local, 2 * I)
     got = moe(x, tw, ids)
     torch.cuda.synchronize()
     native.check_status()

@@ -267,7 +267,7 @@ def test_qwen3_moe_fp8_recipe_runs_on_grouped_fp8_gemm(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(cfg))
     runner, _ = _runner(str(tmp_path), load_format="dummy", cuda_graph_max_bs=8, quantization="fp8_qwen3_30b_a3b")
     moes = [m for m in runner.model.modules() if isinstance(m, FusedMoE)]
-    assert len(moes) == 2 and all(m.fp8 and m.w13_weight is None for m in moes)
+    assert len(moes) == 2 and all(m.fp8 and m.w13_weight.dtype == torch.float8_e4m3fn for m in moes)
     calls = {"n": 0}
     orig = moe_native.fused_experts_fp8
 

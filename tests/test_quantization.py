@@ -151,11 +151,72 @@ def test_fused_moe_fp8_storage_keeps_only_quantised_experts():
     blocky.quantize_(torch.float8_e4m3fn, (16, 16), torch.float8_e4m3fn)
     assert not blocky.fp8 and blocky.w13_weight.dtype == torch.bfloat16
     moe.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)
-    assert moe.fp8 and moe.w13_weight is None and moe.w2_weight is None
-    assert sorted(n for n, _ in moe.named_parameters()) == ["w13_q", "w13_scale", "w2_q", "w2_scale"]
-    assert moe.w13_q.dtype == torch.float8_e4m3fn and moe.w13_scale.shape == (4, 64) and moe.w2_scale.shape == (4, 64)
+    assert moe.fp8 and moe.w13_weight.dtype == torch.float8_e4m3fn and moe.w2_weight.dtype == torch.float8_e4m3fn
+    assert sorted(n for n, _ in moe.named_parameters()) == ["w13_weight", "w2_weight"]
+    assert sorted(n for n, _ in moe.named_buffers()) == ["w13_scale", "w2_scale"]
+    assert moe.w13_scale.shape == (4, 64) and moe.w2_scale.shape == (4, 64)
     got = moe(x, w, ids, add=add).float()
     assert got.std() > 0.05
     assert ((got - want).norm() / want.norm()).item() < 0.08
     w13, w2 = moe._bf16_weights()
     assert w13.shape == (4, 64, 64) and w2.dtype == torch.bfloat16
+
+
+def test_experts_built_in_fp8_storage_quantise_while_loading():
+    """Under `expert_storage(e4m3)` the experts never exist in bf16: per-expert checkpoint tensors are quantised by
+    the weight loader, and the result equals quantising a bf16-loaded layer afterwards (tensor-parallel slices too)."""
+    from sglang_jax_b200.layers.moe import FusedMoE, expert_storage
+    torch.manual_seed(0)
+    E, H, I = 4, 64, 64
+    gate = [torch.randn(I, H).bfloat16() * 0.1 for _ in range(E)]
+    up = [torch.randn(I, H).bfloat16() * 0.1 for _ in range(E)]
+    down = [torch.randn(H, I).bfloat16() * 0.1 for _ in range(E)]
+    for tp, rank in ((1, 0), (2, 1)):
+        plain = FusedMoE(E, H, I, tp_size=tp, tp_rank=rank, ep_size=1)
+        with expert_storage(torch.float8_e4m3fn):
+            lean = FusedMoE(E, H, I, tp_size=tp, tp_rank=rank, ep_size=1)
+        assert lean.fp8 and lean.w13_weight.dtype == torch.float8_e4m3fn and not plain.fp8
+        for m in (plain, lean):
+            for e in range(E):
+                m.weight_loader(m.w13_weight, gate[e], "gate", e)
+                m.weight_loader(m.w13_weight, up[e], "up", e)
+                m.weight_loader(m.w2_weight, down[e], "down", e)
+        plain.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)
+        assert plain.fp8
+        assert torch.equal(plain.w13_weight.view(torch.uint8), lean.w13_weight.view(torch.uint8))
+        assert torch.equal(plain.w2_weight.view(torch.uint8), lean.w2_weight.view(torch.uint8))
+        assert torch.equal(plain.w13_scale, lean.w13_scale) and torch.equal(plain.w2_scale, lean.w2_scale)
+        lean.quantize_(torch.float8_e4m3fn, None, torch.float8_e4m3fn)             # a no-op on fp8-built experts
+        x = torch.randn(9, H).bfloat16()
+        ids = torch.stack([torch.randperm(E)[:2] for _ in range(9)]).int()
+        w = torch.rand(9, 2)
+        assert torch.equal(lean(x, w, ids), plain(x, w, ids))
+    # float32 experts (CPU reference runs) keep the compute-dtype storage
+    with expert_storage(torch.float8_e4m3fn):
+        assert not FusedMoE(E, H, I, dtype=torch.float32, tp_size=1, tp_rank=0, ep_size=1).fp8
+
+
+def test_dummy_loader_builds_fp8_experts_for_w8a8_recipes(tmp_path):
+    import json
+    from sglang_jax_b200.configs.model_config import ModelConfig
+    from sglang_jax_b200.configs.quantization_config import QuantizationConfig
+    from sglang_jax_b200.layers.moe import FusedMoE
+    from sglang_jax_b200.model_loader.loader import DummyModelLoader
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.server_args import ServerArgs
+    cfg = dict(architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", hidden_size=64, intermediate_size=128,
+               moe_intermediate_size=32, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+               num_experts=4, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+               rms_norm_eps=1e-6, rope_theta=10000.0, vocab_size=128, tie_word_embeddings=False,
+               max_position_embeddings=256, torch_dtype="bfloat16")
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    ps.reset_state()
+    ps.init_distributed(0, 1, "cpu")
+    sa = ServerArgs(model_path=str(tmp_path), device="cpu", dtype="bfloat16", skip_tokenizer_init=True,
+                    load_format="dummy", quantization="fp8_qwen3_30b_a3b")
+    mc = ModelConfig.from_server_args(sa)
+    model = DummyModelLoader(0).load_model(mc, "cpu", QuantizationConfig.resolve("fp8_qwen3_30b_a3b"))
+    moes = [m for m in model.modules() if isinstance(m, FusedMoE)]
+    assert len(moes) == 2 and all(m.fp8 and m.w13_weight.dtype == torch.float8_e4m3fn for m in moes)
+    eff = moes[0]._bf16_weights()[0].float()
+    assert 0.01 < eff.std().item() < 0.04                     # e4m3 normal(0, 1) values times the 0.02 default scale
