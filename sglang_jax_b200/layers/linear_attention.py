@@ -16,6 +16,20 @@ from .layernorm import GatedRMSNorm
 from .linear import ReplicatedLinear
 
 
+def track_pieces(a0: int, a1: int, track):
+    """Token ranges of one sequence's extend `[a0, a1)` and, per range, the snapshot slot that receives the
+    recurrent state at its end: `track = (tokens before the checkpoint, slot)` splits the extend there."""
+    if track is None:
+        return [(a0, a1, None)]
+    k, slot = track
+    cut = a0 + k
+    if cut <= a0 or cut > a1:
+        return [(a0, a1, None)]
+    if cut == a1:
+        return [(a0, a1, slot)]
+    return [(a0, cut, slot), (cut, a1, None)]
+
+
 def recurrent_slots(fb) -> torch.Tensor:
     """State slot of every row of the batch: request row + 1 (slot 0 is scratch).  A captured decode step
     supplies them itself so that its padding rows land on the scratch slot."""
@@ -104,19 +118,25 @@ class GatedDeltaNet(nn.Module):
             cu = fb.cu_q_lens.tolist()
             pre = fb.extend_prefix_lens_cpu
             sl = slots.tolist()
+            tracks = fb.extras.get("recurrent_tracks") or {}
             for i in range(fb.batch_size):
-                a0, a1 = cu[i], cu[i + 1]
-                if a1 == a0:
+                if cu[i + 1] == cu[i]:
                     continue
                 fresh = int(pre[i]) == 0
-                y, new_conv = la.causal_conv1d_prefill(mixed[a0:a1], self.conv1d_weight,
-                                                       None if fresh else conv_all[sl[i]])
-                conv_all[sl[i]] = new_conv.to(conv_all.dtype)
-                qq, kk, vv = heads(y)
-                oi, S = la.chunk_gated_delta_rule(qq, kk, vv, g[a0:a1], beta[a0:a1],
-                                                  None if fresh else rec_all[sl[i]])
-                o[a0:a1] = oi
-                rec_all[sl[i]] = S
+                # a checkpoint inside the extend splits it: the state after the first piece also goes to the snapshot slot
+                for a0, a1, snap in track_pieces(cu[i], cu[i + 1], tracks.get(i)):
+                    y, new_conv = la.causal_conv1d_prefill(mixed[a0:a1], self.conv1d_weight,
+                                                           None if fresh else conv_all[sl[i]])
+                    conv_all[sl[i]] = new_conv.to(conv_all.dtype)
+                    qq, kk, vv = heads(y)
+                    oi, S = la.chunk_gated_delta_rule(qq, kk, vv, g[a0:a1], beta[a0:a1],
+                                                      None if fresh else rec_all[sl[i]])
+                    o[a0:a1] = oi
+                    rec_all[sl[i]] = S
+                    fresh = False
+                    if snap is not None:
+                        conv_all[snap] = conv_all[sl[i]]
+                        rec_all[snap] = rec_all[sl[i]]
         out = self.norm(o.reshape(-1, self.dv), z.reshape(-1, self.dv)).reshape(T, self.value_dim)
         return self.out_proj(out)
 
@@ -136,10 +156,17 @@ class _RecurrentMixer(nn.Module):
             return per_batch(conv_all, rec_all, slots)
         cu = fb.cu_q_lens.tolist()
         pre = fb.extend_prefix_lens_cpu
+        tracks = fb.extras.get("recurrent_tracks") or {}
         outs = []
         for i, s in enumerate(slots.tolist()):
             if cu[i + 1] > cu[i]:
-                outs.append(per_seq(conv_all, rec_all, s, cu[i], cu[i + 1], int(pre[i]) == 0))
+                fresh = int(pre[i]) == 0
+                for a0, a1, snap in track_pieces(cu[i], cu[i + 1], tracks.get(i)):
+                    outs.append(per_seq(conv_all, rec_all, s, a0, a1, fresh))
+                    fresh = False
+                    if snap is not None:
+                        conv_all[snap] = conv_all[s]
+                        rec_all[snap] = rec_all[s]
         return torch.cat(outs, 0)
 
 

@@ -433,6 +433,9 @@ class ModelWorkerBatch:
     deepstack_embeds: Any = None
     # (src, dst) recurrent-state slot copies to run, in order, before this forward
     recurrent_copies: list | None = None
+    # (index of the sequence in the batch, tokens of this extend before the checkpoint, snapshot slot): the
+    # linear-attention layers store their state after that many tokens of the sequence into the slot
+    recurrent_tracks: list | None = None
 
     @property
     def batch_size(self):
@@ -543,6 +546,8 @@ class ScheduleBatch:
             if fresh_row and hasattr(self.tree_cache, "on_request_scheduled"):
                 self.tree_cache.on_request_scheduled(r)        # clone the prefix's recurrent state
             seq = len(r.fill_ids)
+            if hasattr(self.tree_cache, "on_extend_scheduled"):
+                self.tree_cache.on_extend_scheduled(r, pre, seq)   # may ask for a state checkpoint inside this extend
             input_ids.extend(r.fill_ids[pre:])
             prefix_lens.append(pre)
             seq_lens.append(seq)
@@ -831,6 +836,9 @@ class ScheduleBatch:
             input_embeds=mm_embeds, input_embeds_rows=mm_rows, mrope_positions=mrope, deepstack_embeds=deepstack,
             recurrent_copies=(self.tree_cache.take_recurrent_copies()
                               if hasattr(self.tree_cache, "take_recurrent_copies") else None) or None,
+            recurrent_tracks=(self.tree_cache.take_recurrent_tracks(self.reqs)
+                              if self.forward_mode.is_extend() and hasattr(self.tree_cache, "take_recurrent_tracks")
+                              else None) or None,
         )
 
     def _multimodal_inputs(self, positions: np.ndarray):

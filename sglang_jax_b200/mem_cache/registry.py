@@ -6,7 +6,7 @@ Factories are looked up by name so a deployment can register its own (`register_
 
 * sliding-window hybrid KV pool      -> `SWARadixCache` over the dual allocator
 * `--disable-radix-cache`            -> `ChunkCache`
-* recurrent (linear-attention) model -> `UnifiedRadixCache` (needs page size 1 and snapshot slots, else no sharing)
+* recurrent (linear-attention) model -> `UnifiedRadixCache` (needs snapshot slots, else no sharing)
 * `--hicache-storage`                -> `HiRadixCache`
 * otherwise                          -> radix tree (C++ when built)
 """
@@ -59,12 +59,11 @@ def default_radix_cache_factory(ctx: TreeCacheBuildContext) -> TreeCacheBuildRes
     from .chunk_cache import ChunkCache
     sa, kv, rp = ctx.server_args, ctx.kv_pool, ctx.recurrent_pool
     recurrent = is_recurrent(ctx)
-    if recurrent and not sa.disable_radix_cache and (rp is None or rp.snapshot_slots <= 0 or ctx.page_size != 1
+    if recurrent and not sa.disable_radix_cache and (rp is None or rp.snapshot_slots <= 0
                                                      or sa.hicache_storage != "disable"):
-        # a shared prefix needs the recurrent state at its end; checkpoints exist only for
-        # token-granular pages and a non-empty snapshot area
-        logger.info("hybrid linear-attention model: prefix sharing is off (needs --page-size 1 and "
-                    "--recurrent-snapshot-slots > 0)")
+        # a shared prefix needs the recurrent state at its end: checkpoints live in the snapshot area
+        logger.info("hybrid linear-attention model: prefix sharing is off (needs --recurrent-snapshot-slots > 0 "
+                    "and no host cache tier)")
         sa.disable_radix_cache = True
     if kv is not None and hasattr(kv, "swa_pool"):
         from .allocator import SWATokenToKVPoolAllocator
@@ -81,7 +80,8 @@ def default_radix_cache_factory(ctx: TreeCacheBuildContext) -> TreeCacheBuildRes
     if recurrent:
         from .unified_radix_cache import UnifiedRadixCache
         cache = UnifiedRadixCache(p.req_to_token_pool, alloc, p.page_size, num_request_slots=rp.size,
-                                  num_snapshot_slots=rp.snapshot_slots, enable_kv_cache_events=p.enable_kv_cache_events)
+                                  num_snapshot_slots=rp.snapshot_slots, enable_kv_cache_events=p.enable_kv_cache_events,
+                                  track_interval=getattr(sa, "recurrent_track_interval", None))
         # a finished request's state is checkpointed from its slot: no extra overlapped step may touch it
         return TreeCacheBuildResult(alloc, cache, needs_sequential_schedule=True)
     if sa.hicache_storage != "disable" and kv is not None:

@@ -7,8 +7,12 @@ at its *end* is available (the RECURRENT component).  Nodes therefore may carry 
 slot of the `RecurrentStatePool` snapshot area holding the conv window and state matrix after the
 node's last token.  Matching walks the tree as usual but stops at the deepest node that has a
 snapshot; the request then starts from a copy of it (copy-on-write into its own slot) and
-recomputes the rest.  A finished request commits its final state to the node that ends exactly
-at its last cached token.
+recomputes the rest.  Snapshots are taken (a) inside every prefill step at the last multiple of the
+track interval the step covers: a slot is reserved when the step is scheduled, the workers store the state there
+while they run the step, and afterwards the page-aligned prefix is published and the snapshot
+attached to the node ending at it (the role of the reference's `recurrent_track_interval` tracking;
+the interval is a multiple of the page size); (b) at the end of a finished request when that end is
+page-aligned.
 
 Differences from the reference's component design, chosen for this runtime: snapshots may sit on
 internal nodes too (the reference keeps them on leaves and drops one when its node gains a
@@ -36,8 +40,14 @@ class ComponentType(IntEnum):
 
 class UnifiedRadixCache(RadixCache):
     def __init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size: int = 1, disable: bool = False,
-                 num_request_slots: int = 0, num_snapshot_slots: int = 0, enable_kv_cache_events: bool = False):
+                 num_request_slots: int = 0, num_snapshot_slots: int = 0, enable_kv_cache_events: bool = False,
+                 track_interval: int | None = None):
         self.components = (ComponentType.FULL, ComponentType.RECURRENT)
+        # prefill checkpoints sit on multiples of this many tokens (a multiple of the page size)
+        self.track_interval = int(track_interval or page_size)
+        if self.track_interval <= 0 or self.track_interval % page_size:
+            raise ValueError(f"recurrent_track_interval ({self.track_interval}) must be a positive multiple of the "
+                             f"page size ({page_size})")
         self.snapshot_base = num_request_slots + 1          # request row r owns state slot r + 1
         self.num_snapshot_slots = num_snapshot_slots
         super().__init__(req_to_token_pool, token_to_kv_pool_allocator, page_size, disable, enable_kv_cache_events)
@@ -50,6 +60,9 @@ class UnifiedRadixCache(RadixCache):
         self._lru: OrderedDict[int, None] = OrderedDict()   # node ids, least recently used first
         self._free_snap = list(range(self.snapshot_base, self.snapshot_base + self.num_snapshot_slots))
         self._copies: list[tuple[int, int]] = []
+        # request id -> [aligned length, tokens of the extend before it, snapshot slot, sent to the workers]
+        self._pending_track: dict[str, list] = {}
+        self._raw_match = False
 
     def supports_recurrent(self) -> bool:
         return True
@@ -69,7 +82,7 @@ class UnifiedRadixCache(RadixCache):
         return len(self._snap)
 
     def assert_recurrent_slot_ledger(self):
-        used = sorted(self._snap.values())
+        used = sorted(list(self._snap.values()) + [t[2] for t in self._pending_track.values()])
         assert len(set(used)) == len(used), "a snapshot slot is owned twice"
         assert sorted(used + self._free_snap) == list(range(self.snapshot_base,
                                                             self.snapshot_base + self.num_snapshot_slots)), \
@@ -79,6 +92,8 @@ class UnifiedRadixCache(RadixCache):
     # ---------------------------------------------------------------- match
     def match_prefix(self, key: RadixKey, req=None, **kw) -> MatchResult:
         res = super().match_prefix(key)
+        if self._raw_match:
+            return res                                    # re-pointing a running request at its own prefix
         node = res.last_device_node
         if self.disable or node is self.root_node:
             if req is not None:
@@ -100,6 +115,9 @@ class UnifiedRadixCache(RadixCache):
 
     # ---------------------------------------------------------------- request hooks
     def cache_finished_req(self, req, is_insert: bool = True, **kw):
+        track = self._pending_track.pop(req.rid, None)       # finished / aborted before its prefill was published
+        if track is not None:
+            self._free_snap.append(track[2])
         kv_len = req.committed_kv_len()
         tokens = (req.origin_input_ids + req.output_ids)[:kv_len]
         row = req.req_pool_idx
@@ -119,9 +137,57 @@ class UnifiedRadixCache(RadixCache):
         self.queue_copy(row + 1, slot)
 
     def cache_unfinished_req(self, req, chunked: bool = False, **kw):
-        # the state of an in-flight prefill is only in the request's own slot: nothing to share yet
-        kv_len = len(req.fill_ids)
-        req.prefix_indices = self.req_to_token_pool.read(req.req_pool_idx, kv_len).copy()
+        """After a prefill step.  Without a checkpoint inside the step the state exists only in the request's own
+        slot and nothing is published.  With one (`on_extend_scheduled`), the page-aligned prefix goes into the
+        tree like in a plain radix cache and the checkpoint is attached to the node that ends at it."""
+        track = self._pending_track.pop(req.rid, None)
+        if self.disable or track is None or not track[3]:
+            if track is not None:
+                self._free_snap.append(track[2])
+            kv_len = len(req.fill_ids)
+            req.prefix_indices = self.req_to_token_pool.read(req.req_pool_idx, kv_len).copy()
+            return
+        aligned, _, slot, _ = track
+        self._raw_match = True
+        try:
+            super().cache_unfinished_req(req, chunked, **kw)
+        finally:
+            self._raw_match = False
+        dp = getattr(req, "dp_rank", 0) or 0
+        tokens = req.fill_ids[:aligned]
+        values, node = self._match(tokens, RadixKey(tokens, req.extra_key, dp).namespace)
+        if node is self.root_node or sum(len(v) for v in values) != aligned or node.id in self._snap:
+            self._free_snap.append(slot)
+            return
+        self._snap[node.id] = slot
+        self._nodes[node.id] = node
+        self._lru[node.id] = None
+
+    def on_extend_scheduled(self, req, prefix_len: int, seq_len: int):
+        """A prefill step covering tokens `[prefix_len, seq_len)` is about to run: if a page boundary falls inside
+        it, reserve a snapshot slot and ask the workers to store the state at the last such boundary."""
+        if self.disable:
+            return
+        old = self._pending_track.pop(req.rid, None)
+        if old is not None:
+            self._free_snap.append(old[2])
+        aligned = seq_len // self.track_interval * self.track_interval
+        if aligned <= prefix_len or aligned <= 0:
+            return
+        slot = self._alloc_snapshot()
+        if slot is None:
+            return
+        self._pending_track[req.rid] = [aligned, aligned - prefix_len, slot, False]
+
+    def take_recurrent_tracks(self, reqs) -> list[tuple[int, int, int]]:
+        """(index in the batch, tokens of the extend before the checkpoint, snapshot slot) per request."""
+        out = []
+        for i, r in enumerate(reqs):
+            t = self._pending_track.get(r.rid)
+            if t is not None:
+                t[3] = True
+                out.append((i, t[1], t[2]))
+        return out
 
     def on_request_scheduled(self, req):
         """First prefill of a request that matched a snapshot: clone it into the request's slot."""

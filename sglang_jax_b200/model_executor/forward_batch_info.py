@@ -141,6 +141,8 @@ class ForwardBatch:
         )
         if getattr(runner, "recurrent_pool", None) is not None:
             fb.extras["recurrent_pool"] = runner.recurrent_pool
+            if getattr(batch, "recurrent_tracks", None):
+                fb.extras["recurrent_tracks"] = {int(i): (int(k), int(slot)) for i, k, slot in batch.recurrent_tracks}
         if getattr(batch, "deepstack_embeds", None) is not None:
             fb.extras["deepstack"] = batch.deepstack_embeds.to(runner.device, runner.dtype)
         if getattr(batch, "mrope_positions", None) is not None:

@@ -434,6 +434,64 @@ def test_bailing_linear_lightning_hybrid_is_chunk_and_batch_invariant(tmp_path):
     assert all(len(o) == 6 for o in out)
 
 
+@pytest.mark.parametrize("family", ["kimi_linear", "bailing_linear"])
+def test_kda_and_lightning_hybrids_share_prefixes_through_page_checkpoints(tmp_path, family):
+    """Pages of 16 tokens and chunked prefill: the recurrent state is checkpointed at the last page boundary inside
+    each prefill step, a later request with the same opening restarts from that checkpoint (KV reused, state cloned)
+    and generates exactly what it generates without any sharing."""
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    if family == "kimi_linear":
+        cfg = dict(architectures=["KimiLinearForCausalLM"], model_type="kimi_linear", hidden_size=64,
+                   intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=4, num_attention_heads=4,
+                   num_key_value_heads=4, rms_norm_eps=1e-5, vocab_size=256, max_position_embeddings=512,
+                   kv_lora_rank=32, q_lora_rank=None, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                   mla_use_nope=True, num_experts=4, num_experts_per_token=2, num_shared_experts=1,
+                   first_k_dense_replace=1, moe_layer_freq=1, moe_router_activation_func="sigmoid",
+                   routed_scaling_factor=1.0, tie_word_embeddings=False,
+                   linear_attn_config={"kda_layers": [1, 2, 3], "full_attn_layers": [4], "num_heads": 4,
+                                       "head_dim": 16, "short_conv_kernel_size": 4})
+    else:
+        cfg = dict(architectures=["BailingMoeLinearForCausalLM"], model_type="bailing_moe_linear", hidden_size=64,
+                   intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=4, num_attention_heads=4,
+                   num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, vocab_size=256, max_position_embeddings=512,
+                   num_experts=4, num_experts_per_tok=2, num_shared_experts=1, first_k_dense_replace=1, n_group=1,
+                   topk_group=1, routed_scaling_factor=1.0, score_function="sigmoid", layer_group_size=4,
+                   tie_word_embeddings=False, rope_theta=10000.0, partial_rotary_factor=0.5)
+    path = tmp_path / family
+    path.mkdir()
+    (path / "config.json").write_text(json.dumps(dict(cfg, torch_dtype="float32")))
+    opening = list(range(5, 75))                                 # 70 tokens: page boundaries at 16 .. 64
+    sp = {"max_new_tokens": 5, "temperature": 0, "ignore_eos": True}
+
+    def run(**kw):
+        ps.reset_state()
+        eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                     max_total_tokens=2048, enable_single_process=True, load_format="dummy", chunked_prefill_size=32,
+                     **kw)
+        try:
+            a = eng.generate(input_ids=opening + [200, 201], sampling_params=sp)
+            b = eng.generate(input_ids=[opening + [210, 211, 212], opening[:40] + [99] * 9], sampling_params=sp)
+            tc = eng.scheduler.tree_cache
+            if hasattr(tc, "assert_recurrent_slot_ledger"):
+                tc.assert_recurrent_slot_ledger()
+            eng.scheduler.check_memory()
+            return (type(tc).__name__, a["output_ids"], [o["output_ids"] for o in b],
+                    [o["meta_info"]["cached_tokens"] for o in b])
+        finally:
+            eng.shutdown()
+
+    shared, plain = run(), run(disable_radix_cache=True)
+    assert shared[0] == "UnifiedRadixCache"
+    assert shared[1:3] == plain[1:3]
+    assert len({t for o in shared[2] for t in o}) > 2
+    assert shared[3] == [64, 32] and plain[3] == [0, 0]          # checkpoints at the chunk ends 32 and 64
+    coarse = run(recurrent_track_interval=32)                    # checkpoints only on multiples of 32 tokens
+    assert coarse[1:3] == plain[1:3] and coarse[3] == [64, 32]
+    with pytest.raises(Exception):
+        run(recurrent_track_interval=24)                         # not a multiple of the page size
+
+
 def test_kda_and_lightning_ops_match_stepwise_recurrence():
     from sglang_jax_b200.ops import linear_attention as la
     g = torch.Generator().manual_seed(0)
@@ -587,8 +645,9 @@ def test_hybrid_recurrent_prefix_sharing_reuses_state_checkpoints(tmp_path):
 
     def run(**kw):
         ps.reset_state()
-        eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=1, skip_tokenizer_init=True,
-                     max_total_tokens=1024, enable_single_process=True, load_format="dummy", **kw)
+        eng = Engine(model_path=str(path), device="cpu", dtype="float32", skip_tokenizer_init=True,
+                     max_total_tokens=1024, enable_single_process=True, load_format="dummy",
+                     **{"page_size": 1, **kw})
         try:
             first = eng.generate(input_ids=base, sampling_params=sp)
             cont = base + first["output_ids"][:5]                      # exactly the first request's cached tokens
@@ -614,11 +673,10 @@ def test_hybrid_recurrent_prefix_sharing_reuses_state_checkpoints(tmp_path):
     # two snapshot slots only: checkpoints are recycled least-recently-used first and nothing leaks
     tight = run(recurrent_snapshot_slots=2)
     assert tight[1:4] == plain[1:4] and tight[6] <= 2
-    # page size > 1 turns sharing off for these models
-    ps.reset_state()
-    eng = Engine(model_path=str(path), device="cpu", dtype="float32", page_size=4, skip_tokenizer_init=True,
-                 max_total_tokens=1024, enable_single_process=True, load_format="dummy")
-    try:
-        assert type(eng.scheduler.tree_cache).__name__ == "ChunkCache"
-    finally:
-        eng.shutdown()
+    # pages of 4 tokens: the state is checkpointed at the last page boundary inside each prefill (here token 40 of
+    # the first prompt), so later requests restart from there and still produce the unshared tokens
+    paged = run(page_size=4)
+    paged_plain = run(page_size=4, disable_radix_cache=True)
+    assert paged[0] == "UnifiedRadixCache"
+    assert paged[1:4] == paged_plain[1:4] == plain[1:4]
+    assert paged[4] == 40 and paged[5] == [40, 0] and paged[6] >= 1
