@@ -44,14 +44,16 @@ class LogitsProcessor(nn.Module):
         self.soft_cap = soft_cap
         self.skip_all_gather = skip_all_gather
 
-    def _project(self, hidden: torch.Tensor, lm_head, local_only: bool = False) -> torch.Tensor:
+    def _project(self, hidden: torch.Tensor, lm_head, local_only: bool = False, fused_gather: bool = True) -> torch.Tensor:
+        """`fused_gather`: the peer-store gather returns a view of one symmetric buffer that the next such call
+        overwrites, so only the step's next-token logits (consumed before the next step) go through it."""
         logits = ops.linear(hidden, lm_head.weight)
         if local_only:
             # this rank's vocab shard (padding columns included); the sampler reduces across ranks
             return logits
         if lm_head.tp_size > 1 and not self.skip_all_gather:
             comm = ps.get_state().fused_comm
-            if comm is not None and comm.supports_logits_gather(logits):
+            if fused_gather and comm is not None and comm.supports_logits_gather(logits):
                 logits = comm.logits_gather(logits)
             else:
                 logits = ps.all_gather(logits, dim=-1)
@@ -67,7 +69,9 @@ class LogitsProcessor(nn.Module):
         else:
             last = hidden_states[fb.last_token_indices]
         local_only = bool(fb.extras.get("skip_logits_gather")) and lm_head.tp_size > 1 and not self.soft_cap
-        out = LogitsProcessorOutput(next_token_logits=self._project(last, lm_head, local_only))
+        # speculative flows keep several logits tensors alive inside one step: they stay off the shared gather buffer
+        plain_step = getattr(fb, "spec_info", None) is None and fb.capture_hidden_mode == 0
+        out = LogitsProcessorOutput(next_token_logits=self._project(last, lm_head, local_only, fused_gather=plain_step))
         if local_only:
             out.extras["vocab_shard"] = (lm_head.vocab_start, self.vocab_size)
         if fb.capture_hidden_mode == 1:
@@ -99,7 +103,7 @@ class LogitsProcessor(nn.Module):
             return
         rows_t = torch.cat(rows)
         tgt = torch.cat(targets).long()
-        logits = self._project(hidden_states[rows_t], lm_head).float()
+        logits = self._project(hidden_states[rows_t], lm_head, fused_gather=False).float()
         lp = torch.log_softmax(logits, dim=-1)
         out.input_token_logprobs = lp.gather(1, tgt.unsqueeze(1)).squeeze(1)
         out.extras["input_logprobs_full"] = lp
