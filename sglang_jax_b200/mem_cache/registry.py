@@ -81,9 +81,12 @@ def default_radix_cache_factory(ctx: TreeCacheBuildContext) -> TreeCacheBuildRes
         from .unified_radix_cache import UnifiedRadixCache
         cache = UnifiedRadixCache(p.req_to_token_pool, alloc, p.page_size, num_request_slots=rp.size,
                                   num_snapshot_slots=rp.snapshot_slots, enable_kv_cache_events=p.enable_kv_cache_events,
-                                  track_interval=getattr(sa, "recurrent_track_interval", None))
-        # a finished request's state is checkpointed from its slot: no extra overlapped step may touch it
-        return TreeCacheBuildResult(alloc, cache, needs_sequential_schedule=True)
+                                  track_interval=getattr(sa, "recurrent_track_interval", None),
+                                  commit_on_finish=bool(sa.disable_overlap_schedule))
+        # checkpoints taken inside prefill steps are safe under overlap scheduling; the one at the end of a finished
+        # request reads the request's own slot, which an overlapped extra decode step may already have advanced, so
+        # it is only taken when the schedule is sequential
+        return TreeCacheBuildResult(alloc, cache)
     if sa.hicache_storage != "disable" and kv is not None:
         from .hiradix_cache import HiRadixCache
         return TreeCacheBuildResult(alloc, HiRadixCache(p.req_to_token_pool, alloc, p.page_size, kv, sa.hicache_ratio,

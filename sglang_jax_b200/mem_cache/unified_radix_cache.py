@@ -41,8 +41,11 @@ class ComponentType(IntEnum):
 class UnifiedRadixCache(RadixCache):
     def __init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size: int = 1, disable: bool = False,
                  num_request_slots: int = 0, num_snapshot_slots: int = 0, enable_kv_cache_events: bool = False,
-                 track_interval: int | None = None):
+                 track_interval: int | None = None, commit_on_finish: bool = True):
         self.components = (ComponentType.FULL, ComponentType.RECURRENT)
+        # checkpoint the final state of a finished request from its own slot: only sound when no overlapped extra
+        # decode step can have advanced that slot past the request's last cached token
+        self.commit_on_finish = commit_on_finish
         # prefill checkpoints sit on multiples of this many tokens (a multiple of the page size)
         self.track_interval = int(track_interval or page_size)
         if self.track_interval <= 0 or self.track_interval % page_size:
@@ -122,7 +125,7 @@ class UnifiedRadixCache(RadixCache):
         tokens = (req.origin_input_ids + req.output_ids)[:kv_len]
         row = req.req_pool_idx
         super().cache_finished_req(req, is_insert, **kw)
-        if self.disable or not is_insert or kv_len == 0 or kv_len % self.page_size:
+        if self.disable or not self.commit_on_finish or not is_insert or kv_len == 0 or kv_len % self.page_size:
             return          # the state belongs to position kv_len; only a node ending there can own it
         dp = getattr(req, "dp_rank", 0) or 0
         values, node = self._match(tokens, RadixKey(tokens, req.extra_key, dp).namespace)

@@ -663,15 +663,20 @@ def test_hybrid_recurrent_prefix_sharing_reuses_state_checkpoints(tmp_path):
         finally:
             eng.shutdown()
 
-    shared = run()
     plain = run(disable_radix_cache=True)
-    assert shared[0] == "UnifiedRadixCache" and plain[0] == "ChunkCache"
+    # overlap scheduling (the default): checkpoints come from the prefill steps only (here the end of the prompt)
+    lapped = run()
+    assert lapped[0] == "UnifiedRadixCache" and plain[0] == "ChunkCache"
+    assert lapped[1:4] == plain[1:4] and lapped[4] == len(base) and lapped[5] == [len(base), 0]
+    # sequential schedule: a finished request also checkpoints its final state
+    shared = run(disable_overlap_schedule=True)
+    assert shared[0] == "UnifiedRadixCache"
     assert shared[1:4] == plain[1:4]
     assert shared[4] == len(base) + 5                   # the second request started from the checkpoint
     assert shared[5][0] == len(base) + 5 and shared[5][1] == 0      # a prefix without a checkpoint is recomputed
     assert plain[4] == 0 and shared[6] >= 3
     # two snapshot slots only: checkpoints are recycled least-recently-used first and nothing leaks
-    tight = run(recurrent_snapshot_slots=2)
+    tight = run(recurrent_snapshot_slots=2, disable_overlap_schedule=True)
     assert tight[1:4] == plain[1:4] and tight[6] <= 2
     # pages of 4 tokens: the state is checkpointed at the last page boundary inside each prefill (here token 40 of
     # the first prompt), so later requests restart from there and still produce the unshared tokens
