@@ -13,14 +13,51 @@ from __future__ import annotations
 
 from ..parallel import state as ps
 
+# The fused path keeps the residual stream token-sharded: a rank only updates the rows of its own
+# slice, the other rows of its `residual` tensor go stale.  That is sound only if every consumer of
+# the residual inside one model forward is a fused step, so the choice is made once per forward
+# (`set_fused_residual`), never per call: a layer that cannot take the fused path (a LoRA adapter), a deep-stack add, an
+# auxiliary hidden-state capture or a tracer switches the whole forward to the library all-reduce.
+_FUSED_RESIDUAL = True
+
+
+def set_fused_residual(on: bool) -> None:
+    global _FUSED_RESIDUAL
+    _FUSED_RESIDUAL = bool(on)
+
+
+def fused_residual_enabled() -> bool:
+    return _FUSED_RESIDUAL and ps.get_state().fused_comm is not None
+
+
+def row_linear_qualifies(lin) -> bool:
+    """A LoRA wrapper adds a term the fused step does not know; everything else (bias, quantised
+    weight) still yields a per-rank partial sum that the fused reduce accepts."""
+    return lin.lora is None
+
+
+def model_supports_fused_residual(model) -> bool:
+    """Every row-parallel projection of the model can feed the fused reduce -> residual -> norm step."""
+    from .linear import RowParallelLinear
+    return all(row_linear_qualifies(m) for m in model.modules()
+               if isinstance(m, RowParallelLinear) and m.tp_size > 1)
+
 
 def row_linear_add_norm(lin, x, residual, norm):
     """Returns `(norm(lin(x) + residual), lin(x) + residual)`."""
-    comm = ps.get_state().fused_comm
-    if comm is not None and lin.tp_size > 1 and lin.bias is None and lin.lora is None and lin.qweight is None \
-            and comm.supports_gemm_ar_norm(x, lin.weight):
-        return comm.gemm_allreduce_add_rmsnorm(x, lin.weight, residual, norm.weight,
-                                               norm.variance_epsilon, norm.gemma)
+    comm = ps.get_state().fused_comm if _FUSED_RESIDUAL else None
+    if comm is not None and lin.tp_size > 1 and comm.supports_gemm_ar_norm(x, lin.out_features):
+        if not row_linear_qualifies(lin):
+            raise RuntimeError("the fused residual dataflow is on but a row-parallel layer carries a LoRA adapter; "
+                               "`model_supports_fused_residual` must gate the forward")
+        if lin.bias is None and lin.qweight is None:
+            return comm.gemm_allreduce_add_rmsnorm(x, lin.weight, residual, norm.weight,
+                                                   norm.variance_epsilon, norm.gemma)
+        # bias (held by rank 0 only) or quantised weight: the local product is still a partial sum
+        from .linear import LinearBase
+        buf = comm.partial_buffer(x.shape[0])
+        buf.copy_(LinearBase.forward(lin, x))
+        return comm.allreduce_add_rmsnorm(x.shape[0], residual, norm.weight, norm.variance_epsilon, norm.gemma)
     y = lin(x)
     return norm(y, residual)
 
@@ -29,7 +66,7 @@ def partial_add_norm(make_partial, num_tokens: int, hidden: int, residual, norm,
     """Like `row_linear_add_norm` for a block whose per-rank partial sum is produced by arbitrary
     code (an MoE layer): `make_partial(out_or_None)` must return the `[T, H]` partial, written into
     `out` when one is given."""
-    comm = ps.get_state().fused_comm
+    comm = ps.get_state().fused_comm if _FUSED_RESIDUAL else None
     if comm is not None and tp_size > 1 and num_tokens <= comm.max_tokens and hidden == comm.hidden:
         buf = comm.partial_buffer(num_tokens)
         y = make_partial(buf)

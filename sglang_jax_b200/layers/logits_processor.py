@@ -62,6 +62,16 @@ class LogitsProcessor(nn.Module):
             logits = self.soft_cap * torch.tanh(logits.float() / self.soft_cap)
         return logits
 
+    @staticmethod
+    def _owned(t: torch.Tensor) -> torch.Tensor:
+        """Hidden states handed to a consumer outside this step (embeddings, draft models) must not alias the
+        fused-communication context's gather buffer, which the next fused call on any model overwrites."""
+        comm = ps.get_state().fused_comm
+        if comm is not None and t.is_cuda and \
+                t.untyped_storage().data_ptr() == comm.gathered.tensor.untyped_storage().data_ptr():
+            return t.clone()
+        return t
+
     def forward(self, hidden_states: torch.Tensor, lm_head, forward_batch) -> LogitsProcessorOutput:
         fb = forward_batch
         if fb.forward_mode.is_decode() or fb.last_token_indices is None:
@@ -75,9 +85,9 @@ class LogitsProcessor(nn.Module):
         if local_only:
             out.extras["vocab_shard"] = (lm_head.vocab_start, self.vocab_size)
         if fb.capture_hidden_mode == 1:
-            out.hidden_states = last
+            out.hidden_states = self._owned(last)
         elif fb.capture_hidden_mode == 2:
-            out.hidden_states = hidden_states
+            out.hidden_states = self._owned(hidden_states)
         if fb.return_logprob and fb.forward_mode.is_extend() and fb.extend_logprob_start_lens_cpu is not None:
             self._input_logprobs(hidden_states, lm_head, fb, out)
         return out

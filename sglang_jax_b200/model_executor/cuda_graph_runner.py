@@ -111,6 +111,7 @@ class CudaGraphRunner:
         comm = ps.get_state().fused_comm
         if comm is not None and not sampled:
             fb.extras["skip_logits_gather"] = True
+        r.select_residual_dataflow(fb)
         out = r.model(ids, fb)
         if sampled:
             # unseeded requests: fresh per-row seeds arrive with the step's inputs; every tensor rank holds the

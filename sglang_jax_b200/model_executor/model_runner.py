@@ -73,6 +73,8 @@ class ModelRunner:
             from ..lora.lora_manager import LoRAManager
             self.lora_manager = LoRAManager(self.model, server_args, self.dtype, self.device)
         self._init_fused_comm()
+        from ..layers.fused_block import model_supports_fused_residual
+        self.fused_residual_ok = model_supports_fused_residual(self.model)
         if self.device.type == "cuda" and not server_args.disable_cuda_graph and not is_draft_worker:
             from .cuda_graph_runner import CudaGraphRunner
             self.cuda_graph_runner = CudaGraphRunner(self)
@@ -197,6 +199,22 @@ class ModelRunner:
             st.fused_comm = None
 
     # ------------------------------------------------------------------ forward
+    def select_residual_dataflow(self, fb) -> bool:
+        """Choose, once per model forward, between the token-sharded residual stream of the fused NVLink kernels
+        and the replicated one of the library all-reduce.  Anything that reads whole rows of the residual between
+        layers (deep-stack features, auxiliary hidden-state capture for EAGLE-3 / DFlash, the precision tracer) or
+        a layer that cannot feed the fused reduce (LoRA on a row-parallel projection) selects the replicated one
+        for the whole forward."""
+        from ..layers.fused_block import set_fused_residual
+        from ..utils.precision_tracer import precision_tracer
+        inner = getattr(self.model, "model", None)
+        on = (self.fused_residual_ok and not precision_tracer.enabled
+              and (fb is None or fb.extras.get("deepstack") is None)
+              and not getattr(inner, "layers_to_capture", None)
+              and not getattr(self.model, "capture_aux_hidden_states", False))
+        set_fused_residual(on)
+        return on
+
     def resolve_future_token_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
         """Negative ids are placeholders `-slot` for tokens the previous step is still
         sampling; replace them from the device-side future map."""
@@ -227,6 +245,7 @@ class ModelRunner:
         if self.server_args is not None and not self.server_args.disable_overlap_schedule:
             fb.input_ids = self.resolve_future_token_ids(fb.input_ids)
         comm = ps.get_state().fused_comm
+        self.select_residual_dataflow(fb)
         si = batch.sampling_info
         if (comm is not None and not skip_sample and not batch.return_logprob and si is not None and si.is_all_greedy
                 and si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None

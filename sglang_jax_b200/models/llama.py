@@ -111,7 +111,8 @@ class DenseModel(nn.Module):
             precision_tracer.record(residual, "embed_tokens", forward_batch.forward_mode.name)
         for i, layer in enumerate(self.layers):
             if i in self.layers_to_capture:
-                aux.append(residual)
+                # the fused add-norm kernels update `residual` in place: keep a copy, not a reference
+                aux.append(residual.clone())
             nxt = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
             h, residual = layer(h, residual, forward_batch, nxt)
             deep = forward_batch.extras.get("deepstack")

@@ -103,8 +103,8 @@ class FusedComm:
         return cls(state, hidden, dtype, max_tokens)
 
     # ------------------------------------------------------------------ GEMM -> AR -> +res -> norm
-    def supports_gemm_ar_norm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
-        return (x.is_cuda and x.dtype == torch.bfloat16 and w.shape[0] == self.hidden
+    def supports_gemm_ar_norm(self, x: torch.Tensor, out_features: int) -> bool:
+        return (x.is_cuda and x.dtype == torch.bfloat16 and out_features == self.hidden
                 and x.shape[0] <= self.max_tokens and x.dim() == 2)
 
     def partial_buffer(self, T: int) -> torch.Tensor:
