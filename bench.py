@@ -349,7 +349,8 @@ def main():
     clocks = ClockSampler(local_rank)
 
     def live_count(s) -> int:
-        live = len(s.running_batch.reqs) + len(s.waiting_queue) + (1 if s.chunked_req is not None else 0)
+        live = sum(1 for r in s.running_batch.reqs if not r.finished()) + len(s.waiting_queue) + \
+            (1 if s.chunked_req is not None else 0)
         if s.last_batch is not None and s.last_batch.forward_mode is not None and s.last_batch.forward_mode.is_extend():
             live += sum(1 for r in s.last_batch.reqs if r not in s.running_batch.reqs and r is not s.chunked_req
                         and not r.finished())
@@ -380,7 +381,7 @@ def main():
         if state["phase"] == "fill":
             state["fill_steps"] += 1
             # steady state: every row decodes, and the first replacement has been prefilled and merged
-            if state["replaced"] >= 1 and batch.forward_mode.is_decode() and len(batch.reqs) == C \
+            if state["replaced"] >= 1 and batch.forward_mode.is_decode() and len(batch.reqs) >= C - 1 \
                     and not s.waiting_queue and s.chunked_req is None:
                 state["phase"] = "warmup"
             if state["phase"] == "fill":

@@ -32,16 +32,6 @@ struct Peers {
   void* p[kMaxWorld];
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-  return v;
-}
-
 // Block-level barrier across ranks: block b of every rank meets block b of all peers.
 // flags layout on every rank: [kMaxBlocks][kMaxWorld] u32; `epochs` is rank-local [kMaxBlocks].
 // Returns false if a peer did not show up within the limit.

@@ -246,6 +246,35 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Cross-GPU flag accesses (flags live in symmetric memory mapped on every peer).
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// Spin until the epoch-valued flag reaches `epoch` (flags only grow), for at most kWaitLimitNs.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t epoch) {
+  if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) < 0) {
+    if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > kWaitLimitNs) return false;
+  }
+  return true;
+}
+
+// 16-byte store through an NVSwitch multicast address: one instruction, every rank's copy is written.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // named barrier among a subset of the CTA's warps
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -78,7 +78,53 @@ struct Params {
   int l2_hints;                       // decode mode: stream weights evict-first, keep the token tile evict-last
   const float* scale_x;               // fp8: per-token activation scale [M]
   const float* scale_w;               // fp8: per-output-channel weight scale [N]
+  // ---- FUSE == 1: the same kernel also reduces the received slices, adds the residual, applies RMSNorm and
+  // all-gathers the normalised rows (see "fused tail" below).  Row ownership: rank o owns token rows
+  // [o * rs_rows_per, (o + 1) * rs_rows_per), cut into chunks of kChunkRows rows.
+  __nv_bfloat16* ag_peer[8];          // every rank's [M, N] buffer of normalised activations
+  __nv_bfloat16* ag_mc;               // NVSwitch multicast address of that buffer (multimem.st) or null
+  uint32_t* flag_peer[8];             // every rank's flag block (kFlagWords u32, symmetric memory)
+  __nv_bfloat16* residual;            // [M, N] local residual stream (rows of this rank's slice are updated) or null
+  const __nv_bfloat16* norm_w;        // [N]
+  uint32_t* seq;                      // device-resident call counter of the fused context (local memory)
+  int* tail_ctrs;                     // local counters (kTailCtrInts ints), zero when idle
+  float eps;
+  int gemma, defer, per_tile, nchunks;
+  // ---- FUSE == 2: the token operand is the all-gather buffer written by a FUSE == 1 launch that did not
+  // wait for its peers: the TMA producer waits for the arrival flag of a chunk before its first load of it.
+  const uint32_t* ag_flags;           // this rank's flag block
+  const uint32_t* ag_seq;
+  int ag_world, ag_rows_per, ag_nchunks;
 };
+
+// Flag block layout (u32, epoch valued, symmetric memory):
+//   [kRsFlag + chunk * 8 + src]      on the owner: src's partial rows of that chunk have all been pushed
+//   [kAgFlag + owner * kMaxChunks + chunk]  on every rank: the owner's normalised rows of that chunk have landed
+constexpr int kChunkRows = 128;
+constexpr int kMaxChunks = 160;
+constexpr int kRsFlag = 0;
+constexpr int kAgFlag = kMaxChunks * 8;
+constexpr int kFlagWords = kAgFlag + 8 * kMaxChunks;
+// local counters: [0] CTAs done with their GEMM work, [1] CTAs that left the tail, then per chunk: next row to
+// hand out, rows finished, and (per 128-row token tile) weight tiles finished
+constexpr int kCtrDone = 0, kCtrExit = 1, kCtrNextRow = 8, kCtrRowsDone = kCtrNextRow + kMaxChunks,
+              kCtrTile = kCtrRowsDone + kMaxChunks, kTailCtrInts = kCtrTile + kMaxChunks;
+
+// Ownership layout shared by the producer, the consumer and the host: with at least one full 128-row tile per
+// rank the slices are multiples of 128 rows (a token tile never straddles two owners, so arrival can be
+// signalled per tile); smaller batches have one chunk per owner.
+__host__ __device__ inline void fused_layout(int M, int world, int* rows_per, int* nchunks, int* per_tile) {
+  if (M >= kChunkRows * world && M > 256) {
+    const int r = (M + world - 1) / world;
+    *rows_per = (r + kChunkRows - 1) / kChunkRows * kChunkRows;
+    *nchunks = *rows_per / kChunkRows;
+    *per_tile = 1;
+  } else {
+    *rows_per = (M + world - 1) / world;
+    *nchunks = (*rows_per + kChunkRows - 1) / kChunkRows;      // 1, or 2 on a single rank with more than 128 rows
+    *per_tile = 0;
+  }
+}
 
 __device__ __forceinline__ __nv_bfloat16* out_ptr(const Params& p, int tok, int gn) {
   if (p.rs_world == 0) return p.out + static_cast<size_t>(tok) * p.N + gn;
@@ -220,7 +266,7 @@ struct SegIter {
 // FP8: both operands are e4m3 bytes (128 per swizzle row instead of 64 bf16, so the byte layout of a
 // stage is unchanged), `tcgen05.mma.kind::f8f6f4` accumulates in fp32 and the epilogue multiplies by
 // `scale_x[token] * scale_w[channel]` (per-token activation scale, per-channel weight scale).
-template <int BN, int MODE, bool FP8 = false>
+template <int BN, int MODE, bool FP8 = false, int FUSE = 0>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const Params p) {
@@ -273,6 +319,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // everything above is CTA-local; operands, counters and the tile lists may come from the previous kernel
   pdl_wait();
   if (threadIdx.x == 0) stamp(1);
+  // fused tail: every launch of the fused context is one epoch; the last CTA to leave publishes it
+  [[maybe_unused]] uint32_t epoch = 0;
+  if constexpr (FUSE == 1) epoch = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -284,7 +333,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // decode mode: operand A is the weight matrix, read exactly once by the whole grid; operand B is
       // the token tile every CTA re-reads for each k-block
       const uint64_t pol_a = l2_policy_evict_first(), pol_b = l2_policy_evict_last();
+      [[maybe_unused]] uint32_t ag_epoch = 0;
+      [[maybe_unused]] unsigned long long ag_seen[(8 * kMaxChunks + 63) / 64] = {};
+      if constexpr (FUSE == 2) ag_epoch = *reinterpret_cast<const volatile uint32_t*>(p.ag_seq);
+      // rows [r_lo, r_hi) of the gathered buffer are about to be read: wait for their chunks' arrival flags
+      auto ag_wait_rows = [&](int r_lo, int r_hi) -> bool {
+        if constexpr (FUSE == 2) {
+          r_hi = min(r_hi, p.M);
+          for (int r = r_lo; r < r_hi;) {
+            const int o = r / p.ag_rows_per;
+            const int j = (r - o * p.ag_rows_per) / kChunkRows;
+            const int id = o * kMaxChunks + j;
+            if (!((ag_seen[id >> 6] >> (id & 63)) & 1ull)) {
+              if (!wait_flag_ge(p.ag_flags + kAgFlag + id, ag_epoch)) {
+                report(p.status, kTimeoutPeerFlag, o, 20 + j);
+                return false;
+              }
+              ag_seen[id >> 6] |= 1ull << (id & 63);
+            }
+            r = min(o * p.ag_rows_per + (j + 1) * kChunkRows, (o + 1) * p.ag_rows_per);   // first row of the next chunk
+          }
+        }
+        return true;
+      };
       while (!*abort_flag && iter.next(p, sg)) {
+        if constexpr (FUSE == 2) {
+          const bool got = MODE == 0 ? ag_wait_rows(sg.a_row, sg.a_row + BM) : ag_wait_rows(0, p.M);
+          if (!got) {
+            *abort_flag = 1;
+            break;
+          }
+        }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
             report(p.status, kTimeoutEmptyBarrier, sg.tile_id, kb);
@@ -487,6 +566,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
 
+      if constexpr (FUSE == 1 && MODE == 0) {
+        if (p.per_tile && direct) {
+          // this rank's partial rows of token tile `ta`: once all weight tiles of the token tile have been
+          // pushed, tell the owner of those rows (release at system scope orders the peer stores before it)
+          __threadfence_system();
+          named_bar_sync(1, kEpiThreads);
+          if (epi_tid == 0) {
+            const int old = atomicAdd(&p.tail_ctrs[kCtrTile + sg.ta], 1);
+            if (old == p.tiles_b - 1) {
+              __threadfence_system();
+              const int owner = sg.m0 / p.rs_rows_per;
+              const int j = (sg.m0 - owner * p.rs_rows_per) / kChunkRows;
+              st_release_sys(p.flag_peer[owner] + kRsFlag + j * 8 + p.rs_rank, epoch);
+            }
+          }
+        }
+      }
+
       if (!direct) {
         __threadfence();
         named_bar_sync(1, kEpiThreads);
@@ -613,6 +710,181 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   }
 
+  // ------------------------------------------------------------------ fused tail
+  // Reduce-scatter arrival -> sum of the `world` partial slices + residual -> RMSNorm -> all-gather by peer
+  // stores, done by the CTAs of this same launch as they run out of GEMM work.  Cross-GPU ordering is by
+  // epoch-valued flags (bounded waits); nothing here waits for a CTA of this GPU that could itself be waiting.
+  if constexpr (FUSE == 1) {
+    __shared__ int s_row;
+    __shared__ int s_ok;
+    __shared__ float s_red[8];
+    const int tid = threadIdx.x;
+    __threadfence_system();          // this thread's peer stores (epilogue warps) are out
+    __syncthreads();
+    if (tid == 0) {
+      s_ok = 1;
+      if (!p.per_tile) {
+        // small batches: the CTA that finishes last tells every owner that all of this rank's rows are out
+        const int old = atomicAdd(&p.tail_ctrs[kCtrDone], 1);
+        if (old == static_cast<int>(gridDim.x) - 1) {
+          __threadfence_system();
+          for (int o = 0; o < p.rs_world; ++o)
+            for (int j = 0; j < p.nchunks; ++j) st_release_sys(p.flag_peer[o] + kRsFlag + j * 8 + p.rs_rank, epoch);
+        }
+      }
+    }
+    __syncthreads();
+    const int nvec = p.N >> 3;
+    constexpr int kMaxVpt = 6;       // N <= 6 * 192 * 8 = 9216
+    const uint4* wv = reinterpret_cast<const uint4*>(p.norm_w);
+    const uint4* ybase = reinterpret_cast<const uint4*>(p.rs_peer[p.rs_rank]);
+    const uint32_t* my_flags = p.flag_peer[p.rs_rank];
+    for (int j = 0; j < p.nchunks && !*abort_flag; ++j) {
+      const int c0 = p.rs_rank * p.rs_rows_per + j * kChunkRows;
+      const int c1 = min(min(c0 + kChunkRows, (p.rs_rank + 1) * p.rs_rows_per), p.M);
+      const int nrows = c1 - c0;
+      if (nrows <= 0) break;
+      bool waited = false;
+      for (;;) {
+        if (tid == 0) s_row = atomicAdd(&p.tail_ctrs[kCtrNextRow + j], 1);
+        __syncthreads();
+        const int lr = s_row;
+        __syncthreads();
+        if (lr >= nrows) break;
+        if (!waited) {
+          if (tid < p.rs_world) {
+            if (!wait_flag_ge(my_flags + kRsFlag + j * 8 + tid, epoch)) {
+              report(p.status, kTimeoutPeerFlag, tid, 10);
+              s_ok = 0;
+            }
+          }
+          __syncthreads();
+          waited = true;
+          if (!s_ok) {
+            *abort_flag = 1;
+            break;
+          }
+        }
+        const int row = c0 + lr;
+        const int local = row - p.rs_rank * p.rs_rows_per;
+        const size_t gbase = static_cast<size_t>(row) * nvec;
+        float vals[kMaxVpt][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxVpt; ++i) {
+          const int idx = tid + i * kNumThreads;
+          if (idx < nvec) {
+            uint4 part[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              if (s < p.rs_world)
+                part[s] = __ldcg(ybase + (static_cast<size_t>(s) * p.rs_rows_per + local) * nvec + idx);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) vals[i][e] = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+              if (s < p.rs_world) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[s]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 t = __bfloat1622float2(h[e]);
+                  vals[i][2 * e] += t.x;
+                  vals[i][2 * e + 1] += t.y;
+                }
+              }
+            }
+            if (p.residual != nullptr) {
+              uint4* rv = reinterpret_cast<uint4*>(p.residual) + gbase + idx;
+              const uint4 r4 = *rv;
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r4);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 t = __bfloat1622float2(h[e]);
+                vals[i][2 * e] += t.x;
+                vals[i][2 * e + 1] += t.y;
+              }
+              // the residual stream is bf16: normalise what the next layer will read back
+              uint4 packed = make_uint4(pack_bf16(vals[i][0], vals[i][1]), pack_bf16(vals[i][2], vals[i][3]),
+                                        pack_bf16(vals[i][4], vals[i][5]), pack_bf16(vals[i][6], vals[i][7]));
+              *rv = packed;
+              const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 t = __bfloat1622float2(hp[e]);
+                vals[i][2 * e] = t.x;
+                vals[i][2 * e + 1] = t.y;
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += vals[i][e] * vals[i][e];
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int wdx = 0; wdx < kNumThreads / 32; ++wdx) tot += s_red[wdx];
+        const float inv = rsqrtf(tot / p.N + p.eps);
+#pragma unroll
+        for (int i = 0; i < kMaxVpt; ++i) {
+          const int idx = tid + i * kNumThreads;
+          if (idx < nvec) {
+            const uint4 w4 = wv[idx];
+            const __nv_bfloat162* hw = reinterpret_cast<const __nv_bfloat162*>(&w4);
+            float o8[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 t = __bfloat1622float2(hw[e]);
+              o8[2 * e] = vals[i][2 * e] * inv * (p.gemma ? t.x + 1.f : t.x);
+              o8[2 * e + 1] = vals[i][2 * e + 1] * inv * (p.gemma ? t.y + 1.f : t.y);
+            }
+            const uint4 out4 = make_uint4(pack_bf16(o8[0], o8[1]), pack_bf16(o8[2], o8[3]), pack_bf16(o8[4], o8[5]),
+                                          pack_bf16(o8[6], o8[7]));
+            if (p.ag_mc != nullptr) {
+              multimem_st_v4(reinterpret_cast<uint4*>(p.ag_mc) + gbase + idx, out4);
+            } else {
+#pragma unroll
+              for (int d = 0; d < 8; ++d)
+                if (d < p.rs_world) reinterpret_cast<uint4*>(p.ag_peer[d])[gbase + idx] = out4;
+            }
+          }
+        }
+        // the row has been pushed everywhere: count it, and let the last row of the chunk tell every rank
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+          const int old = atomicAdd(&p.tail_ctrs[kCtrRowsDone + j], 1);
+          if (old == nrows - 1) {
+            __threadfence_system();
+            for (int d = 0; d < p.rs_world; ++d)
+              st_release_sys(p.flag_peer[d] + kAgFlag + p.rs_rank * kMaxChunks + j, epoch);
+          }
+        }
+      }
+    }
+    // without a flag-aware consumer the launch only ends once every rank's rows have landed here
+    if (!p.defer && blockIdx.x == 0 && !*abort_flag) {
+      for (int id = tid; id < p.rs_world * p.nchunks; id += kNumThreads) {
+        const int o = id / p.nchunks, j = id - o * p.nchunks;
+        if (o * p.rs_rows_per + j * kChunkRows < p.M) {
+          if (!wait_flag_ge(my_flags + kAgFlag + o * kMaxChunks + j, epoch)) report(p.status, kTimeoutPeerFlag, o, 30);
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int old = atomicAdd(&p.tail_ctrs[kCtrExit], 1);
+      if (old == static_cast<int>(gridDim.x) - 1) {
+        // last CTA out: leave the counters clean and publish the epoch for the next launch / the consumer
+        for (int i = 0; i < kTailCtrInts; ++i) p.tail_ctrs[i] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(p.seq) = epoch;
+      }
+    }
+  }
+
   // ------------------------------------------------------------------ teardown
   if (threadIdx.x == 64) stamp(5);
   tc_fence_before_sync();
@@ -631,10 +903,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-template <int BN, int MODE, bool FP8 = false>
+template <int BN, int MODE, bool FP8 = false, int FUSE = 0>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN>;
-  auto* kern = gemm_bf16_kernel<BN, MODE, FP8>;
+  auto* kern = gemm_bf16_kernel<BN, MODE, FP8, FUSE>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -672,10 +944,23 @@ int sglb_gemm_max_counters(int N) { return (N + 127) / 128 + 8; }
 // pointers 16-byte aligned.  `workspace`/`counters` are only touched when M <= 256 and the
 // launcher decides to split K; `counters` must be zero on entry (the kernel restores zeros).
 // force_mode: -1 auto, 0 tokens-on-M, 1 weights-on-M.  force_splits: 0 auto.
+struct SglbFusedHost {
+  int kind;                    // 1: GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather; 2: all-gather -> GEMM
+  void* const* gathered;       // [world] every rank's buffer of normalised activations
+  void* gathered_mc;           // multicast address of that buffer or null
+  void* const* flags;          // [world] every rank's flag block
+  void* seq;                   // device u32: call counter of the fused context
+  void* ctrs;                  // device ints: local tail counters
+  void* residual;
+  const void* norm_w;
+  float eps;
+  int gemma, defer, world, rank;
+};
 int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
                         void* workspace, size_t workspace_bytes, int* counters, int force_mode, int force_splits,
                         void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream,
-                        const float* scale_x = nullptr, const float* scale_w = nullptr);
+                        const float* scale_x = nullptr, const float* scale_w = nullptr,
+                        const SglbFusedHost* fused = nullptr);
 
 // out[M,N] (bf16) = (x_q[M,K] . w_q[N,K]^T) * scale_x[M] * scale_w[N] + bias with e4m3 operands
 // (per-token activation scales, per-output-channel weight scales; K a multiple of 16).
@@ -720,7 +1005,7 @@ void sglb_gemm_set_debug_stamps(void* dev_ptr) { g_debug_stamps = static_cast<un
 int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
                         void* workspace, size_t workspace_bytes, int* counters, int force_mode, int force_splits,
                         void* const* rs_peers, int rs_world, int rs_rank, cudaStream_t stream,
-                        const float* scale_x, const float* scale_w) {
+                        const float* scale_x, const float* scale_w, const SglbFusedHost* fused) {
   using namespace sglb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (N % 8)) return -kBadArgument;
@@ -760,6 +1045,36 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
     p.rs_rows_per = (M + rs_world - 1) / rs_world;
     for (int r = 0; r < rs_world; ++r) p.rs_peer[r] = static_cast<__nv_bfloat16*>(rs_peers[r]);
   }
+  const int fuse = fused != nullptr ? fused->kind : 0;
+  if (fuse != 0) {
+    if (fp8 || fused->world < 1 || fused->world > 8 || M > kMaxChunks * kChunkRows) return -kBadArgument;
+    int rows_per = 0, nchunks = 0, per_tile = 0;
+    fused_layout(M, fused->world, &rows_per, &nchunks, &per_tile);
+    if (fuse == 1) {
+      if (rs_world != fused->world || N > 6 * kNumThreads * 8) return -kBadArgument;
+      p.rs_rows_per = rows_per;
+      p.nchunks = nchunks;
+      p.per_tile = per_tile;
+      for (int r = 0; r < fused->world; ++r) {
+        p.ag_peer[r] = static_cast<__nv_bfloat16*>(fused->gathered[r]);
+        p.flag_peer[r] = static_cast<uint32_t*>(fused->flags[r]);
+      }
+      p.ag_mc = static_cast<__nv_bfloat16*>(fused->gathered_mc);
+      p.residual = static_cast<__nv_bfloat16*>(fused->residual);
+      p.norm_w = static_cast<const __nv_bfloat16*>(fused->norm_w);
+      p.seq = static_cast<uint32_t*>(fused->seq);
+      p.tail_ctrs = static_cast<int*>(fused->ctrs);
+      p.eps = fused->eps;
+      p.gemma = fused->gemma;
+      p.defer = fused->defer;
+    } else {
+      p.ag_flags = static_cast<const uint32_t*>(fused->flags[fused->rank]);
+      p.ag_seq = static_cast<const uint32_t*>(fused->seq);
+      p.ag_world = fused->world;
+      p.ag_rows_per = rows_per;
+      p.ag_nchunks = nchunks;
+    }
+  }
 
   CUtensorMap ta, tb;
   cudaError_t err;
@@ -787,6 +1102,8 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
       }
     }
     if (fp8) err = bn == 256 ? launch<256, 0, true>(ta, tb, p, grid, stream) : launch<128, 0, true>(ta, tb, p, grid, stream);
+    else if (fuse == 1) err = bn == 256 ? launch<256, 0, false, 1>(ta, tb, p, grid, stream) : launch<128, 0, false, 1>(ta, tb, p, grid, stream);
+    else if (fuse == 2) err = bn == 256 ? launch<256, 0, false, 2>(ta, tb, p, grid, stream) : launch<128, 0, false, 2>(ta, tb, p, grid, stream);
     else err = bn == 256 ? launch<256, 0>(ta, tb, p, grid, stream) : launch<128, 0>(ta, tb, p, grid, stream);
   } else {
     const int bn = pick_bn_tokens(M);
@@ -831,6 +1148,22 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
         case 128: err = launch<128, 1, true>(ta, tb, p, grid, stream); break;
         default: err = launch<256, 1, true>(ta, tb, p, grid, stream); break;
       }
+    } else if (fuse == 1) {
+      switch (bn) {
+        case 16: err = launch<16, 1, false, 1>(ta, tb, p, grid, stream); break;
+        case 32: err = launch<32, 1, false, 1>(ta, tb, p, grid, stream); break;
+        case 64: err = launch<64, 1, false, 1>(ta, tb, p, grid, stream); break;
+        case 128: err = launch<128, 1, false, 1>(ta, tb, p, grid, stream); break;
+        default: err = launch<256, 1, false, 1>(ta, tb, p, grid, stream); break;
+      }
+    } else if (fuse == 2) {
+      switch (bn) {
+        case 16: err = launch<16, 1, false, 2>(ta, tb, p, grid, stream); break;
+        case 32: err = launch<32, 1, false, 2>(ta, tb, p, grid, stream); break;
+        case 64: err = launch<64, 1, false, 2>(ta, tb, p, grid, stream); break;
+        case 128: err = launch<128, 1, false, 2>(ta, tb, p, grid, stream); break;
+        default: err = launch<256, 1, false, 2>(ta, tb, p, grid, stream); break;
+      }
     } else {
       switch (bn) {
         case 16: err = launch<16, 1>(ta, tb, p, grid, stream); break;
@@ -843,6 +1176,75 @@ int sglb_gemm_bf16_impl(const void* x, const void* w, const void* bias, void* ou
   }
   return err == cudaSuccess ? 0 : static_cast<int>(err);
 }
+
+// Sizes of the fused context's flag block (u32 words, symmetric memory) and local counter block (ints).
+int sglb_fused_flag_words() { return sglb::kFlagWords; }
+int sglb_fused_ctr_ints() { return sglb::kTailCtrInts; }
+int sglb_fused_max_tokens() { return sglb::kMaxChunks * sglb::kChunkRows; }
+// rows_per / nchunks / per_tile of the ownership layout for M tokens over `world` ranks
+void sglb_fused_layout(int M, int world, int* out3) { sglb::fused_layout(M, world, out3, out3 + 1, out3 + 2); }
+
+// One launch for the row-parallel half of a decoder layer under tensor parallelism:
+//   partial = x[M, K] . w[N, K]^T  (this rank's K shard)
+//   -> reduce-scatter over token rows (the epilogue stores each row into its owner's receive buffer
+//      `ypart_ptrs[owner]`, laid out [src rank][rows_per][N], over NVLink peer mappings)
+//   -> owner: sum of the `world` slices + residual (updated in place for the owned rows) -> RMSNorm
+//   -> all-gather: normalised rows stored into every rank's `gathered_ptrs[r]` ([M, N]; `gathered_mc` non-null
+//      selects one multimem.st through the NVSwitch multicast mapping instead of `world` peer stores).
+// `defer` = 1 returns without waiting for the peers' rows: the consumer must be sglb_gemm_bf16_ag (which waits
+// per chunk) on the same stream.  `seq` (one u32) and `ctrs` (sglb_fused_ctr_ints ints) are device memory owned
+// by the fused context, zero at creation; `flag_ptrs` are the ranks' flag blocks (sglb_fused_flag_words u32,
+// zero at creation, symmetric memory).  Every rank must issue the same sequence of fused launches.
+int sglb_gemm_rs_norm_ag(const void* x, const void* w, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                         int* counters, void* const* ypart_ptrs, void* const* gathered_ptrs, void* gathered_mc,
+                         void* const* flag_ptrs, void* seq, void* ctrs, void* residual, const void* norm_w, float eps,
+                         int gemma, int defer, int world, int rank, cudaStream_t stream) {
+  if (world < 1 || world > 8 || ypart_ptrs == nullptr || gathered_ptrs == nullptr || flag_ptrs == nullptr ||
+      seq == nullptr || ctrs == nullptr || norm_w == nullptr)
+    return -sglb::kBadArgument;
+  SglbFusedHost f{1, gathered_ptrs, gathered_mc, flag_ptrs, seq, ctrs, residual, norm_w, eps, gemma, defer, world, rank};
+  return sglb_gemm_bf16_impl(x, w, nullptr, nullptr, M, N, K, workspace, workspace_bytes, counters, -1, 0, ypart_ptrs,
+                             world, rank, stream, nullptr, nullptr, &f);
+}
+
+// Column-parallel GEMM whose token operand `x` is this rank's all-gather buffer of a deferred
+// sglb_gemm_rs_norm_ag launch with the same M and world: the TMA producer waits for each chunk's arrival flag
+// before its first load of it (plain loads of this GPU's own memory; the peers wrote it with stores).
+int sglb_gemm_bf16_ag(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, void* workspace,
+                      size_t workspace_bytes, int* counters, void* const* flag_ptrs, void* seq, int world, int rank,
+                      cudaStream_t stream) {
+  if (world < 1 || world > 8 || flag_ptrs == nullptr || seq == nullptr) return -sglb::kBadArgument;
+  SglbFusedHost f{2, nullptr, nullptr, flag_ptrs, seq, nullptr, nullptr, nullptr, 0.f, 0, 0, world, rank};
+  return sglb_gemm_bf16_impl(x, w, bias, out, M, N, K, workspace, workspace_bytes, counters, -1, 0, nullptr, 0, 0, stream,
+                             nullptr, nullptr, &f);
+}
+}
+
+namespace sglb {
+namespace {
+__global__ void fused_wait_gather_kernel(const uint32_t* flags, const uint32_t* seq, int M, int world, int rows_per,
+                                         int nchunks, Status* st) {
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(seq);
+  for (int id = threadIdx.x; id < world * nchunks; id += blockDim.x) {
+    const int o = id / nchunks, j = id - o * nchunks;
+    if (o * rows_per + j * kChunkRows < M && !wait_flag_ge(flags + kAgFlag + o * kMaxChunks + j, epoch))
+      report(st, kTimeoutPeerFlag, o, 40);
+  }
+}
+}  // namespace
+}  // namespace sglb
+
+// Blocks the stream until every rank's rows of the last deferred sglb_gemm_rs_norm_ag launch (M tokens) have
+// landed in this rank's all-gather buffer: for consumers that are not sglb_gemm_bf16_ag.
+extern "C" int sglb_fused_wait_gather(const void* flags_local, const void* seq, int M, int world, cudaStream_t stream) {
+  using namespace sglb;
+  if (world < 1 || world > 8 || M <= 0 || M > kMaxChunks * kChunkRows) return -kBadArgument;
+  int rows_per = 0, nchunks = 0, per_tile = 0;
+  fused_layout(M, world, &rows_per, &nchunks, &per_tile);
+  fused_wait_gather_kernel<<<1, 128, 0, stream>>>(static_cast<const uint32_t*>(flags_local),
+                                                  static_cast<const uint32_t*>(seq), M, world, rows_per, nchunks,
+                                                  device_status());
+  return static_cast<int>(cudaGetLastError());
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -9,7 +9,15 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <thread>
 #include <cstdint>
 #include <cstring>
 #include <deque>
@@ -402,6 +410,168 @@ class RadixTree {
   std::map<int, int64_t> evictable_, protected_;
 };
 
+
+// ------------------------------------------------------------------------------------ step ring
+// Single-producer / multi-consumer message ring in POSIX shared memory: tensor rank 0 publishes each
+// step's batch (a fixed-layout block of integers, or a pickled control message) and the follower
+// ranks of the node read it, without a socket round-trip or a host collective per step.
+//
+//   header   : magic | slots | slot_bytes | consumers | write_seq (atomic) | closed | read_seq[consumers]
+//   slot i   : length (u32) | kind (u32) | payload
+// The producer may run at most `slots` messages ahead of the slowest consumer; a push that finds the ring
+// full, or a pop that finds it empty, waits (GIL released) up to its timeout and then reports failure, which
+// is how a dead peer shows up on the host.  Counterpart of the reference's request mirror over ZMQ PUB/SUB
+// (python/sgl_jax/srt/managers/scheduler.py:625-676).
+class StepRing {
+ public:
+  static constexpr uint64_t kMagic = 0x53474c4252494e47ull;   // "SGLBRING"
+  static constexpr int kMaxConsumers = 64;
+  struct alignas(64) Header {
+    uint64_t magic;
+    uint32_t slots, slot_bytes, consumers, pad;
+    alignas(64) std::atomic<uint64_t> write_seq;
+    alignas(64) std::atomic<uint32_t> closed;
+    struct alignas(64) Cursor { std::atomic<uint64_t> seq; } read_seq[kMaxConsumers];
+  };
+
+  // consumer < 0: create (producer side); otherwise attach as that consumer
+  StepRing(const std::string& name, int slots, int slot_bytes, int consumers, int consumer)
+      : name_(name), consumer_(consumer), owner_(consumer < 0) {
+    if (consumers < 1 || consumers > kMaxConsumers) throw std::invalid_argument("StepRing: bad consumer count");
+    const size_t slot_stride = (static_cast<size_t>(slot_bytes) + 8 + 63) / 64 * 64;
+    bytes_ = sizeof(Header) + slot_stride * slots;
+    int fd = -1;
+    if (owner_) {
+      ::shm_unlink(name.c_str());
+      fd = ::shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+      if (fd < 0 || ::ftruncate(fd, bytes_) != 0) throw std::runtime_error("StepRing: cannot create " + name);
+    } else {
+      fd = ::shm_open(name.c_str(), O_RDWR, 0600);
+      if (fd < 0) throw std::runtime_error("StepRing: cannot open " + name);
+    }
+    void* p = ::mmap(nullptr, bytes_, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    ::close(fd);
+    if (p == MAP_FAILED) throw std::runtime_error("StepRing: mmap failed");
+    h_ = static_cast<Header*>(p);
+    data_ = static_cast<uint8_t*>(p) + sizeof(Header);
+    stride_ = slot_stride;
+    if (owner_) {
+      std::memset(p, 0, sizeof(Header));
+      h_->slots = slots;
+      h_->slot_bytes = slot_bytes;
+      h_->consumers = consumers;
+      h_->write_seq.store(0, std::memory_order_relaxed);
+      std::atomic_thread_fence(std::memory_order_release);
+      h_->magic = kMagic;
+    } else if (h_->magic != kMagic || (int)h_->slots != slots || (int)h_->slot_bytes != slot_bytes ||
+               consumer >= (int)h_->consumers) {
+      throw std::runtime_error("StepRing: header mismatch for " + name);
+    }
+  }
+  ~StepRing() {
+    if (h_ != nullptr) ::munmap(h_, bytes_);
+    if (owner_) ::shm_unlink(name_.c_str());
+  }
+
+  int slot_bytes() const { return h_->slot_bytes; }
+  uint64_t written() const { return h_->write_seq.load(std::memory_order_acquire); }
+  uint64_t consumed(int c) const { return h_->read_seq[c].seq.load(std::memory_order_acquire); }
+  void close_ring() { h_->closed.store(1, std::memory_order_release); }
+  bool closed() const { return h_->closed.load(std::memory_order_acquire) != 0; }
+
+  // index of the slowest consumer and how many messages it is behind
+  std::pair<int, uint64_t> slowest() const {
+    const uint64_t w = written();
+    int who = 0;
+    uint64_t lag = 0;
+    for (uint32_t c = 0; c < h_->consumers; ++c) {
+      const uint64_t l = w - consumed(c);
+      if (l >= lag) { lag = l; who = c; }
+    }
+    return {who, lag};
+  }
+
+  // producer: false = ring still full after `timeout_s` (a consumer stopped reading)
+  bool push(py::bytes payload, uint32_t kind, double timeout_s) {
+    char* buf;
+    Py_ssize_t len;
+    if (PyBytes_AsStringAndSize(payload.ptr(), &buf, &len) != 0) throw py::error_already_set();
+    return push_raw(reinterpret_cast<const uint8_t*>(buf), static_cast<size_t>(len), kind, timeout_s);
+  }
+  bool push_ints(i32arr arr, uint32_t kind, double timeout_s) {
+    return push_raw(reinterpret_cast<const uint8_t*>(arr.data()), static_cast<size_t>(arr.size()) * 4, kind, timeout_s);
+  }
+  bool push_raw(const uint8_t* src, size_t len, uint32_t kind, double timeout_s) {
+    if (!owner_) throw std::runtime_error("StepRing: only the creator may push");
+    if (len > h_->slot_bytes) throw std::length_error("StepRing: message larger than a slot");
+    const uint64_t w = h_->write_seq.load(std::memory_order_relaxed);
+    {
+      py::gil_scoped_release nogil;
+      const auto t0 = std::chrono::steady_clock::now();
+      unsigned spins = 0;
+      for (;;) {
+        uint64_t min_read = w;
+        for (uint32_t c = 0; c < h_->consumers; ++c) min_read = std::min(min_read, consumed(c));
+        if (w - min_read < h_->slots) break;
+        if ((++spins & 0x3f) == 0) {
+          if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > timeout_s) return false;
+          std::this_thread::sleep_for(std::chrono::microseconds(50));
+        }
+      }
+      uint8_t* slot = data_ + (w % h_->slots) * stride_;
+      reinterpret_cast<uint32_t*>(slot)[0] = static_cast<uint32_t>(len);
+      reinterpret_cast<uint32_t*>(slot)[1] = kind;
+      std::memcpy(slot + 8, src, len);
+    }
+    h_->write_seq.store(w + 1, std::memory_order_release);
+    return true;
+  }
+
+  // consumer: (kind, payload) or None after `timeout_s` without a message / once the ring is closed and drained
+  py::object pop(double timeout_s, bool as_ints) {
+    if (consumer_ < 0) throw std::runtime_error("StepRing: the creator does not pop");
+    auto& cur = h_->read_seq[consumer_].seq;
+    const uint64_t r = cur.load(std::memory_order_relaxed);
+    bool got = false;
+    {
+      py::gil_scoped_release nogil;
+      const auto t0 = std::chrono::steady_clock::now();
+      unsigned spins = 0;
+      for (;;) {
+        if (h_->write_seq.load(std::memory_order_acquire) > r) { got = true; break; }
+        if (closed()) break;
+        if ((++spins & 0xff) == 0) {
+          const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+          if (dt > timeout_s) break;
+          if (dt > 0.002) std::this_thread::sleep_for(std::chrono::microseconds(dt > 0.1 ? 200 : 20));
+        }
+      }
+    }
+    if (!got) return py::none();
+    const uint8_t* slot = data_ + (r % h_->slots) * stride_;
+    const uint32_t len = reinterpret_cast<const uint32_t*>(slot)[0];
+    const uint32_t kind = reinterpret_cast<const uint32_t*>(slot)[1];
+    py::object payload;
+    if (as_ints && kind != 0) {
+      i32arr out(len / 4);
+      std::memcpy(out.mutable_data(), slot + 8, len / 4 * 4);
+      payload = std::move(out);
+    } else {
+      payload = py::bytes(reinterpret_cast<const char*>(slot + 8), len);
+    }
+    cur.store(r + 1, std::memory_order_release);
+    return py::make_tuple(kind, payload);
+  }
+
+ private:
+  std::string name_;
+  int consumer_;
+  bool owner_;
+  size_t bytes_ = 0, stride_ = 0;
+  Header* h_ = nullptr;
+  uint8_t* data_ = nullptr;
+};
+
 PYBIND11_MODULE(_sched_native, m) {
   m.doc() = "paged KV slot allocator and radix-tree prefix index";
   py::class_<PagedAllocator>(m, "PagedAllocator")
@@ -434,4 +604,16 @@ PYBIND11_MODULE(_sched_native, m) {
       .def("key_value", &RadixTree::key_value)
       .def("alive", &RadixTree::alive)
       .def("num_nodes", &RadixTree::num_nodes);
+  py::class_<StepRing>(m, "StepRing")
+      .def(py::init<const std::string&, int, int, int, int>(), py::arg("name"), py::arg("slots"),
+           py::arg("slot_bytes"), py::arg("consumers"), py::arg("consumer") = -1)
+      .def("push", &StepRing::push, py::arg("payload"), py::arg("kind") = 0, py::arg("timeout_s") = 60.0)
+      .def("push_ints", &StepRing::push_ints, py::arg("ints"), py::arg("kind") = 1, py::arg("timeout_s") = 60.0)
+      .def("pop", &StepRing::pop, py::arg("timeout_s") = 60.0, py::arg("as_ints") = true)
+      .def("written", &StepRing::written)
+      .def("consumed", &StepRing::consumed)
+      .def("slowest", &StepRing::slowest)
+      .def("close", &StepRing::close_ring)
+      .def("closed", &StepRing::closed)
+      .def("slot_bytes", &StepRing::slot_bytes);
 }

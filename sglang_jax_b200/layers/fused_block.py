@@ -43,8 +43,17 @@ def model_supports_fused_residual(model) -> bool:
                if isinstance(m, RowParallelLinear) and m.tp_size > 1)
 
 
-def row_linear_add_norm(lin, x, residual, norm):
-    """Returns `(norm(lin(x) + residual), lin(x) + residual)`."""
+def _plain_consumer(consumer) -> bool:
+    """The layer that reads the normalised rows next is a plain bf16 projection, whose GEMM can wait for the
+    all-gather chunk by chunk (`FusedComm.consume_linear`)."""
+    return (consumer is not None and getattr(consumer, "qweight", 1) is None and getattr(consumer, "lora", 1) is None
+            and getattr(consumer, "weight", None) is not None)
+
+
+def row_linear_add_norm(lin, x, residual, norm, consumer=None):
+    """Returns `(norm(lin(x) + residual), lin(x) + residual)`.  `consumer`: the linear layer that will read the
+    first result next, with nothing in between; when it is a plain projection the all-gather of the normalised
+    rows is not waited for here but inside that projection's GEMM."""
     comm = ps.get_state().fused_comm if _FUSED_RESIDUAL else None
     if comm is not None and lin.tp_size > 1 and comm.supports_gemm_ar_norm(x, lin.out_features):
         if not row_linear_qualifies(lin):
@@ -52,7 +61,8 @@ def row_linear_add_norm(lin, x, residual, norm):
                                "`model_supports_fused_residual` must gate the forward")
         if lin.bias is None and lin.qweight is None:
             return comm.gemm_allreduce_add_rmsnorm(x, lin.weight, residual, norm.weight,
-                                                   norm.variance_epsilon, norm.gemma)
+                                                   norm.variance_epsilon, norm.gemma,
+                                                   defer=_plain_consumer(consumer))
         # bias (held by rank 0 only) or quantised weight: the local product is still a partial sum
         from .linear import LinearBase
         buf = comm.partial_buffer(x.shape[0])

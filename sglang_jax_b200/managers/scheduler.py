@@ -501,7 +501,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
     def get_new_batch_prefill(self) -> ScheduleBatch | None:
         if (self.running_batch.batch_is_full or not self.waiting_queue) and self.chunked_req is None:
             return None
-        running_bs = len(self.running_batch.reqs)
+        # rows of requests that have just finished are free again (they leave the batch at its next filter)
+        running_bs = sum(1 for r in self.running_batch.reqs if not r.finished())
         if running_bs >= self.max_running_requests and self.chunked_req is None:
             self.running_batch.batch_is_full = True
             return None

@@ -10,6 +10,7 @@ step's batch to the follower ranks, which run `run_tp_follower` below.
 from __future__ import annotations
 
 import logging
+import os
 from dataclasses import dataclass
 from typing import Any
 
@@ -69,6 +70,15 @@ class ModelWorker:
         self.max_req_input_len = self.max_req_len - 5
         self.random_seed = server_args.random_seed
         self.broadcast_batches = self.tp_size > 1 and self.tp_rank == 0 and not is_draft_worker
+        # rank 0 -> followers: shared-memory ring on one node, host broadcast across nodes (created by every
+        # rank at the same point of its start-up; the speculative draft worker shares the target's)
+        self.channel = getattr(st, "step_channel", None)
+        if self.tp_size > 1 and not is_draft_worker:
+            from ..parallel.step_channel import StepChannel
+            self.channel = StepChannel(st.tp, use_shm=getattr(server_args, "nnodes", 1) == 1
+                                       and os.environ.get("SGLB_STEP_CHANNEL", "shm") == "shm",
+                                       timeout_s=float(server_args.dist_timeout or 120.0))
+            st.step_channel = self.channel
         self._pinned_ids = None
         self.marks: dict = {}
         # Host collectives with the follower ranks are issued from the scheduler thread (batches)
@@ -98,13 +108,13 @@ class ModelWorker:
         draft / verify sequence on their shards."""
         if self.broadcast_batches:
             with self._comm_lock:
-                ps.broadcast_object(_Control(kind, payload), src=0, group=ps.get_state().tp)
+                self.channel.send(_Control(kind, payload))
 
     def forward_batch_generation(self, batch: ModelWorkerBatch, launch_done=None, skip_sample: bool = False,
                                  broadcast: bool = True) -> GenerationBatchResult:
         if self.broadcast_batches and broadcast:
             with self._comm_lock:
-                ps.broadcast_object(batch, src=0, group=ps.get_state().tp)
+                self.channel.send(batch)
         out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
         res = GenerationBatchResult(out, ids, bid=batch.bid, forward_batch=fb)
         if ids is not None and self.device.type == "cuda":
@@ -131,7 +141,7 @@ class ModelWorker:
     def forward_batch_embedding(self, batch: ModelWorkerBatch):
         if self.broadcast_batches:
             with self._comm_lock:
-                ps.broadcast_object(_Control("embed", batch), src=0, group=ps.get_state().tp)
+                self.channel.send(_Control("embed", batch))
         batch.capture_hidden_mode = 1
         out, _, _ = self.model_runner.forward(batch, skip_sample=True)
         return out.hidden_states
@@ -143,7 +153,7 @@ class ModelWorker:
             return False, "LoRA is not enabled (--enable-lora)"
         if self.broadcast_batches:
             with self._comm_lock:
-                ps.broadcast_object(_Control("load_lora", recv), src=0, group=ps.get_state().tp)
+                self.channel.send(_Control("load_lora", recv))
         return lm.load_adapter(LoRARef(lora_id=recv.lora_id, lora_name=recv.lora_name, lora_path=recv.lora_path))
 
     def unload_lora_adapter(self, recv) -> tuple[bool, str]:
@@ -152,19 +162,21 @@ class ModelWorker:
             return False, "LoRA is not enabled (--enable-lora)"
         if self.broadcast_batches:
             with self._comm_lock:
-                ps.broadcast_object(_Control("unload_lora", recv), src=0, group=ps.get_state().tp)
+                self.channel.send(_Control("unload_lora", recv))
         return lm.unload_adapter(recv.lora_id)
 
     def send_control(self, kind: str, payload=None):
         if self.broadcast_batches:
             with self._comm_lock:
-                ps.broadcast_object(_Control(kind, payload), src=0, group=ps.get_state().tp)
+                self.channel.send(_Control(kind, payload))
 
     def flush(self):
         self.send_control("flush")
 
     def shutdown(self):
         self.send_control("shutdown")
+        if self.broadcast_batches and self.channel is not None:
+            self.channel.close()
 
     def mark(self, tag: str):
         """Record a timing event on this rank's stream and on every follower's."""
@@ -221,7 +233,10 @@ def run_tp_follower(server_args, worker: ModelWorker | None = None, on_message=N
         from ..speculative.spec_info import create_spec_worker
         spec = create_spec_worker(server_args, worker)
     while True:
-        msg = ps.broadcast_object(None, src=0, group=tp)
+        try:
+            msg = worker.channel.recv(on_idle=on_message)
+        except EOFError:
+            break
         if on_message is not None:
             on_message()          # liveness hook (e.g. re-arm a hang watchdog)
         if isinstance(msg, _Control):

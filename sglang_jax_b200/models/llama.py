@@ -78,14 +78,15 @@ class DenseDecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(config.hidden_size, eps, dtype)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps, dtype)
 
-    def forward(self, hidden_normed, residual, forward_batch, next_norm):
+    def forward(self, hidden_normed, residual, forward_batch, next_norm, next_consumer=None):
         """`hidden_normed` is this layer's already-normalised input; returns the next layer's
-        normalised input and the updated residual stream."""
+        normalised input and the updated residual stream.  `next_consumer`: the projection of the next layer
+        that reads the returned activations first (its GEMM then absorbs the all-gather wait)."""
         attn_out = self.self_attn(hidden_normed, forward_batch)
         h, residual = row_linear_add_norm(self.self_attn.o_proj, attn_out, residual,
-                                          self.post_attention_layernorm)
+                                          self.post_attention_layernorm, consumer=self.mlp.gate_up_proj)
         act = self.mlp.act_fn(self.mlp.gate_up_proj(h))
-        return row_linear_add_norm(self.mlp.down_proj, act, residual, next_norm)
+        return row_linear_add_norm(self.mlp.down_proj, act, residual, next_norm, consumer=next_consumer)
 
 
 class DenseModel(nn.Module):
@@ -99,6 +100,9 @@ class DenseModel(nn.Module):
                                      for i in range(config.num_hidden_layers)])
         self.norm = RMSNorm(config.hidden_size, getattr(config, "rms_norm_eps", 1e-6), dtype)
         self.layers_to_capture: list[int] = []
+        # layers of this class read their input only through `self_attn.qkv_proj`, so the previous layer may
+        # leave the all-gather wait to that GEMM; subclasses with other first readers switch this off
+        self.defer_gather = self.layer_cls is DenseDecoderLayer
 
     def forward(self, input_ids, forward_batch, input_embeds=None):
         residual = self.embed_tokens(input_ids) if input_embeds is None else input_embeds
@@ -114,7 +118,10 @@ class DenseModel(nn.Module):
                 # the fused add-norm kernels update `residual` in place: keep a copy, not a reference
                 aux.append(residual.clone())
             nxt = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
-            h, residual = layer(h, residual, forward_batch, nxt)
+            if self.defer_gather and i + 1 < n:
+                h, residual = layer(h, residual, forward_batch, nxt, self.layers[i + 1].self_attn.qkv_proj)
+            else:
+                h, residual = layer(h, residual, forward_batch, nxt)
             deep = forward_batch.extras.get("deepstack")
             if deep is not None and i < deep.shape[0]:
                 # vision features join the residual stream after the first layers (deep-stack)

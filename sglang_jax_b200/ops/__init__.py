@@ -65,6 +65,11 @@ def silu_and_mul(x):
 
 def linear(x, w, bias=None):
     if use_native(x) and w.dtype == torch.bfloat16:
+        from ..parallel import state as ps
+        comm = ps.get_state().fused_comm
+        if comm is not None and comm.pending_gather is not None:
+            # `x` may be a fused all-gather nobody has waited for yet: the GEMM waits per chunk of rows
+            return comm.consume_linear(x, w, bias)
         return _native().linear(x, w, bias)
     return reference.linear(x, w, bias)
 

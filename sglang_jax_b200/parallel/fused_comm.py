@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import ctypes
 import logging
+import os
 
 import torch
 
@@ -32,6 +33,14 @@ class _Symm:
     """One symmetric allocation: local tensor + device pointers of every rank's copy."""
 
     def __init__(self, numel: int, dtype, device, group):
+        if group is None:
+            # single-rank loop-back: an ordinary allocation is its own (and only) peer
+            self.tensor = torch.zeros(numel, dtype=dtype, device=device)
+            self.handle = None
+            self.ptrs = (ctypes.c_void_p * 1)(self.tensor.data_ptr())
+            self.world = 1
+            self.multicast_ptr = 0
+            return
         import torch.distributed._symmetric_memory as symm_mem
         self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
         self.tensor.zero_()
@@ -39,6 +48,8 @@ class _Symm:
         ptrs = list(self.handle.buffer_ptrs)
         self.ptrs = (ctypes.c_void_p * len(ptrs))(*ptrs)
         self.world = len(ptrs)
+        # NVSwitch multicast mapping of the same allocation (0 when the fabric offers none)
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
 
 
 class FusedComm:
@@ -59,6 +70,20 @@ class FusedComm:
                                         ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         self.push_epilogue = True   # GEMM epilogue does the reduce-scatter sends
+        # one launch for GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather (SGLB_FUSED_ONE_KERNEL=0 keeps the
+        # GEMM-with-push-epilogue + separate reduce kernel pair)
+        self.one_kernel = os.environ.get("SGLB_FUSED_ONE_KERNEL", "1") != "0"
+        L.sglb_gemm_rs_norm_ag.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
+                                           ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        L.sglb_gemm_bf16_ag.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                        ctypes.c_void_p]
+        L.sglb_fused_wait_gather.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                             ctypes.c_void_p]
         L.sglb_argmax_gather.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
@@ -70,14 +95,16 @@ class FusedComm:
         self.L = L
         try:
             import torch.distributed._symmetric_memory as symm_mem
-            if hasattr(symm_mem, "enable_symm_mem_for_group"):
+            if group is not None and hasattr(symm_mem, "enable_symm_mem_for_group"):
                 import warnings
                 with warnings.catch_warnings():
                     warnings.simplefilter("ignore")
                     symm_mem.enable_symm_mem_for_group(group.group_name)
         except Exception:
             pass
-        n = (max_tokens + 8) * hidden     # room for ceil(T / world) * world rows
+        max_tokens = min(max_tokens, L.sglb_fused_max_tokens())
+        self.max_tokens = max_tokens
+        n = (max_tokens + 128 * self.world + 8) * hidden     # room for world slices rounded up to whole 128-row tiles
         self.ypart = _Symm(n, dtype, self.device, group)        # row-parallel GEMM partials
         self.gathered = _Symm(n, dtype, self.device, group)     # normalised activations, all rows
         self.flags = _Symm(L.sglb_comm_flag_bytes() // 4, torch.int32, self.device, group)
@@ -88,11 +115,30 @@ class FusedComm:
         self.flags3 = _Symm(L.sglb_comm_flag_bytes() // 4, torch.int32, self.device, group)
         self.epochs3 = torch.zeros(L.sglb_comm_max_blocks(), dtype=torch.int32, device=self.device)
         self.group = group
+        # single-launch path: epoch-valued arrival flags (symmetric), the call counter and the local tail counters
+        self.fflags = _Symm(L.sglb_fused_flag_words(), torch.int32, self.device, group)
+        self.fseq = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.fctrs = torch.zeros(L.sglb_fused_ctr_ints(), dtype=torch.int32, device=self.device)
+        # all-gather stores through the NVSwitch multicast mapping (one multimem.st instead of `world` stores)
+        self.gathered_mc = self.gathered.multicast_ptr if os.environ.get("SGLB_AG_MULTIMEM", "0") == "1" else 0
+        # (tokens,) of a deferred all-gather whose arrival nobody has waited for yet
+        self.pending_gather: int | None = None
         self.logits_full: _Symm | None = None       # [LOGITS_GATHER_ROWS, world * shard] of the logits dtype, on demand
         self.logits_full_key = None
         torch.cuda.synchronize(self.device)
-        import torch.distributed as dist
-        dist.barrier(group=state.tp.cpu_group)
+        if group is not None:
+            import torch.distributed as dist
+            dist.barrier(group=state.tp.cpu_group)
+
+    @classmethod
+    def create_loopback(cls, hidden: int, device, max_tokens: int = 4096) -> "FusedComm":
+        """A one-rank context on ordinary device memory: the same kernels with `world == 1` (every peer store
+        lands in this GPU's own buffers, every flag wait is satisfied by this launch itself).  For single-GPU
+        tests of the fused kernels; no process group is needed."""
+        from types import SimpleNamespace
+        st = SimpleNamespace(tp=SimpleNamespace(rank=0, size=1, device_group=None, cpu_group=None),
+                             device=torch.device(device))
+        return cls(st, hidden, torch.bfloat16, max_tokens)
 
     @classmethod
     def create(cls, state, hidden: int, dtype, max_tokens: int = 16384) -> "FusedComm":
@@ -111,8 +157,26 @@ class FusedComm:
         """This rank's `[T, hidden]` slot for a partial sum that `allreduce_add_rmsnorm` will reduce."""
         return self.ypart.tensor[: T * self.hidden].view(T, self.hidden)
 
-    def gemm_allreduce_add_rmsnorm(self, x, w, residual, norm_w, eps, gemma=False):
+    def gemm_allreduce_add_rmsnorm(self, x, w, residual, norm_w, eps, gemma=False, defer: bool = False):
+        """`norm(x @ w.T summed over ranks + residual)` for all `T` rows, and the residual (rows of this rank's
+        slice updated in place).  `defer`: return without waiting for the other ranks' rows; the result must then
+        be consumed by `consume_linear` (or after `ensure_gathered`)."""
         T, K = x.shape
+        self.ensure_gathered()
+        if self.one_kernel and K % 8 == 0 and x.is_contiguous() and w.is_contiguous():
+            assert residual is None or (residual.is_contiguous() and residual.shape == (T, self.hidden))
+            sc = native.gemm_scratch(x.device)
+            rc = self.L.sglb_gemm_rs_norm_ag(x.data_ptr(), w.data_ptr(), T, self.hidden, K, sc.workspace.data_ptr(),
+                                             sc.bytes, sc.counters.data_ptr(), self.ypart.ptrs, self.gathered.ptrs,
+                                             self.gathered_mc or None, self.fflags.ptrs, self.fseq.data_ptr(),
+                                             self.fctrs.data_ptr(),
+                                             residual.data_ptr() if residual is not None else None, norm_w.data_ptr(),
+                                             float(eps), int(gemma), int(defer), self.world, self.rank,
+                                             torch.cuda.current_stream().cuda_stream)
+            native._check(rc, "gemm_rs_norm_ag")
+            if defer:
+                self.pending_gather = T
+            return self.gathered.tensor[: T * self.hidden].view(T, self.hidden), residual
         if self.push_epilogue and K % 8 == 0 and x.is_contiguous() and w.is_contiguous():
             sc = native.gemm_scratch(x.device)
             rc = self.L.sglb_gemm_bf16_rs(x.data_ptr(), w.data_ptr(), T, self.hidden, K, sc.workspace.data_ptr(),
@@ -123,7 +187,44 @@ class FusedComm:
         native.linear(x, w, None, out=self.partial_buffer(T))
         return self.allreduce_add_rmsnorm(T, residual, norm_w, eps, gemma)
 
+    def rows_per(self, T: int) -> int:
+        """Token rows each rank owns (reduces, normalises, keeps the residual of) in the single-launch path."""
+        out = (ctypes.c_int * 3)()
+        self.L.sglb_fused_layout(T, self.world, out)
+        return int(out[0])
+
+    def ensure_gathered(self):
+        """Make the stream wait for a deferred all-gather that no flag-aware consumer has picked up."""
+        T = self.pending_gather
+        if T is None:
+            return
+        self.pending_gather = None
+        rc = self.L.sglb_fused_wait_gather(self.fflags.ptrs[self.rank], self.fseq.data_ptr(), T, self.world,
+                                           torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "fused_wait_gather")
+
+    def consume_linear(self, x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+        """`x @ w.T (+ bias)` where `x` may be the result of a deferred fused call: the GEMM's loader then waits for
+        each chunk of rows as it needs it (all-gather -> GEMM in one launch) instead of a barrier before the GEMM."""
+        T = self.pending_gather
+        K, N = x.shape[-1], w.shape[0]
+        if (T is None or x.dim() != 2 or x.shape[0] != T or K != self.hidden or not x.is_contiguous()
+                or x.data_ptr() != self.gathered.tensor.data_ptr() or N % 8 or not w.is_contiguous()
+                or w.dtype != torch.bfloat16):
+            self.ensure_gathered()
+            return native.linear(x, w, bias)
+        self.pending_gather = None
+        out = torch.empty((T, N), dtype=x.dtype, device=x.device)
+        sc = native.gemm_scratch(x.device)
+        rc = self.L.sglb_gemm_bf16_ag(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                      out.data_ptr(), T, N, K, sc.workspace.data_ptr(), sc.bytes, sc.counters.data_ptr(),
+                                      self.fflags.ptrs, self.fseq.data_ptr(), self.world, self.rank,
+                                      torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "gemm_bf16_ag")
+        return out
+
     def allreduce_add_rmsnorm(self, T: int, residual, norm_w, eps, gemma=False, rs_mode: int = 0):
+        self.ensure_gathered()
         H = self.hidden
         assert residual is None or (residual.is_contiguous() and residual.shape == (T, H))
         rc = self.L.sglb_ar_residual_rmsnorm(self.ypart.ptrs, self.gathered.ptrs, self.flags.ptrs,

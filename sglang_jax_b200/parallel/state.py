@@ -39,6 +39,7 @@ class ParallelState:
     world: GroupInfo = field(default_factory=GroupInfo)
     initialized: bool = False
     fused_comm: Any = None                              # parallel.fused_comm.FusedComm or None
+    step_channel: Any = None                            # parallel.step_channel.StepChannel (rank 0 -> followers)
 
 
 _STATE = ParallelState()

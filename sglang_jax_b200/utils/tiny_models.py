@@ -80,6 +80,11 @@ def tiny_qwen3_state_dict(config: dict = TINY_QWEN3, seed: int = 0, std: float =
         sd[p + "self_attn.k_proj.weight"] = w(nkv * D, H)
         sd[p + "self_attn.v_proj.weight"] = w(nkv * D, H)
         sd[p + "self_attn.o_proj.weight"] = w(H, nh * D)
+        if config.get("attention_bias"):
+            sd[p + "self_attn.q_proj.bias"] = w(nh * D)
+            sd[p + "self_attn.k_proj.bias"] = w(nkv * D)
+            sd[p + "self_attn.v_proj.bias"] = w(nkv * D)
+            sd[p + "self_attn.o_proj.bias"] = w(H)
         sd[p + "self_attn.q_norm.weight"] = torch.ones(D)
         sd[p + "self_attn.k_norm.weight"] = torch.ones(D)
         sd[p + "mlp.gate_proj.weight"] = w(I, H)
@@ -93,11 +98,14 @@ def tiny_qwen3_state_dict(config: dict = TINY_QWEN3, seed: int = 0, std: float =
     return sd
 
 
-def write_tiny_qwen3_checkpoint(path: str, seed: int = 0, config: dict | None = None, dtype=torch.float32) -> str:
+def write_tiny_qwen3_checkpoint(path: str, seed: int = 0, config: dict | None = None, dtype=torch.float32,
+                                std: float = 0.02) -> str:
     from safetensors.torch import save_file
     cfg = dict(config or TINY_QWEN3)
     write_config_only(path, cfg)
-    sd = {k: v.to(dtype).contiguous() for k, v in tiny_qwen3_state_dict(cfg, seed).items()}
+    sd = {k: v.to(dtype).contiguous() for k, v in tiny_qwen3_state_dict(cfg, seed, std).items()}
+    if cfg.get("model_type") == "llama":
+        sd = {k: v for k, v in sd.items() if "q_norm" not in k and "k_norm" not in k}
     save_file(sd, os.path.join(path, "model.safetensors"))
     return path
 

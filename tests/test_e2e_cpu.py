@@ -5,6 +5,7 @@ exactly, independent of radix cache, chunking, overlap scheduling and tensor par
 
 import os
 import sys
+import time
 
 import numpy as np
 import pytest
@@ -144,3 +145,136 @@ def test_tensor_parallel_gloo_matches_oracle(ckpt, oracle, world):
             if p.is_alive():
                 p.kill()
     assert outs == oracle
+
+
+# ------------------------------------------------------------------------------------------
+# rank 0 -> follower step channel (shared-memory ring) and what happens when a follower dies
+def test_step_channel_codec_roundtrip():
+    import numpy as np
+    from sglang_jax_b200.managers.schedule_batch import ForwardMode, ModelWorkerBatch, ModelWorkerSamplingInfo
+    from sglang_jax_b200.parallel.step_channel import decode_batch, encode_batch
+    B, T = 3, 7
+    si = ModelWorkerSamplingInfo(temperatures=np.array([0.0, 0.7, 1.0], np.float32), top_ps=np.array([1, 0.9, 0.5], np.float32),
+                                 top_ks=np.array([1, 40, 1 << 30], np.int32), min_ps=np.zeros(3, np.float32),
+                                 sampling_seeds=np.array([5, 6, 7], np.int32), is_all_greedy=False,
+                                 need_top_p_sampling=True, need_top_k_sampling=True, need_min_p_sampling=False,
+                                 positions=np.array([4, 9, 2], np.int32))
+    b = ModelWorkerBatch(bid=11, forward_mode=ForwardMode.EXTEND, input_ids=np.arange(T, dtype=np.int32) - 3,
+                         req_pool_indices=np.array([2, 0, 5], np.int32), seq_lens=np.array([9, 3, 4], np.int32),
+                         out_cache_loc=np.arange(T, dtype=np.int32) + 64, positions=np.arange(T, dtype=np.int32),
+                         extend_prefix_lens=np.array([6, 0, 2], np.int32), extend_seq_lens=np.array([3, 3, 1], np.int32),
+                         page_delta_rows=np.array([2, 5], np.int32), page_delta_pos=np.array([0, 1], np.int32),
+                         page_delta_ids=np.array([9, 8], np.int32), sampling_info=si,
+                         future_slots=np.array([3, 1, 6], np.int64), real_bs=3)
+    ints = encode_batch(b)
+    assert ints is not None and ints.dtype == np.int32
+    d = decode_batch(ints)
+    for f in ("input_ids", "req_pool_indices", "seq_lens", "out_cache_loc", "positions", "extend_prefix_lens",
+              "extend_seq_lens", "page_delta_rows", "page_delta_pos", "page_delta_ids", "future_slots"):
+        assert np.array_equal(getattr(d, f), getattr(b, f)), f
+    assert d.future_slots.dtype == np.int64 and d.bid == 11 and d.forward_mode == ForwardMode.EXTEND
+    for f in ("temperatures", "top_ps", "top_ks", "min_ps", "sampling_seeds", "positions"):
+        assert np.array_equal(getattr(d.sampling_info, f), getattr(si, f)), f
+    assert d.sampling_info.need_top_p_sampling and not d.sampling_info.is_all_greedy
+    b.return_logprob = True          # anything beyond a plain step's integers travels pickled
+    assert encode_batch(b) is None
+
+
+def _ring_consumer(name, idx, n, q):
+    sys.path.insert(0, ROOT)
+    from sglang_jax_b200.mem_cache import _sched_native as sn
+    ring = sn.StepRing(name, 4, 4096, 2, idx)
+    got = []
+    while len(got) < n:
+        m = ring.pop(5.0, True)
+        if m is None:
+            break
+        got.append((int(m[0]), bytes(m[1]) if m[0] == 0 else [int(x) for x in m[1]]))
+    q.put((idx, got))
+
+
+def test_step_ring_two_consumers_and_backpressure():
+    import multiprocessing as mp
+    import numpy as np
+    from sglang_jax_b200.mem_cache import _sched_native as sn
+    name = f"/sglb_test_ring_{os.getpid()}"
+    ring = sn.StepRing(name, 4, 4096, 2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    n = 20
+    procs = [ctx.Process(target=_ring_consumer, args=(name, i, n, q)) for i in range(2)]
+    for p in procs:
+        p.start()
+    for i in range(n):            # more messages than slots: the producer waits for both readers
+        if i % 2:
+            assert ring.push(b"msg%d" % i, 0, 10.0)
+        else:
+            assert ring.push_ints(np.arange(i, i + 3, dtype=np.int32), 1, 10.0)
+    res = dict(q.get(timeout=30) for _ in range(2))
+    for p in procs:
+        p.join(timeout=10)
+    want = [(0, b"msg%d" % i) if i % 2 else (1, [i, i + 1, i + 2]) for i in range(n)]
+    assert res[0] == want and res[1] == want
+    # nobody reads any more: the ring fills and a bounded push reports it instead of blocking
+    for _ in range(4):
+        assert ring.push(b"x", 0, 0.2)
+    assert not ring.push(b"x", 0, 0.2)
+    assert ring.slowest()[1] == 4
+
+
+def _tp_rank_dies(rank, world, port, ckpt, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    sys.path.insert(0, ROOT)
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.server_args import ServerArgs
+    torch.set_num_threads(2)
+    ps.init_distributed(rank, world, "cpu", init_method=f"tcp://127.0.0.1:{port}", timeout_s=20)
+    sa = ServerArgs(model_path=ckpt, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                    max_total_tokens=8192, enable_single_process=True, max_running_requests=16, tp_size=world,
+                    log_level="critical", watchdog_timeout=0, dist_timeout=5)
+    if rank != 0:
+        from sglang_jax_b200.managers.tp_worker import run_tp_follower
+        seen = {"n": 0}
+
+        def die_mid_stream():
+            seen["n"] += 1
+            if seen["n"] >= 12:          # between two steps: nothing of this rank is in flight
+                os._exit(0)
+
+        run_tp_follower(sa, on_message=die_mid_stream)
+        return
+    from sglang_jax_b200 import Engine
+    eng = Engine(server_args=sa)
+    t0 = time.time()
+    try:
+        outs = eng.generate(input_ids=workload(), sampling_params={"max_new_tokens": 200, "temperature": 0.0,
+                                                                    "ignore_eos": True})
+        q.put(("finished", [len(o["output_ids"]) for o in outs], time.time() - t0))
+    except Exception as e:
+        q.put(("failed", f"{type(e).__name__}: {e}", time.time() - t0))
+    q.close()
+    q.join_thread()          # the result must leave this process before it exits without clean-up
+    os._exit(0)
+
+
+def test_follower_death_fails_pending_requests(ckpt):
+    """A follower rank exits between two steps.  Rank 0 learns of it on the host (its next host collective
+    errors out, or the step ring fills up) and fails the requests in flight instead of hanging."""
+    import torch.multiprocessing as mp
+    from sglang_jax_b200.utils.common import get_free_port
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = get_free_port()
+    procs = [ctx.Process(target=_tp_rank_dies, args=(r, 2, port, ckpt, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        kind, detail, waited = q.get(timeout=240)
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    assert kind == "failed", (kind, detail)
+    assert waited < 200, waited

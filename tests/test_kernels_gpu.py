@@ -589,3 +589,68 @@ def test_gemm_fp8_per_token_per_channel(native, M, N, K):
     _close(got, want, 2e-2, 2e-2)
     full = x @ w.t() + bias.float()
     assert ((got.float() - full).norm() / full.norm()).item() < 0.08       # and close to the unquantised product
+
+
+# ------------------------------------------------------------------------------------------
+# The tensor-parallel kernels with world == 1 (loop-back on one GPU): the same code paths as on 2..8
+# GPUs (peer stores land in this GPU's own buffers, flag waits are met by the launch itself).
+def _fused_case(T, H, K, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(T, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(H, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    res = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    nw = (torch.randn(H, device="cuda", generator=g) * 0.1 + 1).to(torch.bfloat16)
+    y = (x.float() @ w.float().t()).to(torch.bfloat16).float() + res.float()
+    new_res = y.to(torch.bfloat16)
+    return x, w, res, nw, new_res, ref.rmsnorm(new_res, nw, 1e-6)
+
+
+@pytest.mark.parametrize("T", [1, 7, 128, 200, 300, 1100])
+@pytest.mark.parametrize("defer", [False, True])
+def test_fused_gemm_rs_norm_ag_loopback(native, T, defer):
+    from sglang_jax_b200.parallel.fused_comm import FusedComm
+    H, K, N2 = 1024, 512, 768
+    comm = FusedComm.create_loopback(H, "cuda", max_tokens=2048)
+    for it in range(3):      # repeated launches reuse buffers, flags and counters
+        x, w, res, nw, want_res, want = _fused_case(T, H, K, 100 + it)
+        got_res = res.clone()
+        out, _ = comm.gemm_allreduce_add_rmsnorm(x, w, got_res, nw, 1e-6, defer=defer)
+        if defer:
+            g = torch.Generator(device="cuda").manual_seed(7 + it)
+            w2 = (torch.randn(N2, H, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+            y2 = comm.consume_linear(out, w2)
+            assert comm.pending_gather is None
+            want2 = (want.float() @ w2.float().t())
+            err2 = (y2.float() - want2).abs().max().item()
+            assert err2 < 0.06 * max(1.0, want2.abs().max().item()), (T, it, err2)
+        torch.cuda.synchronize()
+        native.check_status()
+        err = (out.float() - want.float()).abs().max().item()
+        rerr = (got_res.float() - want_res.float()).abs().max().item()
+        assert err < 0.1 and rerr < 0.07, (T, it, err, rerr)
+    assert int(comm.fseq.item()) == 3 and int(comm.fctrs.abs().sum().item()) == 0
+
+
+def test_fused_two_kernel_path_and_gathers_loopback(native):
+    """The GEMM-with-push-epilogue + reduce kernel pair, the cross-rank argmax and the logits gather at world == 1."""
+    from sglang_jax_b200.parallel.fused_comm import FusedComm
+    H, K = 1024, 512
+    comm = FusedComm.create_loopback(H, "cuda", max_tokens=1024)
+    comm.one_kernel = False
+    for T in (5, 128, 400):
+        x, w, res, nw, want_res, want = _fused_case(T, H, K, 200 + T)
+        got_res = res.clone()
+        out, _ = comm.gemm_allreduce_add_rmsnorm(x, w, got_res, nw, 1e-6)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert (out.float() - want.float()).abs().max().item() < 0.1
+        assert (got_res.float() - want_res.float()).abs().max().item() < 0.07
+    g = torch.Generator(device="cuda").manual_seed(5)
+    logits = torch.randn(37, 1000, device="cuda", generator=g)
+    logits[3, 10] = logits[3, 700] = 50.0
+    ids = comm.argmax_gather(logits, 0, 995)
+    assert ids.long().tolist() == torch.argmax(logits[:, :995], dim=-1).tolist()
+    lb = logits.to(torch.bfloat16)
+    assert torch.equal(comm.logits_gather(lb), lb)
+    torch.cuda.synchronize()
+    native.check_status()

@@ -165,3 +165,25 @@ def test_varlen_page_packing_and_reference_attention():
         q[5:69].transpose(0, 1)[None], k[5:69].transpose(0, 1).repeat_interleave(2, 0)[None],
         v[5:69].transpose(0, 1).repeat_interleave(2, 0)[None])[0].transpose(0, 1)
     assert torch.allclose(alone, sd, atol=1e-5)
+
+
+def test_fused_residual_dataflow_is_chosen_per_model():
+    """A LoRA adapter on a row-parallel projection cannot feed the fused reduce: the whole model then keeps the
+    replicated residual stream; bias and quantised weights still qualify (their local product is a partial sum)."""
+    import torch
+    from sglang_jax_b200.layers.fused_block import model_supports_fused_residual, row_linear_qualifies
+    from sglang_jax_b200.layers.linear import RowParallelLinear
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.o_proj = RowParallelLinear(64, 32, True, torch.float32, tp_size=2, tp_rank=0)
+            self.down_proj = RowParallelLinear(64, 32, False, torch.float32, tp_size=2, tp_rank=0)
+
+    m = Block()
+    assert model_supports_fused_residual(m)
+    m.o_proj.lora = object()
+    assert not row_linear_qualifies(m.o_proj) and not model_supports_fused_residual(m)
+    m.o_proj.lora = None
+    m.down_proj.qweight = object()
+    assert model_supports_fused_residual(m)

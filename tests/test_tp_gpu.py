@@ -65,7 +65,7 @@ def _kernels(rank, world):
     from sglang_jax_b200.parallel import state as ps
     from sglang_jax_b200.parallel.fused_comm import FusedComm
     H = 1024
-    comm = FusedComm.create(ps.get_state(), H, torch.bfloat16, max_tokens=512)
+    comm = FusedComm.create(ps.get_state(), H, torch.bfloat16, max_tokens=2048)
     dev = torch.device("cuda", rank)
     report = {}
     for T in (1, 7, 128, 300):
@@ -93,24 +93,45 @@ def _kernels(rank, world):
         res_err = (res_mine[lo:hi].float() - exp_res[lo:hi].float()).abs().max().item() if hi > lo else 0.0
         report[T] = (err, res_err)
         assert err < 0.1 and res_err < 0.07, (T, err, res_err)
-    # GEMM whose epilogue pushes the reduce-scatter slices, then reduce + norm + all-gather
-    for T in (5, 128, 400):
-        K = 512
-        gx = [torch.Generator(device=dev).manual_seed(300 + r) for r in range(world)]
-        xs = [torch.randn(T, K, device=dev, generator=g).to(torch.bfloat16) for g in gx]
-        ws = [(torch.randn(H, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for g in gx]
-        g0 = torch.Generator(device=dev).manual_seed(9)
-        res = torch.randn(T, H, device=dev, generator=g0).to(torch.bfloat16)
-        nw = (torch.randn(H, device=dev, generator=g0) * 0.1 + 1).to(torch.bfloat16)
-        mine = res.clone()
-        out, _ = comm.gemm_allreduce_add_rmsnorm(xs[rank], ws[rank], mine, nw, 1e-6)
-        torch.cuda.synchronize()
-        native.check_status()
-        total = sum((x.float() @ w_.float().t()).to(torch.bfloat16).float() for x, w_ in zip(xs, ws)) + res.float()
-        exp = ref.rmsnorm(total.to(torch.bfloat16), nw, 1e-6)
-        err = (out.float() - exp.float()).abs().max().item()
-        assert err < 0.15, ("gemm_rs", T, err)
-        report[f"gemm_rs_{T}"] = err
+    # row-parallel GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather: the single launch (with and without
+    # the deferred all-gather wait, whose consumer is the next GEMM) and the two-kernel pair
+    N2 = 768
+    for one_kernel, defer in ((True, False), (True, True), (False, False)):
+        comm.one_kernel = one_kernel
+        for T in (5, 128, 300, 400, 1100):
+            K = 512
+            gx = [torch.Generator(device=dev).manual_seed(300 + r) for r in range(world)]
+            xs = [torch.randn(T, K, device=dev, generator=g).to(torch.bfloat16) for g in gx]
+            ws = [(torch.randn(H, K, device=dev, generator=g) * 0.05).to(torch.bfloat16) for g in gx]
+            g0 = torch.Generator(device=dev).manual_seed(9)
+            res = torch.randn(T, H, device=dev, generator=g0).to(torch.bfloat16)
+            nw = (torch.randn(H, device=dev, generator=g0) * 0.1 + 1).to(torch.bfloat16)
+            w2 = (torch.randn(N2, H, device=dev, generator=g0) * 0.05).to(torch.bfloat16)
+            total = sum((x.float() @ w_.float().t()).to(torch.bfloat16).float() for x, w_ in zip(xs, ws)) + res.float()
+            exp_res = total.to(torch.bfloat16)
+            exp = ref.rmsnorm(exp_res, nw, 1e-6)
+            for it in range(4):          # back-to-back launches reuse the buffers, flags and counters
+                mine = res.clone()
+                out, _ = comm.gemm_allreduce_add_rmsnorm(xs[rank], ws[rank], mine, nw, 1e-6, defer=defer)
+                if defer:
+                    y2 = comm.consume_linear(out, w2)
+                    assert comm.pending_gather is None
+            torch.cuda.synchronize()
+            native.check_status()
+            err = (out.float() - exp.float()).abs().max().item()
+            assert err < 0.15, ("gemm_rs", one_kernel, defer, T, err)
+            rows_per = comm.rows_per(T) if one_kernel else (T + world - 1) // world
+            lo, hi = rank * rows_per, min(T, (rank + 1) * rows_per)
+            if hi > lo:
+                rerr = (mine[lo:hi].float() - exp_res[lo:hi].float()).abs().max().item()
+                assert rerr < 0.07, ("gemm_rs residual", one_kernel, defer, T, rerr)
+            if defer:
+                want2 = exp.float() @ w2.float().t()
+                err2 = (y2.float() - want2).abs().max().item()
+                assert err2 < 0.06 * max(1.0, want2.abs().max().item()), ("ag_gemm", T, err2)
+            report[f"gemm_rs_{int(one_kernel)}{int(defer)}_{T}"] = err
+            ps.barrier()
+    comm.one_kernel = True
     # vocab-parallel argmax
     B, V = 37, 1000
     g = torch.Generator(device=dev).manual_seed(5)
@@ -145,12 +166,17 @@ def test_fused_comm_kernels_two_ranks():
 
 
 # ------------------------------------------------------------------------------------------
-def _engine(rank, world, fused):
+def _engine(rank, world, fused, biased=False):
     from sglang_jax_b200.server_args import ServerArgs
     from sglang_jax_b200.utils.tiny_models import TINY_QWEN3, write_tiny_qwen3_checkpoint
     cfg = dict(TINY_QWEN3, head_dim=128, num_attention_heads=8, num_key_value_heads=2, hidden_size=1024,
                intermediate_size=2048, num_hidden_layers=3, torch_dtype="bfloat16", tie_word_embeddings=False)
-    path = write_tiny_qwen3_checkpoint(f"/tmp/sglb200_tp_test_{rank}", config=cfg, dtype=torch.bfloat16)
+    if biased:
+        # Llama with attention biases: o_proj feeds the fused reduce as a plain partial sum (bias on rank 0),
+        # down_proj through the GEMM with the push epilogue, inside one forward
+        cfg.update(architectures=["LlamaForCausalLM"], model_type="llama", attention_bias=True)
+    path = write_tiny_qwen3_checkpoint(f"/tmp/sglb200_tp_test_{rank}_{int(biased)}", config=cfg, dtype=torch.bfloat16,
+                                       std=0.05)
     sa = ServerArgs(model_path=path, device="cuda", dtype="bfloat16", page_size=16, skip_tokenizer_init=True,
                     max_total_tokens=8192, max_running_requests=8, enable_single_process=True, tp_size=world,
                     cuda_graph_max_bs=8, disable_fused_comm=not fused, log_level="error", watchdog_timeout=0,
@@ -165,23 +191,47 @@ def _engine(rank, world, fused):
     eng = Engine(server_args=sa)
     try:
         assert (ps.get_state().fused_comm is not None) == fused
-        prompts = [list(range(1, 50)), list(range(3, 200)), [7] * 20, list(range(100, 420))]
-        outs = eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 10, "temperature": 0.0,
-                                                                "ignore_eos": True})
+        prompts = [list(range(1, 50)), list(range(3, 200)), [7, 900, 33, 512, 5] * 4, list(range(100, 420))]
+        sp = {"max_new_tokens": 10, "temperature": 0.0, "ignore_eos": True}
+        outs = eng.generate(input_ids=prompts, sampling_params=sp)
+        # the same prompts again with log-probabilities: every candidate's value at the first decoded position
+        lp = eng.generate(input_ids=prompts, sampling_params=dict(sp, max_new_tokens=2), return_logprob=True,
+                          top_logprobs_num=5)
         torch.cuda.synchronize()
         native.check_status()
-        return [o["output_ids"] for o in outs]
+        tops = [[(t[1], t[0]) for t in o["meta_info"]["output_top_logprobs"][0]] for o in lp]
+        return [o["output_ids"] for o in outs], tops
     finally:
         eng.shutdown()
 
 
+def _check_engines_agree(fused, nccl):
+    toks_f, tops_f = fused
+    toks_n, tops_n = nccl
+    assert all(len(x) == 10 for x in toks_f)
+    # log-probabilities of the five best first tokens agree closely, so does their order where they are apart
+    for tf, tn in zip(tops_f, tops_n):
+        df, dn = dict(tf), dict(tn)
+        assert tf[0][0] == tn[0][0] or abs(tf[0][1] - tf[1][1]) < 0.05, (tf, tn)
+        common = set(df) & set(dn)
+        assert len(common) >= 3, (tf, tn)
+        for t in common:
+            assert abs(df[t] - dn[t]) < 0.08, (t, df[t], dn[t])
+    flat_f = [t for o in toks_f for t in o]
+    flat_n = [t for o in toks_n for t in o]
+    assert len(set(flat_f)) > 5, toks_f                      # not a degenerate echo
+    agree = sum(a == b for a, b in zip(flat_f, flat_n)) / len(flat_f)
+    assert agree >= 0.7, (toks_f, toks_n)
+
+
 def test_engine_tp2_fused_matches_nccl():
     _need2()
-    fused = _spawn(_engine, args=(True,))[0]
-    nccl = _spawn(_engine, args=(False,))[0]
-    assert all(len(x) == 10 for x in fused)
-    agree = sum(a[:3] == b[:3] for a, b in zip(fused, nccl))
-    assert agree >= 3, (fused, nccl)
+    _check_engines_agree(_spawn(_engine, args=(True,))[0], _spawn(_engine, args=(False,))[0])
+
+
+def test_engine_tp2_fused_matches_nccl_with_biased_row_parallel_layer():
+    _need2()
+    _check_engines_agree(_spawn(_engine, args=(True, True))[0], _spawn(_engine, args=(False, True))[0])
 
 
 # ------------------------------------------------------------------------------------------
