@@ -98,26 +98,44 @@ class ExpertLocation:
 
 
 class ExpertDistributionRecorder:
-    """Ring buffer of per-layer expert hit counts (`--enable-expert-distribution-recorder`)."""
+    """Per-layer expert hit counts (`--enable-expert-distribution-recorder`; reference flags
+    `expert_distribution_recorder_buffer_size` / `_output_file`).  Counting happens on the device with a
+    scatter-add (no synchronisation inside the forward); every `buffer_size` recorded forwards, and at
+    shutdown, the totals are written to the output file as a `[layers, experts]` array that
+    `--init-expert-location <file>` and `eplb/tools.py` read back."""
 
-    def __init__(self, num_layers: int, num_experts: int, buffer_size: int = 100, output_file: str | None = None):
-        self.buf = np.zeros((buffer_size, num_layers, num_experts), dtype=np.int64)
-        self.pos = 0
-        self.filled = 0
+    def __init__(self, num_layers: int, num_experts: int, buffer_size: int = 100, output_file: str | None = None,
+                 device="cpu"):
+        self.counts = torch.zeros((num_layers, num_experts), dtype=torch.int64, device=device)
+        self.buffer_size = max(int(buffer_size), 1)
         self.output_file = output_file
+        self.forwards = 0
+        # kept for callers that used the host ring of the first version
+        self.buf = np.zeros((1, num_layers, num_experts), dtype=np.int64)
 
     def record(self, layer_id: int, topk_ids: torch.Tensor):
-        c = torch.bincount(topk_ids.reshape(-1).long().cpu(), minlength=self.buf.shape[2]).numpy()
-        self.buf[self.pos, layer_id] = c[: self.buf.shape[2]]
+        ids = topk_ids.reshape(-1).long()
+        if ids.device != self.counts.device:
+            ids = ids.to(self.counts.device)
+        self.counts[layer_id].scatter_add_(0, ids.clamp_(0, self.counts.shape[1] - 1), torch.ones_like(ids))
 
     def step(self):
-        self.pos = (self.pos + 1) % len(self.buf)
-        self.filled = min(self.filled + 1, len(self.buf))
-        self.buf[self.pos] = 0
+        self.forwards += 1
+        if self.forwards % self.buffer_size == 0:
+            self.dump()
 
     def aggregate(self) -> np.ndarray:
-        return self.buf[: max(self.filled, 1)].sum(0)
+        return self.counts.cpu().numpy()
 
     def dump(self):
         if self.output_file:
             np.save(self.output_file, self.aggregate())
+
+
+def load_expert_load(path: str) -> np.ndarray:
+    """`[layers, experts]` hit counts from a recorder dump (`.npy`) or a JSON list of lists."""
+    if path.endswith(".json"):
+        import json
+        with open(path) as f:
+            return np.asarray(json.load(f), dtype=np.float64)
+    return np.asarray(np.load(path), dtype=np.float64)

@@ -40,6 +40,28 @@ def expert_storage(dtype):
         _EXPERT_STORAGE = prev
 
 
+class MoeRuntime:
+    """Expert-placement options the model runner sets before the model is built (reference flags
+    `ep_num_redundant_experts`, `init_expert_location`, `enable_expert_distribution_recorder`)."""
+
+    num_redundant: int = 0
+    expert_load = None            # [layers, experts] hit counts that seed the placement, or None ("trivial")
+    recorder = None               # eplb.ExpertDistributionRecorder
+
+
+_RUNTIME = MoeRuntime()
+
+
+def configure_moe_runtime(num_redundant: int = 0, init_expert_location: str | None = "trivial", recorder=None):
+    _RUNTIME.num_redundant = int(num_redundant or 0)
+    _RUNTIME.expert_load = None
+    if init_expert_location and init_expert_location != "trivial":
+        from ..eplb.expert_location import load_expert_load
+        _RUNTIME.expert_load = load_expert_load(init_expert_location)
+    _RUNTIME.recorder = recorder
+    return _RUNTIME
+
+
 class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, hidden_size: int, intermediate_size: int, dtype=torch.bfloat16,
                  ep_size: int | None = None, tp_size=None, tp_rank=None, layer_id: int = 0,
@@ -50,8 +72,22 @@ class FusedMoE(nn.Module):
         self.tp_rank = tp_rank if tp_rank is not None else ps.tp_rank()
         ep = ep_size if ep_size is not None else ps.ep_size()
         self.expert_parallel = ep > 1 and ep == self.tp_size
-        self.num_experts = num_experts
+        self.num_logical_experts = num_experts
         self.layer_id = layer_id
+        # Redundant experts (EPLB): the router keeps choosing among the logical experts; hot ones own several
+        # physical slots spread over the expert-parallel ranks and tokens are dealt over the replicas
+        # (reference `eplb/expert_location.py`, `layers/gate.py:163`).
+        self.expert_location = None
+        if self.expert_parallel and _RUNTIME.num_redundant > 0:
+            from ..eplb.expert_location import ExpertLocation
+            load = _RUNTIME.expert_load
+            if load is not None and layer_id < len(load) and len(load[layer_id]) == num_experts:
+                self.expert_location = ExpertLocation.from_load(load[layer_id], ep, _RUNTIME.num_redundant)
+            else:
+                self.expert_location = ExpertLocation(num_experts, ep, _RUNTIME.num_redundant)
+            num_experts = self.expert_location.num_physical
+        self.recorder = _RUNTIME.recorder
+        self.num_experts = num_experts
         if self.expert_parallel:
             assert num_experts % self.tp_size == 0
             self.num_local_experts = num_experts // self.tp_size
@@ -92,7 +128,15 @@ class FusedMoE(nn.Module):
                              else torch.full((E, H), 0.02, dtype=torch.float32, device=device))
 
     def weight_loader(self, param, w, shard_id: str, expert_id: int):
-        """`shard_id` in {"gate", "up", "down"}; `w` is the full `[out, in]` tensor of one expert."""
+        """`shard_id` in {"gate", "up", "down"}; `w` is the full `[out, in]` tensor of one (logical) expert."""
+        if self.expert_location is not None:
+            # every physical slot of the logical expert that lives on this rank gets a copy
+            for phys in (self.expert_location.phy2log == expert_id).nonzero()[0].tolist():
+                self._load_slot(param, w, shard_id, int(phys))
+            return
+        self._load_slot(param, w, shard_id, expert_id)
+
+    def _load_slot(self, param, w, shard_id: str, expert_id: int):
         local = expert_id - self.expert_start
         if local < 0 or local >= self.num_local_experts:
             return
@@ -162,6 +206,10 @@ class FusedMoE(nn.Module):
         shared expert's partial output)."""
         if self.routed_experts_capturer is not None:
             self.routed_experts_capturer.capture(self.layer_id, topk_ids)
+        if self.recorder is not None:
+            self.recorder.record(self.layer_id, topk_ids)
+        if self.expert_location is not None:
+            topk_ids = self.expert_location.logical_to_physical(topk_ids)
         if ops.use_native(x) and self.activation == "silu":
             from ..ops import moe_native
             pairs = x.shape[0] * topk_ids.shape[1]

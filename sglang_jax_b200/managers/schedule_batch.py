@@ -326,6 +326,7 @@ class Req:
         self.kv_committed_len = 0
         self.kv_allocated_len = 0
         self.swa_evicted_seqlen = 0
+        self.routed_experts = []       # the re-prefill computes (and records) every token again
         self.input_token_logprobs_val = None if not self.input_logprob_sent else self.input_token_logprobs_val
 
     def offload_kv_cache(self, *a, **k):  # hook used by HiCache / PD
@@ -414,6 +415,7 @@ class ModelWorkerBatch:
     token_ids_logprobs: list | None = None
     return_output_logprob_only: bool = False
     capture_hidden_mode: int = 0
+    return_routed_experts: bool = False      # some request of the batch wants its routed expert ids back
     lora_ids: list | None = None
     num_decode_in_mixed: int = 0     # MIXED: trailing rows that are 1-token decodes
     spec_info: Any = None
@@ -829,6 +831,7 @@ class ScheduleBatch:
             token_ids_logprobs=[r.token_ids_logprob for r in self.reqs] if self.return_logprob else None,
             return_output_logprob_only=all(r.return_output_logprob_only or not r.return_logprob for r in self.reqs),
             capture_hidden_mode=1 if self.return_hidden_states else 0,
+            return_routed_experts=any(r.return_routed_experts for r in self.reqs),
             lora_ids=[r.lora_id for r in self.reqs],
             num_decode_in_mixed=self.num_decode_in_mixed,
             spec_info=self.spec_info, spec_algorithm=self.spec_algorithm,

@@ -22,6 +22,7 @@ class SchedulerOutputProcessorMixin:
     # ------------------------------------------------------------------ prefill
     def process_batch_result_prefill(self, batch: ScheduleBatch, result):
         ids = self.tp_worker.resolve(result).tolist() if result.next_token_ids is not None else []
+        self._collect_routed_experts(batch, result)
         lo = result.logits_output
         n_prefill = len(batch.reqs) - batch.num_decode_in_mixed
         lp_val = lo.next_token_logprobs.tolist() if (lo is not None and lo.next_token_logprobs is not None) else None
@@ -66,9 +67,29 @@ class SchedulerOutputProcessorMixin:
                 self.tree_cache.cache_unfinished_req(req)
         self.stream_output(batch.reqs, batch.return_logprob)
 
+    def _collect_routed_experts(self, batch: ScheduleBatch, result):
+        """Hand every request that asked for them the routed expert ids of the tokens this step computed for it
+        (`[tokens, layers, top_k]` per step; tokens served from the prefix cache were not computed)."""
+        snap = getattr(result, "routed_experts", None)
+        if snap is None:
+            return
+        from ..layers.routed_experts_capturer import RoutedExpertsCapturer
+        if batch.forward_mode.is_extend() and batch.extend_lens:
+            lens = [int(x) for x in batch.extend_lens]
+        else:
+            lens = [1] * len(batch.reqs)
+        spans, o = [], 0
+        for n in lens:
+            spans.append((o, n))
+            o += n
+        for req, arr in zip(batch.reqs, RoutedExpertsCapturer.per_request(snap[0], snap[1], spans)):
+            if req.return_routed_experts and not req.is_retracted and not req.finished():
+                req.routed_experts.extend(arr.tolist())
+
     # ------------------------------------------------------------------ decode
     def process_batch_result_decode(self, batch: ScheduleBatch, result):
         ids = self.tp_worker.resolve(result).tolist()
+        self._collect_routed_experts(batch, result)
         lo = result.logits_output
         lp_val = lo.next_token_logprobs.tolist() if (lo is not None and lo.next_token_logprobs is not None) else None
         self.num_generated_tokens += len(batch.reqs)

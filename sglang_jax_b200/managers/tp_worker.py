@@ -39,6 +39,7 @@ class GenerationBatchResult:
     copy_done: Any = None            # CUDA event: D2H of `next_token_ids_cpu` finished
     next_token_ids_cpu: Any = None
     forward_batch: Any = None
+    routed_experts: Any = None       # (pinned host tensor [layers, tokens, top_k], event) of the capturer
 
 
 class _Control:
@@ -117,6 +118,9 @@ class ModelWorker:
                 self.channel.send(batch)
         out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
         res = GenerationBatchResult(out, ids, bid=batch.bid, forward_batch=fb)
+        cap = getattr(self.model_runner, "routed_capturer", None)
+        if cap is not None and getattr(batch, "return_routed_experts", False):
+            res.routed_experts = cap.snapshot(len(batch.input_ids))
         if ids is not None and self.device.type == "cuda":
             # start the D2H copy right away; the scheduler waits on the event when it needs the ids
             n = ids.numel()

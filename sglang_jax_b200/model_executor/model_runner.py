@@ -56,7 +56,22 @@ class ModelRunner:
         from ..configs.quantization_config import QuantizationConfig
         self.quant_config = QuantizationConfig.resolve(server_args.quantization, server_args.quantization_config_path,
                                                        model_config.hf_config)
+        # expert placement (redundant experts, seeded from recorded load) and the hit-count recorder are fixed
+        # before the routed-expert layers are built
+        from ..layers.moe import configure_moe_runtime
+        self.expert_recorder = None
+        n_exp = int(getattr(model_config.hf_config, "num_experts", None)
+                    or getattr(model_config.hf_config, "n_routed_experts", None)
+                    or getattr(model_config.hf_config, "num_local_experts", None) or 0)
+        if getattr(server_args, "enable_expert_distribution_recorder", False) and n_exp and not is_draft_worker:
+            from ..eplb.expert_location import ExpertDistributionRecorder
+            self.expert_recorder = ExpertDistributionRecorder(
+                model_config.num_hidden_layers, n_exp, server_args.expert_distribution_recorder_buffer_size,
+                server_args.expert_distribution_recorder_output_file, device=self.device)
+        configure_moe_runtime(getattr(server_args, "ep_num_redundant_experts", 0),
+                              getattr(server_args, "init_expert_location", "trivial"), self.expert_recorder)
         self.model = loader.load_model(model_config, self.device, self.quant_config)
+        configure_moe_runtime()          # later models (a draft head) start from the defaults
         self.weight_bytes = sum(p.numel() * p.element_size() for p in self.model.parameters())
         logger.info("model loaded in %.1fs, %.2f GB weights on %s", time.time() - t0,
                     self.weight_bytes / 2 ** 30, self.device)
@@ -73,6 +88,14 @@ class ModelRunner:
             from ..lora.lora_manager import LoRAManager
             self.lora_manager = LoRAManager(self.model, server_args, self.dtype, self.device)
         self._init_fused_comm()
+        self.routed_capturer = None
+        if getattr(server_args, "enable_return_routed_experts", False) and not is_draft_worker:
+            from ..layers.routed_experts_capturer import RoutedExpertsCapturer
+            hf = model_config.hf_config
+            cap_tokens = max(server_args.chunked_prefill_size or 0, server_args.max_prefill_tokens) + \
+                self.max_running_requests
+            self.routed_capturer = RoutedExpertsCapturer.attach(
+                self.model, cap_tokens, self.device, int(getattr(hf, "num_experts_per_tok", None) or 8))
         from ..layers.fused_block import model_supports_fused_residual
         self.fused_residual_ok = model_supports_fused_residual(self.model)
         if self.device.type == "cuda" and not server_args.disable_cuda_graph and not is_draft_worker:
@@ -224,6 +247,8 @@ class ModelRunner:
     def forward(self, batch: ModelWorkerBatch, skip_sample: bool = False):
         """One step: returns `(logits_output, next_token_ids [B] int32 device tensor, forward_batch)`."""
         self.forward_ct += 1
+        if self.expert_recorder is not None:
+            self.expert_recorder.step()
         if batch.forward_mode.is_idle():
             return None, torch.empty(0, dtype=torch.int32, device=self.device), None
         if getattr(batch, "recurrent_copies", None) and self.recurrent_pool is not None:

@@ -82,3 +82,116 @@ def test_data_parallel_replicas_route_and_match_single_engine(tmp_path):
         assert len(eng.get_server_info()["internal_states"]) == 2
     finally:
         eng.shutdown()
+
+
+# ------------------------------------------------------------------------------------------
+# routed-expert capture, hit-count recorder and redundant experts inside a running engine
+def _tiny_moe(tmp_path):
+    import torch
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+    from test_models_cpu import _init, _save
+    cfg = dict(hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, rope_theta=1e6,
+               vocab_size=512, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+               mlp_only_layers=[], tie_word_embeddings=False, max_position_embeddings=512)
+    hf = _init(Qwen3MoeForCausalLM(Qwen3MoeConfig(**cfg)))
+    return hf, _save(str(tmp_path / "moe"), hf, cfg, "Qwen3MoeForCausalLM", "qwen3_moe")
+
+
+def test_engine_returns_routed_experts_and_records_expert_load(tmp_path):
+    import numpy as np
+    import torch
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    hf, path = _tiny_moe(tmp_path)
+    dump = str(tmp_path / "load.npy")
+    prompts = [list(range(5, 40)), [9, 8, 7, 6, 5, 4, 3] * 3]
+    ps.reset_state()
+    eng = Engine(model_path=path, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                 max_total_tokens=4096, enable_single_process=True, enable_return_routed_experts=True,
+                 enable_expert_distribution_recorder=True, expert_distribution_recorder_buffer_size=1,
+                 expert_distribution_recorder_output_file=dump, disable_radix_cache=True)
+    try:
+        outs = eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 4, "temperature": 0,
+                                                                "ignore_eos": True}, return_routed_experts=True)
+        plain = eng.generate(input_ids=prompts[:1], sampling_params={"max_new_tokens": 2, "temperature": 0})
+    finally:
+        eng.shutdown()
+    assert "routed_experts" not in plain[0]["meta_info"] or not plain[0]["meta_info"]["routed_experts"]
+    for ids, o in zip(prompts, outs):
+        got = np.asarray(o["meta_info"]["routed_experts"])          # [tokens, layers, top_k]
+        assert got.shape == (len(ids) + 4 - 1, 2, 2), got.shape
+        # the router's choice for the prompt tokens is the HF model's
+        with torch.no_grad():
+            ref = hf(torch.tensor([ids]), output_router_logits=True).router_logits
+        for layer in range(2):
+            want = torch.topk(ref[layer].float(), 2, dim=-1).indices.sort(-1).values.numpy()
+            assert np.array_equal(np.sort(got[: len(ids), layer], -1), want), layer
+    load = np.load(dump)
+    assert load.shape == (2, 8) and load.sum() >= 2 * 2 * sum(len(p) for p in prompts)
+
+
+def _ep_rank(rank, world, port, path, q, redundant, load_file):
+    import os
+    import sys
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.server_args import ServerArgs
+    torch.set_num_threads(2)
+    ps.init_distributed(rank, world, "cpu", 1, world, init_method=f"tcp://127.0.0.1:{port}", timeout_s=120)
+    sa = ServerArgs(model_path=path, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                    max_total_tokens=4096, enable_single_process=True, tp_size=world, ep_size=world,
+                    ep_num_redundant_experts=redundant, init_expert_location=load_file or "trivial",
+                    log_level="error", watchdog_timeout=0)
+    if rank != 0:
+        from sglang_jax_b200.managers.tp_worker import run_tp_follower
+        run_tp_follower(sa)
+    else:
+        from sglang_jax_b200 import Engine
+        from sglang_jax_b200.layers.moe import FusedMoE
+        eng = Engine(server_args=sa)
+        moes = [m for m in eng.scheduler.tp_worker.model_runner.model.modules() if isinstance(m, FusedMoE)]
+        info = [(m.num_experts, m.num_local_experts, m.expert_location.phy2log.tolist()) for m in moes]
+        outs = eng.generate(input_ids=[list(range(5, 40)), [9, 8, 7, 6, 5, 4, 3] * 5],
+                            sampling_params={"max_new_tokens": 8, "temperature": 0.0, "ignore_eos": True})
+        q.put(([o["output_ids"] for o in outs], info))
+        eng.shutdown()
+    ps.destroy()
+
+
+def test_redundant_experts_keep_outputs_and_follow_recorded_load(tmp_path):
+    """EP2 with two redundant expert slots: replicas hold copies of their logical expert, tokens are dealt over
+    the replicas, outputs equal the single-GPU HF model; a recorded load file steers which experts are doubled."""
+    import numpy as np
+    import torch.multiprocessing as mp
+    from test_models_cpu import _hf_generate
+    from sglang_jax_b200.utils.common import get_free_port
+    hf, path = _tiny_moe(tmp_path)
+    want = _hf_generate(hf, [list(range(5, 40)), [9, 8, 7, 6, 5, 4, 3] * 5], n=8)
+    load = np.ones((2, 8))
+    load[:, 5] = 50
+    load[:, 2] = 30          # experts 5 and 2 are the hot ones
+    load_file = str(tmp_path / "load.npy")
+    np.save(load_file, load)
+    for lf in (None, load_file):
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = get_free_port()
+        procs = [ctx.Process(target=_ep_rank, args=(r, 2, port, path, q, 2, lf)) for r in range(2)]
+        for p in procs:
+            p.start()
+        try:
+            outs, info = q.get(timeout=300)
+        finally:
+            for p in procs:
+                p.join(timeout=60)
+                if p.is_alive():
+                    p.kill()
+        assert outs == want
+        for n_phys, n_local, phy2log in info:
+            assert n_phys == 10 and n_local == 5 and sorted(set(phy2log)) == list(range(8))
+            if lf:
+                assert sorted(phy2log.count(e) for e in (5, 2)) == [2, 2]
