@@ -72,10 +72,15 @@ def row_linear_add_norm(lin, x, residual, norm, consumer=None):
     return norm(y, residual)
 
 
-def partial_add_norm(make_partial, num_tokens: int, hidden: int, residual, norm, tp_size: int):
+def partial_add_norm(make_partial, num_tokens: int, hidden: int, residual, norm, tp_size: int, block=None, x=None):
     """Like `row_linear_add_norm` for a block whose per-rank partial sum is produced by arbitrary
     code (an MoE layer): `make_partial(out_or_None)` must return the `[T, H]` partial, written into
-    `out` when one is given."""
+    `out` when one is given.  With `--moe-backend fused` and a routed-expert `block` that qualifies, the
+    block's input `x` goes through the token all-to-all dataflow instead (`layers/fused_ep_moe.py`)."""
+    if block is not None and x is not None and tp_size > 1:
+        from . import fused_ep_moe
+        if fused_ep_moe.ENABLED and fused_ep_moe.supported(block):
+            return fused_ep_moe.moe_a2a_add_norm(block, x, residual, norm)
     comm = ps.get_state().fused_comm if _FUSED_RESIDUAL else None
     if comm is not None and tp_size > 1 and num_tokens <= comm.max_tokens and hidden == comm.hidden:
         buf = comm.partial_buffer(num_tokens)

@@ -72,6 +72,11 @@ class ModelRunner:
                               getattr(server_args, "init_expert_location", "trivial"), self.expert_recorder)
         self.model = loader.load_model(model_config, self.device, self.quant_config)
         configure_moe_runtime()          # later models (a draft head) start from the defaults
+        if not is_draft_worker:
+            # `--moe-backend fused` / `fused_v2` / `auto`: token all-to-all between the expert-parallel ranks
+            from ..layers import fused_ep_moe
+            fused_ep_moe.ENABLED = server_args.moe_backend in ("fused", "fused_v2") or \
+                (server_args.moe_backend == "auto" and st.ep.size > 1)
         self.weight_bytes = sum(p.numel() * p.element_size() for p in self.model.parameters())
         logger.info("model loaded in %.1fs, %.2f GB weights on %s", time.time() - t0,
                     self.weight_bytes / 2 ** 30, self.device)

@@ -155,7 +155,7 @@ class DeepseekDecoderLayer(nn.Module):
         h, residual = row_linear_add_norm(self.self_attn.o_proj, a, residual, self.post_attention_layernorm)
         if self.is_sparse:
             return partial_add_norm(lambda out: self.mlp.partial(h, out), h.shape[0], h.shape[1], residual, next_norm,
-                                    self.mlp.tp_size)
+                                    self.mlp.tp_size, block=self.mlp, x=h)
         act = self.mlp.act_fn(self.mlp.gate_up_proj(h))
         return row_linear_add_norm(self.mlp.down_proj, act, residual, next_norm)
 

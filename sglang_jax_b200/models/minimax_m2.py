@@ -103,7 +103,7 @@ class MiniMaxM2DecoderLayer(nn.Module):
         a = self.self_attn(h_normed, fb)
         h, residual = row_linear_add_norm(self.self_attn.o_proj, a, residual, self.post_attention_layernorm)
         return partial_add_norm(lambda out: self.mlp.partial(h, out), h.shape[0], h.shape[1], residual, next_norm,
-                                self.mlp.tp_size)
+                                self.mlp.tp_size, block=self.mlp, x=h)
 
 
 class MiniMaxM2Model(DenseModel):

@@ -1,3 +1,4 @@
+import pytest
 import numpy as np
 import torch
 
@@ -131,7 +132,7 @@ def test_engine_returns_routed_experts_and_records_expert_load(tmp_path):
     assert load.shape == (2, 8) and load.sum() >= 2 * 2 * sum(len(p) for p in prompts)
 
 
-def _ep_rank(rank, world, port, path, q, redundant, load_file):
+def _ep_rank(rank, world, port, path, q, redundant, load_file, moe_backend="epmoe"):
     import os
     import sys
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -145,7 +146,7 @@ def _ep_rank(rank, world, port, path, q, redundant, load_file):
     sa = ServerArgs(model_path=path, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
                     max_total_tokens=4096, enable_single_process=True, tp_size=world, ep_size=world,
                     ep_num_redundant_experts=redundant, init_expert_location=load_file or "trivial",
-                    log_level="error", watchdog_timeout=0)
+                    log_level="error", watchdog_timeout=0, moe_backend=moe_backend)
     if rank != 0:
         from sglang_jax_b200.managers.tp_worker import run_tp_follower
         run_tp_follower(sa)
@@ -154,9 +155,12 @@ def _ep_rank(rank, world, port, path, q, redundant, load_file):
         from sglang_jax_b200.layers.moe import FusedMoE
         eng = Engine(server_args=sa)
         moes = [m for m in eng.scheduler.tp_worker.model_runner.model.modules() if isinstance(m, FusedMoE)]
-        info = [(m.num_experts, m.num_local_experts, m.expert_location.phy2log.tolist()) for m in moes]
+        info = [(m.num_experts, m.num_local_experts,
+                 m.expert_location.phy2log.tolist() if m.expert_location is not None else None) for m in moes]
         outs = eng.generate(input_ids=[list(range(5, 40)), [9, 8, 7, 6, 5, 4, 3] * 5],
                             sampling_params={"max_new_tokens": 8, "temperature": 0.0, "ignore_eos": True})
+        from sglang_jax_b200.layers import fused_ep_moe
+        assert (fused_ep_moe.CALLS > 0) == (moe_backend == "fused")
         q.put(([o["output_ids"] for o in outs], info))
         eng.shutdown()
     ps.destroy()
@@ -195,3 +199,29 @@ def test_redundant_experts_keep_outputs_and_follow_recorded_load(tmp_path):
             assert n_phys == 10 and n_local == 5 and sorted(set(phy2log)) == list(range(8))
             if lf:
                 assert sorted(phy2log.count(e) for e in (5, 2)) == [2, 2]
+
+
+@pytest.mark.parametrize("world,redundant", [(2, 0), (4, 0), (2, 2)])
+def test_token_all_to_all_moe_matches_hf(tmp_path, world, redundant):
+    """`--moe-backend fused`: tokens stay sharded over the expert-parallel ranks, (token, expert) rows travel to the
+    expert's rank and back (here through the process group's all-to-all, the oracle of the NVLink kernels)."""
+    import torch.multiprocessing as mp
+    from test_models_cpu import _hf_generate
+    from sglang_jax_b200.utils.common import get_free_port
+    hf, path = _tiny_moe(tmp_path)
+    prompts = [list(range(5, 40)), [9, 8, 7, 6, 5, 4, 3] * 5]
+    want = _hf_generate(hf, prompts, n=8)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = get_free_port()
+    procs = [ctx.Process(target=_ep_rank, args=(r, world, port, path, q, redundant, None, "fused")) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        outs, _ = q.get(timeout=300)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    assert outs == want
