@@ -26,18 +26,22 @@ from ..parallel import state as ps
 
 
 _EXPERT_STORAGE = None
+_EXPERT_BLOCK = None
 
 
 @contextlib.contextmanager
-def expert_storage(dtype):
+def expert_storage(dtype, block_size=None):
     """Experts constructed inside the block store their weights in `dtype` (only `torch.float8_e4m3fn` changes
-    anything) instead of the compute dtype."""
-    global _EXPERT_STORAGE
-    prev, _EXPERT_STORAGE = _EXPERT_STORAGE, dtype
+    anything) instead of the compute dtype; `block_size == (128, 128)` selects block scales (the DeepSeek-V3
+    format) instead of per-output-channel ones."""
+    global _EXPERT_STORAGE, _EXPERT_BLOCK
+    prev = _EXPERT_STORAGE, _EXPERT_BLOCK
+    _EXPERT_STORAGE = dtype
+    _EXPERT_BLOCK = tuple(block_size) if block_size else None
     try:
         yield
     finally:
-        _EXPERT_STORAGE = prev
+        _EXPERT_STORAGE, _EXPERT_BLOCK = prev
 
 
 class MoeRuntime:
@@ -105,6 +109,10 @@ class FusedMoE(nn.Module):
         # e4m3 storage from the start (set by the loader for W8A8 per-channel recipes): the bf16 experts of a large
         # model never exist on the device; each expert is quantised as its checkpoint tensor arrives
         self.fp8 = (_EXPERT_STORAGE == torch.float8_e4m3fn and self._fp8_capable(dtype, activation, hidden_size, I))
+        # 128 x 128 block scales need whole blocks per expert matrix
+        self.fp8_block = bool(self.fp8 and _EXPERT_BLOCK == (128, 128) and hidden_size % 128 == 0 and I % 128 == 0)
+        if self.fp8 and _EXPERT_BLOCK and not self.fp8_block:
+            self.fp8 = False
         store = torch.float8_e4m3fn if self.fp8 else dtype
         self.w13_weight = nn.Parameter(torch.empty(self.num_local_experts, 2 * I, hidden_size, dtype=store),
                                        requires_grad=False)
@@ -122,10 +130,14 @@ class FusedMoE(nn.Module):
         """Per-expert, per-output-channel fp32 scales (buffers: they follow the module across devices and are
         not checkpoint parameters).  The default 0.02 gives dummy-initialised e4m3 values the usual weight scale."""
         E, I2, H = self.w13_weight.shape
+        if getattr(self, "fp8_block", False):
+            s13, s2 = (E, I2 // 128, H // 128), (E, H // 128, I2 // 2 // 128)
+        else:
+            s13, s2 = (E, I2), (E, H)
         self.register_buffer("w13_scale", w13_scale if w13_scale is not None
-                             else torch.full((E, I2), 0.02, dtype=torch.float32, device=device))
+                             else torch.full(s13, 0.02, dtype=torch.float32, device=device))
         self.register_buffer("w2_scale", w2_scale if w2_scale is not None
-                             else torch.full((E, H), 0.02, dtype=torch.float32, device=device))
+                             else torch.full(s2, 0.02, dtype=torch.float32, device=device))
 
     def weight_loader(self, param, w, shard_id: str, expert_id: int):
         """`shard_id` in {"gate", "up", "down"}; `w` is the full `[out, in]` tensor of one (logical) expert."""
@@ -148,7 +160,13 @@ class FusedMoE(nn.Module):
             src = w if self.expert_parallel or self.tp_size == 1 else w.narrow(1, self.tp_rank * I, I)
             row0 = 0
         dst = param.data[local].narrow(0, row0, src.shape[0])
-        if self.fp8:
+        if self.fp8_block:
+            from ..utils.quantization import quantize_tensor
+            q, sc = quantize_tensor(src.to(dst.device), torch.float8_e4m3fn, "block", (128, 128))
+            dst.copy_(q)
+            scale = self.w2_scale if shard_id == "down" else self.w13_scale
+            scale[local].narrow(0, row0 // 128, sc.shape[0]).copy_(sc)
+        elif self.fp8:
             from ..utils.quantization import quantize_tensor
             q, sc = quantize_tensor(src.to(dst.device), torch.float8_e4m3fn, "per_channel")
             dst.copy_(q)
@@ -172,7 +190,27 @@ class FusedMoE(nn.Module):
         E, I2, H = self.w13_weight.shape
         fp8_storage = (dtype == torch.float8_e4m3fn and activation_dtype == torch.float8_e4m3fn and not block_size
                        and self._fp8_capable(self.w13_weight.dtype, self.activation, H, I2 // 2))
-        if fp8_storage:
+        block_storage = (dtype == torch.float8_e4m3fn and activation_dtype in (torch.float8_e4m3fn, None)
+                         and tuple(block_size or ()) == (128, 128) and H % 128 == 0 and (I2 // 2) % 128 == 0
+                         and self._fp8_capable(self.w13_weight.dtype, self.activation, H, I2 // 2))
+        if block_storage:
+            # real block-scaled fp8 storage: the bf16 tensors are released, the forward runs the grouped
+            # block-scaled tensor-core GEMM with per-token-group-128 activation scales
+            scales = {}
+            for name in ("w13", "w2"):
+                p = getattr(self, f"{name}_weight")
+                q = torch.empty(p.shape, dtype=dtype, device=p.device)
+                sc = torch.empty((p.shape[0], p.shape[1] // 128, p.shape[2] // 128), dtype=torch.float32,
+                                 device=p.device)
+                for e in range(p.shape[0]):
+                    qe, se = quantize_tensor(p.data[e], dtype, "block", (128, 128))
+                    q[e].copy_(qe)
+                    sc[e].copy_(se)
+                setattr(self, f"{name}_weight", nn.Parameter(q, requires_grad=False))
+                scales[name] = sc
+            self.fp8 = self.fp8_block = True
+            self._register_scales(self.w13_weight.device, scales["w13"], scales["w2"])
+        elif fp8_storage:
             scales = {}
             for name in ("w13", "w2"):
                 p = getattr(self, f"{name}_weight")
@@ -197,6 +235,10 @@ class FusedMoE(nn.Module):
         """Expert weights in the compute dtype (de-quantised on the fly under fp8 storage)."""
         if not self.fp8:
             return self.w13_weight, self.w2_weight
+        if self.fp8_block:
+            def deq(w, s):
+                return (w.float() * s.repeat_interleave(128, 1).repeat_interleave(128, 2)).to(self.dtype)
+            return deq(self.w13_weight, self.w13_scale), deq(self.w2_weight, self.w2_scale)
         return ((self.w13_weight.float() * self.w13_scale[..., None]).to(self.dtype),
                 (self.w2_weight.float() * self.w2_scale[..., None]).to(self.dtype))
 
@@ -215,6 +257,10 @@ class FusedMoE(nn.Module):
             pairs = x.shape[0] * topk_ids.shape[1]
             if self.workspace is None or self.workspace.max_pairs < pairs:
                 self.workspace = moe_native.MoeWorkspace(max(pairs, 2048), self.num_local_experts, x.device)
+            if self.fp8_block:
+                return moe_native.fused_experts_fp8_block(x, self.w13_weight, self.w13_scale, self.w2_weight,
+                                                          self.w2_scale, topk_weights, topk_ids, self.expert_start,
+                                                          self.workspace, add, out)
             if self.fp8:
                 return moe_native.fused_experts_fp8(x, self.w13_weight, self.w13_scale, self.w2_weight, self.w2_scale,
                                                     topk_weights, topk_ids, self.expert_start, self.workspace, add,
@@ -246,9 +292,25 @@ def _fp8_reference_experts(x, moe: "FusedMoE", topk_weights, topk_ids):
     T, H = x.shape
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
     I = moe.local_intermediate
+    block = getattr(moe, "fp8_block", False)
+
+    def expand(s):
+        return s.repeat_interleave(128, 0).repeat_interleave(128, 1)
+
     for e in range(moe.num_local_experts):
         tok, slot = (topk_ids == e + moe.expert_start).nonzero(as_tuple=True)
         if tok.numel() == 0:
+            continue
+        if block:
+            # per-token-group-128 activation scales, 128 x 128 weight block scales
+            xq, sx = quantize_activation(x[tok], torch.float8_e4m3fn, 128)
+            xd = xq.float() * sx.repeat_interleave(128, 1)
+            h = (xd @ (moe.w13_weight[e].float() * expand(moe.w13_scale[e])).t()).to(x.dtype).float()
+            a = (torch.nn.functional.silu(h[:, :I]) * h[:, I:]).to(x.dtype)
+            aq, sa = quantize_activation(a, torch.float8_e4m3fn, 128)
+            ad = aq.float() * sa.repeat_interleave(128, 1)
+            y = (ad @ (moe.w2_weight[e].float() * expand(moe.w2_scale[e])).t()).to(x.dtype).float()
+            out.index_add_(0, tok, y * topk_weights[tok, slot].float()[:, None])
             continue
         xq, sx = quantize_activation(x[tok], torch.float8_e4m3fn)
         h = (xq.float() @ moe.w13_weight[e].float().t()) * sx * moe.w13_scale[e][None, :]

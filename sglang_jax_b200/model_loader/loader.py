@@ -80,15 +80,24 @@ def _expert_storage_for(quant_config):
     bf16 experts would not fit on the device can still be loaded (each expert is quantised as it arrives)."""
     from ..layers.moe import expert_storage
     fp8 = torch.float8_e4m3fn
-    native = (quant_config is not None and not quant_config.is_static_checkpoint
-              and quant_config.moe_weight_dtype == fp8 and quant_config.moe_activation_dtype == fp8
-              and not quant_config.moe_weight_block_size)
-    return expert_storage(fp8 if native else None)
+    if quant_config is None or quant_config.moe_weight_dtype != fp8:
+        return expert_storage(None)
+    block = tuple(quant_config.moe_weight_block_size or ()) or None
+    if quant_config.is_static_checkpoint:
+        # block-scaled fp8 release checkpoints (DeepSeek-V3): the experts stay e4m3 with their 128 x 128 scales
+        return expert_storage(fp8 if block == (128, 128) else None, block)
+    if quant_config.moe_activation_dtype != fp8 or (block and block != (128, 128)):
+        return expert_storage(None)
+    return expert_storage(fp8, block)
 
 
 def _apply_dynamic_quantization(model, quant_config):
-    """Dynamic recipes quantise the loaded (or dummy-initialised) bf16 weights in place."""
-    if quant_config is None or quant_config.is_static_checkpoint:
+    """Dynamic recipes quantise the loaded (or dummy-initialised) bf16 weights in place.  Static 128 x 128
+    block-scaled fp8 checkpoints take the same pass: their tensors arrive de-quantised from the iterator and are
+    put back on the checkpoint's own block grid, so the dense projections end up in fp8 storage as well."""
+    if quant_config is None:
+        return
+    if quant_config.is_static_checkpoint and tuple(getattr(quant_config, "weight_block_size", None) or ()) != (128, 128):
         return
     from ..utils.quantization import apply_linear_quantization, apply_moe_quantization
     n = apply_linear_quantization(model, quant_config) + apply_moe_quantization(model, quant_config)
@@ -138,9 +147,11 @@ class DummyModelLoader:
 
 def dequant_static_fp8(weights, block_size=None):
     """Static block-FP8 checkpoints (DeepSeek-V3 release format) ship `X.weight` in float8_e4m3fn
-    next to `X.weight_scale_inv` ([ceil(N/128), ceil(K/128)] fp32).  The pair is folded into one
-    bf16 tensor while streaming, whatever order the two arrive in; everything else passes
-    through.  (The matmuls then run on the bf16 tcgen05 kernel.)"""
+    next to `X.weight_scale_inv` ([ceil(N/128), ceil(K/128)] fp32).  The pair is multiplied out into one
+    fp32 tensor while streaming, whatever order the two arrive in; everything else passes through.  The
+    layers' loaders shard that tensor like any other weight, and for the 128 x 128 format the quantisation pass
+    after loading puts it back on the checkpoint's own block grid in e4m3 storage (in a bf16 model the detour
+    through the bf16 parameter leaves the e4m3 values unchanged and moves a block's scale by at most 2^-9)."""
     from ..utils.quantization import dequantize_tensor
     bs = tuple(block_size) if block_size else (128, 128)
     pend_w: dict[str, torch.Tensor] = {}
@@ -164,14 +175,14 @@ def dequant_static_fp8(weights, block_size=None):
             continue
         yield name, w
     for name, w in pend_w.items():      # fp8 tensors without a scale: plain cast
-        yield name, w.to(torch.bfloat16)
+        yield name, w.to(torch.float32)
 
 
 def _fold(w, scale, bs, inv, dequantize_tensor):
     # both `weight_scale_inv` (DeepSeek) and `weight_scale` hold the multiplier that restores the weight
     if scale.dim() == 1 and scale.numel() == w.shape[0]:
         scale = scale.view(-1, 1)
-    return dequantize_tensor(w, scale.float(), bs, torch.bfloat16)
+    return dequantize_tensor(w, scale.float(), bs, torch.float32)
 
 
 def check_all_loaded(model, loaded):

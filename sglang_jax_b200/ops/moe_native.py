@@ -131,6 +131,44 @@ def fused_experts_fp8(x, w13_q, w13_scale, w2_q, w2_scale, topk_weights, topk_id
     return moe_combine(y, topk_weights, ws, T, add=add, out=out)
 
 
+def grouped_gemm_fp8_block(xq_sorted, sx, wq, sw, ws: MoeWorkspace, rows: int):
+    """Block-scaled e4m3 grouped GEMM: `xq_sorted [rows, K]` with group scales `sx [K/128, >=rows]`, `wq [E, N, K]`
+    with `sw [E, N/128, K/128]` -> bf16 `[rows, N]` (`csrc/gemm_fp8_block.cu`)."""
+    E, N, K = wq.shape
+    out = torch.empty((rows, N), dtype=torch.bfloat16, device=xq_sorted.device)
+    L = _lib()
+    L.sglb_grouped_gemm_fp8_block.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    rc = L.sglb_grouped_gemm_fp8_block(xq_sorted.data_ptr(), wq.data_ptr(), sx.data_ptr(), sx.shape[1], sw.data_ptr(),
+                                       out.data_ptr(), ws.offsets.data_ptr(), ws.tile_group.data_ptr(),
+                                       ws.tile_row0.data_ptr(), ws.counts.data_ptr() + 4, rows, N, K, E,
+                                       native._stream())
+    native._check(rc, "grouped_gemm_fp8_block")
+    return out
+
+
+def fused_experts_fp8_block(x, w13_q, w13_scale, w2_q, w2_scale, topk_weights, topk_ids, expert_start: int = 0,
+                            ws: MoeWorkspace | None = None, add=None, out=None):
+    """Routed-expert FFN on 128 x 128 block-scaled e4m3 weights (DeepSeek-V3 format) with per-token-group-128
+    activation scales: align -> gather -> group quantise -> grouped block GEMM (gate|up) -> SiLU*mul -> group
+    quantise -> grouped block GEMM (down) -> weighted combine."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E_local = w13_q.shape[0]
+    pairs = T * k
+    if ws is None or ws.max_pairs < pairs:
+        ws = MoeWorkspace(pairs, E_local, x.device)
+    moe_align(topk_ids, expert_start, E_local, ws)
+    xs = moe_gather(x, ws, pairs)
+    valid = ws.counts[0:1]
+    xq, sx = native.quant_fp8_group128(xs, valid_rows=valid)
+    h = grouped_gemm_fp8_block(xq, sx, w13_q, w13_scale, ws, pairs)
+    a = native.silu_and_mul(h)
+    aq, sa = native.quant_fp8_group128(a, valid_rows=valid)
+    y = grouped_gemm_fp8_block(aq, sa, w2_q, w2_scale, ws, pairs)
+    return moe_combine(y, topk_weights, ws, T, add=add, out=out)
+
+
 def moe_combine(y_sorted, topk_weights, ws: MoeWorkspace, T: int, add=None, out=None):
     k = topk_weights.shape[1]
     H = y_sorted.shape[1]

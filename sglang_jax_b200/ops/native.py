@@ -359,6 +359,47 @@ def quant_fp8_rows(x, gated: bool = False, valid_rows=None):
     return q, s
 
 
+def quant_fp8_group128(x, valid_rows=None):
+    """Per-token-group (1 x 128) dynamic e4m3 quantisation of `x [T, K]` bf16 (K a multiple of 128) ->
+    `(q [T, K], scale [K / 128, T])`: the activation format of 128 x 128 block-scaled weights."""
+    assert x.dtype == torch.bfloat16 and x.shape[-1] % 128 == 0
+    x = x.contiguous()
+    K = x.shape[-1]
+    T = x.numel() // K
+    q = torch.empty((T, K), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((K // 128, max(T, 1)), dtype=torch.float32, device=x.device)
+    L = lib()
+    L.sglb_quant_fp8_group128.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+    _check(L.sglb_quant_fp8_group128(_p(x), _p(q), _p(s), T, K, max(T, 1),
+                                     valid_rows.data_ptr() if valid_rows is not None else None, _stream()),
+           "quant_fp8_group128")
+    return q, s
+
+
+def gemm_fp8_block_supported(wq, scale_w, block_size) -> bool:
+    return (wq.dtype == torch.float8_e4m3fn and tuple(block_size or ()) == (128, 128) and wq.dim() == 2
+            and wq.shape[1] % 128 == 0 and wq.shape[0] % 8 == 0 and wq.is_contiguous() and wq.data_ptr() % 16 == 0
+            and tuple(scale_w.shape) == ((wq.shape[0] + 127) // 128, wq.shape[1] // 128))
+
+
+def gemm_fp8_block(xq, sx, wq, sw, bias=None):
+    """Block-scaled e4m3 product (DeepSeek-V3 format): `xq [M, K]` with group scales `sx [K/128, >=M]`, `wq [N, K]`
+    with block scales `sw [ceil(N/128), K/128]` -> bf16 `[M, N]`; every 128-wide K block is promoted with its two
+    scales into fp32 accumulators (`csrc/gemm_fp8_block.cu`)."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
+    if M == 0:
+        return out
+    L = lib()
+    L.sglb_gemm_fp8_block.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                      c_int, c_void_p]
+    sw = sw.float().contiguous()
+    _check(L.sglb_gemm_fp8_block(_p(xq), _p(wq), _p(sx), sx.shape[1], _p(sw), _p(bias), _p(out), M, N, K, _stream()),
+           "gemm_fp8_block")
+    return out
+
+
 def gemm_fp8_supported(xq, wq) -> bool:
     return (xq.dtype == torch.float8_e4m3fn and wq.dtype == torch.float8_e4m3fn and xq.shape[-1] % 16 == 0
             and wq.shape[0] % 8 == 0 and wq.is_contiguous() and wq.data_ptr() % 16 == 0)

@@ -106,6 +106,17 @@ class QuantizedWeight(nn.Module):
                     xq, xs = quantize_activation(x2, self.act_dtype, None)
                 y = native.gemm_fp8(xq, self.qweight, xs, self.scale, bias)
                 return y.view(*x.shape[:-1], self.qweight.shape[0])
+        if (self.qweight.dtype == torch.float8_e4m3fn and self.block_size is not None and x.is_cuda
+                and self.act_dtype in (torch.float8_e4m3fn, None) and self.out_dtype == torch.bfloat16
+                and x.dtype == torch.bfloat16 and not ops._FORCE_REFERENCE):
+            # 128 x 128 block-scaled weights (DeepSeek-V3 format) with per-token-group-128 activation scales:
+            # the fp8 weights stay fp8 and every K block is promoted with its scales inside the GEMM
+            native = ops._native()
+            if native.gemm_fp8_block_supported(self.qweight, self.scale, self.block_size):
+                x2 = x.reshape(-1, x.shape[-1])
+                xq, xs = native.quant_fp8_group128(x2)
+                y = native.gemm_fp8_block(xq, xs, self.qweight, self.scale, bias)
+                return y.view(*x.shape[:-1], self.qweight.shape[0])
         if self.act_dtype is not None and self.act_dtype in _QMAX:
             xq, xs = quantize_activation(x.reshape(-1, x.shape[-1]), self.act_dtype,
                                          self.block_size[1] if self.block_size else None)

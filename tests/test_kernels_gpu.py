@@ -654,3 +654,53 @@ def test_fused_two_kernel_path_and_gathers_loopback(native):
     assert torch.equal(comm.logits_gather(lb), lb)
     torch.cuda.synchronize()
     native.check_status()
+
+
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (100, 384, 1024), (128, 7168, 2048), (300, 2048, 7168), (1000, 1536, 512)])
+def test_gemm_fp8_block_scaled(native, M, N, K):
+    """128 x 128 block-scaled weights x per-token-group-128 activations against the fp32 product of the very
+    same quantised operands."""
+    from sglang_jax_b200.utils.quantization import dequantize_tensor, quantize_tensor
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = (torch.randn(M, K, device="cuda", generator=g) * torch.rand(M, 1, device="cuda", generator=g) * 3).to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    w[: N // 2] *= 7.0                     # very different block magnitudes
+    wq, sw = quantize_tensor(w, torch.float8_e4m3fn, "block", (128, 128))
+    xq, sx = native.quant_fp8_group128(x)
+    assert native.gemm_fp8_block_supported(wq, sw, (128, 128))
+    # the quantiser: scales are amax / 448 per (token, 128 group) and the values round-trip
+    xg = x.float().view(M, K // 128, 128)
+    want_s = (xg.abs().amax(-1) / 448.0).clamp_min(1e-12).t()
+    assert torch.allclose(sx[:, :M], want_s, rtol=1e-5, atol=0)
+    xd = (xq.float().view(M, K // 128, 128) * sx[:, :M].t()[..., None]).view(M, K)
+    assert (xd - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+    y = native.gemm_fp8_block(xq, sx, wq, sw)
+    want = xd @ dequantize_tensor(wq, sw, (128, 128), torch.float32).t()
+    torch.cuda.synchronize()
+    native.check_status()
+    _close(y, want, atol=0.02 * want.abs().max().item(), rtol=0.02)
+
+
+@pytest.mark.parametrize("T,E,E_local,e0,k,H,I", [(5, 8, 8, 0, 2, 256, 128), (128, 16, 4, 8, 4, 512, 256),
+                                                  (700, 8, 8, 0, 2, 1024, 384)])
+def test_fused_experts_fp8_block_scaled(native, T, E, E_local, e0, k, H, I):
+    """Expert FFN on 128 x 128 block-scaled e4m3 weights with per-token-group-128 activation scales (grouped
+    block-scaled tcgen05 GEMM) vs the PyTorch statement on the same quantised weights."""
+    from sglang_jax_b200.layers.moe import FusedMoE, _fp8_reference_experts
+    moe = FusedMoE(E, H, I, tp_size=E // E_local, tp_rank=e0 // E_local, ep_size=E // E_local).cuda()
+    moe.w13_weight.data.copy_(_bf16(E_local, 2 * I, H, scale=0.05, seed=61))
+    moe.w2_weight.data.copy_(_bf16(E_local, H, I, scale=0.05, seed=62))
+    x = _bf16(T, H, seed=60)
+    logits = torch.randn(T, E, device="cuda", generator=torch.Generator(device="cuda").manual_seed(63))
+    tw, ids = ref.topk_route(logits, k)
+    full = ref.moe_forward(x.float(), moe.w13_weight.float(), moe.w2_weight.float(), tw, ids, e0)
+    moe.quantize_(torch.float8_e4m3fn, (128, 128), torch.float8_e4m3fn)
+    assert moe.fp8_block and moe.w13_weight.dtype == torch.float8_e4m3fn
+    assert moe.w13_scale.shape == (E_local, 2 * I // 128, H // 128) and moe.w2_scale.shape == (E_local, H // 128, I // 128)
+    got = moe(x, tw, ids)
+    torch.cuda.synchronize()
+    native.check_status()
+    want = _fp8_reference_experts(x, moe, tw, ids)
+    assert ((got.float() - want.float()).norm() / want.float().norm()).item() < 0.03
+    assert ((got.float() - full).norm() / full.norm()).item() < 0.1

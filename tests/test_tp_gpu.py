@@ -17,13 +17,13 @@ def _need2():
         pytest.skip("needs 2 GPUs")
 
 
-def _spawn(fn, world=2, timeout=600, args=()):
+def _spawn(fn, world=2, timeout=600, args=(), ep=False):
     import torch.multiprocessing as mp
     from sglang_jax_b200.utils.common import get_free_port
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = get_free_port()
-    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args, ep)) for r in range(world)]
     for p in procs:
         p.start()
     results = {}
@@ -42,15 +42,15 @@ def _spawn(fn, world=2, timeout=600, args=()):
     return results
 
 
-def _entry(fn, rank, world, port, q, args):
+def _entry(fn, rank, world, port, q, args, ep=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     sys.path.insert(0, ROOT)
     try:
         from sglang_jax_b200.parallel import state as ps
-        ps.init_distributed(rank, world, "cuda", init_method=f"tcp://127.0.0.1:{port}", local_rank=rank,
-                            timeout_s=120)
+        ps.init_distributed(rank, world, "cuda", 1, world if ep else 1, init_method=f"tcp://127.0.0.1:{port}",
+                            local_rank=rank, timeout_s=120)
         out = fn(rank, world, *args)
         q.put((rank, out))
         ps.destroy()
@@ -270,3 +270,64 @@ def test_bounded_wait_reports_absent_peer():
     res = _spawn(_absent_peer)
     raised, ok, waited = res[0]
     assert raised and ok and 1.0 < waited < 30.0
+
+
+# ------------------------------------------------------------------------------------------
+def _moe_ckpt(path):
+    """A small Qwen3-MoE checkpoint (8 experts, top-2) whose shapes the native kernels accept."""
+    import json
+    from safetensors.torch import save_file
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+    cfg = dict(hidden_size=512, intermediate_size=1024, moe_intermediate_size=256, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
+               vocab_size=1024, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+               mlp_only_layers=[], tie_word_embeddings=False, max_position_embeddings=2048)
+    torch.manual_seed(0)
+    hf = Qwen3MoeForCausalLM(Qwen3MoeConfig(**cfg))
+    for p in hf.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.05)
+    os.makedirs(path, exist_ok=True)
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+              os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(dict(cfg, architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", torch_dtype="bfloat16"), f)
+    return path
+
+
+def _moe_engine(rank, world, backend, fused):
+    from sglang_jax_b200.server_args import ServerArgs
+    path = _moe_ckpt(f"/tmp/sglb200_moe_test_{rank}")
+    sa = ServerArgs(model_path=path, device="cuda", dtype="bfloat16", page_size=16, skip_tokenizer_init=True,
+                    max_total_tokens=8192, max_running_requests=8, enable_single_process=True, tp_size=world,
+                    ep_size=world, moe_backend=backend, cuda_graph_max_bs=8, disable_fused_comm=not fused,
+                    log_level="error", watchdog_timeout=0, chunked_prefill_size=256, max_prefill_tokens=512)
+    if rank != 0:
+        from sglang_jax_b200.managers.tp_worker import run_tp_follower
+        run_tp_follower(sa)
+        return "follower done"
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.layers import fused_ep_moe
+    from sglang_jax_b200.ops import native
+    eng = Engine(server_args=sa)
+    try:
+        prompts = [list(range(1, 50)), list(range(3, 200)), [7, 900, 33, 512, 5] * 4, list(range(100, 420))]
+        sp = {"max_new_tokens": 10, "temperature": 0.0, "ignore_eos": True}
+        outs = eng.generate(input_ids=prompts, sampling_params=sp)
+        lp = eng.generate(input_ids=prompts, sampling_params=dict(sp, max_new_tokens=2), return_logprob=True,
+                          top_logprobs_num=5)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert (fused_ep_moe.CALLS > 0) == (backend == "fused")
+        tops = [[(t[1], t[0]) for t in o["meta_info"]["output_top_logprobs"][0]] for o in lp]
+        return [o["output_ids"] for o in outs], tops
+    finally:
+        eng.shutdown()
+
+
+def test_engine_ep2_token_all_to_all_matches_replicated_experts():
+    """The NVLink dispatch / combine kernels (`--moe-backend fused`) against the replicate-all-tokens expert
+    path on library collectives."""
+    _need2()
+    _check_engines_agree(_spawn(_moe_engine, args=("fused", True), ep=True)[0],
+                         _spawn(_moe_engine, args=("epmoe", False), ep=True)[0])
