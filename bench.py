@@ -237,6 +237,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _leave(world: int):
+    """End a rank of a multi-rank run without tearing the communicators down: with captured CUDA graphs that
+    hold library collectives still alive, the teardown can wait forever for a peer that has already gone."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if world > 1:
+        os._exit(0)
+
+
 def percentile(xs, q):
     if not xs:
         return None
@@ -312,7 +321,7 @@ def main():
         from sglang_jax_b200.managers.tp_worker import run_tp_follower
         run_tp_follower(sa, on_message=arm)
         faulthandler.cancel_dump_traceback_later()
-        ps.destroy()
+        _leave(world)
         return 0
 
     from sglang_jax_b200 import Engine
@@ -348,16 +357,11 @@ def main():
     runner = getattr(worker, "model_runner", None)
     clocks = ClockSampler(local_rank)
 
-    def live_count(s) -> int:
-        live = sum(1 for r in s.running_batch.reqs if not r.finished()) + len(s.waiting_queue) + \
-            (1 if s.chunked_req is not None else 0)
-        if s.last_batch is not None and s.last_batch.forward_mode is not None and s.last_batch.forward_mode.is_extend():
-            live += sum(1 for r in s.last_batch.reqs if r not in s.running_batch.reqs and r is not s.chunked_req
-                        and not r.finished())
-        return live
+    finished: set = set()              # ids of requests seen finished
 
     def top_up(s):
-        live = live_count(s)
+        # requests in flight = submitted (some may still sit in the scheduler's input queue) - finished
+        live = state["submitted"] - len(finished)
         while live < C and state["phase"] != "done":
             i = state["submitted"]
             s._recv_q.put(new_request(i, None if i >= C else -(-(i + 1) * L // C)))
@@ -372,11 +376,14 @@ def main():
     def hook(s, batch):
         if state["phase"] == "done":
             return
-        top_up(s)
         if batch is None:
+            top_up(s)
             return
         for r in batch.reqs:
             seen[r.rid] = len(r.output_ids)
+            if r.finished():
+                finished.add(r.rid)
+        top_up(s)
         arm()
         if state["phase"] == "fill":
             state["fill_steps"] += 1
@@ -562,7 +569,7 @@ def main():
     faulthandler.cancel_dump_traceback_later()
     print(json.dumps(out), flush=True)
     engine.shutdown()
-    ps.destroy()
+    _leave(world)
     return 0
 
 

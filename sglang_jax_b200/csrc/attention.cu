@@ -561,6 +561,344 @@ paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Prefill attention on the 5th-generation tensor cores (head_dim 128, causal, bf16).
+//
+// One CTA per (128-row query tile of one sequence, query head).  Warp 0 drives TMA (Q tile once, then
+// 128-token K/V tiles gathered page by page into a two-stage ring), warp 1 issues tcgen05.mma, warps 2..5
+// (one thread per query row) do the softmax:
+//
+//   S_j = Q K_j^T            128 x 128 x 128, accumulator in tensor memory (two S buffers, so S_{j+1}
+//                            is computed while the softmax of S_j runs)
+//   P_j = exp2(S_j - m)      read with tcgen05.ld, written as bf16 into a 128-byte-swizzled smem tile
+//   O  += P_j V_j            128 x 128 x 128, accumulator stays in tensor memory for the whole row of tiles
+//
+// The running maximum is only raised when it grows by more than 2^8: then the softmax threads wait for
+// the P V product in flight, multiply O (tcgen05.ld / tcgen05.st) and the row sums by the correction
+// factor, and carry on; between such events O is never touched by the CUDA cores.  K is the K-major B
+// operand of the first product; V, laid out [token][dim] by the same TMA gathers, is the MN-major B
+// operand of the second.  All waits are bounded; a timeout unwinds through the normal teardown.
+// Reference contract: python/sgl_jax/srt/kernels/ragged_paged_attention/ragged_paged_attention_v3.py:1667.
+// ---------------------------------------------------------------------------------------------
+namespace tc {
+constexpr int BQ2 = 128, BKV = 128, HD = 128;
+constexpr int kBlk = 128 * 128;                    // bytes of one [128 rows][64 bf16] swizzled block
+constexpr int kQBytes = 2 * kBlk;
+constexpr int kKVStage = 4 * kBlk;                 // K (2 blocks by dim half) + V (2 blocks by dim half)
+constexpr int kStagesKV = 2;
+constexpr int kPBytes = 2 * kBlk;
+constexpr int kSmem = kQBytes + kStagesKV * kKVStage + kPBytes + 256 + 1024;
+constexpr int kThreadsTc = 192;
+constexpr float kRescale = 8.f;                    // raise the running max only past 2^8
+
+struct Bars {
+  uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_free[2], p_ready, pv_done;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+}  // namespace tc
+
+__global__ void __launch_bounds__(tc::kThreadsTc, 1)
+paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_q,
+                       const AttnParams p) {
+  using namespace tc;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = smem + kQBytes;
+  uint8_t* p_s = kv_s + kStagesKV * kKVStage;
+  Bars* bars = reinterpret_cast<Bars*>(p_s + kPBytes);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  // (sequence, 128-row query tile) of this CTA
+  int b = 0, tile_in_seq = 0;
+  {
+    int acc = 0;
+    const int want = blockIdx.x;
+    bool found = false;
+    for (int i = 0; i < p.B; ++i) {
+      const int n = p.cu_q_lens[i + 1] - p.cu_q_lens[i];
+      const int nt = (n + BQ2 - 1) / BQ2;
+      if (want < acc + nt) {
+        b = i;
+        tile_in_seq = want - acc;
+        found = true;
+        break;
+      }
+      acc += nt;
+    }
+    if (!found) return;
+  }
+  const int hq = blockIdx.y;
+  const int kvh = hq / (p.Hq / p.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_begin = p.cu_q_lens[b];
+  const int q_len = p.cu_q_lens[b + 1] - q_begin;
+  const int prefix = p.prefix_lens[b];
+  const int seq = p.seq_lens[b];
+  const int q0 = tile_in_seq * BQ2;
+  const int q_hi = min(q0 + BQ2, q_len);
+  const int kv_end = p.bidirectional ? seq : min(seq, prefix + q_hi);
+  const int n_tiles = (kv_end + BKV - 1) / BKV;
+  const int* pt_row = p.page_table + static_cast<size_t>(p.req_pool_indices[b]) * p.max_pages;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_kv);
+    prefetch_tmap(&tmap_q);
+    mbar_init(smem_u32(&bars->q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars->kv_full[i]), 1);
+      mbar_init(smem_u32(&bars->kv_empty[i]), 1);
+      mbar_init(smem_u32(&bars->s_full[i]), 1);
+      mbar_init(smem_u32(&bars->s_free[i]), 128);
+    }
+    mbar_init(smem_u32(&bars->p_ready), 128);
+    mbar_init(smem_u32(&bars->pv_done), 1);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&bars->tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;          // S buffers at columns 0 and 128, O at 256
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t qb = smem_u32(&bars->q_full);
+      mbar_expect_tx(qb, kQBytes);
+      tma_load_2d(smem_u32(q_s), &tmap_q, qb, hq * HD, q_begin + q0);
+      tma_load_2d(smem_u32(q_s + kBlk), &tmap_q, qb, hq * HD + 64, q_begin + q0);
+      const int run = p.page_size < 64 ? p.page_size : 64;       // tokens per TMA box
+      const int n_runs = BKV / run;
+      for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(smem_u32(&bars->kv_empty[st]), ((j >> 1) & 1) ^ 1)) {
+          report(p.status, kTimeoutEmptyBarrier, b, j);
+          *abort_flag = 1;
+          break;
+        }
+        const uint32_t fb = smem_u32(&bars->kv_full[st]);
+        mbar_expect_tx(fb, kKVStage);
+        const uint32_t base = smem_u32(kv_s + st * kKVStage);
+        for (int r = 0; r < n_runs; ++r) {
+          const int tok = j * BKV + r * run;
+          int pg = tok / p.page_size;
+          if (pg >= p.max_pages) pg = p.max_pages - 1;
+          const int page = pt_row[pg];
+          const int off = tok - (tok / p.page_size) * p.page_size;
+#pragma unroll
+          for (int kv = 0; kv < 2; ++kv) {
+            const int row = ((page * 2 + kv) * p.Hkv + kvh) * p.page_size + off;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              tma_load_2d(base + (kv * 2 + h) * kBlk + r * run * 128, &tmap_kv, fb, h * 64, row);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = make_idesc(BQ2, BKV, 1, 1);                  // Q (K-major) x K (K-major)
+      constexpr uint32_t idesc_pv = make_idesc(BQ2, HD, 1, 1) | (1u << 16);     // P (K-major) x V (MN-major)
+      bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
+      if (!ok) {
+        report(p.status, kTimeoutFullBarrier, b, -1);
+        *abort_flag = 1;
+      }
+      tc_fence_after_sync();
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      auto issue_pv = [&](int i) -> bool {
+        // P_i is in shared memory (and O has been rescaled if that was due)
+        if (!mbar_wait(smem_u32(&bars->p_ready), i & 1)) {
+          report(p.status, kTimeoutTmemFull, b, 1000 + i);
+          return false;
+        }
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(kv_s + (i & 1) * kKVStage) + 2 * kBlk;
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(p_addr + (kk >> 2) * kBlk) + 2 * (kk & 3);
+          const uint64_t db = make_smem_desc_sw128_mn(v_addr + kk * 16 * 128, kBlk);
+          umma_bf16(tmem_o, da, db, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars->kv_empty[i & 1]));
+        umma_commit(smem_u32(&bars->pv_done));
+        return true;
+      };
+      for (int j = 0; ok && j < n_tiles && !*abort_flag; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(smem_u32(&bars->kv_full[st]), (j >> 1) & 1) ||
+            !mbar_wait(smem_u32(&bars->s_free[st]), ((j >> 1) & 1) ^ 1)) {
+          report(p.status, kTimeoutFullBarrier, b, j);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(kv_s + st * kKVStage);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(q_addr + (kk >> 2) * kBlk) + 2 * (kk & 3);
+          const uint64_t db = make_smem_desc_sw128(k_addr + (kk >> 2) * kBlk) + 2 * (kk & 3);
+          umma_bf16(tmem_base + st * BKV, da, db, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars->s_full[st]));
+        if (j >= 1) ok = issue_pv(j - 1);
+      }
+      if (ok && !*abort_flag) ok = issue_pv(n_tiles - 1);
+      if (!ok) *abort_flag = 1;
+    }
+  } else if (n_tiles > 0) {
+    // ------------------------------------------------------------------ softmax (warps 2..5, one thread per row)
+    const int qd = warp & 3;
+    const int row = qd * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(qd * 32) << 16;
+    const int r_seq = q0 + row;                                     // row within the sequence's new tokens
+    const int kmax = (p.bidirectional || r_seq >= q_len) ? seq - 1 : min(prefix + r_seq, seq - 1);
+    const float scale_log2 = p.scale * kLog2e;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      if (!mbar_wait(smem_u32(&bars->s_full[st]), (j >> 1) & 1)) {
+        report(p.status, kTimeoutTmemFull, b, j);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t v0[32], v1[32], v2[32], v3[32];
+      const uint32_t s_addr = tmem_base + lane_base + st * BKV;
+      tmem_ld32(s_addr, v0);
+      tmem_ld32(s_addr + 32, v1);
+      tmem_ld32(s_addr + 64, v2);
+      tmem_ld32(s_addr + 96, v3);
+      tmem_ld_wait();
+      // S_j is in registers: the MMA warp may overwrite this S buffer with tile j + 2
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars->s_free[st]));
+      const int kv0 = j * BKV;
+      const int nvalid = kmax - kv0 + 1;                            // keys [kv0, kv0 + nvalid) are visible
+      float mx = -INFINITY;
+      if (nvalid >= BKV) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          mx = fmaxf(mx, fmaxf(fmaxf(__uint_as_float(v0[e]), __uint_as_float(v1[e])),
+                               fmaxf(__uint_as_float(v2[e]), __uint_as_float(v3[e]))));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          if (e < nvalid) mx = fmaxf(mx, __uint_as_float(v0[e]));
+          if (e + 32 < nvalid) mx = fmaxf(mx, __uint_as_float(v1[e]));
+          if (e + 64 < nvalid) mx = fmaxf(mx, __uint_as_float(v2[e]));
+          if (e + 96 < nvalid) mx = fmaxf(mx, __uint_as_float(v3[e]));
+        }
+      }
+      mx *= scale_log2;
+      // the previous P V product must be done before P is overwritten (and before O may be rescaled)
+      if (j >= 1 && !mbar_wait(smem_u32(&bars->pv_done), (j - 1) & 1)) {
+        report(p.status, kTimeoutTmemFull, b, 2000 + j);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      if (j == 0) {
+        m_used = mx;
+      } else if (mx > m_used + kRescale) {
+        // rare: bring O and the row sum to the new maximum
+        tc_fence_after_sync();
+        const float f = exp2f(m_used - mx);
+        l *= f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld32(tmem_o + lane_base + c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+          tmem_st32(tmem_o + lane_base + c0, o);
+        }
+        tmem_st_wait();
+        m_used = mx;
+      }
+      // P = exp2(S * scale - m), bf16, into the swizzled P tile: chunk c (8 keys) of this row
+      float sum = 0.f;
+      uint8_t* prow = p_s + row * 128;
+      const int sw = row & 7;
+      auto emit = [&](const uint32_t (&v)[32], int cbase) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float e8[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int key = cbase * 8 + c * 8 + e;
+            float pv = exp2f(fmaf(__uint_as_float(v[c * 8 + e]), scale_log2, -m_used));
+            if (key >= nvalid) pv = 0.f;
+            e8[e] = pv;
+            sum += pv;
+          }
+          const int chunk = cbase + c;                  // 0..15 over the 128 keys
+          const uint4 packed = make_uint4(pack_bf16(e8[0], e8[1]), pack_bf16(e8[2], e8[3]), pack_bf16(e8[4], e8[5]),
+                                          pack_bf16(e8[6], e8[7]));
+          *reinterpret_cast<uint4*>(prow + (chunk >> 3) * kBlk + (((chunk & 7) ^ sw) << 4)) = packed;
+        }
+      };
+      emit(v0, 0);
+      emit(v1, 4);
+      emit(v2, 8);
+      emit(v3, 12);
+      l += sum;
+      // make the generic-proxy writes visible to the tensor core's async proxy, then hand P over
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars->p_ready));
+    }
+    // epilogue: O / l
+    if (ok && mbar_wait(smem_u32(&bars->pv_done), (n_tiles - 1) & 1)) {
+      tc_fence_after_sync();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.out + (static_cast<size_t>(q_begin + r_seq) * p.Hq + hq) * HD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + lane_base + c0, o);
+        tmem_ld_wait();
+        if (r_seq < q_len) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8)
+            *reinterpret_cast<uint4*>(orow + c0 + e) =
+                make_uint4(pack_bf16(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv),
+                           pack_bf16(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv),
+                           pack_bf16(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv),
+                           pack_bf16(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv));
+        }
+      }
+    } else if (ok) {
+      report(p.status, kTimeoutTmemFull, b, 3000);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // tensor map over the whole page pool viewed as [num_pages*2*Hkv*P, D]; box = 64 x min(P, 64)
 struct TmapKey {
   const void* ptr;
@@ -663,6 +1001,45 @@ int sglb_paged_decode(const void* q, void* out, const void* kv_buffer, long long
       e = cudaGetLastError();
     }
   }
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Causal (or bidirectional: `bidirectional` != 0) prefill attention for head_dim 128 on tcgen05 (see
+// paged_extend_tc_kernel).  `total_q` = rows of q; `num_q_tiles_bound` >= sum_b ceil(q_len_b / 128).
+int sglb_paged_extend_tc(const void* q, void* out, const void* kv_buffer, long long num_pages, const int* page_table,
+                         int max_pages, const int* req_pool_indices, const int* seq_lens, const int* prefix_lens,
+                         const int* cu_q_lens, int B, int num_q_tiles_bound, int total_q, int Hq, int Hkv, int D,
+                         int page_size, float scale, int bidirectional, cudaStream_t stream) {
+  using namespace sglb;
+  if (B <= 0 || num_q_tiles_bound <= 0 || total_q <= 0) return 0;
+  if (D != 128 || Hq % Hkv != 0) return -kBadArgument;
+  if (page_size < TN ? (TN % page_size != 0) : (page_size % TN != 0)) return -kBadArgument;
+  CUtensorMap tm, tq;
+  if (!get_kv_tmap(kv_buffer, num_pages * 2 * Hkv * page_size, D, page_size, &tm)) return -100;
+  // q viewed as [total_q, Hq * D]: one box = 128 rows x 64 columns (half a head)
+  if (!encode_tmap_2d(&tq, q, static_cast<uint64_t>(Hq) * D, total_q, static_cast<uint64_t>(Hq) * D * 2, 64, 128, 2))
+    return -101;
+  AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.page_table = page_table;
+  p.req_pool_indices = req_pool_indices;
+  p.seq_lens = seq_lens;
+  p.prefix_lens = prefix_lens;
+  p.cu_q_lens = cu_q_lens;
+  p.status = device_status();
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.max_pages = max_pages; p.page_size = page_size;
+  p.num_splits = 1; p.scale = scale;
+  p.bidirectional = bidirectional;
+  static bool cfg = false;
+  if (!cfg) {
+    cudaError_t e = cudaFuncSetAttribute(paged_extend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cfg = true;
+  }
+  dim3 grid(num_q_tiles_bound, Hq, 1);
+  paged_extend_tc_kernel<<<grid, tc::kThreadsTc, tc::kSmem, stream>>>(tm, tq, p);
+  cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
 

@@ -113,10 +113,17 @@ class ModelWorker:
 
     def forward_batch_generation(self, batch: ModelWorkerBatch, launch_done=None, skip_sample: bool = False,
                                  broadcast: bool = True) -> GenerationBatchResult:
-        if self.broadcast_batches and broadcast:
+        if self.broadcast_batches and broadcast and self.device.type == "cpu":
+            # on CPU the model's collectives and the host-side ones (marks, reports) share one gloo group: a whole
+            # step is one transaction, or another thread's collective could land between this step's
             with self._comm_lock:
                 self.channel.send(batch)
-        out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
+                out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
+        else:
+            if self.broadcast_batches and broadcast:
+                with self._comm_lock:
+                    self.channel.send(batch)
+            out, ids, fb = self.model_runner.forward(batch, skip_sample=skip_sample)
         res = GenerationBatchResult(out, ids, bid=batch.bid, forward_batch=fb)
         cap = getattr(self.model_runner, "routed_capturer", None)
         if cap is not None and getattr(batch, "return_routed_experts", False):

@@ -223,6 +223,10 @@ def decode_num_splits(B: int, Hkv: int, max_seq_len: int) -> int:
     return lib().sglb_decode_num_splits(B, Hkv, max(max_seq_len, 1))
 
 
+# SGLB_EXTEND_TC=0 keeps prefill attention on the mma.sync kernel (A/B switch)
+_EXTEND_TC = os.environ.get("SGLB_EXTEND_TC", "1") != "0"
+
+
 def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_size, scale, cu_q_lens=None,
                     prefix_lens=None, sliding_window=0, soft_cap=0.0, max_q_len=0, max_seq_len=0, num_splits=None,
                     tail_mask=None):
@@ -259,6 +263,14 @@ def paged_attention(q, kv_buffer, page_table, req_pool_indices, seq_lens, page_s
                                           bound, Hq, Hkv, D, page_size, scale, int(sliding_window or 0),
                                           float(soft_cap or 0.0), _p(tm), tm.shape[2], tm.shape[1], _stream()),
                "paged_extend_masked")
+    elif D == 128 and not sliding_window and not soft_cap and _EXTEND_TC:
+        # causal prefill on the tcgen05 kernel: 128-row query tiles, S and O in tensor memory
+        L.sglb_paged_extend_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_int, c_float, c_int, c_void_p]
+        _check(L.sglb_paged_extend_tc(_p(q), _p(out), _p(kv_buffer), num_pages, _p(page_table), max_pages,
+                                      _p(req_pool_indices), _p(seq_lens), _p(prefix_lens), _p(cu_q_lens), B,
+                                      T // 128 + B, T, Hq, Hkv, D, page_size, scale, 0, _stream()), "paged_extend_tc")
     else:
         bound = T // 64 + B
         _check(L.sglb_paged_extend(_p(q), _p(out), _p(kv_buffer), num_pages, _p(page_table), max_pages,

@@ -704,3 +704,30 @@ def test_fused_experts_fp8_block_scaled(native, T, E, E_local, e0, k, H, I):
     want = _fp8_reference_experts(x, moe, tw, ids)
     assert ((got.float() - want.float()).norm() / want.float().norm()).item() < 0.03
     assert ((got.float() - full).norm() / full.norm()).item() < 0.1
+
+
+@pytest.mark.parametrize("P", [16, 64, 128])
+def test_paged_extend_tcgen05_long_and_rescaled(native, P):
+    """The tcgen05 prefill kernel (head_dim 128): long sequences over many 128-key tiles, prefixes that are not
+    tile aligned, and scores that grow along the sequence so that the running maximum is raised (and the
+    accumulator in tensor memory rescaled) many times."""
+    Hq, Hkv, D = 8, 2, 128
+    prefix = [0, 300, 1000, 7]
+    ext = [700, 129, 1, 2048]
+    seqs = [a + b for a, b in zip(prefix, ext)]
+    B = len(seqs)
+    cache, pt, rows = _attn_setup(B, seqs, P, Hkv, D, seed=70)
+    T = sum(ext)
+    q = _bf16(T, Hq, D, seed=71)
+    # keys later in a page get larger norms: maxima keep growing along a sequence
+    ramp = torch.linspace(0.2, 3.0, P, device="cuda").view(1, 1, P, 1)
+    cache[:, 0] = (cache[:, 0].float() * ramp).to(torch.bfloat16)
+    sl = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    pl = torch.tensor(prefix, dtype=torch.int32, device="cuda")
+    cu = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
+    cu[1:] = torch.tensor(ext, device="cuda").cumsum(0)
+    for scale in (D ** -0.5, 0.6):
+        got = native.paged_attention(q, cache, pt, rows, sl, P, scale, cu, pl)
+        torch.cuda.synchronize()
+        native.check_status()
+        _close(got, ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, cu, pl), 3e-2, 3e-2)

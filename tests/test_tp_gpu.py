@@ -53,10 +53,14 @@ def _entry(fn, rank, world, port, q, args, ep=False):
                             local_rank=rank, timeout_s=120)
         out = fn(rank, world, *args)
         q.put((rank, out))
-        ps.destroy()
     except Exception:
         import traceback
         q.put((rank, "ERR " + traceback.format_exc()))
+    # leave without tearing the communicators down: with captured graphs that hold library collectives alive the
+    # teardown can wait for a peer that has already gone
+    q.close()
+    q.join_thread()
+    os._exit(0)
 
 
 # ------------------------------------------------------------------------------------------
