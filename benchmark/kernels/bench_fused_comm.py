@@ -10,6 +10,7 @@ Variants (same inputs, same outputs):
   two       GEMM with reduce-scatter push epilogue + reduce/norm/all-gather kernel (two barriers) + GEMM
   one       one launch: GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather (waits for its peers) + GEMM
   one+ag    the same launch without the final wait + the consumer GEMM that waits per chunk of rows
+  gemms     the two GEMMs alone (no reduction, no norm): the floor of this repo's GEMM kernels
 
 Shapes are Qwen3-32B's at tensor-parallel size N: hidden 5120; o_proj (K = 8192 / N) feeding gate_up
 (N2 = 51200 / N), and down_proj (K = 25600 / N) feeding qkv (N2 = 10240 / N).  Every iteration uses another copy
@@ -76,18 +77,41 @@ def main():
                     return comm.consume_linear(h, w2s[i % copies]) if defer else native.linear(h, w2s[i % copies])
                 return run
 
-            for label, fn in (("nccl", nccl), ("two", fused(False, False)), ("one", fused(True, False)),
-                              ("one+ag", fused(True, True))):
+            def gemms_only(i):
+                y = ops.linear(x, ws[i % copies])
+                return ops.linear(y, w2s[i % copies])
+
+            for label, fn in (("gemms", gemms_only), ("nccl", nccl), ("two", fused(False, False)),
+                              ("one", fused(True, False)), ("one+ag", fused(True, True))):
                 for i in range(3):
                     fn(i)
                 torch.cuda.synchronize()
                 if world > 1:
                     dist.barrier(group=st.tp.cpu_group)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for i in range(args.iters):
-                    fn(i)
-                e1.record()
+                if T <= 256:
+                    # decode-sized: the launches of a step run from a captured graph in serving, so time them that way
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(side):
+                        fn(0)
+                        with torch.cuda.graph(graph, stream=side):
+                            for i in range(args.iters):
+                                fn(i)
+                    torch.cuda.current_stream().wait_stream(side)
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    if world > 1:
+                        dist.barrier(group=st.tp.cpu_group)
+                    e0.record()
+                    graph.replay()
+                    e1.record()
+                else:
+                    e0.record()
+                    for i in range(args.iters):
+                        fn(i)
+                    e1.record()
                 torch.cuda.synchronize()
                 native.check_status()
                 us = e0.elapsed_time(e1) * 1e3 / args.iters

@@ -285,6 +285,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
   return v;
 }
 
+// Release / acquire fence at system scope (cheaper than the sequentially consistent __threadfence_system()).
+// Used by the one thread of a CTA that signals another GPU after a CTA barrier: the barrier orders the other
+// threads' stores before this thread, the fence makes the whole set visible before the flag store that follows.
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
 // Spin until the epoch-valued flag reaches `epoch` (flags only grow), for at most kWaitLimitNs.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t epoch) {
   if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;

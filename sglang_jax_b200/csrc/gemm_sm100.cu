@@ -110,18 +110,19 @@ constexpr int kFlagWords = kAgFlag + 8 * kMaxChunks;
 constexpr int kCtrDone = 0, kCtrExit = 1, kCtrNextRow = 8, kCtrRowsDone = kCtrNextRow + kMaxChunks,
               kCtrTile = kCtrRowsDone + kMaxChunks, kTailCtrInts = kCtrTile + kMaxChunks;
 
-// Ownership layout shared by the producer, the consumer and the host: with at least one full 128-row tile per
-// rank the slices are multiples of 128 rows (a token tile never straddles two owners, so arrival can be
-// signalled per tile); smaller batches have one chunk per owner.
+// Ownership layout shared by the producer, the consumer and the host: large batches (at least four 128-row
+// tiles per rank) are cut into slices that are multiples of 128 rows: a token tile never straddles two
+// owners, so arrival can be signalled per tile, at the price of slices that differ by up to one tile.
+// Smaller batches are split evenly to the row and signalled once per rank.
 __host__ __device__ inline void fused_layout(int M, int world, int* rows_per, int* nchunks, int* per_tile) {
-  if (M >= kChunkRows * world && M > 256) {
+  if (M >= 4 * kChunkRows * world && M > 256) {
     const int r = (M + world - 1) / world;
     *rows_per = (r + kChunkRows - 1) / kChunkRows * kChunkRows;
     *nchunks = *rows_per / kChunkRows;
     *per_tile = 1;
   } else {
     *rows_per = (M + world - 1) / world;
-    *nchunks = (*rows_per + kChunkRows - 1) / kChunkRows;      // 1, or 2 on a single rank with more than 128 rows
+    *nchunks = (*rows_per + kChunkRows - 1) / kChunkRows;
     *per_tile = 0;
   }
 }
@@ -570,12 +571,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (p.per_tile && direct) {
           // this rank's partial rows of token tile `ta`: once all weight tiles of the token tile have been
           // pushed, tell the owner of those rows (release at system scope orders the peer stores before it)
-          __threadfence_system();
           named_bar_sync(1, kEpiThreads);
           if (epi_tid == 0) {
+            fence_acq_rel_sys();
             const int old = atomicAdd(&p.tail_ctrs[kCtrTile + sg.ta], 1);
             if (old == p.tiles_b - 1) {
-              __threadfence_system();
+              fence_acq_rel_sys();
               const int owner = sg.m0 / p.rs_rows_per;
               const int j = (sg.m0 - owner * p.rs_rows_per) / kChunkRows;
               st_release_sys(p.flag_peer[owner] + kRsFlag + j * 8 + p.rs_rank, epoch);
@@ -712,154 +713,226 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   // ------------------------------------------------------------------ fused tail
   // Reduce-scatter arrival -> sum of the `world` partial slices + residual -> RMSNorm -> all-gather by peer
-  // stores, done by the CTAs of this same launch as they run out of GEMM work.  Cross-GPU ordering is by
-  // epoch-valued flags (bounded waits); nothing here waits for a CTA of this GPU that could itself be waiting.
+  // stores, done by the warps of this same launch as their CTA runs out of GEMM work.  One warp owns one row
+  // at a time (rows are handed out by an atomic counter per chunk): pass 1 sums the slices and the residual,
+  // keeps the row in the now idle operand ring of shared memory and accumulates the sum of squares; pass 2
+  // normalises and pushes.  Nothing in here is a CTA-wide barrier, so the six warps of a CTA work on six rows
+  // independently.  Cross-GPU ordering is by epoch-valued flags (bounded waits); no wait depends on a CTA of
+  // this GPU that could itself be waiting.
   if constexpr (FUSE == 1) {
-    __shared__ int s_row;
-    __shared__ int s_ok;
-    __shared__ float s_red[8];
     const int tid = threadIdx.x;
-    __threadfence_system();          // this thread's peer stores (epilogue warps) are out
-    __syncthreads();
-    if (tid == 0) {
-      s_ok = 1;
-      if (!p.per_tile) {
-        // small batches: the CTA that finishes last tells every owner that all of this rank's rows are out
-        const int old = atomicAdd(&p.tail_ctrs[kCtrDone], 1);
-        if (old == static_cast<int>(gridDim.x) - 1) {
-          __threadfence_system();
-          for (int o = 0; o < p.rs_world; ++o)
-            for (int j = 0; j < p.nchunks; ++j) st_release_sys(p.flag_peer[o] + kRsFlag + j * 8 + p.rs_rank, epoch);
-        }
+    __syncthreads();                 // the epilogue's peer stores are issued, every role is done with the operand ring
+    if (tid == 0 && !p.per_tile) {
+      // small batches: the CTA that finishes last tells every owner that all of this rank's rows are out
+      fence_acq_rel_sys();
+      const int old = atomicAdd(&p.tail_ctrs[kCtrDone], 1);
+      if (old == static_cast<int>(gridDim.x) - 1) {
+        fence_acq_rel_sys();
+        for (int o = 0; o < p.rs_world; ++o)
+          for (int j = 0; j < p.nchunks; ++j) st_release_sys(p.flag_peer[o] + kRsFlag + j * 8 + p.rs_rank, epoch);
       }
     }
-    __syncthreads();
     const int nvec = p.N >> 3;
-    constexpr int kMaxVpt = 6;       // N <= 6 * 192 * 8 = 9216
     const uint4* wv = reinterpret_cast<const uint4*>(p.norm_w);
     const uint4* ybase = reinterpret_cast<const uint4*>(p.rs_peer[p.rs_rank]);
     const uint32_t* my_flags = p.flag_peer[p.rs_rank];
-    for (int j = 0; j < p.nchunks && !*abort_flag; ++j) {
-      const int c0 = p.rs_rank * p.rs_rows_per + j * kChunkRows;
-      const int c1 = min(min(c0 + kChunkRows, (p.rs_rank + 1) * p.rs_rows_per), p.M);
-      const int nrows = c1 - c0;
-      if (nrows <= 0) break;
-      bool waited = false;
-      for (;;) {
-        if (tid == 0) s_row = atomicAdd(&p.tail_ctrs[kCtrNextRow + j], 1);
+    const int slice0 = p.rs_rank * p.rs_rows_per;
+    const int slice_rows = max(0, min(p.M, slice0 + p.rs_rows_per) - slice0);
+    // sum of the `world` slices (+ residual, which is updated in place) of 8 consecutive values of one row
+    auto reduce8 = [&](const uint4 (&part)[8], int local, size_t gbase, int idx, float (&v)[8]) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl) {
+        if (sl < p.rs_world) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[sl]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t = __bfloat1622float2(h[e]);
+            v[2 * e] += t.x;
+            v[2 * e + 1] += t.y;
+          }
+        }
+      }
+      if (p.residual != nullptr) {
+        uint4* rv = reinterpret_cast<uint4*>(p.residual) + gbase + idx;
+        const uint4 r4 = *rv;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t = __bfloat1622float2(h[e]);
+          v[2 * e] += t.x;
+          v[2 * e + 1] += t.y;
+        }
+        // the residual stream is bf16: normalise what the next layer will read back
+        const uint4 packed = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
+                                        pack_bf16(v[6], v[7]));
+        *rv = packed;
+        const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t = __bfloat1622float2(hp[e]);
+          v[2 * e] = t.x;
+          v[2 * e + 1] = t.y;
+        }
+      }
+    };
+    auto load_parts = [&](uint4 (&part)[8], int local, int idx) {
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl)
+        if (sl < p.rs_world) part[sl] = __ldcg(ybase + (static_cast<size_t>(sl) * p.rs_rows_per + local) * nvec + idx);
+    };
+    auto push8 = [&](const float (&v)[8], float inv, size_t gbase, int idx) {
+      const uint4 w4 = wv[idx];
+      const __nv_bfloat162* hw = reinterpret_cast<const __nv_bfloat162*>(&w4);
+      const float g = p.gemma ? 1.f : 0.f;
+      float o8[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 t = __bfloat1622float2(hw[e]);
+        o8[2 * e] = v[2 * e] * inv * (t.x + g);
+        o8[2 * e + 1] = v[2 * e + 1] * inv * (t.y + g);
+      }
+      const uint4 out4 = make_uint4(pack_bf16(o8[0], o8[1]), pack_bf16(o8[2], o8[3]), pack_bf16(o8[4], o8[5]),
+                                    pack_bf16(o8[6], o8[7]));
+      if (p.ag_mc != nullptr) {
+        multimem_st_v4(reinterpret_cast<uint4*>(p.ag_mc) + gbase + idx, out4);
+      } else {
+#pragma unroll
+        for (int d = 0; d < 8; ++d)
+          if (d < p.rs_world) reinterpret_cast<uint4*>(p.ag_peer[d])[gbase + idx] = out4;
+      }
+    };
+    // a row of chunk j has been pushed everywhere: count it; the last row of the chunk tells every rank
+    auto row_done = [&](int j, int nrows) {
+      fence_acq_rel_sys();
+      const int old = atomicAdd(&p.tail_ctrs[kCtrRowsDone + j], 1);
+      if (old == nrows - 1) {
+        fence_acq_rel_sys();
+        for (int d = 0; d < p.rs_world; ++d) st_release_sys(p.flag_peer[d] + kAgFlag + p.rs_rank * kMaxChunks + j, epoch);
+      }
+    };
+
+    if (slice_rows <= 2 * static_cast<int>(gridDim.x) && nvec <= 4 * kNumThreads) {
+      // ---- small slices: one CTA per row (two at most), every load of the row in flight at once
+      __shared__ float s_red[2][kNumThreads / 32];
+      __shared__ int s_ok;
+      for (int lr_all = blockIdx.x, pass = 0; lr_all < slice_rows && !*abort_flag; lr_all += gridDim.x, ++pass) {
+        const int j = lr_all / kChunkRows;
+        const int row = slice0 + lr_all;
+        const int c0 = slice0 + j * kChunkRows;
+        const int nrows = min(min(c0 + kChunkRows, slice0 + p.rs_rows_per), p.M) - c0;
+        if (tid == 0) s_ok = 1;
         __syncthreads();
-        const int lr = s_row;
+        if (tid < p.rs_world && !wait_flag_ge(my_flags + kRsFlag + j * 8 + tid, epoch)) {
+          report(p.status, kTimeoutPeerFlag, tid, 10);
+          s_ok = 0;
+        }
         __syncthreads();
-        if (lr >= nrows) break;
-        if (!waited) {
-          if (tid < p.rs_world) {
-            if (!wait_flag_ge(my_flags + kRsFlag + j * 8 + tid, epoch)) {
-              report(p.status, kTimeoutPeerFlag, tid, 10);
-              s_ok = 0;
+        if (s_ok) {
+          const size_t gbase = static_cast<size_t>(row) * nvec;
+          float vals[4][8];
+          float ss = 0.f;
+          {
+            uint4 part[4][8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (tid + i * kNumThreads < nvec) load_parts(part[i], lr_all, tid + i * kNumThreads);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int idx = tid + i * kNumThreads;
+              if (idx < nvec) {
+                reduce8(part[i], lr_all, gbase, idx, vals[i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += vals[i][e] * vals[i][e];
+              }
             }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (lane == 0) s_red[pass & 1][warp] = ss;
+          __syncthreads();
+          float tot = 0.f;
+#pragma unroll
+          for (int wdx = 0; wdx < kNumThreads / 32; ++wdx) tot += s_red[pass & 1][wdx];
+          const float inv = rsqrtf(tot / p.N + p.eps);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * kNumThreads;
+            if (idx < nvec) push8(vals[i], inv, gbase, idx);
           }
           __syncthreads();
-          waited = true;
-          if (!s_ok) {
-            *abort_flag = 1;
-            break;
-          }
+          if (tid == 0) row_done(j, nrows);
+        } else {
+          *abort_flag = 1;
         }
-        const int row = c0 + lr;
-        const int local = row - p.rs_rank * p.rs_rows_per;
-        const size_t gbase = static_cast<size_t>(row) * nvec;
-        float vals[kMaxVpt][8];
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < kMaxVpt; ++i) {
-          const int idx = tid + i * kNumThreads;
-          if (idx < nvec) {
-            uint4 part[8];
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-              if (s < p.rs_world)
-                part[s] = __ldcg(ybase + (static_cast<size_t>(s) * p.rs_rows_per + local) * nvec + idx);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) vals[i][e] = 0.f;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-              if (s < p.rs_world) {
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[s]);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 t = __bfloat1622float2(h[e]);
-                  vals[i][2 * e] += t.x;
-                  vals[i][2 * e + 1] += t.y;
-                }
+      }
+    } else {
+      // ---- prefill-sized slices: one warp per row (rows handed out by an atomic counter per chunk), the row
+      // kept in the now idle operand ring between the two passes; no CTA-wide barrier, so the warps of a CTA
+      // work on different rows independently
+      constexpr int kRingBytes = C::kStages * C::kStageBytes;
+      const int tail_warps = min(kNumThreads / 32, kRingBytes / (p.N * 4));
+      float* stash = reinterpret_cast<float*>(stage_base) + static_cast<size_t>(warp) * p.N;
+      if (warp < tail_warps) {
+        for (int j = 0; j < p.nchunks && !*abort_flag; ++j) {
+          const int c0 = slice0 + j * kChunkRows;
+          const int nrows = min(min(c0 + kChunkRows, slice0 + p.rs_rows_per), p.M) - c0;
+          if (nrows <= 0) break;
+          bool waited = false;
+          for (;;) {
+            int lr = 0;
+            if (lane == 0) lr = atomicAdd(&p.tail_ctrs[kCtrNextRow + j], 1);
+            lr = __shfl_sync(0xffffffffu, lr, 0);
+            if (lr >= nrows) break;
+            if (!waited) {
+              int good = 1;
+              if (lane < p.rs_world && !wait_flag_ge(my_flags + kRsFlag + j * 8 + lane, epoch)) {
+                report(p.status, kTimeoutPeerFlag, lane, 10);
+                good = 0;
+              }
+              good = __all_sync(0xffffffffu, good);
+              waited = true;
+              if (!good) {
+                *abort_flag = 1;
+                break;
               }
             }
-            if (p.residual != nullptr) {
-              uint4* rv = reinterpret_cast<uint4*>(p.residual) + gbase + idx;
-              const uint4 r4 = *rv;
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r4);
+            const int row = c0 + lr;
+            const int local = row - slice0;
+            const size_t gbase = static_cast<size_t>(row) * nvec;
+            float ss = 0.f;
+            // two vectors per lane and step: their loads are all issued before the first use
+            for (int idx = lane; idx < nvec; idx += 64) {
+              uint4 pa[8], pb[8];
+              const bool two = idx + 32 < nvec;
+              load_parts(pa, local, idx);
+              if (two) load_parts(pb, local, idx + 32);
+              float v[8];
+              reduce8(pa, local, gbase, idx, v);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 t = __bfloat1622float2(h[e]);
-                vals[i][2 * e] += t.x;
-                vals[i][2 * e + 1] += t.y;
+              for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+              reinterpret_cast<float4*>(stash)[2 * idx] = make_float4(v[0], v[1], v[2], v[3]);
+              reinterpret_cast<float4*>(stash)[2 * idx + 1] = make_float4(v[4], v[5], v[6], v[7]);
+              if (two) {
+                reduce8(pb, local, gbase, idx + 32, v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+                reinterpret_cast<float4*>(stash)[2 * (idx + 32)] = make_float4(v[0], v[1], v[2], v[3]);
+                reinterpret_cast<float4*>(stash)[2 * (idx + 32) + 1] = make_float4(v[4], v[5], v[6], v[7]);
               }
-              // the residual stream is bf16: normalise what the next layer will read back
-              uint4 packed = make_uint4(pack_bf16(vals[i][0], vals[i][1]), pack_bf16(vals[i][2], vals[i][3]),
-                                        pack_bf16(vals[i][4], vals[i][5]), pack_bf16(vals[i][6], vals[i][7]));
-              *rv = packed;
-              const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&packed);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 t = __bfloat1622float2(hp[e]);
-                vals[i][2 * e] = t.x;
-                vals[i][2 * e + 1] = t.y;
-              }
             }
 #pragma unroll
-            for (int e = 0; e < 8; ++e) ss += vals[i][e] * vals[i][e];
-          }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) s_red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-#pragma unroll
-        for (int wdx = 0; wdx < kNumThreads / 32; ++wdx) tot += s_red[wdx];
-        const float inv = rsqrtf(tot / p.N + p.eps);
-#pragma unroll
-        for (int i = 0; i < kMaxVpt; ++i) {
-          const int idx = tid + i * kNumThreads;
-          if (idx < nvec) {
-            const uint4 w4 = wv[idx];
-            const __nv_bfloat162* hw = reinterpret_cast<const __nv_bfloat162*>(&w4);
-            float o8[8];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 t = __bfloat1622float2(hw[e]);
-              o8[2 * e] = vals[i][2 * e] * inv * (p.gemma ? t.x + 1.f : t.x);
-              o8[2 * e + 1] = vals[i][2 * e + 1] * inv * (p.gemma ? t.y + 1.f : t.y);
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv = rsqrtf(ss / p.N + p.eps);
+            for (int idx = lane; idx < nvec; idx += 32) {
+              const float4 a4 = reinterpret_cast<const float4*>(stash)[2 * idx];
+              const float4 b4 = reinterpret_cast<const float4*>(stash)[2 * idx + 1];
+              const float v[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
+              push8(v, inv, gbase, idx);
             }
-            const uint4 out4 = make_uint4(pack_bf16(o8[0], o8[1]), pack_bf16(o8[2], o8[3]), pack_bf16(o8[4], o8[5]),
-                                          pack_bf16(o8[6], o8[7]));
-            if (p.ag_mc != nullptr) {
-              multimem_st_v4(reinterpret_cast<uint4*>(p.ag_mc) + gbase + idx, out4);
-            } else {
-#pragma unroll
-              for (int d = 0; d < 8; ++d)
-                if (d < p.rs_world) reinterpret_cast<uint4*>(p.ag_peer[d])[gbase + idx] = out4;
-            }
-          }
-        }
-        // the row has been pushed everywhere: count it, and let the last row of the chunk tell every rank
-        __threadfence_system();
-        __syncthreads();
-        if (tid == 0) {
-          const int old = atomicAdd(&p.tail_ctrs[kCtrRowsDone + j], 1);
-          if (old == nrows - 1) {
-            __threadfence_system();
-            for (int d = 0; d < p.rs_world; ++d)
-              st_release_sys(p.flag_peer[d] + kAgFlag + p.rs_rank * kMaxChunks + j, epoch);
+            __syncwarp();
+            if (lane == 0) row_done(j, nrows);
           }
         }
       }
@@ -875,13 +948,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     __syncthreads();
     if (tid == 0) {
+      *last_flag = 0;
       const int old = atomicAdd(&p.tail_ctrs[kCtrExit], 1);
       if (old == static_cast<int>(gridDim.x) - 1) {
-        // last CTA out: leave the counters clean and publish the epoch for the next launch / the consumer
-        for (int i = 0; i < kTailCtrInts; ++i) p.tail_ctrs[i] = 0;
-        __threadfence();
-        *reinterpret_cast<volatile uint32_t*>(p.seq) = epoch;
+        *last_flag = 1;
       }
+    }
+    __syncthreads();
+    if (*last_flag) {
+      // last CTA out: leave the counters clean and publish the epoch for the next launch / the consumer
+      for (int i = tid; i < kTailCtrInts; i += kNumThreads) p.tail_ctrs[i] = 0;
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) *reinterpret_cast<volatile uint32_t*>(p.seq) = epoch;
     }
   }
 
