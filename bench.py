@@ -427,9 +427,8 @@ def main():
             state["phase"] = "done"
             state["done"].set()
 
-    sched.step_hooks.append(hook)
-    top_up(sched)
-    state["done"].wait()
+    sched.step_hooks.append(hook)      # the scheduler thread's idle iterations call it: requests are only ever
+    state["done"].wait()               # submitted from that one thread
     arm()
     clock_info = clocks.stop()
     ms = worker.elapsed_ms_max_over_ranks("t0", "t1")

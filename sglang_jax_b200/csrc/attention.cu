@@ -809,12 +809,15 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
         ok = false;
         break;
       }
+      // Raising the maximum is a warp-wide step (tcgen05.ld / .st are warp-collective): rows that do not need it
+      // take part with a factor of one.
+      const bool raise = j > 0 && mx > m_used + kRescale;
       if (j == 0) {
         m_used = mx;
-      } else if (mx > m_used + kRescale) {
+      } else if (__any_sync(0xffffffffu, raise)) {
         // rare: bring O and the row sum to the new maximum
         tc_fence_after_sync();
-        const float f = exp2f(m_used - mx);
+        const float f = raise ? exp2f(m_used - mx) : 1.f;
         l *= f;
 #pragma unroll 1
         for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -826,7 +829,7 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
           tmem_st32(tmem_o + lane_base + c0, o);
         }
         tmem_st_wait();
-        m_used = mx;
+        if (raise) m_used = mx;
       }
       // P = exp2(S * scale - m), bf16, into the swizzled P tile: chunk c (8 keys) of this row
       float sum = 0.f;
