@@ -50,6 +50,7 @@ sys.path.insert(0, ROOT)
 # request shapes of the named configurations: (input min, input max, output, concurrency)
 MODEL_SHAPES = {
     "qwen3-32b": (512, 2048, 256, 128),
+    "qwen3-32b-tp8-shard": (512, 2048, 256, 128),
     "llama3-8b": (1024, 1024, 512, 64),
     "qwen3-8b": (1024, 1024, 1024, 64),
     "qwen3-30b-a3b": (1024, 1024, 512, 256),

@@ -1,6 +1,9 @@
 """Serving benchmark client (reference `python/sgl_jax/bench_serving.py`): an asyncio load generator
-against the native `/generate` or the OpenAI `/v1/completions` endpoint with the datasets `random`
-(synthetic ids) and `generated-shared-prefix`, a request rate / max-concurrency limiter, and the
+against the native `/generate`, the OpenAI `/v1/completions` or the `/v1/chat/completions` endpoint with the
+datasets of the reference's `get_dataset` (:780): `random` (synthetic ids), `generated-shared-prefix` (:1778),
+`sharegpt` (:1177, a local ShareGPT json), `custom` (a jsonl of prompts / conversations), `mooncake` (a jsonl
+trace replayed at its own timestamps), `image` (:1624, synthetic images attached to chat requests) and `mmmu`
+(:1092, a local copy of the benchmark), a request rate / max-concurrency limiter, and the
 reference's metric definitions (`calculate_metrics` :1942-2117): TTFT = latency of the first streamed
 chunk, ITL = gaps between chunks, TPOT = (latency - TTFT) / (output_len - 1), throughput =
 tokens / duration, percentiles p50/p90/p99, peak output tok/s from 1-second buckets.
@@ -56,9 +59,179 @@ def sample_generated_shared_prefix_requests(num_groups: int, prompts_per_group: 
     return reqs
 
 
+class _Lengths:
+    """Token counts of text prompts: a HF tokenizer when `--tokenizer` names one, else whitespace words
+    (good enough to size a load; the server reports exact counts in its usage fields)."""
+
+    def __init__(self, path: str | None):
+        self.tok = None
+        if path:
+            from transformers import AutoTokenizer
+            self.tok = AutoTokenizer.from_pretrained(path)
+
+    def __call__(self, text: str) -> int:
+        return len(self.tok.encode(text)) if self.tok is not None else max(len(text.split()), 1)
+
+
+def sample_sharegpt_requests(path: str, num_prompts: int, lengths: _Lengths, fixed_output_len: int | None = None,
+                             context_len: int | None = None, seed: int = 1):
+    """ShareGPT json: a list of `{"conversations": [{"from": "human", "value": ...}, {"from": "gpt", ...}]}`.
+    The first human turn is the prompt, the length of the first reply the output length (reference :1177)."""
+    with open(path) as f:
+        data = json.load(f)
+    data = [d for d in data if len(d.get("conversations", d.get("conversation", []))) >= 2]
+    random.Random(seed).shuffle(data)
+    reqs = []
+    for d in data:
+        conv = d.get("conversations", d.get("conversation"))
+        prompt, reply = conv[0]["value"], conv[1]["value"]
+        n_in = lengths(prompt)
+        n_out = fixed_output_len or lengths(reply)
+        if n_in < 2 or n_out < 2 or (context_len and n_in + n_out > context_len):
+            continue
+        reqs.append((prompt, n_out))
+        if len(reqs) == num_prompts:
+            break
+    return reqs
+
+
+def sample_custom_requests(path: str, num_prompts: int, lengths: _Lengths, fixed_output_len: int | None = None,
+                           seed: int = 1):
+    """jsonl, one request per line: `{"prompt": str | [ids], "output_len": int}` or
+    `{"conversations": [...]}` in the ShareGPT turn format."""
+    reqs = []
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if not line:
+                continue
+            d = json.loads(line)
+            if "conversations" in d:
+                conv = d["conversations"]
+                prompt = conv[0].get("value", conv[0].get("content", ""))
+                n_out = fixed_output_len or (lengths(conv[1].get("value", conv[1].get("content", ""))) if len(conv) > 1 else 128)
+            else:
+                prompt = d.get("prompt", d.get("input_ids"))
+                n_out = fixed_output_len or int(d.get("output_len", d.get("max_tokens", 128)))
+            reqs.append((prompt, n_out))
+            if len(reqs) == num_prompts:
+                break
+    return reqs
+
+
+def sample_mooncake_requests(path: str, num_prompts: int, vocab_size: int, block_tokens: int = 512, seed: int = 1):
+    """Mooncake trace jsonl: `{"timestamp": ms, "input_length": n, "output_length": m, "hash_ids": [...]}`.
+    Each hash id stands for one block of `block_tokens` tokens, so equal ids reproduce the trace's prefix sharing;
+    returns `(ids, output_len, arrival_s)` triples."""
+    reqs = []
+    with open(path) as f:
+        for line in f:
+            if not line.strip():
+                continue
+            d = json.loads(line)
+            ids: list[int] = []
+            for h in d.get("hash_ids", []):
+                ids.extend(np.random.RandomState(int(h) % (2 ** 31)).randint(0, vocab_size, size=block_tokens).tolist())
+            n = int(d["input_length"])
+            if len(ids) < n:
+                ids.extend(np.random.RandomState(seed + len(reqs)).randint(0, vocab_size, size=n - len(ids)).tolist())
+            reqs.append((ids[:n], int(d["output_length"]), float(d.get("timestamp", 0)) / 1000.0))
+            if len(reqs) == num_prompts:
+                break
+    return reqs
+
+
+def _png_data_url(width: int, height: int, rng) -> str:
+    """A random RGB image as a base64 PNG data URL (stored-deflate blocks, no imaging library needed)."""
+    import base64
+    import struct
+    import zlib
+    raw = b"".join(b"\x00" + rng.bytes(width * 3) for _ in range(height))
+
+    def chunk(kind: bytes, data: bytes) -> bytes:
+        return struct.pack(">I", len(data)) + kind + data + struct.pack(">I", zlib.crc32(kind + data) & 0xFFFFFFFF)
+
+    png = b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", width, height, 8, 2, 0, 0, 0)) + \
+        chunk(b"IDAT", zlib.compress(raw, 1)) + chunk(b"IEND", b"")
+    return "data:image/png;base64," + base64.b64encode(png).decode()
+
+
+def sample_image_requests(num_prompts: int, image_count: int, resolution: str, input_len: int, output_len: int,
+                          seed: int = 1):
+    """Chat requests with `image_count` synthetic images of `resolution` (`WxH`, or 360p/720p/1080p/4k) and a random
+    text of about `input_len` words (reference :1624); returns `(messages, output_len)` pairs."""
+    presets = {"360p": (640, 360), "720p": (1280, 720), "1080p": (1920, 1080), "4k": (3840, 2160)}
+    w, h = presets[resolution] if resolution in presets else tuple(int(x) for x in resolution.lower().split("x"))
+    rng = np.random.RandomState(seed)
+    reqs = []
+    for _ in range(num_prompts):
+        content = [{"type": "image_url", "image_url": {"url": _png_data_url(w, h, rng)}} for _ in range(image_count)]
+        content.append({"type": "text", "text": " ".join(f"w{int(x)}" for x in rng.randint(0, 5000, size=input_len))})
+        reqs.append(([{"role": "user", "content": content}], output_len))
+    return reqs
+
+
+def sample_mmmu_requests(path: str, num_prompts: int, output_len: int):
+    """A local MMMU split as jsonl (`{"question": ..., "options": [...], "image": <path or data url>}`); the hub
+    copy cannot be fetched offline (reference :1092 downloads it)."""
+    reqs = []
+    with open(path) as f:
+        for line in f:
+            if not line.strip():
+                continue
+            d = json.loads(line)
+            img = d.get("image") or d.get("image_1")
+            if img and not str(img).startswith("data:"):
+                import base64
+                with open(img, "rb") as g:
+                    img = "data:image/png;base64," + base64.b64encode(g.read()).decode()
+            text = d["question"] + "".join(f"\n({chr(65 + i)}) {o}" for i, o in enumerate(d.get("options", [])))
+            content = ([{"type": "image_url", "image_url": {"url": img}}] if img else []) + [{"type": "text", "text": text}]
+            reqs.append(([{"role": "user", "content": content}], output_len))
+            if len(reqs) == num_prompts:
+                break
+    return reqs
+
+
+async def _request_openai_chat(session, url, messages, out_len, extra, model) -> RequestFuncOutput:
+    out = RequestFuncOutput(prompt_len=sum(len(str(m.get("content", ""))) for m in messages) // 4)
+    body = {"model": model, "messages": messages, "max_tokens": out_len, "temperature": 0.0, "stream": True,
+            "ignore_eos": True, "stream_options": {"include_usage": True}, **extra}
+    out.start = st = time.perf_counter()
+    last, n = st, 0
+    try:
+        async with session.post(url + "/v1/chat/completions", json=body) as resp:
+            if resp.status != 200:
+                out.error = f"HTTP {resp.status}"
+                return out
+            async for raw in resp.content:
+                line = raw.decode().strip()
+                if not line.startswith("data:") or line.endswith("[DONE]"):
+                    continue
+                d = json.loads(line[5:])
+                now = time.perf_counter()
+                if d.get("usage"):
+                    out.output_len = d["usage"]["completion_tokens"]
+                    out.prompt_len = d["usage"].get("prompt_tokens", out.prompt_len)
+                if d.get("choices") and (d["choices"][0].get("delta") or {}).get("content"):
+                    if n == 0:
+                        out.ttft = now - st
+                    else:
+                        out.itl.append(now - last)
+                    out.chunk_times.append(now)
+                    last = now
+                    n += 1
+        out.latency = time.perf_counter() - st
+        out.output_len = out.output_len or n
+        out.success = n > 0
+    except Exception as e:
+        out.error = repr(e)
+    return out
+
+
 async def _request_sglang_generate(session, url, ids, out_len, extra) -> RequestFuncOutput:
-    out = RequestFuncOutput(prompt_len=len(ids))
-    body = {"input_ids": ids, "stream": True,
+    out = RequestFuncOutput(prompt_len=len(ids) if not isinstance(ids, str) else max(len(ids.split()), 1))
+    body = {("text" if isinstance(ids, str) else "input_ids"): ids, "stream": True,
             "sampling_params": {"temperature": 0.0, "max_new_tokens": out_len, "ignore_eos": True, **extra}}
     out.start = st = time.perf_counter()
     last = st
@@ -81,6 +254,7 @@ async def _request_sglang_generate(session, url, ids, out_len, extra) -> Request
                     return out
                 now = time.perf_counter()
                 n_new = d["meta_info"]["completion_tokens"]
+                out.prompt_len = d["meta_info"].get("prompt_tokens", out.prompt_len)
                 if n_new > n_tok:
                     if n_tok == 0:
                         out.ttft = now - st
@@ -98,7 +272,7 @@ async def _request_sglang_generate(session, url, ids, out_len, extra) -> Request
 
 
 async def _request_openai_completions(session, url, ids, out_len, extra, model) -> RequestFuncOutput:
-    out = RequestFuncOutput(prompt_len=len(ids))
+    out = RequestFuncOutput(prompt_len=len(ids) if not isinstance(ids, str) else max(len(ids.split()), 1))
     body = {"model": model, "prompt": ids, "max_tokens": out_len, "temperature": 0.0, "stream": True,
             "ignore_eos": True, "stream_options": {"include_usage": True}, **extra}
     out.start = st = time.perf_counter()
@@ -182,8 +356,13 @@ async def benchmark(args, reqs) -> dict:
 
         async def one(ids, out_len):
             async def call():
+                if isinstance(ids, list) and ids and isinstance(ids[0], dict):       # chat messages (image datasets)
+                    return await _request_openai_chat(session, url, ids, out_len, extra, args.model or "default")
                 if args.backend == "sglang":
                     return await _request_sglang_generate(session, url, ids, out_len, extra)
+                if args.backend == "sglang-oai-chat":
+                    msgs = [{"role": "user", "content": ids if isinstance(ids, str) else " ".join(map(str, ids))}]
+                    return await _request_openai_chat(session, url, msgs, out_len, extra, args.model or "default")
                 return await _request_openai_completions(session, url, ids, out_len, extra, args.model or "default")
             if sem is None:
                 return await call()
@@ -195,9 +374,15 @@ async def benchmark(args, reqs) -> dict:
                 pass
         t0 = time.perf_counter()
         tasks = []
-        for ids, out_len in reqs:
+        for req in reqs:
+            ids, out_len = req[0], req[1]
+            if len(req) > 2:
+                # trace replay: the request leaves at its recorded offset (scaled by --mooncake-slowdown-factor)
+                wait = req[2] * args.mooncake_slowdown_factor - (time.perf_counter() - t0)
+                if wait > 0:
+                    await asyncio.sleep(wait)
             tasks.append(asyncio.create_task(one(ids, out_len)))
-            if args.request_rate != float("inf"):
+            if len(req) == 2 and args.request_rate != float("inf"):
                 await asyncio.sleep(np.random.exponential(1.0 / args.request_rate))
         outputs = await asyncio.gather(*tasks)
         duration = time.perf_counter() - t0
@@ -234,9 +419,27 @@ def run_benchmark(args) -> dict:
         reqs = sample_generated_shared_prefix_requests(args.gsp_num_groups, args.gsp_prompts_per_group,
                                                        args.gsp_system_prompt_len, args.gsp_question_len,
                                                        args.gsp_output_len, args.vocab_size, args.seed)
+    elif args.dataset_name in ("sharegpt", "custom", "mooncake", "mmmu"):
+        if not args.dataset_path:
+            raise SystemExit(f"dataset {args.dataset_name} reads a local file (there is no network to fetch it): "
+                             f"pass --dataset-path")
+        lengths = _Lengths(args.tokenizer)
+        if args.dataset_name == "sharegpt":
+            reqs = sample_sharegpt_requests(args.dataset_path, args.num_prompts, lengths, args.sharegpt_output_len,
+                                            args.sharegpt_context_len, args.seed)
+        elif args.dataset_name == "custom":
+            reqs = sample_custom_requests(args.dataset_path, args.num_prompts, lengths, args.sharegpt_output_len,
+                                          args.seed)
+        elif args.dataset_name == "mooncake":
+            reqs = sample_mooncake_requests(args.dataset_path, args.num_prompts, args.vocab_size,
+                                            args.mooncake_block_tokens, args.seed)
+        else:
+            reqs = sample_mmmu_requests(args.dataset_path, args.num_prompts, args.random_output_len)
+    elif args.dataset_name == "image":
+        reqs = sample_image_requests(args.num_prompts, args.image_count, args.image_resolution,
+                                     args.random_input_len, args.random_output_len, args.seed)
     else:
-        raise SystemExit(f"dataset {args.dataset_name} needs files that are not available offline; "
-                         f"use random or generated-shared-prefix")
+        raise SystemExit(f"unknown dataset {args.dataset_name}")
     m = asyncio.run(benchmark(args, reqs))
     print_metrics(m)
     if args.output_file:
@@ -247,12 +450,21 @@ def run_benchmark(args) -> dict:
 
 def build_parser():
     p = argparse.ArgumentParser()
-    p.add_argument("--backend", default="sglang", choices=["sglang", "sglang-oai", "vllm"])
+    p.add_argument("--backend", default="sglang", choices=["sglang", "sglang-oai", "sglang-oai-chat", "vllm"])
     p.add_argument("--base-url", default=None)
     p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=30000)
     p.add_argument("--model", default=None)
-    p.add_argument("--dataset-name", default="random", choices=["random", "generated-shared-prefix", "sharegpt"])
+    p.add_argument("--dataset-name", default="random",
+                   choices=["random", "generated-shared-prefix", "sharegpt", "custom", "mooncake", "image", "mmmu"])
+    p.add_argument("--dataset-path", default=None, help="local file of the sharegpt / custom / mooncake / mmmu datasets")
+    p.add_argument("--tokenizer", default=None, help="HF tokenizer directory used to size text prompts")
+    p.add_argument("--sharegpt-output-len", type=int, default=None)
+    p.add_argument("--sharegpt-context-len", type=int, default=None)
+    p.add_argument("--mooncake-slowdown-factor", type=float, default=1.0)
+    p.add_argument("--mooncake-block-tokens", type=int, default=512)
+    p.add_argument("--image-count", type=int, default=1)
+    p.add_argument("--image-resolution", default="360p")
     p.add_argument("--num-prompts", type=int, default=1000)
     p.add_argument("--random-input-len", type=int, default=1024)
     p.add_argument("--random-output-len", type=int, default=1024)

@@ -25,13 +25,18 @@
 //     (cudaGetSymbolAddress, with that device current) and caches it.  Make that first call
 //     before any stream capture.
 //   * All calls share the one array, which keeps the contents of the previous call: the header
-//     (status + counters) is cleared with cudaMemsetAsync on `stream` at the start of each call.
+//     (status + counters) is cleared with cudaMemsetAsync on `stream` at the start of each call,
+//     which also erases a status word of the previous call that nobody has read yet: read the
+//     status between calls if a failure must not go unnoticed.
 //     Calls that overlap on the GPU (different streams, no ordering between them) race on it;
 //     serialise them.
 //   * No cudaMalloc, cudaFree or allocating library routine is called; the caller provides
 //     x, w, bias (may be null) and out.
-//   * Waits inside the kernel are bounded; sglb_gemm_bf16_noalloc_status() returns the status
-//     word (0 = ok) after synchronising.
+//   * Waits inside the kernel are bounded; sglb_gemm_bf16_noalloc_status() copies the status word
+//     (0 = ok) to the host with a blocking cudaMemcpy.  That copy waits for work of the legacy
+//     default stream only: a caller that launched on another stream (in particular one created
+//     with cudaStreamNonBlocking) must synchronise that stream itself before asking for the
+//     status, or it can read 0 while the GEMM is still running.
 #pragma once
 
 #include <cuda_runtime.h>

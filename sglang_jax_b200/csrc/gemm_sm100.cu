@@ -1450,7 +1450,8 @@ int sglb_gemm_bf16_noalloc(const void* x, const void* w, const void* bias, void*
   return 0;
 }
 
-// Copies the entry point's status word (code, block, aux0, aux1) to the host; synchronises.
+// Copies the entry point's status word (code, block, aux0, aux1) to the host with a blocking copy; the caller
+// synchronises the stream it launched on first (see gemm_noalloc.h).
 int sglb_gemm_bf16_noalloc_status(int* out4) {
   using namespace sglb;
   int rc = 0;

@@ -32,6 +32,13 @@ ARCH_CONFIGS = {
                       num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
                       vocab_size=151936, tie_word_embeddings=False, max_position_embeddings=40960,
                       torch_dtype="bfloat16"),
+    # the per-rank shard of Qwen3-32B under 8-way tensor parallelism as a model of its own (8 query heads, 1 KV head,
+    # intermediate 3200, vocabulary 18992): run on ONE GPU it shows what a rank computes when communication is free
+    "qwen3-32b-tp8-shard": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=5120,
+                                intermediate_size=3200, num_hidden_layers=64, num_attention_heads=8,
+                                num_key_value_heads=1, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
+                                vocab_size=18992, tie_word_embeddings=False, max_position_embeddings=40960,
+                                torch_dtype="bfloat16"),
     "qwen3-8b": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096,
                      intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
                      num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,

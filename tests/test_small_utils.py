@@ -187,3 +187,37 @@ def test_fused_residual_dataflow_is_chosen_per_model():
     m.o_proj.lora = None
     m.down_proj.qweight = object()
     assert model_supports_fused_residual(m)
+
+
+def test_bench_serving_dataset_samplers(tmp_path):
+    import json
+    from sglang_jax_b200 import bench_serving as bs
+    lengths = bs._Lengths(None)
+    sg = tmp_path / "sg.json"
+    sg.write_text(json.dumps([{"conversations": [{"from": "human", "value": f"question number {i} please"},
+                                                 {"from": "gpt", "value": "an answer of six words here"}]}
+                              for i in range(6)] + [{"conversations": [{"from": "human", "value": "x"}]}]))
+    reqs = bs.sample_sharegpt_requests(str(sg), 4, lengths)
+    assert len(reqs) == 4 and all(o == 6 and p.startswith("question") for p, o in reqs)
+    assert bs.sample_sharegpt_requests(str(sg), 4, lengths, fixed_output_len=9)[0][1] == 9
+    cu = tmp_path / "c.jsonl"
+    cu.write_text("\n".join([json.dumps({"prompt": "a b c", "output_len": 7}), json.dumps({"input_ids": [1, 2, 3]}),
+                             json.dumps({"conversations": [{"content": "hi"}, {"content": "hello you"}]})]))
+    assert bs.sample_custom_requests(str(cu), 10, lengths) == [("a b c", 7), ([1, 2, 3], 128), ("hi", 2)]
+    mc = tmp_path / "m.jsonl"
+    mc.write_text("\n".join(json.dumps({"timestamp": 250 * i, "input_length": 600, "output_length": 3,
+                                        "hash_ids": [7, 100 + i]}) for i in range(3)))
+    tr = bs.sample_mooncake_requests(str(mc), 3, 1000, block_tokens=512)
+    assert [(len(a), b, c) for a, b, c in tr] == [(600, 3, 0.0), (600, 3, 0.25), (600, 3, 0.5)]
+    assert tr[0][0][:512] == tr[1][0][:512] and tr[0][0][512:] != tr[1][0][512:]      # shared first block only
+    msgs, out = bs.sample_image_requests(1, 2, "32x16", 8, 4)[0]
+    kinds = [c["type"] for c in msgs[0]["content"]]
+    assert kinds == ["image_url", "image_url", "text"] and out == 4
+    import base64
+    png = base64.b64decode(msgs[0]["content"][0]["image_url"]["url"].split(",", 1)[1])
+    assert png[:8] == b"\x89PNG\r\n\x1a\n" and png[16:24] == (32).to_bytes(4, "big") + (16).to_bytes(4, "big")
+    # peak output throughput: tokens per one-second bucket of chunk arrivals
+    o = bs.RequestFuncOutput(success=True, latency=2.0, ttft=0.1, itl=[0.1] * 9, prompt_len=5, output_len=10, start=0.0,
+                             chunk_times=[0.1 * (i + 1) for i in range(10)])
+    m = bs.calculate_metrics([o], 2.0)
+    assert m["peak_output_throughput"] >= 9 and m["output_throughput"] == 5.0
