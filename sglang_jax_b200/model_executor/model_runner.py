@@ -103,9 +103,17 @@ class ModelRunner:
                 self.model, cap_tokens, self.device, int(getattr(hf, "num_experts_per_tok", None) or 8))
         from ..layers.fused_block import model_supports_fused_residual
         self.fused_residual_ok = model_supports_fused_residual(self.model)
+        self.gemm_plan = None
+        if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "0") == "1" and not is_draft_worker:
+            # measured GEMM plan, kept on disk between runs (counterpart of the reference's compile / AOT caches)
+            from ..ops import native
+            from .tuning_cache import GemmPlan
+            self.gemm_plan = native.gemm_plan = GemmPlan(GemmPlan.default_path(native._LIB_PATH))
         if self.device.type == "cuda" and not server_args.disable_cuda_graph and not is_draft_worker:
             from .cuda_graph_runner import CudaGraphRunner
             self.cuda_graph_runner = CudaGraphRunner(self)
+        if self.gemm_plan is not None:
+            self.gemm_plan.save()
 
     # ------------------------------------------------------------------ memory
     def _free_mem(self) -> int:

@@ -173,6 +173,10 @@ def gemm_scratch(device) -> _GemmScratch:
     return s
 
 
+# measured plan of decode-sized GEMM shapes (model_executor/tuning_cache.GemmPlan), set by the model runner
+gemm_plan = None
+
+
 def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0, out=None):
     K = x.shape[-1]
     N = w.shape[0]
@@ -195,6 +199,10 @@ def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0, out=Non
     if M == 0:
         return out.view(*x.shape[:-1], N)
     sc = gemm_scratch(x.device)
+    if gemm_plan is not None and force_mode < 0 and M <= 256:
+        force_mode = gemm_plan.mode_for(
+            M, N, K, lambda mode: lib().sglb_gemm_bf16(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _p(sc.workspace),
+                                                       sc.bytes, _p(sc.counters), mode, 0, _stream()))
     _check(lib().sglb_gemm_bf16(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _p(sc.workspace), sc.bytes,
                                 _p(sc.counters), force_mode, force_splits, _stream()), "gemm_bf16")
     return out.view(*x.shape[:-1], N)

@@ -221,3 +221,19 @@ def test_bench_serving_dataset_samplers(tmp_path):
                              chunk_times=[0.1 * (i + 1) for i in range(10)])
     m = bs.calculate_metrics([o], 2.0)
     assert m["peak_output_throughput"] >= 9 and m["output_throughput"] == 5.0
+
+
+def test_gemm_plan_is_measured_once_and_persisted(tmp_path):
+    """The tuning cache measures a decode-sized GEMM shape the first time it is met, keeps the winner on disk and
+    answers from the table afterwards (also in a fresh process: a second instance on the same file)."""
+    from sglang_jax_b200.model_executor.tuning_cache import GemmPlan
+    path = str(tmp_path / "plan.json")
+    calls = []
+    plan = GemmPlan(path, measure=False)
+    assert plan.mode_for(128, 5120, 1024, lambda m: calls.append(m)) == -1 and not calls   # nothing known, no measuring
+    plan.table["128x5120x1024"] = 0
+    plan.dirty = True
+    plan.save()
+    again = GemmPlan(path, measure=True)
+    assert again.mode_for(100, 5120, 1024, lambda m: calls.append(m)) == 0 and not calls    # bucket 128, from disk
+    assert again.mode_for(4096, 5120, 1024, lambda m: calls.append(m)) == -1               # prefill sizes: default
