@@ -113,6 +113,55 @@ class PagedAllocator {
     return out;
   }
 
+  // One decode step's batch metadata in one call (the per-request Python loops of the scheduler's hot path):
+  // for every row r with `kv_lens[i]` committed tokens, take the slot of token `kv_lens[i]` (the next slot of the
+  // row's last page, or the first slot of a fresh page when that page is full), write it into the request ->
+  // slot table, and return everything the worker batch needs:
+  //   (out_cache_loc, new_lens, positions, placeholder_ids, delta_rows, delta_pos, delta_ids)
+  // `placeholder_ids[i] = -(row + 1)` are the overlap scheduler's future-token references; the deltas are the
+  // page-table entries this step created.  Returns None, and changes nothing, if the pool lacks the pages.
+  // Counterpart of the reference's prepare_for_decode + get_model_worker_batch arithmetic
+  // (python/sgl_jax/srt/managers/schedule_batch.py:1680-1811, :3034-3293).
+  py::object build_decode_step(py::array_t<int32_t, py::array::c_style> table, i32arr rows, i32arr kv_lens) {
+    const int64_t B = rows.size();
+    if (kv_lens.size() != B || table.ndim() != 2) throw std::invalid_argument("build_decode_step: bad shapes");
+    const int64_t width = table.shape(1), nrows = table.shape(0);
+    int32_t* tab = table.mutable_data();
+    const int32_t *r = rows.data(), *len = kv_lens.data();
+    int64_t need = 0;
+    for (int64_t i = 0; i < B; ++i) {
+      if (r[i] < 0 || r[i] >= nrows || len[i] < 1 || len[i] >= width) throw std::out_of_range("build_decode_step: row / length");
+      need += (len[i] % page_ == 0);
+    }
+    if (need > (int64_t)free_.size()) return py::none();
+    i32arr out(B), new_lens(B), positions(B), placeholders(B), d_rows(need), d_pos(need), d_ids(need);
+    int32_t *o = out.mutable_data(), *nl = new_lens.mutable_data(), *ps = positions.mutable_data(),
+            *ph = placeholders.mutable_data(), *dr = d_rows.mutable_data(), *dp = d_pos.mutable_data(),
+            *di = d_ids.mutable_data();
+    int64_t nd = 0;
+    for (int64_t i = 0; i < B; ++i) {
+      int32_t* row = tab + (int64_t)r[i] * width;
+      int32_t slot;
+      if (len[i] % page_ == 0) {
+        const int32_t page = free_.front();
+        free_.pop_front();
+        slot = page * page_;
+        dr[nd] = r[i];
+        dp[nd] = len[i] / page_;
+        di[nd] = page;
+        ++nd;
+      } else {
+        slot = row[len[i] - 1] + 1;
+      }
+      row[len[i]] = slot;
+      o[i] = slot;
+      nl[i] = len[i] + 1;
+      ps[i] = len[i];
+      ph[i] = -(r[i] + 1);
+    }
+    return py::make_tuple(out, new_lens, positions, placeholders, d_rows, d_pos, d_ids);
+  }
+
   void free_slots(i32arr idx) {
     if (idx.size() == 0) return;
     if (in_group_) {
@@ -582,6 +631,7 @@ PYBIND11_MODULE(_sched_native, m) {
       .def("alloc", &PagedAllocator::alloc)
       .def("alloc_extend", &PagedAllocator::alloc_extend)
       .def("alloc_decode", &PagedAllocator::alloc_decode)
+      .def("build_decode_step", &PagedAllocator::build_decode_step)
       .def("free", &PagedAllocator::free_slots)
       .def("free_group_begin", &PagedAllocator::free_group_begin)
       .def("free_group_end", &PagedAllocator::free_group_end)

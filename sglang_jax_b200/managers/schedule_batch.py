@@ -727,6 +727,36 @@ class ScheduleBatch:
             return
         pool = self.req_to_token_pool
         alloc = self.token_to_kv_pool_allocator
+        if self.enable_overlap and hasattr(alloc, "build_decode_step") and not hasattr(self.tree_cache, "evict_req_swa") \
+                and pool.req_to_token.flags["C_CONTIGUOUS"]:
+            # native fast path: slot choice, request -> slot table writes, positions, future-token placeholders and
+            # page-table deltas of the whole batch in one C++ call
+            rows = np.fromiter((r.req_pool_idx for r in reqs), np.int32, len(reqs))
+            lens = np.fromiter((r.kv_committed_len for r in reqs), np.int32, len(reqs))
+            built = alloc.build_decode_step(pool.req_to_token, rows, lens)
+            if built is None:
+                if self.tree_cache is not None:
+                    self._cache_evict(len(reqs) * self.page_size)
+                built = alloc.build_decode_step(pool.req_to_token, rows, lens)
+                if built is None:
+                    raise RuntimeError("Decode out of memory. Try to lower your batch size.")
+            out, new_lens, _positions, placeholders, d_rows, d_pos, _d_ids = built
+            for r_, p_ in zip(d_rows.tolist(), d_pos.tolist()):
+                pool._dirty.append((r_, p_, p_ + 1))
+            for r in reqs:
+                r.kv_committed_len += 1
+                r.kv_allocated_len = r.kv_committed_len
+            self.input_ids = placeholders
+            self.output_ids = None
+            self.req_pool_indices = rows
+            self.seq_lens = new_lens
+            self.out_cache_loc = out
+            self.prefix_lens = []
+            self.extend_lens = []
+            self.extend_num_tokens = 0
+            self.num_decode_in_mixed = 0
+            self.decoding_reqs = None
+            return
         if self.enable_overlap:
             # The previous step may still be in flight: feed placeholders `-(row + 1)`.  The
             # future-token map slot of a row always holds the latest token sampled for the

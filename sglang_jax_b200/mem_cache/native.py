@@ -51,6 +51,11 @@ class NativePagedAllocator(BaseTokenToKVPoolAllocator):
     def alloc_decode(self, seq_lens, last_loc, dp_rank: int = 0):
         return self._a.alloc_decode(np.asarray(seq_lens, np.int64), np.asarray(last_loc, np.int64))
 
+    def build_decode_step(self, req_to_token: np.ndarray, rows: np.ndarray, kv_lens: np.ndarray):
+        """One decode step's slots, table writes and batch arrays in a single native call
+        (`PagedAllocator::build_decode_step`); None when the pool lacks the pages (nothing changed)."""
+        return self._a.build_decode_step(req_to_token, rows, kv_lens)
+
     def free(self, free_index, dp_rank: int = 0):
         self._a.free(np.asarray(free_index, np.int32).ravel())
 

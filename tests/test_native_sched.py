@@ -163,3 +163,44 @@ def test_engine_tokens_do_not_depend_on_the_implementation(tmp_path, monkeypatch
     kind_p, b1, b2, cached_p = run()
     assert kind_p == ("RadixCache", "PagedTokenToKVPoolAllocator")
     assert a1 == a2 == b1 == b2 and cached_n == cached_p and min(cached_n) > 0
+
+
+def test_native_decode_step_builder_matches_python_arithmetic():
+    """`PagedAllocator.build_decode_step` = last-slot gather + alloc_decode + table writes + page deltas."""
+    import numpy as np
+    from sglang_jax_b200.mem_cache import native as nat
+    if not nat.available():
+        import pytest
+        pytest.skip("native scheduler structures not built")
+    P = 4
+    a = nat.NativePagedAllocator(64 * P, P)
+    b = nat.NativePagedAllocator(64 * P, P)
+    rng = np.random.RandomState(0)
+    table_a = np.zeros((6, 40), np.int32)
+    table_b = np.zeros((6, 40), np.int32)
+    lens = np.array([3, 4, 8, 1, 9], np.int32)          # rows 1 and 2 sit on a page boundary
+    rows = np.array([4, 0, 2, 5, 1], np.int32)
+    for t, al in ((table_a, a), (table_b, b)):
+        for r, n in zip(rows, lens):
+            pre = np.zeros(1, np.int64)
+            got = al.alloc_extend(pre, np.array([n], np.int64), np.array([-1], np.int64), int(n))
+            t[r, :n] = got
+    assert np.array_equal(table_a, table_b)
+    # python statement of the step
+    last = np.array([table_a[r, n - 1] for r, n in zip(rows, lens)], np.int32)
+    want = a.alloc_decode(lens + 1, last)
+    for r, n, loc in zip(rows, lens, want):
+        table_a[r, n] = loc
+    out, new_lens, positions, placeholders, d_rows, d_pos, d_ids = b.build_decode_step(table_b, rows, lens)
+    assert np.array_equal(out, want) and np.array_equal(table_a, table_b)
+    assert new_lens.tolist() == (lens + 1).tolist() and positions.tolist() == lens.tolist()
+    assert placeholders.tolist() == (-(rows + 1)).tolist()
+    assert d_rows.tolist() == [0, 2] and d_pos.tolist() == [1, 2] and d_ids.tolist() == [want[1] // P, want[2] // P]
+    assert a.available_size() == b.available_size()
+    # not enough pages: nothing changes
+    small = nat.NativePagedAllocator(1 * P, P)
+    t = np.zeros((2, 16), np.int32)
+    t[0, :4] = small.alloc(4)
+    before = t.copy()
+    assert small.build_decode_step(t, np.array([0], np.int32), np.array([4], np.int32)) is None
+    assert np.array_equal(t, before) and small.available_size() == 0
