@@ -47,10 +47,14 @@ class EngineBase:
 
 class Engine(EngineBase):
     def __new__(cls, **kwargs):
-        # dp_size > 1: a set of replicas behind a router stands in for the engine
+        # dp_size > 1 runs as data-parallel attention under one scheduler (`managers/dp_scheduler.py`) when the
+        # ranks are processes; in single-process mode, or with SGLB_DP_MODE=replicas, a set of independent
+        # replicas behind a router stands in for the engine
         sa = kwargs.get("server_args")
         dp = sa.dp_size if sa is not None else int(kwargs.get("dp_size", 1) or 1)
-        if dp > 1 and not kwargs.get("_replica"):
+        single = sa.enable_single_process if sa is not None else bool(kwargs.get("enable_single_process", False))
+        replicas = single or os.environ.get("SGLB_DP_MODE", "attention") == "replicas"
+        if dp > 1 and replicas and not kwargs.get("_replica"):
             from ..managers.data_parallel_controller import DataParallelEngine
             if sa is None:
                 kwargs.setdefault("log_level", "error")

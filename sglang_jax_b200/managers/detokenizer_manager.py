@@ -127,7 +127,8 @@ class DetokenizerManager:
             output_token_ids_logprobs_val=recv.output_token_ids_logprobs_val,
             output_token_ids_logprobs_idx=recv.output_token_ids_logprobs_idx,
             output_hidden_states=recv.output_hidden_states, cache_miss_count=recv.cache_miss_count,
-            output_routed_experts=recv.output_routed_experts, spec_verify_ct=recv.spec_verify_ct)
+            output_routed_experts=recv.output_routed_experts, spec_verify_ct=recv.spec_verify_ct,
+            dp_ranks=recv.dp_ranks)
 
     def handle(self, obj):
         if isinstance(obj, BatchTokenIDOut):

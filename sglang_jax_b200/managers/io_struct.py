@@ -291,6 +291,7 @@ class BatchTokenIDOut:
     cache_miss_count: int | None = None
     output_routed_experts: list | None = None
     spec_verify_ct: list[int] | None = None
+    dp_ranks: list[int] | None = None       # data-parallel section of each request (dp_size > 1 only)
 
 
 @dataclass
@@ -318,6 +319,7 @@ class BatchStrOut:
     cache_miss_count: int | None = None
     output_routed_experts: list | None = None
     spec_verify_ct: list[int] | None = None
+    dp_ranks: list[int] | None = None       # data-parallel section of each request (dp_size > 1 only)
 
 
 @dataclass

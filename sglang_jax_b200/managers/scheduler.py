@@ -938,15 +938,28 @@ def run_scheduler_process(server_args, port_args, pipe_writer=None, rank: int = 
         local = rank % max(world_size // max(server_args.nnodes, 1), 1)
         if server_args.device_indexes:
             local = server_args.device_indexes[local]
-        ps.init_distributed(rank, world_size, server_args.device, 1, server_args.ep_size,
+        dp = server_args.dp_size if world_size > 1 else 1
+        ps.init_distributed(rank, world_size, server_args.device, dp, server_args.ep_size,
                             init_method=init_method, local_rank=local, timeout_s=server_args.dist_timeout)
         if rank != 0:
             from .tp_worker import run_tp_follower
             if pipe_writer is not None:
                 pipe_writer.send({"status": "ready"})
-            run_tp_follower(server_args)
+            if dp > 1 and rank % (world_size // dp) == 0:
+                # first rank of a data-parallel section: executes that section's batches for the one scheduler
+                from .dp_scheduler import run_dp_leader
+                run_dp_leader(server_args)
+            else:
+                run_tp_follower(server_args)
             return
-        sched = Scheduler(server_args, port_args)
+        if dp > 1:
+            from .dp_scheduler import DPScheduler, connect_sections
+            from .tp_worker import ModelWorker
+            assert server_args.speculative_algorithm is None and server_args.disaggregation_mode in (None, "null"), \
+                "data-parallel attention runs without speculative decoding and without PD disaggregation"
+            sched = DPScheduler(server_args, port_args, connect_sections(server_args, ModelWorker(server_args)))
+        else:
+            sched = Scheduler(server_args, port_args)
         if pipe_writer is not None:
             pipe_writer.send({"status": "ready", "max_total_num_tokens": sched.max_total_num_tokens,
                               "max_req_input_len": sched.max_req_input_len})

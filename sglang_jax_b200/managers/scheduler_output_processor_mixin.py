@@ -257,6 +257,8 @@ class SchedulerOutputProcessorMixin:
             out.prompt_tokens.append(len(req.origin_input_ids))
             out.completion_tokens.append(len(out_ids))
             out.cached_tokens.append(req.cached_tokens)
+            if getattr(self, "section_rank", None) is not None:
+                out.dp_ranks = (out.dp_ranks or []) + [self.section_rank]
             if return_logprob:
                 first = not req.input_logprob_sent
                 if req.return_logprob and first and req.input_token_logprobs_val is not None:

@@ -528,6 +528,8 @@ class TokenizerManager:
                     meta["routed_experts"] = recv.output_routed_experts[i]
                 if recv.spec_verify_ct:
                     meta["spec_verify_ct"] = recv.spec_verify_ct[i]
+                if recv.dp_ranks:
+                    meta["dp_rank"] = recv.dp_ranks[i]
                 if recv.cache_miss_count is not None:
                     meta["cache_miss_count"] = recv.cache_miss_count
                 if self.server_args.stream_output and fr is None:

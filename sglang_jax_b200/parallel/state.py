@@ -113,8 +113,9 @@ def init_distributed(rank: int, world_size: int, device: str = "cuda", dp_size: 
                 if g is not None:
                     st.dp = g
         if ep_size > 1:
-            assert ep_size == world_size, "expert parallelism spans all devices of the replica set"
-            st.ep = st.world
+            # experts span the devices of one data-parallel section (all devices when there is one section)
+            assert ep_size == tensor, "expert parallelism spans all devices of a data-parallel section"
+            st.ep = st.tp if dp_size > 1 else st.world
     st.initialized = True
     _STATE = st
     return st

@@ -202,9 +202,10 @@ class StepChannel:
             self.ring.close()
 
     # ------------------------------------------------------------------ followers
-    def recv(self, poll_s: float = 1.0, on_idle=None):
+    def recv(self, poll_s: float = 1.0, on_idle=None, block: bool = True):
         """Next message from rank 0.  Waits in `poll_s` slices (calling `on_idle()` between them);
-        raises `EOFError` once rank 0 closed the channel."""
+        raises `EOFError` once rank 0 closed the channel.  `block=False` (ring transport only) returns `None`
+        when no message has started to arrive within `poll_s`."""
         if self.ring is None:
             return ps.broadcast_object(None, src=0, group=self.group)
         parts = []
@@ -213,6 +214,8 @@ class StepChannel:
             if got is None:
                 if self.ring.closed():
                     raise EOFError("step channel closed by rank 0")
+                if not block and not parts:
+                    return None
                 if on_idle is not None:
                     on_idle()
                 continue
