@@ -89,6 +89,18 @@ def bench_gemm():
         tb = timeit(lambda: native.linear(x, w))
         byts = 1.0 * (M * K + N * K) + 2.0 * M * N
         print(f"{f'{M}x{N}x{K}':>28} {label:>22} {t:9.4f} {2.0 * M * N * K / t / 1e9:9.1f} {byts / t / 1e6:8.0f} {tb:9.4f}")
+    print(f"{'fp8 e4m3 (1x128 activation groups, 128x128 weight blocks)':>51} {'fp8 ms':>9} {'TFLOP/s':>9} {'GB/s':>8} {'quant ms':>9}")
+    for M, N, K, label in [(8192, 7168, 2048, "deepseek o_proj"), (8192, 4096, 7168, "deepseek up"),
+                           (4096, 10240, 5120, "qkv prefill 4k"), (128, 7168, 18432, "deepseek down decode"),
+                           (128, 51200, 5120, "gate_up decode tp1")]:
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        wq = (torch.randn(N, K, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+        sw = torch.rand((N + 127) // 128, K // 128, device="cuda") + 0.5
+        xq, sx = native.quant_fp8_group128(x)
+        t = timeit(lambda: native.gemm_fp8_block(xq, sx, wq, sw))
+        tq = timeit(lambda: native.quant_fp8_group128(x))
+        byts = 1.0 * (M * K + N * K) + 2.0 * M * N
+        print(f"{f'{M}x{N}x{K}':>28} {label:>22} {t:9.4f} {2.0 * M * N * K / t / 1e9:9.1f} {byts / t / 1e6:8.0f} {tq:9.4f}")
     torch.cuda.synchronize()
     native.check_status()
     print(f"(roofline = slower of FLOPs / {tf} TFLOP/s and bytes / {hbm} GB/s, {src})")

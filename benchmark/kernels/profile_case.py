@@ -2,7 +2,7 @@
 """One small, self-terminating case per kernel for `ncu` captures (inputs larger than L2, a few
 hundred MB on the device, a handful of launches).
 
-    python benchmark/kernels/profile_case.py gemm_prefill|gemm_decode|attn_decode|attn_extend|sampling|gemm_fp8|moe_fp8
+    python benchmark/kernels/profile_case.py gemm_prefill|gemm_decode|attn_decode|attn_extend|sampling|gemm_fp8|gemm_fp8_block|moe_fp8
 """
 
 import os
@@ -62,6 +62,14 @@ def main():
         sx, sw = torch.rand(M, device="cuda") + 0.5, torch.rand(N, device="cuda") + 0.5
         for _ in range(n):
             native.gemm_fp8(xq, wq, sx, sw)
+    elif case == "gemm_fp8_block":
+        M, N, K = 4096, 7168, 4096
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        wq = (torch.randn(N, K, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+        sw = torch.rand((N + 127) // 128, K // 128, device="cuda") + 0.5
+        for _ in range(n):
+            xq, sx = native.quant_fp8_group128(x)
+            native.gemm_fp8_block(xq, sx, wq, sw)
     elif case == "moe_fp8":
         from sglang_jax_b200.layers.moe import FusedMoE
         from sglang_jax_b200.ops import reference

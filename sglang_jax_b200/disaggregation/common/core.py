@@ -37,6 +37,8 @@ class CommonKVSender(KVSender):
     def send(self) -> None:
         """Publish the pages; the transfer completes when the decode side acknowledges."""
         self.mgr.backend.register(self.transfer_id, self.pages, self.meta)
+        if self.mgr.mirror is not None:
+            self.mgr.mirror.register(self.transfer_id, self.pages, self.meta)
         self.t_send = time.monotonic()
         self.state.transition(KVPoll.TRANSFERRING)
         self.mgr._track_sender(self)
@@ -87,9 +89,19 @@ class CommonKVReceiver(KVReceiver):
         if self.state.state.terminal:
             return
         self.state.transition(KVPoll.TRANSFERRING)
+        mirror = self.mgr.mirror
         try:
+            if mirror is not None:
+                # the follower ranks pull their shards from the prefill ranks of the same index meanwhile
+                mirror.pull(self.transfer_id, self.dst_pages, self.mgr.backend.query_peers(self.prefill_addr))
             self.meta = self.mgr.backend.pull(self.prefill_addr, self.transfer_id, self.dst_pages)
+            if mirror is not None:
+                bad = mirror.wait(self.transfer_id)
+                if bad:
+                    raise RuntimeError(bad)
         except Exception as e:  # noqa: BLE001
+            if mirror is not None:
+                mirror.drop(self.transfer_id)
             self.state.fail(str(e))
             metrics.count_transfer("decode", "failed")
             self._ack(False, str(e))
@@ -123,8 +135,9 @@ class CommonKVReceiver(KVReceiver):
 class CommonKVManager(KVManager):
     def __init__(self, role: str, backend, page_bytes: int, host: str = "127.0.0.1", side_channel_port: int = 0,
                  secret: str | None = None, num_pull_workers: int = 4, pull_timeout: float = 30.0,
-                 ack_timeout: float = 60.0, reaper_interval: float = 5.0):
+                 ack_timeout: float = 60.0, reaper_interval: float = 5.0, mirror=None):
         assert role in ("prefill", "decode")
+        self.mirror = mirror      # `tp_mirror.RankMirror` when the engine has more than one tensor rank
         self.role, self.backend, self.page_bytes = role, backend, page_bytes
         self.pull_timeout, self.ack_timeout = pull_timeout, ack_timeout
         self.senders: dict[str, CommonKVSender] = {}
@@ -178,6 +191,9 @@ class CommonKVManager(KVManager):
             self.senders.pop(s.transfer_id, None)
         if s.transfer_id:
             self.backend.unregister(s.transfer_id)
+            if self.mirror is not None:
+                # runs on the scheduler thread, before the request's pages are released
+                self.mirror.unregister(s.transfer_id)
 
     def _forget_receiver(self, r: CommonKVReceiver):
         with self.lock:
@@ -254,5 +270,7 @@ class CommonKVManager(KVManager):
         if self.ack_listener is not None:
             self.ack_listener.stop()
         self.ack_sender.close()
+        if self.mirror is not None:
+            self.mirror.stop()
         if hasattr(self.backend, "stop"):
             self.backend.stop()

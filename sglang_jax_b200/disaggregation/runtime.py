@@ -42,13 +42,22 @@ def build_kv_manager(scheduler, role: str, engine_id: str):
     backend = ZmqTransferBackend(pool, host, sa.disaggregation_transfer_port if role == "prefill" else 0,
                                  pick_transfer_mode(sa, on_gpu), secret, sa.disaggregation_pull_timeout_seconds)
     transfer_addr = backend.start() if role == "prefill" else None
+    mirror = None
+    worker = scheduler.tp_worker
+    if getattr(worker, "tp_size", 1) > 1 and hasattr(worker, "send_control"):
+        from .tp_mirror import RankMirror
+        mirror = RankMirror(worker, role, host, secret, backend.mode, sa.disaggregation_pull_timeout_seconds, transfer_addr)
+        if role == "prefill":
+            backend.peer_addrs = mirror.addrs
     mgr = CommonKVManager(role, backend, sum(layout["page_bytes_per_layer"]), host,
                           sa.disaggregation_side_channel_port if role == "prefill" else 0, secret,
                           sa.disaggregation_channel_number, sa.disaggregation_pull_timeout_seconds,
-                          sa.disaggregation_ack_timeout_seconds, sa.disaggregation_orphan_reaper_interval_seconds)
+                          sa.disaggregation_ack_timeout_seconds, sa.disaggregation_orphan_reaper_interval_seconds,
+                          mirror=mirror)
     hb = None
     if role == "prefill":
         info = dict(layout, engine_id=engine_id, tp_rank=0, transfer_addr=transfer_addr, ack_addr=mgr.ack_addr,
+                    transfer_addrs=backend.peer_addrs or [transfer_addr],
                     http_url=f"http://{sa.host}:{sa.port}", transfer_mode=backend.mode)
         client = BootstrapClient(sa.disaggregation_bootstrap_url, secret, sa.disaggregation_bootstrap_timeout_seconds)
         hb = HeartbeatDaemon(client, info).start()

@@ -59,6 +59,8 @@ class ZmqTransferBackend:
         self.bytes_sent = 0
         self.bytes_received = 0
         self.addr: str | None = None
+        self.peer_addrs: list[str] | None = None       # set on rank 0 of a tensor-parallel prefill engine
+        self._peers_cache: dict[str, list[str]] = {}
 
     # ------------------------------------------------------------------ prefill side
     def start(self) -> str:
@@ -102,6 +104,10 @@ class ZmqTransferBackend:
                 self._sock.send_multipart([ident, b"error", b"unauthorized"])
                 continue
             req = json.loads(body)
+            if req.get("op") == "peers":
+                # transfer address of every tensor rank of this engine, rank 0 (this server) first
+                self._sock.send_multipart([ident, b"ok", json.dumps(self.peer_addrs or [self.addr]).encode()])
+                continue
             with self.lock:
                 ent = self.registered.get(req["transfer_id"])
             if ent is None:
@@ -179,6 +185,27 @@ class ZmqTransferBackend:
                                         f"reserved {len(dst_pages)}")
                 self._scatter(addr, head, frames[2:], np.asarray(dst_pages, np.int64))
                 return head
+        finally:
+            sock.close()
+
+    def query_peers(self, addr: str) -> list[str]:
+        """Transfer addresses of all tensor ranks of the prefill engine whose rank 0 listens at `addr`."""
+        if addr in self._peers_cache:
+            return self._peers_cache[addr]
+        import zmq
+        sock = (self._ctx or zmq.Context.instance()).socket(zmq.DEALER)
+        sock.setsockopt(zmq.LINGER, 0)
+        sock.connect(f"tcp://{addr}")
+        try:
+            body = json.dumps({"op": "peers"}).encode()
+            sock.send_multipart([pd_auth.sign(body, self.secret), body])
+            if not sock.poll(int(self.pull_timeout * 1000)):
+                raise TransferError(f"{addr} did not answer the peer-address query")
+            frames = sock.recv_multipart()
+            if frames[0] != b"ok":
+                raise TransferError(f"peer-address query refused: {frames[1].decode(errors='replace')}")
+            self._peers_cache[addr] = json.loads(frames[1])
+            return self._peers_cache[addr]
         finally:
             sock.close()
 

@@ -274,6 +274,10 @@ def run_tp_follower(server_args, worker: ModelWorker | None = None, on_message=N
                     LoRARef(lora_id=r.lora_id, lora_name=r.lora_name, lora_path=r.lora_path))
             elif msg.kind == "unload_lora":
                 worker.model_runner.lora_manager.unload_adapter(msg.payload.lora_id)
+            elif msg.kind.startswith("pd_"):
+                # KV hand-over of this rank's shard between a prefill and a decode engine
+                from ..disaggregation.tp_mirror import handle_follower_control
+                handle_follower_control(worker, msg.kind, msg.payload)
             continue
         worker.model_runner.forward(msg)
     return worker

@@ -48,10 +48,14 @@ class CudaGraphRunner:
         self.graphs: dict = {}
         self.outputs: dict = {}
         self.seed_rng = np.random.default_rng(int(getattr(sa, "random_seed", 0) or 0) + 7919)
-        # sampled steps gather the vocabulary shards with a library all-gather; that variant is captured for
-        # single-GPU engines only (tensor-parallel engines sample eagerly)
+        # sampled steps need the full-vocabulary logits on every tensor rank: under tensor parallelism they are
+        # captured when the peer-store gather of the fused-communication context can serve the bucket (its
+        # symmetric result buffer is allocated by the eager warm-up step, never inside a capture); without that
+        # context tensor-parallel engines sample eagerly
         from ..parallel import state as ps
-        self.sample_in_graph = ps.tp_size() == 1
+        comm = ps.get_state().fused_comm
+        self.sample_in_graph = ps.tp_size() == 1 or comm is not None
+        self.sample_max_bs = self.max_bs if ps.tp_size() == 1 or comm is None else min(self.max_bs, comm.LOGITS_GATHER_ROWS)
         self.pool = None
         self.stream = torch.cuda.Stream(device=dev)
         self.copy_event: torch.cuda.Event | None = None
@@ -134,6 +138,8 @@ class CudaGraphRunner:
         with torch.inference_mode():
             for sampled in ((False, True) if self.sample_in_graph else (False,)):
                 for bs in reversed(self.buckets):
+                    if sampled and bs > self.sample_max_bs:
+                        continue
                     torch.cuda.synchronize()
                     s = self.stream
                     s.wait_stream(torch.cuda.current_stream())
@@ -188,15 +194,16 @@ class CudaGraphRunner:
         return (self.enabled and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
                 and not batch.return_logprob and batch.capture_hidden_mode == 0 and batch.spec_info is None
                 and (si is None or (si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None
-                                    and (si.is_all_greedy or self._can_sample_in_graph(si))))
+                                    and (si.is_all_greedy or self._can_sample_in_graph(si, len(batch.req_pool_indices)))))
                 and (batch.page_delta_rows is None or len(batch.page_delta_rows) <= MAX_PAGE_DELTAS)
                 and not any(batch.lora_ids or []) and getattr(batch, "mrope_positions", None) is None)
 
-    def _can_sample_in_graph(self, si) -> bool:
+    def _can_sample_in_graph(self, si, bs: int) -> bool:
         """Sampled steps run in a graph when no request carries its own seed (seeded and deterministic runs keep
         the reference's hash, which the eager sampler applies) and the logits are fp32 / bf16 on this device."""
         sa = self.runner.server_args
         return (self.sample_in_graph and si.sampling_seeds is None
+                and self.buckets[bisect.bisect_left(self.buckets, bs)] <= self.sample_max_bs
                 and not getattr(sa, "enable_deterministic_sampling", False) and si.positions is not None)
 
     def replay(self, batch: ModelWorkerBatch):

@@ -274,3 +274,46 @@ def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
         prefill.shutdown()
         decode.shutdown()
         srv.stop()
+
+
+def test_tensor_parallel_engines_hand_over_every_ranks_shard(tmp_path):
+    """Prefill and decode engines with two tensor ranks each (gloo processes): rank r of the decode engine pulls the
+    KV heads of its shard from rank r of the prefill engine; the decoded tokens equal a single engine's."""
+    from sglang_jax_b200.entrypoints.engine import Engine
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import write_tiny_qwen3_checkpoint
+    ckpt = write_tiny_qwen3_checkpoint(str(tmp_path / "m"))
+    rng = np.random.RandomState(2)
+    prompts = [rng.randint(5, 1000, size=n).tolist() for n in (40, 17, 70, 33)]
+    sp = {"temperature": 0.0, "max_new_tokens": 8, "ignore_eos": True}
+    common = dict(model_path=ckpt, device="cpu", page_size=16, skip_tokenizer_init=True, max_total_tokens=2048,
+                  dtype="float32", log_level="error", watchdog_timeout=0)
+    ps.reset_state()
+    plain = Engine(**common, enable_single_process=True)
+    try:
+        want = [o["output_ids"] for o in plain.generate(input_ids=prompts, sampling_params=sp)]
+    finally:
+        plain.shutdown()
+    srv = BootstrapServer(port=get_free_port(), secret="pd").start()
+    pd_kw = dict(disaggregation_bootstrap_url=srv.url, disaggregation_shared_secret="pd",
+                 disaggregation_transfer_port=0, disaggregation_side_channel_port=0, tp_size=2)
+    prefill = Engine(**common, disaggregation_mode="prefill", chunked_prefill_size=32, **pd_kw)
+    decode = Engine(**common, disaggregation_mode="decode", **pd_kw)
+    try:
+        res = {}
+
+        def run(name, eng):
+            res[name] = eng.generate(input_ids=prompts, sampling_params=sp, bootstrap_room=[21, 22, 23, 24])
+
+        ts = [threading.Thread(target=run, args=("decode", decode)), threading.Thread(target=run, args=("prefill", prefill))]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout=180)
+        assert "decode" in res and "prefill" in res
+        assert [o["output_ids"] for o in res["decode"]] == want
+        assert [o["output_ids"] for o in res["prefill"]] == [w[:1] for w in want]
+    finally:
+        prefill.shutdown()
+        decode.shutdown()
+        srv.stop()

@@ -201,8 +201,16 @@ def _engine(rank, world, fused, biased=False):
         # the same prompts again with log-probabilities: every candidate's value at the first decoded position
         lp = eng.generate(input_ids=prompts, sampling_params=dict(sp, max_new_tokens=2), return_logprob=True,
                           top_logprobs_num=5)
+        # sampled steps: a vanishing nucleus keeps only the best token, so the draws must follow the greedy run; with
+        # the fused context they replay captured graphs (peer-store logits gather + sampling kernel inside)
+        smp = eng.generate(input_ids=prompts, sampling_params=dict(sp, temperature=0.8, top_p=1e-6))
         torch.cuda.synchronize()
         native.check_status()
+        gr = eng.scheduler.tp_worker.model_runner.cuda_graph_runner
+        assert any(isinstance(k, tuple) for k in gr.graphs) == fused, list(gr.graphs)
+        flat_g = [t for o in outs for t in o["output_ids"]]
+        flat_s = [t for o in smp for t in o["output_ids"]]
+        assert sum(a == b for a, b in zip(flat_g, flat_s)) / len(flat_g) >= 0.7, (flat_g, flat_s)
         tops = [[(t[1], t[0]) for t in o["meta_info"]["output_top_logprobs"][0]] for o in lp]
         return [o["output_ids"] for o in outs], tops
     finally:
