@@ -2,7 +2,7 @@
 """One small, self-terminating case per kernel for `ncu` captures (inputs larger than L2, a few
 hundred MB on the device, a handful of launches).
 
-    python benchmark/kernels/profile_case.py gemm_prefill|gemm_decode|attn_decode|attn_extend|sampling|gemm_fp8|gemm_fp8_block|moe_fp8
+    python benchmark/kernels/profile_case.py gemm_prefill|gemm_decode|attn_decode|attn_extend|sampling|gemm_fp8|gemm_fp8_block|moe_fp8|decode_step:<architecture>
 """
 
 import os
@@ -83,6 +83,21 @@ def main():
         ids = ids.int()
         for _ in range(n):
             moe(x, tw, ids)
+    elif case.startswith("decode_step:"):
+        # whole decode steps of a named architecture with random weights straight on the model runner (captured CUDA
+        # graph replays): `decode_step:qwen3-32b-tp8-shard [steps] [batch] [context]`; meant for a launch list
+        import tempfile
+        from sglang_jax_b200.bench_one_batch import run_one_batch
+        from sglang_jax_b200.server_args import ServerArgs
+        from sglang_jax_b200.utils.tiny_models import ARCH_CONFIGS, write_config_only
+        B = int(sys.argv[3]) if len(sys.argv) > 3 else 128
+        ctx = int(sys.argv[4]) if len(sys.argv) > 4 else 1024
+        path = write_config_only(tempfile.mkdtemp(prefix="sglb_case_"), dict(ARCH_CONFIGS[case.split(":", 1)[1]]))
+        sa = ServerArgs(model_path=path, load_format="dummy", device="cuda", dtype="bfloat16", page_size=64,
+                        skip_tokenizer_init=True, max_running_requests=B, cuda_graph_max_bs=B,
+                        max_total_tokens=(B + 2) * (ctx + 64 * 3), mem_fraction_static=0.8, log_level="error",
+                        chunked_prefill_size=-1, max_prefill_tokens=B * ctx + 64)
+        print(run_one_batch(sa, B, ctx, n))
     else:
         raise SystemExit(f"unknown case {case}")
     torch.cuda.synchronize()

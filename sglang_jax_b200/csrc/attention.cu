@@ -582,24 +582,38 @@ paged_extend_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p
 // Reference contract: python/sgl_jax/srt/kernels/ragged_paged_attention/ragged_paged_attention_v3.py:1667.
 // ---------------------------------------------------------------------------------------------
 namespace tc {
-constexpr int BQ2 = 128, BKV = 128, HD = 128;
-constexpr int kBlk = 128 * 128;                    // bytes of one [128 rows][64 bf16] swizzled block
+// Two CTAs share an SM (113 KB of shared memory and 256 columns of tensor memory each): while one CTA's four
+// softmax warps work through their exponentials, the other CTA's products keep the tensor pipe busy.
+constexpr int BQ2 = 128, BKV = 64, HD = 128;
+constexpr int kBlk = 128 * 128;                    // bytes of one [128 rows][64 bf16] swizzled block (Q halves, P)
+constexpr int kBlkKV = BKV * 128;                  // bytes of one [64 keys][64 bf16] swizzled block
 constexpr int kQBytes = 2 * kBlk;
-constexpr int kKVStage = 4 * kBlk;                 // K (2 blocks by dim half) + V (2 blocks by dim half)
+constexpr int kKVStage = 4 * kBlkKV;               // K (2 blocks by dim half) + V (2 blocks by dim half)
 constexpr int kStagesKV = 2;
-constexpr int kPBytes = 2 * kBlk;
-constexpr int kSmem = kQBytes + kStagesKV * kKVStage + kPBytes + 256 + 1024;
+constexpr int kPBytes = kBlk;
+constexpr int kSmem = kQBytes + kStagesKV * kKVStage + kPBytes + 256 + 768;   // 113 KB: two CTAs per SM
+constexpr int kTmemCols = 256;                     // S (2 x 64 columns) + O (128 columns)
 constexpr int kThreadsTc = 192;
 constexpr float kRescale = 8.f;                    // raise the running max only past 2^8
 
 struct Bars {
-  uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_free[2], p_ready, pv_done;
+  // p_ready[i] / pv_done[i] serve the tiles with (tile & 1) == i: each completes once per two tiles, so a waiter is
+  // never more than one phase behind the barrier it waits on
+  // K and V of a stage have barriers of their own: the K half is free again as soon as Q K^T of its tile is done,
+  // one whole tile before the V half, so the loads of the next keys start that much earlier
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_ready[2], pv_done[2];
   uint32_t tmem_slot;
   int abort_flag;
 };
 }  // namespace tc
 
-__global__ void __launch_bounds__(tc::kThreadsTc, 1)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(tc::kThreadsTc, 2)
 paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_q,
                        const AttnParams p) {
   using namespace tc;
@@ -610,6 +624,11 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
   uint8_t* p_s = kv_s + kStagesKV * kKVStage;
   Bars* bars = reinterpret_cast<Bars*>(p_s + kPBytes);
   volatile int* abort_flag = &bars->abort_flag;
+  if (reinterpret_cast<uint8_t*>(bars) + sizeof(Bars) > smem_raw + kSmem) {
+    // the dynamic window started less aligned than the carve-up allows for: refuse, uniformly, before any barrier
+    if (threadIdx.x == 0) report(p.status, kBadArgument, blockIdx.x, 9000);
+    return;
+  }
 
   // (sequence, 128-row query tile) of this CTA
   int b = 0, tile_in_seq = 0;
@@ -648,25 +667,27 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
     prefetch_tmap(&tmap_q);
     mbar_init(smem_u32(&bars->q_full), 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&bars->kv_full[i]), 1);
-      mbar_init(smem_u32(&bars->kv_empty[i]), 1);
+      mbar_init(smem_u32(&bars->k_full[i]), 1);
+      mbar_init(smem_u32(&bars->k_empty[i]), 1);
+      mbar_init(smem_u32(&bars->v_full[i]), 1);
+      mbar_init(smem_u32(&bars->v_empty[i]), 1);
       mbar_init(smem_u32(&bars->s_full[i]), 1);
-      mbar_init(smem_u32(&bars->s_free[i]), 128);
+      mbar_init(smem_u32(&bars->s_free[i]), 4);       // one arrival per softmax warp
+      mbar_init(smem_u32(&bars->p_ready[i]), 4);
+      mbar_init(smem_u32(&bars->pv_done[i]), 1);
     }
-    mbar_init(smem_u32(&bars->p_ready), 128);
-    mbar_init(smem_u32(&bars->pv_done), 1);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&bars->tmem_slot), 512);
+    tmem_alloc(smem_u32(&bars->tmem_slot), kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;          // S buffers at columns 0 and 128, O at 256
+  const uint32_t tmem_o = tmem_base + 2 * BKV;      // S buffers at columns 0 and 64, O at 128
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -677,30 +698,37 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
       tma_load_2d(smem_u32(q_s + kBlk), &tmap_q, qb, hq * HD + 64, q_begin + q0);
       const int run = p.page_size < 64 ? p.page_size : 64;       // tokens per TMA box
       const int n_runs = BKV / run;
-      for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
+      // one half (kv = 0: keys, 1: values) of tile j into its stage; false when the wait for the slot ran out
+      auto load_half = [&](int j, int kv) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(smem_u32(&bars->kv_empty[st]), ((j >> 1) & 1) ^ 1)) {
+        uint64_t* empty = kv == 0 ? &bars->k_empty[st] : &bars->v_empty[st];
+        uint64_t* full = kv == 0 ? &bars->k_full[st] : &bars->v_full[st];
+        if (!mbar_wait(smem_u32(empty), ((j >> 1) & 1) ^ 1)) {
           report(p.status, kTimeoutEmptyBarrier, b, j);
           *abort_flag = 1;
-          break;
+          return false;
         }
-        const uint32_t fb = smem_u32(&bars->kv_full[st]);
-        mbar_expect_tx(fb, kKVStage);
-        const uint32_t base = smem_u32(kv_s + st * kKVStage);
+        const uint32_t fb = smem_u32(full);
+        mbar_expect_tx(fb, 2 * kBlkKV);
+        const uint32_t base = smem_u32(kv_s + st * kKVStage) + kv * 2 * kBlkKV;
         for (int r = 0; r < n_runs; ++r) {
           const int tok = j * BKV + r * run;
           int pg = tok / p.page_size;
           if (pg >= p.max_pages) pg = p.max_pages - 1;
           const int page = pt_row[pg];
           const int off = tok - (tok / p.page_size) * p.page_size;
+          const int row = ((page * 2 + kv) * p.Hkv + kvh) * p.page_size + off;
 #pragma unroll
-          for (int kv = 0; kv < 2; ++kv) {
-            const int row = ((page * 2 + kv) * p.Hkv + kvh) * p.page_size + off;
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-              tma_load_2d(base + (kv * 2 + h) * kBlk + r * run * 128, &tmap_kv, fb, h * 64, row);
-          }
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(base + h * kBlkKV + r * run * 128, &tmap_kv, fb, h * 64, row);
         }
+        return true;
+      };
+      // order of slot availability: K(j + 1) frees after Q K^T (j - 1), V(j) after P V (j - 2), which comes later
+      bool fed = load_half(0, 0);
+      for (int j = 0; fed && j < n_tiles && !*abort_flag; ++j) {
+        if (j + 1 < n_tiles) fed = load_half(j + 1, 0);
+        if (fed) fed = load_half(j, 1);
       }
     }
   } else if (warp == 1) {
@@ -717,25 +745,29 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
       const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
       auto issue_pv = [&](int i) -> bool {
         // P_i is in shared memory (and O has been rescaled if that was due)
-        if (!mbar_wait(smem_u32(&bars->p_ready), i & 1)) {
+        if (!mbar_wait(smem_u32(&bars->p_ready[i & 1]), (i >> 1) & 1)) {
           report(p.status, kTimeoutTmemFull, b, 1000 + i);
           return false;
         }
+        if (!mbar_wait(smem_u32(&bars->v_full[i & 1]), (i >> 1) & 1)) {
+          report(p.status, kTimeoutFullBarrier, b, 5000 + i);
+          return false;
+        }
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(kv_s + (i & 1) * kKVStage) + 2 * kBlk;
+        const uint32_t v_addr = smem_u32(kv_s + (i & 1) * kKVStage) + 2 * kBlkKV;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(p_addr + (kk >> 2) * kBlk) + 2 * (kk & 3);
-          const uint64_t db = make_smem_desc_sw128_mn(v_addr + kk * 16 * 128, kBlk);
+          const uint64_t da = make_smem_desc_sw128(p_addr) + 2 * kk;
+          const uint64_t db = make_smem_desc_sw128_mn(v_addr + kk * 16 * 128, kBlkKV);
           umma_bf16(tmem_o, da, db, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(smem_u32(&bars->kv_empty[i & 1]));
-        umma_commit(smem_u32(&bars->pv_done));
+        umma_commit(smem_u32(&bars->v_empty[i & 1]));
+        umma_commit(smem_u32(&bars->pv_done[i & 1]));
         return true;
       };
       for (int j = 0; ok && j < n_tiles && !*abort_flag; ++j) {
         const int st = j & 1;
-        if (!mbar_wait(smem_u32(&bars->kv_full[st]), (j >> 1) & 1) ||
+        if (!mbar_wait(smem_u32(&bars->k_full[st]), (j >> 1) & 1) ||
             !mbar_wait(smem_u32(&bars->s_free[st]), ((j >> 1) & 1) ^ 1)) {
           report(p.status, kTimeoutFullBarrier, b, j);
           ok = false;
@@ -746,9 +778,10 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint64_t da = make_smem_desc_sw128(q_addr + (kk >> 2) * kBlk) + 2 * (kk & 3);
-          const uint64_t db = make_smem_desc_sw128(k_addr + (kk >> 2) * kBlk) + 2 * (kk & 3);
+          const uint64_t db = make_smem_desc_sw128(k_addr + (kk >> 2) * kBlkKV) + 2 * (kk & 3);
           umma_bf16(tmem_base + st * BKV, da, db, idesc_s, kk > 0 ? 1u : 0u);
         }
+        umma_commit(smem_u32(&bars->k_empty[st]));
         umma_commit(smem_u32(&bars->s_full[st]));
         if (j >= 1) ok = issue_pv(j - 1);
       }
@@ -767,43 +800,39 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
-      if (!mbar_wait(smem_u32(&bars->s_full[st]), (j >> 1) & 1)) {
+      // (votes keep the warp's control flow uniform: one lane per warp arrives on the barriers below)
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->s_full[st]), (j >> 1) & 1))) {
         report(p.status, kTimeoutTmemFull, b, j);
         *abort_flag = 1;
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      uint32_t v0[32], v1[32], v2[32], v3[32];
+      uint32_t v0[32], v1[32];
       const uint32_t s_addr = tmem_base + lane_base + st * BKV;
       tmem_ld32(s_addr, v0);
       tmem_ld32(s_addr + 32, v1);
-      tmem_ld32(s_addr + 64, v2);
-      tmem_ld32(s_addr + 96, v3);
       tmem_ld_wait();
       // S_j is in registers: the MMA warp may overwrite this S buffer with tile j + 2
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bars->s_free[st]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->s_free[st]));
       const int kv0 = j * BKV;
       const int nvalid = kmax - kv0 + 1;                            // keys [kv0, kv0 + nvalid) are visible
       float mx = -INFINITY;
       if (nvalid >= BKV) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e)
-          mx = fmaxf(mx, fmaxf(fmaxf(__uint_as_float(v0[e]), __uint_as_float(v1[e])),
-                               fmaxf(__uint_as_float(v2[e]), __uint_as_float(v3[e]))));
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[e]), __uint_as_float(v1[e])));
       } else {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           if (e < nvalid) mx = fmaxf(mx, __uint_as_float(v0[e]));
           if (e + 32 < nvalid) mx = fmaxf(mx, __uint_as_float(v1[e]));
-          if (e + 64 < nvalid) mx = fmaxf(mx, __uint_as_float(v2[e]));
-          if (e + 96 < nvalid) mx = fmaxf(mx, __uint_as_float(v3[e]));
         }
       }
       mx *= scale_log2;
       // the previous P V product must be done before P is overwritten (and before O may be rescaled)
-      if (j >= 1 && !mbar_wait(smem_u32(&bars->pv_done), (j - 1) & 1)) {
+      if (j >= 1 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->pv_done[(j - 1) & 1]), ((j - 1) >> 1) & 1))) {
         report(p.status, kTimeoutTmemFull, b, 2000 + j);
         *abort_flag = 1;
         ok = false;
@@ -835,36 +864,35 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
       float sum = 0.f;
       uint8_t* prow = p_s + row * 128;
       const int sw = row & 7;
+      const bool full = nvalid >= BKV;                  // no key of this tile is masked for this row
       auto emit = [&](const uint32_t (&v)[32], int cbase) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float e8[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int key = cbase * 8 + c * 8 + e;
-            float pv = exp2f(fmaf(__uint_as_float(v[c * 8 + e]), scale_log2, -m_used));
-            if (key >= nvalid) pv = 0.f;
+            float pv = ex2_approx(fmaf(__uint_as_float(v[c * 8 + e]), scale_log2, -m_used));
+            if (!full && cbase * 8 + c * 8 + e >= nvalid) pv = 0.f;
             e8[e] = pv;
-            sum += pv;
           }
-          const int chunk = cbase + c;                  // 0..15 over the 128 keys
+          sum += ((e8[0] + e8[1]) + (e8[2] + e8[3])) + ((e8[4] + e8[5]) + (e8[6] + e8[7]));
+          const int chunk = cbase + c;                  // 0..7 over the 64 keys
           const uint4 packed = make_uint4(pack_bf16(e8[0], e8[1]), pack_bf16(e8[2], e8[3]), pack_bf16(e8[4], e8[5]),
                                           pack_bf16(e8[6], e8[7]));
-          *reinterpret_cast<uint4*>(prow + (chunk >> 3) * kBlk + (((chunk & 7) ^ sw) << 4)) = packed;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ sw) << 4)) = packed;
         }
       };
       emit(v0, 0);
       emit(v1, 4);
-      emit(v2, 8);
-      emit(v3, 12);
       l += sum;
       // make the generic-proxy writes visible to the tensor core's async proxy, then hand P over
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bars->p_ready));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready[st]));
     }
     // epilogue: O / l
-    if (ok && mbar_wait(smem_u32(&bars->pv_done), (n_tiles - 1) & 1)) {
+    if (ok && mbar_wait(smem_u32(&bars->pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1)) {
       tc_fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.out + (static_cast<size_t>(q_begin + r_seq) * p.Hq + hq) * HD;
@@ -898,7 +926,7 @@ paged_extend_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid
   }
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -1038,6 +1066,9 @@ int sglb_paged_extend_tc(const void* q, void* out, const void* kv_buffer, long l
   if (!cfg) {
     cudaError_t e = cudaFuncSetAttribute(paged_extend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
+    // two CTAs per SM need the whole shared-memory carve-out
+    cudaFuncSetAttribute(paged_extend_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     cfg = true;
   }
   dim3 grid(num_q_tiles_bound, Hq, 1);

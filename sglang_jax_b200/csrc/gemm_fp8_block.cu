@@ -8,9 +8,10 @@
 //
 // The tensor core cannot apply a scale that changes along K, so every 128-wide K block is multiplied on its
 // own into tensor memory (tcgen05.mma kind::f8f6f4, 128 x 128 x 32 per instruction, accumulate reset per
-// block) and "promoted": four warps read the block's partial product out of tensor memory
-// (tcgen05.ld), multiply by the two scales and add it to fp32 accumulators in registers, while the MMA
-// warp already fills the other half of tensor memory with the next block.  One K block is exactly one
+// block) and "promoted": eight warps (two per lane quarter of tensor memory, each owning 64 of the 128
+// columns) read the block's partial product out of tensor memory (tcgen05.ld, both loads in flight before
+// one wait), hand the buffer back, multiply by the two scales and add to fp32 accumulators in registers,
+// while the MMA warp already fills the other half of tensor memory with the next block.  One K block is exactly one
 // 128-byte swizzle row, i.e. one stage of the TMA ring.
 //
 // Dense and grouped (MoE experts: rows sorted by expert, 128-row token tiles from the list `moe_align`
@@ -26,9 +27,11 @@ namespace {
 constexpr int BM = 128, BN = 128, BKB = 128;      // tile, and bytes (= fp8 elements) of one K block
 constexpr int kStages = 6;
 constexpr int kStageBytes = (BM + BN) * BKB;
-constexpr int kThreads = 192;
-constexpr int kEpi = 128;
-constexpr int kSmem = kStages * kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
+constexpr int kEpi = 256;                        // promotion / epilogue threads: warps 2..9
+constexpr int kThreads = 64 + kEpi;
+constexpr int kCols = BN / 2;                     // accumulator columns per promotion thread
+constexpr int kAccBufs = 4;                       // K-block products in flight in tensor memory (4 x 128 columns)
+constexpr int kSmem = kStages * kStageBytes + (2 * kStages + 2 * kAccBufs) * 8 + 16 + 1024;
 
 struct BParams {
   __nv_bfloat16* out;        // [M, N]
@@ -86,9 +89,11 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
-  uint64_t* acc_full = bars + 2 * kStages;       // [2] one K block's product is in tensor memory
-  uint64_t* acc_empty = acc_full + 2;            // [2] ... and has been read out again
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  // The hand-over of one K block (commit -> promotion warps wake -> tcgen05.ld -> arrive -> MMA warp wakes) is a
+  // round trip of about a microsecond, several times the block's MMA time: four buffers keep that many in flight.
+  uint64_t* acc_full = bars + 2 * kStages;       // [kAccBufs] one K block's product is in tensor memory
+  uint64_t* acc_empty = acc_full + kAccBufs;     // [kAccBufs] ... and has been read out again
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccBufs);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -99,15 +104,15 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kAccBufs; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
-      mbar_init(smem_u32(&acc_empty[a]), kEpi);
+      mbar_init(smem_u32(&acc_empty[a]), kEpi / 32);   // one arrival per promotion warp
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+    tmem_alloc(smem_u32(tmem_slot), kAccBufs * BN);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -174,58 +179,82 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             stage = 0;
             phase ^= 1;
           }
-          buf ^= 1;
-          if (buf == 0) buf_phase ^= 1;
+          if (++buf == kAccBufs) {
+            buf = 0;
+            buf_phase ^= 1;
+          }
         }
       }
     }
   } else {
-    // ------------------------------------------------------------------ promotion + epilogue (warps 2..5)
-    const int q = warp & 3;
+    // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
+    const int q = warp & 3;                        // lane quarter of tensor memory this warp may read
+    const int col0 = ((warp - 2) >> 2) * kCols;    // its half of the tile's columns
     const int row = q * 32 + lane;
     int it = 0, buf = 0;
     uint32_t buf_phase = 0;
     BTile t;
     bool ok = true;
     while (ok && !*abort_flag && next_tile(p, it, t)) {
-      float acc[BN];
+      float acc[kCols];
 #pragma unroll
-      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+      for (int c = 0; c < kCols; ++c) acc[c] = 0.f;
       const int m = t.m0 + row;
       const bool live = m < t.m_limit;
-      for (int kb = 0; kb < p.KB; ++kb) {
-        const float s = (live ? __ldg(p.sx + static_cast<size_t>(kb) * p.sx_stride + m) : 0.f) * __ldg(p.sw + t.sw_off + kb);
-        if (!mbar_wait(smem_u32(&acc_full[buf]), buf_phase)) {
-          report(p.status, kTimeoutTmemFull, t.m0, kb);
-          *abort_flag = 1;
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      // The scale of a K block comes from global memory (an L2 round trip): a register ring keeps the loads four
+      // blocks ahead of their use, so that latency stays off the per-block critical path.
+      auto load_scale = [&](int kb) -> float {
+        if (kb >= p.KB) return 0.f;
+        return (live ? __ldg(p.sx + static_cast<size_t>(kb) * p.sx_stride + m) : 0.f) * __ldg(p.sw + t.sw_off + kb);
+      };
+      float ring[4];
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + c0, v);
+      for (int i = 0; i < 4; ++i) ring[i] = load_scale(i);
+      for (int kb0 = 0; ok && kb0 < p.KB; kb0 += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kb = kb0 + i;
+          if (kb >= p.KB) break;
+          const float s = ring[i];
+          ring[i] = load_scale(kb + 4);
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_full[buf]), buf_phase))) {
+            report(p.status, kTimeoutTmemFull, t.m0, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + col0;
+          uint32_t v0[32], v1[32];
+          tmem_ld32(taddr, v0);
+          tmem_ld32(taddr + 32, v1);
           tmem_ld_wait();
+          // the block's product is in registers: the MMA warp may reuse this part of tensor memory
+          // (one elected lane per warp arrives: hundreds of arrivals on one barrier word would serialise)
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
 #pragma unroll
-          for (int e = 0; e < 32; ++e) acc[c0 + e] = fmaf(s, __uint_as_float(v[e]), acc[c0 + e]);
+          for (int e = 0; e < 32; ++e) {
+            acc[e] = fmaf(s, __uint_as_float(v0[e]), acc[e]);
+            acc[32 + e] = fmaf(s, __uint_as_float(v1[e]), acc[32 + e]);
+          }
+          if (++buf == kAccBufs) {
+            buf = 0;
+            buf_phase ^= 1;
+          }
         }
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&acc_empty[buf]));
-        buf ^= 1;
-        if (buf == 0) buf_phase ^= 1;
       }
       if (!ok) break;
       if (live) {
-        __nv_bfloat16* orow = p.out + static_cast<size_t>(m) * p.N + t.n0;
+        __nv_bfloat16* orow = p.out + static_cast<size_t>(m) * p.N + t.n0 + col0;
 #pragma unroll
-        for (int c = 0; c < BN; c += 8) {
-          if (t.n0 + c < p.N) {
+        for (int c = 0; c < kCols; c += 8) {
+          if (t.n0 + col0 + c < p.N) {
             float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (p.bias != nullptr) {
 #pragma unroll
-              for (int e = 0; e < 8; ++e) b[e] = __bfloat162float(p.bias[t.n0 + c + e]);
+              for (int e = 0; e < 8; ++e) b[e] = __bfloat162float(p.bias[t.n0 + col0 + c + e]);
             }
             *reinterpret_cast<uint4*>(orow + c) =
                 make_uint4(pack_bf16(acc[c] + b[0], acc[c + 1] + b[1]), pack_bf16(acc[c + 2] + b[2], acc[c + 3] + b[3]),
@@ -245,7 +274,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   }
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, kAccBufs * BN);
   }
 }
 

@@ -202,6 +202,9 @@ class ServerArgs:
     disaggregation_bootstrap_port: int = 8998
     disaggregation_transfer_port: int = 30001
     disaggregation_enable_d2h: bool = False
+    # KV data path between engines of one NVLink domain: "cuda_ipc" lets the decode engine's page-copy kernel read
+    # the prefill engine's pool directly; "tcp" stages through pinned host memory (works across nodes)
+    disaggregation_transfer_backend: str = field(default="tcp", metadata=_m(choices=["tcp", "cuda_ipc"]))
     disaggregation_use_raiden: bool = False
     disaggregation_enable_chunk_prefill_transfer: bool = False
     disaggregation_side_channel_port: int = 9600
