@@ -91,6 +91,8 @@ def parse_args():
                          "prefix plus a 128-token unique suffix")
     ap.add_argument("--quantization", default=None)
     ap.add_argument("--moe-backend", default=None)
+    ap.add_argument("--enable-mixed-chunk", action="store_true",
+                    help="let prefill steps carry the running batch's decode tokens (the server flag of the same name)")
     ap.add_argument("--disable-cuda-graph", action="store_true")
     ap.add_argument("--disable-fused-comm", action="store_true")
     ap.add_argument("--disable-overlap", action="store_true")
@@ -307,6 +309,8 @@ def main():
         extra["quantization"] = args.quantization
     if args.moe_backend:
         extra["moe_backend"] = args.moe_backend
+    if args.enable_mixed_chunk:
+        extra["enable_mixed_chunk"] = True
     sa = ServerArgs(
         model_path=model_dir, load_format="dummy", tp_size=world, ep_size=world if moe_model else 1, device=device,
         dtype="bfloat16" if device == "cuda" else "float32",
@@ -551,6 +555,7 @@ def main():
                          f"({runner.weight_bytes / 2**30:.1f} GiB) plus KV" if runner is not None else "n/a",
                    "window": "steady-state closed loop (staggered fill, periodic decode/prefill mix)",
                    "cuda_graph": gr is not None, "fused_comm": st.fused_comm is not None,
+                   "mixed_chunk": bool(sa.enable_mixed_chunk),
                    "overlap_schedule": sched.enable_overlap, "layers": cfg["num_hidden_layers"]},
         "clocks": clock_info, "e2e": e2e, "latency": latency,
         "p50_ttft_ms": latency["p50_ttft_ms"] if latency else None,

@@ -52,4 +52,25 @@ int sglb_kv_page_copy(void* dst, const void* src, const long long* dst_pages, co
   }
   return static_cast<int>(cudaGetLastError());
 }
+
+// Lets kernels running on `device` dereference memory of `peer` (needed before a page copy reads a peer's pool
+// through a CUDA IPC mapping).  Returns 0 when access is on (now or already), a negative code when the two
+// devices cannot reach each other, a positive CUDA error otherwise.  The current device is left unchanged.
+int sglb_enable_peer_access(int device, int peer) {
+  if (device == peer) return 0;
+  int can = 0;
+  cudaError_t e = cudaDeviceCanAccessPeer(&can, device, peer);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (!can) return -sglb::kBadArgument;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(device);
+  e = cudaDeviceEnablePeerAccess(peer, 0);
+  cudaSetDevice(prev);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();      // clear the sticky-less error state this call leaves behind
+    return 0;
+  }
+  return static_cast<int>(e);
+}
 }

@@ -9,7 +9,7 @@ from . import pd_auth
 from .bootstrap import BootstrapClient, HeartbeatDaemon
 from .common.core import CommonKVManager
 from .host_ip import get_host_ip
-from .transfer.zmq_transfer import ZmqTransferBackend
+from .factory import create_transfer_backend, pick_transfer_mode  # noqa: F401
 
 logger = logging.getLogger(__name__)
 
@@ -23,24 +23,13 @@ def kv_layout_of(scheduler) -> dict:
             "model": scheduler.model_config.architectures[0] if scheduler.model_config is not None else ""}
 
 
-def pick_transfer_mode(server_args, on_gpu: bool) -> str:
-    """`cuda_ipc` (NVLink peer reads) when both engines share a node and run on GPUs, else `tcp`.
-    `--disaggregation-enable-d2h` forces the host-staged path."""
-    if not on_gpu or server_args.disaggregation_enable_d2h:
-        return "tcp"
-    return getattr(server_args, "disaggregation_transfer_backend", None) or "tcp"
-
-
 def build_kv_manager(scheduler, role: str, engine_id: str):
     sa = scheduler.server_args
     secret = pd_auth.resolve_secret(sa.disaggregation_shared_secret)
     host = get_host_ip(sa.disaggregation_host_ip) if sa.disaggregation_host_ip else "127.0.0.1"
     layout = kv_layout_of(scheduler)
-    pool = scheduler.token_to_kv_pool
-    from ..mem_cache.host_kv_pool import _layer_views
-    on_gpu = _layer_views(pool)[0].is_cuda
-    backend = ZmqTransferBackend(pool, host, sa.disaggregation_transfer_port if role == "prefill" else 0,
-                                 pick_transfer_mode(sa, on_gpu), secret, sa.disaggregation_pull_timeout_seconds)
+    backend = create_transfer_backend(scheduler.token_to_kv_pool, sa, local_host=host, role=role, shared_secret=secret,
+                                      max_req_input_len=getattr(scheduler, "max_req_input_len", None))
     transfer_addr = backend.start() if role == "prefill" else None
     mirror = None
     worker = scheduler.tp_worker

@@ -10,8 +10,8 @@ behind one control channel (a ZMQ ROUTER socket on the prefill side):
   and scattered from pinned memory after they are received.  Works across nodes and on CPU.
 * `mode="cuda_ipc"`: both engines sit in one NVLink domain.  The reply carries CUDA IPC handles
   of the prefill engine's KV layer buffers (once per peer) and the page ids; the decode engine
-  maps them and its page-copy kernel reads the peer's pages directly over NVLink — no staging,
-  no host copy.
+  maps them, gathers the pages on the exporting GPU, moves them with one device-to-device copy
+  per layer over NVLink and scatters them into its own pool — no host staging.
 """
 
 from __future__ import annotations
@@ -40,8 +40,14 @@ class ZmqTransferBackend:
     name = "zmq"
 
     def __init__(self, device_pool, host: str = "127.0.0.1", port: int = 0, mode: str = "tcp",
-                 secret: str | None = None, pull_timeout: float = 30.0):
+                 secret: str | None = None, pull_timeout: float = 30.0, staging_pages: int = 0):
+        """`staging_pages` > 0 (host-staged mode on a GPU): a `QueueHostKVPool` of that many pinned pages that the
+        transfer threads reserve from, instead of allocating pinned memory per transfer."""
         self.views = _layer_views(device_pool)
+        self.staging = None
+        if staging_pages > 0 and mode == "tcp" and self.views[0].is_cuda:
+            from ...mem_cache.host_kv_pool import QueueHostKVPool
+            self.staging = QueueHostKVPool(device_pool, staging_pages)
         self.on_gpu = self.views[0].is_cuda
         if mode == "cuda_ipc" and not self.on_gpu:
             raise ValueError("cuda_ipc transfer needs the KV pool on a GPU")
@@ -81,7 +87,7 @@ class ZmqTransferBackend:
     def register(self, transfer_id: str, pages: np.ndarray, meta: dict) -> None:
         if self.on_gpu:
             # the KV of these pages must be complete before a peer may read it
-            torch.cuda.current_stream().synchronize()
+            torch.cuda.current_stream(self.views[0].device).synchronize()
         with self.lock:
             self.registered[transfer_id] = (np.asarray(pages, np.int64).copy(), dict(meta))
 
@@ -120,7 +126,17 @@ class ZmqTransferBackend:
                 logger.exception("transfer reply failed")
                 self._sock.send_multipart([ident, b"error", str(e).encode()])
 
+    def _device_guard(self):
+        """Transfers run on helper threads, whose current CUDA device is device 0 unless set: kernels and streams
+        must belong to the GPU that holds this engine's pool."""
+        import contextlib
+        return torch.cuda.device(self.views[0].device) if self.on_gpu else contextlib.nullcontext()
+
     def _payload(self, pages: np.ndarray, meta: dict, req: dict) -> list[bytes]:
+        with self._device_guard():
+            return self._payload_on_device(pages, meta, req)
+
+    def _payload_on_device(self, pages: np.ndarray, meta: dict, req: dict) -> list[bytes]:
         head = dict(meta, num_pages=int(len(pages)), mode=self.mode)
         if self.mode == "cuda_ipc":
             head["pages"] = pages.tolist()
@@ -129,7 +145,17 @@ class ZmqTransferBackend:
             return [json.dumps(head).encode()]
         idx = torch.as_tensor(pages)
         frames = [json.dumps(head).encode()]
-        if self.on_gpu:
+        stage_pages = self.staging.reserve(len(pages), self.pull_timeout) if self.staging is not None else None
+        if stage_pages is not None:
+            # pinned staging slots of the queue pool: device -> host with the page-copy kernel, then one frame per layer
+            try:
+                self.staging.backup_from_device(pages, stage_pages)
+                torch.cuda.current_stream().synchronize()
+                for layer in range(len(self.views)):
+                    frames.append(self.staging.host_bytes(layer, stage_pages))
+            finally:
+                self.staging.release(stage_pages)
+        elif self.on_gpu:
             from ...ops import native
             dev_idx = idx.to(self.views[0].device)
             seq = torch.arange(len(pages), device=dev_idx.device)
@@ -210,17 +236,28 @@ class ZmqTransferBackend:
             sock.close()
 
     def _scatter(self, addr: str, head: dict, frames: list[bytes], dst_pages: np.ndarray):
+        with self._device_guard():
+            self._scatter_on_device(addr, head, frames, dst_pages)
+
+    def _scatter_on_device(self, addr: str, head: dict, frames: list[bytes], dst_pages: np.ndarray):
         if head.get("mode") == "cuda_ipc":
-            from ...ops import native
             if "ipc_handles" in head:
                 self._ipc_cache[addr] = [self._open_handle(h) for h in head["ipc_handles"]]
             peer = self._ipc_cache[addr]
             dev = self.views[0].device
-            d = torch.as_tensor(dst_pages).to(dev)
-            s = torch.as_tensor(np.asarray(head["pages"], np.int64)).to(dev)
+            # The mapping of the prefill engine's pool belongs to ITS GPU's context inside this process.  Pages are
+            # gathered there (a kernel of that GPU reading its own memory), cross NVLink as one device-to-device copy
+            # per layer (the copy engine, no kernel dereferences another GPU's memory), and are scattered into this
+            # engine's pool by a kernel of this GPU.
+            src_dev = peer[0].device
+            s_idx = torch.as_tensor(np.asarray(head["pages"], np.int64)).to(src_dev)
+            d_idx = torch.as_tensor(dst_pages).to(dev)
             for dv, sv in zip(self.views, peer):
-                native.kv_page_copy(dv, sv, d, s)
-            torch.cuda.current_stream().synchronize()
+                with torch.cuda.device(src_dev):
+                    staged = sv.index_select(0, s_idx)
+                dv.index_copy_(0, d_idx, staged.to(dev, non_blocking=True))
+            torch.cuda.current_stream(src_dev).synchronize()
+            torch.cuda.current_stream(dev).synchronize()
             self.bytes_received += sum(v.shape[1] * v.element_size() for v in self.views) * len(dst_pages)
             return
         if len(frames) != len(self.views):
@@ -230,6 +267,18 @@ class ZmqTransferBackend:
             want = len(dst_pages) * v.shape[1] * v.element_size()
             if len(raw) != want:
                 raise TransferError(f"layer payload is {len(raw)} bytes, expected {want}")
+        stage_pages = self.staging.reserve(len(dst_pages), self.pull_timeout) if self.staging is not None else None
+        if stage_pages is not None:
+            try:
+                for layer, raw in enumerate(frames):
+                    self.staging.fill_host(layer, stage_pages, raw)
+                    self.bytes_received += len(raw)
+                self.staging.load_to_device(stage_pages, dst_pages)
+                torch.cuda.current_stream().synchronize()
+            finally:
+                self.staging.release(stage_pages)
+            return
+        for v, raw in zip(self.views, frames):
             if self.on_gpu:
                 from ...ops import native
                 stage = torch.empty((len(dst_pages), v.shape[1]), dtype=v.dtype, pin_memory=True)

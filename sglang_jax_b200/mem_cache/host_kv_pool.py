@@ -109,6 +109,43 @@ class QueueHostKVPool(HostKVPool):
         self.entries.append((key, pages))
         return True
 
+    # -- reservations: the PD transfer threads stage pages here (reserve -> copy -> send / scatter -> release)
+    def reserve(self, n: int, timeout: float = 30.0) -> np.ndarray | None:
+        """`n` staging pages, waiting up to `timeout` seconds for other transfers to release theirs; `None` when the
+        pool is smaller than `n` or the wait ran out (the caller then stages through a one-off buffer)."""
+        import threading
+        import time
+        if not hasattr(self, "_cv"):
+            self._cv = threading.Condition()
+        if n > self.num_pages:
+            return None
+        deadline = time.monotonic() + timeout
+        with self._cv:
+            while len(self.free_pages) < n:
+                left = deadline - time.monotonic()
+                if left <= 0:
+                    return None
+                self._cv.wait(left)
+            return self.alloc(n)
+
+    def release(self, pages) -> None:
+        import threading
+        if not hasattr(self, "_cv"):
+            self._cv = threading.Condition()
+        with self._cv:
+            self.free(pages)
+            self._cv.notify_all()
+
+    def host_bytes(self, layer: int, host_pages: np.ndarray) -> bytes:
+        """The staged pages of one layer as one contiguous byte string (page order = `host_pages` order)."""
+        v = self.host_views[layer][torch.as_tensor(np.asarray(host_pages, np.int64))]
+        return v.contiguous().view(torch.uint8).numpy().tobytes()
+
+    def fill_host(self, layer: int, host_pages: np.ndarray, raw) -> None:
+        v = self.host_views[layer]
+        src = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(v.dtype).view(len(host_pages), v.shape[1])
+        v[torch.as_tensor(np.asarray(host_pages, np.int64))] = src
+
     def get(self, key: str, device_pages: np.ndarray) -> bool:
         for i, (k, pages) in enumerate(self.entries):
             if k == key:

@@ -103,6 +103,9 @@ class ModelRunner:
                 self.model, cap_tokens, self.device, int(getattr(hf, "num_experts_per_tok", None) or 8))
         from ..layers.fused_block import model_supports_fused_residual
         self.fused_residual_ok = model_supports_fused_residual(self.model)
+        # forwards with fewer tokens than this use the library all-reduce + add-RMSNorm kernel instead of the fused
+        # NVLink kernels (a per-forward choice: both dataflows are exact, they differ in latency)
+        self.fused_min_tokens = int(os.environ.get("SGLB_FUSED_MIN_TOKENS", "0"))
         self.gemm_plan = None
         if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "0") == "1" and not is_draft_worker:
             # measured GEMM plan, kept on disk between runs (counterpart of the reference's compile / AOT caches)
@@ -245,6 +248,7 @@ class ModelRunner:
         from ..utils.precision_tracer import precision_tracer
         inner = getattr(self.model, "model", None)
         on = (self.fused_residual_ok and not precision_tracer.enabled
+              and (fb is None or fb.num_tokens >= self.fused_min_tokens)
               and (fb is None or fb.extras.get("deepstack") is None)
               and not getattr(inner, "layers_to_capture", None)
               and not getattr(self.model, "capture_aux_hidden_states", False))

@@ -527,6 +527,16 @@ def kv_page_copy(dst: torch.Tensor, src: torch.Tensor, dst_pages: torch.Tensor, 
            "kv_page_copy")
 
 
+def enable_peer_access(device: torch.device, peer: torch.device) -> None:
+    """Allow kernels on `device` to read / write memory of `peer` (both CUDA devices of this process)."""
+    if device.index == peer.index:
+        return
+    rc = lib().sglb_enable_peer_access(int(device.index), int(peer.index))
+    if rc < 0:
+        raise RuntimeError(f"cuda:{device.index} cannot access the memory of cuda:{peer.index} (no peer path)")
+    _check(rc, "enable_peer_access")
+
+
 def verify_tree_greedy(tokens, parent, target_ids, max_depth: int):
     """`(accept [B], path [B, max_depth+1], bonus [B])`, all int64; see `speculative/eagle_util.py`."""
     B, n = tokens.shape

@@ -317,3 +317,38 @@ def test_tensor_parallel_engines_hand_over_every_ranks_shard(tmp_path):
         prefill.shutdown()
         decode.shutdown()
         srv.stop()
+
+
+@pytest.mark.gpu
+def test_host_staged_transfer_uses_the_queue_pool_on_gpu():
+    """Host-staged (tcp) hand-over between two pools on a GPU: pages travel through the pinned `QueueHostKVPool`
+    slots (reserve -> page-copy kernel -> frames -> page-copy kernel -> release); several transfers share the slots."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+
+    def pool(seed=None):
+        p = MHATokenToKVPool(16 * 16, 16, torch.bfloat16, 2, 64, 3, "cuda")
+        if seed is not None:
+            g = torch.Generator(device="cuda").manual_seed(seed)
+            for b in p.kv_buffer:
+                b.copy_(torch.randn(b.shape, generator=g, device="cuda"))
+        return p
+
+    src, dst = pool(3), pool()
+    pb = ZmqTransferBackend(src, secret="k", staging_pages=4)
+    db = ZmqTransferBackend(dst, secret="k", pull_timeout=10, staging_pages=4)
+    assert pb.staging is not None and db.staging is not None and pb.staging.num_pages == 4
+    pb.start()
+    try:
+        for i, (sp, dp) in enumerate((([2, 5, 7], [9, 3, 4]), ([1, 6], [10, 11]), ([8, 12, 13, 14], [1, 2, 5, 6]))):
+            pb.register(f"t{i}", np.asarray(sp), {"first_token": i})
+            head = db.pull(pb.addr, f"t{i}", np.asarray(dp))
+            assert head["first_token"] == i
+            assert kv_digest(src, sp) == kv_digest(dst, dp)
+        assert pb.staging.available_pages() == 4 and db.staging.available_pages() == 4     # every slot came back
+        # a transfer larger than the pool falls back to a one-off buffer
+        pb.register("big", np.arange(1, 7), {})
+        db.pull(pb.addr, "big", np.arange(7, 13))
+        assert kv_digest(src, list(range(1, 7))) == kv_digest(dst, list(range(7, 13)))
+    finally:
+        pb.stop()

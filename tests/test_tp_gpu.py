@@ -8,7 +8,8 @@ import sys
 import pytest
 import torch
 
-pytestmark = pytest.mark.gpu
+# every test here spawns rank processes: a lost rank must end the test, not the session
+pytestmark = [pytest.mark.gpu, pytest.mark.timeout(420)]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -17,7 +18,7 @@ def _need2():
         pytest.skip("needs 2 GPUs")
 
 
-def _spawn(fn, world=2, timeout=600, args=(), ep=False):
+def _spawn(fn, world=2, timeout=300, args=(), ep=False):
     import torch.multiprocessing as mp
     from sglang_jax_b200.utils.common import get_free_port
     ctx = mp.get_context("spawn")
@@ -200,7 +201,7 @@ def _engine(rank, world, fused, biased=False):
         outs = eng.generate(input_ids=prompts, sampling_params=sp)
         # the same prompts again with log-probabilities: every candidate's value at the first decoded position
         lp = eng.generate(input_ids=prompts, sampling_params=dict(sp, max_new_tokens=2), return_logprob=True,
-                          top_logprobs_num=5)
+                          top_logprobs_num=5, logprob_start_len=0)
         # sampled steps: a vanishing nucleus keeps only the best token, so the draws must follow the greedy run; with
         # the fused context they replay captured graphs (peer-store logits gather + sampling kernel inside)
         smp = eng.generate(input_ids=prompts, sampling_params=dict(sp, temperature=0.8, top_p=1e-6))
@@ -208,19 +209,33 @@ def _engine(rank, world, fused, biased=False):
         native.check_status()
         gr = eng.scheduler.tp_worker.model_runner.cuda_graph_runner
         assert any(isinstance(k, tuple) for k in gr.graphs) == fused, list(gr.graphs)
+        tops = [[(t[1], t[0]) for t in o["meta_info"]["output_top_logprobs"][0]] for o in lp]
+        # (runs differ in prefix-cache hits, hence in kernel shapes: a near-tie may flip, so the draw is checked
+        # against the best candidates of the log-probability run rather than against the greedy token itself)
+        for o, cand in zip(smp, tops):
+            assert len(o["output_ids"]) == 10 and o["output_ids"][0] in [c[0] for c in cand[:3]], (o["output_ids"], cand)
         flat_g = [t for o in outs for t in o["output_ids"]]
         flat_s = [t for o in smp for t in o["output_ids"]]
-        assert sum(a == b for a, b in zip(flat_g, flat_s)) / len(flat_g) >= 0.7, (flat_g, flat_s)
-        tops = [[(t[1], t[0]) for t in o["meta_info"]["output_top_logprobs"][0]] for o in lp]
-        return [o["output_ids"] for o in outs], tops
+        assert sum(a == b for a, b in zip(flat_g, flat_s)) / len(flat_g) >= 0.25, (flat_g, flat_s)
+        # teacher-forced: the log-probability of every prompt token given its prefix (the first position has none)
+        prompt_lp = [[t[0] for t in o["meta_info"]["input_token_logprobs"] if t[0] is not None] for o in lp]
+        return [o["output_ids"] for o in outs], tops, prompt_lp
     finally:
         eng.shutdown()
 
 
 def _check_engines_agree(fused, nccl):
-    toks_f, tops_f = fused
-    toks_n, tops_n = nccl
+    toks_f, tops_f, plp_f = fused
+    toks_n, tops_n, plp_n = nccl
     assert all(len(x) == 10 for x in toks_f)
+    # every prompt position, same prefix in both engines: hundreds of log-probabilities that must agree closely
+    import numpy as np
+    for a, b in zip(plp_f, plp_n):
+        a, b = np.asarray(a), np.asarray(b)
+        assert a.shape == b.shape and a.size >= 15
+        # (a routed expert that flips at a near-tie moves single positions of an MoE model more than that)
+        d = np.abs(a - b)
+        assert np.quantile(d, 0.95) < 0.15 and d.mean() < 0.03 and d.max() < 1.0, (d.max(), d.mean())
     # log-probabilities of the five best first tokens agree closely, so does their order where they are apart
     for tf, tn in zip(tops_f, tops_n):
         df, dn = dict(tf), dict(tn)
@@ -232,8 +247,11 @@ def _check_engines_agree(fused, nccl):
     flat_f = [t for o in toks_f for t in o]
     flat_n = [t for o in toks_n for t in o]
     assert len(set(flat_f)) > 5, toks_f                      # not a degenerate echo
+    # free-running greedy tokens: a flipped near-tie changes everything after it, so only the first tokens and a
+    # loose overall agreement are asked for (the teacher-forced comparison above is the strict one)
+    assert sum(f[0] == n[0] for f, n in zip(toks_f, toks_n)) >= len(toks_f) - 1, (toks_f, toks_n)
     agree = sum(a == b for a, b in zip(flat_f, flat_n)) / len(flat_f)
-    assert agree >= 0.7, (toks_f, toks_n)
+    assert agree >= 0.35, (toks_f, toks_n)
 
 
 def test_engine_tp2_fused_matches_nccl():
@@ -327,12 +345,14 @@ def _moe_engine(rank, world, backend, fused):
         sp = {"max_new_tokens": 10, "temperature": 0.0, "ignore_eos": True}
         outs = eng.generate(input_ids=prompts, sampling_params=sp)
         lp = eng.generate(input_ids=prompts, sampling_params=dict(sp, max_new_tokens=2), return_logprob=True,
-                          top_logprobs_num=5)
+                          top_logprobs_num=5, logprob_start_len=0)
         torch.cuda.synchronize()
         native.check_status()
         assert (fused_ep_moe.CALLS > 0) == (backend == "fused")
         tops = [[(t[1], t[0]) for t in o["meta_info"]["output_top_logprobs"][0]] for o in lp]
-        return [o["output_ids"] for o in outs], tops
+        # teacher-forced: the log-probability of every prompt token given its prefix (the first position has none)
+        prompt_lp = [[t[0] for t in o["meta_info"]["input_token_logprobs"] if t[0] is not None] for o in lp]
+        return [o["output_ids"] for o in outs], tops, prompt_lp
     finally:
         eng.shutdown()
 
@@ -346,7 +366,7 @@ def test_engine_ep2_token_all_to_all_matches_replicated_experts():
 
 
 # ------------------------------------------------------------------------------------------
-def _pd_engine(role, gpu, url, q):
+def _pd_engine(role, gpu, url, q, backend="cuda_ipc"):
     """One engine of a prefill / decode pair, alone in its process on its own GPU."""
     os.environ["LOCAL_RANK"] = str(gpu)
     sys.path.insert(0, ROOT)
@@ -372,7 +392,7 @@ def _pd_engine(role, gpu, url, q):
             ps.reset_state()
         eng = Engine(**common, disaggregation_mode=role, disaggregation_bootstrap_url=url,
                      disaggregation_shared_secret="pd", disaggregation_transfer_port=0,
-                     disaggregation_side_channel_port=0, disaggregation_transfer_backend="cuda_ipc",
+                     disaggregation_side_channel_port=0, disaggregation_transfer_backend=backend,
                      disaggregation_pull_timeout_seconds=60.0)
         outs = eng.generate(input_ids=prompts, sampling_params=sp, bootstrap_room=[31, 32, 33])
         torch.cuda.synchronize()
@@ -393,9 +413,12 @@ def _pd_engine(role, gpu, url, q):
     os._exit(0)
 
 
-def test_pd_disaggregation_over_cuda_ipc_between_two_gpus():
-    """Prefill engine on GPU 0, decode engine on GPU 1, separate processes: the decode engine's page-copy kernel reads
-    the prefill engine's KV pool through CUDA IPC mappings (plain peer loads); tokens equal a single engine's."""
+@pytest.mark.timeout(400)
+@pytest.mark.parametrize("backend", ["tcp", "cuda_ipc"])
+def test_pd_disaggregation_between_two_gpus(backend):
+    """Prefill engine on GPU 0, decode engine on GPU 1, separate processes.  `tcp`: pages are staged through the
+    pinned queue pool on both sides.  `cuda_ipc`: the decode engine maps the prefill engine's KV pool, gathers the
+    pages on the exporting GPU and moves them with device-to-device copies.  Tokens follow a single engine's."""
     _need2()
     import torch.multiprocessing as mp
     from sglang_jax_b200.disaggregation.bootstrap import BootstrapServer
@@ -403,11 +426,12 @@ def test_pd_disaggregation_over_cuda_ipc_between_two_gpus():
     srv = BootstrapServer(port=get_free_port(), secret="pd").start()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_pd_engine, args=(role, gpu, srv.url, q)) for role, gpu in (("prefill", 0), ("decode", 1))]
+    procs = [ctx.Process(target=_pd_engine, args=(role, gpu, srv.url, q, backend))
+             for role, gpu in (("prefill", 0), ("decode", 1))]
     try:
         for p in procs:
             p.start()
-        res = dict(q.get(timeout=600) for _ in procs)
+        res = dict(q.get(timeout=240) for _ in procs)
     finally:
         for p in procs:
             p.join(timeout=60)
@@ -418,10 +442,44 @@ def test_pd_disaggregation_over_cuda_ipc_between_two_gpus():
         assert not (isinstance(v, str) and v.startswith("ERR")), f"{role}: {v}"
     d_out, want, mode, received, _ = res["decode"]
     p_out, _, pmode, _, _ = res["prefill"]
-    assert mode == "cuda_ipc" and pmode == "cuda_ipc" and received > 0
+    assert mode == backend and pmode == backend and received > 0
     assert p_out == [w[:1] for w in want]
     # the transferred requests may join the decode batch one by one, so kernels see other batch shapes than in the
     # single-engine run: near-ties can flip in bf16, wrong KV would not agree at all
     assert [o[0] for o in d_out] == [w[0] for w in want] and all(len(o) == 8 for o in d_out)
     flat_d, flat_w = [t for o in d_out for t in o], [t for o in want for t in o]
     assert sum(a == b for a, b in zip(flat_d, flat_w)) / len(flat_w) >= 0.8, (d_out, want)
+
+
+# ------------------------------------------------------------------------------------------
+def test_dp_attention_two_sections_on_two_gpus(tmp_path):
+    """dp 2 x tensor 1 on two GPUs under ONE scheduler: section 1's batches run on GPU 1 through the step ring;
+    requests alternate between the sections and the tokens follow a single-GPU engine."""
+    _need2()
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.utils.tiny_models import TINY_QWEN3, write_tiny_qwen3_checkpoint
+    cfg = dict(TINY_QWEN3, head_dim=128, num_attention_heads=4, num_key_value_heads=2, hidden_size=512,
+               intermediate_size=1024, num_hidden_layers=3, torch_dtype="bfloat16", tie_word_embeddings=False)
+    path = write_tiny_qwen3_checkpoint(str(tmp_path / "m"), config=cfg, dtype=torch.bfloat16, std=0.05)
+    common = dict(model_path=path, device="cuda", dtype="bfloat16", page_size=16, skip_tokenizer_init=True,
+                  max_total_tokens=4096, max_running_requests=8, log_level="error", watchdog_timeout=0,
+                  cuda_graph_max_bs=8, dp_schedule_policy="round_robin")
+    prompts = [list(range(1, 50)), list(range(3, 120)), [7, 900, 33, 512, 5] * 5, list(range(200, 260))]
+    sp = {"max_new_tokens": 8, "temperature": 0.0, "ignore_eos": True}
+    one = Engine(**common)
+    try:
+        want = [o["output_ids"] for o in one.generate(input_ids=prompts, sampling_params=sp)]
+    finally:
+        one.shutdown()
+    eng = Engine(**common, dp_size=2, tp_size=2)
+    try:
+        outs = eng.generate(input_ids=prompts, sampling_params=sp)
+        lp = eng.generate(input_ids=prompts[:1], sampling_params=sp, dp_rank=1, return_logprob=True)
+    finally:
+        eng.shutdown()
+    assert [o["meta_info"]["dp_rank"] for o in outs] == [0, 1, 0, 1]
+    assert lp[0]["meta_info"]["dp_rank"] == 1 and len(lp[0]["meta_info"]["output_token_logprobs"]) == 8
+    got = [o["output_ids"] for o in outs]
+    assert [g[0] for g in got] == [w[0] for w in want]
+    flat_g, flat_w = [t for o in got for t in o], [t for o in want for t in o]
+    assert sum(a == b for a, b in zip(flat_g, flat_w)) / len(flat_w) >= 0.8, (got, want)
