@@ -65,18 +65,24 @@ def bench_gemm():
         (128, 5120, 3200, "down decode tp8"), (128, 18992, 5120, "lm_head decode tp8"),
         (16, 51200, 5120, "gate_up bs16"), (1, 51200, 5120, "gate_up bs1"),
     ]
-    print(f"{'shape':>28} {'label':>22} {'ours ms':>9} {'TFLOP/s':>9} {'GB/s':>8} {'roof%':>7} {'torch ms':>9} {'vs torch':>8}")
+    print(f"{'shape':>28} {'label':>22} {'ours ms':>9} {'TFLOP/s':>9} {'GB/s':>8} {'roof%':>7} {'torch ms':>9} {'vs torch':>8} {'cluster ms':>10}")
+    native.gemm_plan = None            # the persistent kernel with its own default choice, not the measured plan
     for M, N, K, label in shapes:
         x = torch.randn(M, K, device="cuda").bfloat16()
         w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
         t = timeit(lambda: native.linear(x, w))
         tt = timeit(lambda: torch.nn.functional.linear(x, w))
+        tc = None
+        if M <= 128 and K % 64 == 0 and native.lib().sglb_gemm_decode_cluster_size(M, N, K) > 0:
+            o = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            tc = timeit(lambda: native.gemm_decode_cluster(x, w, None, o))
         flops = 2.0 * M * N * K
         byts = 2.0 * (M * K + N * K + M * N)
         tfl = flops / t / 1e9
         gbs = byts / t / 1e6
         roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3   # ms at the roofline
-        print(f"{f'{M}x{N}x{K}':>28} {label:>22} {t:9.4f} {tfl:9.1f} {gbs:8.0f} {100 * roof / t:6.1f}% {tt:9.4f} {tt / t:8.2f}")
+        print(f"{f'{M}x{N}x{K}':>28} {label:>22} {t:9.4f} {tfl:9.1f} {gbs:8.0f} {100 * roof / t:6.1f}% {tt:9.4f} {tt / t:8.2f} "
+              + (f"{tc:10.4f}" if tc is not None else f"{'-':>10}"))
     print(f"{'fp8 e4m3 (per-token x per-channel scales)':>51} {'fp8 ms':>9} {'TFLOP/s':>9} {'GB/s':>8} {'bf16 ms':>9}")
     for M, N, K, label in [(8192, 10240, 5120, "qkv prefill tp1"), (8192, 51200, 5120, "gate_up prefill tp1"),
                            (128, 10240, 5120, "qkv decode tp1"), (128, 51200, 5120, "gate_up decode tp1"),

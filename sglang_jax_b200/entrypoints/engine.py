@@ -225,6 +225,19 @@ class Engine(EngineBase):
             p.join(timeout=5)
             if p.is_alive():
                 p.kill()
+        # the tokenizer manager's receive loop is a task of this engine's event loop: cancel it and let the loop
+        # run the cancellation, or the interpreter reports a destroyed pending task at exit
+        loop = getattr(self, "loop", None)
+        if loop is not None and not loop.is_closed() and not loop.is_running():
+            try:
+                tasks = [t for t in asyncio.all_tasks(loop) if not t.done()]
+                for t in tasks:
+                    t.cancel()
+                if tasks:
+                    loop.run_until_complete(asyncio.gather(*tasks, return_exceptions=True))
+                loop.run_until_complete(loop.shutdown_asyncgens())
+            except Exception:
+                pass
 
     def __enter__(self):
         return self

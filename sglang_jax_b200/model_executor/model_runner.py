@@ -107,7 +107,7 @@ class ModelRunner:
         # NVLink kernels (a per-forward choice: both dataflows are exact, they differ in latency)
         self.fused_min_tokens = int(os.environ.get("SGLB_FUSED_MIN_TOKENS", "0"))
         self.gemm_plan = None
-        if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "0") == "1" and not is_draft_worker:
+        if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "1") == "1" and not is_draft_worker:
             # measured GEMM plan, kept on disk between runs (counterpart of the reference's compile / AOT caches)
             from ..ops import native
             from .tuning_cache import GemmPlan

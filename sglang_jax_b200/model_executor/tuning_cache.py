@@ -4,9 +4,12 @@ The reference avoids paying for compilation twice with a persistent XLA compile 
 ahead-of-time executable cache (`python/sgl_jax/srt/model_executor/aot_dispatch.py`, `SGLANG_JAX_AOT_DISPATCH`),
 and ships tables of tuned block sizes per kernel and device.  Kernels here are compiled ahead of time and CUDA
 graphs cannot be serialised, so what is worth keeping between runs is the *plan*: for every decode-sized GEMM
-shape of the model, which operand assignment of the tcgen05 kernel is faster on this GPU (tokens on the MMA M
-dimension with stream-K, or weight rows on M).  With `SGLB_GEMM_AUTOTUNE=1` the first engine start measures each
-shape it meets (a few launches per candidate, CUDA events) before the decode graphs are captured, and stores
+shape of the model, which candidate is fastest on this GPU: the tcgen05 kernel with tokens on the MMA M dimension
+(0), with weight rows on M and stream-K (1), the library GEMM (2: plain projections only; the fused
+GEMM + collective kernels are not part of the choice), or the cluster split-K kernel of `csrc/gemm_decode_cluster.cu`
+(3: up to 128 tokens).  With `SGLB_GEMM_AUTOTUNE=1` the first engine start measures
+each shape it meets (a few launches per candidate with the L2 flushed in between, CUDA events, median) before the
+decode graphs are captured, and stores
 the table under `SGLB_TUNING_CACHE_DIR` (default `~/.cache/sglang_jax_b200`), keyed by GPU name and by a digest
 of the kernel library; later starts load it and measure nothing.
 """
@@ -39,6 +42,9 @@ class GemmPlan:
         self.table: dict[str, int] = {}
         self.dirty = False
         self.measured = 0
+        self._flush = None
+        # SGLB_GEMM_PLAN_LIBRARY=0 keeps the choice among this library's own kernels
+        self.candidates = (0, 1, 2) if os.environ.get("SGLB_GEMM_PLAN_LIBRARY", "1") == "1" else (0, 1)
         if path and os.path.exists(path):
             try:
                 with open(path) as f:
@@ -56,30 +62,38 @@ class GemmPlan:
             h.update(f.read())
         return os.path.join(root, f"tuning_{gpu}_{h.hexdigest()[:12]}.json")
 
-    def mode_for(self, M: int, N: int, K: int, run) -> int:
-        """Operand assignment for a decode-sized GEMM (-1 = the launcher's default).  `run(mode)` launches the GEMM
-        once with that assignment on the current stream; it is only called for shapes not in the table, and never
-        while a graph is being captured."""
+    def mode_for(self, M: int, N: int, K: int, run, extra: tuple = ()) -> int:
+        """Candidate for a decode-sized GEMM (-1 = the launcher's default).  `run(mode)` launches the GEMM once with
+        that candidate on the current stream; it is only called for shapes not in the table, and never while a graph
+        is being captured.  `extra`: further candidates the caller can run for this shape."""
         b = _bucket(M)
         if b == 0:
             return -1
         key = f"{b}x{N}x{K}"
+        allowed = tuple(self.candidates) + tuple(extra)
         mode = self.table.get(key)
-        if mode is not None:
-            return mode
+        if mode is not None and mode in allowed:
+            return mode                 # (an entry for a candidate that is switched off here is measured again)
         if not self.measure or torch.cuda.is_current_stream_capturing():
             return -1
         times = {}
-        for cand in (0, 1):
+        if self._flush is None:
+            # weights come from HBM in a real step (every layer has its own): measure with a cold L2
+            with torch.inference_mode(False):      # a plain tensor: it is written in and out of inference mode
+                self._flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+        for cand in allowed:
             for _ in range(2):
                 run(cand)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+            ts = []
             for _ in range(5):
+                self._flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
                 run(cand)
-            e1.record()
-            e1.synchronize()
-            times[cand] = e0.elapsed_time(e1)
+                e1.record()
+                e1.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            times[cand] = sorted(ts)[len(ts) // 2]
         mode = min(times, key=times.get)
         self.table[key] = mode
         self.dirty = True
@@ -87,6 +101,7 @@ class GemmPlan:
         return mode
 
     def save(self):
+        self._flush = None
         if not (self.path and self.dirty):
             return
         os.makedirs(os.path.dirname(self.path), exist_ok=True)

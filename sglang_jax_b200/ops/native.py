@@ -35,6 +35,9 @@ def lib():
                 f"run `python -m sglang_jax_b200.csrc.build`") from e
     L = ctypes.CDLL(_LIB_PATH)
     L.sglb_version.restype = ctypes.c_char_p
+    L.sglb_gemm_decode_cluster.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    L.sglb_gemm_decode_cluster_size.argtypes = [c_int, c_int, c_int]
+    L.sglb_enable_peer_access.argtypes = [c_int, c_int]
     L.sglb_gemm_workspace_bytes.restype = c_size_t
     L.sglb_gemm_workspace_bytes.argtypes = [c_int, c_int, c_int]
     L.sglb_gemm_max_counters.argtypes = [c_int]
@@ -175,6 +178,27 @@ def gemm_scratch(device) -> _GemmScratch:
 
 # measured plan of decode-sized GEMM shapes (model_executor/tuning_cache.GemmPlan), set by the model runner
 gemm_plan = None
+LIBRARY_GEMM = 2          # plan entry: the library GEMM measured faster than both operand assignments for this shape
+CLUSTER_GEMM = 3          # plan entry: split-K inside thread-block clusters (csrc/gemm_decode_cluster.cu)
+_PLAN_CLUSTER = os.environ.get("SGLB_GEMM_PLAN_CLUSTER", "1") == "1"
+
+
+def gemm_decode_cluster(x2, w, bias=None, out=None):
+    """`x2 [M <= 128, K] @ w [N, K]^T (+ bias)` with the cluster split-K kernel; K a multiple of 64, N of 8."""
+    M, K = x2.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=x2.dtype, device=x2.device)
+    L = lib()
+    _check(L.sglb_gemm_decode_cluster(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _stream()), "gemm_decode_cluster")
+    return out
+
+
+def _library_gemm(x2, w, bias, out):
+    if bias is None:
+        torch.matmul(x2, w.t(), out=out)
+    else:
+        torch.addmm(bias, x2, w.t(), out=out)
 
 
 def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0, out=None):
@@ -200,9 +224,25 @@ def linear(x, w, bias=None, force_mode: int = -1, force_splits: int = 0, out=Non
         return out.view(*x.shape[:-1], N)
     sc = gemm_scratch(x.device)
     if gemm_plan is not None and force_mode < 0 and M <= 256:
-        force_mode = gemm_plan.mode_for(
-            M, N, K, lambda mode: lib().sglb_gemm_bf16(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _p(sc.workspace),
-                                                       sc.bytes, _p(sc.counters), mode, 0, _stream()))
+        def run(mode):
+            if mode == LIBRARY_GEMM:
+                _library_gemm(x2, w, bias, out)
+            elif mode == CLUSTER_GEMM:
+                lib().sglb_gemm_decode_cluster(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _stream())
+            else:
+                lib().sglb_gemm_bf16(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _p(sc.workspace), sc.bytes,
+                                     _p(sc.counters), mode, 0, _stream())
+        cluster_ok = (_PLAN_CLUSTER and M <= 128 and K % 64 == 0
+                      and lib().sglb_gemm_decode_cluster_size(M, N, K) > 0)
+        force_mode = gemm_plan.mode_for(M, N, K, run, extra=(CLUSTER_GEMM,) if cluster_ok else ())
+        if force_mode == LIBRARY_GEMM:
+            _library_gemm(x2, w, bias, out)
+            return out.view(*x.shape[:-1], N)
+        if force_mode == CLUSTER_GEMM:
+            if cluster_ok:
+                gemm_decode_cluster(x2, w, bias, out)
+                return out.view(*x.shape[:-1], N)
+            force_mode = -1          # a table entry measured for another M of the same bucket
     _check(lib().sglb_gemm_bf16(_p(x2), _p(w), _p(bias), _p(out), M, N, K, _p(sc.workspace), sc.bytes,
                                 _p(sc.counters), force_mode, force_splits, _stream()), "gemm_bf16")
     return out.view(*x.shape[:-1], N)

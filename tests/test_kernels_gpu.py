@@ -731,3 +731,26 @@ def test_paged_extend_tcgen05_long_and_rescaled(native, P):
         torch.cuda.synchronize()
         native.check_status()
         _close(got, ref.paged_attention(q.float(), cache.float(), pt, rows, sl, P, scale, cu, pl), 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 1280, 5120), (128, 6400, 5120), (128, 5120, 3200), (16, 51200, 5120),
+                                   (1, 10240, 5120), (100, 5120, 1024), (7, 1000, 640), (33, 256, 64)])
+def test_gemm_decode_cluster_split_k(native, M, N, K):
+    """Split-K inside thread-block clusters with the reduction through distributed shared memory vs the fp32 product
+    (cluster sizes 1..8, ragged M, N not a multiple of the tile, ranks with unequal K ranges, bias)."""
+    x = _bf16(M, K, seed=90)
+    w = (_bf16(N, K, seed=91).float() * 0.05).bfloat16()
+    bias = _bf16(N, seed=92)
+    cs = native.lib().sglb_gemm_decode_cluster_size(M, N, K)
+    assert cs in (1, 2, 4, 8)
+    for b in (None, bias):
+        got = native.gemm_decode_cluster(x, w, b)
+        again = native.gemm_decode_cluster(x, w, b)
+        torch.cuda.synchronize()
+        native.check_status()
+        want = x.float() @ w.float().t() + (b.float() if b is not None else 0.0)
+        _close(got, want, 2e-2, 2e-2)
+        assert torch.equal(got, again)                    # fixed summation order: bitwise repeatable
+    # out-of-range shapes are refused, not run
+    assert native.lib().sglb_gemm_decode_cluster_size(129, N, K) == 0
+    assert native.lib().sglb_gemm_decode_cluster_size(M, N, K + 8) == 0

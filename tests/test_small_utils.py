@@ -237,3 +237,22 @@ def test_gemm_plan_is_measured_once_and_persisted(tmp_path):
     again = GemmPlan(path, measure=True)
     assert again.mode_for(100, 5120, 1024, lambda m: calls.append(m)) == 0 and not calls    # bucket 128, from disk
     assert again.mode_for(4096, 5120, 1024, lambda m: calls.append(m)) == -1               # prefill sizes: default
+
+
+def test_suite_runner_checks_floors_on_the_cpu_smoke_suite():
+    """The named-suite runner: cases run through the engine, metrics are compared with floors, a floor that is out of
+    reach fails the case (reference `test/srt/nightly/single_host/suite_runner.py`)."""
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.test import suite_runner as sr
+    assert {"perf-text-models-b200-1", "perf-moe-models-b200", "smoke-cpu"} <= set(sr.SUITES)
+    big = sr.SUITES["perf-text-models-b200-1"]
+    assert [c.kind for c in big] == ["decode", "decode", "prefill"] and big[1].floors == {"out_tps": 865.6}
+    ps.reset_state()
+    res = sr.run_suite("smoke-cpu")
+    assert len(res) == 3 and all(r["passed"] for r in res)
+    assert res[0]["requests"] == 4 and res[-1]["kind"] == "prefill" and res[-1]["in_tps"] > res[-1]["out_tps"]
+    ps.reset_state()
+    import dataclasses
+    hard = sr.run_case(dataclasses.replace(sr.SUITES["smoke-cpu"][0], floors={"out_tps": 1e12}))
+    assert not hard["passed"] and "out_tps" in hard["violations"]
+    ps.reset_state()
