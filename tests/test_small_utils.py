@@ -256,3 +256,60 @@ def test_suite_runner_checks_floors_on_the_cpu_smoke_suite():
     hard = sr.run_case(dataclasses.replace(sr.SUITES["smoke-cpu"][0], floors={"out_tps": 1e12}))
     assert not hard["passed"] and "out_tps" in hard["violations"]
     ps.reset_state()
+
+
+def test_further_accuracy_evals_score_scripted_samplers(tmp_path):
+    """MATH / AIME / GPQA / HumanEval / MGSM / C-SimpleQA against samplers with scripted replies: extraction rules,
+    option shuffling, sandboxed execution with a time limit, grader labels."""
+    import csv
+    import json
+    from sglang_jax_b200.test.eval import simple_eval_more as m
+    from sglang_jax_b200.test.run_eval import build_eval
+    # MATH: last "Answer:" line, LaTeX normalisation, checker only asked when strings differ
+    with open(tmp_path / "math.csv", "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerows([["Question", "Answer"], ["1/2 + 1/4?", "\\frac{3}{4}"], ["2+2?", "4"], ["sqrt(16)?", "4"]])
+    replies = {"1/2": "think...\nAnswer: $\\dfrac{3}{4}$", "2+2": "Answer: 5", "sqrt": "no final line"}
+    asked = []
+    res = m.MathEval(str(tmp_path / "math.csv"), equality_checker=lambda msgs: asked.append(1) or "No")(
+        lambda msgs: next(v for k, v in replies.items() if k in msgs[0]["content"]))
+    assert abs(res.score - 1 / 3) < 1e-9 and abs(res.metrics["invalid"] - 1 / 3) < 1e-9 and len(asked) == 1
+    # AIME: nested braces, integer compare
+    assert m.boxed_answer("so \\boxed{\\frac{1}{2}} then \\boxed{042}") == "042" and m.same_integer("42", "042")
+    (tmp_path / "aime.jsonl").write_text(json.dumps({"problem": "p1", "answer": 42}) + "\n" + json.dumps({"question": "p2", "answer": "7"}) + "\n")
+    res = build_eval("aime25", str(tmp_path / "aime.jsonl"), None, 1)(lambda msgs: "\\boxed{42}")
+    assert res.score == 0.5
+    # GPQA: the correct option moves with the seeded permutation; a sampler that finds it by text scores 1
+    with open(tmp_path / "gpqa.csv", "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["Question", "Correct Answer", "Incorrect Answer 1", "Incorrect Answer 2", "Incorrect Answer 3"])
+        for i in range(6):
+            w.writerow([f"q{i}", f"right{i}", "w1", "w2", "w3"])
+
+    def finder(msgs):
+        lines = msgs[0]["content"].splitlines()
+        return "Answer: " + next(l[0] for l in lines if "right" in l)
+    ev = m.GPQAEval(str(tmp_path / "gpqa.csv"))
+    assert ev(finder).score == 1.0 and ev(lambda msgs: "Answer: A").score < 1.0
+    assert len({tuple(e["permutation"]) for e in ev.examples}) > 1
+    # HumanEval: fenced code is extracted and run; wrong code and endless loops fail within the limit
+    task = {"task_id": "t/0", "prompt": "def add(a, b):\n    \"\"\"sum\"\"\"\n", "entry_point": "add",
+            "test": "def check(f):\n    assert f(2, 3) == 5\n"}
+    (tmp_path / "he.jsonl").write_text(json.dumps(task) + "\n")
+    he = m.HumanEvalEval(str(tmp_path / "he.jsonl"), timeout=3.0, num_threads=1)
+    assert he(lambda msgs: "```python\ndef add(a, b):\n    return a + b\n```").score == 1.0
+    assert he(lambda msgs: "    return a + b\n").score == 1.0                       # bare body continues the stub
+    assert he(lambda msgs: "```python\ndef add(a, b):\n    return a - b\n```").score == 0.0
+    assert he(lambda msgs: "```python\ndef add(a, b):\n    while True:\n        pass\n```").score == 0.0
+    # MGSM: per-language prefix
+    (tmp_path / "mgsm_en.tsv").write_text("q1\t18\nq2\t3\n")
+    (tmp_path / "mgsm_de.tsv").write_text("f1\t5\n")
+    mg = m.MGSMEval(str(tmp_path))
+    res = mg(lambda msgs: "Antwort: 5" if msgs[0]["content"].startswith("Löse") else "steps\nAnswer: 18.")
+    assert res.metrics["de"] == 1.0 and res.metrics["en"] == 0.5 and abs(res.score - 2 / 3) < 1e-9
+    # C-SimpleQA: grader letters -> correct / incorrect / not attempted, F1 of accuracy-given-attempted and correct
+    (tmp_path / "sqa.jsonl").write_text("".join(json.dumps({"question": f"q{i}", "answer": f"a{i}"}) + "\n" for i in range(4)))
+    grades = iter(["A", "B: INCORRECT", "C", "A"])
+    res = m.CSimpleQAEval(str(tmp_path / "sqa.jsonl"), grader=lambda msgs: next(grades), num_threads=1)(lambda msgs: "x")
+    assert res.score == 0.5 and res.metrics["is_not_attempted"] == 0.25
+    assert abs(res.metrics["accuracy_given_attempted"] - 2 / 3) < 1e-9 and abs(res.metrics["f1"] - 4 / 7) < 1e-9

@@ -51,7 +51,7 @@ def _entry(fn, rank, world, port, q, args, ep=False):
     try:
         from sglang_jax_b200.parallel import state as ps
         ps.init_distributed(rank, world, "cuda", 1, world if ep else 1, init_method=f"tcp://127.0.0.1:{port}",
-                            local_rank=rank, timeout_s=120)
+                            local_rank=rank, timeout_s=60)
         out = fn(rank, world, *args)
         q.put((rank, out))
     except Exception:
