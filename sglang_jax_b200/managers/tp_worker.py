@@ -76,9 +76,15 @@ class ModelWorker:
         self.channel = getattr(st, "step_channel", None)
         if self.tp_size > 1 and not is_draft_worker:
             from ..parallel.step_channel import StepChannel
-            self.channel = StepChannel(st.tp, use_shm=getattr(server_args, "nnodes", 1) == 1
-                                       and os.environ.get("SGLB_STEP_CHANNEL", "shm") == "shm",
-                                       timeout_s=float(server_args.dist_timeout or 120.0))
+            mode = os.environ.get("SGLB_STEP_CHANNEL", "shm")
+            multi_node = getattr(server_args, "nnodes", 1) > 1
+            # several nodes (or SGLB_STEP_CHANNEL=zmq): rank 0 publishes the steps at the address the ranks
+            # rendezvous on; one node: shared-memory ring
+            host = None
+            if multi_node or mode == "zmq":
+                host = (server_args.dist_init_addr or "127.0.0.1").rsplit(":", 1)[0]
+            self.channel = StepChannel(st.tp, use_shm=not multi_node and mode == "shm",
+                                       timeout_s=float(server_args.dist_timeout or 120.0), pubsub_host=host)
             st.step_channel = self.channel
         self._pinned_ids = None
         self.marks: dict = {}

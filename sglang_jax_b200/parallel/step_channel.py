@@ -7,7 +7,8 @@ the scheduler on tensor rank 0 ships every step's `ModelWorkerBatch` to the othe
 that goes through a shared-memory ring (`csrc/sched/sched_native.cpp: StepRing`): a plain decode / extend
 step travels as one fixed-layout block of int32 (no pickling, no socket, no host collective), anything
 richer (log-probabilities, adapters, speculative inputs, control messages) as a pickled blob through the
-same ring, so ordering is preserved.  Across nodes the channel falls back to `broadcast_object_list`.
+same ring, so ordering is preserved.  Across nodes the channel is a ZMQ PUB / SUB mirror (rank 0 publishes, the other
+nodes subscribe; sequence numbers expose a dropped message), or `broadcast_object_list` when no address is given.
 
 Failure detection: a follower that stops consuming fills the ring, and the producer's `send` raises after
 `timeout_s`; a follower waits in bounded slices and gives up when the ring is closed.
@@ -135,16 +136,24 @@ def decode_batch(a: np.ndarray):
 class StepChannel:
     """`send(obj)` on the group's first rank, `recv()` on the others."""
 
-    def __init__(self, group, use_shm: bool = True, timeout_s: float = 120.0):
+    def __init__(self, group, use_shm: bool = True, timeout_s: float = 120.0, pubsub_host: str | None = None):
+        """`pubsub_host`: address of rank 0 that the other ranks can reach; selects the ZMQ PUB / SUB mirror (the
+        reference's multi-node form, `managers/scheduler.py:625-676`: the leader publishes every step, follower
+        nodes subscribe) instead of a host collective when the ranks do not share a node."""
         self.group = group
         self.is_root = group.rank == 0
         self.timeout_s = timeout_s
         self.ring = None
+        self.pub = self.sub = None
+        self.seq = 0
         self.sent_fixed = self.sent_pickled = 0
         if group.size <= 1:
             return
         ok = 0
         name = None
+        if pubsub_host and not use_shm:
+            self._init_pubsub(pubsub_host)
+            return
         if use_shm:
             try:
                 from ..mem_cache import _sched_native as sn
@@ -166,13 +175,62 @@ class StepChannel:
         if int(t.item()) == 0:
             self.ring = None
 
+    def _init_pubsub(self, host: str):
+        """Rank 0 binds a PUB socket, the others subscribe and then prove they receive: a PUB socket drops what is
+        published before a subscriber has connected, so rank 0 publishes probes until every rank has seen one
+        (checked through the host group), and only then the channel is open.  Messages carry a sequence number; a
+        gap (dropped message: the subscriber fell behind its high-water mark) is an error, not silent skew."""
+        import threading
+        import zmq
+        ctx = zmq.Context.instance()
+        if self.is_root:
+            self.pub = ctx.socket(zmq.PUB)
+            self.pub.setsockopt(zmq.SNDHWM, 1 << 16)
+            self.pub.setsockopt(zmq.LINGER, 2000)
+            port = self.pub.bind_to_random_port("tcp://*")
+            ps.broadcast_object(f"{host}:{port}", src=0, group=self.group)
+            stop = threading.Event()
+
+            def probe():
+                while not stop.is_set():
+                    self.pub.send_multipart([b"probe", b""])
+                    stop.wait(0.01)
+            t = threading.Thread(target=probe, daemon=True)
+            t.start()
+            ps.barrier(self.group)          # every subscriber has seen a probe
+            stop.set()
+            t.join()
+        else:
+            addr = ps.broadcast_object(None, src=0, group=self.group)
+            self.sub = ctx.socket(zmq.SUB)
+            self.sub.setsockopt(zmq.RCVHWM, 1 << 16)
+            self.sub.setsockopt(zmq.SUBSCRIBE, b"")
+            self.sub.connect(f"tcp://{addr}")
+            if not self.sub.poll(int(self.timeout_s * 1000)):
+                raise RuntimeError(f"no probe from rank 0 at {addr} within {self.timeout_s:.0f}s")
+            ps.barrier(self.group)
+
     @property
     def transport(self) -> str:
+        if self.pub is not None or self.sub is not None:
+            return "zmq-pubsub"
         return "shm-ring" if self.ring is not None else ("none" if self.group.size <= 1 else "gloo-broadcast")
 
     # ------------------------------------------------------------------ root
     def send(self, obj) -> None:
         if self.group.size <= 1:
+            return
+        if self.pub is not None:
+            from ..managers.schedule_batch import ModelWorkerBatch
+            self.seq += 1
+            head = self.seq.to_bytes(8, "little")
+            ints = encode_batch(obj) if isinstance(obj, ModelWorkerBatch) else None
+            if ints is not None:
+                self.pub.send_multipart([b"batch", head, ints.tobytes()])
+                self.sent_fixed += 1
+            else:
+                self.pub.send_multipart([b"pickle", head, pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL)])
+                self.sent_pickled += 1
             return
         if self.ring is None:
             ps.broadcast_object(obj, src=0, group=self.group)
@@ -200,12 +258,37 @@ class StepChannel:
     def close(self):
         if self.ring is not None and self.is_root:
             self.ring.close()
+        if self.pub is not None:
+            self.pub.send_multipart([b"close", b""])
+            self.pub.close()
+            self.pub = None
 
     # ------------------------------------------------------------------ followers
     def recv(self, poll_s: float = 1.0, on_idle=None, block: bool = True):
         """Next message from rank 0.  Waits in `poll_s` slices (calling `on_idle()` between them);
         raises `EOFError` once rank 0 closed the channel.  `block=False` (ring transport only) returns `None`
         when no message has started to arrive within `poll_s`."""
+        if self.sub is not None:
+            while True:
+                if not self.sub.poll(int(poll_s * 1000)):
+                    if on_idle is not None:
+                        on_idle()
+                    if not block:
+                        return None
+                    continue
+                frames = self.sub.recv_multipart()
+                kind = frames[0]
+                if kind == b"probe":
+                    continue
+                if kind == b"close":
+                    raise EOFError("step channel closed by rank 0")
+                seq = int.from_bytes(frames[1], "little")
+                if seq != self.seq + 1:
+                    raise RuntimeError(f"step channel lost messages {self.seq + 1}..{seq - 1} (subscriber fell behind)")
+                self.seq = seq
+                if kind == b"batch":
+                    return decode_batch(np.frombuffer(frames[2], dtype=np.int32))
+                return pickle.loads(frames[2])
         if self.ring is None:
             return ps.broadcast_object(None, src=0, group=self.group)
         parts = []

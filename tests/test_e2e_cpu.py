@@ -119,6 +119,9 @@ def _tp_rank(rank, world, port, ckpt, q):
     else:
         from sglang_jax_b200 import Engine
         eng = Engine(server_args=sa)
+        want = os.environ.get("SGLB_EXPECT_TRANSPORT")
+        if want:
+            assert eng.scheduler.tp_worker.channel.transport == want, eng.scheduler.tp_worker.channel.transport
         outs = eng.generate(input_ids=workload(), sampling_params={"max_new_tokens": 32, "temperature": 0.0,
                                                                     "ignore_eos": True})
         q.put([o["output_ids"] for o in outs])
@@ -135,6 +138,29 @@ def test_tensor_parallel_gloo_matches_oracle(ckpt, oracle, world):
     q = ctx.Queue()
     port = get_free_port()
     procs = [ctx.Process(target=_tp_rank, args=(r, world, port, ckpt, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        outs = q.get(timeout=300)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    assert outs == oracle
+
+
+def test_tensor_parallel_over_the_pubsub_mirror(ckpt, oracle, monkeypatch):
+    """The multi-node form of the step hand-over on one machine: rank 0 publishes every step on a ZMQ PUB socket, the
+    other rank subscribes (probe hand-shake, sequence numbers); same tokens as the oracle."""
+    import torch.multiprocessing as mp
+    from sglang_jax_b200.utils.common import get_free_port
+    monkeypatch.setenv("SGLB_STEP_CHANNEL", "zmq")
+    monkeypatch.setenv("SGLB_EXPECT_TRANSPORT", "zmq-pubsub")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = get_free_port()
+    procs = [ctx.Process(target=_tp_rank, args=(r, 2, port, ckpt, q)) for r in range(2)]
     for p in procs:
         p.start()
     try:
