@@ -355,6 +355,7 @@ class ModelWorkerSamplingInfo:
     vocab_mask: np.ndarray | None = None       # i32 [bs, ceil(vocab/32)], bit set = allowed
     logit_bias: np.ndarray | None = None
     positions: np.ndarray | None = None        # i32 [bs]: position of the token being sampled
+    penalties: object | None = None            # `sampling.penaltylib.PenaltyInfo` when a request uses a penalty
 
     @staticmethod
     def from_reqs(reqs: list[Req], vocab_size: int, penalizer=None) -> "ModelWorkerSamplingInfo":
@@ -491,7 +492,6 @@ class ScheduleBatch:
         self.has_stream = any(r.stream for r in reqs)
         self.has_grammar = any(r.grammar is not None for r in reqs)
         self.spec_info = None
-        self.penalizer = None
 
     @classmethod
     def init_new(cls, reqs, req_to_token_pool, token_to_kv_pool_allocator, tree_cache, vocab_size,
@@ -847,8 +847,9 @@ class ScheduleBatch:
         rows, pos, ids = self.req_to_token_pool.take_page_deltas()
         mm_embeds, mm_rows, mrope, deepstack = self._multimodal_inputs(positions)
         sinfo = ModelWorkerSamplingInfo.from_reqs(self.reqs, self.vocab_size)
-        if self.penalizer is not None:
-            sinfo.linear_penalty = self.penalizer.linear_penalty(self.reqs)
+        if mode != ForwardMode.MIXED:
+            from ..sampling.penaltylib import PenaltyInfo
+            sinfo.penalties = PenaltyInfo.from_reqs(self.reqs, self.seq_lens, mode.is_extend())
         return ModelWorkerBatch(
             bid=_next_bid(), forward_mode=mode, input_ids=self.input_ids,
             req_pool_indices=self.req_pool_indices, seq_lens=self.seq_lens.astype(np.int32),

@@ -194,6 +194,7 @@ class CudaGraphRunner:
         return (self.enabled and batch.forward_mode.is_decode() and len(batch.req_pool_indices) <= self.max_bs
                 and not batch.return_logprob and batch.capture_hidden_mode == 0 and batch.spec_info is None
                 and (si is None or (si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None
+                                    and getattr(si, "penalties", None) is None
                                     and (si.is_all_greedy or self._can_sample_in_graph(si, len(batch.req_pool_indices)))))
                 and (batch.page_delta_rows is None or len(batch.page_delta_rows) <= MAX_PAGE_DELTAS)
                 and not any(batch.lora_ids or []) and getattr(batch, "mrope_positions", None) is None)

@@ -106,6 +106,7 @@ class ModelRunner:
         # forwards with fewer tokens than this use the library all-reduce + add-RMSNorm kernel instead of the fused
         # NVLink kernels (a per-forward choice: both dataflows are exact, they differ in latency)
         self.fused_min_tokens = int(os.environ.get("SGLB_FUSED_MIN_TOKENS", "0"))
+        self.penalty_state = None          # sampling/penaltylib.PenaltyState, created when a request uses a penalty
         self.gemm_plan = None
         if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "1") == "1" and not is_draft_worker:
             # measured GEMM plan, kept on disk between runs (counterpart of the reference's compile / AOT caches)
@@ -291,6 +292,7 @@ class ModelRunner:
         si = batch.sampling_info
         if (comm is not None and not skip_sample and not batch.return_logprob and si is not None and si.is_all_greedy
                 and si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None
+                and getattr(si, "penalties", None) is None
                 and batch.capture_hidden_mode == 0 and len(batch.req_pool_indices) <= 1024):
             fb.extras["skip_logits_gather"] = True     # greedy: reduce (max, index) pairs, not logits
         if self.lora_manager is not None:
@@ -314,6 +316,17 @@ class ModelRunner:
             start, vocab = out.extras["vocab_shard"]
             ids = comm.argmax_gather(out.next_token_logits, start, vocab)
         else:
+            if si is not None and getattr(si, "penalties", None) is not None:
+                # frequency / presence penalties, min_new_tokens: token counts per request slot live on the device
+                # and are brought up to date from this step's (resolved) input ids
+                if self.penalty_state is None:
+                    from ..sampling.penaltylib import PenaltyState
+                    self.penalty_state = PenaltyState(self.req_to_token_pool.size + 1, out.next_token_logits.shape[-1],
+                                                      self.device)
+                decode = batch.forward_mode.is_decode()
+                out.next_token_logits = self.penalty_state.apply(out.next_token_logits, si.penalties,
+                                                                 batch.req_pool_indices,
+                                                                 fb.input_ids if decode else None, decode)
             meta = SamplingMetadata.from_worker_batch(batch, self.device)
             ids = self.sampler(out, meta)
         if batch.future_slots is not None:

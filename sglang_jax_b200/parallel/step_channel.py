@@ -42,7 +42,8 @@ def _plain(batch) -> bool:
             and batch.input_embeds_rows is None and batch.mrope_positions is None and batch.deepstack_embeds is None
             and not batch.recurrent_copies and not batch.recurrent_tracks and batch.extend_logprob_start_lens is None
             and batch.launch_done is None
-            and (si is None or (si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None)))
+            and (si is None or (si.linear_penalty is None and si.vocab_mask is None and si.logit_bias is None
+                                and getattr(si, "penalties", None) is None)))
 
 
 def encode_batch(batch) -> np.ndarray | None:

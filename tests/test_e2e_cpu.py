@@ -304,3 +304,67 @@ def test_follower_death_fails_pending_requests(ckpt):
                 p.kill()
     assert kind == "failed", (kind, detail)
     assert waited < 200, waited
+
+
+# ------------------------------------------------------------------------------------------
+# penalties: token counts live with the model runner and are updated from each step's input ids
+def _penalised_oracle(prompts, n_new, freq, pres, min_new, stop_id):
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    cfg = Qwen3Config(**{k: v for k, v in TINY_QWEN3.items() if k not in ("architectures", "torch_dtype")})
+    m = Qwen3ForCausalLM(cfg).float().eval()
+    sd = tiny_qwen3_state_dict()
+    sd["lm_head.weight"] = sd["model.embed_tokens.weight"]
+    m.load_state_dict(sd, strict=False)
+    outs = []
+    for ids in prompts:
+        cur, gen = list(ids), []
+        counts = torch.zeros(1024)
+        for _ in range(n_new):
+            with torch.no_grad():
+                lg = m(torch.tensor([cur])).logits[0, -1].float()
+            lg = lg - freq * counts - pres * (counts > 0).float()
+            if len(gen) < min_new:
+                lg[stop_id] = float("-inf")
+            t = int(lg.argmax())
+            gen.append(t)
+            cur.append(t)
+            counts[t] += 1
+            if t == stop_id:
+                break
+        outs.append(gen)
+    return outs
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_frequency_presence_penalties_and_min_new_tokens_match_a_manual_oracle(ckpt, overlap):
+    """Greedy decoding with penalties against HF logits penalised by hand: fresh requests, a batch that mixes
+    penalised and plain requests, both schedules (with overlap the host does not know the last token when it
+    builds the next step: the counts are updated on the device from the step's own input ids)."""
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    prompts = workload()[:4]
+    freq, pres, n_new = 0.9, 0.6, 24
+    plain = _penalised_oracle(prompts, n_new, 0.0, 0.0, 0, -1)
+    want = _penalised_oracle(prompts, n_new, freq, pres, 0, -1)
+    assert want != plain                                           # the penalties change these sequences
+    stop = plain[0][2]                                             # a token the plain run emits early
+    want_min = _penalised_oracle(prompts[:1], n_new, 0.0, 0.0, 6, stop)[0]
+    assert stop not in want_min[:6]
+    ps.reset_state()
+    eng = Engine(model_path=ckpt, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                 max_total_tokens=8192, enable_single_process=True, max_running_requests=16,
+                 disable_overlap_schedule=not overlap, log_level="error")
+    try:
+        sp = {"max_new_tokens": n_new, "temperature": 0.0, "ignore_eos": True}
+        pen = dict(sp, frequency_penalty=freq, presence_penalty=pres)
+        got = eng.generate(input_ids=prompts, sampling_params=[pen, pen, sp, pen])
+        assert [o["output_ids"] for o in got] == [want[0], want[1], plain[2], want[3]]
+        # min_new_tokens: the stop token is suppressed for the first six tokens, then ends the request
+        r = eng.generate(input_ids=prompts[0], sampling_params={"max_new_tokens": n_new, "temperature": 0.0,
+                                                                "min_new_tokens": 6, "stop_token_ids": [stop]})
+        assert r["output_ids"] == want_min and len(want_min) >= 6
+        # the slot's counts are reset when another request reuses it
+        again = eng.generate(input_ids=prompts[:2], sampling_params=pen)
+        assert [o["output_ids"] for o in again] == want[:2]
+    finally:
+        eng.shutdown()

@@ -313,3 +313,24 @@ def test_further_accuracy_evals_score_scripted_samplers(tmp_path):
     res = m.CSimpleQAEval(str(tmp_path / "sqa.jsonl"), grader=lambda msgs: next(grades), num_threads=1)(lambda msgs: "x")
     assert res.score == 0.5 and res.metrics["is_not_attempted"] == 0.25
     assert abs(res.metrics["accuracy_given_attempted"] - 2 / 3) < 1e-9 and abs(res.metrics["f1"] - 4 / 7) < 1e-9
+
+
+def test_penalty_state_restart_and_decode_updates():
+    """The device-side count table: a (re)starting request seeds its slot with the tokens it already generated (a
+    retracted request prefills again over prompt + output), decode steps add their input ids, other slots stay."""
+    import numpy as np
+    import torch
+    from sglang_jax_b200.sampling.penaltylib import PenaltyInfo, PenaltyState
+    st = PenaltyState(4, 16, torch.device("cpu"))
+    info = PenaltyInfo(np.array([1.0, 0.0], np.float32), np.array([0.5, 0.0], np.float32), np.array([0, 3], np.int32),
+                       np.array([3, 0], np.int32), np.array([[-1, -1], [7, 9]], np.int32),
+                       np.array([0, 1], np.int32), [[5, 5, 2], []])
+    out = st.apply(torch.zeros(2, 16), info, [2, 0], None, False)
+    assert st.counts[2].tolist()[2] == 1 and st.counts[2].tolist()[5] == 2 and int(st.counts[0].sum()) == 0
+    assert out[0, 5] == -2.5 and out[0, 2] == -1.5 and out[0, 0] == 0.0
+    assert out[1, 7] == float("-inf") and out[1, 9] == float("-inf") and out[1, 8] == 0.0     # min_new_tokens
+    dec = PenaltyInfo(info.frequency, info.presence, info.min_new_tokens, np.array([4, 3], np.int32), info.stop_ids,
+                      np.empty(0, np.int32), [])
+    out = st.apply(torch.zeros(2, 16), dec, [2, 0], torch.tensor([5, 7]), True)
+    assert st.counts[2, 5] == 3 and st.counts[0, 7] == 1 and out[0, 5] == -3.5 and out[1, 7] == 0.0
+    assert int(st.counts[1].sum()) == 0 and int(st.counts[3].sum()) == 0
