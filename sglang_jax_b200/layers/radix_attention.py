@@ -75,9 +75,24 @@ class RadixAttention(nn.Module):
         else:
             mask = fb.spec_info.custom_mask if (fb.spec_info is not None and
                                                 getattr(fb.spec_info, "custom_mask", None) is not None) else None
-            out = attn(q, kv_buffer, page_table, fb.req_pool_indices, fb.seq_lens, fb.page_size, self.scaling,
-                       fb.cu_q_lens, fb.extend_prefix_lens, self.sliding_window_size, self.logit_cap, sinks,
-                       mask, **kw)
+            nd = int(getattr(fb, "num_decode_in_mixed", 0) or 0)
+            B = fb.req_pool_indices.shape[0]
+            if nd > 0 and mask is None and nd < B:
+                # mixed step: the trailing `nd` requests are one-token decodes.  They go through the decode kernel
+                # (split-KV over their whole context) instead of occupying a 128-row query tile each in the
+                # prefill kernel; the leading requests are ordinary prefill rows.
+                np_ = B - nd
+                tp = q.shape[0] - nd
+                out_p = attn(q[:tp], kv_buffer, page_table, fb.req_pool_indices[:np_], fb.seq_lens[:np_], fb.page_size,
+                             self.scaling, fb.cu_q_lens[:np_ + 1], fb.extend_prefix_lens[:np_],
+                             self.sliding_window_size, self.logit_cap, sinks, None, **kw)
+                out_d = attn(q[tp:], kv_buffer, page_table, fb.req_pool_indices[np_:], fb.seq_lens[np_:], fb.page_size,
+                             self.scaling, None, None, self.sliding_window_size, self.logit_cap, sinks, None, **kw)
+                out = torch.cat([out_p.reshape(tp, -1), out_d.reshape(nd, -1)], dim=0)
+            else:
+                out = attn(q, kv_buffer, page_table, fb.req_pool_indices, fb.seq_lens, fb.page_size, self.scaling,
+                           fb.cu_q_lens, fb.extend_prefix_lens, self.sliding_window_size, self.logit_cap, sinks,
+                           mask, **kw)
         return out.reshape(out.shape[0], self.num_heads * self.head_dim)
 
 
