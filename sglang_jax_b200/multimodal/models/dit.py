@@ -72,6 +72,19 @@ def _sdpa(q, k, v):
                                                             ).transpose(1, 2)
 
 
+def _self_attention(q, k, v):
+    """Dense bidirectional self-attention `[B, N, H, D]`.  On the GPU (bf16, head dim up to 128) the batch is one
+    packed sequence list for the varlen attention kernel (tcgen05 for head dim 128), counterpart of the reference's
+    `multimodal/kernels/flash_attention.py`; elsewhere torch SDPA."""
+    B, N, H, D = q.shape
+    from ... import ops
+    if ops.use_native(q) and q.dtype == torch.bfloat16 and D in (64, 128):
+        o = ops.varlen_attention(q.reshape(B * N, H, D).contiguous(), k.reshape(B * N, H, D).contiguous(),
+                                 v.reshape(B * N, H, D).contiguous(), [N] * B, D ** -0.5)
+        return o.reshape(B, N, H, D)
+    return _sdpa(q, k, v)
+
+
 class WanBlock(nn.Module):
     def __init__(self, dim, heads, ffn, dtype):
         super().__init__()
@@ -96,7 +109,7 @@ class WanBlock(nn.Module):
         q = _rms(_apply(self.q, h), self.norm_q).view(B, N, H, -1)
         k = _rms(_apply(self.k, h), self.norm_k).view(B, N, H, -1)
         v = _apply(self.v, h).view(B, N, H, -1)
-        a = _sdpa(apply_rope_pairs(q, cos, sin), apply_rope_pairs(k, cos, sin), v).reshape(B, N, D)
+        a = _self_attention(apply_rope_pairs(q, cos, sin), apply_rope_pairs(k, cos, sin), v).reshape(B, N, D)
         x = (x.float() + _apply(self.o, a).float() * m[2][:, None]).to(x.dtype)
         h = torch.nn.functional.layer_norm(x.float(), (D,), self.norm3_w.float(), self.norm3_b.float(), 1e-6).to(x.dtype)
         q = _rms(_apply(self.cq, h), self.norm_cq).view(B, N, H, -1)
