@@ -14,7 +14,9 @@ class VaeScheduler(StageScheduler):
     def __init__(self, stage_config, devices, model_dir, dtype=torch.bfloat16, config_overrides=None, **kw):
         super().__init__(stage_config, devices, model_dir, dtype)
         from ...models.vae import AutoencoderKL, AutoencoderKLWan
-        classes = {"AutoencoderKLWan": AutoencoderKLWan, "AutoencoderKL": AutoencoderKL}
+        from ...models.wan_vae import WanVAE
+        # "AutoencoderKLWan": the reduced causal decoder; "WanVAE": the full encoder / decoder with feature cache
+        classes = {"AutoencoderKLWan": AutoencoderKLWan, "AutoencoderKL": AutoencoderKL, "WanVAE": WanVAE}
         sub = stage_config.stage_sub_dir or "vae"
         cfg = load_stage_config(model_dir, sub, config_overrides)
         # decoding in fp32: group norms over large activations lose too much in bf16

@@ -748,3 +748,50 @@ def test_media_preprocessing_matches_hf_processors():
     assert expand_placeholders([1, 9, 2, 9, 3], 9, [3, 1]) == [1, 9, 9, 9, 2, 9, 3]
     with pytest.raises(ValueError):
         expand_placeholders([1, 9], 9, [1, 2])
+
+
+def test_wan_vae_encoder_decoder_with_feature_cache():
+    """The full Wan video VAE: 1 + 4k frames <-> 1 + k latent frames (8x in space), processed in chunks with cached
+    convolution tails.  Causality makes the chunked pass prefix-stable: the latents of a longer clip start with the
+    latents of its prefix, and so do the decoded frames."""
+    from types import SimpleNamespace
+    import torch
+    from sglang_jax_b200.multimodal.models.wan_vae import WanVAE
+    torch.manual_seed(0)
+    cfg = SimpleNamespace(base_dim=8, z_dim=4, dim_mult=(1, 2, 4, 4), num_res_blocks=1,
+                          temporal_downsample=(False, True, True), latents_mean=[0.1, -0.2, 0.0, 0.3],
+                          latents_std=[1.5, 0.5, 1.0, 2.0])
+    vae = WanVAE(cfg).eval()
+    for p in vae.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.15)
+    video = torch.rand(1, 3, 9, 32, 32) * 2 - 1
+    z9 = vae.encode(video)
+    assert z9.shape == (1, 4, 3, 4, 4)
+    z5 = vae.encode(video[:, :, :5])
+    z1 = vae.encode(video[:, :, :1])
+    assert z5.shape == (1, 4, 2, 4, 4) and z1.shape == (1, 4, 1, 4, 4)
+    assert torch.allclose(z9[:, :, :2], z5, atol=1e-5) and torch.allclose(z9[:, :, :1], z1, atol=1e-5)
+    other = video.clone()
+    other[:, :, 5:] = 0.5                                    # later frames differ: earlier latents must not move
+    assert torch.allclose(vae.encode(other)[:, :, :2], z9[:, :, :2], atol=1e-5)
+    assert not torch.allclose(vae.encode(other)[:, :, 2], z9[:, :, 2], atol=1e-3)
+    out = vae.decode(z9)
+    assert out.shape == (1, 3, 9, 32, 32) and out.abs().max() <= 1.0
+    out5 = vae.decode(z9[:, :, :2])
+    assert out5.shape == (1, 3, 5, 32, 32) and torch.allclose(out[:, :, :5], out5, atol=1e-5)
+    assert vae.decode(z9[:, :, :1]).shape == (1, 3, 1, 32, 32)
+    # the latent normalisation is undone by decode: scaling statistics cancel
+    raw = WanVAE(SimpleNamespace(**{**cfg.__dict__, "latents_mean": None, "latents_std": None})).eval()
+    raw.load_state_dict(vae.state_dict())
+    zr = raw.encode(video)
+    mean, std = torch.tensor(cfg.latents_mean).view(1, 4, 1, 1, 1), torch.tensor(cfg.latents_std).view(1, 4, 1, 1, 1)
+    assert torch.allclose((zr - mean) / std, z9, atol=1e-5) and torch.allclose(raw.decode(zr), out, atol=1e-5)
+    # checkpoint tensors load by name
+    names = set(n for n, _ in vae.named_parameters())
+    assert {"encoder.conv_in.weight", "encoder.down_blocks.0.norm1.gamma", "encoder.mid_block.attentions.0.to_qkv.weight",
+            "quant_conv.weight", "post_quant_conv.weight", "decoder.up_blocks.0.upsamplers.0.time_conv.weight",
+            "decoder.up_blocks.2.upsamplers.0.resample.1.weight", "decoder.conv_out.bias"} <= names
+    fresh = WanVAE(cfg).eval()
+    assert fresh.load_weights(vae.state_dict().items()) == names
+    assert torch.allclose(fresh.encode(video), z9, atol=1e-6)
