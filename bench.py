@@ -400,13 +400,18 @@ def main():
                 return
         state["steps"] += 1
         now = time.perf_counter()
+        this_kind = "decode" if batch.forward_mode.is_decode() else "prefill"
         if state["phase"] == "timed":
-            kind = "decode" if batch.forward_mode.is_decode() else "prefill"
+            # With overlap scheduling this hook runs after batch i was launched and batch i-1's result was waited
+            # for, so the interval that ends here is the device time of batch i-1: it is booked to that batch's kind.
+            kind = state.get("prev_kind", this_kind) if s.enable_overlap else this_kind
             state[kind + "_s"] = state.get(kind + "_s", 0.0) + now - state["last_t"]
             state[kind + "_n"] = state.get(kind + "_n", 0) + 1
             if not batch.forward_mode.is_decode():
                 state["prefill_tok"] = state.get("prefill_tok", 0) + int(sum(batch.extend_lens))
+                state["prefill_batches"] = state.get("prefill_batches", 0) + 1
             state["d2h"] += 4 * len(batch.reqs)
+        state["prev_kind"] = this_kind
         state["last_t"] = now
         if state["steps"] == W + 1 and state["phase"] == "warmup":
             # the steady state's first step counts as warm-up step 0; W more have run since
@@ -555,6 +560,8 @@ def main():
                          f"({runner.weight_bytes / 2**30:.1f} GiB) plus KV" if runner is not None else "n/a",
                    "window": "steady-state closed loop (staggered fill, periodic decode/prefill mix)",
                    "cuda_graph": gr is not None, "fused_comm": st.fused_comm is not None,
+                   "fused_tokens": ([runner.fused_min_tokens, runner.fused_max_tokens]
+                                    if st.fused_comm is not None and runner is not None else None),
                    "mixed_chunk": bool(sa.enable_mixed_chunk),
                    "overlap_schedule": sched.enable_overlap, "layers": cfg["num_hidden_layers"]},
         "clocks": clock_info, "e2e": e2e, "latency": latency,
@@ -567,7 +574,8 @@ def main():
         "timed_h2d_bytes_per_step": int((state.get("h2d1", 0) - state.get("h2d0", 0)) // max(K, 1)),
         "step_breakdown": {"decode": {"steps": dn, "host_ms_per_step": round(1e3 * state.get("decode_s", 0.0) / max(dn, 1), 3)},
                            "prefill": {"steps": pn, "host_ms_per_step": round(1e3 * state.get("prefill_s", 0.0) / max(pn, 1), 3),
-                                       "tokens_per_step": round(state.get("prefill_tok", 0) / max(pn, 1), 1)}},
+                                       "tokens_per_step": round(state.get("prefill_tok", 0)
+                                                                / max(state.get("prefill_batches", 0), 1), 1)}},
     }
     if args.layers:
         out["invalid"] = "debug run with fewer layers than the named model"

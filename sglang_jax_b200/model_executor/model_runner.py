@@ -105,7 +105,13 @@ class ModelRunner:
         self.fused_residual_ok = model_supports_fused_residual(self.model)
         # forwards with fewer tokens than this use the library all-reduce + add-RMSNorm kernel instead of the fused
         # NVLink kernels (a per-forward choice: both dataflows are exact, they differ in latency)
+        # Forwards of `fused_min_tokens <= T <= fused_max_tokens` rows take the fused NVLink dataflow, the others the
+        # library all-reduce.  Measured on Qwen3-32B (TP2 and TP4, 128 running requests): a decode step (T = 128) is
+        # faster fused (12.9 ms against 16.0 ms at TP4), a prefill step (T ~ 1300) is faster with the library
+        # all-reduce (19.0 ms against 31.8 ms at TP4): the first is bound by the latency of 128 reduces, which one
+        # launch with peer stores shortens; the second by GEMM throughput, which the fused kernel's tail interrupts.
         self.fused_min_tokens = int(os.environ.get("SGLB_FUSED_MIN_TOKENS", "0"))
+        self.fused_max_tokens = int(os.environ.get("SGLB_FUSED_MAX_TOKENS", "512"))
         self.penalty_state = None          # sampling/penaltylib.PenaltyState, created when a request uses a penalty
         self.gemm_plan = None
         if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "1") == "1" and not is_draft_worker:
@@ -249,7 +255,7 @@ class ModelRunner:
         from ..utils.precision_tracer import precision_tracer
         inner = getattr(self.model, "model", None)
         on = (self.fused_residual_ok and not precision_tracer.enabled
-              and (fb is None or fb.num_tokens >= self.fused_min_tokens)
+              and (fb is None or self.fused_min_tokens <= fb.num_tokens <= self.fused_max_tokens)
               and (fb is None or fb.extras.get("deepstack") is None)
               and not getattr(inner, "layers_to_capture", None)
               and not getattr(self.model, "capture_aux_hidden_states", False))

@@ -159,6 +159,36 @@ def test_engine_generate_gpu(tiny_path):
     assert agree >= 2, outs
 
 
+def test_engine_mixed_chunk_and_penalties_gpu(tiny_path):
+    """`--enable-mixed-chunk` on the GPU kernels: in a mixed step the prefill rows run on the extend kernel and the
+    decode rows on the decode kernel; greedy output starts like the unmixed engine's.  A request with penalties
+    (token counts kept on the device, outside the CUDA graphs) runs in the same engine."""
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.ops import native
+    from sglang_jax_b200.parallel import state as ps
+    prompts = [list(range(1, 50)), list(range(3, 200)), [7] * 20]
+    sp = {"max_new_tokens": 12, "temperature": 0.0, "ignore_eos": True}
+    outs = {}
+    for mixed in (False, True):
+        ps.reset_state()
+        eng = Engine(model_path=tiny_path, device="cuda", dtype="bfloat16", page_size=16, skip_tokenizer_init=True,
+                     max_total_tokens=8192, max_running_requests=8, enable_single_process=True, cuda_graph_max_bs=8,
+                     enable_mixed_chunk=mixed, chunked_prefill_size=64)
+        try:
+            outs[mixed] = [x["output_ids"] for x in eng.generate(input_ids=prompts, sampling_params=sp)]
+            if mixed:
+                pen = eng.generate(input_ids=[7] * 20, sampling_params=dict(sp, frequency_penalty=1.5,
+                                                                            presence_penalty=0.5, min_new_tokens=4))
+                assert len(pen["output_ids"]) == 12
+        finally:
+            eng.shutdown()
+    torch.cuda.synchronize()
+    native.check_status()
+    assert all(len(x) == 12 for x in outs[True])
+    agree = sum(a[:4] == b[:4] for a, b in zip(outs[True], outs[False]))
+    assert agree >= 2, outs
+
+
 @pytest.mark.parametrize("algo,topk,steps,ndraft,page", [("STANDALONE", 1, 3, 4, 16), ("STANDALONE", 3, 3, 8, 16),
                                                          ("EAGLE", 2, 3, 6, 1)])
 def test_speculative_decoding_gpu(tiny_path, algo, topk, steps, ndraft, page):

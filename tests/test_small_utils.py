@@ -334,3 +334,24 @@ def test_penalty_state_restart_and_decode_updates():
     out = st.apply(torch.zeros(2, 16), dec, [2, 0], torch.tensor([5, 7]), True)
     assert st.counts[2, 5] == 3 and st.counts[0, 7] == 1 and out[0, 5] == -3.5 and out[1, 7] == 0.0
     assert int(st.counts[1].sum()) == 0 and int(st.counts[3].sum()) == 0
+
+
+def test_residual_dataflow_token_window():
+    """The fused NVLink dataflow is chosen for forwards inside the token window only (decode-sized ones by default)."""
+    from types import SimpleNamespace
+    from sglang_jax_b200.layers import fused_block
+    from sglang_jax_b200.model_executor.model_runner import ModelRunner
+    model = SimpleNamespace(model=SimpleNamespace(layers_to_capture=None), capture_aux_hidden_states=False)
+    r = SimpleNamespace(fused_residual_ok=True, fused_min_tokens=0, fused_max_tokens=512, model=model)
+    fb = lambda n: SimpleNamespace(num_tokens=n, extras={})
+    try:
+        assert ModelRunner.select_residual_dataflow(r, fb(128)) is True
+        assert fused_block._FUSED_RESIDUAL is True
+        assert ModelRunner.select_residual_dataflow(r, fb(1300)) is False
+        assert fused_block._FUSED_RESIDUAL is False
+        r.fused_min_tokens = 256
+        assert ModelRunner.select_residual_dataflow(r, fb(128)) is False
+        assert ModelRunner.select_residual_dataflow(r, fb(300)) is True
+        assert ModelRunner.select_residual_dataflow(r, SimpleNamespace(num_tokens=300, extras={"deepstack": 1})) is False
+    finally:
+        fused_block.set_fused_residual(True)
