@@ -274,9 +274,13 @@ class HiRadixCache(RadixCache):
             n.host_value = None
             p = n.parent
             del p.children[n.child_key]
+            self._on_host_node_removed(n)
             if p is not self.root_node and p.evicted and p.backuped and not p.children and p.lock_ref == 0:
                 heapq.heappush(cands, p)
         return freed
+
+    def _on_host_node_removed(self, n: TreeNode):
+        """A host-only node left the tree for good (hook for trees that keep more than KV on a node)."""
 
     def host_size_pages(self) -> int:
         return self.host_pool.num_pages - self.host_pool.available_pages()

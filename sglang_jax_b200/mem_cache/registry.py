@@ -6,7 +6,8 @@ Factories are looked up by name so a deployment can register its own (`register_
 
 * sliding-window hybrid KV pool      -> `SWARadixCache` over the dual allocator
 * `--disable-radix-cache`            -> `ChunkCache`
-* recurrent (linear-attention) model -> `UnifiedRadixCache` (needs snapshot slots, else no sharing)
+* recurrent (linear-attention) model -> `UnifiedRadixCache` (needs snapshot slots, else no sharing);
+  with `--hicache-storage` `UnifiedHiRadixCache`
 * `--hicache-storage`                -> `HiRadixCache`
 * otherwise                          -> radix tree (C++ when built)
 """
@@ -59,11 +60,9 @@ def default_radix_cache_factory(ctx: TreeCacheBuildContext) -> TreeCacheBuildRes
     from .chunk_cache import ChunkCache
     sa, kv, rp = ctx.server_args, ctx.kv_pool, ctx.recurrent_pool
     recurrent = is_recurrent(ctx)
-    if recurrent and not sa.disable_radix_cache and (rp is None or rp.snapshot_slots <= 0
-                                                     or sa.hicache_storage != "disable"):
+    if recurrent and not sa.disable_radix_cache and (rp is None or rp.snapshot_slots <= 0):
         # a shared prefix needs the recurrent state at its end: checkpoints live in the snapshot area
-        logger.info("hybrid linear-attention model: prefix sharing is off (needs --recurrent-snapshot-slots > 0 "
-                    "and no host cache tier)")
+        logger.info("hybrid linear-attention model: prefix sharing is off (needs --recurrent-snapshot-slots > 0)")
         sa.disable_radix_cache = True
     if kv is not None and hasattr(kv, "swa_pool"):
         from .allocator import SWATokenToKVPoolAllocator
@@ -78,11 +77,18 @@ def default_radix_cache_factory(ctx: TreeCacheBuildContext) -> TreeCacheBuildRes
     if sa.disable_radix_cache:
         return TreeCacheBuildResult(alloc, ChunkCache(p.req_to_token_pool, alloc, p.page_size))
     if recurrent:
-        from .unified_radix_cache import UnifiedRadixCache
-        cache = UnifiedRadixCache(p.req_to_token_pool, alloc, p.page_size, num_request_slots=rp.size,
-                                  num_snapshot_slots=rp.snapshot_slots, enable_kv_cache_events=p.enable_kv_cache_events,
-                                  track_interval=getattr(sa, "recurrent_track_interval", None),
-                                  commit_on_finish=bool(sa.disable_overlap_schedule))
+        from .unified_radix_cache import UnifiedHiRadixCache, UnifiedRadixCache
+        snap = dict(num_request_slots=rp.size, num_snapshot_slots=rp.snapshot_slots,
+                    enable_kv_cache_events=p.enable_kv_cache_events,
+                    track_interval=getattr(sa, "recurrent_track_interval", None),
+                    commit_on_finish=bool(sa.disable_overlap_schedule))
+        if sa.hicache_storage != "disable" and kv is not None:
+            # KV of the full-attention layers gets the host tier; checkpoints of the recurrent state stay on the device
+            cache = UnifiedHiRadixCache(p.req_to_token_pool, alloc, p.page_size, kv, hicache_ratio=sa.hicache_ratio,
+                                        write_policy=sa.hicache_write_policy,
+                                        write_through_threshold=sa.hicache_write_through_threshold, **snap)
+        else:
+            cache = UnifiedRadixCache(p.req_to_token_pool, alloc, p.page_size, **snap)
         # checkpoints taken inside prefill steps are safe under overlap scheduling; the one at the end of a finished
         # request reads the request's own slot, which an overlapped extra decode step may already have advanced, so
         # it is only taken when the schedule is sequential

@@ -20,6 +20,13 @@ child), and they have their own LRU over a fixed number of snapshot slots instea
 eviction — a node can lose its snapshot and keep its KV.  State copies are not executed here:
 the tree runs in the scheduler, the pools live in every tensor rank, so copies are queued
 (`take_recurrent_copies`) and travel with the next batch to all ranks, in order.
+
+The snapshot logic is a mixin over the tree that stores the KV (`UnifiedRadixCache`: the plain radix tree;
+`UnifiedHiRadixCache`: the tree with a host-memory tier, the reference's HiCache hooks `write_backup` :835,
+`evict_host` :1022, `init_load_back` :1061).  With the host tier a node whose KV was demoted to the host keeps its
+snapshot (snapshots are small and have their own LRU), so a later request can match through host-only nodes up to the
+deepest checkpoint, have the KV of that chain loaded back and start from the checkpoint; if the load-back finds no
+device memory the request falls back to the deepest checkpoint whose KV is still on the device.
 """
 
 from __future__ import annotations
@@ -30,6 +37,7 @@ from enum import IntEnum
 import numpy as np
 
 from .base_prefix_cache import MatchResult
+from .hiradix_cache import HiRadixCache
 from .radix_cache import RadixCache, RadixKey, TreeNode
 
 
@@ -38,10 +46,11 @@ class ComponentType(IntEnum):
     RECURRENT = 1
 
 
-class UnifiedRadixCache(RadixCache):
-    def __init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size: int = 1, disable: bool = False,
-                 num_request_slots: int = 0, num_snapshot_slots: int = 0, enable_kv_cache_events: bool = False,
-                 track_interval: int | None = None, commit_on_finish: bool = True):
+class _RecurrentSnapshots:
+    """Checkpoints of the recurrent state on tree nodes; mixed into a radix tree class (see the module docstring)."""
+
+    def _init_snapshots(self, page_size: int, num_request_slots: int, num_snapshot_slots: int,
+                        track_interval: int | None, commit_on_finish: bool):
         self.components = (ComponentType.FULL, ComponentType.RECURRENT)
         # checkpoint the final state of a finished request from its own slot: only sound when no overlapped extra
         # decode step can have advanced that slot past the request's last cached token
@@ -53,7 +62,6 @@ class UnifiedRadixCache(RadixCache):
                              f"page size ({page_size})")
         self.snapshot_base = num_request_slots + 1          # request row r owns state slot r + 1
         self.num_snapshot_slots = num_snapshot_slots
-        super().__init__(req_to_token_pool, token_to_kv_pool_allocator, page_size, disable, enable_kv_cache_events)
 
     # ---------------------------------------------------------------- state
     def reset(self):
@@ -66,6 +74,8 @@ class UnifiedRadixCache(RadixCache):
         # request id -> [aligned length, tokens of the extend before it, snapshot slot, sent to the workers]
         self._pending_track: dict[str, list] = {}
         self._raw_match = False
+        # host-tier matches: id of the host-only checkpoint node -> the device checkpoint node the match fell back to
+        self._load_stop: dict[int, TreeNode] = {}
 
     def supports_recurrent(self) -> bool:
         return True
@@ -97,24 +107,47 @@ class UnifiedRadixCache(RadixCache):
         res = super().match_prefix(key)
         if self._raw_match:
             return res                                    # re-pointing a running request at its own prefix
-        node = res.last_device_node
-        if self.disable or node is self.root_node:
-            if req is not None:
-                req.recurrent_cow_src = None
-            return MatchResult(np.empty(0, np.int32), self.root_node, self.root_node)
-        total = len(res.device_indices)
-        # deepest node on the matched path that also has the recurrent state at its end
-        while node is not self.root_node and node.id not in self._snap:
-            total -= len(node.key)
-            node = node.parent
-        if node is self.root_node:
-            if req is not None:
-                req.recurrent_cow_src = None
-            return MatchResult(np.empty(0, np.int32), self.root_node, self.root_node)
-        self._lru.move_to_end(node.id)
+        root = self.root_node
+        empty = MatchResult(np.empty(0, np.int32), root, root)
+        deepest = res.last_host_node if res.host_hit_length else res.last_device_node
         if req is not None:
-            req.recurrent_cow_src = self._snap[node.id]
-        return MatchResult(res.device_indices[:total], node, node)
+            req.recurrent_cow_src = None
+        if self.disable or deepest is None or deepest is root:
+            return empty
+        path = []
+        n = deepest
+        while n is not root:
+            path.append(n)
+            n = n.parent
+        path.reverse()
+        # deepest node with the recurrent state at its end: on the whole matched path, and on its device part
+        dev_total = len(res.device_indices)
+        cum = 0
+        on_dev = on_any = None
+        for n in path:
+            cum += len(n.key)
+            if n.id in self._snap:
+                on_any = (n, cum)
+                if cum <= dev_total and not n.evicted:
+                    on_dev = (n, cum)
+        if on_any is None:
+            return empty
+        self._lru.move_to_end(on_any[0].id)
+        if on_dev is not None:
+            self._lru.move_to_end(on_dev[0].id)
+        if on_any is on_dev or on_any[1] <= dev_total:
+            node, total = on_any
+            if req is not None:
+                req.recurrent_cow_src = self._snap[node.id]
+            return MatchResult(res.device_indices[:total], node, node)
+        # the deepest checkpoint sits on a node whose KV is on the host tier: report the device part up to the
+        # deepest device checkpoint and the rest as a host hit; `init_load_back` completes it
+        dev_node, dev_len = on_dev if on_dev is not None else (root, 0)
+        host_node, host_end = on_any
+        self._load_stop[host_node.id] = dev_node
+        if req is not None:
+            req.recurrent_cow_src = self._snap[(dev_node if on_dev is not None else host_node).id]
+        return MatchResult(res.device_indices[:dev_len], dev_node, host_node, host_end - dev_len)
 
     # ---------------------------------------------------------------- request hooks
     def cache_finished_req(self, req, is_insert: bool = True, **kw):
@@ -193,9 +226,13 @@ class UnifiedRadixCache(RadixCache):
         return out
 
     def on_request_scheduled(self, req):
-        """First prefill of a request that matched a snapshot: clone it into the request's slot."""
+        """First prefill of a request that matched a snapshot: clone it into the request's slot.  The request's last
+        node decides which one: after a load-back from the host tier it is the deeper checkpoint."""
         src = getattr(req, "recurrent_cow_src", None)
         if src is not None and len(req.prefix_indices) > 0:
+            node = getattr(req, "last_node", None)
+            if node is not None and getattr(node, "id", None) in self._snap:
+                src = self._snap[node.id]
             self.queue_copy(src, req.req_pool_idx + 1)
         req.recurrent_cow_src = None
 
@@ -218,6 +255,55 @@ class UnifiedRadixCache(RadixCache):
         return None
 
     def _drop(self, n: TreeNode):
-        if n.id in self._snap:
+        # a node that stays in the tree as a host-only node keeps its checkpoint
+        if n.id in self._snap and not n.backuped:
             self._release_snapshot(n.id)
         super()._drop(n)
+
+    def _on_host_node_removed(self, n: TreeNode):
+        if n.id in self._snap:
+            self._release_snapshot(n.id)
+        self._load_stop.pop(n.id, None)
+
+
+class UnifiedRadixCache(_RecurrentSnapshots, RadixCache):
+    def __init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size: int = 1, disable: bool = False,
+                 num_request_slots: int = 0, num_snapshot_slots: int = 0, enable_kv_cache_events: bool = False,
+                 track_interval: int | None = None, commit_on_finish: bool = True):
+        self._init_snapshots(page_size, num_request_slots, num_snapshot_slots, track_interval, commit_on_finish)
+        RadixCache.__init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size, disable,
+                            enable_kv_cache_events)
+
+
+class UnifiedHiRadixCache(_RecurrentSnapshots, HiRadixCache):
+    """FULL + RECURRENT components over the tree with a host-memory KV tier."""
+
+    def __init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size: int, device_pool,
+                 num_request_slots: int = 0, num_snapshot_slots: int = 0, track_interval: int | None = None,
+                 commit_on_finish: bool = True, hicache_ratio: float = 2.0, write_policy: str = "write_through",
+                 write_through_threshold: int = 1, host_pages: int | None = None, disable: bool = False,
+                 enable_kv_cache_events: bool = False):
+        self._init_snapshots(page_size, num_request_slots, num_snapshot_slots, track_interval, commit_on_finish)
+        HiRadixCache.__init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size, device_pool,
+                              hicache_ratio, write_policy, write_through_threshold, host_pages, disable=disable,
+                              enable_kv_cache_events=enable_kv_cache_events)
+
+    def init_load_back(self, last_host_node: TreeNode, host_hit_length: int):
+        """Host-tier trees only.  The host hit of a checkpoint match spans the device-resident nodes between the device
+        checkpoint and the host-only chain, then the chain itself: return the slots of both, in order."""
+        root = self.root_node
+        stop = self._load_stop.pop(last_host_node.id, root)
+        n = last_host_node
+        while n is not root and n.evicted:
+            n = n.parent
+        middle = []
+        while n is not root and n is not stop:
+            middle.append(n)
+            n = n.parent
+        if n is not stop:
+            return np.empty(0, np.int32), stop            # the tree changed under the match: keep the device part
+        slots, new_last = super().init_load_back(last_host_node, host_hit_length)
+        if not len(slots):
+            return slots, stop
+        middle.reverse()
+        return np.concatenate([m.value for m in middle] + [slots]).astype(np.int32), new_last
