@@ -16,11 +16,15 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(os.path.dirname(HERE), "ops")
-LIB_PATH = os.path.join(OUT_DIR, "libsglb200.so")
+# `SGLB_BOUNDS_CHECK=1` selects the checked build: kernels compiled with -DSGLB_BOUNDS_CHECK verify the indices they
+# write through against the extents given to `sglb_debug_set_kv_pages`, report a violation through the status word
+# and skip the access.  It is a library of its own so the regular one stays as it is.
+CHECKED = os.environ.get("SGLB_BOUNDS_CHECK", "0") == "1"
+LIB_PATH = os.path.join(OUT_DIR, "libsglb200_checked.so" if CHECKED else "libsglb200.so")
 STAMP = LIB_PATH + ".stamp"
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math", "-Xcompiler", "-fPIC", "-shared"]
+              "--use_fast_math", "-Xcompiler", "-fPIC", "-shared"] + (["-DSGLB_BOUNDS_CHECK"] if CHECKED else [])
 
 
 def _nvcc() -> str:
@@ -55,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and is_current():
         return LIB_PATH
     objs = []
-    tmp = os.path.join(HERE, "build")
+    tmp = os.path.join(HERE, "build_checked" if CHECKED else "build")
     os.makedirs(tmp, exist_ok=True)
     procs = []
     for src in sources():

@@ -25,6 +25,7 @@ enum StatusCode : int {
   kTimeoutTmemEmpty = 4,      // MMA warp waited for the epilogue to drain TMEM
   kTimeoutPeerFlag = 5,       // wait on a flag another GPU sets
   kBadArgument = 6,
+  kOutOfBounds = 7,           // checked build (-DSGLB_BOUNDS_CHECK): an index left its buffer; the access was skipped
 };
 
 struct Status {

@@ -219,6 +219,12 @@ __global__ void argmax_kernel(int* __restrict__ out, const T* __restrict__ logit
 //   v heads: -> cache[page, 1, h, off, :]
 // Lane l holds elements l, l+32, l+64, ... of the head, so the neox partner i + rd/2 of an element
 // lives in the same lane (rd/2 is a multiple of 32).
+#ifdef SGLB_BOUNDS_CHECK
+// Checked build only: the extent of the KV buffers and where to report, set by sglb_debug_set_kv_pages().
+__device__ int g_dbg_kv_pages = 0;
+__device__ Status* g_dbg_status = nullptr;
+#endif
+
 template <int D>
 __global__ void rope_qknorm_kvwrite_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv,
                                            const int* __restrict__ positions, const float* __restrict__ cos_sin,
@@ -292,6 +298,12 @@ __global__ void rope_qknorm_kvwrite_kernel(__nv_bfloat16* __restrict__ q_out, co
     if (kv == nullptr) return;
     const int slot = loc[t];
     const int page = slot / page_size, off = slot - page * page_size;
+#ifdef SGLB_BOUNDS_CHECK
+    if (g_dbg_kv_pages > 0 && (slot < 0 || page >= g_dbg_kv_pages)) {
+      if (lane == 0) report(g_dbg_status, kOutOfBounds, static_cast<int>(t), slot);
+      return;
+    }
+#endif
     const int kvsel = is_k ? 0 : 1;
     const int hh = is_k ? h - Hq : h - Hq - Hkv;
     dst = kv + ((((static_cast<long long>(page) * 2 + kvsel) * Hkv + hh) * page_size) + off) * D;
@@ -396,6 +408,21 @@ int sglb_argmax(int* out, const void* logits, int B, int V, long long row_stride
   if (dtype_bytes == 4) launch_pdl(argmax_kernel<float>, dim3(B), dim3(1024), 0, s, out, static_cast<const float*>(logits), V, row_stride);
   else launch_pdl(argmax_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, s, out, static_cast<const __nv_bfloat16*>(logits), V, row_stride);
   return static_cast<int>(cudaGetLastError());
+}
+
+// Checked build (-DSGLB_BOUNDS_CHECK): tell the KV-write kernel how many pages the KV buffers have; a slot outside
+// them is then reported through the status word (code kOutOfBounds, aux = token row, slot) and its store skipped.
+// Returns 1 when the library was built with the checks, 0 otherwise (the call is then a no-op).
+int sglb_debug_set_kv_pages(int pages) {
+#ifdef SGLB_BOUNDS_CHECK
+  sglb::Status* st = sglb::device_status();
+  if (cudaMemcpyToSymbol(sglb::g_dbg_kv_pages, &pages, sizeof(int)) != cudaSuccess) return -sglb::kBadArgument;
+  if (cudaMemcpyToSymbol(sglb::g_dbg_status, &st, sizeof(st)) != cudaSuccess) return -sglb::kBadArgument;
+  return 1;
+#else
+  (void)pages;
+  return 0;
+#endif
 }
 
 int sglb_rope_qknorm_kvwrite(void* q_out, const void* qkv, const int* positions, const float* cos_sin, const void* q_w,

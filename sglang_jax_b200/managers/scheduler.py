@@ -867,6 +867,9 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
             return
         if not self.running_batch.is_empty() or self.waiting_queue and any(r.req_pool_idx is not None for r in self.waiting_queue):
             return
+        pool = getattr(getattr(self.tp_worker, "model_runner", None), "token_to_kv_pool", None)
+        if getattr(pool, "check_canaries", None) is not None:
+            pool.check_canaries()          # guard pages behind the KV buffers (SGLB_KV_CANARY_PAGES), untouched?
         if hasattr(self.tree_cache, "swa_evictable_size"):
             # hybrid sliding-window pools: the invariant holds for each pool separately
             al, tc = self.token_to_kv_pool_allocator, self.tree_cache

@@ -17,6 +17,8 @@ Roles match the reference's `python/sgl_jax/srt/mem_cache/memory_pool.py`
 
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -152,16 +154,41 @@ class KVCache:
             self.set_kv_buffer(layer + self.start_layer, tgt_loc, a, b)
 
 
+CANARY_BYTE = 0x5A
+
+
 class MHATokenToKVPool(KVCache):
+    """`SGLB_KV_CANARY_PAGES=n` (a debugging aid, the stand-in for a memory checker on the pools): every layer's
+    buffer is followed, in the same allocation, by `n` guard pages filled with a byte pattern.  A kernel that writes
+    through a page id just past the pool lands there instead of in a neighbouring tensor, and `check_canaries()`
+    (run by the scheduler's idle-time memory check) names the layer and page that were hit."""
+
     def __init__(self, size, page_size, dtype, head_num, head_dim, layer_num, device,
-                 start_layer: int = 0):
+                 start_layer: int = 0, canary_pages: int | None = None):
         super().__init__(size, page_size, dtype, layer_num, device, start_layer)
         self.head_num = head_num
         self.head_dim = head_dim
-        self.kv_buffer = [
-            torch.zeros((self.num_pages, 2, head_num, page_size, head_dim), dtype=dtype, device=device)
-            for _ in range(layer_num)
-        ]
+        if canary_pages is None:
+            canary_pages = int(os.environ.get("SGLB_KV_CANARY_PAGES", "0"))
+        self.canary_pages = max(int(canary_pages), 0)
+        self.kv_buffer, self._canaries = [], []
+        for _ in range(layer_num):
+            whole = torch.zeros((self.num_pages + self.canary_pages, 2, head_num, page_size, head_dim), dtype=dtype,
+                                device=device)
+            self.kv_buffer.append(whole[: self.num_pages] if self.canary_pages else whole)
+            if self.canary_pages:
+                guard = whole[self.num_pages:].view(torch.uint8)
+                guard.fill_(CANARY_BYTE)
+                self._canaries.append(guard)
+
+    def check_canaries(self) -> None:
+        """Raise if any guard page has been written (synchronises the device)."""
+        for layer, guard in enumerate(self._canaries):
+            bad = guard != CANARY_BYTE
+            if bool(bad.any()):
+                page = int(bad.view(self.canary_pages, -1).any(dim=1).nonzero()[0])
+                raise RuntimeError(f"KV pool overrun: guard page {self.num_pages + page} of layer "
+                                   f"{layer + self.start_layer} was written ({int(bad.sum())} bytes differ)")
 
     @staticmethod
     def cell_size(head_num, head_dim, layer_num, dtype) -> int:
@@ -231,6 +258,10 @@ class SWAKVPool(KVCache):
 
     def get_kv_size_bytes(self):
         return self.full_pool.get_kv_size_bytes() + self.swa_pool.get_kv_size_bytes()
+
+    def check_canaries(self) -> None:
+        self.full_pool.check_canaries()
+        self.swa_pool.check_canaries()
 
     def is_swa_layer(self, layer_id):
         return self.layers_mapping[layer_id][1]

@@ -221,6 +221,13 @@ class ModelRunner:
                                                      heads, dim, n_layers, str(self.device))
         logger.info("KV pool: %d tokens, %.2f GB, max_running_requests=%d", self.max_total_num_tokens,
                     self.token_to_kv_pool.get_kv_size_bytes() / 2 ** 30, max_reqs)
+        if self.device.type == "cuda" and os.environ.get("SGLB_BOUNDS_CHECK", "0") == "1":
+            # checked build of the kernel library: the KV-write kernel verifies its slots against the pool's extent
+            from ..ops import native
+            pages = max(p.num_pages for p in (getattr(self.token_to_kv_pool, "full_pool", self.token_to_kv_pool),
+                                              getattr(self.token_to_kv_pool, "swa_pool", self.token_to_kv_pool)))
+            if native.set_debug_kv_pages(pages):
+                logger.info("checked kernel build: KV writes are verified against %d pages", pages)
 
     def _init_fused_comm(self):
         st = ps.get_state()

@@ -16,7 +16,10 @@ from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
 import torch
 
 _LIB = None
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsglb200.so")
+# SGLB_BOUNDS_CHECK=1: the checked build of the library (see csrc/build.py)
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                         "libsglb200_checked.so" if os.environ.get("SGLB_BOUNDS_CHECK", "0") == "1"
+                         else "libsglb200.so")
 LOADED = False
 
 
@@ -38,6 +41,8 @@ def lib():
     L.sglb_gemm_decode_cluster.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     L.sglb_gemm_decode_cluster_size.argtypes = [c_int, c_int, c_int]
     L.sglb_enable_peer_access.argtypes = [c_int, c_int]
+    if hasattr(L, "sglb_debug_set_kv_pages"):
+        L.sglb_debug_set_kv_pages.argtypes = [c_int]
     L.sglb_gemm_workspace_bytes.restype = c_size_t
     L.sglb_gemm_workspace_bytes.argtypes = [c_int, c_int, c_int]
     L.sglb_gemm_max_counters.argtypes = [c_int]
@@ -121,7 +126,8 @@ def check_status():
     if code != 0:
         names = {1: "timeout waiting for TMA data", 2: "timeout waiting for a free stage",
                  3: "timeout waiting for the accumulator", 4: "timeout waiting for TMEM to drain",
-                 5: "timeout waiting for a peer flag", 6: "bad argument"}
+                 5: "timeout waiting for a peer flag", 6: "bad argument",
+                 7: "index out of bounds (checked build; the access was skipped)"}
         raise RuntimeError(f"kernel status {code} ({names.get(code, '?')}), block={buf[1]} aux=({buf[2]}, {buf[3]})")
 
 
@@ -565,6 +571,18 @@ def kv_page_copy(dst: torch.Tensor, src: torch.Tensor, dst_pages: torch.Tensor, 
     _check(lib().sglb_kv_page_copy(dst.data_ptr(), src.data_ptr(), _p(dst_pages), _p(src_pages), n,
                                    dst.shape[1] * es, dst.stride(0) * es, src.stride(0) * es, _stream()),
            "kv_page_copy")
+
+
+def set_debug_kv_pages(pages: int) -> bool:
+    """Checked build (`SGLB_BOUNDS_CHECK=1`): give the KV-write kernel the extent of the KV buffers; a slot outside
+    them is then reported by `check_status()` and its store skipped.  False when the loaded library has no checks."""
+    L = lib()
+    if not hasattr(L, "sglb_debug_set_kv_pages"):
+        return False
+    rc = L.sglb_debug_set_kv_pages(int(pages))
+    if rc < 0:
+        raise RuntimeError(f"sglb_debug_set_kv_pages failed with code {rc}")
+    return rc == 1
 
 
 def enable_peer_access(device: torch.device, peer: torch.device) -> None:

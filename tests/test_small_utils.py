@@ -355,3 +355,45 @@ def test_residual_dataflow_token_window():
         assert ModelRunner.select_residual_dataflow(r, SimpleNamespace(num_tokens=300, extras={"deepstack": 1})) is False
     finally:
         fused_block.set_fused_residual(True)
+
+
+def test_kv_pool_canary_pages_catch_a_write_past_the_pool(monkeypatch):
+    """Guard pages behind every layer's KV buffer (the stand-in for a memory checker on the pools)."""
+    import pytest
+    import torch
+    from sglang_jax_b200.mem_cache.memory_pool import MHATokenToKVPool
+    pool = MHATokenToKVPool(32, 4, torch.float32, 2, 8, 2, "cpu", canary_pages=2)
+    assert pool.kv_buffer[0].shape[0] == pool.num_pages and pool.kv_buffer[0].is_contiguous()
+    loc = torch.arange(4, 36)
+    pool.set_kv_buffer(0, loc, torch.randn(32, 2, 8), torch.randn(32, 2, 8))       # every legal slot
+    pool.check_canaries()
+    # a page id one past the pool (what a kernel with a bad page-table entry would write through)
+    whole = pool.kv_buffer[1]._base
+    whole[pool.num_pages, 0, 0, 0, 0] = 1.0
+    with pytest.raises(RuntimeError, match=f"guard page {pool.num_pages} of layer 1"):
+        pool.check_canaries()
+    # the environment switch is the default source of the page count; without it nothing is added
+    monkeypatch.setenv("SGLB_KV_CANARY_PAGES", "1")
+    assert MHATokenToKVPool(8, 4, torch.float32, 1, 8, 1, "cpu").canary_pages == 1
+    monkeypatch.delenv("SGLB_KV_CANARY_PAGES")
+    plain = MHATokenToKVPool(8, 4, torch.float32, 1, 8, 1, "cpu")
+    assert plain.canary_pages == 0 and plain.kv_buffer[0]._base is None
+    plain.check_canaries()
+
+
+def test_checked_kernel_build_compiles(tmp_path):
+    """The -DSGLB_BOUNDS_CHECK variant of the KV-write kernel keeps compiling for sm_100a (it cannot run here)."""
+    import os
+    import shutil
+    import subprocess
+    from sglang_jax_b200.csrc import build as b
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    src = os.path.join(b.HERE, "elementwise.cu")
+    flags = [f for f in b.NVCC_FLAGS if f not in ("-shared", "-DSGLB_BOUNDS_CHECK")]
+    r = subprocess.run([nvcc, *flags, "-DSGLB_BOUNDS_CHECK", "-I", b.HERE, "-c", src, "-o", str(tmp_path / "e.o")],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert r.returncode == 0, r.stdout
+    syms = subprocess.run(["nm", "-C", str(tmp_path / "e.o")], stdout=subprocess.PIPE, text=True).stdout
+    assert "sglb_debug_set_kv_pages" in syms
