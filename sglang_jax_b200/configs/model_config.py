@@ -63,6 +63,8 @@ _NEXTN_ARCH = {
     "MiMoForCausalLM": "MiMoMTP",
     "DeepseekV3ForCausalLM": "DeepseekV3ForCausalLMNextN",
     "MiMoV2FlashForCausalLM": "MiMoV2NextN",
+    "MiMoV2ProForCausalLM": "MiMoV2NextN",
+    "MiMoV2ForCausalLM": "MiMoV2NextN",
     "Glm4MoeForCausalLM": "Glm4MoeForCausalLMNextN",
 }
 

@@ -113,7 +113,13 @@ class DefaultModelLoader:
         with torch.device(device), _expert_storage_for(quant_config):
             model = cls(model_config.hf_config, dtype=model_config.dtype, quant_config=quant_config) \
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
-        it = dequant_static_fp8(self._iterator(model_config.model_path), getattr(quant_config, "weight_block_size", None))
+        it = self._iterator(model_config.model_path)
+        pre = getattr(model, "preprocess_checkpoint", None)
+        if pre is not None:
+            # checkpoint tensors whose layout the generic passes below would misread (e.g. a fused projection that was
+            # quantised shard by shard) are rewritten by the model first
+            it = pre(it)
+        it = dequant_static_fp8(it, getattr(quant_config, "weight_block_size", None))
         loaded = model.load_weights(it)
         check_all_loaded(model, loaded)
         _apply_dynamic_quantization(model, quant_config)

@@ -119,4 +119,9 @@ class BailingMoeLinearForCausalLM(LlamaForCausalLM):
         return loaded
 
 
-EntryClass = [BailingMoeLinearForCausalLM]
+class BailingMoeV2_5ForCausalLM(BailingMoeLinearForCausalLM):
+    """The architecture string Ling-2.5 / Ring-2.5 linear-attention checkpoints carry (reference
+    `models/bailing_moe_linear.py` `EntryClass`)."""
+
+
+EntryClass = [BailingMoeLinearForCausalLM, BailingMoeV2_5ForCausalLM]

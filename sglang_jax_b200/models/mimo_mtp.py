@@ -119,4 +119,8 @@ class MiMoMTP(nn.Module):
         return loaded | {"model.embed_tokens.weight", "lm_head.weight"}
 
 
-EntryClass = [MiMoMTP]
+class MiMoMTPForCausalLM(MiMoMTP):
+    """Name under which the reference registers the MiMo MTP draft model (`models/mimo_mtp.py` `EntryClass`)."""
+
+
+EntryClass = [MiMoMTP, MiMoMTPForCausalLM]

@@ -137,8 +137,85 @@ class MiMoV2FlashForCausalLM(LlamaForCausalLM):
         return loaded
 
 
+def infer_qkv_shards(rows: int, scale_rows: int, nh: int, nkv: int, hd: int, vd: int, block: int) -> tuple[int, int]:
+    """`(shards, kv_heads)` of a fused QKV tensor that was block-quantised shard by shard: the shard count (largest
+    first, a smaller one can satisfy the sizes too but splits Q / K / V in the wrong places) and the number of KV
+    heads the checkpoint really holds (the config may list a replicated count) for which `shards` blocks of
+    `ceil(per_shard / block)` scale rows and `per_shard` weight rows add up to what the checkpoint has."""
+    for kv in sorted((d for d in range(1, nkv + 1) if nkv % d == 0), reverse=True):
+        for tp in sorted((d for d in range(1, nh + 1) if nh % d == 0), reverse=True):
+            if kv % tp:
+                continue
+            per = (nh // tp) * hd + (kv // tp) * (hd + vd)
+            if per * tp == rows and -(-per // block) * tp == scale_rows:
+                return tp, kv
+    raise ValueError(f"cannot infer how the fused QKV was sharded: rows={rows} scale_rows={scale_rows} heads={nh} "
+                     f"kv_heads={nkv} head_dim={hd} v_head_dim={vd} block={block}")
+
+
 class MiMoV2ProForCausalLM(MiMoV2FlashForCausalLM):
-    pass
+    """MiMo-V2-Pro (reference `python/sgl_jax/srt/models/mimo_v2_pro.py`): the Flash architecture with the attention
+    input projection stored fused as `self_attn.qkv_proj`.  In bf16 checkpoints its rows are `[Q | K | V]`.  In the
+    block-FP8 release the tensor was quantised per tensor-parallel shard and the shards concatenated
+    (`[Q0 K0 V0 | Q1 K1 V1 | ...]`, each shard with its own `ceil(rows / 128)` scale rows, so a scale block can
+    straddle a K / V border inside a shard but never a shard border): every shard is de-quantised on its own grid
+    and its Q / K / V rows are regrouped; the attention projections then hold bf16 weights like in the reference
+    (`utils/weight_utils.py` `dequant_fused_qkv`)."""
+
+    def preprocess_checkpoint(self, weights):
+        cfg = self.config
+        qc = getattr(cfg, "quantization_config", None) or {}
+        wbs = qc.get("weight_block_size") if isinstance(qc, dict) else getattr(qc, "weight_block_size", None)
+        block = int(wbs[0]) if wbs else 128
+        fp8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+        pending: dict[str, dict[str, torch.Tensor]] = {}
+
+        def dims(prefix: str):
+            i = int(prefix.split("layers.")[1].split(".")[0])
+            if _is_swa(cfg, i):
+                return (cfg.swa_num_attention_heads, cfg.swa_num_key_value_heads, cfg.swa_head_dim,
+                        getattr(cfg, "swa_v_head_dim", None) or cfg.swa_head_dim)
+            return (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                    getattr(cfg, "v_head_dim", None) or cfg.head_dim)
+
+        def emit(prefix, q, k, v):
+            yield prefix + "q_proj.weight", q
+            yield prefix + "k_proj.weight", k
+            yield prefix + "v_proj.weight", v
+
+        for name, w in weights:
+            if ".self_attn.qkv_proj." not in name:
+                yield name, w
+                continue
+            prefix, leaf = name.split("qkv_proj.")
+            nh, nkv, hd, vd = dims(prefix)
+            if leaf == "weight" and w.dtype not in fp8:
+                kv = (w.shape[0] - nh * hd) // (hd + vd)                   # KV heads the checkpoint really holds
+                q, k, v = torch.split(w, [nh * hd, kv * hd, kv * vd], 0)
+                yield from emit(prefix, q, k, v)
+                continue
+            got = pending.setdefault(prefix, {})
+            got["scale" if leaf.startswith("weight_scale") else "weight"] = w
+            if len(got) < 2:
+                continue
+            pending.pop(prefix)
+            wq, sc = got["weight"], got["scale"].float()
+            tp, kv = infer_qkv_shards(wq.shape[0], sc.shape[0], nh, nkv, hd, vd, block)
+            pq, pk, pv = (nh // tp) * hd, (kv // tp) * hd, (kv // tp) * vd
+            per, nb = pq + pk + pv, -(-(pq + pk + pv) // block)
+            parts = ([], [], [])
+            for s in range(tp):
+                rows = wq[s * per:(s + 1) * per].float()
+                rs = sc[s * nb:(s + 1) * nb].repeat_interleave(block, 0)[:per].repeat_interleave(block, 1)
+                for dst, piece in zip(parts, torch.split(rows * rs[:, : rows.shape[1]], [pq, pk, pv], 0)):
+                    dst.append(piece)
+            yield from emit(prefix, *(torch.cat(p, 0).to(self.dtype) for p in parts))
+        if pending:
+            raise RuntimeError(f"fused QKV without its scale (or the reverse): {sorted(pending)[:3]}")
 
 
-EntryClass = [MiMoV2FlashForCausalLM, MiMoV2ProForCausalLM]
+class MiMoV2ForCausalLM(MiMoV2ProForCausalLM):
+    """The architecture string MiMo-V2-Pro checkpoints carry."""
+
+
+EntryClass = [MiMoV2FlashForCausalLM, MiMoV2ProForCausalLM, MiMoV2ForCausalLM]

@@ -115,4 +115,8 @@ class MiMoV2NextN(nn.Module):
         return loaded | {"model.embed_tokens.weight", "lm_head.weight"}
 
 
-EntryClass = [MiMoV2NextN]
+class MiMoV2MTPForCausalLM(MiMoV2NextN):
+    """Name under which the reference registers the MiMo-V2 MTP draft model (`models/mimo_v2_nextn.py`)."""
+
+
+EntryClass = [MiMoV2NextN, MiMoV2MTPForCausalLM]

@@ -142,12 +142,58 @@ class Qwen3NextForCausalLM(LlamaForCausalLM):
             skip=("mtp.", "visual."), stacked=[(".gate_up_proj", ".gate_proj", 0), (".gate_up_proj", ".up_proj", 1)])
 
 
+def fuse_split_gdn_projections(weights, config):
+    """Qwen3.5 checkpoints store the Gated DeltaNet input projection as four tensors (`in_proj_qkv` with all query
+    heads, then all key heads, then all value heads; `in_proj_z`; `in_proj_b`; `in_proj_a`), Qwen3-Next as two
+    tensors grouped per key head (`in_proj_qkvz`: q, k, the group's values, the group's gates; `in_proj_ba`).  The
+    layer keeps the grouped layout (one GEMM each); this regroups the rows of a Qwen3.5 checkpoint while it streams
+    by (reference `models/qwen3_5.py` `_create_qwen3_5_weight_mappings`, the fused targets of the four HF keys)."""
+    nk, nv = config.linear_num_key_heads, config.linear_num_value_heads
+    dk, dv = config.linear_key_head_dim, config.linear_value_head_dim
+    r, key_dim = nv // nk, nk * dk
+    parts = ("in_proj_qkv", "in_proj_z", "in_proj_b", "in_proj_a")
+    pending: dict[str, dict[str, torch.Tensor]] = {}
+    for name, w in weights:
+        hit = next((p for p in parts if name.endswith(f".linear_attn.{p}.weight")), None)
+        if hit is None:
+            yield name, w
+            continue
+        prefix = name[: -len(f"{hit}.weight")]
+        got = pending.setdefault(prefix, {})
+        got[hit] = w
+        if len(got) < 4:
+            continue
+        pending.pop(prefix)
+        qkv, z, b, a = (got[p] for p in parts)
+        H = qkv.shape[1]
+        q = qkv[:key_dim].reshape(nk, dk, H)
+        k = qkv[key_dim:2 * key_dim].reshape(nk, dk, H)
+        v = qkv[2 * key_dim:].reshape(nk, r * dv, H)
+        yield prefix + "in_proj_qkvz.weight", torch.cat([q, k, v, z.reshape(nk, r * dv, H)], 1).reshape(-1, H)
+        yield prefix + "in_proj_ba.weight", torch.cat([b.reshape(nk, r, H), a.reshape(nk, r, H)], 1).reshape(-1, H)
+    if pending:
+        raise RuntimeError(f"incomplete Gated DeltaNet projections in the checkpoint: {sorted(pending)[:3]}")
+
+
 class Qwen3_5ForCausalLM(Qwen3NextForCausalLM):
+    """Qwen3.5 text model (dense); also the text part of `Qwen3_5ForConditionalGeneration` checkpoints, whose vision
+    tower and multi-token-prediction head are skipped like in the reference."""
+
+    def load_weights(self, weights):
+        return super().load_weights(fuse_split_gdn_projections(weights, self.config))
+
+
+class Qwen3_5MoeForCausalLM(Qwen3_5ForCausalLM):
     pass
 
 
-class Qwen3_5MoeForCausalLM(Qwen3NextForCausalLM):
+class Qwen3_5ForConditionalGeneration(Qwen3_5ForCausalLM):
     pass
 
 
-EntryClass = [Qwen3NextForCausalLM, Qwen3_5ForCausalLM, Qwen3_5MoeForCausalLM]
+class Qwen3_5MoeForConditionalGeneration(Qwen3_5ForCausalLM):
+    pass
+
+
+EntryClass = [Qwen3NextForCausalLM, Qwen3_5ForCausalLM, Qwen3_5MoeForCausalLM, Qwen3_5ForConditionalGeneration,
+              Qwen3_5MoeForConditionalGeneration]

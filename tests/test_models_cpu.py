@@ -373,6 +373,52 @@ def test_qwen3_next_hybrid_gated_deltanet_matches_hf(tmp_path, moe):
     assert _generate(path, prompts, n=8, chunked_prefill_size=32) == want
 
 
+@pytest.mark.parametrize("moe,wrapped", [(False, False), (True, False), (False, True)])
+def test_qwen3_5_matches_hf(tmp_path, moe, wrapped):
+    """Qwen3.5 (dense and MoE): the Gated DeltaNet input projection arrives as four tensors and is regrouped at load.
+    `wrapped`: the layout of a `Qwen3_5ForConditionalGeneration` checkpoint (text model under
+    `model.language_model.`, nested `text_config`, vision tower and MTP head present and skipped)."""
+    import transformers
+    cfg = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, vocab_size=512, tie_word_embeddings=False,
+               max_position_embeddings=512, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+               linear_value_head_dim=16, linear_conv_kernel_dim=4,
+               layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+               rope_parameters={"rope_theta": 10000.0, "rope_type": "default", "partial_rotary_factor": 0.25,
+                                "mrope_section": [2, 1, 1], "mrope_interleaved": True})
+    if moe:
+        cfg.update(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64)
+        hf = _init(transformers.Qwen3_5MoeForCausalLM(transformers.Qwen3_5MoeTextConfig(**cfg)))
+    else:
+        hf = _init(transformers.Qwen3_5ForCausalLM(transformers.Qwen3_5TextConfig(**cfg)))
+    for n, p in hf.named_parameters():
+        if n.endswith("A_log"):
+            p.data.uniform_(-1.0, 1.0)
+        elif n.endswith("dt_bias"):
+            p.data.uniform_(0.5, 1.5)
+        elif "norm" in n:
+            p.data.normal_(0, 0.1)
+    text = dict(cfg, rope_theta=10000.0, partial_rotary_factor=0.25)
+    if wrapped:
+        def rename(sd):
+            out = {k.replace("model.", "model.language_model.", 1) if k.startswith("model.") else k: v
+                   for k, v in sd.items()}
+            out["model.visual.patch_embed.proj.bias"] = torch.zeros(8)
+            out["mtp.fc.weight"] = torch.zeros(4, 4)
+            return out
+        path = _save(str(tmp_path / "q35"), hf, dict(text_config=dict(text, model_type="qwen3_5_text"),
+                                                     vision_config={"depth": 1}, tie_word_embeddings=False),
+                     "Qwen3_5ForConditionalGeneration", "qwen3_5", rename=rename)
+    else:
+        path = _save(str(tmp_path / "q35"), hf, text, "Qwen3_5MoeForCausalLM" if moe else "Qwen3_5ForCausalLM",
+                     "qwen3_5_moe_text" if moe else "qwen3_5_text")
+    prompts = [list(range(5, 90)), [9, 8, 7, 6, 5, 4, 3] * 5, [100, 200, 300]]
+    want = _hf_generate(hf, prompts, n=8)
+    assert _generate(path, prompts, n=8) == want
+    if not wrapped:
+        assert _generate(path, prompts, n=8, chunked_prefill_size=32) == want
+
+
 @pytest.mark.parametrize("kind", ["umt5", "t5"])
 def test_t5_family_encoder_matches_hf(tmp_path, kind):
     import transformers
@@ -393,6 +439,51 @@ def test_t5_family_encoder_matches_hf(tmp_path, kind):
         want = hf(input_ids=ids, attention_mask=mask).last_hidden_state
     got = model.encode(ids, mask)
     assert torch.allclose(got[0], want[0], atol=2e-5) and torch.allclose(got[1, :17], want[1, :17], atol=2e-5)
+
+
+@pytest.mark.parametrize("tied", [False, True])
+def test_umt5_conditional_generation_matches_hf(tied):
+    """Encoder-decoder UMT5: teacher-forced logits, the bare decoder / encoder-decoder classes and greedy generation
+    with cached keys / values against HF `UMT5ForConditionalGeneration`."""
+    import transformers
+    from sglang_jax_b200.models.umt5 import UMT5DecoderModel, UMT5ForConditionalGeneration, UMT5Model
+    cfg = transformers.UMT5Config(vocab_size=300, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_decoder_layers=3,
+                                  num_heads=4, relative_attention_num_buckets=32, relative_attention_max_distance=128,
+                                  feed_forward_proj="gated-gelu", dropout_rate=0.0, tie_word_embeddings=tied,
+                                  decoder_start_token_id=0, pad_token_id=0, eos_token_id=1)
+    hf = _init(transformers.UMT5ForConditionalGeneration(cfg), 0.1)
+    if tied:
+        hf.tie_weights()
+    model = UMT5ForConditionalGeneration(cfg, dtype=torch.float32)
+    loaded = model.load_weights(hf.state_dict().items())
+    assert loaded == {n for n, _ in model.named_parameters()}
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(2, 300, (2, 19), generator=g)
+    mask = torch.ones(2, 19, dtype=torch.long)
+    mask[1, 13:] = 0
+    dec = torch.randint(2, 300, (2, 9), generator=g)
+    dec[:, 0] = 0
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=mask, decoder_input_ids=dec, output_hidden_states=True,
+                 use_cache=False)
+    got = model(ids, dec, mask)
+    assert torch.allclose(got, ref.logits, atol=1e-4), (got - ref.logits).abs().max()
+    # the head-less classes load the same checkpoint and give the decoder's last hidden state
+    plain = UMT5Model(cfg, dtype=torch.float32)
+    plain.load_weights(hf.state_dict().items())
+    hid = plain(ids, dec, mask)
+    assert torch.allclose(hid, ref.decoder_hidden_states[-1], atol=1e-4)
+    only = UMT5DecoderModel(cfg, dtype=torch.float32)
+    assert only.load_weights(hf.state_dict().items()) == {n for n, _ in only.named_parameters()}
+    assert torch.allclose(only(dec, ref.encoder_last_hidden_state, mask), hid, atol=1e-4)
+    # greedy generation with the incremental cache == HF generate
+    with torch.no_grad():
+        want = hf.generate(input_ids=ids, attention_mask=mask, max_new_tokens=8, do_sample=False, num_beams=1,
+                           use_cache=False)
+    mine = model.generate(ids, max_new_tokens=8, attention_mask=mask)
+    want = want[:, 1:]                                   # HF returns the start token first
+    n = min(want.shape[1], mine.shape[1])
+    assert n >= 1 and torch.equal(mine[:, :n], want[:, :n])
 
 
 def _run_dummy(cfg: dict, tmp_path, name: str, prompts, n=6, **kw):
@@ -538,6 +629,74 @@ def test_mimo_v2_flash_hybrid_swa_sinks_and_narrow_values(tmp_path):
     assert m.model.layers[1].self_attn.attention_sink_bias is not None
     assert m.model.layers[0].self_attn.attention_sink_bias is None
     assert m.model.layers[0].self_attn.o_proj.weight.shape[1] == 4 * 8
+
+
+def test_mimo_v2_pro_fused_qkv_checkpoints_bf16_and_per_shard_fp8():
+    """MiMo-V2-Pro stores the attention input projection fused.  bf16: rows are [Q | K | V].  Block-FP8: quantised per
+    tensor shard and concatenated, so every shard is de-quantised on its own block grid (a scale block straddles the
+    K / V border inside a shard) before Q / K / V are regrouped.  Both must fill the fused parameter exactly like the
+    Flash layout with separate projections does."""
+    from types import SimpleNamespace
+    from sglang_jax_b200.models.mimo_v2_flash import (MiMoV2FlashForCausalLM, MiMoV2ForCausalLM, infer_qkv_shards)
+    from sglang_jax_b200.model_loader.loader import dequant_static_fp8
+    from sglang_jax_b200.models.registry import get_model_class
+    cfg = dict(hidden_size=256, intermediate_size=96, moe_intermediate_size=32, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=64, v_head_dim=32, swa_num_attention_heads=4,
+               swa_num_key_value_heads=2, swa_head_dim=64, swa_v_head_dim=32, rope_theta=1e6, sliding_window_size=24,
+               hybrid_layer_pattern=[0, 1], moe_layer_freq=[0, 0], add_swa_attention_sink_bias=False,
+               add_full_attention_sink_bias=False, partial_rotary_factor=0.5, n_routed_experts=0,
+               num_experts_per_tok=2, layernorm_epsilon=1e-5, vocab_size=64, max_position_embeddings=128,
+               tie_word_embeddings=False, quantization_config={"weight_block_size": [128, 128]})
+    assert get_model_class(["MiMoV2ForCausalLM"]) is MiMoV2ForCausalLM
+    g = torch.Generator().manual_seed(0)
+    nh, nkv, hd, vd, H = 4, 2, 64, 32, 256
+    qkv = {i: [torch.randn(n, H, generator=g) * 0.05 for n in (nh * hd, nkv * hd, nkv * vd)] for i in range(2)}
+
+    def flash_names(tensors):
+        for i, (q, k, v) in tensors.items():
+            for n, w in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
+                yield f"model.layers.{i}.self_attn.{n}.weight", w
+
+    def fused_param(model, i):
+        return model.model.layers[i].self_attn.qkv_proj.weight.clone()
+
+    want = MiMoV2FlashForCausalLM(SimpleNamespace(**cfg), dtype=torch.float32)
+    want.load_weights(flash_names(qkv))
+    # bf16 layout
+    pro = MiMoV2ForCausalLM(SimpleNamespace(**cfg), dtype=torch.float32)
+    pro.load_weights(pro.preprocess_checkpoint(
+        (f"model.layers.{i}.self_attn.qkv_proj.weight", torch.cat(t, 0)) for i, t in qkv.items()))
+    for i in range(2):
+        assert torch.equal(fused_param(pro, i), fused_param(want, i))
+    # block-FP8, two shards of 128 + 64 + 32 = 224 rows: the second scale block of a shard covers K and V rows
+    tp, blk = 2, 128
+    assert infer_qkv_shards(448, 4, nh, nkv, hd, vd, blk) == (2, 2)
+    assert infer_qkv_shards(448, 4, nh, 4, hd, vd, blk) == (2, 2)          # config lists replicated KV heads
+    names, deq = [], {}
+    for i, (q, k, v) in qkv.items():
+        ws, ss, dq = [], [], ([], [], [])
+        for s in range(tp):
+            shard = torch.cat([q.chunk(tp)[s], k.chunk(tp)[s], v.chunk(tp)[s]], 0)          # [224, 256]
+            pad = torch.zeros(256, H)
+            pad[:224] = shard
+            blocks = pad.view(2, blk, 2, blk)
+            scale = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-8) / 448.0                    # [2, 2]
+            wq = (blocks / scale[:, None, :, None]).to(torch.float8_e4m3fn)
+            back = (wq.float() * scale[:, None, :, None]).view(256, H)[:224]
+            ws.append(wq.view(256, H)[:224])
+            ss.append(scale)
+            for dst, piece in zip(dq, torch.split(back, [128, 64, 32], 0)):
+                dst.append(piece)
+        names.append((f"model.layers.{i}.self_attn.qkv_proj.weight_scale_inv", torch.cat(ss, 0)))
+        names.append((f"model.layers.{i}.self_attn.qkv_proj.weight", torch.cat(ws, 0)))
+        deq[i] = [torch.cat(p, 0) for p in dq]
+    want8 = MiMoV2FlashForCausalLM(SimpleNamespace(**cfg), dtype=torch.float32)
+    want8.load_weights(flash_names(deq))
+    pro8 = MiMoV2ForCausalLM(SimpleNamespace(**cfg), dtype=torch.float32)
+    pro8.load_weights(dequant_static_fp8(pro8.preprocess_checkpoint(iter(names)), (128, 128)))
+    for i in range(2):
+        assert torch.equal(fused_param(pro8, i), fused_param(want8, i))
+        assert not torch.equal(fused_param(pro8, i), fused_param(want, i))                   # it really was quantised
 
 
 @pytest.mark.parametrize("moe", [False, True])
@@ -689,3 +848,18 @@ def test_hybrid_recurrent_prefix_sharing_reuses_state_checkpoints(tmp_path):
     hosted = run(hicache_storage="host", disable_overlap_schedule=True)
     assert hosted[0] == "UnifiedHiRadixCache"
     assert hosted[1:4] == plain[1:4] and hosted[4] == shared[4] and hosted[5] == shared[5]
+
+
+def test_every_reference_architecture_name_resolves():
+    """The `architectures[0]` strings the reference registers (`EntryClass` of each file under its `models/`)."""
+    from sglang_jax_b200.models.registry import supported_architectures
+    have = set(supported_architectures())
+    ref = """BailingMoEForCausalLM BailingMoeForCausalLM BailingMoeV2ForCausalLM BailingMoeV2_5ForCausalLM
+    DeepseekV3ForCausalLM DeepseekV2ForCausalLM DFlashDraftModel Gemma2ForCausalLM Gemma4ForCausalLM
+    Gemma4ForConditionalGeneration Glm4MoeForCausalLM Glm5ForCausalLM GlmMoeDsaForCausalLM Grok1ForCausalLM
+    KimiK25ForConditionalGeneration KimiLinearForCausalLM LlamaForCausalLM Phi3ForCausalLM InternLM3ForCausalLM
+    LlamaForCausalLMEagle3 MiMoForCausalLM MiMoMTPForCausalLM MiMoV2FlashForCausalLM MiMoV2MTPForCausalLM
+    MiMoV2ForCausalLM MiniMaxM2ForCausalLM QWenLMHeadModel Qwen2ForCausalLM Qwen2MoeForCausalLM Qwen3ForCausalLM
+    Qwen3_5MoeForConditionalGeneration Qwen3_5ForConditionalGeneration Qwen3MoeForCausalLM UMT5EncoderModel
+    UMT5DecoderModel UMT5Model UMT5ForConditionalGeneration""".split()
+    assert [r for r in ref if r not in have] == []
