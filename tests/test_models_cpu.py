@@ -850,6 +850,36 @@ def test_hybrid_recurrent_prefix_sharing_reuses_state_checkpoints(tmp_path):
     assert hosted[1:4] == plain[1:4] and hosted[4] == shared[4] and hosted[5] == shared[5]
 
 
+@pytest.mark.parametrize("which", ["phi3", "mistral", "qwen2_moe", "deepseek_v2"])
+def test_more_families_match_hf(tmp_path, which):
+    """Phi-3 (fused qkv / gate_up checkpoint tensors), Mistral, Qwen2-MoE (biased attention, fused expert tensors,
+    gated shared expert) and DeepSeek-V2 (MLA without a query LoRA, greedy routing)."""
+    import transformers
+    base = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, rms_norm_eps=1e-5, vocab_size=512, tie_word_embeddings=False,
+                max_position_embeddings=512, rope_theta=10000.0)
+    if which == "phi3":
+        cfg = dict(base, pad_token_id=0, original_max_position_embeddings=512, partial_rotary_factor=1.0)
+        hf, arch = transformers.Phi3ForCausalLM(transformers.Phi3Config(**cfg)), "Phi3ForCausalLM"
+    elif which == "mistral":
+        cfg = dict(base, sliding_window=None, head_dim=32)
+        hf, arch = transformers.MistralForCausalLM(transformers.MistralConfig(**cfg)), "MistralForCausalLM"
+    elif which == "qwen2_moe":
+        cfg = dict(base, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                   shared_expert_intermediate_size=96, norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[],
+                   use_sliding_window=False)
+        hf, arch = transformers.Qwen2MoeForCausalLM(transformers.Qwen2MoeConfig(**cfg)), "Qwen2MoeForCausalLM"
+    else:
+        cfg = dict(base, num_hidden_layers=3, kv_lora_rank=32, q_lora_rank=None, qk_nope_head_dim=16,
+                   qk_rope_head_dim=8, v_head_dim=16, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
+                   moe_intermediate_size=64, first_k_dense_replace=1, routed_scaling_factor=1.0, topk_method="greedy",
+                   n_group=1, topk_group=1, norm_topk_prob=False, num_key_value_heads=4)
+        hf, arch = transformers.DeepseekV2ForCausalLM(transformers.DeepseekV2Config(**cfg)), "DeepseekV2ForCausalLM"
+    hf = _init(hf)
+    path = _save(str(tmp_path / which), hf, cfg, arch, which)
+    assert _generate(path, PROMPTS, n=8) == _hf_generate(hf, PROMPTS, n=8)
+
+
 def test_every_reference_architecture_name_resolves():
     """The `architectures[0]` strings the reference registers (`EntryClass` of each file under its `models/`)."""
     from sglang_jax_b200.models.registry import supported_architectures
