@@ -152,6 +152,8 @@ class Req:
         self.extend_input_len = 0
         self.last_node: Any = None
         self.last_host_node: Any = None
+        self.host_token_pending = False     # latest token known on the host only (arrived with transferred KV)
+        self.penalty_restart = False        # this step must (re)build the request's device-side token counts
         self.swa_evicted_seqlen = 0          # SWA slots before this position were already released
         self.host_hit_length = 0
         self.cached_tokens = 0
@@ -698,6 +700,10 @@ class ScheduleBatch:
         """Requests whose prompt KV arrived from a prefill engine: they join the decode batch
         as if their prefill had just run here."""
         self.forward_mode = ForwardMode.DECODE
+        for r in self.reqs:
+            # the first token was sampled by the prefill engine: this engine's device-side map of latest tokens has
+            # nothing for the request's row yet, so its first decode step is fed the id itself, not a placeholder
+            r.host_token_pending = True
         self.req_pool_indices = np.asarray([r.req_pool_idx for r in self.reqs], dtype=np.int32)
         self.seq_lens = np.asarray([r.kv_committed_len for r in self.reqs], dtype=np.int32)
         self.output_ids = None
@@ -743,9 +749,12 @@ class ScheduleBatch:
             out, new_lens, _positions, placeholders, d_rows, d_pos, _d_ids = built
             for r_, p_ in zip(d_rows.tolist(), d_pos.tolist()):
                 pool._dirty.append((r_, p_, p_ + 1))
-            for r in reqs:
+            for i, r in enumerate(reqs):
                 r.kv_committed_len += 1
                 r.kv_allocated_len = r.kv_committed_len
+                if r.host_token_pending:
+                    placeholders[i] = r.output_ids[-1]
+                    r.host_token_pending, r.penalty_restart = False, True
             self.input_ids = placeholders
             self.output_ids = None
             self.req_pool_indices = rows
@@ -762,7 +771,14 @@ class ScheduleBatch:
             # future-token map slot of a row always holds the latest token sampled for the
             # request that occupies the row, whether or not the host has seen it yet.
             self.input_ids = -(np.asarray([r.req_pool_idx for r in reqs], dtype=np.int32) + 1)
+            for i, r in enumerate(reqs):
+                if r.host_token_pending:
+                    self.input_ids[i] = r.output_ids[-1]
+                    r.host_token_pending, r.penalty_restart = False, True
         else:
+            for r in reqs:
+                if r.host_token_pending:
+                    r.host_token_pending, r.penalty_restart = False, True
             self.input_ids = np.asarray([r.output_ids[-1] if r.output_ids else r.origin_input_ids[-1]
                                          for r in reqs], dtype=np.int32)
         self.output_ids = None

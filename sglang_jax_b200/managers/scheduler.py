@@ -163,9 +163,8 @@ class Scheduler(SchedulerOutputProcessorMixin, SchedulerMetricsMixin, SchedulerP
         if self.disagg_mode == "prefill":
             self.init_disaggregation_prefill()
         elif self.disagg_mode == "decode":
-            # transferred requests enter the decode batch with a host-known first token
-            self.enable_overlap = False
-            server_args.disable_overlap_schedule = True
+            # transferred requests enter the decode batch with a host-known first token: their first decode step is
+            # fed that id instead of a placeholder (`ScheduleBatch.prepare_for_decode`), so overlap scheduling stays on
             self.init_disaggregation_decode()
 
         self._dispatch = {

@@ -55,8 +55,17 @@ class PenaltyInfo:
         stop_ids = np.full((n, max(width, 1)), -1, np.int32)
         for i, s in enumerate(stops):
             stop_ids[i, :len(s)] = s
-        rows = np.arange(n, dtype=np.int32) if is_extend else np.empty(0, np.int32)
-        toks = [list(r.output_ids) for r in reqs] if is_extend else []
+        if is_extend:
+            rows = np.arange(n, dtype=np.int32)
+            toks = [list(r.output_ids) for r in reqs]
+        else:
+            # a request that enters decoding without a prefill here (its KV was transferred): its slot still holds the
+            # previous occupant's counts.  The token fed to this step is counted by the decode update itself.
+            rows = np.asarray([i for i, r in enumerate(reqs) if getattr(r, "penalty_restart", False)], np.int32)
+            toks = [list(reqs[i].output_ids[:-1]) for i in rows.tolist()]
+        for r in reqs:
+            if getattr(r, "penalty_restart", False):
+                r.penalty_restart = False
         return PenaltyInfo(freq, pres, mnt, gen, stop_ids, rows, toks)
 
 

@@ -231,6 +231,8 @@ def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
     plain = Engine(**common)
     try:
         want = [o["output_ids"] for o in plain.generate(input_ids=prompts, sampling_params=sp)]
+        sp_pen = dict(sp, frequency_penalty=1.2, presence_penalty=0.4)
+        want_pen = plain.generate(input_ids=prompts[0], sampling_params=sp_pen)["output_ids"]
     finally:
         plain.shutdown()
     srv = BootstrapServer(port=get_free_port(), secret="pd").start()
@@ -250,6 +252,8 @@ def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
         for t in ts:
             t.join(timeout=120)
         assert "decode" in res and "prefill" in res
+        # the decode engine keeps overlap scheduling: a transferred request's first step is fed its host-known token
+        assert decode.scheduler.enable_overlap and prefill.scheduler.enable_overlap
         assert [o["output_ids"] for o in res["decode"]] == want
         assert [o["output_ids"] for o in res["prefill"]] == [w[:1] for w in want]
         # both engines are clean afterwards: the prefill released the pages once they were acknowledged
@@ -260,6 +264,17 @@ def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
         time.sleep(0.1)
         prefill.scheduler.check_memory()
         decode.scheduler.check_memory()
+        # penalties follow a transferred request: its token counts are rebuilt on the decode engine's device state
+        pen = {}
+        tp = [threading.Thread(target=lambda: pen.update(d=decode.generate(input_ids=prompts[0], sampling_params=sp_pen,
+                                                                          bootstrap_room=21))),
+              threading.Thread(target=lambda: pen.update(p=prefill.generate(input_ids=prompts[0], sampling_params=sp_pen,
+                                                                           bootstrap_room=21)))]
+        for t in tp:
+            t.start()
+        for t in tp:
+            t.join(timeout=120)
+        assert pen["d"]["output_ids"] == want_pen and want_pen != want[0]
         # a request whose prefill never happens fails cleanly on the decode side (bounded pull)
         decode.scheduler.disagg_kv_manager.backend.pull_timeout = 0.5
         lost = decode.generate(input_ids=prompts[:1], sampling_params=sp, bootstrap_room=[999])[0]
