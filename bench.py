@@ -74,6 +74,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=60)
     ap.add_argument("--warmup", type=int, default=6)
     ap.add_argument("--impl", default="ours", choices=["ours", "nccl", "reference"])
+    ap.add_argument("--fused-max-tokens", type=int, default=None,
+                    help="A/B arm: forwards of at most this many rows use the fused NVLink residual dataflow "
+                         "(1000000 = every forward; default: the engine's own default)")
     ap.add_argument("--model", default="qwen3-32b")
     ap.add_argument("--concurrency", type=int, default=None)
     ap.add_argument("--input-len-min", type=int, default=None)
@@ -264,6 +267,8 @@ def main():
         return reference_arm(args)
     if args.impl == "nccl":
         args.disable_fused_comm = True
+    if args.fused_max_tokens is not None:
+        os.environ["SGLB_FUSED_MAX_TOKENS"] = str(args.fused_max_tokens)
 
     import numpy as np
     import torch

@@ -105,13 +105,16 @@ class ModelRunner:
         self.fused_residual_ok = model_supports_fused_residual(self.model)
         # forwards with fewer tokens than this use the library all-reduce + add-RMSNorm kernel instead of the fused
         # NVLink kernels (a per-forward choice: both dataflows are exact, they differ in latency)
-        # Forwards of `fused_min_tokens <= T <= fused_max_tokens` rows take the fused NVLink dataflow, the others the
-        # library all-reduce.  Measured on Qwen3-32B (TP2 and TP4, 128 running requests): a decode step (T = 128) is
-        # faster fused (12.9 ms against 16.0 ms at TP4), a prefill step (T ~ 1300) is faster with the library
-        # all-reduce (19.0 ms against 31.8 ms at TP4): the first is bound by the latency of 128 reduces, which one
-        # launch with peer stores shortens; the second by GEMM throughput, which the fused kernel's tail interrupts.
+        # Forwards of `fused_min_tokens <= T <= fused_max_tokens` rows take the fused NVLink dataflow (one launch for
+        # GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather), the others GEMM + library all-reduce +
+        # add-RMSNorm.  The default window is empty: measured end to end on Qwen3-32B with 128 running requests, the
+        # library path is faster at two GPUs (decode step 15.6 ms against 17.5 ms, prefill steps equal) and at four
+        # (17.4 ms against 19.3 ms per step).  The fused launch saves the reduction's latency but computes the
+        # row-parallel product with its own small-M GEMM, which loses more than that against the measured per-shape
+        # GEMM plan of the plain path.  `SGLB_FUSED_MAX_TOKENS=1000000` selects the fused dataflow for every forward,
+        # `512` for decode-sized ones only.
         self.fused_min_tokens = int(os.environ.get("SGLB_FUSED_MIN_TOKENS", "0"))
-        self.fused_max_tokens = int(os.environ.get("SGLB_FUSED_MAX_TOKENS", "512"))
+        self.fused_max_tokens = int(os.environ.get("SGLB_FUSED_MAX_TOKENS", "-1"))
         self.penalty_state = None          # sampling/penaltylib.PenaltyState, created when a request uses a penalty
         self.gemm_plan = None
         if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "1") == "1" and not is_draft_worker:

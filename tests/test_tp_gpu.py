@@ -172,7 +172,10 @@ def test_fused_comm_kernels_two_ranks():
 
 # ------------------------------------------------------------------------------------------
 def _engine(rank, world, fused, biased=False):
+    import os
     from sglang_jax_b200.server_args import ServerArgs
+    # the fused residual dataflow is opt-in (the library all-reduce path measured faster end to end)
+    os.environ["SGLB_FUSED_MAX_TOKENS"] = "1000000" if fused else "-1"
     from sglang_jax_b200.utils.tiny_models import TINY_QWEN3, write_tiny_qwen3_checkpoint
     cfg = dict(TINY_QWEN3, head_dim=128, num_attention_heads=8, num_key_value_heads=2, hidden_size=1024,
                intermediate_size=2048, num_hidden_layers=3, torch_dtype="bfloat16", tie_word_embeddings=False)
@@ -326,7 +329,9 @@ def _moe_ckpt(path):
 
 
 def _moe_engine(rank, world, backend, fused):
+    import os
     from sglang_jax_b200.server_args import ServerArgs
+    os.environ["SGLB_FUSED_MAX_TOKENS"] = "1000000" if fused else "-1"
     path = _moe_ckpt(f"/tmp/sglb200_moe_test_{rank}")
     sa = ServerArgs(model_path=path, device="cuda", dtype="bfloat16", page_size=16, skip_tokenizer_init=True,
                     max_total_tokens=8192, max_running_requests=8, enable_single_process=True, tp_size=world,
