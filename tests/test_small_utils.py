@@ -397,3 +397,56 @@ def test_checked_kernel_build_compiles(tmp_path):
     assert r.returncode == 0, r.stdout
     syms = subprocess.run(["nm", "-C", str(tmp_path / "e.o")], stdout=subprocess.PIPE, text=True).stdout
     assert "sglb_debug_set_kv_pages" in syms
+
+
+def test_moe_parity_tool_on_a_tiny_checkpoint(tmp_path, capsys):
+    """`utils/moe_parity.py`: one MoE layer's checkpoint weights through the framework's expert FFN against an fp32
+    expert-by-expert loop; per-expert and fused checkpoint layouts, key listing, quantised experts, npz dump."""
+    import json
+    import numpy as np
+    import torch
+    from safetensors.torch import save_file
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils import moe_parity
+    ps.reset_state()
+    E, H, I = 8, 64, 32
+    g = torch.Generator().manual_seed(0)
+    sd = {"model.layers.1.mlp.gate.weight": torch.randn(E, H, generator=g) * 0.2,
+          "model.layers.1.post_attention_layernorm.weight": 1 + 0.1 * torch.randn(H, generator=g)}
+    for e in range(E):
+        for n, shape in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+            sd[f"model.layers.1.mlp.experts.{e}.{n}.weight"] = torch.randn(*shape, generator=g) * 0.1
+    d = tmp_path / "per_expert"
+    d.mkdir()
+    save_file(sd, str(d / "model.safetensors"))
+    (d / "config.json").write_text(json.dumps(dict(num_experts=E, num_experts_per_tok=2, norm_topk_prob=True)))
+    common = ["--model-dir", str(d), "--from-config", "--layer-idx", "1", "--num-tokens", "24", "--device", "cpu"]
+    assert moe_parity.main(common + ["--dtype", "float32", "--atol", "1e-4", "--tokens-apply-rmsnorm",
+                                     "--dump-npz", str(tmp_path / "o.npz"), "--debug-topn", "2"]) == 0
+    out = capsys.readouterr().out
+    rep = json.loads(out.splitlines()[0])
+    assert rep["experts"] == E and rep["hidden"] == H and rep["intermediate"] == I and rep["max_abs"] < 1e-4
+    assert "token" in out.splitlines()[1]
+    z = np.load(tmp_path / "o.npz")
+    assert z["framework"].shape == (24, H) and np.allclose(z["framework"], z["reference"], atol=1e-4)
+    # key listing with a filter
+    assert moe_parity.main(["--model-dir", str(d), "--list-keys", "--match", r"experts\.3\."]) == 0
+    assert "3 keys" in capsys.readouterr().out
+    # the fused checkpoint layout gives the same layer
+    fused = {"model.layers.1.mlp.gate.weight": sd["model.layers.1.mlp.gate.weight"],
+             "model.layers.1.mlp.experts.gate_up_proj": torch.stack([torch.cat(
+                 [sd[f"model.layers.1.mlp.experts.{e}.gate_proj.weight"],
+                  sd[f"model.layers.1.mlp.experts.{e}.up_proj.weight"]], 0) for e in range(E)]),
+             "model.layers.1.mlp.experts.down_proj": torch.stack(
+                 [sd[f"model.layers.1.mlp.experts.{e}.down_proj.weight"] for e in range(E)])}
+    d2 = tmp_path / "fused"
+    d2.mkdir()
+    save_file(fused, str(d2 / "model.safetensors"))
+    (d2 / "config.json").write_text((d / "config.json").read_text())
+    assert moe_parity.main(["--model-dir", str(d2), "--from-config", "--layer-idx", "1", "--num-tokens", "24",
+                            "--device", "cpu", "--dtype", "float32", "--atol", "1e-4"]) == 0
+    capsys.readouterr()
+    # quantised experts: the report is the recipe's error on this layer (small, not zero), bf16 tokens
+    assert moe_parity.main(common + ["--moe-weight-dtype", "float8_e4m3fn", "--deterministic-router"]) == 0
+    q = json.loads(capsys.readouterr().out.splitlines()[0])
+    assert 1e-5 < q["rel_fro"] < 0.1 and q["cosine"] > 0.99 and q["experts_hit"] == E
