@@ -4,7 +4,8 @@
 `ExpertLocation` maps each logical expert to one or more physical slots spread over the EP
 ranks; the router's ids are rewritten to physical slots (replicas picked round-robin by token) so
 hot experts are served by several GPUs.  `rebalance` implements the DeepSeek EPLB heuristic:
-replicate the heaviest experts, then pack physical experts onto ranks greedily by load."""
+replicate the heaviest experts, then pack physical experts onto ranks greedily by load;
+`rebalance_hierarchical` is its node-aware form for group-limited routing."""
 
 from __future__ import annotations
 
@@ -54,6 +55,45 @@ def rebalance(expert_load: np.ndarray, num_phy: int, num_ranks: int) -> np.ndarr
     return phy2log[order]
 
 
+def rebalance_hierarchical(expert_load: np.ndarray, num_phy: int, num_groups: int, num_nodes: int,
+                           num_ranks: int) -> np.ndarray:
+    """Placement for group-limited routing across several nodes (reference `eplb_algorithms/deepseek.py`
+    `rebalance_experts_hierarchical`): (1) whole expert groups are packed onto nodes so that the groups a token may
+    choose from sit on one node, (2) inside every node the spare slots go to its experts with the highest load per
+    replica, (3) the node's physical experts are packed onto its ranks.  Returns phy2log of length `num_phy`, rank r
+    owning slots `[r * S, (r + 1) * S)`, ranks `[n * R, (n + 1) * R)` forming node n."""
+    load = np.asarray(expert_load, dtype=np.float64)
+    E = len(load)
+    if num_groups % num_nodes or E % num_groups or num_ranks % num_nodes or num_phy % num_ranks:
+        raise ValueError(f"groups ({num_groups}) must divide over nodes ({num_nodes}), experts ({E}) over groups, "
+                         f"ranks ({num_ranks}) over nodes and physical experts ({num_phy}) over ranks")
+    gsize = E // num_groups
+    group_node = balanced_packing(load.reshape(num_groups, gsize).sum(1), num_nodes)
+    phy_per_node, ranks_per_node = num_phy // num_nodes, num_ranks // num_nodes
+    out = []
+    for node in range(num_nodes):
+        experts = np.concatenate([np.arange(g * gsize, (g + 1) * gsize) for g in np.nonzero(group_node == node)[0]])
+        local, cnt = replicate_experts(load[experts], phy_per_node)
+        pack = balanced_packing(load[experts][local] / cnt[local], ranks_per_node)
+        out.append(experts[local[np.argsort(pack, kind="stable")]])
+    return np.concatenate(out).astype(np.int64)
+
+
+def rebalance_experts(expert_load: np.ndarray, num_phy: int, num_ranks: int, num_groups: int = 1, num_nodes: int = 1,
+                      algorithm: str = "auto") -> np.ndarray:
+    """One layer's phy2log.  `algorithm`: `deepseek` (global), `deepseek_hierarchical`, or `auto`, which takes the
+    hierarchical form when the groups divide over the nodes (reference `eplb_algorithms/__init__.py`
+    `compute_algorithm`)."""
+    if algorithm == "auto":
+        algorithm = "deepseek_hierarchical" if num_nodes > 1 and num_groups > 1 and num_groups % num_nodes == 0 \
+            else "deepseek"
+    if algorithm == "deepseek_hierarchical":
+        return rebalance_hierarchical(expert_load, num_phy, num_groups, num_nodes, num_ranks)
+    if algorithm != "deepseek":
+        raise ValueError(f"unknown EPLB algorithm {algorithm!r}")
+    return rebalance(np.asarray(expert_load, dtype=np.float64), num_phy, num_ranks)
+
+
 class ExpertLocation:
     def __init__(self, num_logical: int, ep_size: int, num_redundant: int = 0, phy2log: np.ndarray | None = None,
                  device="cpu"):
@@ -92,9 +132,11 @@ class ExpertLocation:
         return logical_weights[torch.as_tensor(self.phy2log, device=logical_weights.device)]
 
     @classmethod
-    def from_load(cls, expert_load, ep_size: int, num_redundant: int, device="cpu") -> "ExpertLocation":
+    def from_load(cls, expert_load, ep_size: int, num_redundant: int, device="cpu", num_groups: int = 1,
+                  num_nodes: int = 1, algorithm: str = "auto") -> "ExpertLocation":
         load = np.asarray(expert_load, dtype=np.float64)
-        return cls(len(load), ep_size, num_redundant, rebalance(load, len(load) + num_redundant, ep_size), device)
+        phy2log = rebalance_experts(load, len(load) + num_redundant, ep_size, num_groups, num_nodes, algorithm)
+        return cls(len(load), ep_size, num_redundant, phy2log, device)
 
 
 class ExpertDistributionRecorder:

@@ -51,13 +51,17 @@ class MoeRuntime:
     num_redundant: int = 0
     expert_load = None            # [layers, experts] hit counts that seed the placement, or None ("trivial")
     recorder = None               # eplb.ExpertDistributionRecorder
+    num_groups: int = 1           # expert groups of group-limited routing (`n_group`)
+    num_nodes: int = 1            # nodes the expert-parallel ranks span: with groups, the placement keeps a group on a node
 
 
 _RUNTIME = MoeRuntime()
 
 
-def configure_moe_runtime(num_redundant: int = 0, init_expert_location: str | None = "trivial", recorder=None):
+def configure_moe_runtime(num_redundant: int = 0, init_expert_location: str | None = "trivial", recorder=None,
+                          num_groups: int = 1, num_nodes: int = 1):
     _RUNTIME.num_redundant = int(num_redundant or 0)
+    _RUNTIME.num_groups, _RUNTIME.num_nodes = max(int(num_groups or 1), 1), max(int(num_nodes or 1), 1)
     _RUNTIME.expert_load = None
     if init_expert_location and init_expert_location != "trivial":
         from ..eplb.expert_location import load_expert_load
@@ -86,7 +90,9 @@ class FusedMoE(nn.Module):
             from ..eplb.expert_location import ExpertLocation
             load = _RUNTIME.expert_load
             if load is not None and layer_id < len(load) and len(load[layer_id]) == num_experts:
-                self.expert_location = ExpertLocation.from_load(load[layer_id], ep, _RUNTIME.num_redundant)
+                self.expert_location = ExpertLocation.from_load(load[layer_id], ep, _RUNTIME.num_redundant,
+                                                                num_groups=_RUNTIME.num_groups,
+                                                                num_nodes=_RUNTIME.num_nodes)
             else:
                 self.expert_location = ExpertLocation(num_experts, ep, _RUNTIME.num_redundant)
             num_experts = self.expert_location.num_physical

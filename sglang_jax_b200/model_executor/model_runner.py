@@ -69,7 +69,9 @@ class ModelRunner:
                 model_config.num_hidden_layers, n_exp, server_args.expert_distribution_recorder_buffer_size,
                 server_args.expert_distribution_recorder_output_file, device=self.device)
         configure_moe_runtime(getattr(server_args, "ep_num_redundant_experts", 0),
-                              getattr(server_args, "init_expert_location", "trivial"), self.expert_recorder)
+                              getattr(server_args, "init_expert_location", "trivial"), self.expert_recorder,
+                              num_groups=getattr(model_config.hf_text_config, "n_group", 1) or 1,
+                              num_nodes=getattr(server_args, "nnodes", 1) or 1)
         self.model = loader.load_model(model_config, self.device, self.quant_config)
         configure_moe_runtime()          # later models (a draft head) start from the defaults
         if not is_draft_worker:

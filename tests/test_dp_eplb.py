@@ -50,6 +50,33 @@ def test_eplb_replication_and_packing():
     assert loc.physical_weights(w).view(-1).tolist() == [float(x) for x in loc.phy2log]
 
 
+def test_eplb_hierarchical_keeps_groups_on_nodes_and_balances_ranks():
+    """Node-aware placement for group-limited routing: whole expert groups stay on one node, spare slots go to the
+    node's hot experts, ranks inside a node carry similar load; `auto` picks it when the groups divide over nodes."""
+    from sglang_jax_b200.eplb.expert_location import rebalance_experts, rebalance_hierarchical
+    rng = np.random.RandomState(0)
+    E, groups, nodes, ranks, phy = 32, 4, 2, 8, 40
+    load = rng.gamma(0.6, 100.0, size=E) + 1
+    m = rebalance_hierarchical(load, phy, groups, nodes, ranks)
+    assert len(m) == phy and set(m.tolist()) == set(range(E))
+    per_node = phy // nodes
+    node_of_group = {}
+    for p, e in enumerate(m.tolist()):
+        assert node_of_group.setdefault(e // (E // groups), p // per_node) == p // per_node     # a group lives on one node
+    cnt = np.bincount(m, minlength=E)
+    slots = phy // ranks
+    rank_load = np.array([sum(load[e] / cnt[e] for e in m[r * slots:(r + 1) * slots]) for r in range(ranks)])
+    naive = load.reshape(ranks, -1).sum(1)
+    assert rank_load.max() / rank_load.mean() < naive.max() / naive.mean()
+    assert np.array_equal(rebalance_experts(load, phy, ranks, groups, nodes, "auto"), m)
+    flat = rebalance_experts(load, phy, ranks, groups, 1, "auto")                # one node: the global algorithm
+    assert np.array_equal(flat, rebalance(load, phy, ranks))
+    loc = ExpertLocation.from_load(load, ep_size=ranks, num_redundant=phy - E, num_groups=groups, num_nodes=nodes)
+    assert np.array_equal(loc.phy2log, m)
+    with pytest.raises(ValueError):
+        rebalance_hierarchical(load, phy, 3, 2, ranks)
+
+
 def test_data_parallel_replicas_route_and_match_single_engine(tmp_path):
     """dp_size=2: two replicas behind the router produce exactly the single-engine outputs, the
     router spreads the requests, and a pinned `dp_rank` is honoured."""
