@@ -69,6 +69,9 @@ class SectionScheduler(Scheduler):
         self.section_rank = dp_rank
         self.owner = owner
         self.inbox: queue.Queue = queue.Queue()
+        # prompt tokens routed here that the section has not taken out of its inbox yet: a burst that arrives in one
+        # intake tick is balanced against what the same tick already sent (reference `dp_rank_assignment.py`)
+        self.inbox_tokens = 0
         super().__init__(server_args, None, tp_worker=tp_worker, recv_queue=self.inbox, send_queue=None,
                          tokenizer=tokenizer, model_config=model_config)
 
@@ -80,6 +83,7 @@ class SectionScheduler(Scheduler):
 
     def handle_generate_request(self, recv):
         recv.dp_rank = self.section_rank
+        self.inbox_tokens = max(self.inbox_tokens - len(recv.input_ids or ()), 0)
         return super().handle_generate_request(recv)
 
     def on_idle(self):
@@ -95,7 +99,8 @@ class SectionScheduler(Scheduler):
     def load(self) -> DPRankLoad:
         used, _ = self.token_usage()
         return DPRankLoad(running=len(self.running_batch.reqs), queued=len(self.waiting_queue) + self.inbox.qsize(),
-                          queued_tokens=sum(len(r.origin_input_ids) for r in self.waiting_queue), used_tokens=used)
+                          queued_tokens=sum(len(r.origin_input_ids) for r in self.waiting_queue) + self.inbox_tokens,
+                          used_tokens=used)
 
 
 class _FrontDoor(Scheduler):
@@ -154,6 +159,8 @@ class DPScheduler:
                 d = self.select_dp_for_request(m)
                 self.assignment.assign(m.rid, d)
                 self.routed[d] += 1
+                if isinstance(m, TokenizedGenerateReqInput):
+                    self.sections[d].inbox_tokens += len(m.input_ids or ())
                 self.sections[d].inbox.put(m)
             elif isinstance(m, AbortReq):
                 for s in self.sections:
