@@ -280,7 +280,12 @@ def _launch_threads(engine: Engine, server_args: ServerArgs):
 
     configure_logger(server_args)
     st = ps.get_state()
-    if not st.initialized:
+    own_state = None
+    if server_args.device_indexes and server_args.tp_size == 1:
+        # an engine pinned to one device of several: its scheduler thread gets a state of its own, so other engines
+        # of this process (on other devices) are not disturbed
+        own_state = ps.single_device_state(server_args.device, server_args.device_indexes[0])
+    elif not st.initialized:
         if server_args.tp_size > 1:
             raise RuntimeError("enable_single_process with tp_size > 1 needs the ranks to be launched externally "
                                "(torchrun) and `parallel.state.init_distributed` called first")
@@ -293,6 +298,9 @@ def _launch_threads(engine: Engine, server_args: ServerArgs):
     def sched_main():
         try:
             import torch
+            if own_state is not None:
+                ps.bind_thread_state(own_state)
+                engine.parallel_state = own_state
             if ps.get_state().device.type == "cuda":
                 torch.cuda.set_device(ps.get_state().device)
             sched = Scheduler(server_args, None, recv_queue=to_sched, send_queue=_Router(to_detok, to_tok))

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import datetime
 import os
+import threading
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -43,26 +44,45 @@ class ParallelState:
 
 
 _STATE = ParallelState()
+# Several single-process engines can live in one process, each on its own device (the reference's
+# "multiple engines in one process" mode for RL roll-outs, `device_indexes`): an engine's scheduler thread then
+# carries its own state, which wins over the process-wide one for everything that runs on that thread.
+_THREAD = threading.local()
 
 
 def get_state() -> ParallelState:
-    return _STATE
+    return getattr(_THREAD, "state", None) or _STATE
+
+
+def bind_thread_state(state: ParallelState | None) -> None:
+    """Make `state` what `get_state()` returns on the calling thread (None: back to the process-wide state)."""
+    _THREAD.state = state
+
+
+def single_device_state(device: str = "cuda", index: int | None = None) -> ParallelState:
+    """State of a one-rank engine on `device` (`cuda:index` when an index is given); nothing process-wide changes."""
+    st = ParallelState()
+    if device.startswith("cuda") and torch.cuda.is_available():
+        st.local_rank = int(index if index is not None else 0)
+        st.device = torch.device("cuda", st.local_rank)
+    st.initialized = True
+    return st
 
 
 def tp_rank() -> int:
-    return _STATE.tp.rank
+    return get_state().tp.rank
 
 
 def tp_size() -> int:
-    return _STATE.tp.size
+    return get_state().tp.size
 
 
 def ep_rank() -> int:
-    return _STATE.ep.rank
+    return get_state().ep.rank
 
 
 def ep_size() -> int:
-    return _STATE.ep.size
+    return get_state().ep.size
 
 
 def _mk_group(ranks: list[int], my_rank: int, backend_dev: str | None) -> GroupInfo | None:
@@ -137,7 +157,7 @@ def destroy():
 
 # --------------------------------------------------------------------------- collectives (NCCL / gloo path)
 def all_reduce(x: torch.Tensor, group: GroupInfo | None = None) -> torch.Tensor:
-    g = group or _STATE.tp
+    g = group or get_state().tp
     if g.size == 1:
         return x
     dist.all_reduce(x, group=g.device_group)
@@ -145,7 +165,7 @@ def all_reduce(x: torch.Tensor, group: GroupInfo | None = None) -> torch.Tensor:
 
 
 def all_gather(x: torch.Tensor, dim: int = -1, group: GroupInfo | None = None) -> torch.Tensor:
-    g = group or _STATE.tp
+    g = group or get_state().tp
     if g.size == 1:
         return x
     x = x.contiguous()
@@ -161,7 +181,7 @@ def all_gather(x: torch.Tensor, dim: int = -1, group: GroupInfo | None = None) -
 
 def reduce_scatter(x: torch.Tensor, group: GroupInfo | None = None) -> torch.Tensor:
     """Sum over ranks, each rank keeps its slice of dim 0."""
-    g = group or _STATE.tp
+    g = group or get_state().tp
     if g.size == 1:
         return x
     out = torch.empty((x.shape[0] // g.size, *x.shape[1:]), dtype=x.dtype, device=x.device)
@@ -171,7 +191,7 @@ def reduce_scatter(x: torch.Tensor, group: GroupInfo | None = None) -> torch.Ten
 
 def all_to_all_single(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits,
                       group: GroupInfo | None = None):
-    g = group or _STATE.ep
+    g = group or get_state().ep
     if g.size == 1:
         out.copy_(inp)
         return out
@@ -180,7 +200,7 @@ def all_to_all_single(out: torch.Tensor, inp: torch.Tensor, out_splits, in_split
 
 
 def broadcast_object(obj, src: int = 0, group: GroupInfo | None = None):
-    g = group or _STATE.world
+    g = group or get_state().world
     if g.size == 1:
         return obj
     box = [obj]
@@ -189,6 +209,6 @@ def broadcast_object(obj, src: int = 0, group: GroupInfo | None = None):
 
 
 def barrier(group: GroupInfo | None = None):
-    g = group or _STATE.world
+    g = group or get_state().world
     if g.size > 1:
         dist.barrier(group=g.cpu_group)

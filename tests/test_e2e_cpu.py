@@ -368,3 +368,33 @@ def test_frequency_presence_penalties_and_min_new_tokens_match_a_manual_oracle(c
         assert [o["output_ids"] for o in again] == want[:2]
     finally:
         eng.shutdown()
+
+
+def test_several_engines_in_one_process_keep_their_own_parallel_state(ckpt, oracle):
+    """`device_indexes` pins a single-process engine to one device; its scheduler thread carries its own parallel
+    state, so two engines of one process (RL roll-out workers) do not disturb each other or the process-wide state
+    (reference `test/srt/rl/test_multi_engines_in_one_process.py`)."""
+    import threading
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    ps.reset_state()
+    kw = dict(model_path=ckpt, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+              max_total_tokens=8192, enable_single_process=True)
+    a = Engine(device_indexes=[0], **kw)
+    b = Engine(device_indexes=[1], **kw)
+    try:
+        assert a.parallel_state is not b.parallel_state and not ps.get_state().initialized
+        assert a.parallel_state.local_rank == 0 and a.parallel_state.initialized
+        sp = {"max_new_tokens": 32, "temperature": 0.0, "ignore_eos": True}
+        res = {}
+        ts = [threading.Thread(target=lambda n=n, e=e: res.update({n: e.generate(input_ids=workload(), sampling_params=sp)}))
+              for n, e in (("a", a), ("b", b))]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout=300)
+        assert [o["output_ids"] for o in res["a"]] == oracle and [o["output_ids"] for o in res["b"]] == oracle
+        assert res["a"][0]["meta_info"].get("cache_miss_count", 0) == 0
+    finally:
+        a.shutdown()
+        b.shutdown()
