@@ -14,6 +14,7 @@ import time
 
 import numpy as np
 
+from . import req_time_stats
 from .base.kv_manager import KVPoll
 from .common import metrics
 
@@ -27,6 +28,7 @@ class DecodePreallocQueue:
 
     def add(self, req):
         req.disagg_enqueue_time = time.perf_counter()
+        req_time_stats.mark(self.s, req, "created")
         self.queue.append(req)
         metrics.set_queue_depth("decode_prealloc", len(self.queue))
 
@@ -87,6 +89,7 @@ class DecodePreallocQueue:
             recv = s.disagg_kv_manager.create_receiver(req.rid)
             recv.init(pages, str(req.bootstrap_room), addr)
             req.disagg_receiver = recv
+            req_time_stats.mark(s, req, "prealloc_done")
             out.append(req)
         self.queue = keep
         metrics.set_queue_depth("decode_prealloc", len(keep))
@@ -117,6 +120,7 @@ class DecodeTransferQueue:
                 req.output_ids = [int(meta["first_token"])]
                 req.kv_committed_len = n
                 req.first_token_time = time.perf_counter()
+                req_time_stats.mark(s, req, "transfer_done")
                 done.append(req)
             elif st == KVPoll.FAILED:
                 reason = req.disagg_receiver.state.failure
@@ -147,6 +151,17 @@ class SchedulerDisaggregationDecodeMixin:
                             sa.disaggregation_bootstrap_timeout_seconds), kv_layout_of(self))
         self.disagg_received = 0
         self.disagg_failed = 0
+        # `--disaggregation-decode-watchdog-seconds`: complain when the loop has not turned for that long although
+        # requests wait in the prealloc / transfer queues or decode (reference `runtime.py:136`)
+        from .decode_watchdog import EventLoopWatchdog
+        self.disagg_decode_watchdog = EventLoopWatchdog(
+            float(getattr(sa, "disaggregation_decode_watchdog_seconds", 0) or 0),
+            has_work=lambda: bool(self.disagg_prealloc_queue.queue or self.disagg_transfer_queue.queue
+                                  or not self.running_batch.is_empty()),
+            on_stall=lambda idle: logger.error(
+                "PD decode loop has not turned for %.1fs: prealloc=%d transfer=%d running=%d", idle,
+                len(self.disagg_prealloc_queue.queue), len(self.disagg_transfer_queue.queue),
+                len(self.running_batch.reqs))).start()
 
     def disagg_decode_admit(self, req) -> bool:
         """Route a PD request into the prealloc queue; False = treat as an ordinary request."""
@@ -174,6 +189,7 @@ class SchedulerDisaggregationDecodeMixin:
 
     def process_disagg_decode_queues(self) -> int:
         """One turn of the decode-side pipeline: prealloc -> transfer -> running batch."""
+        self.disagg_decode_watchdog.beat()
         moved = self.disagg_prealloc_queue.pop_preallocated()
         if moved:
             self.disagg_transfer_queue.extend(moved)

@@ -14,6 +14,7 @@ import uuid
 
 import numpy as np
 
+from . import req_time_stats
 from .base.kv_manager import KVPoll
 from .common import metrics
 
@@ -51,6 +52,7 @@ class SchedulerDisaggregationPrefillMixin:
         kv_len = min(req.kv_committed_len, len(req.origin_input_ids))
         slots = self.req_to_token_pool.read(req.req_pool_idx, kv_len)
         pages = (slots[::P] // P).astype(np.int64)
+        req_time_stats.mark(self, req, "forward_done")
         try:
             sender = self.disagg_kv_manager.create_sender(req.rid)
             sender.init(pages, str(req.bootstrap_room), int(req.output_ids[0]),
@@ -61,6 +63,7 @@ class SchedulerDisaggregationPrefillMixin:
             return False
         req.disagg_sender = sender
         req.disagg_sent_time = time.perf_counter()
+        req_time_stats.mark(self, req, "transfer_start")
         self.disagg_prefill_inflight.append(req)
         metrics.set_queue_depth("prefill_inflight", len(self.disagg_prefill_inflight))
         return True
@@ -82,6 +85,7 @@ class SchedulerDisaggregationPrefillMixin:
                 logger.warning("KV transfer of %s failed: %s", req.rid, req.disagg_sender.state.failure)
             req.disagg_sender.clear()
             req.disagg_done = True
+            req_time_stats.mark(self, req, "transfer_done", final=True)
             # a failed hand-over leaves nothing worth caching under this engine's name either way;
             # the pages are valid KV of the prompt, so they can serve later prefixes
             self._finish_req(req)

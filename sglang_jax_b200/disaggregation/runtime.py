@@ -4,6 +4,7 @@
 from __future__ import annotations
 
 import logging
+import os
 
 from . import pd_auth
 from .bootstrap import BootstrapClient, HeartbeatDaemon
@@ -27,6 +28,14 @@ def build_kv_manager(scheduler, role: str, engine_id: str):
     sa = scheduler.server_args
     secret = pd_auth.resolve_secret(sa.disaggregation_shared_secret)
     host = get_host_ip(sa.disaggregation_host_ip) if sa.disaggregation_host_ip else "127.0.0.1"
+    if os.environ.get("DISAGG_LAUNCH_BOOTSTRAP", "") == "1" and getattr(scheduler, "disagg_bootstrap_server", None) is None:
+        # one engine of the deployment hosts the registry itself (reference `runtime.py:66`), on
+        # `--disaggregation-bootstrap-port`
+        from .bootstrap import BootstrapServer
+        scheduler.disagg_bootstrap_server = BootstrapServer(host, sa.disaggregation_bootstrap_port, secret=secret).start()
+        logger.info("embedded PD bootstrap server at %s", scheduler.disagg_bootstrap_server.url)
+        if not sa.disaggregation_bootstrap_url:
+            sa.disaggregation_bootstrap_url = scheduler.disagg_bootstrap_server.url
     layout = kv_layout_of(scheduler)
     backend = create_transfer_backend(scheduler.token_to_kv_pool, sa, local_host=host, role=role, shared_secret=secret,
                                       max_req_input_len=getattr(scheduler, "max_req_input_len", None))
@@ -58,9 +67,16 @@ def build_kv_manager(scheduler, role: str, engine_id: str):
 def shutdown_disaggregation(scheduler, drain_timeout: float = 10.0):
     mgr = getattr(scheduler, "disagg_kv_manager", None)
     hb = getattr(scheduler, "disagg_heartbeat", None)
+    wd = getattr(scheduler, "disagg_decode_watchdog", None)
+    if wd is not None:
+        wd.stop()
     if hb is not None:
         hb.stop()          # stop advertising first, then let running transfers finish
     if mgr is not None:
         if not mgr.drain(drain_timeout):
             logger.warning("PD shutdown: %d transfers still in flight", mgr.inflight())
         mgr.shutdown()
+    srv = getattr(scheduler, "disagg_bootstrap_server", None)
+    if srv is not None:
+        srv.stop()
+        scheduler.disagg_bootstrap_server = None

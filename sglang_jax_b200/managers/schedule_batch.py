@@ -755,6 +755,8 @@ class ScheduleBatch:
                 if r.host_token_pending:
                     placeholders[i] = r.output_ids[-1]
                     r.host_token_pending, r.penalty_restart = False, True
+                    if getattr(r, "pd_time_stats", None) is not None:
+                        r.pd_time_stats.mark("first_decode_step")
             self.input_ids = placeholders
             self.output_ids = None
             self.req_pool_indices = rows
@@ -775,10 +777,14 @@ class ScheduleBatch:
                 if r.host_token_pending:
                     self.input_ids[i] = r.output_ids[-1]
                     r.host_token_pending, r.penalty_restart = False, True
+                    if getattr(r, "pd_time_stats", None) is not None:
+                        r.pd_time_stats.mark("first_decode_step")
         else:
             for r in reqs:
                 if r.host_token_pending:
                     r.host_token_pending, r.penalty_restart = False, True
+                    if getattr(r, "pd_time_stats", None) is not None:
+                        r.pd_time_stats.mark("first_decode_step")
             self.input_ids = np.asarray([r.output_ids[-1] if r.output_ids else r.origin_input_ids[-1]
                                          for r in reqs], dtype=np.int32)
         self.output_ids = None

@@ -171,6 +171,9 @@ class SchedulerOutputProcessorMixin:
         req.finished_time = time.perf_counter()
         if getattr(self, "disagg_mode", "null") == "prefill" and self.disagg_prefill_hold(req):
             return      # the KV stays until the decode engine has pulled it
+        if getattr(self, "disagg_mode", "null") == "decode" and getattr(req, "pd_time_stats", None) is not None:
+            from ..disaggregation import req_time_stats
+            req_time_stats.mark(self, req, "finished", final=True)
         if req.req_pool_idx is not None:
             self.tree_cache.cache_finished_req(req, is_insert=insert and not isinstance(req.finished_reason, FINISH_ABORT))
             self.req_to_token_pool.free(req.req_pool_idx)

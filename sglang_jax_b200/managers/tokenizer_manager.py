@@ -186,6 +186,24 @@ class TokenizerManager:
             input_ids = self.tokenizer.encode(text)
         return self._create_tokenized_object(obj, text, list(input_ids))
 
+    def _batch_tokenize(self, subs: list):
+        """`--enable-tokenizer-batch-encode` (reference `tokenizer_manager.py:493`, `:632`): the texts of a batch
+        request go through the tokenizer in one call; requests that carry token ids, embeddings or media cannot."""
+        if self.tokenizer is None:
+            raise ValueError("The engine was initialised with skip_tokenizer_init=True: pass input_ids, not text.")
+        for sub in subs:
+            if getattr(sub, "input_ids", None) is not None:
+                raise ValueError("Batch tokenization is not needed for pre-tokenized input_ids. "
+                                 "Do not set `enable_tokenizer_batch_encode`.")
+            if getattr(sub, "input_embeds", None) is not None:
+                raise ValueError("Batch tokenization is not needed for input_embeds. "
+                                 "Do not set `enable_tokenizer_batch_encode`.")
+            if getattr(sub, "image_data", None) or getattr(sub, "audio_data", None) or getattr(sub, "video_data", None):
+                raise ValueError("For multimodal input processing do not set `enable_tokenizer_batch_encode`.")
+        texts = [sub.text for sub in subs]
+        enc = self.tokenizer(texts)["input_ids"] if callable(self.tokenizer) else [self.tokenizer.encode(t) for t in texts]
+        return [self._create_tokenized_object(sub, sub.text, list(ids)) for sub, ids in zip(subs, enc)]
+
     def _validate_len(self, obj, n_in: int, sp: SamplingParams | None):
         if self.max_req_input_len is not None and n_in >= self.max_req_input_len and not self.server_args.allow_auto_truncate:
             raise ValueError(f"The input ({n_in} tokens) is longer than the model's context length "
@@ -265,9 +283,12 @@ class TokenizerManager:
         gens, rids = [], []
         n = getattr(obj, "parallel_sample_num", 1)
         if n == 1:
-            for i in range(bs):
-                sub = obj[i]
-                tok = await self._tokenize_one_request(sub)
+            subs = [obj[i] for i in range(bs)]
+            if getattr(self.server_args, "enable_tokenizer_batch_encode", False):
+                toks = self._batch_tokenize(subs)          # one tokenizer call for the whole batch
+            else:
+                toks = [await self._tokenize_one_request(sub) for sub in subs]
+            for sub, tok in zip(subs, toks):
                 st = self._send_one_request(sub, tok, created)
                 gens.append(self._wait_one_response(sub, st, request))
                 rids.append(sub.rid)

@@ -292,6 +292,10 @@ class ServerArgs:
             self.disable_overlap_schedule = True
             self.enable_mixed_chunk = False
         if self.disaggregation_mode != "null":
+            if not self.disaggregation_bootstrap_url and os.environ.get("DISAGG_LAUNCH_BOOTSTRAP", "") == "1":
+                # this engine hosts the registry itself, on --disaggregation-bootstrap-port
+                host = self.disaggregation_host_ip or "127.0.0.1"
+                self.disaggregation_bootstrap_url = f"http://{host}:{self.disaggregation_bootstrap_port}"
             assert self.disaggregation_bootstrap_url, "PD mode requires --disaggregation-bootstrap-url"
             assert self.page_size >= 16, "PD mode requires a page_size of at least 16"
         self.check_lora_server_args()

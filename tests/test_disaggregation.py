@@ -238,8 +238,20 @@ def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
     srv = BootstrapServer(port=get_free_port(), secret="pd").start()
     pd_kw = dict(disaggregation_bootstrap_url=srv.url, disaggregation_shared_secret="pd",
                  disaggregation_transfer_port=0, disaggregation_side_channel_port=0)
-    prefill = Engine(**common, disaggregation_mode="prefill", chunked_prefill_size=32, **pd_kw)
-    decode = Engine(**common, disaggregation_mode="decode", **pd_kw)
+    prefill = Engine(**common, disaggregation_mode="prefill", chunked_prefill_size=32,
+                     enable_request_time_stats_logging=True, **pd_kw)
+    decode = Engine(**common, disaggregation_mode="decode", enable_request_time_stats_logging=True, **pd_kw)
+    stats_lines = []
+    import logging as _logging
+
+    class _Grab(_logging.Handler):
+        def emit(self, record):
+            if "PD time stats" in record.getMessage():
+                stats_lines.append(record.getMessage())
+
+    grab = _Grab()
+    _logging.getLogger("sglang_jax_b200.disaggregation.req_time_stats").addHandler(grab)
+    _logging.getLogger("sglang_jax_b200.disaggregation.req_time_stats").setLevel(_logging.INFO)
     try:
         res = {}
 
@@ -261,6 +273,11 @@ def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
         while time.time() - t0 < 5 and prefill.scheduler.disagg_prefill_inflight:
             time.sleep(0.02)
         assert prefill.scheduler.disagg_sent == 3 and decode.scheduler.disagg_received == 3
+        # --enable-request-time-stats-logging: one line per request and role with the stage durations
+        roles = [("role=prefill" in l, "role=decode" in l) for l in stats_lines]
+        assert sum(p for p, _ in roles) == 3 and sum(d for _, d in roles) == 3
+        assert any("transfer_start->transfer_done" in l for l in stats_lines)
+        assert any("transfer_done->first_decode_step" in l and "total_s" in l for l in stats_lines)
         time.sleep(0.1)
         prefill.scheduler.check_memory()
         decode.scheduler.check_memory()
@@ -289,6 +306,7 @@ def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
         prefill.shutdown()
         decode.shutdown()
         srv.stop()
+        _logging.getLogger("sglang_jax_b200.disaggregation.req_time_stats").removeHandler(grab)
 
 
 def test_tensor_parallel_engines_hand_over_every_ranks_shard(tmp_path):
@@ -367,3 +385,46 @@ def test_host_staged_transfer_uses_the_queue_pool_on_gpu():
         assert kv_digest(src, list(range(1, 7))) == kv_digest(dst, list(range(7, 13)))
     finally:
         pb.stop()
+
+
+def test_embedded_bootstrap_server_and_decode_watchdog_flags(tmp_path, monkeypatch):
+    """`DISAGG_LAUNCH_BOOTSTRAP=1`: the engine hosts the registry on `--disaggregation-bootstrap-port` and needs no
+    URL; `--disaggregation-decode-watchdog-seconds` arms the loop watchdog of the decode engine."""
+    from sglang_jax_b200.entrypoints.engine import Engine
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import write_tiny_qwen3_checkpoint
+    from sglang_jax_b200.disaggregation.runtime import shutdown_disaggregation
+    ckpt = write_tiny_qwen3_checkpoint(str(tmp_path / "m"))
+    port = get_free_port()
+    monkeypatch.setenv("DISAGG_LAUNCH_BOOTSTRAP", "1")
+    ps.reset_state()
+    common = dict(model_path=ckpt, device="cpu", enable_single_process=True, page_size=16, skip_tokenizer_init=True,
+                  max_total_tokens=1024, dtype="float32", log_level="error", disaggregation_shared_secret="pd",
+                  disaggregation_transfer_port=0, disaggregation_side_channel_port=0)
+    prefill = Engine(**common, disaggregation_mode="prefill", disaggregation_bootstrap_port=port)
+    monkeypatch.delenv("DISAGG_LAUNCH_BOOTSTRAP")
+    decode = Engine(**common, disaggregation_mode="decode", disaggregation_bootstrap_url=f"http://127.0.0.1:{port}",
+                    disaggregation_decode_watchdog_seconds=30.0)
+    try:
+        assert prefill.scheduler.disagg_bootstrap_server.url == f"http://127.0.0.1:{port}"
+        assert prefill.scheduler.server_args.disaggregation_bootstrap_url == f"http://127.0.0.1:{port}"
+        wd = decode.scheduler.disagg_decode_watchdog
+        assert wd.timeout == 30.0 and wd._thread.is_alive() and wd.stalls == 0
+        sp = {"temperature": 0.0, "max_new_tokens": 4, "ignore_eos": True}
+        res = {}
+        ts = [threading.Thread(target=lambda: res.update(d=decode.generate(input_ids=list(range(5, 45)), sampling_params=sp,
+                                                                          bootstrap_room=7))),
+              threading.Thread(target=lambda: res.update(p=prefill.generate(input_ids=list(range(5, 45)), sampling_params=sp,
+                                                                           bootstrap_room=7)))]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout=120)
+        assert len(res["d"]["output_ids"]) == 4 and res["d"]["output_ids"][0] == res["p"]["output_ids"][0]
+    finally:
+        shutdown_disaggregation(prefill.scheduler, 1)
+        shutdown_disaggregation(decode.scheduler, 1)
+        prefill.shutdown()
+        decode.shutdown()
+    assert not decode.scheduler.disagg_decode_watchdog._thread.is_alive()
+    assert prefill.scheduler.disagg_bootstrap_server is None

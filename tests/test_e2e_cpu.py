@@ -398,3 +398,44 @@ def test_several_engines_in_one_process_keep_their_own_parallel_state(ckpt, orac
     finally:
         a.shutdown()
         b.shutdown()
+
+
+def test_tokenizer_batch_encode_tokenizes_a_batch_in_one_call(ckpt):
+    """`--enable-tokenizer-batch-encode`: the texts of a batch request go through the tokenizer in one call and
+    produce the outputs of the per-request path; token-id inputs are refused under the flag."""
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+
+    class Tok:
+        eos_token_id = None
+        calls = []
+
+        def encode(self, text, **kw):
+            self.calls.append(("one", text))
+            return [5 + (ord(c) % 200) for c in text]
+
+        def __call__(self, texts, **kw):
+            self.calls.append(("batch", len(texts)))
+            return {"input_ids": [[5 + (ord(c) % 200) for c in t] for t in texts]}
+
+        def decode(self, ids, **kw):
+            return " ".join(map(str, ids))
+
+    ps.reset_state()
+    eng = Engine(model_path=ckpt, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                 max_total_tokens=8192, enable_single_process=True)
+    try:
+        tok = Tok()
+        eng.tokenizer_manager.tokenizer = tok
+        texts = ["the quick brown fox", "jumps over", "the lazy dog again and again"]
+        sp = {"max_new_tokens": 6, "temperature": 0.0, "ignore_eos": True}
+        want = [o["output_ids"] for o in eng.generate(prompt=texts, sampling_params=sp)]
+        assert [c[0] for c in tok.calls] == ["one"] * 3
+        tok.calls.clear()
+        eng.tokenizer_manager.server_args.enable_tokenizer_batch_encode = True
+        got = [o["output_ids"] for o in eng.generate(prompt=texts, sampling_params=sp)]
+        assert got == want and tok.calls == [("batch", 3)]
+        with pytest.raises(Exception, match="pre-tokenized"):
+            eng.generate(input_ids=[[5, 6, 7], [8, 9]], sampling_params=sp)
+    finally:
+        eng.shutdown()
