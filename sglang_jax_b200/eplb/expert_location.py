@@ -9,6 +9,10 @@ replicate the heaviest experts, then pack physical experts onto ranks greedily b
 
 from __future__ import annotations
 
+import csv
+import os
+import time
+
 import numpy as np
 import torch
 
@@ -118,11 +122,17 @@ class ExpertLocation:
         self.log2phy = torch.as_tensor(table, device=device)
         self.rep_count = torch.as_tensor([len(r) for r in reps], device=device)
 
+    # `--ep-dispatch-algorithm` (reference `expert_location.py:338-392`): `static` sends every token of a logical
+    # expert to its first physical slot, `dynamic` (the default here) deals the tokens over the replicas
+    dispatch_algorithm = "dynamic"
+
     def logical_to_physical(self, topk_ids: torch.Tensor) -> torch.Tensor:
         ids = topk_ids.long()
         if self.log2phy.device != ids.device:
             self.log2phy = self.log2phy.to(ids.device)
             self.rep_count = self.rep_count.to(ids.device)
+        if self.dispatch_algorithm == "static":
+            return self.log2phy[ids, 0].to(topk_ids.dtype)
         tok = torch.arange(ids.shape[0], device=ids.device).view(-1, 1)
         pick = tok % self.rep_count[ids]
         return self.log2phy[ids, pick].to(topk_ids.dtype)
@@ -172,6 +182,59 @@ class ExpertDistributionRecorder:
     def dump(self):
         if self.output_file:
             np.save(self.output_file, self.aggregate())
+
+
+class ExpertBalanceAnalyzer(ExpertDistributionRecorder):
+    """`--enable-expert-balance-debug`: the recorder's per-layer hit counts, cut into segments of
+    `--expert-balance-segment-counter` decode steps; at the end of a segment one CSV row per layer goes to
+    `--expert-balance-output-file` with the counts and, when the experts divide over the expert-parallel ranks, how far
+    the busiest rank is above the mean (reference `layers/routed_experts_capturer.py` `_ExpertBalanceAnalyzer`)."""
+
+    HEADER = ["timestamp", "segment_idx", "segment_counter", "segment_decode_steps", "layer", "num_experts", "topk",
+              "ep_size", "total_assignments", "max_over_mean_expert", "max_over_mean_device", "experts_count"]
+
+    def __init__(self, num_layers: int, num_experts: int, topk: int, ep_size: int, segment_counter: int = 100,
+                 output_file: str | None = None, device="cpu"):
+        super().__init__(num_layers, num_experts, buffer_size=1 << 30, output_file=None, device=device)
+        self.topk, self.ep_size = int(topk), int(ep_size)
+        self.segment_counter = max(int(segment_counter), 1)
+        self.csv_file = output_file
+        self.segment_idx = 0
+        self.decode_steps = 0
+        if output_file:
+            os.makedirs(os.path.dirname(os.path.abspath(output_file)), exist_ok=True)
+            if not os.path.exists(output_file) or os.path.getsize(output_file) == 0:
+                with open(output_file, "w", newline="") as f:
+                    csv.writer(f).writerow(self.HEADER)
+
+    def step(self, is_decode: bool = True):
+        self.forwards += 1
+        if not is_decode:
+            return
+        self.decode_steps += 1
+        if self.decode_steps >= self.segment_counter:
+            self.flush_segment()
+
+    def flush_segment(self):
+        counts = self.aggregate().copy()          # on CPU the array shares the tensor's memory
+        self.counts.zero_()
+        steps, self.decode_steps = self.decode_steps, 0
+        if self.csv_file and counts.sum() > 0:
+            now = time.strftime("%Y-%m-%dT%H:%M:%S")
+            E = counts.shape[1]
+            with open(self.csv_file, "a", newline="") as f:
+                w = csv.writer(f)
+                for layer, c in enumerate(counts):
+                    if c.sum() == 0:
+                        continue
+                    dev = ""
+                    if self.ep_size > 0 and E % self.ep_size == 0:
+                        per_dev = c.reshape(self.ep_size, -1).sum(1)
+                        dev = round(float(per_dev.max() / max(per_dev.mean(), 1e-9)), 4)
+                    w.writerow([now, self.segment_idx, self.segment_counter, steps, layer, E, self.topk, self.ep_size,
+                                int(c.sum()), round(float(c.max() / max(c.mean(), 1e-9)), 4), dev,
+                                " ".join(map(str, c.tolist()))])
+        self.segment_idx += 1
 
 
 def load_expert_load(path: str) -> np.ndarray:

@@ -51,6 +51,7 @@ class MoeRuntime:
     num_redundant: int = 0
     expert_load = None            # [layers, experts] hit counts that seed the placement, or None ("trivial")
     recorder = None               # eplb.ExpertDistributionRecorder
+    dispatch_algorithm: str = "dynamic"   # `--ep-dispatch-algorithm`: how tokens pick among an expert's replicas
     num_groups: int = 1           # expert groups of group-limited routing (`n_group`)
     num_nodes: int = 1            # nodes the expert-parallel ranks span: with groups, the placement keeps a group on a node
 
@@ -59,8 +60,9 @@ _RUNTIME = MoeRuntime()
 
 
 def configure_moe_runtime(num_redundant: int = 0, init_expert_location: str | None = "trivial", recorder=None,
-                          num_groups: int = 1, num_nodes: int = 1):
+                          num_groups: int = 1, num_nodes: int = 1, dispatch_algorithm: str | None = None):
     _RUNTIME.num_redundant = int(num_redundant or 0)
+    _RUNTIME.dispatch_algorithm = "static" if dispatch_algorithm == "static" else "dynamic"
     _RUNTIME.num_groups, _RUNTIME.num_nodes = max(int(num_groups or 1), 1), max(int(num_nodes or 1), 1)
     _RUNTIME.expert_load = None
     if init_expert_location and init_expert_location != "trivial":
@@ -95,6 +97,7 @@ class FusedMoE(nn.Module):
                                                                 num_nodes=_RUNTIME.num_nodes)
             else:
                 self.expert_location = ExpertLocation(num_experts, ep, _RUNTIME.num_redundant)
+            self.expert_location.dispatch_algorithm = _RUNTIME.dispatch_algorithm
             num_experts = self.expert_location.num_physical
         self.recorder = _RUNTIME.recorder
         self.num_experts = num_experts

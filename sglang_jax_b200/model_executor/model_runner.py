@@ -63,7 +63,15 @@ class ModelRunner:
         n_exp = int(getattr(model_config.hf_config, "num_experts", None)
                     or getattr(model_config.hf_config, "n_routed_experts", None)
                     or getattr(model_config.hf_config, "num_local_experts", None) or 0)
-        if getattr(server_args, "enable_expert_distribution_recorder", False) and n_exp and not is_draft_worker:
+        if getattr(server_args, "enable_expert_balance_debug", False) and n_exp and not is_draft_worker:
+            from ..eplb.expert_location import ExpertBalanceAnalyzer
+            cfg = model_config.hf_text_config
+            self.expert_recorder = ExpertBalanceAnalyzer(
+                model_config.num_hidden_layers, n_exp + int(getattr(server_args, "ep_num_redundant_experts", 0) or 0),
+                int(getattr(cfg, "num_experts_per_tok", None) or getattr(cfg, "top_k_experts", None) or 1),
+                st.ep.size, server_args.expert_balance_segment_counter, server_args.expert_balance_output_file,
+                device=self.device)
+        elif getattr(server_args, "enable_expert_distribution_recorder", False) and n_exp and not is_draft_worker:
             from ..eplb.expert_location import ExpertDistributionRecorder
             self.expert_recorder = ExpertDistributionRecorder(
                 model_config.num_hidden_layers, n_exp, server_args.expert_distribution_recorder_buffer_size,
@@ -71,7 +79,8 @@ class ModelRunner:
         configure_moe_runtime(getattr(server_args, "ep_num_redundant_experts", 0),
                               getattr(server_args, "init_expert_location", "trivial"), self.expert_recorder,
                               num_groups=getattr(model_config.hf_text_config, "n_group", 1) or 1,
-                              num_nodes=getattr(server_args, "nnodes", 1) or 1)
+                              num_nodes=getattr(server_args, "nnodes", 1) or 1,
+                              dispatch_algorithm=getattr(server_args, "ep_dispatch_algorithm", None))
         self.model = loader.load_model(model_config, self.device, self.quant_config)
         configure_moe_runtime()          # later models (a draft head) start from the defaults
         if not is_draft_worker:
@@ -284,7 +293,10 @@ class ModelRunner:
         """One step: returns `(logits_output, next_token_ids [B] int32 device tensor, forward_batch)`."""
         self.forward_ct += 1
         if self.expert_recorder is not None:
-            self.expert_recorder.step()
+            if hasattr(self.expert_recorder, "flush_segment"):      # balance debug counts decode steps only
+                self.expert_recorder.step(batch.forward_mode.is_decode())
+            else:
+                self.expert_recorder.step()
         if batch.forward_mode.is_idle():
             return None, torch.empty(0, dtype=torch.int32, device=self.device), None
         if getattr(batch, "recurrent_copies", None) and self.recurrent_pool is not None:

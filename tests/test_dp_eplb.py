@@ -157,6 +157,20 @@ def test_engine_returns_routed_experts_and_records_expert_load(tmp_path):
             assert np.array_equal(np.sort(got[: len(ids), layer], -1), want), layer
     load = np.load(dump)
     assert load.shape == (2, 8) and load.sum() >= 2 * 2 * sum(len(p) for p in prompts)
+    # --enable-expert-balance-debug through the engine: segments of two decode steps land in the CSV
+    import csv
+    bal = str(tmp_path / "balance.csv")
+    ps.reset_state()
+    eng = Engine(model_path=path, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                 max_total_tokens=4096, enable_single_process=True, enable_expert_balance_debug=True,
+                 expert_balance_segment_counter=2, expert_balance_output_file=bal, disable_radix_cache=True)
+    try:
+        eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 6, "temperature": 0, "ignore_eos": True})
+    finally:
+        eng.shutdown()
+    rows = list(csv.DictReader(open(bal)))
+    assert len(rows) >= 4 and {r["layer"] for r in rows} == {"0", "1"} and rows[0]["topk"] == "2"
+    assert all(int(r["total_assignments"]) > 0 and len(r["experts_count"].split()) == 8 for r in rows)
 
 
 def _ep_rank(rank, world, port, path, q, redundant, load_file, moe_backend="epmoe"):
@@ -252,3 +266,32 @@ def test_token_all_to_all_moe_matches_hf(tmp_path, world, redundant):
             if p.is_alive():
                 p.kill()
     assert outs == want
+
+
+def test_expert_balance_debug_writes_segments_and_static_dispatch(tmp_path):
+    """`--enable-expert-balance-debug`: one CSV row per layer and segment of decode steps with the hit counts and the
+    imbalance over experts / expert-parallel ranks; `--ep-dispatch-algorithm static` keeps a logical expert's tokens
+    on its first replica."""
+    import csv
+    from sglang_jax_b200.eplb.expert_location import ExpertBalanceAnalyzer
+    out = tmp_path / "bal" / "balance.csv"
+    a = ExpertBalanceAnalyzer(num_layers=2, num_experts=8, topk=2, ep_size=4, segment_counter=3, output_file=str(out))
+    ids = torch.tensor([[0, 1], [0, 2], [0, 3], [0, 7]])
+    for stepno in range(7):
+        a.record(0, ids)
+        if stepno % 2 == 0:
+            a.record(1, ids[:, :1] + 4)
+        a.step(is_decode=True)
+        a.step(is_decode=False)                 # prefill steps do not advance a segment
+    rows = list(csv.DictReader(open(out)))
+    assert len(rows) == 4 and [r["segment_idx"] for r in rows] == ["0", "0", "1", "1"]
+    first = rows[0]
+    assert first["layer"] == "0" and first["total_assignments"] == "24" and first["segment_decode_steps"] == "3"
+    assert first["experts_count"].split()[0] == "12" and float(first["max_over_mean_expert"]) == 4.0
+    assert float(first["max_over_mean_device"]) == pytest.approx(15 / 6, rel=1e-3)       # ranks hold experts (0,1), (2,3), ...
+    assert a.segment_idx == 2 and a.decode_steps == 1
+    loc = ExpertLocation(4, 2, 2, phy2log=np.array([0, 1, 0, 2, 3, 0]))
+    hot = torch.zeros(6, 1, dtype=torch.int32)
+    assert len(set(loc.logical_to_physical(hot).flatten().tolist())) == 3                # dealt over the replicas
+    loc.dispatch_algorithm = "static"
+    assert set(loc.logical_to_physical(hot).flatten().tolist()) == {0}
