@@ -11,6 +11,36 @@ from __future__ import annotations
 import torch
 
 
+def slot_bytes(num_layers: int, conv_dim: int, conv_kernel: int, num_heads: int, head_k_dim: int, head_v_dim: int,
+               conv_dtype=torch.bfloat16, state_dtype=torch.float32) -> int:
+    """Bytes one state slot takes over all linear-attention layers (what `RecurrentStatePool` allocates per slot)."""
+    conv = conv_dim * (conv_kernel - 1) * torch.empty((), dtype=conv_dtype).element_size()
+    rec = num_heads * head_k_dim * head_v_dim * torch.empty((), dtype=state_dtype).element_size()
+    return num_layers * (conv + rec)
+
+
+def plan_state_slots(request_slots: int, per_slot_bytes: int, available_bytes: int, max_state_size: int | None,
+                     snapshot_slots: int, memory_ratio: float, sharing: bool) -> tuple[int, int]:
+    """`(snapshot slots, bytes the pool will take)` (reference `model_runner_kv_cache_mixin.py`
+    `handle_recurrent_cache`, `_split_state_kv_budget`).  Priority: an explicit total (`--max-recurrent-state-size`,
+    request slots included); without prefix sharing no checkpoint slots at all; an explicit
+    `--recurrent-snapshot-slots >= 0`; else (`-1`) the share `ratio / (1 + ratio)` of the available memory, less the
+    request slots."""
+    if max_state_size is not None:
+        snap = max(int(max_state_size) - request_slots, 0)
+    elif not sharing:
+        snap = 0
+    elif snapshot_slots >= 0:
+        snap = int(snapshot_slots)
+    else:
+        if memory_ratio <= 0:
+            raise ValueError(f"recurrent_state_memory_ratio={memory_ratio} is invalid for a hybrid recurrent model; "
+                             f"set --recurrent-state-memory-ratio > 0")
+        total = int(available_bytes * memory_ratio / (1.0 + memory_ratio)) // max(per_slot_bytes, 1)
+        snap = max(total - request_slots, 0)
+    return snap, (request_slots + 1 + snap) * per_slot_bytes
+
+
 class RecurrentStatePool:
     def __init__(self, size: int, num_layers: int, conv_dim: int, conv_kernel: int, num_heads: int, head_k_dim: int,
                  head_v_dim: int, device: str = "cpu", conv_dtype=torch.bfloat16, state_dtype=torch.float32,

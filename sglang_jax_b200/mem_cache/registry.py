@@ -76,12 +76,15 @@ def default_radix_cache_factory(ctx: TreeCacheBuildContext) -> TreeCacheBuildRes
                         is_eagle=ctx.spec_algorithm in ("EAGLE", "EAGLE3"), kv_pool=kv)
     if sa.disable_radix_cache:
         return TreeCacheBuildResult(alloc, ChunkCache(p.req_to_token_pool, alloc, p.page_size))
-    if recurrent:
+    if recurrent or getattr(sa, "enable_unified_radix_tree", False):
+        # `--enable-unified-radix-tree` (reference `mem_cache/registry.py`): the unified tree for every model; without
+        # linear-attention layers it carries the FULL component only
         from .unified_radix_cache import UnifiedHiRadixCache, UnifiedRadixCache
-        snap = dict(num_request_slots=rp.size, num_snapshot_slots=rp.snapshot_slots,
+        snap = dict(num_request_slots=rp.size if rp is not None else 0,
+                    num_snapshot_slots=rp.snapshot_slots if rp is not None else 0,
                     enable_kv_cache_events=p.enable_kv_cache_events,
                     track_interval=getattr(sa, "recurrent_track_interval", None),
-                    commit_on_finish=bool(sa.disable_overlap_schedule))
+                    commit_on_finish=bool(sa.disable_overlap_schedule), recurrent=recurrent)
         if sa.hicache_storage != "disable" and kv is not None:
             # KV of the full-attention layers gets the host tier; checkpoints of the recurrent state stay on the device
             cache = UnifiedHiRadixCache(p.req_to_token_pool, alloc, p.page_size, kv, hicache_ratio=sa.hicache_ratio,

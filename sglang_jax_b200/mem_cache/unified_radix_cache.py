@@ -50,8 +50,11 @@ class _RecurrentSnapshots:
     """Checkpoints of the recurrent state on tree nodes; mixed into a radix tree class (see the module docstring)."""
 
     def _init_snapshots(self, page_size: int, num_request_slots: int, num_snapshot_slots: int,
-                        track_interval: int | None, commit_on_finish: bool):
-        self.components = (ComponentType.FULL, ComponentType.RECURRENT)
+                        track_interval: int | None, commit_on_finish: bool, recurrent: bool = True):
+        # `--enable-unified-radix-tree` selects this tree for models without linear-attention layers too: with the
+        # FULL component alone every hook below hands over to the tree underneath
+        self.components = (ComponentType.FULL, ComponentType.RECURRENT) if recurrent else (ComponentType.FULL,)
+        self.recurrent = recurrent
         # checkpoint the final state of a finished request from its own slot: only sound when no overlapped extra
         # decode step can have advanced that slot past the request's last cached token
         self.commit_on_finish = commit_on_finish
@@ -78,7 +81,7 @@ class _RecurrentSnapshots:
         self._load_stop: dict[int, TreeNode] = {}
 
     def supports_recurrent(self) -> bool:
-        return True
+        return self.recurrent
 
     def take_recurrent_copies(self) -> list[tuple[int, int]]:
         """(src slot, dst slot) state copies to run, in order, before the next forward."""
@@ -105,7 +108,7 @@ class _RecurrentSnapshots:
     # ---------------------------------------------------------------- match
     def match_prefix(self, key: RadixKey, req=None, **kw) -> MatchResult:
         res = super().match_prefix(key)
-        if self._raw_match:
+        if self._raw_match or not self.recurrent:
             return res                                    # re-pointing a running request at its own prefix
         root = self.root_node
         empty = MatchResult(np.empty(0, np.int32), root, root)
@@ -151,6 +154,8 @@ class _RecurrentSnapshots:
 
     # ---------------------------------------------------------------- request hooks
     def cache_finished_req(self, req, is_insert: bool = True, **kw):
+        if not self.recurrent:
+            return super().cache_finished_req(req, is_insert, **kw)
         track = self._pending_track.pop(req.rid, None)       # finished / aborted before its prefill was published
         if track is not None:
             self._free_snap.append(track[2])
@@ -176,6 +181,8 @@ class _RecurrentSnapshots:
         """After a prefill step.  Without a checkpoint inside the step the state exists only in the request's own
         slot and nothing is published.  With one (`on_extend_scheduled`), the page-aligned prefix goes into the
         tree like in a plain radix cache and the checkpoint is attached to the node that ends at it."""
+        if not self.recurrent:
+            return super().cache_unfinished_req(req, chunked, **kw)
         track = self._pending_track.pop(req.rid, None)
         if self.disable or track is None or not track[3]:
             if track is not None:
@@ -202,7 +209,7 @@ class _RecurrentSnapshots:
     def on_extend_scheduled(self, req, prefix_len: int, seq_len: int):
         """A prefill step covering tokens `[prefix_len, seq_len)` is about to run: if a page boundary falls inside
         it, reserve a snapshot slot and ask the workers to store the state at the last such boundary."""
-        if self.disable:
+        if self.disable or not self.recurrent:
             return
         old = self._pending_track.pop(req.rid, None)
         if old is not None:
@@ -269,8 +276,9 @@ class _RecurrentSnapshots:
 class UnifiedRadixCache(_RecurrentSnapshots, RadixCache):
     def __init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size: int = 1, disable: bool = False,
                  num_request_slots: int = 0, num_snapshot_slots: int = 0, enable_kv_cache_events: bool = False,
-                 track_interval: int | None = None, commit_on_finish: bool = True):
-        self._init_snapshots(page_size, num_request_slots, num_snapshot_slots, track_interval, commit_on_finish)
+                 track_interval: int | None = None, commit_on_finish: bool = True, recurrent: bool = True):
+        self._init_snapshots(page_size, num_request_slots, num_snapshot_slots, track_interval, commit_on_finish,
+                             recurrent)
         RadixCache.__init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size, disable,
                             enable_kv_cache_events)
 
@@ -282,8 +290,9 @@ class UnifiedHiRadixCache(_RecurrentSnapshots, HiRadixCache):
                  num_request_slots: int = 0, num_snapshot_slots: int = 0, track_interval: int | None = None,
                  commit_on_finish: bool = True, hicache_ratio: float = 2.0, write_policy: str = "write_through",
                  write_through_threshold: int = 1, host_pages: int | None = None, disable: bool = False,
-                 enable_kv_cache_events: bool = False):
-        self._init_snapshots(page_size, num_request_slots, num_snapshot_slots, track_interval, commit_on_finish)
+                 enable_kv_cache_events: bool = False, recurrent: bool = True):
+        self._init_snapshots(page_size, num_request_slots, num_snapshot_slots, track_interval, commit_on_finish,
+                             recurrent)
         HiRadixCache.__init__(self, req_to_token_pool, token_to_kv_pool_allocator, page_size, device_pool,
                               hicache_ratio, write_policy, write_through_threshold, host_pages, disable=disable,
                               enable_kv_cache_events=enable_kv_cache_events)

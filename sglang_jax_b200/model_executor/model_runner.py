@@ -173,6 +173,7 @@ class ModelRunner:
             rest = free_now - total * (1.0 - self.server_args.mem_fraction_static)
         else:
             rest = min(free_now * 0.25, 4 << 30)   # CPU runs are tests: stay small
+        rest -= self._plan_recurrent_pool(rest)
         n = int(rest // self.cell_size())
         if self.tp_size > 1:
             t = torch.tensor([n], dtype=torch.int64)
@@ -180,6 +181,24 @@ class ModelRunner:
             dist.all_reduce(t, op=dist.ReduceOp.MIN, group=ps.get_state().tp.cpu_group)
             n = int(t.item())
         return n
+
+    def _plan_recurrent_pool(self, available_bytes: float) -> int:
+        """Hybrid linear-attention models: decide the number of checkpoint slots of the recurrent state pool from
+        `--max-recurrent-state-size` / `--recurrent-snapshot-slots` / `--recurrent-state-memory-ratio` and return the
+        bytes the pool will take, which come out of the KV budget."""
+        spec = getattr(self.model, "recurrent_spec", None)
+        if not spec:
+            return 0
+        from ..mem_cache.recurrent_state_pool import plan_state_slots, slot_bytes
+        sa = self.server_args
+        reqs = (sa.max_running_requests or 256) + 8
+        per = slot_bytes(conv_dtype=self.dtype, **spec)
+        self._recurrent_snapshots, used = plan_state_slots(
+            reqs, per, int(max(available_bytes, 0)), sa.max_recurrent_state_size, int(sa.recurrent_snapshot_slots),
+            float(sa.recurrent_state_memory_ratio), not sa.disable_radix_cache)
+        logger.info("recurrent state pool: %d request + %d checkpoint slots of %.2f MB", reqs,
+                    self._recurrent_snapshots, per / 2 ** 20)
+        return used
 
     def _init_memory_pool(self, free_before, req_to_token_pool, token_to_kv_pool, max_total):
         sa, mc = self.server_args, self.model_config
@@ -211,7 +230,12 @@ class ModelRunner:
         if spec:
             from ..mem_cache.recurrent_state_pool import RecurrentStatePool
             # one state slot per request row (slot = row + 1)
-            snap = 0 if sa.disable_radix_cache else int(sa.recurrent_snapshot_slots)
+            snap = getattr(self, "_recurrent_snapshots", None)
+            if snap is None:         # the KV size was given from outside (draft worker, CI size): plan without a budget
+                from ..mem_cache.recurrent_state_pool import plan_state_slots, slot_bytes
+                snap, _ = plan_state_slots(req_to_token_pool.size, slot_bytes(conv_dtype=self.dtype, **spec), 0,
+                                           sa.max_recurrent_state_size, max(int(sa.recurrent_snapshot_slots), 0),
+                                           float(sa.recurrent_state_memory_ratio), not sa.disable_radix_cache)
             self.recurrent_pool = RecurrentStatePool(req_to_token_pool.size, device=str(self.device),
                                                      conv_dtype=self.dtype, snapshot_slots=snap, **spec)
         n_layers = getattr(self.model, "num_kv_layers", None) or mc.num_hidden_layers

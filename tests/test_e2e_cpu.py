@@ -79,19 +79,24 @@ def test_matches_hf_oracle_with_radix_cache(ckpt, oracle):
     dict(enable_mixed_chunk=True, chunked_prefill_size=64),
     dict(max_running_requests=3),
     dict(schedule_policy="lpm"),
+    dict(enable_unified_radix_tree=True),
+    dict(enable_unified_radix_tree=True, hicache_storage="host"),
 ])
 def test_outputs_invariant_to_scheduling_options(ckpt, oracle, kw):
     outs, _, _ = run_engine(ckpt, **kw)
     assert outs == oracle
 
 
-def test_prefix_cache_hits_are_reported(ckpt):
+@pytest.mark.parametrize("unified", [False, True])
+def test_prefix_cache_hits_are_reported(ckpt, unified):
     from sglang_jax_b200 import Engine
     from sglang_jax_b200.parallel import state as ps
     ps.reset_state()
     eng = Engine(model_path=ckpt, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
-                 max_total_tokens=8192, enable_single_process=True)
+                 max_total_tokens=8192, enable_single_process=True, enable_unified_radix_tree=unified)
     try:
+        # --enable-unified-radix-tree: the unified tree (FULL component alone for this model) shares prefixes alike
+        assert (type(eng.scheduler.tree_cache).__name__ == "UnifiedRadixCache") == unified
         reqs = workload()
         sp = {"max_new_tokens": 4, "temperature": 0.0, "ignore_eos": True}
         first = eng.generate(input_ids=reqs[0], sampling_params=sp)

@@ -844,6 +844,9 @@ def test_hybrid_recurrent_prefix_sharing_reuses_state_checkpoints(tmp_path):
     assert paged[0] == "UnifiedRadixCache"
     assert paged[1:4] == paged_plain[1:4] == plain[1:4]
     assert paged[4] == 40 and paged[5] == [40, 0] and paged[6] >= 1
+    # --max-recurrent-state-size counts request slots and checkpoint slots together
+    sized = run(max_recurrent_state_size=264 + 3, disable_overlap_schedule=True)     # 256 + 8 request rows, 3 checkpoints
+    assert sized[1:4] == plain[1:4] and sized[6] <= 3
     # with a host-memory KV tier the same tree logic runs over the host-tier radix tree
     hosted = run(hicache_storage="host", disable_overlap_schedule=True)
     assert hosted[0] == "UnifiedHiRadixCache"

@@ -450,3 +450,25 @@ def test_moe_parity_tool_on_a_tiny_checkpoint(tmp_path, capsys):
     assert moe_parity.main(common + ["--moe-weight-dtype", "float8_e4m3fn", "--deterministic-router"]) == 0
     q = json.loads(capsys.readouterr().out.splitlines()[0])
     assert 1e-5 < q["rel_fro"] < 0.1 and q["cosine"] > 0.99 and q["experts_hit"] == E
+
+
+def test_recurrent_state_pool_sizing_rules():
+    """`--max-recurrent-state-size` (total slots, request slots included) wins; without prefix sharing there are no
+    checkpoint slots; an explicit `--recurrent-snapshot-slots` is taken as is; `-1` derives the pool from the share
+    `ratio / (1 + ratio)` of the available memory."""
+    import pytest
+    import torch
+    from sglang_jax_b200.mem_cache.recurrent_state_pool import RecurrentStatePool, plan_state_slots, slot_bytes
+    spec = dict(num_layers=3, conv_dim=64, conv_kernel=4, num_heads=4, head_k_dim=8, head_v_dim=8)
+    per = slot_bytes(**spec)
+    pool = RecurrentStatePool(5, snapshot_slots=2, **spec)
+    assert pool.size_bytes() == (5 + 1 + 2) * per
+    assert plan_state_slots(16, per, 0, 40, 7, 0.9, True) == (24, (16 + 1 + 24) * per)
+    assert plan_state_slots(16, per, 0, 10, 7, 0.9, True)[0] == 0            # smaller than the request slots
+    assert plan_state_slots(16, per, 0, None, 7, 0.9, False)[0] == 0
+    assert plan_state_slots(16, per, 0, None, 7, 0.9, True)[0] == 7
+    avail = 1000 * per
+    snap, used = plan_state_slots(16, per, avail, None, -1, 1.0, True)       # half of the memory -> 500 slots
+    assert snap == 500 - 16 and used == (16 + 1 + snap) * per
+    with pytest.raises(ValueError):
+        plan_state_slots(16, per, avail, None, -1, 0.0, True)
