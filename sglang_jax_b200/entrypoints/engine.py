@@ -51,6 +51,15 @@ class Engine(EngineBase):
         # ranks are processes; in single-process mode, or with SGLB_DP_MODE=replicas, a set of independent
         # replicas behind a router stands in for the engine
         sa = kwargs.get("server_args")
+        pd = sa.pd_disaggregation if sa is not None else kwargs.get("pd_disaggregation", "")
+        mode = sa.disaggregation_mode if sa is not None else kwargs.get("disaggregation_mode", "null")
+        if pd and mode in (None, "null") and not kwargs.get("_replica"):
+            # `--pd-disaggregation`: prefill and decode engines of one node behind this one front door
+            from ..disaggregation.local_pd import LocalPDEngine
+            if sa is None:
+                kwargs.setdefault("log_level", "error")
+                sa = ServerArgs(**{k: v for k, v in kwargs.items() if k != "_replica"})
+            return LocalPDEngine(sa)
         dp = sa.dp_size if sa is not None else int(kwargs.get("dp_size", 1) or 1)
         single = sa.enable_single_process if sa is not None else bool(kwargs.get("enable_single_process", False))
         replicas = single or os.environ.get("SGLB_DP_MODE", "attention") == "replicas"

@@ -265,7 +265,8 @@ class ServerArgs:
             if self.speculative_draft_model_path is None:
                 self.speculative_draft_model_path = self.model_path
         if self.pd_disaggregation and self.disaggregation_mode == "null":
-            pass  # launcher-level flag; the router assigns modes per replica
+            # launcher-level flag: `disaggregation/local_pd.py` builds the prefill and decode engines from this one
+            assert self.page_size >= 16, "PD mode requires a page_size of at least 16"
         self.check_server_args()
 
     # ------------------------------------------------------------------

@@ -428,3 +428,46 @@ def test_embedded_bootstrap_server_and_decode_watchdog_flags(tmp_path, monkeypat
         decode.shutdown()
     assert not decode.scheduler.disagg_decode_watchdog._thread.is_alive()
     assert prefill.scheduler.disagg_bootstrap_server is None
+
+
+def test_in_node_pd_front_door_matches_single_engine(tmp_path):
+    """`--pd-disaggregation`: one `Engine(...)` call builds prefill and decode engines on slices of the node's
+    devices with an embedded registry; requests fan out to a prefill and a decode engine and the answers are those
+    of a monolithic engine (reference: the in-process P/D split of `pathways_pd.py` / `pathways_scheduler.py`)."""
+    from sglang_jax_b200.disaggregation.local_pd import LocalPDEngine
+    from sglang_jax_b200.entrypoints.engine import Engine
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import write_tiny_qwen3_checkpoint
+    ckpt = write_tiny_qwen3_checkpoint(str(tmp_path / "m"))
+    rng = np.random.RandomState(3)
+    prompts = [rng.randint(5, 1000, size=n).tolist() for n in (33, 70, 18, 51)]
+    sp = {"temperature": 0.0, "max_new_tokens": 6, "ignore_eos": True}
+    common = dict(model_path=ckpt, device="cpu", enable_single_process=True, page_size=16, skip_tokenizer_init=True,
+                  max_total_tokens=2048, dtype="float32", log_level="error")
+    ps.reset_state()
+    plain = Engine(**common)
+    try:
+        want = [o["output_ids"] for o in plain.generate(input_ids=prompts, sampling_params=sp)]
+    finally:
+        plain.shutdown()
+    ps.reset_state()
+    eng = Engine(**common, pd_disaggregation="local", pd_num_prefill=1, pd_num_decode=2,
+                 disaggregation_bootstrap_port=get_free_port(), chunked_prefill_size=32)
+    try:
+        assert isinstance(eng, LocalPDEngine) and len(eng.prefill) == 1 and len(eng.decode) == 2
+        assert [e.server_args.device_indexes for e in eng.engines()] == [[0], [1], [2]]
+        assert eng.prefill[0].server_args.disaggregation_mode == "prefill"
+        outs = eng.generate(input_ids=prompts, sampling_params=sp)
+        assert [o["output_ids"] for o in outs] == want
+        assert sorted(o["meta_info"]["pd_decode_engine"] for o in outs) == [0, 0, 1, 1]      # spread over both
+        one = eng.generate(input_ids=prompts[0], sampling_params=sp)
+        assert one["output_ids"] == want[0] and one["meta_info"]["bootstrap_room"] == 5
+        info = eng.get_server_info()
+        assert info["pd_routed"] == {"prefill": [5], "decode": [3, 2]} or sum(info["pd_routed"]["decode"]) == 5
+        time.sleep(0.2)
+        for e in eng.engines():
+            e.scheduler.check_memory()
+    finally:
+        eng.shutdown()
+    with pytest.raises(ValueError, match="needs 3 devices"):
+        Engine(**common, pd_disaggregation="local", pd_num_decode=2, device_indexes=[0, 1])
