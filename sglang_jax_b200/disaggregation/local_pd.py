@@ -59,6 +59,7 @@ class LocalPDEngine:
             s.disaggregation_engine_id = f"{mode}-{index}"
             s.device_indexes = list(slice_)
             s.dp_size = 1
+            s.enable_engine_loop_run_forever_daemon = True      # calls from several threads may overlap on an engine
             if mode == "prefill":
                 s.tp_size = tp_p
                 s.ep_size = int(sa.pd_prefill_ep_size) or (max(sa.ep_size * tp_p // tp_d, 1) if sa.ep_size > 1 else 1)
@@ -104,14 +105,14 @@ class LocalPDEngine:
         return p, d
 
     def _call(self, eng, lock, idx, prompts, ids, sps, rooms, kw):
-        """One batched `generate` on one engine (an engine's synchronous `generate` is not re-entrant)."""
+        """One batched `generate` on one engine (the engines run their event loop on a thread of their own, so calls
+        of concurrent `generate`s of this front door overlap)."""
         args = dict(sampling_params=[sps[i] for i in idx], bootstrap_room=[rooms[i] for i in idx], **kw)
         if ids is not None:
             args["input_ids"] = [ids[i] for i in idx]
         else:
             args["prompt"] = [prompts[i] for i in idx]
-        with lock:
-            return eng.generate(**args)
+        return eng.generate(**args)
 
     def generate(self, prompt=None, sampling_params=None, input_ids=None, **kw):
         single = isinstance(prompt, str) or (input_ids is not None and len(input_ids) > 0

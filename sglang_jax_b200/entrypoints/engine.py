@@ -88,11 +88,27 @@ class Engine(EngineBase):
         self._stop = threading.Event()
         self.scheduler = None
         self.loop = asyncio.new_event_loop()
+        self._loop_thread = None
+        if server_args.enable_engine_loop_run_forever_daemon:
+            # the loop turns on a daemon thread of its own: the synchronous entry points hand it coroutines, so
+            # `generate` can be called from several threads at once (reference `entrypoints/engine.py:133`)
+            self._loop_thread = threading.Thread(target=self._loop_forever, daemon=True, name="engine-loop")
+            self._loop_thread.start()
         if server_args.enable_single_process:
             self.tokenizer_manager, self.scheduler_info = _launch_threads(self, server_args)
         else:
             self.tokenizer_manager, self.scheduler_info = _launch_subprocesses(self, server_args)
         self.tokenizer_manager.max_req_input_len = self.scheduler_info.get("max_req_input_len")
+
+    def _loop_forever(self):
+        asyncio.set_event_loop(self.loop)
+        self.loop.run_forever()
+
+    def _run(self, coro):
+        """Drive one coroutine of the tokenizer manager to completion from synchronous code."""
+        if self._loop_thread is not None:
+            return asyncio.run_coroutine_threadsafe(coro, self.loop).result()
+        return self.loop.run_until_complete(coro)
 
     # ------------------------------------------------------------------ generation
     def _make_req(self, prompt, sampling_params, input_ids, return_logprob, logprob_start_len, top_logprobs_num,
@@ -116,11 +132,11 @@ class Engine(EngineBase):
             def sync_iter():
                 while True:
                     try:
-                        yield self.loop.run_until_complete(gen.__anext__())
+                        yield self._run(gen.__anext__())
                     except StopAsyncIteration:
                         break
             return sync_iter()
-        return self.loop.run_until_complete(gen.__anext__())
+        return self._run(gen.__anext__())
 
     async def async_generate(self, prompt=None, sampling_params=None, input_ids=None, return_logprob=False,
                              logprob_start_len=None, top_logprobs_num=None, token_ids_logprob=None, lora_path=None,
@@ -137,7 +153,7 @@ class Engine(EngineBase):
     def encode(self, prompt=None, input_ids=None, normalize: bool = True) -> dict | list[dict]:
         obj = EmbeddingReqInput(text=prompt, input_ids=input_ids, normalize=normalize)
         gen = self.tokenizer_manager.generate_request(obj, None)
-        return self.loop.run_until_complete(gen.__anext__())
+        return self._run(gen.__anext__())
 
     def rerank(self, query: str, documents: list[str]) -> list[dict]:
         """Cross-encoder style scoring through the embedding path: one (query, document) pair per row."""
@@ -147,7 +163,7 @@ class Engine(EngineBase):
         return sorted(scored, key=lambda x: -x["score"])
 
     def score(self, query=None, items=None, label_token_ids=None, apply_softmax=False, item_first=False):
-        return self.loop.run_until_complete(self.tokenizer_manager.score_request(
+        return self._run(self.tokenizer_manager.score_request(
             query, items, label_token_ids, apply_softmax, item_first))
 
     async def async_score(self, query=None, items=None, label_token_ids=None, apply_softmax=False, item_first=False):
@@ -155,52 +171,52 @@ class Engine(EngineBase):
 
     # ------------------------------------------------------------------ control
     def flush_cache(self):
-        return self.loop.run_until_complete(self.tokenizer_manager.flush_cache())
+        return self._run(self.tokenizer_manager.flush_cache())
 
     def load_lora_adapter(self, lora_name: str, lora_path: str, pinned: bool = False):
         from ..managers.io_struct import LoadLoRAAdapterReqInput
-        return self.loop.run_until_complete(self.tokenizer_manager.load_lora_adapter(
+        return self._run(self.tokenizer_manager.load_lora_adapter(
             LoadLoRAAdapterReqInput(lora_name=lora_name, lora_path=lora_path, pinned=pinned)))
 
     def unload_lora_adapter(self, lora_name: str):
         from ..managers.io_struct import UnloadLoRAAdapterReqInput
-        return self.loop.run_until_complete(self.tokenizer_manager.unload_lora_adapter(
+        return self._run(self.tokenizer_manager.unload_lora_adapter(
             UnloadLoRAAdapterReqInput(lora_name=lora_name)))
 
     def pause_generation(self, mode: str = "abort"):
-        return self.loop.run_until_complete(self.tokenizer_manager.pause_generation(PauseGenerationReqInput(mode=mode)))
+        return self._run(self.tokenizer_manager.pause_generation(PauseGenerationReqInput(mode=mode)))
 
     def continue_generation(self):
-        return self.loop.run_until_complete(self.tokenizer_manager.continue_generation(ContinueGenerationReqInput()))
+        return self._run(self.tokenizer_manager.continue_generation(ContinueGenerationReqInput()))
 
     def abort_request(self, rid: str = "", abort_all: bool = False):
         self.tokenizer_manager.abort_request(rid, abort_all)
 
     def start_profile(self, **kw):
-        return self.loop.run_until_complete(self.tokenizer_manager.start_profile(**kw))
+        return self._run(self.tokenizer_manager.start_profile(**kw))
 
     def stop_profile(self):
-        return self.loop.run_until_complete(self.tokenizer_manager.stop_profile())
+        return self._run(self.tokenizer_manager.stop_profile())
 
     def get_server_info(self) -> dict:
-        internal = self.loop.run_until_complete(self.tokenizer_manager.get_internal_state())
+        internal = self._run(self.tokenizer_manager.get_internal_state())
         from .. import __version__
         return {**dataclasses.asdict(self.server_args), **self.scheduler_info, "internal_states": internal,
                 "version": __version__}
 
     def get_load(self):
-        return self.loop.run_until_complete(self.tokenizer_manager.get_load())
+        return self._run(self.tokenizer_manager.get_load())
 
     def set_internal_state(self, **state):
-        return self.loop.run_until_complete(self.tokenizer_manager.set_internal_state(
+        return self._run(self.tokenizer_manager.set_internal_state(
             SetInternalStateReq(state_data=state)))
 
     def open_session(self, session_id: str | None = None) -> str:
-        return self.loop.run_until_complete(self.tokenizer_manager.open_session(
+        return self._run(self.tokenizer_manager.open_session(
             OpenSessionReqInput(session_id=session_id or "")))
 
     def close_session(self, session_id: str):
-        return self.loop.run_until_complete(self.tokenizer_manager.close_session(
+        return self._run(self.tokenizer_manager.close_session(
             CloseSessionReqInput(session_id=session_id)))
 
     def release_memory_occupation(self):
@@ -237,7 +253,22 @@ class Engine(EngineBase):
         # the tokenizer manager's receive loop is a task of this engine's event loop: cancel it and let the loop
         # run the cancellation, or the interpreter reports a destroyed pending task at exit
         loop = getattr(self, "loop", None)
-        if loop is not None and not loop.is_closed() and not loop.is_running():
+        if getattr(self, "_loop_thread", None) is not None and loop is not None and loop.is_running():
+            # run-forever mode: cancel the pending tasks on the loop's own thread, then stop it
+            async def _cancel_all():
+                tasks = [t for t in asyncio.all_tasks(loop) if t is not asyncio.current_task() and not t.done()]
+                for t in tasks:
+                    t.cancel()
+                await asyncio.gather(*tasks, return_exceptions=True)
+                await loop.shutdown_asyncgens()
+            try:
+                asyncio.run_coroutine_threadsafe(_cancel_all(), loop).result(timeout=5)
+            except Exception:
+                pass
+            loop.call_soon_threadsafe(loop.stop)
+            self._loop_thread.join(timeout=5)
+            self._loop_thread = None
+        elif loop is not None and not loop.is_closed() and not loop.is_running():
             try:
                 tasks = [t for t in asyncio.all_tasks(loop) if not t.done()]
                 for t in tasks:

@@ -462,8 +462,17 @@ def test_in_node_pd_front_door_matches_single_engine(tmp_path):
         assert sorted(o["meta_info"]["pd_decode_engine"] for o in outs) == [0, 0, 1, 1]      # spread over both
         one = eng.generate(input_ids=prompts[0], sampling_params=sp)
         assert one["output_ids"] == want[0] and one["meta_info"]["bootstrap_room"] == 5
+        # concurrent callers overlap on the same engines
+        res = {}
+        ts = [threading.Thread(target=lambda i=i: res.update({i: eng.generate(input_ids=prompts[i], sampling_params=sp)}))
+              for i in range(4)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout=120)
+        assert [res[i]["output_ids"] for i in range(4)] == want
         info = eng.get_server_info()
-        assert info["pd_routed"] == {"prefill": [5], "decode": [3, 2]} or sum(info["pd_routed"]["decode"]) == 5
+        assert info["pd_routed"]["prefill"] == [9] and sum(info["pd_routed"]["decode"]) == 9
         time.sleep(0.2)
         for e in eng.engines():
             e.scheduler.check_memory()

@@ -444,3 +444,34 @@ def test_tokenizer_batch_encode_tokenizes_a_batch_in_one_call(ckpt):
             eng.generate(input_ids=[[5, 6, 7], [8, 9]], sampling_params=sp)
     finally:
         eng.shutdown()
+
+
+def test_engine_loop_daemon_lets_threads_generate_concurrently(ckpt, oracle):
+    """`--enable-engine-loop-run-forever-daemon`: the engine's event loop turns on its own thread and the synchronous
+    `generate` only hands it coroutines, so several threads can call it at once (without the flag the loop belongs to
+    the calling thread and a second concurrent call is an error)."""
+    import threading
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.parallel import state as ps
+    ps.reset_state()
+    eng = Engine(model_path=ckpt, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                 max_total_tokens=8192, enable_single_process=True, enable_engine_loop_run_forever_daemon=True)
+    try:
+        reqs = workload()
+        sp = {"max_new_tokens": 32, "temperature": 0.0, "ignore_eos": True}
+        res = [None] * len(reqs)
+
+        def one(i):
+            res[i] = eng.generate(input_ids=reqs[i], sampling_params=sp)["output_ids"]
+
+        ts = [threading.Thread(target=one, args=(i,)) for i in range(len(reqs))]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout=300)
+        assert res == oracle
+        assert [c["output_ids"] for c in eng.generate(input_ids=reqs[0], sampling_params=sp, stream=True)][-1] == oracle[0]
+        assert eng.get_server_info()["internal_states"]
+    finally:
+        eng.shutdown()
+    assert eng._loop_thread is None
