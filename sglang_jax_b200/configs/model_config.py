@@ -74,7 +74,10 @@ class ModelConfig:
                  trust_remote_code: bool = False, revision: str | None = None, quantization: str | None = None,
                  model_override_args: str | dict | None = None, is_embedding: bool = False,
                  model_layer_nums: int | None = None, moe_backend: str = "epmoe", ep_size: int = 1,
-                 is_draft_model: bool = False):
+                 is_draft_model: bool = False, download_dir: str | None = None):
+        if isinstance(model_path, str) and not os.path.isdir(model_path) and hf_config is None:
+            from ..utils.hf_transformers_utils import resolve_model_path
+            model_path = resolve_model_path(model_path, download_dir, revision)
         self.model_path = model_path
         override = json.loads(model_override_args) if isinstance(model_override_args, str) else (model_override_args or {})
         self.hf_config = hf_config if hf_config is not None else load_hf_config(
@@ -146,8 +149,12 @@ class ModelConfig:
 
     @classmethod
     def from_server_args(cls, sa, model_path: str | None = None, **kw) -> "ModelConfig":
+        # a draft model has its own revision (`--speculative-draft-model-revision`)
+        revision = (getattr(sa, "speculative_draft_model_revision", None) or sa.revision) if kw.get("is_draft_model") \
+            else sa.revision
+        kw.setdefault("download_dir", getattr(sa, "download_dir", None))
         return cls(model_path or sa.model_path, dtype=sa.dtype, context_length=sa.context_length,
-                   trust_remote_code=sa.trust_remote_code, revision=sa.revision, quantization=sa.quantization,
+                   trust_remote_code=sa.trust_remote_code, revision=revision, quantization=sa.quantization,
                    model_override_args=sa.json_model_override_args, is_embedding=sa.is_embedding,
                    model_layer_nums=sa.model_layer_nums, moe_backend=sa.moe_backend, ep_size=sa.ep_size, **kw)
 

@@ -229,6 +229,11 @@ class TokenizerManager:
         sp.verify(self.model_config.vocab_size)
         self._validate_len(obj, len(input_ids), sp)
         lora_id = obj.lora_id
+        if self.lora_registry is not None and getattr(self.server_args, "enable_static_lora", False) \
+                and self.lora_registry._by_name:
+            # `--enable-static-lora`: the first loaded adapter serves every request, whatever the request names
+            # (reference `schedule_batch.py:2685`: all rows carry adapter "0")
+            obj.lora_path = next(iter(self.lora_registry._by_name))
         if obj.lora_path is not None and self.lora_registry is not None:
             lora_id = self.lora_registry.acquire(obj.lora_path)
         return TokenizedGenerateReqInput(

@@ -44,3 +44,19 @@ def get_context_length(config) -> int:
         if v is not None:
             return int(v)
     return 2048
+
+
+def resolve_model_path(model_path: str, download_dir: str | None = None, revision: str | None = None) -> str:
+    """A local directory is used as is; anything else is taken as a hub repository id and fetched once into
+    `download_dir` (`--download-dir`, default: the hub cache) at `revision` (reference `model_loader/loader.py`,
+    `configs/load_config.py` `download_dir`).  Only the files a server needs are fetched."""
+    import os
+    if model_path is None or os.path.isdir(model_path):
+        return model_path
+    try:
+        from huggingface_hub import snapshot_download
+    except ImportError as e:
+        raise FileNotFoundError(f"{model_path} is not a local directory and huggingface_hub is not installed") from e
+    return snapshot_download(model_path, cache_dir=download_dir, revision=revision,
+                             allow_patterns=["*.json", "*.safetensors", "*.model", "*.txt", "*.tiktoken", "*.jinja"])
+

@@ -93,6 +93,17 @@ def test_adapter_equals_merged_weights_and_mixed_batch(env):
     assert mixed == [want_a[0], want_b[1], want_base[2]]
 
 
+def test_static_lora_applies_the_first_adapter_to_every_request(env):
+    """`--enable-static-lora`: requests need not name an adapter; the first loaded one serves them all."""
+    want_a, _ = _run(env["a_merged"], PROMPTS)
+    got, _ = _run(env["base"], PROMPTS, lora_path=None, lora_paths=[f"a={env['a']}", f"b={env['b']}"],
+                  max_loras_per_batch=2, enable_static_lora=True)
+    assert got == want_a
+    got, _ = _run(env["base"], PROMPTS, lora_path=["b", None, "b"], lora_paths=[f"a={env['a']}", f"b={env['b']}"],
+                  max_loras_per_batch=2, enable_static_lora=True)
+    assert got == want_a
+
+
 def test_more_adapters_than_slots_are_served_in_turns(env):
     want_a, _ = _run(env["a_merged"], PROMPTS[:1])
     want_b, _ = _run(env["b_merged"], PROMPTS[1:2])

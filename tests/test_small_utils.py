@@ -472,3 +472,34 @@ def test_recurrent_state_pool_sizing_rules():
     assert snap == 500 - 16 and used == (16 + 1 + snap) * per
     with pytest.raises(ValueError):
         plan_state_slots(16, per, avail, None, -1, 0.0, True)
+
+
+def test_hub_ids_resolve_through_download_dir_and_draft_revision(tmp_path, monkeypatch):
+    """A model path that is not a directory is fetched into `--download-dir` at the configured revision; the draft
+    model of speculative decoding uses `--speculative-draft-model-revision`."""
+    import json
+    import sys
+    import types
+    from sglang_jax_b200.configs.model_config import ModelConfig
+    from sglang_jax_b200.server_args import ServerArgs
+    from sglang_jax_b200.utils.tiny_models import TINY_QWEN3
+    local = tmp_path / "snap"
+    local.mkdir()
+    (local / "config.json").write_text(json.dumps(dict(TINY_QWEN3)))
+    calls = []
+    fake = types.ModuleType("huggingface_hub")
+
+    def snapshot_download(repo_id, cache_dir=None, revision=None, allow_patterns=None, **kw):
+        calls.append((repo_id, cache_dir, revision))
+        return str(local)
+
+    fake.snapshot_download = snapshot_download
+    monkeypatch.setitem(sys.modules, "huggingface_hub", fake)
+    sa = ServerArgs(model_path="org/tiny-model", download_dir=str(tmp_path / "dl"), revision="r1",
+                    speculative_draft_model_revision="d7", skip_tokenizer_init=True, device="cpu")
+    mc = ModelConfig.from_server_args(sa)
+    assert mc.model_path == str(local) and calls[-1] == ("org/tiny-model", str(tmp_path / "dl"), "r1")
+    ModelConfig.from_server_args(sa, model_path="org/tiny-draft", is_draft_model=True)
+    assert calls[-1] == ("org/tiny-draft", str(tmp_path / "dl"), "d7")
+    ModelConfig.from_server_args(sa, model_path=str(local))             # a directory is used as is
+    assert len(calls) == 2
