@@ -29,6 +29,13 @@ from .forward_batch_info import ForwardBatch, _PinnedRing
 logger = logging.getLogger(__name__)
 
 
+def fused_token_window(server_args) -> tuple[int, int]:
+    """`(min, max)` rows of the forwards that take the fused NVLink residual dataflow: empty by default,
+    every forward with `--enable-sequence-parallel`; `SGLB_FUSED_MIN_TOKENS` / `SGLB_FUSED_MAX_TOKENS` override."""
+    default_max = "1000000" if getattr(server_args, "enable_sequence_parallel", False) else "-1"
+    return (int(os.environ.get("SGLB_FUSED_MIN_TOKENS", "0")), int(os.environ.get("SGLB_FUSED_MAX_TOKENS", default_max)))
+
+
 class ModelRunner:
     def __init__(self, model_config: ModelConfig, server_args, device: str | torch.device | None = None,
                  req_to_token_pool: ReqToTokenPool | None = None, is_draft_worker: bool = False,
@@ -114,8 +121,6 @@ class ModelRunner:
                 self.model, cap_tokens, self.device, int(getattr(hf, "num_experts_per_tok", None) or 8))
         from ..layers.fused_block import model_supports_fused_residual
         self.fused_residual_ok = model_supports_fused_residual(self.model)
-        # forwards with fewer tokens than this use the library all-reduce + add-RMSNorm kernel instead of the fused
-        # NVLink kernels (a per-forward choice: both dataflows are exact, they differ in latency)
         # Forwards of `fused_min_tokens <= T <= fused_max_tokens` rows take the fused NVLink dataflow (one launch for
         # GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather), the others GEMM + library all-reduce +
         # add-RMSNorm.  The default window is empty: measured end to end on Qwen3-32B with 128 running requests, the
@@ -124,8 +129,9 @@ class ModelRunner:
         # row-parallel product with its own small-M GEMM, which loses more than that against the measured per-shape
         # GEMM plan of the plain path.  `SGLB_FUSED_MAX_TOKENS=1000000` selects the fused dataflow for every forward,
         # `512` for decode-sized ones only.
-        self.fused_min_tokens = int(os.environ.get("SGLB_FUSED_MIN_TOKENS", "0"))
-        self.fused_max_tokens = int(os.environ.get("SGLB_FUSED_MAX_TOKENS", "-1"))
+        # `--enable-sequence-parallel` (reference `utils/parallel_utils.py`: reduce-scatter on the token dimension after a
+        # row-parallel layer instead of an all-reduce) is this dataflow: it selects it for every forward
+        self.fused_min_tokens, self.fused_max_tokens = fused_token_window(server_args)
         self.penalty_state = None          # sampling/penaltylib.PenaltyState, created when a request uses a penalty
         self.gemm_plan = None
         if self.device.type == "cuda" and os.environ.get("SGLB_GEMM_AUTOTUNE", "1") == "1" and not is_draft_worker:

@@ -503,3 +503,17 @@ def test_hub_ids_resolve_through_download_dir_and_draft_revision(tmp_path, monke
     assert calls[-1] == ("org/tiny-draft", str(tmp_path / "dl"), "d7")
     ModelConfig.from_server_args(sa, model_path=str(local))             # a directory is used as is
     assert len(calls) == 2
+
+
+def test_sequence_parallel_flag_selects_the_token_sharded_dataflow(monkeypatch):
+    """`--enable-sequence-parallel` turns the token-sharded (reduce-scatter) residual dataflow on for every forward;
+    the default window is empty; the environment variables override both."""
+    from types import SimpleNamespace
+    from sglang_jax_b200.model_executor.model_runner import fused_token_window
+    monkeypatch.delenv("SGLB_FUSED_MAX_TOKENS", raising=False)
+    monkeypatch.delenv("SGLB_FUSED_MIN_TOKENS", raising=False)
+    assert fused_token_window(SimpleNamespace(enable_sequence_parallel=False)) == (0, -1)
+    assert fused_token_window(SimpleNamespace(enable_sequence_parallel=True)) == (0, 1000000)
+    monkeypatch.setenv("SGLB_FUSED_MAX_TOKENS", "512")
+    monkeypatch.setenv("SGLB_FUSED_MIN_TOKENS", "64")
+    assert fused_token_window(SimpleNamespace(enable_sequence_parallel=True)) == (64, 512)
