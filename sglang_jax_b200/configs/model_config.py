@@ -74,7 +74,7 @@ class ModelConfig:
                  trust_remote_code: bool = False, revision: str | None = None, quantization: str | None = None,
                  model_override_args: str | dict | None = None, is_embedding: bool = False,
                  model_layer_nums: int | None = None, moe_backend: str = "epmoe", ep_size: int = 1,
-                 is_draft_model: bool = False, download_dir: str | None = None):
+                 is_draft_model: bool = False, download_dir: str | None = None, dtype_config=None):
         if isinstance(model_path, str) and not os.path.isdir(model_path) and hf_config is None:
             from ..utils.hf_transformers_utils import resolve_model_path
             model_path = resolve_model_path(model_path, download_dir, revision)
@@ -138,6 +138,10 @@ class ModelConfig:
                 self.dtype = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         else:
             self.dtype = _DTYPES[dtype]
+        # per-module parameter dtypes (`--dtype-config`: a JSON object, a file, or a ready `DtypeConfig`)
+        from .dtype_config import DtypeConfig
+        self.dtype_config = dtype_config if isinstance(dtype_config, DtypeConfig) or dtype_config is None \
+            else DtypeConfig.from_arg(dtype_config, self.dtype)
 
         eos = getattr(c, "eos_token_id", None)
         self.hf_eos_token_id = set(eos) if isinstance(eos, (list, tuple)) else ({eos} if eos is not None else set())
@@ -153,6 +157,8 @@ class ModelConfig:
         revision = (getattr(sa, "speculative_draft_model_revision", None) or sa.revision) if kw.get("is_draft_model") \
             else sa.revision
         kw.setdefault("download_dir", getattr(sa, "download_dir", None))
+        if not kw.get("is_draft_model"):
+            kw.setdefault("dtype_config", getattr(sa, "dtype_config", None))
         return cls(model_path or sa.model_path, dtype=sa.dtype, context_length=sa.context_length,
                    trust_remote_code=sa.trust_remote_code, revision=revision, quantization=sa.quantization,
                    model_override_args=sa.json_model_override_args, is_embedding=sa.is_embedding,

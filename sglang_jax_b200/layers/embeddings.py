@@ -41,6 +41,7 @@ class VocabParallelEmbedding(nn.Module):
         self.local = self.padded // self.tp_size
         self.vocab_start = self.tp_rank * self.local
         self.weight = nn.Parameter(torch.zeros(self.local, embedding_dim, dtype=dtype), requires_grad=False)
+        self.out_dtype = dtype            # the activations' dtype, also when `--dtype-config` stores the table wider
 
     def weight_loader(self, param, w, shard_id=None):
         lo = self.vocab_start
@@ -50,9 +51,11 @@ class VocabParallelEmbedding(nn.Module):
 
     def forward(self, ids):
         if self.tp_size == 1:
-            return ops.embedding(ids, self.weight)
+            out = ops.embedding(ids, self.weight)
+            return out if out.dtype == self.out_dtype else out.to(self.out_dtype)
         out = ops.embedding(ids, self.weight, self.vocab_start, masked=True)
-        return ps.all_reduce(out)
+        out = ps.all_reduce(out)
+        return out if out.dtype == self.out_dtype else out.to(self.out_dtype)
 
 
 class ParallelLMHead(nn.Module):

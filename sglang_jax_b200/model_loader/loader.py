@@ -123,6 +123,7 @@ class DefaultModelLoader:
         loaded = model.load_weights(it)
         check_all_loaded(model, loaded)
         _apply_dynamic_quantization(model, quant_config)
+        _apply_dtype_config(model, model_config)
         return model.eval()
 
     def _iterator(self, path):
@@ -148,7 +149,18 @@ class DummyModelLoader:
                 if _accepts_quant(cls) else cls(model_config.hf_config, dtype=model_config.dtype)
         initialize_dummy_weights(model, self.seed)
         _apply_dynamic_quantization(model, quant_config)
+        _apply_dtype_config(model, model_config)
         return model.eval()
+
+
+def _apply_dtype_config(model, model_config):
+    """`--dtype-config`: per-module parameter dtypes (`configs/dtype_config.py`)."""
+    cfg = getattr(model_config, "dtype_config", None)
+    if cfg is None:
+        return
+    from ..configs.dtype_config import apply_dtype_config
+    changed = apply_dtype_config(model, cfg)
+    logger.info("dtype config changed %d parameters, e.g. %s", len(changed), list(changed.items())[:3])
 
 
 def dequant_static_fp8(weights, block_size=None):

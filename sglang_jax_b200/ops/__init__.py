@@ -46,13 +46,13 @@ def _native():
 
 
 def rmsnorm(x, w, eps, gemma=False):
-    if use_native(x):
+    if use_native(x) and w.dtype == x.dtype:
         return _native().rmsnorm(x, w, eps, gemma)
     return reference.rmsnorm(x, w, eps, gemma)
 
 
 def fused_add_rmsnorm(x, residual, w, eps, gemma=False):
-    if use_native(x):
+    if use_native(x) and w.dtype == x.dtype:
         return _native().fused_add_rmsnorm(x, residual, w, eps, gemma)
     return reference.fused_add_rmsnorm(x, residual, w, eps, gemma)
 
@@ -64,6 +64,9 @@ def silu_and_mul(x):
 
 
 def linear(x, w, bias=None):
+    if w.dtype != x.dtype and w.is_floating_point() and w.dtype.itemsize >= 2:
+        # a per-module dtype (`--dtype-config`): compute in the weight's dtype, hand back the activations' dtype
+        return reference.linear(x.to(w.dtype), w, bias.to(w.dtype) if bias is not None else None).to(x.dtype)
     if use_native(x) and w.dtype == torch.bfloat16:
         from ..parallel import state as ps
         comm = ps.get_state().fused_comm

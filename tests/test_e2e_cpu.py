@@ -475,3 +475,44 @@ def test_engine_loop_daemon_lets_threads_generate_concurrently(ckpt, oracle):
     finally:
         eng.shutdown()
     assert eng._loop_thread is None
+
+
+def test_dtype_config_sets_per_module_parameter_dtypes(ckpt, oracle, tmp_path):
+    """`--dtype-config`: a nested mapping of module names to dtypes; missing keys fall back to the level's default,
+    fused projections follow their first member, and a layer with a different weight dtype computes in it."""
+    import json
+    import torch
+    from sglang_jax_b200 import Engine
+    from sglang_jax_b200.configs.dtype_config import DtypeConfig
+    from sglang_jax_b200.parallel import state as ps
+    cfg = {"model": {"norm": "bfloat16", "layers": {"input_layernorm": "bfloat16",
+                                                     "self_attn": {"q_proj": "bfloat16"},
+                                                     "mlp": {"down_proj": "bfloat16"}}}}
+    d = DtypeConfig(cfg, default_dtype="float32")
+    assert d.resolve("model.layers.3.self_attn.qkv_proj.weight") == torch.bfloat16           # via q_proj
+    assert d.resolve("model.layers.0.self_attn.o_proj.weight") == torch.float32
+    assert d.resolve("model.layers.1.mlp.gate_up_proj.weight") == torch.float32
+    assert d.resolve("lm_head.weight") == torch.float32 and d.resolve("model.norm.weight") == torch.bfloat16
+    assert d.get_config("model").get_config("layers").get_optional_dtype("softmax") is None
+    with pytest.raises(ValueError):
+        DtypeConfig({"model": "float7"})
+    path = tmp_path / "dt.json"
+    path.write_text(json.dumps(cfg))
+    ps.reset_state()
+    eng = Engine(model_path=ckpt, device="cpu", dtype="float32", page_size=16, skip_tokenizer_init=True,
+                 max_total_tokens=8192, enable_single_process=True, dtype_config=str(path))
+    try:
+        params = dict(eng.scheduler.tp_worker.model_runner.model.named_parameters())
+        assert params["model.layers.0.self_attn.qkv_proj.weight"].dtype == torch.bfloat16
+        assert params["model.layers.0.mlp.down_proj.weight"].dtype == torch.bfloat16
+        assert params["model.layers.0.input_layernorm.weight"].dtype == torch.bfloat16
+        assert params["model.layers.0.self_attn.o_proj.weight"].dtype == torch.float32
+        assert params["model.layers.0.post_attention_layernorm.weight"].dtype == torch.float32
+        outs = eng.generate(input_ids=workload(), sampling_params={"max_new_tokens": 8, "temperature": 0.0,
+                                                                   "ignore_eos": True})
+        got = [o["output_ids"] for o in outs]
+        # bf16 weights in a few layers: same length, first tokens mostly those of the all-fp32 model
+        assert all(len(g) == 8 for g in got)
+        assert sum(g[:2] == w[:2] for g, w in zip(got, oracle)) >= len(oracle) // 2
+    finally:
+        eng.shutdown()
