@@ -21,6 +21,9 @@ import secrets
 import threading
 from concurrent.futures import ThreadPoolExecutor
 
+from fastapi import FastAPI, Request          # module level: the route signatures are resolved from these names
+from fastapi.responses import JSONResponse
+
 logger = logging.getLogger(__name__)
 
 
@@ -185,3 +188,46 @@ class LocalPDEngine:
         if self.bootstrap is not None:
             self.bootstrap.stop()
             self.bootstrap = None
+
+
+def build_pd_app(engine: LocalPDEngine):
+    """HTTP surface of the in-node PD front door: `/generate` (non-streaming; text or token ids, one request or a
+    batch), `/health`, `/get_server_info`, `/flush_cache`, `/abort_request`.  The OpenAI routes are served by the
+    per-role servers behind `launch_router`; this app is what `launch_server --pd-disaggregation` exposes."""
+    import asyncio
+    app = FastAPI()
+
+    @app.get("/health")
+    async def health():
+        return JSONResponse({"status": "ok", "prefill": len(engine.prefill), "decode": len(engine.decode)})
+
+    @app.get("/get_server_info")
+    async def info():
+        return JSONResponse(engine.get_server_info())
+
+    @app.post("/flush_cache")
+    async def flush():
+        await asyncio.get_running_loop().run_in_executor(None, engine.flush_cache)
+        return JSONResponse({"success": True})
+
+    @app.post("/abort_request")
+    async def abort(request: Request):
+        body = await request.json()
+        engine.abort_request(body.get("rid", ""), bool(body.get("abort_all", False)))
+        return JSONResponse({"success": True})
+
+    @app.post("/generate")
+    async def generate(request: Request):
+        body = await request.json()
+        if body.get("stream"):
+            return JSONResponse({"error": "streaming is served by the per-role servers behind launch_router"}, 400)
+        kw = {k: body[k] for k in ("return_logprob", "logprob_start_len", "top_logprobs_num", "lora_path") if k in body}
+        try:
+            out = await asyncio.get_running_loop().run_in_executor(
+                None, lambda: engine.generate(prompt=body.get("text"), sampling_params=body.get("sampling_params"),
+                                              input_ids=body.get("input_ids"), **kw))
+        except ValueError as e:
+            return JSONResponse({"error": str(e)}, 400)
+        return JSONResponse(out)
+
+    return app

@@ -386,6 +386,15 @@ def launch(server_args: ServerArgs):
     if server_args.enable_metrics:
         set_prometheus_multiproc_dir()
     engine = Engine(server_args=server_args)
+    if server_args.pd_disaggregation and server_args.disaggregation_mode in (None, "null"):
+        # in-node PD launcher: the front door over the prefill and decode engines has its own small app
+        from ..disaggregation.local_pd import build_pd_app
+        try:
+            uvicorn.run(build_pd_app(engine), host=server_args.host, port=server_args.port,
+                        log_level=server_args.log_level_http or server_args.log_level, timeout_keep_alive=5)
+        finally:
+            engine.shutdown()
+        return
     if engine.tokenizer_manager is None:
         return   # follower node
     build_app_for_engine(engine)

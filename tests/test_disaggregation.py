@@ -473,6 +473,17 @@ def test_in_node_pd_front_door_matches_single_engine(tmp_path):
         assert [res[i]["output_ids"] for i in range(4)] == want
         info = eng.get_server_info()
         assert info["pd_routed"]["prefill"] == [9] and sum(info["pd_routed"]["decode"]) == 9
+        # the HTTP surface `launch_server --pd-disaggregation` exposes
+        from fastapi.testclient import TestClient
+        from sglang_jax_b200.disaggregation.local_pd import build_pd_app
+        with TestClient(build_pd_app(eng)) as client:
+            assert client.get("/health").json() == {"status": "ok", "prefill": 1, "decode": 2}
+            r = client.post("/generate", json={"input_ids": prompts[1], "sampling_params": sp})
+            assert r.status_code == 200 and r.json()["output_ids"] == want[1]
+            r = client.post("/generate", json={"input_ids": prompts[:2], "sampling_params": sp})
+            assert [o["output_ids"] for o in r.json()] == want[:2]
+            assert client.post("/generate", json={"input_ids": prompts[0], "stream": True}).status_code == 400
+            assert client.get("/get_server_info").json()["pd_routed"]["prefill"] == [12]
         time.sleep(0.2)
         for e in eng.engines():
             e.scheduler.check_memory()
