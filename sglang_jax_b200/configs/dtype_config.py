@@ -33,13 +33,13 @@ def _to_dtype(v) -> torch.dtype:
         return v
     if isinstance(v, str) and v.lower() in STR_TO_DTYPE:
         return STR_TO_DTYPE[v.lower()]
-    raise ValueError(f"Unknown dtype: {v}, provided value type: {type(v)}")
+    raise ValueError(f"dtype config: {v!r} ({type(v).__name__}) does not name a dtype; known: {sorted(STR_TO_DTYPE)}")
 
 
 class DtypeConfig:
     def __init__(self, config_dict: dict[str, Any] | None = None, default_dtype=None):
         if config_dict is None and default_dtype is None:
-            raise ValueError("At least one of config_dict and default_dtype must be provided.")
+            raise ValueError("a dtype config needs a mapping, a default dtype, or both")
         self.config_dict = self._parse(config_dict or {})
         self.default_dtype = self.config_dict["default"] if "default" in self.config_dict else \
             (_to_dtype(default_dtype) if default_dtype is not None else None)
