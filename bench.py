@@ -567,6 +567,11 @@ def main():
                    "cuda_graph": gr is not None, "fused_comm": st.fused_comm is not None,
                    "fused_tokens": ([runner.fused_min_tokens, runner.fused_max_tokens]
                                     if st.fused_comm is not None and runner is not None else None),
+                   "tp_dataflow": (None if world == 1 else
+                                   "fused NVLink kernels for forwards inside fused_tokens, NCCL all-reduce + add-RMSNorm "
+                                   "otherwise" if (st.fused_comm is not None and runner is not None
+                                                   and runner.fused_max_tokens >= runner.fused_min_tokens)
+                                   else "NCCL all-reduce + add-RMSNorm"),
                    "mixed_chunk": bool(sa.enable_mixed_chunk),
                    "overlap_schedule": sched.enable_overlap, "layers": cfg["num_hidden_layers"]},
         "clocks": clock_info, "e2e": e2e, "latency": latency,

@@ -2,6 +2,7 @@
 
 import base64
 import json
+import os
 
 import numpy as np
 import pytest
@@ -517,3 +518,30 @@ def test_sequence_parallel_flag_selects_the_token_sharded_dataflow(monkeypatch):
     monkeypatch.setenv("SGLB_FUSED_MAX_TOKENS", "512")
     monkeypatch.setenv("SGLB_FUSED_MIN_TOKENS", "64")
     assert fused_token_window(SimpleNamespace(enable_sequence_parallel=True)) == (64, 512)
+
+
+def test_bench_py_contract_on_cpu():
+    """`bench.py` end to end on CPU with a one-layer debug model: one JSON line with the keys the driver reads, the
+    per-kind step breakdown, and the `invalid` mark of a debug run."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.join(os.path.dirname(__file__), "..")
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--model", "qwen3-8b", "--layers", "1",
+                        "--concurrency", "4", "--input-len-min", "16", "--input-len-max", "32", "--output-len", "8",
+                        "--steps", "6", "--warmup", "3", "--no-latency", "--no-e2e"],
+                       stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+              "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "step_breakdown"):
+        assert k in d, k
+    assert d["steps"] == 6 and d["warmup"] == 3 and d["n_gpus"] == 1 and d["value"] > 0 and d["invalid"]
+    sb = d["step_breakdown"]
+    assert sb["decode"]["steps"] + sb["prefill"]["steps"] == 6 and d["config"]["tp_dataflow"] is None
+    ref = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"],
+                         stdout=subprocess.PIPE, text=True, timeout=300, cwd=root)
+    out = json.loads([l for l in ref.stdout.splitlines() if l.startswith("{")][-1])
+    assert ref.returncode == 0 and out["impl"] == "reference" and "unavailable" in out
