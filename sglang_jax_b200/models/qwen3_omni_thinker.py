@@ -25,6 +25,8 @@ def _text_config(config):
     tc.rope_parameters = None
     if not hasattr(tc, "tie_word_embeddings"):
         tc.tie_word_embeddings = bool(getattr(config, "tie_word_embeddings", False))
+    if getattr(tc, "num_experts", None) is None and getattr(tc, "num_local_experts", None):
+        tc.num_experts = tc.num_local_experts          # configs re-saved by recent `transformers` use this name
     return tc
 
 

@@ -883,6 +883,42 @@ def test_more_families_match_hf(tmp_path, which):
     assert _generate(path, PROMPTS, n=8) == _hf_generate(hf, PROMPTS, n=8)
 
 
+@pytest.mark.parametrize("which", ["qwen2_vl", "qwen3_vl_moe"])
+def test_vision_language_checkpoints_text_path_matches_hf(tmp_path, which):
+    """Text-only prompts through the language half of Qwen2-VL and Qwen3-VL-MoE checkpoints (nested text config,
+    weights under `model.language_model.`, vision tower present): three-stream rotary positions collapse to plain
+    ones, and the expert count may be stored as `num_local_experts`."""
+    import transformers
+    if which == "qwen2_vl":
+        text = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, rms_norm_eps=1e-6, vocab_size=512, max_position_embeddings=512,
+                    rope_theta=10000.0, tie_word_embeddings=False,
+                    rope_scaling={"type": "mrope", "mrope_section": [4, 6, 6]})
+        vis = dict(depth=1, embed_dim=32, hidden_size=128, num_heads=2, patch_size=4, spatial_merge_size=2,
+                   temporal_patch_size=2, in_channels=3, mlp_ratio=2)
+        cfg = transformers.Qwen2VLConfig(text_config=text, vision_config=vis, image_token_id=500, video_token_id=501,
+                                         vision_start_token_id=502, vision_end_token_id=503, tie_word_embeddings=False)
+        hf, arch = transformers.Qwen2VLForConditionalGeneration(cfg), "Qwen2VLForConditionalGeneration"
+    else:
+        text = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, vocab_size=512, max_position_embeddings=512,
+                    rope_theta=10000.0, tie_word_embeddings=False, num_experts=8, num_experts_per_tok=2,
+                    moe_intermediate_size=64, decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True,
+                    rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True})
+        vis = dict(depth=1, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, spatial_merge_size=2,
+                   temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=64, deepstack_visual_indexes=[0],
+                   in_channels=3)
+        cfg = transformers.Qwen3VLMoeConfig(text_config=text, vision_config=vis, image_token_id=500,
+                                            video_token_id=501, vision_start_token_id=502, vision_end_token_id=503,
+                                            tie_word_embeddings=False)
+        hf, arch = transformers.Qwen3VLMoeForConditionalGeneration(cfg), "Qwen3VLMoeForConditionalGeneration"
+    hf = _init(hf)
+    d = cfg.to_dict()
+    d.pop("architectures", None)
+    path = _save(str(tmp_path / which), hf, d, arch, which)
+    assert _generate(path, PROMPTS, n=8) == _hf_generate(hf, PROMPTS, n=8)
+
+
 def test_every_reference_architecture_name_resolves():
     """The `architectures[0]` strings the reference registers (`EntryClass` of each file under its `models/`)."""
     from sglang_jax_b200.models.registry import supported_architectures
