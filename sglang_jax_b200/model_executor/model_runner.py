@@ -120,7 +120,9 @@ class ModelRunner:
             self.routed_capturer = RoutedExpertsCapturer.attach(
                 self.model, cap_tokens, self.device, int(getattr(hf, "num_experts_per_tok", None) or 8))
         from ..layers.fused_block import model_supports_fused_residual
-        self.fused_residual_ok = model_supports_fused_residual(self.model)
+        # the fused kernels read norm weights and row-parallel weights in the model dtype: per-module dtypes rule them out
+        self.fused_residual_ok = model_supports_fused_residual(self.model) and \
+            getattr(model_config, "dtype_config", None) is None
         # Forwards of `fused_min_tokens <= T <= fused_max_tokens` rows take the fused NVLink dataflow (one launch for
         # GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather), the others GEMM + library all-reduce +
         # add-RMSNorm.  The default window is empty: measured end to end on Qwen3-32B with 128 running requests, the
