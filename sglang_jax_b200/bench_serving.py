@@ -6,7 +6,11 @@ trace replayed at its own timestamps), `image` (:1624, synthetic images attached
 (:1092, a local copy of the benchmark), a request rate / max-concurrency limiter, and the
 reference's metric definitions (`calculate_metrics` :1942-2117): TTFT = latency of the first streamed
 chunk, ITL = gaps between chunks, TPOT = (latency - TTFT) / (output_len - 1), throughput =
-tokens / duration, percentiles p50/p90/p99, peak output tok/s from 1-second buckets.
+tokens / duration, percentiles p50/p90/p99, peak output tok/s from 1-second buckets.  Request shaping and reporting
+options of the reference client: `--disable-stream`, `--disable-ignore-eos`, `--apply-chat-template`,
+`--prompt-suffix`, `--header`, `--served-model-name`, `--lora-name` with `--lora-request-distribution` /
+`--lora-zipf-alpha`, `--return-logprob`, `--return-routed-experts`, `--gsp-ordered`, `--gsp-send-routing-key`,
+`--warmup-requests`, `--tokenize-prompt`, `--print-requests`, `--output-details`, `--tag`.
 
     python -m sglang_jax_b200.bench_serving --backend sglang --dataset-name random \
         --random-input-len 1024 --random-output-len 512 --num-prompts 1024 --max-concurrency 64
@@ -48,14 +52,19 @@ def sample_random_requests(input_len: int, output_len: int, num_prompts: int, ra
 
 
 def sample_generated_shared_prefix_requests(num_groups: int, prompts_per_group: int, system_prompt_len: int,
-                                            question_len: int, output_len: int, vocab_size: int, seed: int = 1):
+                                            question_len: int, output_len: int, vocab_size: int, seed: int = 1,
+                                            ordered: bool = False):
+    """`(ids, output_len, None, group)`: the third slot is the departure offset of trace datasets (none here), the
+    fourth names the group whose system prompt the request shares (`--gsp-send-routing-key`); `ordered` keeps the
+    groups together instead of shuffling the requests."""
     rng = np.random.RandomState(seed)
     reqs = []
-    for _ in range(num_groups):
+    for g in range(num_groups):
         sys_ids = rng.randint(0, vocab_size, size=system_prompt_len).tolist()
         for _ in range(prompts_per_group):
-            reqs.append((sys_ids + rng.randint(0, vocab_size, size=question_len).tolist(), output_len))
-    random.Random(seed).shuffle(reqs)
+            reqs.append((sys_ids + rng.randint(0, vocab_size, size=question_len).tolist(), output_len, None, g))
+    if not ordered:
+        random.Random(seed).shuffle(reqs)
     return reqs
 
 
@@ -229,10 +238,31 @@ async def _request_openai_chat(session, url, messages, out_len, extra, model) ->
     return out
 
 
-async def _request_sglang_generate(session, url, ids, out_len, extra) -> RequestFuncOutput:
+async def _request_sglang_generate(session, url, ids, out_len, extra, opt=None) -> RequestFuncOutput:
+    opt = opt or {}
     out = RequestFuncOutput(prompt_len=len(ids) if not isinstance(ids, str) else max(len(ids.split()), 1))
-    body = {("text" if isinstance(ids, str) else "input_ids"): ids, "stream": True,
-            "sampling_params": {"temperature": 0.0, "max_new_tokens": out_len, "ignore_eos": True, **extra}}
+    body = {("text" if isinstance(ids, str) else "input_ids"): ids, "stream": not opt.get("disable_stream"),
+            "sampling_params": {"temperature": 0.0, "max_new_tokens": out_len,
+                                "ignore_eos": not opt.get("disable_ignore_eos"), **extra}}
+    for k in ("lora_path", "return_logprob", "return_routed_experts", "routing_key"):
+        if opt.get(k) is not None:
+            body[k] = opt[k]
+    if opt.get("disable_stream"):
+        out.start = st = time.perf_counter()
+        try:
+            async with session.post(url + "/generate", json=body) as resp:
+                if resp.status != 200:
+                    out.error = f"HTTP {resp.status}: {await resp.text()}"
+                    return out
+                d = await resp.json()
+            out.latency = out.ttft = time.perf_counter() - st
+            out.output_len = d["meta_info"]["completion_tokens"]
+            out.prompt_len = d["meta_info"].get("prompt_tokens", out.prompt_len)
+            out.chunk_times.append(time.perf_counter())
+            out.success = out.output_len > 0
+        except Exception as e:
+            out.error = repr(e)
+        return out
     out.start = st = time.perf_counter()
     last = st
     n_tok = 0
@@ -349,46 +379,80 @@ async def benchmark(args, reqs) -> dict:
     sem = asyncio.Semaphore(args.max_concurrency) if args.max_concurrency else None
     timeout = aiohttp.ClientTimeout(total=6 * 3600)
     conn = aiohttp.TCPConnector(limit=0)
-    async with aiohttp.ClientSession(timeout=timeout, connector=conn) as session:
+    headers = dict(h.split("=", 1) for h in (args.header or []))
+    async with aiohttp.ClientSession(timeout=timeout, connector=conn, headers=headers or None) as session:
         if args.flush_cache:
             async with session.post(url + "/flush_cache"):
                 pass
 
-        async def one(ids, out_len):
+        model = args.served_model_name or args.model or "default"
+        lora_rng = np.random.RandomState(args.seed)
+
+        def pick_lora(i: int):
+            """`--lora-name a b c` with `--lora-request-distribution`: uniform draws, distinct = round robin, skewed =
+            Zipf over the list (`--lora-zipf-alpha`)."""
+            names = args.lora_name or []
+            if not names:
+                return None
+            if args.lora_request_distribution == "distinct":
+                return names[i % len(names)]
+            if args.lora_request_distribution == "skewed":
+                w = 1.0 / np.arange(1, len(names) + 1) ** args.lora_zipf_alpha
+                return names[int(lora_rng.choice(len(names), p=w / w.sum()))]
+            return names[int(lora_rng.randint(len(names)))]
+
+        async def one(ids, out_len, index=0, routing_key=None):
+            opt = {"disable_stream": args.disable_stream, "disable_ignore_eos": args.disable_ignore_eos,
+                   "lora_path": pick_lora(index), "return_logprob": True if args.return_logprob else None,
+                   "return_routed_experts": True if args.return_routed_experts else None,
+                   "routing_key": routing_key if args.gsp_send_routing_key else None}
+            if isinstance(ids, str) and args.prompt_suffix:
+                ids = ids + args.prompt_suffix
+            if args.print_requests:
+                print(json.dumps({"index": index, "prompt": ids if isinstance(ids, str) else f"<{len(ids)} items>",
+                                  "output_len": out_len, "lora": opt["lora_path"]}))
+
             async def call():
                 if isinstance(ids, list) and ids and isinstance(ids[0], dict):       # chat messages (image datasets)
-                    return await _request_openai_chat(session, url, ids, out_len, extra, args.model or "default")
+                    return await _request_openai_chat(session, url, ids, out_len, extra, model)
                 if args.backend == "sglang":
-                    return await _request_sglang_generate(session, url, ids, out_len, extra)
-                if args.backend == "sglang-oai-chat":
+                    return await _request_sglang_generate(session, url, ids, out_len, extra, opt)
+                if args.backend == "sglang-oai-chat" or (args.apply_chat_template and isinstance(ids, str)):
                     msgs = [{"role": "user", "content": ids if isinstance(ids, str) else " ".join(map(str, ids))}]
-                    return await _request_openai_chat(session, url, msgs, out_len, extra, args.model or "default")
-                return await _request_openai_completions(session, url, ids, out_len, extra, args.model or "default")
+                    return await _request_openai_chat(session, url, msgs, out_len, extra, model)
+                return await _request_openai_completions(session, url, ids, out_len, extra, model)
             if sem is None:
                 return await call()
             async with sem:
                 return await call()
 
+        for w in range(min(args.warmup_requests, len(reqs))):      # untimed, one at a time
+            await one(reqs[w][0], min(reqs[w][1], 16), w)
         if args.profile:
             async with session.post(url + "/start_profile", json={"num_steps": args.profile_num_steps}):
                 pass
         t0 = time.perf_counter()
         tasks = []
-        for req in reqs:
+        for i, req in enumerate(reqs):
             ids, out_len = req[0], req[1]
-            if len(req) > 2:
+            if len(req) > 2 and req[2] is not None:
                 # trace replay: the request leaves at its recorded offset (scaled by --mooncake-slowdown-factor)
                 wait = req[2] * args.mooncake_slowdown_factor - (time.perf_counter() - t0)
                 if wait > 0:
                     await asyncio.sleep(wait)
-            tasks.append(asyncio.create_task(one(ids, out_len)))
-            if len(req) == 2 and args.request_rate != float("inf"):
+            tasks.append(asyncio.create_task(one(ids, out_len, i, f"group-{req[3]}" if len(req) > 3 else None)))
+            if (len(req) == 2 or req[2] is None) and args.request_rate != float("inf"):
                 await asyncio.sleep(np.random.exponential(1.0 / args.request_rate))
         outputs = await asyncio.gather(*tasks)
         duration = time.perf_counter() - t0
     m = calculate_metrics(outputs, duration)
     m.update(backend=args.backend, dataset_name=args.dataset_name, request_rate=args.request_rate,
              max_concurrency=args.max_concurrency)
+    if args.tag:
+        m["tag"] = args.tag
+    if args.output_details:
+        m["details"] = [{"prompt_len": o.prompt_len, "output_len": o.output_len, "ttft": o.ttft, "latency": o.latency,
+                         "itl": o.itl, "error": o.error} for o in outputs]
     errs = [o.error for o in outputs if not o.success][:3]
     if errs:
         m["errors"] = errs
@@ -418,7 +482,8 @@ def run_benchmark(args) -> dict:
     elif args.dataset_name == "generated-shared-prefix":
         reqs = sample_generated_shared_prefix_requests(args.gsp_num_groups, args.gsp_prompts_per_group,
                                                        args.gsp_system_prompt_len, args.gsp_question_len,
-                                                       args.gsp_output_len, args.vocab_size, args.seed)
+                                                       args.gsp_output_len, args.vocab_size, args.seed,
+                                                       args.gsp_ordered)
     elif args.dataset_name in ("sharegpt", "custom", "mooncake", "mmmu"):
         if not args.dataset_path:
             raise SystemExit(f"dataset {args.dataset_name} reads a local file (there is no network to fetch it): "
@@ -440,6 +505,13 @@ def run_benchmark(args) -> dict:
                                      args.random_input_len, args.random_output_len, args.seed)
     else:
         raise SystemExit(f"unknown dataset {args.dataset_name}")
+    if args.tokenize_prompt:
+        # send token ids instead of text (needs --tokenizer): the server's tokenizer is left out of the measurement
+        if not args.tokenizer:
+            raise SystemExit("--tokenize-prompt needs --tokenizer")
+        from transformers import AutoTokenizer
+        tok = AutoTokenizer.from_pretrained(args.tokenizer)
+        reqs = [((tok.encode(r[0]) if isinstance(r[0], str) else r[0]), *r[1:]) for r in reqs]
     m = asyncio.run(benchmark(args, reqs))
     print_metrics(m)
     if args.output_file:
@@ -478,6 +550,25 @@ def build_parser():
     p.add_argument("--gsp-question-len", type=int, default=128)
     p.add_argument("--gsp-output-len", type=int, default=256)
     p.add_argument("--seed", type=int, default=1)
+    p.add_argument("--disable-stream", action="store_true", help="non-streaming requests (TTFT equals the latency)")
+    p.add_argument("--disable-ignore-eos", action="store_true")
+    p.add_argument("--apply-chat-template", action="store_true", help="text prompts go through the chat route")
+    p.add_argument("--prompt-suffix", default="", help="appended to every text prompt")
+    p.add_argument("--header", nargs="*", default=None, help="extra HTTP headers, KEY=VALUE")
+    p.add_argument("--served-model-name", default=None)
+    p.add_argument("--lora-name", nargs="*", default=None, help="adapters the requests are spread over")
+    p.add_argument("--lora-request-distribution", default="uniform", choices=["uniform", "distinct", "skewed"])
+    p.add_argument("--lora-zipf-alpha", type=float, default=1.5)
+    p.add_argument("--return-logprob", action="store_true")
+    p.add_argument("--return-routed-experts", action="store_true")
+    p.add_argument("--gsp-ordered", action="store_true", help="keep the groups together instead of shuffling")
+    p.add_argument("--gsp-send-routing-key", action="store_true",
+                   help="generated-shared-prefix: requests of one group carry the group's routing key")
+    p.add_argument("--warmup-requests", type=int, default=0)
+    p.add_argument("--tokenize-prompt", action="store_true")
+    p.add_argument("--print-requests", action="store_true")
+    p.add_argument("--output-details", action="store_true", help="per-request records in the output file")
+    p.add_argument("--tag", default=None, help="label copied into the result record")
     p.add_argument("--extra-request-body", default=None)
     p.add_argument("--output-file", default=None)
     p.add_argument("--flush-cache", action="store_true")

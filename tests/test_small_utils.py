@@ -545,3 +545,73 @@ def test_bench_py_contract_on_cpu():
                          stdout=subprocess.PIPE, text=True, timeout=300, cwd=root)
     out = json.loads([l for l in ref.stdout.splitlines() if l.startswith("{")][-1])
     assert ref.returncode == 0 and out["impl"] == "reference" and "unavailable" in out
+
+
+def test_bench_serving_client_options_against_a_fake_server(tmp_path):
+    """The serving benchmark client against a recording server: non-streaming requests, adapters spread over the
+    requests, routing keys of shared-prefix groups, extra headers, warm-up requests, tags and per-request details."""
+    import asyncio
+    import json
+    import threading
+    from aiohttp import web
+    from sglang_jax_b200 import bench_serving as bs
+    from sglang_jax_b200.utils.common import get_free_port
+    seen = []
+
+    async def generate(request):
+        body = await request.json()
+        seen.append((body, request.headers.get("X-Test")))
+        n = body["sampling_params"]["max_new_tokens"]
+        meta = {"completion_tokens": n, "prompt_tokens": len(body.get("input_ids") or [])}
+        if body.get("stream"):
+            resp = web.StreamResponse(headers={"Content-Type": "text/event-stream"})
+            await resp.prepare(request)
+            for i in range(1, n + 1):
+                await resp.write(("data: " + json.dumps({"meta_info": dict(meta, completion_tokens=i)}) + "\n\n").encode())
+            await resp.write(b"data: [DONE]\n\n")
+            return resp
+        return web.json_response({"meta_info": meta})
+
+    port = get_free_port()
+    loop = asyncio.new_event_loop()
+    app = web.Application()
+    app.router.add_post("/generate", generate)
+    runner = web.AppRunner(app)
+
+    def serve():
+        asyncio.set_event_loop(loop)
+        loop.run_until_complete(runner.setup())
+        loop.run_until_complete(web.TCPSite(runner, "127.0.0.1", port).start())
+        loop.run_forever()
+
+    t = threading.Thread(target=serve, daemon=True)
+    t.start()
+    import time
+    time.sleep(0.5)
+    out = tmp_path / "res.jsonl"
+    try:
+        args = bs.build_parser().parse_args([
+            "--port", str(port), "--dataset-name", "generated-shared-prefix", "--gsp-num-groups", "2",
+            "--gsp-prompts-per-group", "3", "--gsp-system-prompt-len", "8", "--gsp-question-len", "4",
+            "--gsp-output-len", "5", "--gsp-ordered", "--gsp-send-routing-key", "--disable-stream",
+            "--lora-name", "a", "b", "--lora-request-distribution", "distinct", "--header", "X-Test=yes",
+            "--warmup-requests", "1", "--tag", "run-7", "--output-details", "--output-file", str(out),
+            "--return-logprob", "--disable-ignore-eos"])
+        m = bs.run_benchmark(args)
+        assert m["completed"] == 6 and m["failed"] == 0 and m["tag"] == "run-7" and len(m["details"]) == 6
+        timed = seen[1:]                                             # the first request is the warm-up
+        assert len(seen) == 7 and all(h == "yes" for _, h in seen)
+        assert [b["lora_path"] for b, _ in timed] == ["a", "b", "a", "b", "a", "b"]
+        assert [b["routing_key"] for b, _ in timed] == ["group-0"] * 3 + ["group-1"] * 3
+        assert all(b["stream"] is False and b["return_logprob"] is True for b, _ in timed)
+        assert all(b["sampling_params"]["ignore_eos"] is False for b, _ in timed)
+        assert json.loads(out.read_text().splitlines()[-1])["tag"] == "run-7"
+        # the streaming path still measures inter-token times
+        seen.clear()
+        args = bs.build_parser().parse_args(["--port", str(port), "--dataset-name", "random", "--num-prompts", "3",
+                                             "--random-input-len", "6", "--random-output-len", "4"])
+        m = bs.run_benchmark(args)
+        assert m["completed"] == 3 and m["total_output_tokens"] == 12 and all(b["stream"] for b, _ in seen)
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+        t.join(timeout=5)
