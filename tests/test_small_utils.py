@@ -615,3 +615,26 @@ def test_bench_serving_client_options_against_a_fake_server(tmp_path):
     finally:
         loop.call_soon_threadsafe(loop.stop)
         t.join(timeout=5)
+
+
+def test_offline_throughput_bench_on_a_tiny_model(tmp_path):
+    """`bench_offline_throughput` through the in-process engine: random and shared-prefix datasets, result file."""
+    import json
+    from sglang_jax_b200 import bench_offline_throughput as bo
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import write_tiny_qwen3_checkpoint
+    ckpt = write_tiny_qwen3_checkpoint(str(tmp_path / "m"))
+    out = tmp_path / "r.jsonl"
+    common = ["--model-path", ckpt, "--device", "cpu", "--dtype", "float32", "--skip-tokenizer-init",
+              "--enable-single-process", "--page-size", "16", "--max-total-tokens", "4096", "--log-level", "error"]
+    ps.reset_state()
+    r = bo.main(common + ["--num-prompts", "5", "--random-input-len", "24", "--random-output-len", "6",
+                          "--result-filename", str(out)])
+    assert r["successful_requests"] == 5 and r["total_output_tokens"] == 30 and r["output_throughput"] > 0
+    ps.reset_state()
+    r = bo.main(common + ["--dataset-name", "generated-shared-prefix", "--gsp-num-groups", "2",
+                          "--gsp-prompts-per-group", "2", "--gsp-system-prompt-len", "32", "--gsp-question-len", "8",
+                          "--gsp-output-len", "4", "--skip-warmup", "--result-filename", str(out)])
+    assert r["successful_requests"] == 4 and r["total_input_tokens"] == 4 * 40
+    recs = [json.loads(l) for l in out.read_text().splitlines()]
+    assert [x["dataset_name"] for x in recs] == ["random", "generated-shared-prefix"]
