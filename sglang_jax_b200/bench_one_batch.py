@@ -16,7 +16,8 @@ import torch
 from .server_args import ServerArgs
 
 
-def run_one_batch(server_args: ServerArgs, batch_size: int, input_len: int, output_len: int) -> dict:
+def run_one_batch(server_args: ServerArgs, batch_size: int, input_len: int, output_len: int,
+                  log_decode_step: int = 0) -> dict:
     from .configs.model_config import ModelConfig
     from .managers.schedule_batch import ForwardMode, ModelWorkerBatch, ModelWorkerSamplingInfo
     from .model_executor.model_runner import ModelRunner
@@ -70,6 +71,8 @@ def run_one_batch(server_args: ServerArgs, batch_size: int, input_len: int, outp
         _, tok, _ = runner.forward(db)
         tok_np = tok.cpu().numpy()
         decode.append(time.perf_counter() - t0)
+        if log_decode_step and (step + 1) % log_decode_step == 0:
+            print(f"decode step {step + 1}: {decode[-1] * 1e3:.2f} ms, {B / decode[-1]:.1f} tok/s", flush=True)
     med = float(np.median(decode)) if decode else 0.0
     return {"batch_size": B, "input_len": input_len, "output_len": output_len, "prefill_latency_s": prefill_s,
             "prefill_throughput": B * input_len / prefill_s, "median_decode_latency_s": med,
@@ -77,15 +80,81 @@ def run_one_batch(server_args: ServerArgs, batch_size: int, input_len: int, outp
             "total_latency_s": prefill_s + sum(decode)}
 
 
-if __name__ == "__main__":
+def correctness_test(server_args: ServerArgs, cut_len: int = 4, output_len: int = 8, prompts=None) -> dict:
+    """`--correctness-test` (reference `bench_one_batch.py` `correctness_test`): every prompt is generated twice,
+    prefilled in one piece and prefilled as `cut_len` tokens followed by the rest (the second part extends a cached
+    prefix); both must give the same greedy continuation, which is printed."""
+    from .entrypoints.engine import Engine
+    from .parallel import state as ps
+    prompts = prompts or [list(range(11, 11 + 3 * cut_len)), list(range(40, 40 + 2 * cut_len + 1)),
+                          [7, 3, 9] * (cut_len + 1)]
+    sp = {"temperature": 0.0, "max_new_tokens": output_len, "ignore_eos": True}
+    P = server_args.page_size
+    cut = max(cut_len // P, 1) * P                      # a cached prefix is whole pages
+    outs = {}
+    for name in ("whole", "split"):
+        ps.reset_state()
+        eng = Engine(server_args=server_args)
+        try:
+            if name == "split":
+                eng.generate(input_ids=[p[:cut] for p in prompts if len(p) > cut],
+                             sampling_params={**sp, "max_new_tokens": 1})
+            res = eng.generate(input_ids=prompts, sampling_params=sp)
+            outs[name] = [o["output_ids"] for o in res]
+            outs[name + "_cached"] = [o["meta_info"].get("cached_tokens", 0) for o in res]
+        finally:
+            eng.shutdown()
+    for i, (a, b) in enumerate(zip(outs["whole"], outs["split"])):
+        print(f"prompt {i}: whole {a}\n          split {b} (cached {outs['split_cached'][i]})")
+    ok = outs["whole"] == outs["split"]
+    print("correctness test", "passed" if ok else "FAILED")
+    return {"passed": ok, **outs}
+
+
+def main(argv=None) -> list[dict]:
     p = argparse.ArgumentParser()
     ServerArgs.add_cli_args(p)
     p.add_argument("--batch-size", type=int, nargs="+", default=[1])
     p.add_argument("--input-len", type=int, nargs="+", default=[1024])
     p.add_argument("--output-len", type=int, nargs="+", default=[16])
-    ns = p.parse_args()
+    p.add_argument("--run-name", default="default")
+    p.add_argument("--result-filename", default=None, help="append one JSON line per configuration")
+    p.add_argument("--log-decode-step", type=int, default=0, help="print the latency of every n-th decode step")
+    p.add_argument("--correctness-test", action="store_true")
+    p.add_argument("--cut-len", type=int, default=4)
+    p.add_argument("--prompt-filename", default=None, help="correctness test: a JSON list of token-id prompts")
+    p.add_argument("--profile", action="store_true", help="a torch profiler trace per configuration")
+    p.add_argument("--profile-filename-prefix", default="profile")
+    ns = p.parse_args(argv)
     sa = ServerArgs.from_cli_args(ns)
+    if ns.correctness_test:
+        prompts = None
+        if ns.prompt_filename:
+            with open(ns.prompt_filename) as f:
+                prompts = json.load(f)
+        return [correctness_test(sa, ns.cut_len, ns.output_len[0], prompts)]
+    out = []
     for bs in ns.batch_size:
         for il in ns.input_len:
             for ol in ns.output_len:
-                print(json.dumps(run_one_batch(sa, bs, il, ol)))
+                if ns.profile:
+                    from torch.profiler import ProfilerActivity, profile
+                    acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+                    with profile(activities=acts) as prof:
+                        rec = run_one_batch(sa, bs, il, ol, ns.log_decode_step)
+                    name = f"{ns.profile_filename_prefix}_batch{bs}_input{il}_output{ol}.trace.json"
+                    prof.export_chrome_trace(name)
+                    rec["profile"] = name
+                else:
+                    rec = run_one_batch(sa, bs, il, ol, ns.log_decode_step)
+                rec["run_name"] = ns.run_name
+                print(json.dumps(rec))
+                out.append(rec)
+                if ns.result_filename:
+                    with open(ns.result_filename, "a") as f:
+                        f.write(json.dumps(rec) + "\n")
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -638,3 +638,25 @@ def test_offline_throughput_bench_on_a_tiny_model(tmp_path):
     assert r["successful_requests"] == 4 and r["total_input_tokens"] == 4 * 40
     recs = [json.loads(l) for l in out.read_text().splitlines()]
     assert [x["dataset_name"] for x in recs] == ["random", "generated-shared-prefix"]
+
+
+def test_bench_one_batch_options_and_correctness_test(tmp_path, capsys):
+    """`bench_one_batch`: result file with the run name, decode-step logging, and `--correctness-test` (prefill in
+    one piece against a cached prefix plus the rest)."""
+    import json
+    from sglang_jax_b200 import bench_one_batch as b1
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils.tiny_models import write_tiny_qwen3_checkpoint
+    ckpt = write_tiny_qwen3_checkpoint(str(tmp_path / "m"))
+    common = ["--model-path", ckpt, "--device", "cpu", "--dtype", "float32", "--skip-tokenizer-init",
+              "--enable-single-process", "--page-size", "16", "--max-total-tokens", "4096", "--log-level", "error"]
+    ps.reset_state()
+    out = tmp_path / "one.jsonl"
+    recs = b1.main(common + ["--batch-size", "2", "--input-len", "32", "--output-len", "4", "--run-name", "r1",
+                             "--result-filename", str(out), "--log-decode-step", "2"])
+    assert recs[0]["run_name"] == "r1" and recs[0]["batch_size"] == 2 and recs[0]["median_decode_latency_s"] > 0
+    assert "decode step 2:" in capsys.readouterr().out
+    assert json.loads(out.read_text().splitlines()[0])["input_len"] == 32
+    ps.reset_state()
+    res = b1.main(common + ["--correctness-test", "--cut-len", "16", "--output-len", "5"])[0]
+    assert res["passed"] and max(res["split_cached"]) == 16 and all(len(o) == 5 for o in res["whole"])
