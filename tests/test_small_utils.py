@@ -660,3 +660,53 @@ def test_bench_one_batch_options_and_correctness_test(tmp_path, capsys):
     ps.reset_state()
     res = b1.main(common + ["--correctness-test", "--cut-len", "16", "--output-len", "5"])[0]
     assert res["passed"] and max(res["split_cached"]) == 16 and all(len(o) == 5 for o in res["whole"])
+
+
+def test_bench_one_batch_server_against_a_fake_server(tmp_path, capsys):
+    """`bench_one_batch_server`: streamed batches against a recording server, unequal prompt lengths, report, file."""
+    import asyncio
+    import json
+    import threading
+    import time
+    from aiohttp import web
+    from sglang_jax_b200 import bench_one_batch_server as b
+    from sglang_jax_b200.utils.common import get_free_port
+    seen = []
+
+    async def generate(request):
+        body = await request.json()
+        seen.append(body)
+        resp = web.StreamResponse(headers={"Content-Type": "text/event-stream"})
+        await resp.prepare(request)
+        for i in range(body["sampling_params"]["max_new_tokens"]):
+            await resp.write(("data: " + json.dumps({"meta_info": {"completion_tokens": i + 1}}) + "\n\n").encode())
+        await resp.write(b"data: [DONE]\n\n")
+        return resp
+
+    port = get_free_port()
+    loop = asyncio.new_event_loop()
+    app = web.Application()
+    app.router.add_post("/generate", generate)
+    runner = web.AppRunner(app)
+
+    def serve():
+        asyncio.set_event_loop(loop)
+        loop.run_until_complete(runner.setup())
+        loop.run_until_complete(web.TCPSite(runner, "127.0.0.1", port).start())
+        loop.run_forever()
+
+    t = threading.Thread(target=serve, daemon=True)
+    t.start()
+    time.sleep(0.5)
+    out = tmp_path / "srv.jsonl"
+    try:
+        rows = b.main(["--base-url", f"http://127.0.0.1:{port}", "--batch-size", "2", "4", "--input-len", "40",
+                       "--output-len", "3", "--input-len-step-percentage", "0.5", "--run-name", "s1", "--show-report",
+                       "--result-filename", str(out), "--return-logprob"])
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+        t.join(timeout=5)
+    assert [r["batch_size"] for r in rows] == [2, 4] and all(r["run_name"] == "s1" and r["ttft_s"] for r in rows)
+    assert len(seen) == 3 and len(seen[0]["input_ids"]) == 1                      # the warm-up request comes first
+    assert [len(x) for x in seen[2]["input_ids"]] == [40, 35, 30, 25] and seen[2]["return_logprob"] is True
+    assert "out tok/s" in capsys.readouterr().out and len(out.read_text().splitlines()) == 2
