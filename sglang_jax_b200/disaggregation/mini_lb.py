@@ -9,6 +9,7 @@ engine in `bootstrap_host` / `bootstrap_port`; it comes from the bootstrap regis
 from __future__ import annotations
 
 import asyncio
+import contextlib
 import itertools
 import json
 import logging
@@ -103,12 +104,26 @@ class MiniLoadBalancer:
         dec = dict(body, bootstrap_room=rooms)
         if p.transfer_addr:
             host, port = p.transfer_addr.rsplit(":", 1)
+            host = self.args.prefill_bootstrap_host or host
             dec["bootstrap_host"] = [host] * n if n else host
             dec["bootstrap_port"] = [int(port)] * n if n else int(port)
         return pre, dec
 
+    def _gate(self):
+        """`--max-concurrent-requests`: one semaphore for the router (created on the serving loop, on first use)."""
+        n = int(getattr(self.args, "max_concurrent_requests", 0) or 0)
+        if n <= 0:
+            return contextlib.nullcontext()
+        if getattr(self, "_sem", None) is None:
+            self._sem = asyncio.Semaphore(n)
+        return self._sem
+
     async def forward(self, path: str, body: dict):
         """Returns `(status, json)` for non-streaming bodies."""
+        async with self._gate():
+            return await self._forward(path, body)
+
+    async def _forward(self, path: str, body: dict):
         p, d = self.pick()
         pre, dec = self._augment(body, p, new_room())
         p.inflight += 1
@@ -129,6 +144,11 @@ class MiniLoadBalancer:
 
     async def forward_stream(self, path: str, body: dict):
         """Async generator of raw SSE chunks from the decode engine."""
+        async with self._gate():
+            async for chunk in self._forward_stream(path, body):
+                yield chunk
+
+    async def _forward_stream(self, path: str, body: dict):
         p, d = self.pick()
         pre, dec = self._augment(body, p, new_room())
         p.inflight += 1

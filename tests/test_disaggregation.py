@@ -215,6 +215,37 @@ def test_router_policies_and_room_fanout():
     empty = MiniLoadBalancer(RouterArgs(decode_urls=["http://d0"]))
     with pytest.raises(RuntimeError):
         empty.pick()
+    # --prefill-bootstrap-host rewrites the host the decode engine is told to pull from
+    lb.args.prefill_bootstrap_host = "pod-7.internal"
+    _, dec = lb._augment({"text": "hi"}, ep, 8)
+    assert dec["bootstrap_host"] == "pod-7.internal" and dec["bootstrap_port"] == 30001
+    # --max-concurrent-requests: a gate of that many slots; command lines of the reference launcher parse
+    import argparse
+    import asyncio
+    ap = argparse.ArgumentParser()
+    RouterArgs.add_cli_args(ap)
+    ns = ap.parse_args(["--decode", "http://d0", "--mini-lb", "--pd-disaggregation", "--request-timeout-secs", "30",
+                        "--max-concurrent-requests", "2", "--prefill-bootstrap-host", "h"])
+    ra = RouterArgs.from_cli_args(ns)
+    assert ra.request_timeout == 30.0 and ra.max_concurrent_requests == 2 and ra.prefill_bootstrap_host == "h"
+    gated = MiniLoadBalancer(ra)
+    running, peak = 0, 0
+
+    async def fake(path, body):
+        nonlocal running, peak
+        running += 1
+        peak = max(peak, running)
+        await asyncio.sleep(0.02)
+        running -= 1
+        return 200, {}
+
+    gated._forward = fake
+
+    async def burst():
+        await asyncio.gather(*[gated.forward("/generate", {}) for _ in range(6)])
+
+    asyncio.run(burst())
+    assert peak == 2
 
 
 def test_end_to_end_prefill_transfer_decode_matches_single_engine(tmp_path):
