@@ -216,7 +216,8 @@ async def start_profile_async(obj: ProfileReqInput | None = None):
     try:
         await _global_state.tokenizer_manager.start_profile(
             output_dir=obj.output_dir, start_step=obj.start_step, num_steps=obj.num_steps,
-            profile_by_stage=bool(obj.profile_by_stage), profile_stages=obj.profile_stages)
+            profile_by_stage=bool(obj.profile_by_stage), profile_stages=obj.profile_stages,
+            activities=obj.activities, profile_name=obj.profile_name)
     except RuntimeError as e:
         return _err(str(e))
     return Response(content="Start profiling.\n", status_code=200)

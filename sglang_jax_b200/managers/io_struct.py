@@ -474,6 +474,8 @@ class ProfileReqInput:
     stage_id: int | None = None
     profile_by_stage: bool | None = False
     profile_stages: list[str] | None = None
+    activities: list[str] | None = None      # subset of CPU, GPU, MEM (default CPU + GPU)
+    profile_name: str | None = None          # file-name stem of the traces (default: a time stamp)
 
 
 class ProfileReqType(Enum):
@@ -494,6 +496,7 @@ class ProfileReq:
     stage_id: int | None = None
     profile_by_stage: bool | None = False
     profile_stages: list[str] | None = None
+    activities: list[str] | None = None
 
 
 @dataclass

@@ -71,6 +71,7 @@ class SchedulerProfilerMixin:
         self.profile_id = req.profile_id or str(int(time.time()))
         self.profile_steps_left = req.num_steps
         self.profile_start_step = req.start_step
+        self.profile_activities = [a.upper() for a in (req.activities or ["CPU", "GPU"])]
         if req.profile_by_stage:
             self.profile_stage_trigger = _StageBasedTrigger(req.profile_stages or ["prefill", "decode"],
                                                             req.num_steps or 5)
@@ -83,10 +84,15 @@ class SchedulerProfilerMixin:
 
     def _begin_trace(self):
         import torch
-        acts = [torch.profiler.ProfilerActivity.CPU]
-        if torch.cuda.is_available():
+        want = getattr(self, "profile_activities", None) or ["CPU", "GPU"]
+        acts = [torch.profiler.ProfilerActivity.CPU] if "CPU" in want or not torch.cuda.is_available() else []
+        if "GPU" in want and torch.cuda.is_available():
             acts.append(torch.profiler.ProfilerActivity.CUDA)
-        self.profiler = torch.profiler.profile(activities=acts, record_shapes=False, with_stack=False)
+        mem = "MEM" in want
+        if mem and torch.cuda.is_available():
+            torch.cuda.memory._record_memory_history(max_entries=100000)     # allocator history for memory_viz
+        self.profiler = torch.profiler.profile(activities=acts or [torch.profiler.ProfilerActivity.CPU],
+                                               record_shapes=False, with_stack=False, profile_memory=mem)
         self.profiler.start()
 
     def _end_trace(self, suffix: str = ""):
@@ -97,6 +103,12 @@ class SchedulerProfilerMixin:
         self.profiler.export_chrome_trace(path)
         logger.info("Profiler trace written to %s", path)
         self.profiler = None
+        import torch
+        if "MEM" in (getattr(self, "profile_activities", None) or []) and torch.cuda.is_available():
+            snap = os.path.join(self.profile_output_dir, f"{self.profile_id}{suffix}-TP-{self.tp_rank}-memory.pickle")
+            torch.cuda.memory._dump_snapshot(snap)
+            torch.cuda.memory._record_memory_history(enabled=None)
+            logger.info("Memory snapshot written to %s", snap)
 
     def stop_profile(self) -> ProfileReqOutput:
         if not self.profile_in_progress:

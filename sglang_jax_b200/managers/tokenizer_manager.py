@@ -419,10 +419,11 @@ class TokenizerManager:
         return [dataclasses.asdict(r) for r in await self.get_load_communicator(GetLoadReqInput())]
 
     async def start_profile(self, output_dir=None, start_step=None, num_steps=None, profile_by_stage=False,
-                            profile_stages=None, **kw):
+                            profile_stages=None, activities=None, profile_name=None, **kw):
         self.auto_create_handle_loop()
         req = ProfileReq(ProfileReqType.START_PROFILE, output_dir, start_step, num_steps,
-                         profile_id=str(time.time()), profile_by_stage=profile_by_stage, profile_stages=profile_stages)
+                         profile_id=profile_name or str(time.time()), profile_by_stage=profile_by_stage,
+                         profile_stages=profile_stages, activities=activities)
         res = (await self.profile_communicator(req))[0]
         if not res.success:
             raise RuntimeError(res.message)

@@ -197,3 +197,17 @@ def test_reasoning_parser_streaming():
     assert ReasoningParser("deepseek-r1").parse_non_stream("abc</think>x") == ("abc", "x")
     with pytest.raises(ValueError):
         ReasoningParser("unknown-model")
+
+
+def test_profile_endpoints_honour_name_and_activities(client, tmp_path):
+    """`/start_profile` with a run name and an activity list (what `python -m sglang_jax_b200.profiler --profile-name
+    ... --no-gpu --mem` sends): the trace file carries the name; stop is refused when nothing runs."""
+    import glob
+    out = str(tmp_path / "prof")
+    r = client.post("/start_profile", json={"output_dir": out, "profile_name": "run-a", "activities": ["CPU", "MEM"]})
+    assert r.status_code == 200
+    assert client.get("/profile_status").status_code == 200
+    client.post("/generate", json={"input_ids": [5, 6, 7], "sampling_params": {"max_new_tokens": 3, "temperature": 0}})
+    assert client.post("/stop_profile").status_code == 200
+    assert glob.glob(out + "/run-a*-TP-0.trace.json.gz")
+    assert client.post("/stop_profile").status_code != 200
