@@ -90,6 +90,8 @@ class ModelRunner:
                               dispatch_algorithm=getattr(server_args, "ep_dispatch_algorithm", None))
         self.model = loader.load_model(model_config, self.device, self.quant_config)
         configure_moe_runtime()          # later models (a draft head) start from the defaults
+        from ..utils.debug_utils import print_parameter_shardings
+        print_parameter_shardings(self.model)       # SGLANG_FRAMEWORK_LOG_LEVEL >= 3 only
         if not is_draft_worker:
             # `--moe-backend fused` / `fused_v2` / `auto`: token all-to-all between the expert-parallel ranks
             from ..layers import fused_ep_moe

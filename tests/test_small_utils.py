@@ -710,3 +710,30 @@ def test_bench_one_batch_server_against_a_fake_server(tmp_path, capsys):
     assert len(seen) == 3 and len(seen[0]["input_ids"]) == 1                      # the warm-up request comes first
     assert [len(x) for x in seen[2]["input_ids"]] == [40, 35, 30, 25] and seen[2]["return_logprob"] is True
     assert "out tok/s" in capsys.readouterr().out and len(out.read_text().splitlines()) == 2
+
+
+def test_framework_debug_listing_of_parameters(monkeypatch, capsys):
+    """`SGLANG_FRAMEWORK_LOG_LEVEL>=3`: every parameter with its local shape, dtype and tensor-parallel slice."""
+    import torch
+    from sglang_jax_b200.layers.linear import ColumnParallelLinear
+    from sglang_jax_b200.parallel import state as ps
+    from sglang_jax_b200.utils import debug_utils as du
+    ps.reset_state()
+    m = torch.nn.Module()
+    m.proj = ColumnParallelLinear(8, 16, False, torch.float32)
+    lines = du.parameter_shardings(m)
+    assert lines == ["proj.weight: shape=(16, 8) dtype=float32 device=cpu replicated"]
+    monkeypatch.setenv("SGLANG_FRAMEWORK_LOG_LEVEL", "0")
+    du.print_parameter_shardings(m)
+    assert capsys.readouterr().out == ""
+    monkeypatch.setenv("SGLANG_FRAMEWORK_LOG_LEVEL", "3")
+    du.print_parameter_shardings(m)
+    assert "proj.weight" in capsys.readouterr().out
+
+    @du.log_shapes("f")
+    def f(x):
+        return x.sum(0), 3
+
+    f(torch.zeros(2, 5))
+    out = capsys.readouterr().out
+    assert "f input[0]: (2, 5) float32 cpu" in out and "f output[0]: (5,) float32 cpu" in out
