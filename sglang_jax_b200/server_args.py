@@ -31,8 +31,8 @@ MOE_BACKENDS = ["epmoe", "fused", "fused_v2", "auto"]
 SPEC_ALGOS = [None, "EAGLE", "EAGLE3", "NEXTN", "STANDALONE", "DFLASH"]
 
 
-def _m(help: str = "", choices=None, aliases=()) -> dict:
-    return {"help": help, "choices": choices, "aliases": tuple(aliases)}
+def _m(help: str = "", choices=None, aliases=(), const=None) -> dict:
+    return {"help": help, "choices": choices, "aliases": tuple(aliases), "const": const}
 
 
 @dataclass
@@ -84,7 +84,10 @@ class ServerArgs:
     device: str | None = None
     device_indexes: list[int] | None = None
     # --- PD disaggregation (launcher-level) --------------------------------------
-    pd_disaggregation: str = ""
+    pd_disaggregation: str = field(default="", metadata=_m(
+        const="local", help="in-node P/D split behind one front door: prefill and decode engines on slices of the "
+                            "devices (`local`; `pathways`, the reference's name for its in-process split, is "
+                            "accepted as a synonym)"))
     pd_prefill_mem_fraction: float = 0.85
     pd_decode_mem_fraction: float = 0.85
     pd_prefill_max_tokens: int = 20480
@@ -338,6 +341,8 @@ class ServerArgs:
                 ch = f.metadata.get("choices")
                 if ch:
                     kw["choices"] = [c for c in ch if c is not None]
+                if f.metadata.get("const") is not None:
+                    kw["nargs"], kw["const"] = "?", f.metadata["const"]     # a bare flag takes this value
             parser.add_argument(*names, **kw)
 
     @classmethod

@@ -138,6 +138,11 @@ def test_server_args_flag_parity_and_defaults():
     b = ServerArgs.from_cli(["--model-path", "m", "--tp", "4", "--dp-size", "2", "--device", "cpu", "--page-size", "64",
                              "--chunked-prefill-size", "8192", "--enable-mixed-chunk", "--lora-paths", "a", "b"])
     assert b.tp_size == 4 and b.tensor_size == 2 and b.enable_mixed_chunk and b.lora_paths == ["a", "b"] and b.enable_lora
+    # a bare --pd-disaggregation selects the in-node launcher, like the reference's bare flag selects its split
+    assert ServerArgs.from_cli(["--model-path", "m", "--pd-disaggregation", "--page-size", "16"]).pd_disaggregation == "local"
+    assert ServerArgs.from_cli(["--model-path", "m", "--pd-disaggregation", "pathways", "--page-size", "16"]
+                               ).pd_disaggregation == "pathways"
+    assert ServerArgs.from_cli(["--model-path", "m"]).pd_disaggregation == ""
     with pytest.raises(AssertionError):
         ServerArgs(model_path="m", device="cpu", page_size=48, chunked_prefill_size=100)
     with pytest.raises(AssertionError):
